@@ -1,0 +1,128 @@
+"""ctypes binding of libhmc_b200.so (the C ABI declared in include/hmc_b200.h).
+
+The library is the only compute path of this package: there is no CPU or PyTorch fallback.
+Loading fails loudly when the shared library has not been built.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_char_p, c_double, c_float, c_int32, c_int64, c_uint64, c_void_p
+from pathlib import Path
+
+import torch
+
+_PACKAGE = Path(__file__).resolve().parent
+LIBRARY_PATH = _PACKAGE / "libhmc_b200.so"
+
+HMC_GEMM_RAGGED_M = 0
+HMC_GEMM_RAGGED_K = 1
+HMC_MAJOR_K = 0
+HMC_MAJOR_MN = 1
+HMC_EPI_STORE_BF16 = 0
+HMC_EPI_STORE_F32 = 1
+HMC_EPI_SWIGLU = 2
+HMC_EPI_SWIGLU_GRAD = 3
+HMC_STATUS_WORDS = 8
+
+STATUS_NAMES = {
+    0: "ok",
+    1: "pipeline wait timed out",
+    2: "rows of an expert never arrived",
+    3: "a peer never published ready",
+    4: "an index was out of range",
+}
+
+
+class HmcError(RuntimeError):
+    """A check inside the native library failed."""
+
+
+class GroupedGemmArgs(ctypes.Structure):
+    """Mirror of ``hmc_grouped_gemm_args``."""
+
+    _fields_ = [
+        ("mode", c_int32),
+        ("a_major", c_int32),
+        ("b_major", c_int32),
+        ("epilogue", c_int32),
+        ("groups", c_int32),
+        ("max_ctas", c_int32),
+        ("rows", c_int64),
+        ("m", c_int64),
+        ("n", c_int64),
+        ("k", c_int64),
+        ("a", c_void_p),
+        ("b", c_void_p),
+        ("c", c_void_p),
+        ("aux", c_void_p),
+        ("group_ends", c_void_p),
+        ("ready_counters", c_void_p),
+        ("ready_budget_ns", c_uint64),
+        ("status", c_void_p),
+    ]
+
+
+_LIB: ctypes.CDLL | None = None
+
+# name -> (restype, argtypes); every symbol include/hmc_b200.h declares.
+_P = c_void_p
+_I = c_int32
+_L = c_int64
+_F = c_float
+_D = c_double
+SIGNATURES: dict[str, tuple] = {
+    "hmc_last_error": (c_char_p, []),
+    "hmc_abi_version": (_I, []),
+    "hmc_mega_moe_transport_version": (_I, []),
+    "hmc_worker_queue_layout_version": (_I, []),
+    "hmc_grouped_gemm": (_I, [ctypes.POINTER(GroupedGemmArgs), _P]),
+}
+
+
+def load() -> ctypes.CDLL:
+    """Load the native library once; raise if it is missing (no fallback exists)."""
+    global _LIB  # pylint: disable=global-statement
+    if _LIB is not None:
+        return _LIB
+    if not LIBRARY_PATH.exists():
+        raise HmcError(
+            f"{LIBRARY_PATH} is missing: build it with `python -m hyper_multicore_b200.csrc.build` "
+            "(this package has no CPU or PyTorch fallback path)."
+        )
+    lib = ctypes.CDLL(str(LIBRARY_PATH))
+    for name, (restype, argtypes) in SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.restype = restype
+        fn.argtypes = argtypes
+    _LIB = lib
+    return lib
+
+
+def check(code: int) -> None:
+    """Turn a negative return code into HmcError carrying the library's message."""
+    if code != 0:
+        message = load().hmc_last_error().decode("utf-8", "replace")
+        raise HmcError(f"hmc error {code}: {message}")
+
+
+def ptr(tensor: torch.Tensor | None) -> int | None:
+    """Device address of a tensor, or NULL."""
+    return None if tensor is None else tensor.data_ptr()
+
+
+def stream_ptr(device: torch.device | None = None) -> int:
+    """cudaStream_t of torch's current stream on ``device``."""
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def new_status(device: torch.device) -> torch.Tensor:
+    """Zeroed device status words for kernels with bounded waits."""
+    return torch.zeros(HMC_STATUS_WORDS, dtype=torch.int32, device=device)
+
+
+def raise_on_status(status: torch.Tensor, what: str) -> None:
+    """Synchronising check of device status words (used by tests and debug paths)."""
+    words = status.tolist()
+    if words[0] != 0:
+        raise HmcError(f"{what}: device status {words[0]} ({STATUS_NAMES.get(words[0], '?')}), detail {words[1:4]}")

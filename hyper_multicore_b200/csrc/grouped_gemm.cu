@@ -1,0 +1,658 @@
+// Persistent grouped GEMM for the MoE expert FFN on sm_100a: TMA-fed shared-memory ring,
+// tcgen05.mma with FP32 accumulators in TMEM (two accumulator stages), fused epilogues.
+//
+// Replaces the reference's per-expert Cube tasks: GMM1/GMM2 (ops/hyper_mega_moe/op_kernel/
+// worker_kernel.cpp:225-299, ops/common/mega_moe/adapters/arch35/gmm/bf16_worker.h:44-85), the
+// SwiGLU vector task (worker_kernel.cpp:122-223), the backward GEMMs and SwiGLUGrad
+// (ops/hyper_mega_moe_grad/op_kernel/worker_kernel.cpp:164-195), and the "zero dW of cold
+// experts" rule (bf16_worker.h:62-75).
+//
+// One CTA per SM, 192 threads: warp 0 = TMA producer, warp 1 = MMA issuer (+TMEM owner),
+// warps 2..5 = epilogue (one TMEM lane quarter each). Tiles are 128 x 256 x 64.
+//
+//  RAGGED_M : C[r0:r1, :] = A[r0:r1, :] * B_g      rows of group g are [ends[g-1], ends[g])
+//  RAGGED_K : C_g = A[r0:r1, :]^T * B[r0:r1, :]    contraction over the group's rows
+#include <cuda.h>
+
+#include "common.cuh"
+#include "sm100.cuh"
+
+namespace hmc {
+namespace {
+
+using namespace sm100;
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 64;
+constexpr int STAGES = 4;
+constexpr int ACC_STAGES = 2;
+constexpr int A_TILE_BYTES = BM * BK * 2;  // 16 KiB
+constexpr int B_TILE_BYTES = BN * BK * 2;  // 32 KiB
+constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
+constexpr int CHUNK_BYTES = 64 * BK * 2;  // one 64-wide MN-major chunk: BK rows of 128 B
+constexpr int NUM_THREADS = 192;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+constexpr uint32_t TMEM_COLS = 512;
+constexpr uint32_t SWIZZLE_128B = 2;
+
+constexpr uint64_t PIPE_BUDGET_NS = 4ull * 1000 * 1000 * 1000;  // intra-kernel barrier waits
+
+struct Params {
+  int mode;      // HMC_GEMM_RAGGED_M / HMC_GEMM_RAGGED_K
+  int epilogue;  // HMC_EPI_*
+  int groups;
+  int m;  // RAGGED_K: rows of C per group. RAGGED_M: unused
+  int n;  // logical N of the accumulator (SWIGLU: I, the width of one half)
+  int k;  // RAGGED_M: contraction length. RAGGED_K: unused
+  int n_tiles;
+  int m_tiles;  // RAGGED_K only
+  int ldc;      // row stride of C in elements
+  int ld_aux;   // row stride of aux in elements
+  long long rows;
+  const long long* group_ends;
+  void* c;
+  void* aux;
+  const int* ready_counters;  // optional, RAGGED_M: per-group arrival counters (rows landed)
+  unsigned long long ready_budget_ns;
+  int* status;
+};
+
+struct Tile {
+  int group;
+  int m_idx;
+  int n_idx;
+  long long row0;  // first row of the group in the ragged dimension
+  long long row1;  // one past the last row of the group
+};
+
+// Walks the static tile order. Tile indices only grow for a given CTA, so the group cursor only
+// moves forward and every role (producer, MMA, epilogue) reproduces the same sequence.
+struct TileWalker {
+  const Params& p;
+  int group = 0;
+  long long base = 0;  // first linear tile index of `group`
+  long long row0 = 0;
+  long long row1 = 0;
+  int tiles_in_group = 0;
+
+  __device__ explicit TileWalker(const Params& params) : p(params) { load_group(); }
+
+  __device__ void load_group() {
+    if (group >= p.groups) {
+      tiles_in_group = 0;
+      return;
+    }
+    row0 = group == 0 ? 0 : p.group_ends[group - 1];
+    row1 = p.group_ends[group];
+    if (p.mode == HMC_GEMM_RAGGED_M) {
+      long long rows = row1 - row0;
+      tiles_in_group = static_cast<int>((rows + BM - 1) / BM) * p.n_tiles;
+    } else {
+      tiles_in_group = p.m_tiles * p.n_tiles;
+    }
+  }
+
+  __device__ bool get(long long idx, Tile& t) {
+    while (group < p.groups && idx >= base + tiles_in_group) {
+      base += tiles_in_group;
+      ++group;
+      load_group();
+    }
+    if (group >= p.groups) return false;
+    int local = static_cast<int>(idx - base);
+    int mt = p.mode == HMC_GEMM_RAGGED_M ? tiles_in_group / p.n_tiles : p.m_tiles;
+    t.group = group;
+    t.m_idx = local % mt;
+    t.n_idx = local / mt;
+    t.row0 = row0;
+    t.row1 = row1;
+    return true;
+  }
+};
+
+__device__ __forceinline__ int k_iterations(const Params& p, const Tile& t) {
+  if (p.mode == HMC_GEMM_RAGGED_M) return (p.k + BK - 1) / BK;
+  return static_cast<int>((t.row1 - t.row0 + BK - 1) / BK);
+}
+
+__device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)); }
+
+template <int A_MAJOR, int B_MAJOR>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                    const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* full_bar = bars;                                 // [STAGES]
+  uint64_t* empty_bar = bars + STAGES;                       // [STAGES]
+  uint64_t* acc_full_bar = bars + 2 * STAGES;                // [ACC_STAGES]
+  uint64_t* acc_empty_bar = bars + 2 * STAGES + ACC_STAGES;  // [ACC_STAGES]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 2 * ACC_STAGES);
+  volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int s = 0; s < ACC_STAGES; ++s) {
+      mbar_init(&acc_full_bar[s], 1);
+      mbar_init(&acc_empty_bar[s], 4);  // one arrival per epilogue warp
+    }
+    *abort_word = 0;
+    mbar_fence_init();
+    prefetch_tensormap(&tm_a);
+    prefetch_tensormap(&tm_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ======================================================================== TMA producer
+    if (lane == 0) {
+      TileWalker walker(p);
+      Tile t;
+      int stage = 0;
+      uint32_t phase = 0;
+      int ready_group = -1;
+      bool ok = true;
+      for (long long idx = blockIdx.x; ok && walker.get(idx, t); idx += gridDim.x) {
+        const int kiters = k_iterations(p, t);
+        if (p.ready_counters != nullptr && t.group != ready_group) {
+          // Rows of this group are written by peers; wait until all of them have landed, then
+          // order the async-proxy (TMA) reads after the acquire.
+          int seen = 0;
+          const int need = static_cast<int>(t.row1 - t.row0);
+          if (!wait_counter_ge(p.ready_counters + t.group, need, p.ready_budget_ns, &seen)) {
+            report_status(p.status, HMC_STATUS_TIMEOUT_ARRIVAL, t.group, need, seen);
+            *abort_word = 1;
+            ok = false;
+            break;
+          }
+          fence_proxy_async_all();
+          ready_group = t.group;
+        }
+        for (int kb = 0; kb < kiters; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_word, PIPE_BUDGET_NS)) {
+            report_status(p.status, HMC_STATUS_TIMEOUT_PIPELINE, 0, stage, kb);
+            ok = false;
+            break;
+          }
+          uint8_t* a_dst = smem + stage * STAGE_BYTES;
+          uint8_t* b_dst = a_dst + A_TILE_BYTES;
+          mbar_arrive_expect_tx(&full_bar[stage], STAGE_BYTES);
+          if (p.mode == HMC_GEMM_RAGGED_M) {
+            const int row = static_cast<int>(t.row0) + t.m_idx * BM;
+            // A is [rows, K] row-major: K-major operand, one 64 x 128 box.
+            tma_load_2d(a_dst, &tm_a, &full_bar[stage], kb * BK, row);
+            if (p.epilogue == HMC_EPI_SWIGLU) {
+              // Accumulator columns [0,128) = gate columns, [128,256) = matching up columns.
+              const int g0 = t.n_idx * (BN / 2);
+              const int u0 = p.n + g0;
+              if (B_MAJOR == HMC_MAJOR_MN) {
+                tma_load_3d(b_dst + 0 * CHUNK_BYTES, &tm_b, &full_bar[stage], g0, kb * BK, t.group);
+                tma_load_3d(b_dst + 1 * CHUNK_BYTES, &tm_b, &full_bar[stage], g0 + 64, kb * BK, t.group);
+                tma_load_3d(b_dst + 2 * CHUNK_BYTES, &tm_b, &full_bar[stage], u0, kb * BK, t.group);
+                tma_load_3d(b_dst + 3 * CHUNK_BYTES, &tm_b, &full_bar[stage], u0 + 64, kb * BK, t.group);
+              } else {
+                tma_load_3d(b_dst, &tm_b, &full_bar[stage], kb * BK, g0, t.group);
+                tma_load_3d(b_dst + B_TILE_BYTES / 2, &tm_b, &full_bar[stage], kb * BK, u0, t.group);
+              }
+            } else {
+              const int n0 = t.n_idx * BN;
+              if (B_MAJOR == HMC_MAJOR_MN) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+                  tma_load_3d(b_dst + c * CHUNK_BYTES, &tm_b, &full_bar[stage], n0 + c * 64, kb * BK,
+                              t.group);
+              } else {
+                tma_load_3d(b_dst, &tm_b, &full_bar[stage], kb * BK, n0, t.group);
+                tma_load_3d(b_dst + B_TILE_BYTES / 2, &tm_b, &full_bar[stage], kb * BK, n0 + BN / 2,
+                            t.group);
+              }
+            }
+          } else {
+            // Both operands are [rows, width] row-major, contracted over rows: MN-major chunks.
+            const int row = static_cast<int>(t.row0) + kb * BK;
+            const int m0 = t.m_idx * BM;
+            const int n0 = t.n_idx * BN;
+#pragma unroll
+            for (int c = 0; c < 2; ++c)
+              tma_load_2d(a_dst + c * CHUNK_BYTES, &tm_a, &full_bar[stage], m0 + c * 64, row);
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+              tma_load_2d(b_dst + c * CHUNK_BYTES, &tm_b, &full_bar[stage], n0 + c * 64, row);
+          }
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ======================================================================== MMA issuer
+    TileWalker walker(p);
+    Tile t;
+    int stage = 0;
+    uint32_t phase = 0;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    constexpr uint32_t idesc = make_idesc_f32acc(1u, BM, BN, A_MAJOR, B_MAJOR);
+    // Descriptor strides. K-major: 8-row groups are 1024 B apart. MN-major: 64-wide chunks are
+    // CHUNK_BYTES apart (leading), 8-row k groups are 1024 B apart (stride).
+    constexpr uint32_t A_LBO = A_MAJOR == HMC_MAJOR_MN ? CHUNK_BYTES : 16;
+    constexpr uint32_t B_LBO = B_MAJOR == HMC_MAJOR_MN ? CHUNK_BYTES : 16;
+    constexpr uint32_t A_KSTEP = A_MAJOR == HMC_MAJOR_MN ? (16 * 128) >> 4 : 32 >> 4;
+    constexpr uint32_t B_KSTEP = B_MAJOR == HMC_MAJOR_MN ? (16 * 128) >> 4 : 32 >> 4;
+    for (long long idx = blockIdx.x; ok && walker.get(idx, t); idx += gridDim.x) {
+      const int kiters = k_iterations(p, t);
+      if (kiters == 0) continue;  // RAGGED_K cold group: the epilogue writes zeros on its own
+      if (!mbar_wait(&acc_empty_bar[acc], acc_phase ^ 1u, abort_word, PIPE_BUDGET_NS)) {
+        if (lane == 0) report_status(p.status, HMC_STATUS_TIMEOUT_PIPELINE, 1, acc, 0);
+        ok = false;
+        break;
+      }
+      tc_fence_after_sync();
+      const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * BN);
+      for (int kb = 0; kb < kiters; ++kb) {
+        if (!mbar_wait(&full_bar[stage], phase, abort_word, PIPE_BUDGET_NS)) {
+          if (lane == 0) report_status(p.status, HMC_STATUS_TIMEOUT_PIPELINE, 2, stage, kb);
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        uint8_t* a_src = smem + stage * STAGE_BYTES;
+        uint8_t* b_src = a_src + A_TILE_BYTES;
+        if (p.mode == HMC_GEMM_RAGGED_K) {
+          const long long left = t.row1 - (t.row0 + static_cast<long long>(kb) * BK);
+          if (left < BK) {
+            // Rows past the end of this group belong to the next group (or are unwritten):
+            // clear them in both operands. A 128-byte row stays one 128-byte line under the
+            // 128-byte swizzle, so whole lines can be cleared without undoing the swizzle.
+            const int valid = static_cast<int>(left);
+            const int lines = (BK - valid) * 6;  // 2 A chunks + 4 B chunks per row
+            const uint4 zero = make_uint4(0, 0, 0, 0);
+            for (int i = lane; i < lines * 8; i += 32) {
+              const int line = i >> 3;
+              const int chunk = line / (BK - valid);
+              const int row = valid + line % (BK - valid);
+              uint8_t* base = chunk < 2 ? a_src + chunk * CHUNK_BYTES : b_src + (chunk - 2) * CHUNK_BYTES;
+              *reinterpret_cast<uint4*>(base + row * 128 + (i & 7) * 16) = zero;
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+          }
+        }
+        if (lane == 0) {
+          uint64_t da = make_smem_desc(smem_u32(a_src), A_LBO, 1024, SWIZZLE_128B);
+          uint64_t db = make_smem_desc(smem_u32(b_src), B_LBO, 1024, SWIZZLE_128B);
+#pragma unroll
+          for (int ks = 0; ks < BK / 16; ++ks) {
+            umma_bf16(tmem_d, da, db, idesc, (kb > 0 || ks > 0) ? 1u : 0u);
+            da += A_KSTEP;
+            db += B_KSTEP;
+          }
+          umma_commit(&empty_bar[stage]);  // frees this smem slot once the MMAs have read it
+          if (kb == kiters - 1) umma_commit(&acc_full_bar[acc]);
+        }
+        __syncwarp();
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+      if (++acc == ACC_STAGES) {
+        acc = 0;
+        acc_phase ^= 1u;
+      }
+    }
+  } else {
+    // ======================================================================== epilogue
+    TileWalker walker(p);
+    Tile t;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    const int quarter = warp & 3;  // TMEM lane quarter this warp may read
+    const int row_in_tile = quarter * 32 + lane;
+    for (long long idx = blockIdx.x; ok && walker.get(idx, t); idx += gridDim.x) {
+      const int kiters = k_iterations(p, t);
+      long long out_row;
+      bool row_ok;
+      int col_base;
+      if (p.mode == HMC_GEMM_RAGGED_M) {
+        out_row = t.row0 + static_cast<long long>(t.m_idx) * BM + row_in_tile;
+        row_ok = out_row < t.row1;
+        col_base = p.epilogue == HMC_EPI_SWIGLU ? t.n_idx * (BN / 2) : t.n_idx * BN;
+      } else {
+        const int m = t.m_idx * BM + row_in_tile;
+        row_ok = m < p.m;
+        out_row = static_cast<long long>(t.group) * p.m + m;
+        col_base = t.n_idx * BN;
+      }
+      if (kiters == 0) {
+        // Cold group in RAGGED_K: exact zeros, no accumulator involved.
+        if (row_ok) {
+          if (p.epilogue == HMC_EPI_STORE_F32) {
+            float* dst = static_cast<float*>(p.c) + out_row * p.ldc + col_base;
+            for (int c = 0; c < BN && col_base + c < p.n; c += 4)
+              *reinterpret_cast<float4*>(dst + c) = make_float4(0.f, 0.f, 0.f, 0.f);
+          } else {
+            __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.c) + out_row * p.ldc + col_base;
+            for (int c = 0; c < BN && col_base + c < p.n; c += 8)
+              *reinterpret_cast<uint4*>(dst + c) = make_uint4(0, 0, 0, 0);
+          }
+        }
+        continue;
+      }
+      if (!mbar_wait(&acc_full_bar[acc], acc_phase, abort_word, PIPE_BUDGET_NS)) {
+        if (lane == 0) report_status(p.status, HMC_STATUS_TIMEOUT_PIPELINE, 3, acc, 0);
+        ok = false;
+        break;
+      }
+      tc_fence_after_sync();
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                             static_cast<uint32_t>(acc * BN);
+      if (p.epilogue == HMC_EPI_STORE_BF16) {
+        __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.c) + out_row * p.ldc + col_base;
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          uint32_t v[32];
+          tmem_ld_32x32(taddr + c, v);
+          tmem_ld_wait();
+          if (row_ok) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              if (col_base + c + j < p.n) {
+                uint4 o;
+                o.x = pack_bf16x2(__uint_as_float(v[j + 0]), __uint_as_float(v[j + 1]));
+                o.y = pack_bf16x2(__uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+                o.z = pack_bf16x2(__uint_as_float(v[j + 4]), __uint_as_float(v[j + 5]));
+                o.w = pack_bf16x2(__uint_as_float(v[j + 6]), __uint_as_float(v[j + 7]));
+                *reinterpret_cast<uint4*>(dst + c + j) = o;
+              }
+            }
+          }
+        }
+      } else if (p.epilogue == HMC_EPI_STORE_F32) {
+        float* dst = static_cast<float*>(p.c) + out_row * p.ldc + col_base;
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          uint32_t v[32];
+          tmem_ld_32x32(taddr + c, v);
+          tmem_ld_wait();
+          if (row_ok) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              if (col_base + c + j < p.n) {
+                *reinterpret_cast<float4*>(dst + c + j) =
+                    make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
+                                __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+              }
+            }
+          }
+        }
+      } else if (p.epilogue == HMC_EPI_SWIGLU) {
+        // U[row, col] = bf16(gate), U[row, I + col] = bf16(up), Act[row, col] =
+        // bf16(silu(gate_bf16) * up_bf16): the rounding points of the reference's golden
+        // (tests/common/multicore/fp32_expert_reference.py:22-25).
+        __nv_bfloat16* u_dst = static_cast<__nv_bfloat16*>(p.c) + out_row * p.ldc + col_base;
+        __nv_bfloat16* a_dst = static_cast<__nv_bfloat16*>(p.aux) + out_row * p.ld_aux + col_base;
+#pragma unroll 1
+        for (int c = 0; c < BN / 2; c += 32) {
+          uint32_t g[32], u[32];
+          tmem_ld_32x32(taddr + c, g);
+          tmem_ld_32x32(taddr + BN / 2 + c, u);
+          tmem_ld_wait();
+          if (row_ok) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              if (col_base + c + j < p.n) {
+                uint32_t go[4], uo[4], ao[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                  go[q] = pack_bf16x2(__uint_as_float(g[j + 2 * q]), __uint_as_float(g[j + 2 * q + 1]));
+                  uo[q] = pack_bf16x2(__uint_as_float(u[j + 2 * q]), __uint_as_float(u[j + 2 * q + 1]));
+                  const float2 gf = unpack_bf16x2(go[q]);
+                  const float2 uf = unpack_bf16x2(uo[q]);
+                  ao[q] = pack_bf16x2(silu_f(gf.x) * uf.x, silu_f(gf.y) * uf.y);
+                }
+                *reinterpret_cast<uint4*>(u_dst + c + j) = make_uint4(go[0], go[1], go[2], go[3]);
+                *reinterpret_cast<uint4*>(u_dst + p.n + c + j) = make_uint4(uo[0], uo[1], uo[2], uo[3]);
+                *reinterpret_cast<uint4*>(a_dst + c + j) = make_uint4(ao[0], ao[1], ao[2], ao[3]);
+              }
+            }
+          }
+        }
+      } else {  // HMC_EPI_SWIGLU_GRAD
+        // acc = dAct tile. With saved U = [gate | up] (aux): dU[:, col] = bf16(dA*up*s*(1+g(1-s))),
+        // dU[:, I + col] = bf16(dA*silu(g)), dA rounded to BF16 first
+        // (tests/common/multicore/fp32_expert_reference.py:29-33).
+        const __nv_bfloat16* u_src = static_cast<const __nv_bfloat16*>(p.aux) + out_row * p.ld_aux + col_base;
+        __nv_bfloat16* d_dst = static_cast<__nv_bfloat16*>(p.c) + out_row * p.ldc + col_base;
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          uint32_t v[32];
+          tmem_ld_32x32(taddr + c, v);
+          tmem_ld_wait();
+          if (row_ok) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              if (col_base + c + j < p.n) {
+                const uint4 gq = *reinterpret_cast<const uint4*>(u_src + c + j);
+                const uint4 uq = *reinterpret_cast<const uint4*>(u_src + p.n + c + j);
+                const uint32_t gw[4] = {gq.x, gq.y, gq.z, gq.w};
+                const uint32_t uw[4] = {uq.x, uq.y, uq.z, uq.w};
+                uint32_t dg[4], du[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                  const float2 gf = unpack_bf16x2(gw[q]);
+                  const float2 uf = unpack_bf16x2(uw[q]);
+                  const float da0 = bf16_round(__uint_as_float(v[j + 2 * q]));
+                  const float da1 = bf16_round(__uint_as_float(v[j + 2 * q + 1]));
+                  const float s0 = 1.0f / (1.0f + __expf(-gf.x));
+                  const float s1 = 1.0f / (1.0f + __expf(-gf.y));
+                  dg[q] = pack_bf16x2(da0 * uf.x * s0 * (1.0f + gf.x * (1.0f - s0)),
+                                      da1 * uf.y * s1 * (1.0f + gf.y * (1.0f - s1)));
+                  du[q] = pack_bf16x2(da0 * (gf.x * s0), da1 * (gf.y * s1));
+                }
+                *reinterpret_cast<uint4*>(d_dst + c + j) = make_uint4(dg[0], dg[1], dg[2], dg[3]);
+                *reinterpret_cast<uint4*>(d_dst + p.n + c + j) = make_uint4(du[0], du[1], du[2], du[3]);
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty_bar[acc]);
+      if (++acc == ACC_STAGES) {
+        acc = 0;
+        acc_phase ^= 1u;
+      }
+    }
+  }
+
+  // Teardown: everyone meets here (also after a time-out), then the allocating warp frees TMEM.
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ----------------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+    }
+  }
+  return fn;
+}
+
+// BF16 tensor of `rank` dims (dims[0] innermost), box with a 64-element (128-byte) inner extent.
+int make_map(CUtensorMap* out, const void* base, int rank, const cuuint64_t* dims, const cuuint32_t* box) {
+  EncodeTiledFn fn = encode_fn();
+  HMC_REQUIRE(fn != nullptr, HMC_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t strides[4];
+  cuuint64_t acc = 2;
+  for (int i = 0; i + 1 < rank; ++i) {
+    acc *= dims[i];
+    strides[i] = acc;
+  }
+  cuuint32_t elem_strides[5] = {1, 1, 1, 1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, static_cast<cuuint32_t>(rank),
+                  const_cast<void*>(base), dims, strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  HMC_REQUIRE(r == CUDA_SUCCESS, HMC_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return 0;
+}
+
+template <int A_MAJOR, int B_MAJOR>
+int launch(const CUtensorMap& ta, const CUtensorMap& tb, const Params& p, int grid, cudaStream_t stream) {
+  static bool configured = false;
+  auto kernel = grouped_gemm_kernel<A_MAJOR, B_MAJOR>;
+  if (!configured) {
+    HMC_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    configured = true;
+  }
+  kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, p);
+  HMC_LAUNCH_OK();
+  return 0;
+}
+
+}  // namespace
+}  // namespace hmc
+
+extern "C" int hmc_grouped_gemm(const hmc_grouped_gemm_args* args, void* stream_ptr) {
+  using namespace hmc;
+  HMC_REQUIRE(args != nullptr, HMC_ERR_INVALID, "hmc_grouped_gemm: null args");
+  const hmc_grouped_gemm_args& a = *args;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  HMC_REQUIRE(a.mode == HMC_GEMM_RAGGED_M || a.mode == HMC_GEMM_RAGGED_K, HMC_ERR_INVALID,
+              "hmc_grouped_gemm: unknown mode %d", a.mode);
+  HMC_REQUIRE(a.epilogue >= HMC_EPI_STORE_BF16 && a.epilogue <= HMC_EPI_SWIGLU_GRAD, HMC_ERR_INVALID,
+              "hmc_grouped_gemm: unknown epilogue %d", a.epilogue);
+  HMC_REQUIRE(a.groups > 0 && a.rows >= 0 && a.n > 0, HMC_ERR_INVALID,
+              "hmc_grouped_gemm: groups (%d) and n (%lld) must be positive, rows (%lld) non-negative",
+              a.groups, (long long)a.n, (long long)a.rows);
+  HMC_REQUIRE(a.rows < (1ll << 31) && a.n < (1ll << 31) && a.k < (1ll << 31) && a.m < (1ll << 31),
+              HMC_ERR_INVALID, "hmc_grouped_gemm: extents must fit in int32");
+  HMC_REQUIRE(a.a && a.b && a.c && a.group_ends, HMC_ERR_INVALID, "hmc_grouped_gemm: null tensor pointer");
+  HMC_REQUIRE(aligned16(a.a) && aligned16(a.b) && aligned16(a.c), HMC_ERR_INVALID,
+              "hmc_grouped_gemm: tensors must be 16-byte aligned");
+  HMC_REQUIRE(a.n % 8 == 0, HMC_ERR_INVALID, "hmc_grouped_gemm: n (%lld) must be a multiple of 8",
+              (long long)a.n);
+  if (a.rows == 0 && a.mode == HMC_GEMM_RAGGED_M) return 0;
+
+  Params p{};
+  p.mode = a.mode;
+  p.epilogue = a.epilogue;
+  p.groups = a.groups;
+  p.rows = a.rows;
+  p.group_ends = reinterpret_cast<const long long*>(a.group_ends);
+  p.c = a.c;
+  p.aux = a.aux;
+  p.ready_counters = a.ready_counters;
+  p.ready_budget_ns = a.ready_budget_ns ? a.ready_budget_ns : 10ull * 1000 * 1000 * 1000;
+  p.status = a.status;
+  p.n = static_cast<int>(a.n);
+
+  CUtensorMap ta, tb;
+  int rc;
+  if (a.mode == HMC_GEMM_RAGGED_M) {
+    HMC_REQUIRE(a.k > 0 && a.k % 8 == 0, HMC_ERR_INVALID,
+                "hmc_grouped_gemm: k (%lld) must be a positive multiple of 8", (long long)a.k);
+    HMC_REQUIRE(a.a_major == HMC_MAJOR_K, HMC_ERR_INVALID,
+                "hmc_grouped_gemm: RAGGED_M takes a row-major (K-major) A");
+    HMC_REQUIRE(a.epilogue != HMC_EPI_STORE_F32, HMC_ERR_INVALID,
+                "hmc_grouped_gemm: RAGGED_M writes BF16 outputs only");
+    p.k = static_cast<int>(a.k);
+    const bool swiglu = a.epilogue == HMC_EPI_SWIGLU;
+    const bool grad = a.epilogue == HMC_EPI_SWIGLU_GRAD;
+    HMC_REQUIRE(!(swiglu || grad) || (a.aux != nullptr && aligned16(a.aux)), HMC_ERR_INVALID,
+                "hmc_grouped_gemm: the SwiGLU epilogues need a 16-byte aligned aux tensor");
+    const long long b_cols = swiglu ? 2 * a.n : a.n;  // width of B along N
+    p.n_tiles = swiglu ? static_cast<int>((a.n + BN / 2 - 1) / (BN / 2)) : static_cast<int>((a.n + BN - 1) / BN);
+    p.ldc = static_cast<int>((swiglu || grad) ? 2 * a.n : a.n);
+    p.ld_aux = static_cast<int>(swiglu ? a.n : 2 * a.n);
+    {
+      cuuint64_t dims[2] = {static_cast<cuuint64_t>(a.k), static_cast<cuuint64_t>(a.rows)};
+      cuuint32_t box[2] = {64, BM};
+      if ((rc = make_map(&ta, a.a, 2, dims, box)) != 0) return rc;
+    }
+    if (a.b_major == HMC_MAJOR_MN) {  // B = [groups, K, Ncols]
+      cuuint64_t dims[3] = {static_cast<cuuint64_t>(b_cols), static_cast<cuuint64_t>(a.k),
+                            static_cast<cuuint64_t>(a.groups)};
+      cuuint32_t box[3] = {64, BK, 1};
+      if ((rc = make_map(&tb, a.b, 3, dims, box)) != 0) return rc;
+    } else {  // B = [groups, Ncols, K]
+      cuuint64_t dims[3] = {static_cast<cuuint64_t>(a.k), static_cast<cuuint64_t>(b_cols),
+                            static_cast<cuuint64_t>(a.groups)};
+      cuuint32_t box[3] = {64, BN / 2, 1};
+      if ((rc = make_map(&tb, a.b, 3, dims, box)) != 0) return rc;
+    }
+  } else {
+    HMC_REQUIRE(a.m > 0 && a.m % 8 == 0, HMC_ERR_INVALID,
+                "hmc_grouped_gemm: m (%lld) must be a positive multiple of 8", (long long)a.m);
+    HMC_REQUIRE(a.a_major == HMC_MAJOR_MN && a.b_major == HMC_MAJOR_MN, HMC_ERR_INVALID,
+                "hmc_grouped_gemm: RAGGED_K takes row-major [rows, m] and [rows, n] operands");
+    HMC_REQUIRE(a.epilogue == HMC_EPI_STORE_BF16 || a.epilogue == HMC_EPI_STORE_F32, HMC_ERR_INVALID,
+                "hmc_grouped_gemm: RAGGED_K supports plain stores only");
+    HMC_REQUIRE(a.ready_counters == nullptr, HMC_ERR_INVALID,
+                "hmc_grouped_gemm: arrival counters apply to RAGGED_M only");
+    p.m = static_cast<int>(a.m);
+    p.m_tiles = static_cast<int>((a.m + BM - 1) / BM);
+    p.n_tiles = static_cast<int>((a.n + BN - 1) / BN);
+    p.ldc = static_cast<int>(a.n);
+    // A zero-row tensor cannot be described by a tensor map; one row keeps the map valid and is
+    // never read because every group then has zero k iterations.
+    const cuuint64_t map_rows = static_cast<cuuint64_t>(a.rows > 0 ? a.rows : 1);
+    {
+      cuuint64_t dims[2] = {static_cast<cuuint64_t>(a.m), map_rows};
+      cuuint32_t box[2] = {64, BK};
+      if ((rc = make_map(&ta, a.a, 2, dims, box)) != 0) return rc;
+    }
+    {
+      cuuint64_t dims[2] = {static_cast<cuuint64_t>(a.n), map_rows};
+      cuuint32_t box[2] = {64, BK};
+      if ((rc = make_map(&tb, a.b, 2, dims, box)) != 0) return rc;
+    }
+  }
+
+  int grid = a.max_ctas > 0 ? a.max_ctas : sm_count();
+  if (grid > sm_count()) grid = sm_count();
+  if (a.mode == HMC_GEMM_RAGGED_K) {
+    const long long tiles = static_cast<long long>(p.groups) * p.m_tiles * p.n_tiles;
+    if (tiles < grid) grid = static_cast<int>(tiles);
+    return launch<HMC_MAJOR_MN, HMC_MAJOR_MN>(ta, tb, p, grid, stream);
+  }
+  if (a.b_major == HMC_MAJOR_MN) return launch<HMC_MAJOR_K, HMC_MAJOR_MN>(ta, tb, p, grid, stream);
+  return launch<HMC_MAJOR_K, HMC_MAJOR_K>(ta, tb, p, grid, stream);
+}
