@@ -63,6 +63,72 @@ class GroupedGemmArgs(ctypes.Structure):
     ]
 
 
+class GateRouteArgs(ctypes.Structure):
+    """Mirror of ``hmc_gate_route_args``."""
+
+    _fields_ = [
+        ("logits", c_void_p), ("text_bias", c_void_p), ("vision_bias", c_void_p), ("image_mask", c_void_p),
+        ("use_vision_bias", c_int32), ("experts", c_int32), ("top_k", c_int32), ("scoring", c_int32),
+        ("tokens", c_int64), ("scale", c_float),
+        ("weights", c_void_p), ("indices", c_void_p), ("route_scores", c_void_p), ("selected", c_void_p),
+        ("denominator", c_void_p),
+    ]
+
+
+class GateRouteGradArgs(ctypes.Structure):
+    """Mirror of ``hmc_gate_route_grad_args``."""
+
+    _fields_ = [
+        ("logits", c_void_p), ("route_scores", c_void_p), ("selected", c_void_p), ("denominator", c_void_p),
+        ("indices", c_void_p), ("grad_weights", c_void_p),
+        ("experts", c_int32), ("top_k", c_int32), ("scoring", c_int32), ("reserved", c_int32),
+        ("tokens", c_int64), ("scale", c_float),
+        ("grad_logits", c_void_p), ("status", c_void_p),
+    ]
+
+
+class MegaMhcArgs(ctypes.Structure):
+    """Mirror of ``hmc_mega_mhc_args``."""
+
+    _fields_ = [
+        ("tokens", c_int64), ("hidden", c_int64),
+        ("previous_output", c_void_p), ("residual", c_void_p), ("previous_pre_mix", c_void_p),
+        ("previous_post_mix", c_void_p), ("previous_residual_mix", c_void_p), ("phi", c_void_p),
+        ("alpha", c_void_p), ("bias", c_void_p), ("norm_weight", c_void_p),
+        ("new_residual", c_void_p), ("next_pre_mix", c_void_p), ("next_post_mix", c_void_p),
+        ("next_residual_mix", c_void_p), ("block_input", c_void_p),
+        ("hc_before_norm", c_void_p), ("inv_rms", c_void_p), ("sum_out", c_void_p), ("norm_out", c_void_p),
+        ("mixed_input", c_void_p), ("rms_rstd", c_void_p),
+        ("workspace", c_void_p), ("workspace_bytes", c_int64),
+        ("hc_eps", c_float), ("norm_eps", c_float), ("num_iters", c_int32), ("need_backward", c_int32),
+        ("status", c_void_p),
+    ]
+
+
+class MegaMhcGradArgs(ctypes.Structure):
+    """Mirror of ``hmc_mega_mhc_grad_args``."""
+
+    _fields_ = [
+        ("tokens", c_int64), ("hidden", c_int64),
+        ("grad_new_residual", c_void_p), ("grad_next_pre_mix", c_void_p), ("grad_next_post_mix", c_void_p),
+        ("grad_next_residual_mix", c_void_p), ("grad_block_input", c_void_p),
+        ("new_residual", c_void_p), ("hc_before_norm", c_void_p), ("inv_rms", c_void_p),
+        ("mixed_input", c_void_p), ("rms_rstd", c_void_p),
+        ("previous_output", c_void_p), ("residual", c_void_p), ("previous_pre_mix", c_void_p),
+        ("previous_post_mix", c_void_p), ("previous_residual_mix", c_void_p), ("phi", c_void_p),
+        ("alpha", c_void_p), ("bias", c_void_p), ("norm_weight", c_void_p),
+        ("grad_residual", c_void_p), ("grad_phi", c_void_p), ("grad_alpha", c_void_p), ("grad_bias", c_void_p),
+        ("grad_previous_output", c_void_p), ("grad_previous_pre_mix", c_void_p),
+        ("grad_previous_post_mix", c_void_p), ("grad_previous_residual_mix", c_void_p),
+        ("grad_norm_weight", c_void_p),
+        ("workspace", c_void_p), ("workspace_bytes", c_int64),
+        ("hc_eps", c_float), ("num_iters", c_int32),
+        ("status", c_void_p),
+    ]
+
+
+HMC_SCORE = {"sqrtsoftplus": 0, "softmax": 1, "sigmoid": 2}
+
 _LIB: ctypes.CDLL | None = None
 
 # name -> (restype, argtypes); every symbol include/hmc_b200.h declares.
@@ -77,6 +143,23 @@ SIGNATURES: dict[str, tuple] = {
     "hmc_mega_moe_transport_version": (_I, []),
     "hmc_worker_queue_layout_version": (_I, []),
     "hmc_grouped_gemm": (_I, [ctypes.POINTER(GroupedGemmArgs), _P]),
+    "hmc_gate_route": (_I, [ctypes.POINTER(GateRouteArgs), _P]),
+    "hmc_gate_route_grad": (_I, [ctypes.POINTER(GateRouteGradArgs), _P]),
+    "hmc_gate_project": (_I, [_P, _I, _P, _I, _L, _L, _L, _P, _P]),
+    "hmc_moe_sort_workspace_bytes": (_L, [_L, _L]),
+    "hmc_moe_histogram": (_I, [_P, _I, _L, _L, _P, _P, _P]),
+    "hmc_moe_sort_routes": (_I, [_P, _I, _L, _L, _P, _L, _P, _P, _P, _P, _P, _P, _P]),
+    "hmc_moe_gather_rows": (_I, [_P, _P, _L, _L, _L, _P, _P]),
+    "hmc_moe_permute_from_mapping": (_I, [_P, _P, _P, _L, _L, _L, _P, _P, _P, _P]),
+    "hmc_moe_unpermute": (_I, [_P, _P, _P, _L, _L, _L, _L, _P, _P, _P]),
+    "hmc_moe_unpermute_grad": (_I, [_P, _P, _P, _P, _L, _L, _L, _P, _P, _P, _P]),
+    "hmc_moe_token_permute_grad": (_I, [_P, _P, _L, _L, _L, _P, _P, _P]),
+    "hmc_zero_empty_expert_grad": (_I, [_P, _L, _P, _L, _P, _L, _P]),
+    "hmc_route_offsets": (_I, [_P, _L, _L, _L, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
+    "hmc_mega_mhc_workspace_bytes": (_L, [_L, _L]),
+    "hmc_mega_mhc_grad_workspace_bytes": (_L, [_L, _L]),
+    "hmc_mega_mhc": (_I, [ctypes.POINTER(MegaMhcArgs), _P]),
+    "hmc_mega_mhc_grad": (_I, [ctypes.POINTER(MegaMhcGradArgs), _P]),
 }
 
 

@@ -591,8 +591,6 @@ extern "C" int hmc_grouped_gemm(const hmc_grouped_gemm_args* args, void* stream_
                 "hmc_grouped_gemm: k (%lld) must be a positive multiple of 8", (long long)a.k);
     HMC_REQUIRE(a.a_major == HMC_MAJOR_K, HMC_ERR_INVALID,
                 "hmc_grouped_gemm: RAGGED_M takes a row-major (K-major) A");
-    HMC_REQUIRE(a.epilogue != HMC_EPI_STORE_F32, HMC_ERR_INVALID,
-                "hmc_grouped_gemm: RAGGED_M writes BF16 outputs only");
     p.k = static_cast<int>(a.k);
     const bool swiglu = a.epilogue == HMC_EPI_SWIGLU;
     const bool grad = a.epilogue == HMC_EPI_SWIGLU_GRAD;

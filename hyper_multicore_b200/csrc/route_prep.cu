@@ -1,0 +1,557 @@
+// MoE route preparation and token (un)permutation: integer work is bit-exact by construction
+// (stable counting sort), payload work is 16-byte vectorised row copies.
+//
+// Replaces, on the reference side: histogram + expert-major permutation (hyper_multicore/modules/
+// mega_moe/route.py:186-211, 266-295; torch/csrc/moe_token_permute_out.cpp:50-60), offset
+// descriptors (route.py:309-390, ops/common/mega_moe/utilities.asc:89-151), PermuteFromMapping
+// (utilities.asc:162-209), weighted un-permutation and its gradients (route.py:1029-1051,
+// torch/csrc/mega_moe_unpermute.cpp:56-65, moe_token_permute_grad.cpp:29-38) and
+// ZeroEmptyExpertGrad (utilities.asc:17-54).
+#include "common.cuh"
+
+namespace hmc {
+namespace {
+
+constexpr int SORT_CHUNK = 1024;  // flat (token, slot) entries ranked by one CTA
+constexpr int SORT_THREADS = 1024;
+
+__device__ __forceinline__ long long load_index(const void* indices, int is_i64, long long i) {
+  return is_i64 ? static_cast<const long long*>(indices)[i]
+                : static_cast<long long>(static_cast<const int*>(indices)[i]);
+}
+
+// ---- pass 1: per-chunk histogram ---------------------------------------------------------
+__global__ void __launch_bounds__(SORT_THREADS)
+chunk_histogram_kernel(const void* __restrict__ indices, int is_i64, long long entries, int experts,
+                       int* __restrict__ chunk_counts, int* __restrict__ status) {
+  extern __shared__ int hist[];
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) hist[e] = 0;
+  __syncthreads();
+  const long long i = static_cast<long long>(blockIdx.x) * SORT_CHUNK + threadIdx.x;
+  if (i < entries) {
+    const long long e = load_index(indices, is_i64, i);
+    if (e >= 0 && e < experts) {
+      atomicAdd(&hist[e], 1);
+    } else {
+      report_status(status, HMC_STATUS_BAD_INDEX, static_cast<int>(i), static_cast<int>(e), experts);
+    }
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < experts; e += blockDim.x)
+    chunk_counts[static_cast<long long>(blockIdx.x) * experts + e] = hist[e];
+}
+
+// ---- pass 2: one CTA turns chunk histograms into chunk bases and expert bases -------------
+// chunk_counts[c][e] becomes the first destination row of chunk c's entries for expert e.
+__global__ void __launch_bounds__(1024)
+chunk_scan_kernel(int* __restrict__ chunk_counts, int chunks, int experts, int* __restrict__ counts_out,
+                  long long* __restrict__ ends_out) {
+  extern __shared__ int totals[];  // [experts]
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) {
+    int run = 0;
+    for (int c = 0; c < chunks; ++c) {
+      int* slot = chunk_counts + static_cast<long long>(c) * experts + e;
+      const int v = *slot;
+      *slot = run;
+      run += v;
+    }
+    totals[e] = run;
+    if (counts_out != nullptr) counts_out[e] = run;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    // experts <= 4096: a serial scan by one thread costs microseconds and is trivially exact
+    int run = 0;
+    for (int e = 0; e < experts; ++e) {
+      const int v = totals[e];
+      totals[e] = run;
+      run += v;
+      if (ends_out != nullptr) ends_out[e] = run;
+    }
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) {
+    const int base = totals[e];
+    for (int c = 0; c < chunks; ++c) chunk_counts[static_cast<long long>(c) * experts + e] += base;
+  }
+}
+
+// ---- pass 3: stable rank inside each chunk --------------------------------------------------
+// Warps take turns in flat-index order; inside a warp, match_any groups equal experts and the
+// lower lanes rank first, so equal experts keep their flat (token * top_k + slot) order.
+__global__ void __launch_bounds__(SORT_THREADS)
+chunk_rank_kernel(const void* __restrict__ indices, int is_i64, long long entries, int experts,
+                  const int* __restrict__ chunk_bases, int* __restrict__ mapping,
+                  int* __restrict__ source_of_row, int* __restrict__ expert_of_row) {
+  extern __shared__ int cursor[];  // [experts] next free destination row per expert
+  for (int e = threadIdx.x; e < experts; e += blockDim.x)
+    cursor[e] = chunk_bases[static_cast<long long>(blockIdx.x) * experts + e];
+  __syncthreads();
+  const long long i = static_cast<long long>(blockIdx.x) * SORT_CHUNK + threadIdx.x;
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  long long e = -1;
+  if (i < entries) {
+    e = load_index(indices, is_i64, i);
+    if (e < 0 || e >= experts) e = -1;
+  }
+  for (int w = 0; w < SORT_THREADS / 32; ++w) {
+    if (w == warp) {
+      const unsigned peers = __match_any_sync(0xffffffffu, e);
+      if (e >= 0) {
+        const int rank_in_warp = __popc(peers & ((1u << lane) - 1u));
+        const int leader = __ffs(peers) - 1;
+        int base = 0;
+        if (lane == leader) {
+          base = cursor[e];
+          cursor[e] = base + __popc(peers);
+        }
+        base = __shfl_sync(peers, base, leader);
+        const int dest = base + rank_in_warp;
+        mapping[i] = dest;
+        if (source_of_row != nullptr) source_of_row[dest] = static_cast<int>(i);
+        if (expert_of_row != nullptr) expert_of_row[dest] = static_cast<int>(e);
+      } else if (i < entries) {
+        mapping[i] = -1;
+      }
+    }
+    __syncthreads();
+  }
+}
+
+// ---- payload movement ----------------------------------------------------------------------
+// One warp per destination row: out[row] = tokens[source_of_row[row] / top_k].
+__global__ void __launch_bounds__(256)
+gather_rows_kernel(const uint4* __restrict__ tokens, const int* __restrict__ source_of_row, long long rows,
+                   int top_k, int vec_per_row, uint4* __restrict__ out) {
+  const long long row = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  const long long src = source_of_row[row] / top_k;
+  const uint4* s = tokens + src * vec_per_row;
+  uint4* d = out + row * vec_per_row;
+  for (int v = lane; v < vec_per_row; v += 32) st_cs_16(d + v, ld_16(s + v));
+}
+
+// One warp per flat entry i: out[mapping[i]] = tokens[i / top_k], out_p[mapping[i]] = p[i].
+__global__ void __launch_bounds__(256)
+scatter_rows_kernel(const uint4* __restrict__ tokens, const int* __restrict__ mapping,
+                    const float* __restrict__ probs, long long entries, int top_k, int vec_per_row,
+                    uint4* __restrict__ out, float* __restrict__ out_probs, int* __restrict__ status) {
+  const long long i = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  if (i >= entries) return;
+  const int lane = threadIdx.x & 31;
+  const int dest = mapping[i];
+  if (dest < 0 || dest >= entries) {
+    if (lane == 0) report_status(status, HMC_STATUS_BAD_INDEX, static_cast<int>(i), dest, 0);
+    return;
+  }
+  const uint4* s = tokens + (i / top_k) * vec_per_row;
+  uint4* d = out + static_cast<long long>(dest) * vec_per_row;
+  for (int v = lane; v < vec_per_row; v += 32) st_cs_16(d + v, ld_16(s + v));
+  if (lane == 0 && out_probs != nullptr) out_probs[dest] = probs[i];
+}
+
+// out[t] = sum over the token's routes, in ascending expert (= ascending row) order, of
+// bf16(float(y[row]) * p), accumulated in BF16 like the golden's index_add
+// (tests/common/multicore/moe_reference.py:179-180). One CTA of 128 threads per token.
+constexpr int MAX_TOP_K = 64;
+__global__ void __launch_bounds__(128)
+unpermute_kernel(const uint4* __restrict__ y, const int* __restrict__ mapping, const float* __restrict__ probs,
+                 long long tokens, int top_k, int vec_per_row, long long y_rows, uint4* __restrict__ out,
+                 int* __restrict__ status) {
+  __shared__ int rows[MAX_TOP_K];
+  __shared__ float weight[MAX_TOP_K];
+  const long long t = blockIdx.x;
+  if (threadIdx.x == 0) {
+    // insertion sort of the (row, weight) pairs by row; top_k is small
+    for (int k = 0; k < top_k; ++k) {
+      int r = mapping[t * top_k + k];
+      float w = probs != nullptr ? probs[t * top_k + k] : 1.0f;
+      if (r < 0 || r >= y_rows) {
+        report_status(status, HMC_STATUS_BAD_INDEX, static_cast<int>(t), k, r);
+        r = -1;
+      }
+      int j = k;
+      while (j > 0 && rows[j - 1] > r) {
+        rows[j] = rows[j - 1];
+        weight[j] = weight[j - 1];
+        --j;
+      }
+      rows[j] = r;
+      weight[j] = w;
+    }
+  }
+  __syncthreads();
+  for (int v = threadIdx.x; v < vec_per_row; v += blockDim.x) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int k = 0; k < top_k; ++k) {
+      const int r = rows[k];
+      if (r < 0) continue;
+      const uint4 q = ld_nc_16(y + static_cast<long long>(r) * vec_per_row + v);
+      const float w = weight[k];
+      const uint32_t words[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = unpack_bf16x2(words[j]);
+        acc[2 * j] = bf16_round(acc[2 * j] + bf16_round(f.x * w));
+        acc[2 * j + 1] = bf16_round(acc[2 * j + 1] + bf16_round(f.y * w));
+      }
+    }
+    uint4 o;
+    o.x = pack_bf16x2(acc[0], acc[1]);
+    o.y = pack_bf16x2(acc[2], acc[3]);
+    o.z = pack_bf16x2(acc[4], acc[5]);
+    o.w = pack_bf16x2(acc[6], acc[7]);
+    st_cs_16(out + t * vec_per_row + v, o);
+  }
+}
+
+// Backward of the weighted un-permutation. One CTA per token:
+//   grad_permuted[row(t,k)] = bf16(float(dOut[t]) * p[t,k])
+//   grad_probs[t,k]         = sum_h float(dOut[t,h]) * float(y[row(t,k), h])
+__global__ void __launch_bounds__(128)
+unpermute_grad_kernel(const uint4* __restrict__ y, const uint4* __restrict__ grad_out,
+                      const int* __restrict__ mapping, const float* __restrict__ probs, long long tokens,
+                      int top_k, int vec_per_row, uint4* __restrict__ grad_permuted,
+                      float* __restrict__ grad_probs, int* __restrict__ status) {
+  __shared__ float partial[4];
+  const long long t = blockIdx.x;
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  for (int k = 0; k < top_k; ++k) {
+    const int r = mapping[t * top_k + k];
+    const float w = probs[t * top_k + k];
+    float dot = 0.f;
+    if (r >= 0) {
+      for (int v = threadIdx.x; v < vec_per_row; v += blockDim.x) {
+        const uint4 g = ld_16(grad_out + t * vec_per_row + v);
+        const uint32_t gw[4] = {g.x, g.y, g.z, g.w};
+        uint32_t ow[4];
+        float2 yf[4];
+        if (y != nullptr) {
+          const uint4 q = ld_nc_16(y + static_cast<long long>(r) * vec_per_row + v);
+          yf[0] = unpack_bf16x2(q.x);
+          yf[1] = unpack_bf16x2(q.y);
+          yf[2] = unpack_bf16x2(q.z);
+          yf[3] = unpack_bf16x2(q.w);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 gf = unpack_bf16x2(gw[j]);
+          ow[j] = pack_bf16x2(gf.x * w, gf.y * w);
+          if (y != nullptr) dot += gf.x * yf[j].x + gf.y * yf[j].y;
+        }
+        st_cs_16(grad_permuted + static_cast<long long>(r) * vec_per_row + v, make_uint4(ow[0], ow[1], ow[2], ow[3]));
+      }
+    } else if (threadIdx.x == 0) {
+      report_status(status, HMC_STATUS_BAD_INDEX, static_cast<int>(t), k, r);
+    }
+    if (grad_probs != nullptr) {
+      dot = warp_sum(dot);
+      if (lane == 0) partial[warp] = dot;
+      __syncthreads();
+      if (threadIdx.x == 0) grad_probs[t * top_k + k] = partial[0] + partial[1] + partial[2] + partial[3];
+      __syncthreads();
+    }
+  }
+}
+
+// dX[t] = sum_k dXe[row(t,k)] with one FP32 accumulation and a single BF16 rounding.
+__global__ void __launch_bounds__(128)
+permute_grad_kernel(const uint4* __restrict__ grad_permuted, const int* __restrict__ mapping, long long tokens,
+                    int top_k, int vec_per_row, long long rows, uint4* __restrict__ grad_tokens,
+                    int* __restrict__ status) {
+  const long long t = blockIdx.x;
+  for (int v = threadIdx.x; v < vec_per_row; v += blockDim.x) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int k = 0; k < top_k; ++k) {
+      const int r = mapping[t * top_k + k];
+      if (r < 0 || r >= rows) {
+        if (v == 0) report_status(status, HMC_STATUS_BAD_INDEX, static_cast<int>(t), k, r);
+        continue;
+      }
+      const uint4 q = ld_nc_16(grad_permuted + static_cast<long long>(r) * vec_per_row + v);
+      const uint32_t words[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = unpack_bf16x2(words[j]);
+        acc[2 * j] += f.x;
+        acc[2 * j + 1] += f.y;
+      }
+    }
+    uint4 o;
+    o.x = pack_bf16x2(acc[0], acc[1]);
+    o.y = pack_bf16x2(acc[2], acc[3]);
+    o.z = pack_bf16x2(acc[4], acc[5]);
+    o.w = pack_bf16x2(acc[6], acc[7]);
+    st_cs_16(grad_tokens + t * vec_per_row + v, o);
+  }
+}
+
+// Zero the gradient slices of experts whose cumulative row count did not advance.
+__global__ void __launch_bounds__(256)
+zero_empty_kernel(uint4* __restrict__ first, long long first_vec_per_expert, uint4* __restrict__ second,
+                  long long second_vec_per_expert, const long long* __restrict__ cumulative, int experts) {
+  const int e = blockIdx.y;
+  const long long prev = e == 0 ? 0 : cumulative[e - 1];
+  if (cumulative[e] != prev) return;
+  const uint4 zero = make_uint4(0, 0, 0, 0);
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long v = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; v < first_vec_per_expert; v += stride)
+    first[e * first_vec_per_expert + v] = zero;
+  if (second != nullptr)
+    for (long long v = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; v < second_vec_per_expert; v += stride)
+      second[e * second_vec_per_expert + v] = zero;
+}
+
+// Offset descriptors for push dispatch from the gathered count table counts[ep][experts].
+// One CTA; thread s < ep scans source s, thread d < ep scans destination d. Row units.
+__global__ void __launch_bounds__(256)
+route_offsets_kernel(const int* __restrict__ counts, int ep, int experts, int rank,
+                     long long* __restrict__ dispatch_src_off, long long* __restrict__ dispatch_target_off,
+                     int* __restrict__ dispatch_size, long long* __restrict__ combine_src_off,
+                     long long* __restrict__ combine_target_off, int* __restrict__ combine_size,
+                     long long* __restrict__ group_list, long long* __restrict__ totals) {
+  const int local = experts / ep;
+  for (int s = threadIdx.x; s < ep; s += blockDim.x) {
+    // source_prefix[s][e]: first row of expert e in source s's expert-major routed buffer
+    long long run = 0;
+    for (int e = 0; e < experts; ++e) {
+      const int c = counts[s * experts + e];
+      if (s == rank) {
+        dispatch_src_off[e] = run;
+        dispatch_size[e] = c;
+      }
+      if (e >= rank * local && e < (rank + 1) * local) {
+        combine_target_off[s * local + (e - rank * local)] = run;
+        combine_size[s * local + (e - rank * local)] = c;
+      }
+      run += c;
+    }
+    if (s == rank && totals != nullptr) totals[0] = run;  // rows this rank routes (tokens * top_k)
+  }
+  for (int d = threadIdx.x; d < ep; d += blockDim.x) {
+    // destination d lays its receive buffer out local-expert-major, then by source rank
+    long long run = 0;
+    for (int le = 0; le < local; ++le) {
+      for (int s = 0; s < ep; ++s) {
+        if (s == rank) dispatch_target_off[d * local + le] = run;
+        if (d == rank) combine_src_off[s * local + le] = run;
+        run += counts[s * experts + d * local + le];
+      }
+      if (d == rank) group_list[le] = run;
+    }
+    if (d == rank && totals != nullptr) totals[1] = run;  // rows this rank receives
+  }
+}
+
+__global__ void histogram_kernel(const void* __restrict__ indices, int is_i64, long long entries, int experts,
+                                 int* __restrict__ counts, int* __restrict__ status) {
+  extern __shared__ int hist[];
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) hist[e] = 0;
+  __syncthreads();
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < entries; i += stride) {
+    const long long e = load_index(indices, is_i64, i);
+    if (e >= 0 && e < experts) atomicAdd(&hist[e], 1);
+    else report_status(status, HMC_STATUS_BAD_INDEX, static_cast<int>(i), static_cast<int>(e), experts);
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < experts; e += blockDim.x)
+    if (hist[e] != 0) atomicAdd(&counts[e], hist[e]);
+}
+
+}  // namespace
+}  // namespace hmc
+
+using namespace hmc;
+
+extern "C" int64_t hmc_moe_sort_workspace_bytes(int64_t entries, int64_t experts) {
+  const int64_t chunks = (entries + SORT_CHUNK - 1) / SORT_CHUNK;
+  return (chunks > 0 ? chunks : 1) * experts * static_cast<int64_t>(sizeof(int));
+}
+
+extern "C" int hmc_moe_histogram(const void* indices, int indices_are_i64, int64_t entries, int64_t experts,
+                                 int32_t* counts, int32_t* status, void* stream_ptr) {
+  HMC_REQUIRE(counts != nullptr && (entries == 0 || indices != nullptr), HMC_ERR_INVALID,
+              "hmc_moe_histogram: null tensor pointer");
+  HMC_REQUIRE(experts > 0 && experts <= 4096, HMC_ERR_LIMIT, "hmc_moe_histogram: experts must be in [1, 4096]");
+  HMC_REQUIRE(entries >= 0 && entries < (1ll << 31), HMC_ERR_LIMIT, "hmc_moe_histogram: entries must fit in int32");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  HMC_CUDA_OK(cudaMemsetAsync(counts, 0, experts * sizeof(int), stream));
+  if (entries == 0) return 0;
+  int grid = static_cast<int>((entries + 255) / 256);
+  if (grid > 4 * sm_count()) grid = 4 * sm_count();
+  histogram_kernel<<<grid, 256, experts * sizeof(int), stream>>>(indices, indices_are_i64, entries,
+                                                                 static_cast<int>(experts), counts, status);
+  HMC_LAUNCH_OK();
+  return 0;
+}
+
+extern "C" int hmc_moe_sort_routes(const void* indices, int indices_are_i64, int64_t entries, int64_t experts,
+                                   void* workspace, int64_t workspace_bytes, int32_t* mapping,
+                                   int32_t* source_of_row, int32_t* expert_of_row, int32_t* counts,
+                                   int64_t* cumulative, int32_t* status, void* stream_ptr) {
+  HMC_REQUIRE(experts > 0 && experts <= 4096, HMC_ERR_LIMIT, "hmc_moe_sort_routes: experts must be in [1, 4096]");
+  HMC_REQUIRE(entries >= 0 && entries < (1ll << 31), HMC_ERR_LIMIT,
+              "hmc_moe_sort_routes: tokens * top_k must fit in int32");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  if (entries == 0) {
+    if (counts != nullptr) HMC_CUDA_OK(cudaMemsetAsync(counts, 0, experts * sizeof(int), stream));
+    if (cumulative != nullptr) HMC_CUDA_OK(cudaMemsetAsync(cumulative, 0, experts * sizeof(long long), stream));
+    return 0;
+  }
+  HMC_REQUIRE(indices && mapping && workspace, HMC_ERR_INVALID, "hmc_moe_sort_routes: null tensor pointer");
+  HMC_REQUIRE(workspace_bytes >= hmc_moe_sort_workspace_bytes(entries, experts), HMC_ERR_INVALID,
+              "hmc_moe_sort_routes: workspace holds %lld bytes, %lld needed", (long long)workspace_bytes,
+              (long long)hmc_moe_sort_workspace_bytes(entries, experts));
+  const int chunks = static_cast<int>((entries + SORT_CHUNK - 1) / SORT_CHUNK);
+  const int e = static_cast<int>(experts);
+  const size_t smem = experts * sizeof(int);
+  int* chunk_counts = static_cast<int*>(workspace);
+  chunk_histogram_kernel<<<chunks, SORT_THREADS, smem, stream>>>(indices, indices_are_i64, entries, e,
+                                                               chunk_counts, status);
+  HMC_LAUNCH_OK();
+  chunk_scan_kernel<<<1, 1024, smem, stream>>>(chunk_counts, chunks, e, counts,
+                                               reinterpret_cast<long long*>(cumulative));
+  HMC_LAUNCH_OK();
+  chunk_rank_kernel<<<chunks, SORT_THREADS, smem, stream>>>(indices, indices_are_i64, entries, e, chunk_counts,
+                                                          mapping, source_of_row, expert_of_row);
+  HMC_LAUNCH_OK();
+  return 0;
+}
+
+static int check_rows(const char* what, const void* a, const void* b, int64_t hidden) {
+  HMC_REQUIRE(a != nullptr && b != nullptr, HMC_ERR_INVALID, "%s: null tensor pointer", what);
+  HMC_REQUIRE(hidden > 0 && hidden % 8 == 0, HMC_ERR_INVALID,
+              "%s: hidden size (%lld) must be a positive multiple of 8 BF16 elements", what, (long long)hidden);
+  HMC_REQUIRE(aligned16(a) && aligned16(b), HMC_ERR_INVALID, "%s: rows must be 16-byte aligned", what);
+  return 0;
+}
+
+extern "C" int hmc_moe_gather_rows(const void* tokens, const int32_t* source_of_row, int64_t rows, int64_t top_k,
+                                   int64_t hidden, void* out, void* stream_ptr) {
+  if (rows == 0) return 0;
+  int rc = check_rows("hmc_moe_gather_rows", tokens, out, hidden);
+  if (rc != 0) return rc;
+  HMC_REQUIRE(source_of_row != nullptr && top_k > 0, HMC_ERR_INVALID, "hmc_moe_gather_rows: bad arguments");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  gather_rows_kernel<<<static_cast<unsigned>((rows + 7) / 8), 256, 0, stream>>>(
+      static_cast<const uint4*>(tokens), source_of_row, rows, static_cast<int>(top_k), static_cast<int>(hidden / 8),
+      static_cast<uint4*>(out));
+  HMC_LAUNCH_OK();
+  return 0;
+}
+
+extern "C" int hmc_moe_permute_from_mapping(const void* tokens, const int32_t* mapping, const float* probs,
+                                            int64_t num_tokens, int64_t top_k, int64_t hidden, void* out,
+                                            float* out_probs, int32_t* status, void* stream_ptr) {
+  if (num_tokens == 0) return 0;
+  int rc = check_rows("hmc_moe_permute_from_mapping", tokens, out, hidden);
+  if (rc != 0) return rc;
+  HMC_REQUIRE(mapping != nullptr && top_k > 0, HMC_ERR_INVALID, "hmc_moe_permute_from_mapping: bad arguments");
+  HMC_REQUIRE((out_probs == nullptr) == (probs == nullptr), HMC_ERR_INVALID,
+              "hmc_moe_permute_from_mapping: probabilities and their output go together");
+  HMC_REQUIRE(num_tokens * top_k < (1ll << 31), HMC_ERR_LIMIT, "hmc_moe_permute_from_mapping: too many routes");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  const long long entries = num_tokens * top_k;
+  scatter_rows_kernel<<<static_cast<unsigned>((entries + 7) / 8), 256, 0, stream>>>(
+      static_cast<const uint4*>(tokens), mapping, probs, entries, static_cast<int>(top_k),
+      static_cast<int>(hidden / 8), static_cast<uint4*>(out), out_probs, status);
+  HMC_LAUNCH_OK();
+  return 0;
+}
+
+extern "C" int hmc_moe_unpermute(const void* permuted, const int32_t* mapping, const float* probs,
+                                 int64_t num_tokens, int64_t top_k, int64_t hidden, int64_t permuted_rows,
+                                 void* out, int32_t* status, void* stream_ptr) {
+  if (num_tokens == 0) return 0;
+  int rc = check_rows("hmc_moe_unpermute", permuted, out, hidden);
+  if (rc != 0) return rc;
+  HMC_REQUIRE(mapping != nullptr, HMC_ERR_INVALID, "hmc_moe_unpermute: null mapping");
+  HMC_REQUIRE(top_k > 0 && top_k <= MAX_TOP_K, HMC_ERR_LIMIT, "hmc_moe_unpermute: top_k must be in [1, %d]",
+              MAX_TOP_K);
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  unpermute_kernel<<<static_cast<unsigned>(num_tokens), 128, 0, stream>>>(
+      static_cast<const uint4*>(permuted), mapping, probs, num_tokens, static_cast<int>(top_k),
+      static_cast<int>(hidden / 8), permuted_rows, static_cast<uint4*>(out), status);
+  HMC_LAUNCH_OK();
+  return 0;
+}
+
+extern "C" int hmc_moe_unpermute_grad(const void* permuted, const void* grad_out, const int32_t* mapping,
+                                      const float* probs, int64_t num_tokens, int64_t top_k, int64_t hidden,
+                                      void* grad_permuted, float* grad_probs, int32_t* status,
+                                      void* stream_ptr) {
+  if (num_tokens == 0) return 0;
+  int rc = check_rows("hmc_moe_unpermute_grad", grad_out, grad_permuted, hidden);
+  if (rc != 0) return rc;
+  HMC_REQUIRE(mapping != nullptr && probs != nullptr, HMC_ERR_INVALID, "hmc_moe_unpermute_grad: null tensor pointer");
+  HMC_REQUIRE((permuted == nullptr) == (grad_probs == nullptr), HMC_ERR_INVALID,
+              "hmc_moe_unpermute_grad: forward outputs and grad_probs go together");
+  HMC_REQUIRE(permuted == nullptr || aligned16(permuted), HMC_ERR_INVALID,
+              "hmc_moe_unpermute_grad: rows must be 16-byte aligned");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  unpermute_grad_kernel<<<static_cast<unsigned>(num_tokens), 128, 0, stream>>>(
+      static_cast<const uint4*>(permuted), static_cast<const uint4*>(grad_out), mapping, probs, num_tokens,
+      static_cast<int>(top_k), static_cast<int>(hidden / 8), static_cast<uint4*>(grad_permuted), grad_probs, status);
+  HMC_LAUNCH_OK();
+  return 0;
+}
+
+extern "C" int hmc_moe_token_permute_grad(const void* grad_permuted, const int32_t* mapping, int64_t num_tokens,
+                                          int64_t top_k, int64_t hidden, void* grad_tokens, int32_t* status,
+                                          void* stream_ptr) {
+  if (num_tokens == 0) return 0;
+  int rc = check_rows("hmc_moe_token_permute_grad", grad_permuted, grad_tokens, hidden);
+  if (rc != 0) return rc;
+  HMC_REQUIRE(mapping != nullptr && top_k > 0, HMC_ERR_INVALID, "hmc_moe_token_permute_grad: bad arguments");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  permute_grad_kernel<<<static_cast<unsigned>(num_tokens), 128, 0, stream>>>(
+      static_cast<const uint4*>(grad_permuted), mapping, num_tokens, static_cast<int>(top_k),
+      static_cast<int>(hidden / 8), num_tokens * top_k, static_cast<uint4*>(grad_tokens), status);
+  HMC_LAUNCH_OK();
+  return 0;
+}
+
+extern "C" int hmc_zero_empty_expert_grad(void* first, int64_t first_bytes_per_expert, void* second,
+                                          int64_t second_bytes_per_expert, const int64_t* cumulative,
+                                          int64_t experts, void* stream_ptr) {
+  HMC_REQUIRE(first != nullptr && cumulative != nullptr && experts > 0, HMC_ERR_INVALID,
+              "hmc_zero_empty_expert_grad: bad arguments");
+  HMC_REQUIRE(first_bytes_per_expert % 16 == 0 && second_bytes_per_expert % 16 == 0 && aligned16(first) &&
+                  (second == nullptr || aligned16(second)),
+              HMC_ERR_INVALID, "hmc_zero_empty_expert_grad: expert slices must be multiples of 16 bytes");
+  HMC_REQUIRE(experts <= 65535, HMC_ERR_LIMIT, "hmc_zero_empty_expert_grad: too many experts");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  dim3 grid(32, static_cast<unsigned>(experts));
+  zero_empty_kernel<<<grid, 256, 0, stream>>>(static_cast<uint4*>(first), first_bytes_per_expert / 16,
+                                              static_cast<uint4*>(second), second_bytes_per_expert / 16,
+                                              reinterpret_cast<const long long*>(cumulative),
+                                              static_cast<int>(experts));
+  HMC_LAUNCH_OK();
+  return 0;
+}
+
+extern "C" int hmc_route_offsets(const int32_t* counts, int64_t ep, int64_t experts, int64_t rank,
+                                 int64_t* dispatch_src_off, int64_t* dispatch_target_off, int32_t* dispatch_size,
+                                 int64_t* combine_src_off, int64_t* combine_target_off, int32_t* combine_size,
+                                 int64_t* group_list, int64_t* totals, void* stream_ptr) {
+  HMC_REQUIRE(counts && dispatch_src_off && dispatch_target_off && dispatch_size && combine_src_off &&
+                  combine_target_off && combine_size && group_list,
+              HMC_ERR_INVALID, "hmc_route_offsets: null tensor pointer");
+  HMC_REQUIRE(ep > 0 && experts > 0 && experts % ep == 0, HMC_ERR_INVALID,
+              "hmc_route_offsets: experts (%lld) must be a positive multiple of ep (%lld)", (long long)experts,
+              (long long)ep);
+  HMC_REQUIRE(rank >= 0 && rank < ep, HMC_ERR_INVALID, "hmc_route_offsets: rank %lld outside [0, %lld)",
+              (long long)rank, (long long)ep);
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  route_offsets_kernel<<<1, 256, 0, stream>>>(
+      counts, static_cast<int>(ep), static_cast<int>(experts), static_cast<int>(rank),
+      reinterpret_cast<long long*>(dispatch_src_off), reinterpret_cast<long long*>(dispatch_target_off),
+      dispatch_size, reinterpret_cast<long long*>(combine_src_off), reinterpret_cast<long long*>(combine_target_off),
+      combine_size, reinterpret_cast<long long*>(group_list), reinterpret_cast<long long*>(totals));
+  HMC_LAUNCH_OK();
+  return 0;
+}

@@ -79,3 +79,220 @@ def grouped_gemm(
     args.status = _lib.ptr(status)
     with torch.cuda.device(device):
         _lib.check(_lib.load().hmc_grouped_gemm(ctypes.byref(args), _lib.stream_ptr(device)))
+
+
+def _call(name: str, device: torch.device, *args) -> None:
+    with torch.cuda.device(device):
+        _lib.check(getattr(_lib.load(), name)(*args, _lib.stream_ptr(device)))
+
+
+# ------------------------------------------------------------------------------------------- gate
+def gate_project(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """FP32 logits [T, E] = float(x [T, H]) @ float(weight [E, H]).T."""
+    device = _require_cuda(x, weight)
+    for name, tensor in (("hidden states", x), ("weight", weight)):
+        if tensor.dtype not in (torch.bfloat16, torch.float32):
+            raise TypeError(f"MegaGate {name} must be BF16 or FP32, got {tensor.dtype}")
+    x = x.contiguous()
+    weight = weight.contiguous()
+    logits = torch.empty((x.shape[0], weight.shape[0]), dtype=torch.float32, device=device)
+    _call("hmc_gate_project", device, x.data_ptr(), int(x.dtype == torch.bfloat16), weight.data_ptr(),
+          int(weight.dtype == torch.bfloat16), x.shape[0], x.shape[1], weight.shape[0], logits.data_ptr())
+    return logits
+
+
+def gate_route_out(logits, text_bias, vision_bias, image_mask, use_vision_bias, top_k, scale, scoring,
+                   weights, indices, route_scores, selected, denominator) -> None:
+    """Top-k Route on FP32 logits into caller-owned outputs."""
+    device = _require_cuda(logits, text_bias, vision_bias, weights, indices, route_scores, selected, denominator)
+    args = _lib.GateRouteArgs()
+    args.logits = logits.data_ptr()
+    args.text_bias = text_bias.data_ptr()
+    args.vision_bias = vision_bias.data_ptr()
+    args.image_mask = _lib.ptr(image_mask) if use_vision_bias else None
+    args.use_vision_bias = int(bool(use_vision_bias))
+    args.experts = logits.shape[1]
+    args.top_k = top_k
+    args.scoring = _lib.HMC_SCORE[scoring]
+    args.tokens = logits.shape[0]
+    args.scale = scale
+    args.weights = weights.data_ptr()
+    args.indices = indices.data_ptr()
+    args.route_scores = route_scores.data_ptr()
+    args.selected = selected.data_ptr()
+    args.denominator = denominator.data_ptr()
+    _call("hmc_gate_route", device, ctypes.byref(args))
+
+
+def gate_route_grad_out(logits, route_scores, selected, denominator, indices, grad_weights, top_k, scale,
+                        scoring, grad_logits, status=None) -> None:
+    """RouteGrad into a caller-owned FP32 [T, E] gradient."""
+    device = _require_cuda(logits, route_scores, selected, denominator, indices, grad_weights, grad_logits)
+    args = _lib.GateRouteGradArgs()
+    args.logits = logits.data_ptr()
+    args.route_scores = route_scores.data_ptr()
+    args.selected = selected.data_ptr()
+    args.denominator = denominator.data_ptr()
+    args.indices = indices.data_ptr()
+    args.grad_weights = grad_weights.data_ptr()
+    args.experts = logits.shape[1]
+    args.top_k = top_k
+    args.scoring = _lib.HMC_SCORE[scoring]
+    args.tokens = logits.shape[0]
+    args.scale = scale
+    args.grad_logits = grad_logits.data_ptr()
+    args.status = _lib.ptr(status)
+    _call("hmc_gate_route_grad", device, ctypes.byref(args))
+
+
+# ------------------------------------------------------------------------------------ route prep
+def moe_histogram(indices: torch.Tensor, experts: int, status=None) -> torch.Tensor:
+    """INT32 histogram of expert ids."""
+    device = _require_cuda(indices)
+    flat = indices.reshape(-1).contiguous()
+    counts = torch.empty(experts, dtype=torch.int32, device=device)
+    _call("hmc_moe_histogram", device, flat.data_ptr(), int(flat.dtype == torch.int64), flat.numel(), experts,
+          counts.data_ptr(), _lib.ptr(status))
+    return counts
+
+
+def moe_sort_routes(indices: torch.Tensor, experts: int, *, want_sources: bool = True, status=None):
+    """Stable expert-major sort of the flat (token, slot) routes.
+
+    Returns (mapping[T*K] i32, source_of_row[T*K] i32 | None, expert_of_row | None, counts[E] i32,
+    cumulative[E] i64).
+    """
+    device = _require_cuda(indices)
+    if indices.dtype not in (torch.int32, torch.int64):
+        raise TypeError(f"expert indices must be int32 or int64, got {indices.dtype}")
+    flat = indices.reshape(-1).contiguous()
+    entries = flat.numel()
+    lib = _lib.load()
+    workspace = torch.empty(max(1, lib.hmc_moe_sort_workspace_bytes(entries, experts)), dtype=torch.uint8,
+                            device=device)
+    mapping = torch.empty(entries, dtype=torch.int32, device=device)
+    sources = torch.empty(entries, dtype=torch.int32, device=device) if want_sources else None
+    row_experts = torch.empty(entries, dtype=torch.int32, device=device) if want_sources else None
+    counts = torch.empty(experts, dtype=torch.int32, device=device)
+    cumulative = torch.empty(experts, dtype=torch.int64, device=device)
+    _call("hmc_moe_sort_routes", device, flat.data_ptr(), int(flat.dtype == torch.int64), entries, experts,
+          workspace.data_ptr(), workspace.numel(), mapping.data_ptr(), _lib.ptr(sources), _lib.ptr(row_experts),
+          counts.data_ptr(), cumulative.data_ptr(), _lib.ptr(status))
+    return mapping, sources, row_experts, counts, cumulative
+
+
+def moe_gather_rows(tokens: torch.Tensor, source_of_row: torch.Tensor, top_k: int, out: torch.Tensor) -> None:
+    """out[row] = tokens[source_of_row[row] // top_k]."""
+    device = _require_cuda(tokens, source_of_row, out)
+    _call("hmc_moe_gather_rows", device, tokens.data_ptr(), source_of_row.data_ptr(), source_of_row.numel(), top_k,
+          tokens.shape[1], out.data_ptr())
+
+
+def moe_permute_from_mapping(tokens, mapping, probs, top_k, out, out_probs, status=None) -> None:
+    """out[mapping[t*K+k]] = tokens[t]; out_probs[mapping[t*K+k]] = probs[t, k]."""
+    device = _require_cuda(tokens, mapping, out)
+    _call("hmc_moe_permute_from_mapping", device, tokens.data_ptr(), mapping.data_ptr(), _lib.ptr(probs),
+          tokens.shape[0], top_k, tokens.shape[1], out.data_ptr(), _lib.ptr(out_probs), _lib.ptr(status))
+
+
+def moe_unpermute(permuted, mapping, probs, num_tokens, top_k, out, status=None) -> None:
+    """Weighted K-sum of expert-major rows back to token order."""
+    device = _require_cuda(permuted, mapping, out)
+    _call("hmc_moe_unpermute", device, permuted.data_ptr(), mapping.data_ptr(), _lib.ptr(probs), num_tokens, top_k,
+          permuted.shape[1], permuted.shape[0], out.data_ptr(), _lib.ptr(status))
+
+
+def moe_unpermute_grad(permuted, grad_out, mapping, probs, top_k, grad_permuted, grad_probs, status=None) -> None:
+    """grad_permuted[row] = bf16(grad_out[t] * p); grad_probs[t,k] = <grad_out[t], permuted[row]>."""
+    device = _require_cuda(grad_out, mapping, probs, grad_permuted)
+    _call("hmc_moe_unpermute_grad", device, _lib.ptr(permuted), grad_out.data_ptr(), mapping.data_ptr(),
+          probs.data_ptr(), grad_out.shape[0], top_k, grad_out.shape[1], grad_permuted.data_ptr(),
+          _lib.ptr(grad_probs), _lib.ptr(status))
+
+
+def moe_token_permute_grad(grad_permuted, mapping, num_tokens, top_k, grad_tokens, status=None) -> None:
+    """grad_tokens[t] = sum_k grad_permuted[mapping[t*K+k]]."""
+    device = _require_cuda(grad_permuted, mapping, grad_tokens)
+    _call("hmc_moe_token_permute_grad", device, grad_permuted.data_ptr(), mapping.data_ptr(), num_tokens, top_k,
+          grad_permuted.shape[1], grad_tokens.data_ptr(), _lib.ptr(status))
+
+
+def zero_empty_expert_grad(first, second, cumulative) -> None:
+    """Zero the per-expert slices whose cumulative row count did not advance."""
+    device = _require_cuda(first, second, cumulative)
+    experts = cumulative.numel()
+    _call("hmc_zero_empty_expert_grad", device, first.data_ptr(), first.numel() // experts * first.element_size(),
+          _lib.ptr(second), 0 if second is None else second.numel() // experts * second.element_size(),
+          cumulative.data_ptr(), experts)
+
+
+def route_offsets(counts_by_source: torch.Tensor, rank: int):
+    """Row-unit push-mode descriptors from the gathered [EP, E] INT32 count table."""
+    device = _require_cuda(counts_by_source)
+    ep, experts = counts_by_source.shape
+    local = experts // ep
+    i64 = dict(dtype=torch.int64, device=device)
+    i32 = dict(dtype=torch.int32, device=device)
+    out = {
+        "dispatch_src_off": torch.empty(experts, **i64),
+        "dispatch_target_off": torch.empty(experts, **i64),
+        "dispatch_size": torch.empty(experts, **i32),
+        "combine_src_off": torch.empty(ep * local, **i64),
+        "combine_target_off": torch.empty(ep * local, **i64),
+        "combine_size": torch.empty(ep * local, **i32),
+        "group_list": torch.empty(local, **i64),
+        "totals": torch.empty(2, **i64),
+    }
+    _call("hmc_route_offsets", device, counts_by_source.contiguous().data_ptr(), ep, experts, rank,
+          *(out[k].data_ptr() for k in ("dispatch_src_off", "dispatch_target_off", "dispatch_size",
+                                        "combine_src_off", "combine_target_off", "combine_size", "group_list",
+                                        "totals")))
+    return out
+
+
+# -------------------------------------------------------------------------------------------- mHC
+def mega_mhc_out(previous_output, residual, previous_pre_mix, previous_post_mix, previous_residual_mix, phi, alpha,
+                 bias, norm_weight, new_residual, next_pre_mix, next_post_mix, next_residual_mix, block_input,
+                 hc_before_norm, inv_rms, sum_out, norm_out, mixed_input, rms_rstd, *, hc_eps, norm_eps, num_iters,
+                 need_backward, status=None) -> None:
+    """Shifted single-pass mHC forward into caller-owned outputs and caches."""
+    device = _require_cuda(previous_output, residual, phi, new_residual)
+    hidden = residual.shape[-1]
+    tokens = residual.numel() // (4 * hidden)
+    lib = _lib.load()
+    workspace = torch.empty(lib.hmc_mega_mhc_workspace_bytes(tokens, hidden), dtype=torch.uint8, device=device)
+    args = _lib.MegaMhcArgs()
+    args.tokens, args.hidden = tokens, hidden
+    for name, tensor in (("previous_output", previous_output), ("residual", residual),
+                         ("previous_pre_mix", previous_pre_mix), ("previous_post_mix", previous_post_mix),
+                         ("previous_residual_mix", previous_residual_mix), ("phi", phi), ("alpha", alpha),
+                         ("bias", bias), ("norm_weight", norm_weight), ("new_residual", new_residual),
+                         ("next_pre_mix", next_pre_mix), ("next_post_mix", next_post_mix),
+                         ("next_residual_mix", next_residual_mix), ("block_input", block_input),
+                         ("hc_before_norm", hc_before_norm), ("inv_rms", inv_rms), ("sum_out", sum_out),
+                         ("norm_out", norm_out), ("mixed_input", mixed_input), ("rms_rstd", rms_rstd),
+                         ("workspace", workspace), ("status", status)):
+        setattr(args, name, _lib.ptr(tensor))
+    args.workspace_bytes = workspace.numel()
+    args.hc_eps, args.norm_eps, args.num_iters, args.need_backward = hc_eps, norm_eps, num_iters, int(need_backward)
+    _call("hmc_mega_mhc", device, ctypes.byref(args))
+
+
+def mega_mhc_grad_out(tensors: dict, *, hc_eps: float, num_iters: int, status=None) -> None:
+    """mHC backward; ``tensors`` maps every pointer field of ``hmc_mega_mhc_grad_args`` to a tensor."""
+    residual = tensors["residual"]
+    device = _require_cuda(residual)
+    hidden = residual.shape[-1]
+    tokens = residual.numel() // (4 * hidden)
+    lib = _lib.load()
+    workspace = torch.empty(lib.hmc_mega_mhc_grad_workspace_bytes(tokens, hidden), dtype=torch.uint8, device=device)
+    args = _lib.MegaMhcGradArgs()
+    args.tokens, args.hidden = tokens, hidden
+    for name, _ in _lib.MegaMhcGradArgs._fields_:  # pylint: disable=protected-access
+        if name in tensors:
+            setattr(args, name, _lib.ptr(tensors[name]))
+    args.workspace = workspace.data_ptr()
+    args.workspace_bytes = workspace.numel()
+    args.hc_eps, args.num_iters = hc_eps, num_iters
+    args.status = _lib.ptr(status)
+    _call("hmc_mega_mhc_grad", device, ctypes.byref(args))

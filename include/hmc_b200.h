@@ -86,6 +86,190 @@ typedef struct hmc_grouped_gemm_args {
 
 int hmc_grouped_gemm(const hmc_grouped_gemm_args* args, void* stream);
 
+/* ------------------------------------------------------------------------------------------
+ * MegaGate.
+ * hmc_gate_route replaces torch.ops.hyper_multicore.mega_gate_route(_out)
+ * (hyper_multicore/torch/csrc/mega_gate_registration.cpp:10-27, checks mega_gate.cpp:40-61, device
+ * pipeline hyper_multicore/ops/hyper_mega_gate/op_kernel/route_pipeline.h:73-562) and extends it
+ * to the softmax and sigmoid scoring of MegaGate._torch_forward
+ * (hyper_multicore/modules/mega_gate/module.py:189-227).
+ * hmc_gate_route_grad replaces mega_gate_route_grad (mega_gate_registration.cpp:29-41,
+ * mega_gate.cpp:132-176, route_grad_pipeline.h:138-191, hyper_mega_gate_route_grad_post.cpp:59-140).
+ * hmc_gate_project is the FP32 router projection F.linear(x.float(), W.float())
+ * (hyper_multicore/modules/mega_gate/function.py:175-178).
+ * ------------------------------------------------------------------------------------------ */
+#define HMC_SCORE_SQRTSOFTPLUS 0
+#define HMC_SCORE_SOFTMAX 1
+#define HMC_SCORE_SIGMOID 2
+
+typedef struct hmc_gate_route_args {
+  const float* logits;       /* [tokens, experts] */
+  const float* text_bias;    /* [experts] selection-only correction bias */
+  const float* vision_bias;  /* [experts], used where image_mask is true */
+  const uint8_t* image_mask; /* [tokens] bool, or NULL when use_vision_bias == 0 */
+  int32_t use_vision_bias;
+  int32_t experts;
+  int32_t top_k;
+  int32_t scoring; /* HMC_SCORE_* */
+  int64_t tokens;
+  float scale; /* routed_scaling_factor */
+  float* weights;      /* out [tokens, top_k] */
+  int64_t* indices;    /* out [tokens, top_k], descending biased score, ties to the lower id */
+  float* route_scores; /* out [tokens, experts] unbiased scores (saved for backward) */
+  float* selected;     /* out [tokens, top_k] unbiased scores of the winners */
+  float* denominator;  /* out [tokens, 1] sum(selected) + 1e-20 */
+} hmc_gate_route_args;
+
+typedef struct hmc_gate_route_grad_args {
+  const float* logits;
+  const float* route_scores;
+  const float* selected;
+  const float* denominator;
+  const int64_t* indices;
+  const float* grad_weights; /* [tokens, top_k] */
+  int32_t experts;
+  int32_t top_k;
+  int32_t scoring;
+  int32_t reserved;
+  int64_t tokens;
+  float scale;
+  float* grad_logits; /* out [tokens, experts] */
+  int32_t* status;    /* optional */
+} hmc_gate_route_grad_args;
+
+int hmc_gate_route(const hmc_gate_route_args* args, void* stream);
+int hmc_gate_route_grad(const hmc_gate_route_grad_args* args, void* stream);
+int hmc_gate_project(const void* x, int x_is_bf16, const void* w, int w_is_bf16, int64_t tokens, int64_t hidden,
+                     int64_t experts, float* logits, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * MoE route preparation and token (un)permutation.
+ * hmc_moe_histogram         : _resolve_counts (hyper_multicore/modules/mega_moe/route.py:186-211)
+ * hmc_moe_sort_routes       : the expert-major permutation index of npu_moe_init_routing_v2 /
+ *                             npu_moe_token_permute (route.py:266-295) as a stable counting sort over
+ *                             the flat index token * top_k + slot; mapping[flat] = destination row
+ * hmc_moe_gather_rows       : payload half of moe_token_permute_out
+ *                             (hyper_multicore/torch/csrc/moe_token_permute_out.cpp:50-60)
+ * hmc_moe_permute_from_mapping : moe_token_permute_from_mapping_out
+ *                             (hyper_multicore/ops/common/mega_moe/utilities.asc:162-209)
+ * hmc_moe_unpermute         : restore_topk_output (route.py:1029-1051), rounding as in the golden
+ *                             (tests/common/multicore/moe_reference.py:179-180)
+ * hmc_moe_unpermute_grad    : mega_moe_unpermute_grad_out (torch/csrc/mega_moe_unpermute.cpp:56-65)
+ * hmc_moe_token_permute_grad: moe_token_permute_grad (torch/csrc/moe_token_permute_grad.cpp:29-38)
+ * hmc_zero_empty_expert_grad: zero_empty_expert_grad_ (torch/csrc/mega_moe_utilities.cpp:64-92)
+ * hmc_route_offsets         : route_offsets / _compute_route_metadata, push mode
+ *                             (route.py:309-390, utilities.asc:89-151); row units
+ * ------------------------------------------------------------------------------------------ */
+int64_t hmc_moe_sort_workspace_bytes(int64_t entries, int64_t experts);
+int hmc_moe_histogram(const void* indices, int indices_are_i64, int64_t entries, int64_t experts, int32_t* counts,
+                      int32_t* status, void* stream);
+int hmc_moe_sort_routes(const void* indices, int indices_are_i64, int64_t entries, int64_t experts, void* workspace,
+                        int64_t workspace_bytes, int32_t* mapping, int32_t* source_of_row, int32_t* expert_of_row,
+                        int32_t* counts, int64_t* cumulative, int32_t* status, void* stream);
+int hmc_moe_gather_rows(const void* tokens, const int32_t* source_of_row, int64_t rows, int64_t top_k,
+                        int64_t hidden, void* out, void* stream);
+int hmc_moe_permute_from_mapping(const void* tokens, const int32_t* mapping, const float* probs, int64_t num_tokens,
+                                 int64_t top_k, int64_t hidden, void* out, float* out_probs, int32_t* status,
+                                 void* stream);
+int hmc_moe_unpermute(const void* permuted, const int32_t* mapping, const float* probs, int64_t num_tokens,
+                      int64_t top_k, int64_t hidden, int64_t permuted_rows, void* out, int32_t* status, void* stream);
+int hmc_moe_unpermute_grad(const void* permuted, const void* grad_out, const int32_t* mapping, const float* probs,
+                           int64_t num_tokens, int64_t top_k, int64_t hidden, void* grad_permuted, float* grad_probs,
+                           int32_t* status, void* stream);
+int hmc_moe_token_permute_grad(const void* grad_permuted, const int32_t* mapping, int64_t num_tokens, int64_t top_k,
+                               int64_t hidden, void* grad_tokens, int32_t* status, void* stream);
+int hmc_zero_empty_expert_grad(void* first, int64_t first_bytes_per_expert, void* second,
+                               int64_t second_bytes_per_expert, const int64_t* cumulative, int64_t experts,
+                               void* stream);
+int hmc_route_offsets(const int32_t* counts, int64_t ep, int64_t experts, int64_t rank, int64_t* dispatch_src_off,
+                      int64_t* dispatch_target_off, int32_t* dispatch_size, int64_t* combine_src_off,
+                      int64_t* combine_target_off, int32_t* combine_size, int64_t* group_list, int64_t* totals,
+                      void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * MegaMHC.
+ * hmc_mega_mhc replaces torch.ops.hyper_multicore.mega_mhc
+ * (hyper_multicore/torch/csrc/registration_mhc.cpp:19-33, mega_mhc.cpp:40-96, device worker
+ * hyper_multicore/ops/hyper_mega_mhc/op_kernel/worker_kernel.cpp:92-268); hmc_mega_mhc_grad replaces
+ * mega_mhc_grad (registration_mhc.cpp:35-49, hyper_multicore/ops/hyper_mega_mhc_grad/op_kernel/
+ * worker_kernel.cpp). Shapes are the flattened token-major ones: activations [tokens, (4,) hidden]
+ * BF16, coefficients FP32. The caller provides scratch (see the *_workspace_bytes functions).
+ * ------------------------------------------------------------------------------------------ */
+typedef struct hmc_mega_mhc_args {
+  int64_t tokens;
+  int64_t hidden;
+  const void* previous_output;        /* [tokens, hidden] bf16 */
+  const void* residual;               /* [tokens, 4, hidden] bf16 */
+  const float* previous_pre_mix;      /* [tokens, 4] */
+  const float* previous_post_mix;     /* [tokens, 4] */
+  const float* previous_residual_mix; /* [tokens, 4, 4] */
+  const float* phi;                   /* [24, 4 * hidden] */
+  const float* alpha;                 /* [3] */
+  const float* bias;                  /* [24] */
+  const void* norm_weight;            /* [hidden] bf16 */
+  void* new_residual;                 /* out [tokens, 4, hidden] bf16 */
+  float* next_pre_mix;                /* out [tokens, 4] */
+  float* next_post_mix;               /* out [tokens, 4] */
+  float* next_residual_mix;           /* out [tokens, 16] */
+  void* block_input;                  /* out [tokens, hidden] bf16 */
+  float* hc_before_norm;              /* cache [tokens, 24], may be NULL when need_backward == 0 */
+  float* inv_rms;                     /* cache [tokens] */
+  float* sum_out;                     /* cache [2 * iters, tokens, 4] or NULL */
+  float* norm_out;                    /* cache [2 * iters, tokens, 16] or NULL */
+  void* mixed_input;                  /* cache [tokens, hidden] bf16 (always written) */
+  float* rms_rstd;                    /* cache [tokens] */
+  void* workspace;
+  int64_t workspace_bytes;
+  float hc_eps;
+  float norm_eps;
+  int32_t num_iters;
+  int32_t need_backward;
+  int32_t* status; /* optional */
+} hmc_mega_mhc_args;
+
+typedef struct hmc_mega_mhc_grad_args {
+  int64_t tokens;
+  int64_t hidden;
+  const void* grad_new_residual;       /* [tokens, 4, hidden] bf16 */
+  const float* grad_next_pre_mix;      /* [tokens, 4] */
+  const float* grad_next_post_mix;     /* [tokens, 4] */
+  const float* grad_next_residual_mix; /* [tokens, 16] */
+  const void* grad_block_input;        /* [tokens, hidden] bf16 */
+  const void* new_residual;            /* forward output */
+  const float* hc_before_norm;         /* forward caches */
+  const float* inv_rms;
+  const void* mixed_input;
+  const float* rms_rstd;
+  const void* previous_output; /* forward inputs */
+  const void* residual;
+  const float* previous_pre_mix;
+  const float* previous_post_mix;
+  const float* previous_residual_mix;
+  const float* phi;
+  const float* alpha;
+  const float* bias;
+  const void* norm_weight;
+  void* grad_residual;               /* out [tokens, 4, hidden] bf16 */
+  float* grad_phi;                   /* out [24, 4 * hidden] */
+  float* grad_alpha;                 /* out [3] */
+  float* grad_bias;                  /* out [24] */
+  void* grad_previous_output;        /* out [tokens, hidden] bf16 */
+  float* grad_previous_pre_mix;      /* out [tokens, 4] */
+  float* grad_previous_post_mix;     /* out [tokens, 4] */
+  float* grad_previous_residual_mix; /* out [tokens, 16] */
+  float* grad_norm_weight;           /* out [hidden] fp32 */
+  void* workspace;
+  int64_t workspace_bytes;
+  float hc_eps;
+  int32_t num_iters;
+  int32_t* status; /* optional */
+} hmc_mega_mhc_grad_args;
+
+int64_t hmc_mega_mhc_workspace_bytes(int64_t tokens, int64_t hidden);
+int64_t hmc_mega_mhc_grad_workspace_bytes(int64_t tokens, int64_t hidden);
+int hmc_mega_mhc(const hmc_mega_mhc_args* args, void* stream);
+int hmc_mega_mhc_grad(const hmc_mega_mhc_grad_args* args, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,151 @@
+"""GPU parity: MegaGate Route / RouteGrad / projection against the oracle and the reference fixtures."""
+
+import pytest
+import torch
+
+from oracle import gate as ogate
+from tests.helpers import load_cases, sorted_sets
+
+pytestmark = pytest.mark.gpu
+
+
+def _route(K, logits, bias, bias_vl, mask, top_k, scale, scoring):
+    dev = logits.device
+    tokens, experts = logits.shape
+    out = dict(
+        weights=torch.empty(tokens, top_k, device=dev), indices=torch.empty(tokens, top_k, dtype=torch.int64, device=dev),
+        route_scores=torch.empty(tokens, experts, device=dev), selected=torch.empty(tokens, top_k, device=dev),
+        denominator=torch.empty(tokens, 1, device=dev))
+    use_vision = mask is not None
+    K.gate_route_out(logits, bias, bias_vl if use_vision else bias, mask, use_vision, top_k, scale, scoring, **out)
+    return out
+
+
+def _check_against(K, dev, logits_cpu, bias, bias_vl, mask, top_k, scale, scoring):
+    ref = ogate.route_from_logits(logits_cpu, bias, bias_vl, mask, top_k, scoring, scale)
+    got = _route(K, logits_cpu.to(dev), bias.to(dev), None if bias_vl is None else bias_vl.to(dev),
+                 None if mask is None else mask.to(dev), top_k, scale, scoring)
+    torch.cuda.synchronize()
+    torch.testing.assert_close(got["route_scores"].cpu(), ref["scores"], rtol=1e-5, atol=1e-6)
+    margin = ogate.topk_margin(ref["biased"], top_k)
+    safe = margin > 1e-6
+    got_idx, got_w = sorted_sets(got["indices"].cpu(), got["weights"].cpu())
+    ref_idx, ref_w = sorted_sets(ref["indices"], ref["weights"])
+    flips = (got_idx != ref_idx).any(dim=-1)
+    assert not (flips & safe).any(), f"{int((flips & safe).sum())} index flips on rows with a clear top-k margin"
+    keep = ~flips
+    torch.testing.assert_close(got_w[keep], ref_w[keep], rtol=1e-5, atol=1e-6)
+    # every row holds top_k distinct experts
+    assert (got_idx[:, 1:] != got_idx[:, :-1]).all()
+    return got, ref, int(flips.sum())
+
+
+@pytest.mark.parametrize("scoring", ["sqrtsoftplus", "softmax", "sigmoid"])
+def test_route_matches_reference_fixture(cuda_device, scoring):
+    from hyper_multicore_b200 import kernels as K
+
+    for case in load_cases("gate"):
+        if case["scoring"] != scoring:
+            continue
+        tokens, hidden, experts, top_k, vision = (int(v) for v in case["config"])
+        scale = float(case["scale"][0])
+        got, _, flips = _check_against(K, cuda_device, case["logits"], case["bias"],
+                                       case["bias_vl"] if vision else None, case["mask"] if vision else None,
+                                       top_k, scale, scoring)
+        assert flips == 0
+        got_idx, got_w = sorted_sets(got["indices"].cpu(), got["weights"].cpu())
+        ref_idx, ref_w = sorted_sets(case["indices"], case["weights"])
+        assert torch.equal(got_idx, ref_idx)
+        torch.testing.assert_close(got_w, ref_w, rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.parametrize("scoring,experts,top_k", [("sqrtsoftplus", 33, 6), ("softmax", 64, 6), ("sigmoid", 256, 8),
+                                                    ("sqrtsoftplus", 384, 1), ("softmax", 1000, 17)])
+@pytest.mark.parametrize("tokens", [1, 17, 129])
+def test_route_shapes(cuda_device, scoring, experts, top_k, tokens):
+    from hyper_multicore_b200 import kernels as K
+
+    torch.manual_seed(experts * 7 + tokens)
+    logits = torch.randn(tokens, experts) * 3
+    bias = torch.empty(experts).uniform_(-0.5, 0.5)
+    bias_vl = torch.empty(experts).uniform_(-0.5, 0.5)
+    mask = torch.rand(tokens) < 0.5
+    _check_against(K, cuda_device, logits, bias, bias_vl, mask, top_k, 2.5, scoring)
+    _check_against(K, cuda_device, logits, bias, None, None, top_k, 1.0, scoring)
+
+
+def test_score_operation_order_edge_values(cuda_device):
+    """Softplus threshold and tiny-exponential branches (tests/torch/_test_mega_gate.py:722-749)."""
+    from hyper_multicore_b200 import kernels as K
+
+    torch.manual_seed(2302)
+    logits = torch.randn(64, 32) * 3
+    logits[0, :8] = torch.tensor([-80.0, -20.0, -1e-7, 0.0, 20.0 - 2 ** -19, 20.0, 20.0 + 2 ** -19, 80.0])
+    zero = torch.zeros(32)
+    got = _route(K, logits.to(cuda_device), zero.to(cuda_device), None, None, 6, 2.5, "sqrtsoftplus")
+    expected = torch.nn.functional.softplus(logits).sqrt()
+    torch.testing.assert_close(got["route_scores"].cpu(), expected, rtol=2e-7, atol=1e-30)
+
+
+def test_exact_ties_take_the_lower_expert(cuda_device):
+    from hyper_multicore_b200 import kernels as K
+
+    logits = torch.zeros(5, 40)
+    got = _route(K, logits.to(cuda_device), torch.zeros(40, device=cuda_device), None, None, 4, 1.0, "sigmoid")
+    assert got["indices"].cpu().tolist() == [[0, 1, 2, 3]] * 5
+    torch.testing.assert_close(got["weights"].cpu(), torch.full((5, 4), 0.25))
+
+
+@pytest.mark.parametrize("scoring", ["sqrtsoftplus", "softmax", "sigmoid"])
+@pytest.mark.parametrize("top_k", [1, 6])
+def test_route_grad_given_identical_forward_state(cuda_device, scoring, top_k):
+    """RouteGrad against torch autograd on the same forward state (tests/torch/_test_mega_gate.py:752-777)."""
+    from hyper_multicore_b200 import kernels as K
+
+    torch.manual_seed(2302)
+    logits = torch.randn(257, 33)
+    ref = ogate.route_from_logits(logits, torch.zeros(33), None, None, top_k, scoring, 2.5)
+    upstream = ((ref["indices"].float() + 1) / 33) / 2
+    expected = ogate.route_grad(logits, ref["indices"], upstream, top_k, scoring, 2.5)
+    grad = torch.empty(257, 33, device=cuda_device)
+    K.gate_route_grad_out(logits.to(cuda_device), ref["scores"].to(cuda_device), ref["selected"].to(cuda_device),
+                          ref["denominator"].to(cuda_device), ref["indices"].to(cuda_device),
+                          upstream.to(cuda_device), top_k, 2.5, scoring, grad)
+    torch.testing.assert_close(grad.cpu(), expected, rtol=1e-5, atol=1e-6)
+
+
+def test_route_grad_matches_reference_fixture(cuda_device):
+    from hyper_multicore_b200 import kernels as K
+
+    for case in load_cases("gate"):
+        tokens, hidden, experts, top_k, vision = (int(v) for v in case["config"])
+        scale = float(case["scale"][0])
+        ref = ogate.route_from_logits(case["logits"], case["bias"], case["bias_vl"] if vision else None,
+                                      case["mask"] if vision else None, top_k, case["scoring"], scale)
+        order = {tuple(sorted(r)) for r in ref["indices"].tolist()}
+        assert order == {tuple(sorted(r)) for r in case["indices"].tolist()}
+        # selected / denominator must follow the fixture's index order for the gradient to line up
+        selected = ref["scores"].gather(1, case["indices"])
+        denominator = selected.sum(dim=-1, keepdim=True) + 1e-20
+        grad = torch.empty(tokens, experts, device=cuda_device)
+        K.gate_route_grad_out(case["logits"].to(cuda_device), ref["scores"].to(cuda_device),
+                              selected.to(cuda_device), denominator.to(cuda_device),
+                              case["indices"].to(cuda_device), case["grad_weights"].to(cuda_device), top_k, scale,
+                              case["scoring"], grad)
+        torch.testing.assert_close(grad.cpu(), case["grad_logits"], rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.parametrize("x_dtype,w_dtype", [(torch.bfloat16, torch.float32), (torch.float32, torch.float32),
+                                              (torch.bfloat16, torch.bfloat16)])
+def test_projection_is_fp32_accurate(cuda_device, x_dtype, w_dtype):
+    from hyper_multicore_b200 import kernels as K
+
+    torch.manual_seed(3)
+    x = torch.randn(200, 1000).to(x_dtype)
+    w = (torch.randn(70, 1000) * 0.02).to(w_dtype)
+    ref = torch.nn.functional.linear(x.double(), w.double()).float()
+    got = K.gate_project(x.to(cuda_device), w.to(cuda_device)).cpu()
+    torch.testing.assert_close(got, ref, rtol=1e-5, atol=1e-6)
+    for case in load_cases("gate"):
+        got = K.gate_project(case["hidden"].to(cuda_device), case["weight"].to(cuda_device)).cpu()
+        torch.testing.assert_close(got, case["logits"], rtol=1e-5, atol=1e-6)

@@ -1,0 +1,156 @@
+"""GPU: tcgen05 grouped GEMM, every operand layout and fused epilogue, against an FP32 torch reference."""
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+RTOL, ATOL = 2e-2, 2e-3  # the reference's MoE tolerance (tests/torch/_test_mega_moe.py:38-39)
+
+
+def _ends(counts, dev):
+    return torch.tensor(counts, dtype=torch.int64).cumsum(0).to(dev)
+
+
+def _starts(counts):
+    return [0] + torch.tensor(counts).cumsum(0).tolist()
+
+
+def _close(got, ref):
+    torch.testing.assert_close(got.float(), ref.float(), rtol=RTOL, atol=ATOL * max(1.0, float(ref.abs().max())))
+
+
+@pytest.mark.parametrize("b_major", [0, 1])
+@pytest.mark.parametrize("counts,k,n", [([128], 64, 256), ([100, 0, 300, 129, 1], 512, 512),
+                                        ([100, 0, 300, 129, 1], 200, 328), ([0, 0, 5], 64, 8),
+                                        ([700, 1, 0, 900], 1024, 2048)])
+def test_ragged_m_plain(cuda_device, b_major, counts, k, n):
+    from hyper_multicore_b200 import _lib, kernels as K
+
+    torch.manual_seed(sum(counts) + k)
+    dev = cuda_device
+    rows, groups, guard = sum(counts), len(counts), 7
+    a = torch.randn(rows + guard, k, device=dev).bfloat16()
+    w = (torch.randn(groups, k, n, device=dev) * 0.05).bfloat16()
+    b = w if b_major == K.HMC_MAJOR_MN else w.transpose(1, 2).contiguous()
+    c = torch.full((rows + guard, n), 7.0, device=dev, dtype=torch.bfloat16)
+    status = _lib.new_status(dev)
+    K.grouped_gemm(a, b, c, _ends(counts, dev), mode=K.HMC_GEMM_RAGGED_M, b_major=b_major, status=status)
+    starts = _starts(counts)
+    ref = torch.cat([a[starts[g]:starts[g + 1]].float() @ w[g].float() for g in range(groups)])
+    _close(c[:rows], ref)
+    assert (c[rows:] == 7).all(), "rows past the last group were written"
+    _lib.raise_on_status(status, "grouped gemm")
+
+
+@pytest.mark.parametrize("b_major", [0, 1])
+@pytest.mark.parametrize("inter", [384, 200])
+def test_ragged_m_swiglu_forward_and_backward_epilogues(cuda_device, b_major, inter):
+    from hyper_multicore_b200 import kernels as K
+
+    torch.manual_seed(inter)
+    dev = cuda_device
+    counts, k = [257, 64, 0, 511], 1024
+    rows, groups = sum(counts), len(counts)
+    starts = _starts(counts)
+    a = torch.randn(rows, k, device=dev).bfloat16()
+    w = (torch.randn(groups, k, 2 * inter, device=dev) * 0.03).bfloat16()
+    b = w if b_major == K.HMC_MAJOR_MN else w.transpose(1, 2).contiguous()
+    u = torch.empty(rows, 2 * inter, device=dev, dtype=torch.bfloat16)
+    act = torch.empty(rows, inter, device=dev, dtype=torch.bfloat16)
+    K.grouped_gemm(a, b, u, _ends(counts, dev), mode=K.HMC_GEMM_RAGGED_M, b_major=b_major,
+                   epilogue=K.HMC_EPI_SWIGLU, aux=act)
+    ref_u = torch.cat([a[starts[g]:starts[g + 1]].float() @ w[g].float() for g in range(groups)])
+    _close(u, ref_u)
+    ub = u.float()  # activation is defined on the BF16-rounded projection
+    _close(act, torch.nn.functional.silu(ub[:, :inter]) * ub[:, inter:])
+    # backward epilogue: acc = dAct = dY @ W2^T, fused SwiGLU gradient against the saved U
+    hidden = 512
+    dy = torch.randn(rows, hidden, device=dev).bfloat16()
+    w2 = (torch.randn(groups, hidden, inter, device=dev) * 0.03).bfloat16()  # logical [K=hidden, N=inter]
+    b2 = w2 if b_major == K.HMC_MAJOR_MN else w2.transpose(1, 2).contiguous()
+    du = torch.empty(rows, 2 * inter, device=dev, dtype=torch.bfloat16)
+    K.grouped_gemm(dy, b2, du, _ends(counts, dev), mode=K.HMC_GEMM_RAGGED_M, b_major=b_major,
+                   epilogue=K.HMC_EPI_SWIGLU_GRAD, aux=u)
+    d_act = torch.cat([dy[starts[g]:starts[g + 1]].float() @ w2[g].float() for g in range(groups)]).bfloat16().float()
+    gate, up = ub[:, :inter], ub[:, inter:]
+    sig = torch.sigmoid(gate)
+    ref_du = torch.cat([d_act * up * sig * (1 + gate * (1 - sig)), d_act * gate * sig], dim=-1)
+    _close(du, ref_du)
+
+
+@pytest.mark.parametrize("f32", [False, True])
+@pytest.mark.parametrize("counts,m,n", [([64], 128, 256), ([128, 0, 65, 1, 300], 256, 512),
+                                        ([128, 0, 65, 1, 300], 200, 328), ([0, 0], 128, 256)])
+def test_ragged_k_weight_gradient(cuda_device, f32, counts, m, n):
+    from hyper_multicore_b200 import kernels as K
+
+    torch.manual_seed(m + n)
+    dev = cuda_device
+    rows, groups = sum(counts), len(counts)
+    a = torch.randn(rows + 5, m, device=dev).bfloat16()
+    b = (torch.randn(rows + 5, n, device=dev) * 0.1).bfloat16()
+    a[rows:] = float("nan")  # rows past the last group must never leak into a product
+    b[rows:] = float("nan")
+    c = torch.full((groups, m, n), 3.0, device=dev, dtype=torch.float32 if f32 else torch.bfloat16)
+    K.grouped_gemm(a, b, c, _ends(counts, dev), mode=K.HMC_GEMM_RAGGED_K,
+                   epilogue=K.HMC_EPI_STORE_F32 if f32 else K.HMC_EPI_STORE_BF16)
+    starts = _starts(counts)
+    ref = torch.stack([a[starts[g]:starts[g + 1]].float().T @ b[starts[g]:starts[g + 1]].float() for g in range(groups)])
+    _close(c, ref)
+    for g, count in enumerate(counts):
+        if count == 0:
+            assert (c[g] == 0).all(), "a cold expert must get an exact-zero gradient"
+
+
+def test_full_size_linearity(cuda_device):
+    """Size-independent property at the benchmark's GEMM1 shape: C(a1 + a2) == C(a1) + C(a2) within BF16."""
+    from hyper_multicore_b200 import kernels as K
+
+    torch.manual_seed(0)
+    dev = cuda_device
+    counts = [512] * 32
+    rows, k, n = sum(counts), 4096, 3072
+    w = (torch.randn(32, k, n, device=dev) * 0.02).bfloat16()
+    a1 = torch.randn(rows, k, device=dev).bfloat16()
+    a2 = (a1 * 0.5).bfloat16()  # exactly representable, so a1 + a2 = 1.5 * a1 has one rounding
+    outs = []
+    for a in (a1, a2, (a1.float() + a2.float()).bfloat16()):
+        c = torch.empty(rows, n, device=dev, dtype=torch.bfloat16)
+        K.grouped_gemm(a, w, c, _ends(counts, dev), mode=K.HMC_GEMM_RAGGED_M)
+        outs.append(c.float())
+    _close(outs[2], outs[0] + outs[1])
+    spot = torch.randint(0, rows, (64,), device=dev)
+    ref = torch.stack([a1[r].float() @ w[int(r) // 512].float() for r in spot])
+    _close(outs[0][spot], ref)
+
+
+def test_arrival_counters_gate_the_groups(cuda_device):
+    """Counters already at their expected value let every group through; a counter that nothing
+    advances makes the bounded wait run out and sets the status words instead of hanging."""
+    from hyper_multicore_b200 import _lib, kernels as K
+
+    dev = cuda_device
+    counts = [130, 70]
+    a = torch.randn(200, 64, device=dev).bfloat16()
+    w = torch.randn(2, 64, 256, device=dev).bfloat16()
+    c = torch.zeros(200, 256, device=dev, dtype=torch.bfloat16)
+    ready = torch.tensor(counts, dtype=torch.int32, device=dev)
+    status = _lib.new_status(dev)
+    K.grouped_gemm(a, w, c, _ends(counts, dev), mode=K.HMC_GEMM_RAGGED_M, ready_counters=ready, status=status,
+                   ready_budget_ns=200_000_000)
+    torch.cuda.synchronize()
+    assert status.tolist()[0] == 0
+    _close(c[:130], a[:130].float() @ w[0].float())
+    ready[1] = 69  # one row of group 1 never "arrives"
+    K.grouped_gemm(a, w, c, _ends(counts, dev), mode=K.HMC_GEMM_RAGGED_M, ready_counters=ready, status=status,
+                   ready_budget_ns=50_000_000)
+    torch.cuda.synchronize()
+    words = status.tolist()
+    assert words[0] == 2 and words[1:4] == [1, 70, 69]
+    # the context is still healthy
+    status.zero_()
+    ready[1] = 70
+    K.grouped_gemm(a, w, c, _ends(counts, dev), mode=K.HMC_GEMM_RAGGED_M, ready_counters=ready, status=status)
+    torch.cuda.synchronize()
+    assert status.tolist()[0] == 0
