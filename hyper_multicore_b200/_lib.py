@@ -127,6 +127,37 @@ class MegaMhcGradArgs(ctypes.Structure):
     ]
 
 
+class EpDispatchArgs(ctypes.Structure):
+    """Mirror of ``hmc_ep_dispatch_args``."""
+
+    _fields_ = [
+        ("tokens", c_void_p), ("source_of_row", c_void_p), ("expert_of_row", c_void_p),
+        ("dispatch_src_off", c_void_p), ("dispatch_target_off", c_void_p),
+        ("rows", c_int64), ("top_k", c_int64), ("hidden", c_int64), ("ep", c_int64), ("local_experts", c_int64),
+        ("capacity_rows", c_int64),
+        ("peer_buffers", c_void_p), ("peer_ctrl", c_void_p), ("local_ctrl", c_void_p),
+        ("generation", c_int32), ("max_ctas", c_int32), ("budget_ns", c_uint64), ("status", c_void_p),
+    ]
+
+
+class EpCombineArgs(ctypes.Structure):
+    """Mirror of ``hmc_ep_combine_args``."""
+
+    _fields_ = [
+        ("results", c_void_p), ("segment_start", c_void_p), ("combine_target_off", c_void_p),
+        ("rows", c_int64), ("hidden", c_int64), ("ep", c_int64), ("local_experts", c_int64),
+        ("target_rows_limit", c_int64),
+        ("peer_buffers", c_void_p), ("peer_ctrl", c_void_p), ("local_ctrl", c_void_p),
+        ("generation", c_int32), ("max_ctas", c_int32), ("budget_ns", c_uint64), ("status", c_void_p),
+    ]
+
+
+HMC_MAX_EP = 16
+HMC_CTRL_ARRIVAL = 0
+HMC_CTRL_COMBINE = 1024
+HMC_CTRL_READY = 1040
+HMC_CTRL_READY_STRIDE = 16
+HMC_CTRL_WORDS = 2048
 HMC_SCORE = {"sqrtsoftplus": 0, "softmax": 1, "sigmoid": 2}
 
 _LIB: ctypes.CDLL | None = None
@@ -155,7 +186,16 @@ SIGNATURES: dict[str, tuple] = {
     "hmc_moe_unpermute_grad": (_I, [_P, _P, _P, _P, _L, _L, _L, _P, _P, _P, _P]),
     "hmc_moe_token_permute_grad": (_I, [_P, _P, _L, _L, _L, _P, _P, _P]),
     "hmc_zero_empty_expert_grad": (_I, [_P, _L, _P, _L, _P, _L, _P]),
-    "hmc_route_offsets": (_I, [_P, _L, _L, _L, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
+    "hmc_route_offsets": (_I, [_P, _L, _L, _L, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
+    "hmc_symm_alloc": (_I, [_L, ctypes.POINTER(c_void_p)]),
+    "hmc_symm_free": (_I, [_P]),
+    "hmc_ipc_get_handle": (_I, [_P, _P]),
+    "hmc_ipc_open_handle": (_I, [_P, ctypes.POINTER(c_void_p)]),
+    "hmc_ipc_close_handle": (_I, [_P]),
+    "hmc_ep_publish_ready": (_I, [_P, _L, _L, _I, _P]),
+    "hmc_ep_dispatch": (_I, [ctypes.POINTER(EpDispatchArgs), _P]),
+    "hmc_ep_combine": (_I, [ctypes.POINTER(EpCombineArgs), _P]),
+    "hmc_ep_wait": (_I, [_P, _I, c_uint64, _P, _P]),
     "hmc_mega_mhc_workspace_bytes": (_L, [_L, _L]),
     "hmc_mega_mhc_grad_workspace_bytes": (_L, [_L, _L]),
     "hmc_mega_mhc": (_I, [ctypes.POINTER(MegaMhcArgs), _P]),

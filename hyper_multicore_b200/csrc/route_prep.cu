@@ -312,7 +312,8 @@ route_offsets_kernel(const int* __restrict__ counts, int ep, int experts, int ra
                      long long* __restrict__ dispatch_src_off, long long* __restrict__ dispatch_target_off,
                      int* __restrict__ dispatch_size, long long* __restrict__ combine_src_off,
                      long long* __restrict__ combine_target_off, int* __restrict__ combine_size,
-                     long long* __restrict__ group_list, long long* __restrict__ totals) {
+                     long long* __restrict__ group_list, long long* __restrict__ totals,
+                     long long* __restrict__ recv_segment_start) {
   const int local = experts / ep;
   for (int s = threadIdx.x; s < ep; s += blockDim.x) {
     // source_prefix[s][e]: first row of expert e in source s's expert-major routed buffer
@@ -337,7 +338,10 @@ route_offsets_kernel(const int* __restrict__ counts, int ep, int experts, int ra
     for (int le = 0; le < local; ++le) {
       for (int s = 0; s < ep; ++s) {
         if (s == rank) dispatch_target_off[d * local + le] = run;
-        if (d == rank) combine_src_off[s * local + le] = run;
+        if (d == rank) {
+          combine_src_off[s * local + le] = run;
+          if (recv_segment_start != nullptr) recv_segment_start[le * ep + s] = run;
+        }
         run += counts[s * experts + d * local + le];
       }
       if (d == rank) group_list[le] = run;
@@ -537,7 +541,8 @@ extern "C" int hmc_zero_empty_expert_grad(void* first, int64_t first_bytes_per_e
 extern "C" int hmc_route_offsets(const int32_t* counts, int64_t ep, int64_t experts, int64_t rank,
                                  int64_t* dispatch_src_off, int64_t* dispatch_target_off, int32_t* dispatch_size,
                                  int64_t* combine_src_off, int64_t* combine_target_off, int32_t* combine_size,
-                                 int64_t* group_list, int64_t* totals, void* stream_ptr) {
+                                 int64_t* group_list, int64_t* totals, int64_t* recv_segment_start,
+                                 void* stream_ptr) {
   HMC_REQUIRE(counts && dispatch_src_off && dispatch_target_off && dispatch_size && combine_src_off &&
                   combine_target_off && combine_size && group_list,
               HMC_ERR_INVALID, "hmc_route_offsets: null tensor pointer");
@@ -551,7 +556,8 @@ extern "C" int hmc_route_offsets(const int32_t* counts, int64_t ep, int64_t expe
       counts, static_cast<int>(ep), static_cast<int>(experts), static_cast<int>(rank),
       reinterpret_cast<long long*>(dispatch_src_off), reinterpret_cast<long long*>(dispatch_target_off),
       dispatch_size, reinterpret_cast<long long*>(combine_src_off), reinterpret_cast<long long*>(combine_target_off),
-      combine_size, reinterpret_cast<long long*>(group_list), reinterpret_cast<long long*>(totals));
+      combine_size, reinterpret_cast<long long*>(group_list), reinterpret_cast<long long*>(totals),
+      reinterpret_cast<long long*>(recv_segment_start));
   HMC_LAUNCH_OK();
   return 0;
 }

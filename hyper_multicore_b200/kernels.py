@@ -242,11 +242,12 @@ def route_offsets(counts_by_source: torch.Tensor, rank: int):
         "combine_size": torch.empty(ep * local, **i32),
         "group_list": torch.empty(local, **i64),
         "totals": torch.empty(2, **i64),
+        "recv_segment_start": torch.empty(ep * local, **i64),
     }
     _call("hmc_route_offsets", device, counts_by_source.contiguous().data_ptr(), ep, experts, rank,
           *(out[k].data_ptr() for k in ("dispatch_src_off", "dispatch_target_off", "dispatch_size",
                                         "combine_src_off", "combine_target_off", "combine_size", "group_list",
-                                        "totals")))
+                                        "totals", "recv_segment_start")))
     return out
 
 
@@ -296,3 +297,49 @@ def mega_mhc_grad_out(tensors: dict, *, hc_eps: float, num_iters: int, status=No
     args.hc_eps, args.num_iters = hc_eps, num_iters
     args.status = _lib.ptr(status)
     _call("hmc_mega_mhc_grad", device, ctypes.byref(args))
+
+
+# --------------------------------------------------------------------------------- EP transport
+def ep_dispatch(tokens, source_of_row, expert_of_row, dispatch_src_off, dispatch_target_off, *, rows, top_k, ep,
+                local_experts, capacity_rows, peer_buffers, peer_ctrl, local_ctrl, generation, status=None,
+                budget_ns=0, max_ctas=0) -> None:
+    """Push expert-major rows (or gathered token rows) into their owners' receive buffers."""
+    device = _require_cuda(tokens, expert_of_row, dispatch_src_off, dispatch_target_off, local_ctrl)
+    args = _lib.EpDispatchArgs()
+    args.tokens = tokens.data_ptr()
+    args.source_of_row = _lib.ptr(source_of_row)
+    args.expert_of_row = expert_of_row.data_ptr()
+    args.dispatch_src_off = dispatch_src_off.data_ptr()
+    args.dispatch_target_off = dispatch_target_off.data_ptr()
+    args.rows, args.top_k, args.hidden = rows, top_k, tokens.shape[1]
+    args.ep, args.local_experts, args.capacity_rows = ep, local_experts, capacity_rows
+    args.peer_buffers = ctypes.cast(peer_buffers, ctypes.c_void_p)
+    args.peer_ctrl = ctypes.cast(peer_ctrl, ctypes.c_void_p)
+    args.local_ctrl = local_ctrl.data_ptr()
+    args.generation, args.max_ctas, args.budget_ns = generation, max_ctas, budget_ns
+    args.status = _lib.ptr(status)
+    _call("hmc_ep_dispatch", device, ctypes.byref(args))
+
+
+def ep_combine(results, segment_start, combine_target_off, *, rows, ep, local_experts, target_rows_limit,
+               peer_buffers, peer_ctrl, local_ctrl, generation, status=None, budget_ns=0, max_ctas=0) -> None:
+    """Return result rows to the routed buffers of their source ranks."""
+    device = _require_cuda(results, segment_start, combine_target_off, local_ctrl)
+    args = _lib.EpCombineArgs()
+    args.results = results.data_ptr()
+    args.segment_start = segment_start.data_ptr()
+    args.combine_target_off = combine_target_off.data_ptr()
+    args.rows, args.hidden, args.ep, args.local_experts = rows, results.shape[1], ep, local_experts
+    args.target_rows_limit = target_rows_limit
+    args.peer_buffers = ctypes.cast(peer_buffers, ctypes.c_void_p)
+    args.peer_ctrl = ctypes.cast(peer_ctrl, ctypes.c_void_p)
+    args.local_ctrl = local_ctrl.data_ptr()
+    args.generation, args.max_ctas, args.budget_ns = generation, max_ctas, budget_ns
+    args.status = _lib.ptr(status)
+    _call("hmc_ep_combine", device, ctypes.byref(args))
+
+
+def ep_wait(counter: torch.Tensor, expected: int, status=None, budget_ns: int = 0) -> None:
+    """Stream-ordered bounded wait until ``counter[0] >= expected``."""
+    device = _require_cuda(counter)
+    _call("hmc_ep_wait", device, counter.data_ptr(), expected, budget_ns, _lib.ptr(status))

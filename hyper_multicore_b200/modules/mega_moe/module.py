@@ -1,0 +1,496 @@
+"""MegaMoeExperts: router-selected SwiGLU experts with expert parallelism, on B200.
+
+Public contract of the reference executor (hyper_multicore/modules/mega_moe/module.py:164-535):
+parameterless module, expert weights borrowed per call in EIO ([e,H,2I],[e,I,H]) or EOI
+([e,2I,H],[e,H,I]) layout, probabilities applied after FC2, one host synchronisation per call
+(the count table), every EP rank calls in the same order.
+
+Data flow of one forward (reference call stack: module.py:497-535, autograd.py:576-679):
+  sort routes -> count all-gather -> offsets -> [per-call counters zeroed, ready published]
+  -> dispatch rows to their owners (peer stores + per-expert arrival counters)
+  -> grouped GEMM1 with fused SwiGLU, gated per expert on the arrival counters -> grouped GEMM2
+  -> combine rows back to their sources -> weighted K-sum in token order.
+Backward mirrors it with dY / dX and the four gradient GEMMs (autograd.py:681-763).
+"""
+
+from __future__ import annotations
+
+import ctypes
+import math
+import struct
+from typing import Any
+
+import torch
+import torch.distributed as dist
+
+from ... import _lib, kernels
+from ...symm import PeerWorkspace, align_rows
+from .numerics import MegaMoeNumericsOptions, MegaMoeSchedulerOptions, MegaMoeTuningOptions
+from .route import PreparedRoute, prepare_route, validate_topk_inputs
+
+_COMMUNICATION_SPLIT = 128
+
+
+class _InvalidExpertWeights(ValueError):
+    """Shape / device / layout error of the borrowed expert weights."""
+
+
+class _InvalidExpertWeightType(TypeError):
+    """dtype error of the borrowed expert weights."""
+
+
+def _validate_swiglu_limit(limit: Any) -> None:
+    ok = limit is None
+    if not ok and isinstance(limit, (int, float)) and not isinstance(limit, bool):
+        try:
+            encoded = struct.unpack("<f", struct.pack("<f", float(limit)))[0]
+            ok = math.isfinite(limit) and math.isfinite(encoded) and encoded > 0
+        except (OverflowError, struct.error):
+            ok = False
+    if not ok:
+        raise ValueError(
+            f"swiglu_limit must be None or a finite positive float32-representable number, got {limit!r}.")
+
+
+def _resolve_ep_size(ep_group: Any | None) -> int:
+    if ep_group is not None:
+        if not dist.is_initialized():
+            raise ValueError("Initialize torch.distributed before passing ep_group")
+        return dist.get_world_size(ep_group)
+    if dist.is_initialized() and dist.get_world_size() > 1:
+        raise ValueError("Pass ep_group explicitly for distributed MegaMoeExperts")
+    return 1
+
+
+def _resolve_options(precision, numerics_options, tuning_options):
+    if numerics_options is not None and not isinstance(numerics_options, MegaMoeNumericsOptions):
+        raise TypeError("numerics_options must be MegaMoeNumericsOptions or None")
+    if tuning_options is not None and not isinstance(tuning_options, MegaMoeTuningOptions):
+        raise TypeError("tuning_options must be MegaMoeTuningOptions or None")
+    numerics = numerics_options or MegaMoeNumericsOptions()
+    tuning = tuning_options or MegaMoeTuningOptions()
+    for name in ("apply_probs_before_fc2", "clamp_after_silu"):
+        if not isinstance(getattr(numerics, name), bool):
+            raise TypeError(f"{name} must be a boolean")
+    if precision not in ("bf16", "mxfp8"):
+        raise ValueError("MegaMoE precision must be bf16 or mxfp8")
+    if precision == "mxfp8" and (numerics.swiglu_limit is not None or numerics.apply_probs_before_fc2):
+        raise ValueError("MXFP8 does not support clamp or before-FC2 probability weighting")
+    if numerics.partial_weight_grad_dtype not in (None, "native", "float32"):
+        raise ValueError("partial_weight_grad_dtype must be native, float32 or None")
+    _validate_swiglu_limit(numerics.swiglu_limit)
+    if tuning.dispatch_mode not in ("push", "pull"):
+        raise ValueError(f"dispatch_mode must be 'push' or 'pull', got {tuning.dispatch_mode!r}")
+    for name in ("initial_capacity_factor", "capacity_growth_factor"):
+        value = getattr(tuning, name)
+        if value is not None:
+            if tuning.dispatch_mode == "pull":
+                raise ValueError("pull dispatch rejects explicit capacity factors")
+            if isinstance(value, bool) or not isinstance(value, (int, float)) or not math.isfinite(value) or value < 1:
+                raise ValueError(f"{name} must be a finite number >= 1, got {value!r}")
+    scheduler = tuning.scheduler or MegaMoeSchedulerOptions()
+    if not isinstance(scheduler, MegaMoeSchedulerOptions):
+        raise TypeError("scheduler must be MegaMoeSchedulerOptions or None")
+    if scheduler.lowering not in ("auto", "dense", "compact"):
+        raise ValueError(f"unknown lowering {scheduler.lowering!r}")
+    # Device-side tile scheduling replaces the reference's host task graph: its Ascend-only knobs
+    # have no counterpart, so only their defaults are accepted.
+    if (scheduler.policy is not None or scheduler.queue_ready_lookahead is not None or scheduler.batch_experts
+            or scheduler.nominal_schedule or scheduler.lowering == "compact"):
+        raise ValueError("scheduler options other than the defaults do not apply to the sm_100a backend")
+    return numerics, tuning
+
+
+class _LocalWorkspace:
+    """Control block of a single-rank executor: rows never leave the GPU, so only the counters,
+    the ready flag and a one-entry peer table are needed."""
+
+    def __init__(self, device: torch.device) -> None:
+        self.device = device
+        self.ep, self.rank, self.group = 1, 0, None
+        self.ctrl = torch.zeros(_lib.HMC_CTRL_WORDS, dtype=torch.int32, device=device)
+        self.peer_ctrl = (ctypes.c_void_p * 1)(self.ctrl.data_ptr())
+        self.generation = 0
+
+    def begin_call(self) -> int:
+        self.generation += 1
+        self.ctrl[:_lib.HMC_CTRL_READY].zero_()
+        with torch.cuda.device(self.device):
+            _lib.check(_lib.load().hmc_ep_publish_ready(self.peer_ctrl, 1, 0, self.generation,
+                                                        _lib.stream_ptr(self.device)))
+        return self.generation
+
+    def close(self) -> None:
+        """Nothing to release explicitly."""
+
+
+class _MegaMoeFunction(torch.autograd.Function):
+    """Forward / backward of the routed expert FFN on already prepared routes."""
+
+    @staticmethod
+    def forward(ctx, hidden, probs, w1, w2, module, route: PreparedRoute):  # pylint: disable=arguments-differ
+        ctx.module = module
+        ctx.route = route
+        out, saved = module._run_forward(hidden, probs, w1, w2, route)  # pylint: disable=protected-access
+        ctx.save_for_backward(hidden, probs, w1, w2, *saved)
+        return out
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, grad_output):  # pylint: disable=arguments-differ
+        hidden, probs, w1, w2, received, up_proj, activation, routed_out = ctx.saved_tensors
+        grads = ctx.module._run_backward(  # pylint: disable=protected-access
+            grad_output.contiguous(), hidden, probs, w1, w2, received, up_proj, activation, routed_out, ctx.route,
+            need_weight_grads=(ctx.needs_input_grad[2], ctx.needs_input_grad[3]))
+        grad_hidden, grad_probs, grad_w1, grad_w2 = grads
+        return (grad_hidden if ctx.needs_input_grad[0] else None,
+                grad_probs if ctx.needs_input_grad[1] else None,
+                grad_w1 if ctx.needs_input_grad[2] else None,
+                grad_w2 if ctx.needs_input_grad[3] else None, None, None)
+
+
+class MegaMoeExperts(torch.nn.Module):
+    """Execute router-selected local experts; the caller owns the expert parameters."""
+
+    def __init__(self, *, hidden_size: int, intermediate_size: int, num_experts: int, top_k: int,
+                 ep_group: Any | None = None, precision: str = "bf16",
+                 numerics_options: MegaMoeNumericsOptions | None = None,
+                 tuning_options: MegaMoeTuningOptions | None = None, expert_placement: Any | None = None) -> None:
+        super().__init__()
+        numerics, tuning = _resolve_options(precision, numerics_options, tuning_options)
+        if expert_placement is not None and getattr(expert_placement, "strategy", "none") != "none":
+            raise ValueError("adaptive expert placement (HotReplica) is not part of the sm_100a backend")
+        ep_size = _resolve_ep_size(ep_group)
+        for name, value in (("hidden_size", hidden_size), ("intermediate_size", intermediate_size),
+                            ("num_experts", num_experts), ("top_k", top_k), ("ep_size", ep_size)):
+            if not isinstance(value, int) or isinstance(value, bool) or value <= 0:
+                raise ValueError(f"{name} must be a positive integer, got {value!r}.")
+        if top_k > num_experts:
+            raise ValueError(f"top_k ({top_k}) cannot exceed num_experts ({num_experts}).")
+        if num_experts % ep_size:
+            raise ValueError(f"num_experts ({num_experts}) must be divisible by ep_size ({ep_size}).")
+        for name, split in (("dispatch_split", tuning.dispatch_split), ("combine_split", tuning.combine_split)):
+            if (not isinstance(split, int) or isinstance(split, bool) or split <= 0
+                    or split % _COMMUNICATION_SPLIT):
+                raise ValueError(
+                    f"{name} must be a positive integer multiple of {_COMMUNICATION_SPLIT}, got {split!r}.")
+        if hidden_size % 8 or intermediate_size % 8:
+            raise ValueError("hidden_size and intermediate_size must be multiples of 8 (16-byte BF16 rows)")
+        if precision == "mxfp8":
+            raise NotImplementedError(
+                "precision='mxfp8' is not available yet in the sm_100a backend; use precision='bf16'")
+        if tuning.dispatch_mode != "push":
+            raise NotImplementedError("dispatch_mode='pull' is not available in the sm_100a backend; use 'push'")
+        if numerics.swiglu_limit is not None or numerics.apply_probs_before_fc2:
+            raise NotImplementedError(
+                "swiglu_limit and apply_probs_before_fc2 are not available yet in the sm_100a backend")
+        self.hidden_size = hidden_size
+        self.intermediate_size = intermediate_size
+        self.num_experts = num_experts
+        self.top_k = top_k
+        self.ep_size = ep_size
+        self.local_experts = num_experts // ep_size
+        self._ep_group = ep_group
+        self._rank = dist.get_rank(ep_group) if ep_group is not None else 0
+        self._precision = precision
+        self._numerics = numerics
+        self._tuning = tuning
+        self._layout: str | None = None
+        self._workspace: PeerWorkspace | _LocalWorkspace | None = None
+        self._status: torch.Tensor | None = None
+        local, hidden, inter = self.local_experts, hidden_size, intermediate_size
+        self._weight_shapes = {
+            "EIO": ((local, hidden, inter * 2), (local, inter, hidden)),
+            "EOI": ((local, inter * 2, hidden), (local, hidden, inter)),
+        }
+
+    # ------------------------------------------------------------------ read-only properties
+    @property
+    def precision(self) -> str:
+        return self._precision
+
+    @property
+    def swiglu_limit(self) -> float | None:
+        return self._numerics.swiglu_limit
+
+    @property
+    def clamp_after_silu(self) -> bool:
+        return self._numerics.clamp_after_silu
+
+    @property
+    def apply_probs_before_fc2(self) -> bool:
+        return self._numerics.apply_probs_before_fc2
+
+    # ------------------------------------------------------------------ validation
+    def _infer_layout(self, shape1, shape2) -> str:
+        for layout, shapes in self._weight_shapes.items():
+            if (shape1, shape2) == shapes:
+                return layout
+        raise _InvalidExpertWeights(
+            f"expert_weights must have EIO shapes {self._weight_shapes['EIO']} or EOI shapes "
+            f"{self._weight_shapes['EOI']}, got {(shape1, shape2)}.")
+
+    def _validate_weights(self, hidden: torch.Tensor, expert_weights) -> None:
+        try:
+            weight1, weight2 = expert_weights
+            shape1, shape2 = tuple(weight1.shape), tuple(weight2.shape)
+        except (AttributeError, TypeError, ValueError) as error:
+            raise _InvalidExpertWeights("expert_weights must contain two tensors") from error
+        if self._layout is None:
+            layout = self._infer_layout(shape1, shape2)
+        else:
+            layout = self._layout
+            expected1, expected2 = self._weight_shapes[layout]
+            if shape1 != expected1:
+                raise _InvalidExpertWeights(f"gate_up_weight must have shape {expected1}, got {shape1}.")
+            if shape2 != expected2:
+                raise _InvalidExpertWeights(f"down_weight must have shape {expected2}, got {shape2}.")
+        if weight1.device != hidden.device or weight2.device != hidden.device:
+            raise _InvalidExpertWeights("expert weights and hidden states must be on the same GPU.")
+        if weight1.dtype != hidden.dtype or weight2.dtype != hidden.dtype:
+            raise _InvalidExpertWeightType("expert weights and hidden states must all use BF16.")
+        if not weight1.is_contiguous() or not weight2.is_contiguous():
+            raise _InvalidExpertWeights("expert weights must be contiguous for zero-copy execution.")
+        self._pending_layout = layout
+
+    def _validate_forward_inputs(self, hidden_states, topk_ids, topk_weights, tokens_per_expert, expert_weights):
+        if not isinstance(hidden_states, torch.Tensor) or hidden_states.dtype != torch.bfloat16 or \
+                not hidden_states.is_cuda:
+            raise TypeError("MegaMoeExperts requires BF16 CUDA hidden states.")
+        if hidden_states.ndim < 2 or hidden_states.shape[-1] != self.hidden_size:
+            raise ValueError(
+                "hidden_states must have at least two dimensions and configured hidden size "
+                f"{self.hidden_size}, got {tuple(hidden_states.shape)}.")
+        hidden_flat = hidden_states.reshape(-1, self.hidden_size)
+        route_shape = (hidden_flat.shape[0], self.top_k)
+        if tuple(topk_ids.shape) != route_shape:
+            raise ValueError(f"topk_ids must have shape {route_shape}, got {tuple(topk_ids.shape)}.")
+        if tuple(topk_weights.shape) != route_shape:
+            raise ValueError(f"topk_weights must have shape {route_shape}, got {tuple(topk_weights.shape)}.")
+        if tokens_per_expert is not None:
+            if tuple(tokens_per_expert.shape) != (self.num_experts,):
+                raise ValueError(
+                    f"tokens_per_expert must have shape ({self.num_experts},), got {tuple(tokens_per_expert.shape)}.")
+            if tokens_per_expert.dtype not in (torch.int32, torch.int64):
+                raise TypeError(f"tokens_per_expert must be int32 or int64, got {tokens_per_expert.dtype}.")
+        validate_topk_inputs(hidden_flat, topk_ids, topk_weights)
+        limit = (2 ** 31 - 1) // max(self.hidden_size, self.top_k)
+        if hidden_flat.shape[0] > limit:
+            raise ValueError(f"token count {hidden_flat.shape[0]} exceeds the INT32 addressing limit {limit}")
+        self._validate_weights(hidden_flat, expert_weights)
+        return hidden_flat.contiguous()
+
+    # ------------------------------------------------------------------ resources
+    def _ensure_workspace(self, device: torch.device, route: PreparedRoute):
+        if self.ep_size == 1:
+            if self._workspace is None:
+                self._workspace = _LocalWorkspace(device)
+            return self._workspace
+        need_capacity, need_routed = route.max_received_rows, route.max_routed_rows
+        workspace = self._workspace
+        if workspace is not None and need_capacity <= workspace.capacity_rows and need_routed <= workspace.routed_rows:
+            return workspace
+        # Every rank sees the same gathered table, so every rank takes this branch together.
+        growth = self._tuning.capacity_growth_factor or 1.25
+        initial = self._tuning.initial_capacity_factor or 1.25
+        if workspace is None:
+            capacity = max(need_capacity, math.ceil(min(initial, self.ep_size) * need_routed))
+            routed = need_routed
+            generation = 0
+        else:
+            capacity = max(need_capacity, math.ceil(workspace.capacity_rows * growth))
+            routed = max(need_routed, workspace.routed_rows)
+            generation = workspace.generation
+            workspace.close()
+        bound = self.ep_size * align_rows(need_routed)
+        capacity = max(need_capacity, min(capacity, bound))
+        self._workspace = PeerWorkspace(self._ep_group, self.hidden_size, capacity, routed, device)
+        self._workspace.generation = generation
+        return self._workspace
+
+    def close(self) -> None:
+        """Release the workspace. Collective over the EP group when ep_size > 1."""
+        if self._workspace is not None:
+            self._workspace.close()
+            self._workspace = None
+
+    def debug_state(self) -> dict:
+        """Workspace sizes and the last device status words (synchronises)."""
+        state = {"layout": self._layout, "ep_size": self.ep_size}
+        if isinstance(self._workspace, PeerWorkspace):
+            state.update(self._workspace.debug_state())
+        if self._status is not None:
+            state["status"] = self._status.tolist()
+        return state
+
+    def check_status(self) -> None:
+        """Raise if a bounded device wait ran out or an index was rejected (synchronises)."""
+        if self._status is not None:
+            _lib.raise_on_status(self._status, "MegaMoeExperts")
+
+    # ------------------------------------------------------------------ forward
+    def forward(self, hidden_states: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor, *,
+                expert_weights: tuple[torch.Tensor, torch.Tensor],
+                tokens_per_expert: torch.Tensor | None = None) -> torch.Tensor:
+        """Route token states through the configured experts; returns the input shape and dtype."""
+        weight_error: Exception | None = None
+        try:
+            hidden_flat = self._validate_forward_inputs(hidden_states, topk_ids, topk_weights, tokens_per_expert,
+                                                        expert_weights)
+        except (_InvalidExpertWeights, _InvalidExpertWeightType) as error:
+            if self.ep_size == 1:
+                raise
+            # A rank-local weight error is deferred until every rank has joined the count
+            # exchange, so that no peer is left waiting (reference: module.py:474-495).
+            weight_error = error
+            hidden_flat = hidden_states.reshape(-1, self.hidden_size).contiguous()
+        if torch.cuda.is_current_stream_capturing():
+            raise RuntimeError("MegaMoe dynamic tokens and workspace growth do not support graph capture")
+        device = hidden_flat.device
+        if self._status is None:
+            self._status = _lib.new_status(device)
+        route = prepare_route(hidden_flat, topk_ids.contiguous(), num_experts=self.num_experts, top_k=self.top_k,
+                              ep_size=self.ep_size, rank=self._rank, group=self._ep_group,
+                              invalid=weight_error is not None, status=self._status)
+        if weight_error is not None:
+            raise weight_error
+        # prepare_route just synchronised with the device, so earlier kernels' status words are final
+        self.check_status()
+        if self._layout is None:
+            self._layout = self._pending_layout
+        self._ensure_workspace(device, route)
+        weight1, weight2 = expert_weights
+        probs = topk_weights if topk_weights.dtype == torch.float32 else topk_weights.float()
+        out = _MegaMoeFunction.apply(hidden_flat, probs.contiguous(), weight1, weight2, self, route)
+        return out.reshape(hidden_states.shape)
+
+    def _peer_tables(self, workspace, expert_buffer: torch.Tensor):
+        if isinstance(workspace, PeerWorkspace):
+            return workspace.peer_expert, workspace.peer_routed, workspace.peer_ctrl
+        return (ctypes.c_void_p * 1)(expert_buffer.data_ptr()), None, workspace.peer_ctrl
+
+    def _run_forward(self, hidden, probs, w1, w2, route: PreparedRoute):
+        workspace = self._workspace
+        device = hidden.device
+        eio = self._layout == "EIO"
+        b_major = kernels.HMC_MAJOR_MN if eio else kernels.HMC_MAJOR_K
+        received, routed_rows = route.received_rows, route.routed_rows
+        inter, hid = self.intermediate_size, self.hidden_size
+        bf16 = dict(dtype=torch.bfloat16, device=device)
+        generation = workspace.begin_call()
+        if self.ep_size == 1:
+            expert_buffer = torch.empty(max(received, 1), hid, **bf16)
+            capacity = expert_buffer.shape[0]
+        else:
+            expert_buffer = workspace.expert_buffer
+            capacity = workspace.capacity_rows
+        peer_expert, peer_routed, peer_ctrl = self._peer_tables(workspace, expert_buffer)
+        off = route.offsets
+        kernels.ep_dispatch(hidden, route.source_of_row, route.expert_of_row, off["dispatch_src_off"],
+                            off["dispatch_target_off"], rows=routed_rows, top_k=self.top_k, ep=self.ep_size,
+                            local_experts=self.local_experts, capacity_rows=capacity, peer_buffers=peer_expert,
+                            peer_ctrl=peer_ctrl, local_ctrl=workspace.ctrl, generation=generation,
+                            status=self._status)
+        rows = max(received, 1)
+        up_proj = torch.empty(rows, 2 * inter, **bf16)
+        activation = torch.empty(rows, inter, **bf16)
+        down_proj = torch.empty(rows, hid, **bf16)
+        x_recv = expert_buffer[:rows]
+        arrival = workspace.ctrl[_lib.HMC_CTRL_ARRIVAL:_lib.HMC_CTRL_ARRIVAL + self.local_experts]
+        if received > 0:
+            kernels.grouped_gemm(x_recv, w1, up_proj, off["group_list"], mode=kernels.HMC_GEMM_RAGGED_M,
+                                 b_major=b_major, epilogue=kernels.HMC_EPI_SWIGLU, aux=activation,
+                                 ready_counters=arrival, status=self._status)
+            kernels.grouped_gemm(activation, w2, down_proj, off["group_list"], mode=kernels.HMC_GEMM_RAGGED_M,
+                                 b_major=b_major, status=self._status)
+        if self.ep_size == 1:
+            routed_out = down_proj
+            saved_received = x_recv
+        else:
+            kernels.ep_combine(down_proj, off["recv_segment_start"], off["combine_target_off"], rows=received,
+                               ep=self.ep_size, local_experts=self.local_experts,
+                               target_rows_limit=workspace.routed_rows, peer_buffers=peer_routed,
+                               peer_ctrl=peer_ctrl, local_ctrl=workspace.ctrl, generation=generation,
+                               status=self._status)
+            kernels.ep_wait(workspace.ctrl[_lib.HMC_CTRL_COMBINE:], routed_rows, status=self._status)
+            # Owned copies: the symmetric buffers are rewritten by the next call on any rank
+            # (reference: autograd.py:655-663 saves a dispatch copy and clones the combine output).
+            routed_out = workspace.routed_buffer[:max(routed_rows, 1)].clone()
+            saved_received = x_recv.clone()
+        out = torch.empty(hidden.shape[0], hid, **bf16)
+        kernels.moe_unpermute(routed_out, route.mapping, probs, hidden.shape[0], self.top_k, out,
+                              status=self._status)
+        return out, (saved_received, up_proj, activation, routed_out)
+
+    def _run_backward(self, grad_output, hidden, probs, w1, w2, received_x, up_proj, activation, routed_out,
+                      route: PreparedRoute, need_weight_grads):
+        workspace = self._workspace
+        device = hidden.device
+        eio = self._layout == "EIO"
+        received, routed_rows = route.received_rows, route.routed_rows
+        inter, hid = self.intermediate_size, self.hidden_size
+        bf16 = dict(dtype=torch.bfloat16, device=device)
+        off = route.offsets
+        tokens = hidden.shape[0]
+        # dYe (source's expert-major order) and dProbs
+        grad_routed = torch.empty(max(routed_rows, 1), hid, **bf16)
+        grad_probs = torch.empty(tokens, self.top_k, dtype=torch.float32, device=device)
+        kernels.moe_unpermute_grad(routed_out, grad_output, route.mapping, probs, self.top_k, grad_routed,
+                                   grad_probs, status=self._status)
+        generation = workspace.begin_call()
+        if self.ep_size == 1:
+            expert_buffer = torch.empty(max(received, 1), hid, **bf16)
+            capacity = expert_buffer.shape[0]
+        else:
+            expert_buffer = workspace.expert_buffer
+            capacity = workspace.capacity_rows
+        peer_expert, peer_routed, peer_ctrl = self._peer_tables(workspace, expert_buffer)
+        kernels.ep_dispatch(grad_routed, None, route.expert_of_row, off["dispatch_src_off"],
+                            off["dispatch_target_off"], rows=routed_rows, top_k=self.top_k, ep=self.ep_size,
+                            local_experts=self.local_experts, capacity_rows=capacity, peer_buffers=peer_expert,
+                            peer_ctrl=peer_ctrl, local_ctrl=workspace.ctrl, generation=generation,
+                            status=self._status)
+        rows = max(received, 1)
+        dy_recv = expert_buffer[:rows]
+        arrival = workspace.ctrl[_lib.HMC_CTRL_ARRIVAL:_lib.HMC_CTRL_ARRIVAL + self.local_experts]
+        grad_up = torch.empty(rows, 2 * inter, **bf16)
+        grad_x_rows = torch.empty(rows, hid, **bf16)
+        f32_partials = self._numerics.partial_weight_grad_dtype == "float32"
+        wdtype = torch.float32 if f32_partials else torch.bfloat16
+        wepi = kernels.HMC_EPI_STORE_F32 if f32_partials else kernels.HMC_EPI_STORE_BF16
+        grad_w1 = torch.empty(w1.shape, dtype=wdtype, device=device) if need_weight_grads[0] else None
+        grad_w2 = torch.empty(w2.shape, dtype=wdtype, device=device) if need_weight_grads[1] else None
+        # Transposed use of the weights: EIO W2 [e, I, H] is the K-major B of dA = dY . W2^T; EOI the reverse.
+        bt_major = kernels.HMC_MAJOR_K if eio else kernels.HMC_MAJOR_MN
+        if received > 0:
+            kernels.grouped_gemm(dy_recv, w2, grad_up, off["group_list"], mode=kernels.HMC_GEMM_RAGGED_M,
+                                 b_major=bt_major, epilogue=kernels.HMC_EPI_SWIGLU_GRAD, aux=up_proj,
+                                 ready_counters=arrival, status=self._status)
+            kernels.grouped_gemm(grad_up, w1, grad_x_rows, off["group_list"], mode=kernels.HMC_GEMM_RAGGED_M,
+                                 b_major=bt_major, status=self._status)
+        if grad_w2 is not None:
+            # The arrival wait of the dA GEMM above orders this kernel after the rows have landed.
+            a_op, b_op = (activation, dy_recv) if eio else (dy_recv, activation)
+            kernels.grouped_gemm(a_op, b_op, grad_w2, off["group_list"], mode=kernels.HMC_GEMM_RAGGED_K, epilogue=wepi,
+                                 status=self._status)
+        if grad_w1 is not None:
+            a_op, b_op = (received_x, grad_up) if eio else (grad_up, received_x)
+            kernels.grouped_gemm(a_op, b_op, grad_w1, off["group_list"], mode=kernels.HMC_GEMM_RAGGED_K, epilogue=wepi,
+                                 status=self._status)
+        if self.ep_size == 1:
+            returned = grad_x_rows
+        else:
+            kernels.ep_combine(grad_x_rows, off["recv_segment_start"], off["combine_target_off"], rows=received,
+                               ep=self.ep_size, local_experts=self.local_experts,
+                               target_rows_limit=workspace.routed_rows, peer_buffers=peer_routed,
+                               peer_ctrl=peer_ctrl, local_ctrl=workspace.ctrl, generation=generation,
+                               status=self._status)
+            kernels.ep_wait(workspace.ctrl[_lib.HMC_CTRL_COMBINE:], routed_rows, status=self._status)
+            returned = workspace.routed_buffer
+        grad_hidden = torch.empty(tokens, hid, **bf16)
+        kernels.moe_token_permute_grad(returned, route.mapping, tokens, self.top_k, grad_hidden, status=self._status)
+        if grad_w1 is not None and grad_w1.dtype != w1.dtype:
+            grad_w1 = grad_w1.to(w1.dtype)
+        if grad_w2 is not None and grad_w2.dtype != w2.dtype:
+            grad_w2 = grad_w2.to(w2.dtype)
+        return grad_hidden, grad_probs, grad_w1, grad_w2

@@ -1,0 +1,151 @@
+"""Peer-mapped workspace for expert parallelism: one cudaMalloc per rank, CUDA-IPC handles
+exchanged once through torch.distributed, raw peer pointers handed to the kernels.
+
+This is the CUDA counterpart of the reference's symmetric heap for the MoE path
+(hyper_multicore/shmem/_api.py:77-182, hyper_multicore/modules/mega_moe/workspace.py:48-75,
+409-470): a receive buffer for dispatched rows, a routed buffer for returning rows, and a control
+block with per-expert arrival counters, the combine counter and persistent ready flags.
+NCCL / Gloo is used only for the handle exchange.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from typing import Any
+
+import torch
+import torch.distributed as dist
+
+from . import _lib
+
+_ALIGN_ROWS = 128
+
+
+def align_rows(rows: int) -> int:
+    """Round a row capacity up to the 128-row communication split the reference uses."""
+    return max(_ALIGN_ROWS, (rows + _ALIGN_ROWS - 1) // _ALIGN_ROWS * _ALIGN_ROWS)
+
+
+class _DeviceSpan:
+    """Expose raw device memory to torch through __cuda_array_interface__ (no copy)."""
+
+    def __init__(self, address: int, nbytes: int, owner: Any) -> None:
+        self.owner = owner
+        self.__cuda_array_interface__ = {
+            "shape": (nbytes,), "typestr": "|u1", "data": (address, False), "version": 3, "strides": None,
+        }
+
+
+class PeerWorkspace:
+    """Symmetric allocation of one EP group member, with every peer's copy mapped locally."""
+
+    def __init__(self, group: Any | None, hidden_size: int, capacity_rows: int, routed_rows: int,
+                 device: torch.device) -> None:
+        self.group = group
+        self.device = device
+        self.hidden_size = hidden_size
+        self.ep = dist.get_world_size(group) if group is not None else 1
+        self.rank = dist.get_rank(group) if group is not None else 0
+        if self.ep > _lib.HMC_MAX_EP:
+            raise ValueError(f"expert-parallel size {self.ep} exceeds the supported maximum {_lib.HMC_MAX_EP}")
+        self.capacity_rows = align_rows(capacity_rows)
+        self.routed_rows = align_rows(routed_rows)
+        self.generation = 0
+        self._base = ctypes.c_void_p()
+        self._peer_bases: list[int] = []
+        self._opened: list[int] = []
+        self._closed = False
+        row_bytes = hidden_size * 2
+        self._ctrl_bytes = _lib.HMC_CTRL_WORDS * 4
+        self._expert_off = (self._ctrl_bytes + 1023) // 1024 * 1024
+        self._routed_off = self._expert_off + self.capacity_rows * row_bytes
+        self.nbytes = self._routed_off + self.routed_rows * row_bytes
+        lib = _lib.load()
+        with torch.cuda.device(device):
+            _lib.check(lib.hmc_symm_alloc(self.nbytes, ctypes.byref(self._base)))
+            self._exchange_handles(lib)
+        span = torch.as_tensor(_DeviceSpan(self._base.value, self.nbytes, self), device=device)
+        self._bytes = span
+        self.ctrl = span[:self._ctrl_bytes].view(torch.int32)
+        self.expert_buffer = span[self._expert_off:self._routed_off].view(torch.bfloat16).view(
+            self.capacity_rows, hidden_size)
+        self.routed_buffer = span[self._routed_off:self.nbytes].view(torch.bfloat16).view(
+            self.routed_rows, hidden_size)
+        pointer_array = ctypes.c_void_p * self.ep
+        self.peer_ctrl = pointer_array(*self._peer_bases)
+        self.peer_expert = pointer_array(*(base + self._expert_off for base in self._peer_bases))
+        self.peer_routed = pointer_array(*(base + self._routed_off for base in self._peer_bases))
+
+    def _exchange_handles(self, lib: ctypes.CDLL) -> None:
+        if self.ep == 1:
+            self._peer_bases = [self._base.value]
+            return
+        handle = (ctypes.c_ubyte * 64)()
+        _lib.check(lib.hmc_ipc_get_handle(self._base, handle))
+        gathered: list[Any] = [None] * self.ep
+        dist.all_gather_object(gathered, (bytes(handle), self.nbytes), group=self.group)
+        for peer, (peer_handle, peer_bytes) in enumerate(gathered):
+            if peer_bytes != self.nbytes:
+                raise RuntimeError("EP ranks disagree on the symmetric workspace size")
+            if peer == self.rank:
+                self._peer_bases.append(self._base.value)
+                continue
+            mapped = ctypes.c_void_p()
+            raw = (ctypes.c_ubyte * 64).from_buffer_copy(peer_handle)
+            _lib.check(lib.hmc_ipc_open_handle(raw, ctypes.byref(mapped)))
+            self._peer_bases.append(mapped.value)
+            self._opened.append(mapped.value)
+        # every rank has mapped every peer before anyone may write remotely
+        dist.barrier(group=self.group)
+
+    def next_generation(self) -> int:
+        """Generation number of the next operator call (same sequence on every rank)."""
+        self.generation += 1
+        return self.generation
+
+    def begin_call(self) -> int:
+        """Zero the per-call counters on the current stream, then tell every peer this rank's
+        buffers are free for the new generation. Returns the generation."""
+        generation = self.next_generation()
+        self.ctrl[:_lib.HMC_CTRL_READY].zero_()
+        lib = _lib.load()
+        with torch.cuda.device(self.device):
+            _lib.check(lib.hmc_ep_publish_ready(self.peer_ctrl, self.ep, self.rank, generation,
+                                                _lib.stream_ptr(self.device)))
+        return generation
+
+    def debug_state(self) -> dict:
+        """Sizes, peer map and the current control words (synchronises the device)."""
+        words = self.ctrl.tolist()
+        return {
+            "ep": self.ep, "rank": self.rank, "bytes": self.nbytes, "capacity_rows": self.capacity_rows,
+            "routed_rows": self.routed_rows, "generation": self.generation,
+            "peer_bases": [hex(p) for p in self._peer_bases],
+            "combine_counter": words[_lib.HMC_CTRL_COMBINE],
+            "ready": [words[_lib.HMC_CTRL_READY + p * _lib.HMC_CTRL_READY_STRIDE] for p in range(self.ep)],
+        }
+
+    def close(self) -> None:
+        """Unmap peers and free the local allocation. Collective for ep > 1."""
+        if self._closed:
+            return
+        self._closed = True
+        lib = _lib.load()
+        with torch.cuda.device(self.device):
+            torch.cuda.synchronize(self.device)
+            if self.ep > 1 and dist.is_initialized():
+                dist.barrier(group=self.group)  # no peer may still be writing into this rank
+            for mapped in self._opened:
+                lib.hmc_ipc_close_handle(ctypes.c_void_p(mapped))
+            if self.ep > 1 and dist.is_initialized():
+                dist.barrier(group=self.group)
+            lib.hmc_symm_free(self._base)
+        self._opened = []
+
+    def __del__(self) -> None:
+        # Collective teardown cannot run from a finaliser; only a single-rank workspace frees itself.
+        if not self._closed and self.ep == 1:
+            try:
+                self.close()
+            except Exception:  # pylint: disable=broad-except
+                pass

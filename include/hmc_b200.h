@@ -59,7 +59,7 @@ int hmc_worker_queue_layout_version(void);
 #define HMC_MAJOR_K 0       /* operand stored with the contraction index contiguous */
 #define HMC_MAJOR_MN 1      /* operand stored with the M/N index contiguous */
 #define HMC_EPI_STORE_BF16 0
-#define HMC_EPI_STORE_F32 1   /* RAGGED_K only: FP32 partial weight gradients */
+#define HMC_EPI_STORE_F32 1   /* FP32 output (partial weight gradients, mHC projection) */
 #define HMC_EPI_SWIGLU 2      /* B has 2n columns [gate | up]; c = U[rows, 2n], aux = Act[rows, n] */
 #define HMC_EPI_SWIGLU_GRAD 3 /* acc = dAct[rows, n]; aux = U[rows, 2n] (input); c = dU[rows, 2n] */
 
@@ -158,7 +158,9 @@ int hmc_gate_project(const void* x, int x_is_bf16, const void* w, int w_is_bf16,
  * hmc_moe_token_permute_grad: moe_token_permute_grad (torch/csrc/moe_token_permute_grad.cpp:29-38)
  * hmc_zero_empty_expert_grad: zero_empty_expert_grad_ (torch/csrc/mega_moe_utilities.cpp:64-92)
  * hmc_route_offsets         : route_offsets / _compute_route_metadata, push mode
- *                             (route.py:309-390, utilities.asc:89-151); row units
+ *                             (route.py:309-390, utilities.asc:89-151); row units. totals =
+ *                             {rows routed by this rank, rows received by this rank};
+ *                             recv_segment_start[le * ep + s] = first received row of (le, s)
  * ------------------------------------------------------------------------------------------ */
 int64_t hmc_moe_sort_workspace_bytes(int64_t entries, int64_t experts);
 int hmc_moe_histogram(const void* indices, int indices_are_i64, int64_t entries, int64_t experts, int32_t* counts,
@@ -184,7 +186,7 @@ int hmc_zero_empty_expert_grad(void* first, int64_t first_bytes_per_expert, void
 int hmc_route_offsets(const int32_t* counts, int64_t ep, int64_t experts, int64_t rank, int64_t* dispatch_src_off,
                       int64_t* dispatch_target_off, int32_t* dispatch_size, int64_t* combine_src_off,
                       int64_t* combine_target_off, int32_t* combine_size, int64_t* group_list, int64_t* totals,
-                      void* stream);
+                      int64_t* recv_segment_start, void* stream);
 
 /* ------------------------------------------------------------------------------------------
  * MegaMHC.
@@ -269,6 +271,78 @@ int64_t hmc_mega_mhc_workspace_bytes(int64_t tokens, int64_t hidden);
 int64_t hmc_mega_mhc_grad_workspace_bytes(int64_t tokens, int64_t hidden);
 int hmc_mega_mhc(const hmc_mega_mhc_args* args, void* stream);
 int hmc_mega_mhc_grad(const hmc_mega_mhc_grad_args* args, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Expert-parallel transport over CUDA-IPC peer mappings (one process per GPU, one box).
+ * Replaces the reference's private SHMEM heap and its device data plane on the MoE path:
+ * shmem.empty/free (hyper_multicore/shmem/_api.py:77-182), dispatch / combine PUT tasks with
+ * per-expert signal ADD (hyper_multicore/ops/hyper_mega_moe/op_kernel/worker_kernel.cpp:301-366,
+ * hyper_multicore/ops/common/mega_moe/transport_task.h:37-79, hyper_multicore/tasks/alltoall.py:
+ * 90-157) and the ready handshake (ops/common/mega_moe/invocation_protocol.h:9-52).
+ *
+ * Control block (int32 words, one per rank, inside the peer-mapped allocation):
+ *   [HMC_CTRL_ARRIVAL + e]              rows that have landed for local expert e (zeroed per call)
+ *   [HMC_CTRL_COMBINE]                  result rows that have come back to this source (zeroed per call)
+ *   [HMC_CTRL_READY + p * STRIDE]       last generation peer p declared itself ready for (never zeroed)
+ * ------------------------------------------------------------------------------------------ */
+#define HMC_MAX_EP 16
+#define HMC_IPC_HANDLE_BYTES 64
+#define HMC_CTRL_ARRIVAL 0
+#define HMC_CTRL_MAX_LOCAL_EXPERTS 1024
+#define HMC_CTRL_COMBINE 1024
+#define HMC_CTRL_READY 1040
+#define HMC_CTRL_READY_STRIDE 16
+#define HMC_CTRL_WORDS 2048
+
+typedef struct hmc_ep_dispatch_args {
+  const void* tokens;            /* [num_tokens, hidden] bf16, or expert-major rows when source_of_row is NULL */
+  const int32_t* source_of_row;  /* [rows] flat (token * top_k + slot) index of each expert-major row, or NULL */
+  const int32_t* expert_of_row;  /* [rows] global expert of each expert-major row */
+  const int64_t* dispatch_src_off;    /* [experts] rows, from hmc_route_offsets */
+  const int64_t* dispatch_target_off; /* [experts] rows */
+  int64_t rows;                  /* tokens * top_k */
+  int64_t top_k;
+  int64_t hidden;
+  int64_t ep;
+  int64_t local_experts;
+  int64_t capacity_rows;         /* rows each peer's receive buffer can hold */
+  void* const* peer_buffers;     /* host array [ep]: receive buffer of every rank, as mapped here */
+  void* const* peer_ctrl;        /* host array [ep]: control block of every rank, as mapped here */
+  const int32_t* local_ctrl;     /* this rank's own control block */
+  int32_t generation;
+  int32_t max_ctas;              /* 0 = default */
+  uint64_t budget_ns;            /* bound of the ready wait, 0 = 10 s */
+  int32_t* status;
+} hmc_ep_dispatch_args;
+
+typedef struct hmc_ep_combine_args {
+  const void* results;               /* [rows, hidden] bf16 in the owner's receive layout */
+  const int64_t* segment_start;      /* [local_experts * ep] first row of (local expert, source), buffer order */
+  const int64_t* combine_target_off; /* [ep * local_experts] rows, from hmc_route_offsets */
+  int64_t rows;
+  int64_t hidden;
+  int64_t ep;
+  int64_t local_experts;
+  int64_t target_rows_limit;     /* rows each source's routed buffer can hold */
+  void* const* peer_buffers;     /* host array [ep]: routed (combine target) buffer of every rank */
+  void* const* peer_ctrl;
+  const int32_t* local_ctrl;
+  int32_t generation;
+  int32_t max_ctas;
+  uint64_t budget_ns;
+  int32_t* status;
+} hmc_ep_combine_args;
+
+int hmc_symm_alloc(int64_t bytes, void** out); /* cudaMalloc + zero; set-up time only */
+int hmc_symm_free(void* ptr);
+int hmc_ipc_get_handle(void* ptr, void* handle_out_64_bytes);
+int hmc_ipc_open_handle(const void* handle_64_bytes, void** out);
+int hmc_ipc_close_handle(void* ptr);
+int hmc_ep_publish_ready(void* const* peer_ctrl, int64_t ep, int64_t rank, int32_t generation, void* stream);
+int hmc_ep_dispatch(const hmc_ep_dispatch_args* args, void* stream);
+int hmc_ep_combine(const hmc_ep_combine_args* args, void* stream);
+/* Bounded device-side wait until *counter >= expected; on time-out writes HMC_STATUS_TIMEOUT_ARRIVAL. */
+int hmc_ep_wait(const int32_t* counter, int32_t expected, uint64_t budget_ns, int32_t* status, void* stream);
 
 #ifdef __cplusplus
 }
