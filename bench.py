@@ -1,0 +1,361 @@
+"""Benchmark of the MegaMoE layer hot path on B200: tokens/s of forward + backward.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+N = 1 runs the per-rank problem of the expert-parallel BF16 configuration on one GPU (EP = 1):
+4096 tokens, hidden 4096, 32 experts, softmax top-4, SwiGLU experts with intermediate 1536.
+Under torchrun (N > 1) every rank brings its own 4096 tokens and owns 32 / N experts (EP = N,
+weak scaling); rows travel through the peer-mapped buffers, NCCL carries only the count table.
+
+One JSON line is printed by rank 0. `value` times the layer with inputs resident in HBM; `e2e`
+times the same call through the module API with host buffers (pinned host -> device copies of the
+step's inputs and device -> host copies of its results inside the timed region).
+`--impl reference` times the CPU restatement of the reference's golden path on the host cores.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+TOKENS, HIDDEN, EXPERTS, TOP_K, INTER = 4096, 4096, 32, 4, 1536
+METRIC = "moe_layer_fwd_bwd_tokens_per_s"
+UNIT = "tokens/s"
+# forward 6*K*H*I flops per token (two GEMMs), backward 12*K*H*I (four GEMMs)
+FLOPS_PER_TOKEN = 18 * TOP_K * HIDDEN * INTER
+
+# DRAM bytes (read + write) per step of the six grouped-GEMM launches, from an ncu capture of this
+# workload's kernels; None until a capture has been summarised under profiles/.
+GEMM_DRAM_BYTES_PER_STEP = None
+
+
+def make_inputs(rank: int, ep: int):
+    """Seeded synthetic inputs of the configuration's shapes and distributions (CPU, then copied)."""
+    g = torch.Generator().manual_seed(1234 + rank)
+    x = torch.randn(TOKENS, HIDDEN, generator=g).bfloat16()
+    # "uniform-ish" router logits: U(-1, 1) plus small noise, softmax, top-4
+    logits = torch.rand(TOKENS, EXPERTS, generator=g) * 2 - 1 + 0.01 * torch.randn(TOKENS, EXPERTS, generator=g)
+    weights, ids = torch.topk(logits.softmax(dim=-1), TOP_K, dim=-1)
+    grad_out = torch.randn(TOKENS, HIDDEN, generator=g).bfloat16()
+    local = EXPERTS // ep
+    gw = torch.Generator().manual_seed(4321 + rank)
+    w1 = (torch.randn(local, HIDDEN, 2 * INTER, generator=gw) * 0.02).bfloat16()
+    w2 = (torch.randn(local, INTER, HIDDEN, generator=gw) * 0.02).bfloat16()
+    return x, ids, weights.contiguous(), grad_out, w1, w2
+
+
+def config(ep: int) -> dict:
+    return {
+        "workload": (f"MegaMoE BF16 forward+backward, EP={ep}, {TOKENS} tokens/rank, hidden {HIDDEN}, "
+                     f"{EXPERTS} experts ({EXPERTS // ep}/rank), softmax top-{TOP_K}, SwiGLU intermediate {INTER}"),
+        "tokens_per_rank": TOKENS, "hidden": HIDDEN, "experts": EXPERTS, "top_k": TOP_K, "intermediate": INTER,
+        "ep": ep, "layout": "EIO",
+        "l2": "no flush: each step streams >1.4 GB of weights and activations through the 126 MB L2",
+    }
+
+
+# ----------------------------------------------------------------------------------- CPU baseline
+def cpu_baseline(sample_tokens: int, iterations: int) -> dict:
+    """Time the oracle (port of the reference's TorchExperts CPU branch) on a token subsample."""
+    from oracle import moe as omoe
+
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    x, ids, weights, grad_out, w1, w2 = make_inputs(0, 1)
+    x, ids, weights, grad_out = x[:sample_tokens], ids[:sample_tokens], weights[:sample_tokens], grad_out[:sample_tokens]
+    omoe.experts_forward_backward(x[:64], ids[:64], weights[:64], w1, w2, grad_out[:64])  # warm-up
+    times = []
+    for _ in range(iterations):
+        t0 = time.perf_counter()
+        omoe.experts_forward_backward(x, ids, weights, w1, w2, grad_out)
+        times.append(time.perf_counter() - t0)
+    seconds = statistics.median(times)
+    return {
+        "value": sample_tokens / seconds, "unit": UNIT, "cores": threads, "kind": "port",
+        "sample": (f"{sample_tokens} of the {TOKENS} tokens of rank 0 through all {EXPERTS} experts, "
+                   f"forward+backward, median of {iterations} ({seconds:.2f} s each), torch CPU threads={threads}"),
+    }
+
+
+def run_reference(args) -> None:
+    """Reference arm: the CPU restatement of the reference's golden path on the host cores.
+
+    Every step (warm-up and timed alike) is one forward+backward over the same token subsample,
+    sized from a probe so that the whole run stays within a few minutes.
+    """
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import moe as omoe
+
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    inputs = make_inputs(0, 1)
+
+    def run(sample: int) -> float:
+        x, ids, weights, grad_out = (t[:sample] for t in inputs[:4])
+        t0 = time.perf_counter()
+        omoe.experts_forward_backward(x, ids, weights, inputs[4], inputs[5], grad_out)
+        return time.perf_counter() - t0
+
+    probe = run(64)
+    per_step_budget = 150.0 / (args.steps + args.warmup)
+    sample = 64 * max(1, min(TOKENS // 64, int(per_step_budget / probe)))
+    per_step = []
+    for step in range(args.warmup + args.steps):
+        seconds = run(sample)
+        if step >= args.warmup:
+            per_step.append(seconds)
+    seconds = sum(per_step) / len(per_step)
+    value = sample / seconds
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": seconds * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config(1),
+        "cpu_baseline": {
+            "value": value, "unit": UNIT, "cores": threads, "kind": "port",
+            "sample": (f"each step = {sample} of the {TOKENS} tokens through all {EXPERTS} experts, "
+                       f"forward+backward, on the CPU restatement of the reference's golden path"),
+        },
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------ clock sampler
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while a region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int) -> None:
+        self.index = index
+        self.proc = None
+        self.lines: list[str] = []
+        self.thread = None
+
+    def start(self) -> None:
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._pump, daemon=True)
+        self.thread.start()
+
+    def _pump(self) -> None:
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        clocks, maxima, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                clocks.append(float(parts[0]))
+                maxima.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, value in zip(names, parts[2:6]):
+                if value.lower().startswith("active"):
+                    reasons.add(name)
+        return {
+            "sm_mhz": statistics.median(clocks) if clocks else None,
+            "sm_max_mhz": max(maxima) if maxima else None,
+            "reasons": sorted(reasons), "samples": len(clocks),
+        }
+
+
+# ------------------------------------------------------------------------------------------- GPU arm
+def run_gpu(args) -> None:
+    import torch.distributed as dist
+
+    from hyper_multicore_b200 import MegaMoeExperts, kernels
+    from hyper_multicore_b200 import _lib
+
+    _lib.load()  # fail loudly here if the native library is missing: there is no fallback path
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} needs WORLD_SIZE={args.gpus} (launch with torch.distributed.run); "
+                         f"got WORLD_SIZE={world}")
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    group = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+        group = dist.group.WORLD
+
+    def barrier() -> None:
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    x_h, ids_h, p_h, g_h, w1_h, w2_h = make_inputs(rank, world)
+    w1 = w1_h.to(device).requires_grad_(True)
+    w2 = w2_h.to(device).requires_grad_(True)
+    module = MegaMoeExperts(hidden_size=HIDDEN, intermediate_size=INTER, num_experts=EXPERTS, top_k=TOP_K,
+                            ep_group=group)
+
+    # device-resident inputs
+    x_d = x_h.to(device).requires_grad_(True)
+    ids_d = ids_h.to(device)
+    p_d = p_h.to(device).requires_grad_(True)
+    g_d = g_h.to(device)
+
+    def step_resident() -> None:
+        w1.grad = w2.grad = x_d.grad = p_d.grad = None
+        out = module(x_d, ids_d, p_d, expert_weights=(w1, w2))
+        out.backward(g_d)
+
+    # host-resident inputs: pinned staging, copies inside the timed region
+    pinned = [t.pin_memory() for t in (x_h, ids_h, p_h, g_h)]
+    out_host = torch.empty(TOKENS, HIDDEN, dtype=torch.bfloat16).pin_memory()
+    dx_host = torch.empty(TOKENS, HIDDEN, dtype=torch.bfloat16).pin_memory()
+    dp_host = torch.empty(TOKENS, TOP_K, dtype=torch.float32).pin_memory()
+    h2d_bytes = sum(t.numel() * t.element_size() for t in pinned)
+    d2h_bytes = sum(t.numel() * t.element_size() for t in (out_host, dx_host, dp_host))
+
+    def step_host() -> None:
+        w1.grad = w2.grad = None
+        x = pinned[0].to(device, non_blocking=True).requires_grad_(True)
+        ids = pinned[1].to(device, non_blocking=True)
+        p = pinned[2].to(device, non_blocking=True).requires_grad_(True)
+        g = pinned[3].to(device, non_blocking=True)
+        out = module(x, ids, p, expert_weights=(w1, w2))
+        out.backward(g)
+        out_host.copy_(out.detach(), non_blocking=True)
+        dx_host.copy_(x.grad, non_blocking=True)
+        dp_host.copy_(p.grad, non_blocking=True)
+
+    def timed(step, steps: int, warmup: int):
+        for _ in range(warmup):
+            step()
+        barrier()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        launches_before = kernels.LAUNCH_COUNT
+        start.record()
+        for _ in range(steps):
+            step()
+        stop.record()
+        barrier()
+        ms = torch.tensor([start.elapsed_time(stop)], device=device)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item()), kernels.LAUNCH_COUNT - launches_before
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    total_ms, launches = timed(step_resident, args.steps, args.warmup)
+    clocks = sampler.stop() if rank == 0 else None
+    e2e_ms, _ = timed(step_host, args.steps, max(1, args.warmup // 2))
+    module.check_status()
+
+    # per-launch duration of the dominant kernel (the grouped GEMM), CUDA events on the launch stream
+    original = kernels.grouped_gemm
+    pairs: list = []
+
+    def instrumented(*a, **kw):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        original(*a, **kw)
+        e1.record()
+        pairs.append((e0, e1))
+
+    kernels.grouped_gemm = instrumented
+    profile_steps = min(args.steps, 5)
+    for _ in range(profile_steps):
+        step_resident()
+    barrier()
+    kernels.grouped_gemm = original
+    gemm_ms_per_step = sum(a.elapsed_time(b) for a, b in pairs) / profile_steps
+    gemm_launches_per_step = len(pairs) // profile_steps
+
+    module.close()  # collective for EP > 1: every rank unmaps its peers before anyone frees
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peaks_path = ROOT / "MEASURED_PEAKS.json"
+    if peaks_path.exists():
+        peaks = json.loads(peaks_path.read_text())
+        peak_tflops, peak_note = float(peaks["bf16_tflops_sustained"]), "of measured (sustained cuBLAS bf16)"
+    else:
+        peak_tflops, peak_note = 1400.0, "of fallback (sustained)"
+    flops_per_step = FLOPS_PER_TOKEN * TOKENS  # per rank: every rank owns an equal share in expectation
+    achieved = flops_per_step / (gemm_ms_per_step * 1e-3) / 1e12
+    ms_per_step = total_ms / args.steps
+    value = world * TOKENS / (ms_per_step * 1e-3)
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic", "config": config(world),
+        "clocks": clocks,
+        "e2e": {"value": world * TOKENS / (e2e_ms / args.steps * 1e-3), "unit": UNIT,
+                "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes,
+                "ms_per_step": e2e_ms / args.steps},
+        "gpu_launches": launches,
+        "roofline": {
+            "bound": "tensor", "kernel": "grouped_gemm_kernel (tcgen05, 6 launches per step)",
+            "achieved": achieved, "peak": peak_tflops, "unit": "TFLOP/s", "frac": achieved / peak_tflops,
+            "peak_source": peak_note,
+            "traffic": (GEMM_DRAM_BYTES_PER_STEP / gemm_launches_per_step
+                        if GEMM_DRAM_BYTES_PER_STEP and gemm_launches_per_step else None),
+            "gemm_ms_per_step": gemm_ms_per_step, "launches_per_step": gemm_launches_per_step,
+            "algorithmic_flops_per_step": flops_per_step,
+            "layer_frac": flops_per_step / (ms_per_step * 1e-3) / 1e12 / peak_tflops,
+        },
+    }
+    if world == 1:
+        line["cpu_baseline"] = cpu_baseline(sample_tokens=256, iterations=2)
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=20)
+    parser.add_argument("--warmup", type=int, default=5)
+    parser.add_argument("--impl", choices=("b200", "reference"), default="b200")
+    args = parser.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

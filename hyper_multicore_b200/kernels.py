@@ -77,11 +77,21 @@ def grouped_gemm(
     args.ready_counters = _lib.ptr(ready_counters)
     args.ready_budget_ns = ready_budget_ns
     args.status = _lib.ptr(status)
+    _count("hmc_grouped_gemm")
     with torch.cuda.device(device):
         _lib.check(_lib.load().hmc_grouped_gemm(ctypes.byref(args), _lib.stream_ptr(device)))
 
 
+LAUNCH_COUNT = 0  # kernels of this library launched so far in this process
+
+
+def _count(name: str) -> None:
+    global LAUNCH_COUNT  # pylint: disable=global-statement
+    LAUNCH_COUNT += KERNELS_PER_CALL.get(name, 1)
+
+
 def _call(name: str, device: torch.device, *args) -> None:
+    _count(name)
     with torch.cuda.device(device):
         _lib.check(getattr(_lib.load(), name)(*args, _lib.stream_ptr(device)))
 
@@ -343,3 +353,15 @@ def ep_wait(counter: torch.Tensor, expected: int, status=None, budget_ns: int = 
     """Stream-ordered bounded wait until ``counter[0] >= expected``."""
     device = _require_cuda(counter)
     _call("hmc_ep_wait", device, counter.data_ptr(), expected, budget_ns, _lib.ptr(status))
+
+
+# ------------------------------------------------------------------------------ launch accounting
+# Kernels launched per C-ABI call, for callers that report how many device launches a step made.
+KERNELS_PER_CALL = {
+    "hmc_grouped_gemm": 1, "hmc_gate_route": 1, "hmc_gate_route_grad": 1, "hmc_gate_project": 1,
+    "hmc_moe_histogram": 1, "hmc_moe_sort_routes": 3, "hmc_moe_gather_rows": 1,
+    "hmc_moe_permute_from_mapping": 1, "hmc_moe_unpermute": 1, "hmc_moe_unpermute_grad": 1,
+    "hmc_moe_token_permute_grad": 1, "hmc_zero_empty_expert_grad": 1, "hmc_route_offsets": 1,
+    "hmc_mega_mhc": 5, "hmc_mega_mhc_grad": 7, "hmc_ep_publish_ready": 1, "hmc_ep_dispatch": 1,
+    "hmc_ep_combine": 1, "hmc_ep_wait": 1,
+}

@@ -115,9 +115,7 @@ class _LocalWorkspace:
     def begin_call(self) -> int:
         self.generation += 1
         self.ctrl[:_lib.HMC_CTRL_READY].zero_()
-        with torch.cuda.device(self.device):
-            _lib.check(_lib.load().hmc_ep_publish_ready(self.peer_ctrl, 1, 0, self.generation,
-                                                        _lib.stream_ptr(self.device)))
+        kernels._call("hmc_ep_publish_ready", self.device, self.peer_ctrl, 1, 0, self.generation)  # pylint: disable=protected-access
         return self.generation
 
     def close(self) -> None:

@@ -108,10 +108,9 @@ class PeerWorkspace:
         buffers are free for the new generation. Returns the generation."""
         generation = self.next_generation()
         self.ctrl[:_lib.HMC_CTRL_READY].zero_()
-        lib = _lib.load()
-        with torch.cuda.device(self.device):
-            _lib.check(lib.hmc_ep_publish_ready(self.peer_ctrl, self.ep, self.rank, generation,
-                                                _lib.stream_ptr(self.device)))
+        from . import kernels  # pylint: disable=import-outside-toplevel
+
+        kernels._call("hmc_ep_publish_ready", self.device, self.peer_ctrl, self.ep, self.rank, generation)  # pylint: disable=protected-access
         return generation
 
     def debug_state(self) -> dict:
