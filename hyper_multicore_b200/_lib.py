@@ -180,6 +180,7 @@ SIGNATURES: dict[str, tuple] = {
     "hmc_moe_sort_workspace_bytes": (_L, [_L, _L]),
     "hmc_moe_histogram": (_I, [_P, _I, _L, _L, _P, _P, _P]),
     "hmc_moe_sort_routes": (_I, [_P, _I, _L, _L, _P, _L, _P, _P, _P, _P, _P, _P, _P]),
+    "hmc_moe_sort_routes_static": (_I, [_P, _I, _L, _L, _P, _P, _P, _P, _P, _P, _P]),
     "hmc_moe_gather_rows": (_I, [_P, _P, _L, _L, _L, _P, _P]),
     "hmc_moe_permute_from_mapping": (_I, [_P, _P, _P, _L, _L, _L, _P, _P, _P, _P]),
     "hmc_moe_unpermute": (_I, [_P, _P, _P, _L, _L, _L, _L, _P, _P, _P]),

@@ -561,3 +561,49 @@ extern "C" int hmc_route_offsets(const int32_t* counts, int64_t ep, int64_t expe
   HMC_LAUNCH_OK();
   return 0;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant of hmc_moe_sort_routes.
+//
+// Some callers may not allocate device memory at the point where they route tokens: code that
+// runs while a memory pool is frozen, plugins that were handed a fixed set of buffers by their
+// host framework, or real-time loops where a cudaMalloc (which can synchronise the whole device)
+// is not acceptable. For them the chunk-histogram scratch of the sort lives in this file-scope
+// device array instead of a caller-provided workspace. Every GPU that loads the library holds
+// the array (HMC_SORT_STATIC_BYTES) until the process exits.
+// ---------------------------------------------------------------------------------------------
+static __device__ __align__(256) int g_sort_scratch[HMC_SORT_STATIC_BYTES / sizeof(int)];
+
+// In host code the array's name is only a handle; the device address comes from
+// cudaGetSymbolAddress, asked once per device with that device current.
+static int* g_sort_scratch_address[64];
+
+extern "C" int hmc_moe_sort_routes_static(const void* indices, int indices_are_i64, int64_t entries,
+                                          int64_t experts, int32_t* mapping, int32_t* source_of_row,
+                                          int32_t* expert_of_row, int32_t* counts, int64_t* cumulative,
+                                          int32_t* status, void* stream_ptr) {
+  HMC_REQUIRE(experts > 0 && experts <= 4096, HMC_ERR_LIMIT,
+              "hmc_moe_sort_routes_static: experts must be in [1, 4096]");
+  HMC_REQUIRE(entries >= 0 && entries < (1ll << 31), HMC_ERR_LIMIT,
+              "hmc_moe_sort_routes_static: tokens * top_k must fit in int32");
+  const int64_t needed = hmc_moe_sort_workspace_bytes(entries, experts);
+  HMC_REQUIRE(needed <= static_cast<int64_t>(HMC_SORT_STATIC_BYTES), HMC_ERR_LIMIT,
+              "hmc_moe_sort_routes_static: %lld routes over %lld experts need %lld bytes of scratch, the built-in "
+              "array holds %lld; use hmc_moe_sort_routes with a caller-provided workspace",
+              (long long)entries, (long long)experts, (long long)needed, (long long)HMC_SORT_STATIC_BYTES);
+  int device = 0;
+  HMC_CUDA_OK(cudaGetDevice(&device));
+  HMC_REQUIRE(device >= 0 && device < 64, HMC_ERR_LIMIT, "hmc_moe_sort_routes_static: device ordinal %d not supported",
+              device);
+  if (g_sort_scratch_address[device] == nullptr) {
+    int* address = nullptr;
+    HMC_CUDA_OK(cudaGetSymbolAddress(reinterpret_cast<void**>(&address), g_sort_scratch));
+    HMC_REQUIRE(address != nullptr, HMC_ERR_CUDA, "hmc_moe_sort_routes_static: the scratch array has no device address");
+    g_sort_scratch_address[device] = address;
+  }
+  // Nothing in the scratch has to start at zero: the first pass writes every slot the later
+  // passes read, so the previous call's contents are simply overwritten.
+  return hmc_moe_sort_routes(indices, indices_are_i64, entries, experts, g_sort_scratch_address[device],
+                             static_cast<int64_t>(HMC_SORT_STATIC_BYTES), mapping, source_of_row, expert_of_row,
+                             counts, cumulative, status, stream_ptr);
+}

@@ -168,6 +168,24 @@ int hmc_moe_histogram(const void* indices, int indices_are_i64, int64_t entries,
 int hmc_moe_sort_routes(const void* indices, int indices_are_i64, int64_t entries, int64_t experts, void* workspace,
                         int64_t workspace_bytes, int32_t* mapping, int32_t* source_of_row, int32_t* expert_of_row,
                         int32_t* counts, int64_t* cumulative, int32_t* status, void* stream);
+/* No counterpart in the reference: an allocation-free variant of hmc_moe_sort_routes for callers that
+ * cannot obtain device memory when they route (a frozen memory pool, a plugin that was handed a fixed
+ * set of buffers, a latency-critical loop where cudaMalloc may stall the device). Its scratch is a
+ * built-in device array of HMC_SORT_STATIC_BYTES that every GPU loading the library keeps until exit.
+ *  - limit: hmc_moe_sort_workspace_bytes(entries, experts) <= HMC_SORT_STATIC_BYTES, i.e.
+ *    ceil(entries / 1024) * experts <= 1 Mi (for example 1 Mi routes over 1024 experts); larger
+ *    problems return HMC_ERR_LIMIT and must use hmc_moe_sort_routes;
+ *  - the first call on each device looks up the array's device address (with that device current);
+ *    make that first call before any stream capture begins;
+ *  - all calls on a device share the array: two calls whose kernels overlap on the GPU (different
+ *    streams, no ordering) race on it. Calls ordered on one stream are safe, and nothing needs
+ *    clearing between them;
+ *  - calls no cudaMalloc / cudaFree and no allocating library routine; inputs and outputs are the
+ *    caller's, with the same meaning as in hmc_moe_sort_routes. */
+#define HMC_SORT_STATIC_BYTES (4 * 1024 * 1024)
+int hmc_moe_sort_routes_static(const void* indices, int indices_are_i64, int64_t entries, int64_t experts,
+                               int32_t* mapping, int32_t* source_of_row, int32_t* expert_of_row, int32_t* counts,
+                               int64_t* cumulative, int32_t* status, void* stream);
 int hmc_moe_gather_rows(const void* tokens, const int32_t* source_of_row, int64_t rows, int64_t top_k,
                         int64_t hidden, void* out, void* stream);
 int hmc_moe_permute_from_mapping(const void* tokens, const int32_t* mapping, const float* probs, int64_t num_tokens,
