@@ -1,0 +1,102 @@
+"""Worker of the multi-GPU expert-parallel test: one process per GPU, launched by torch.distributed.run.
+
+Every rank regenerates all ranks' seeded inputs, runs MegaMoeExperts over its own tokens with its own
+expert shard, and checks outputs and gradients against the CPU oracle evaluated on the concatenated
+global batch (the reference's multi-rank golden replicates rows the same way,
+tests/common/multicore/moe_reference.py:37-75).
+"""
+
+import os
+import sys
+from pathlib import Path
+
+import torch
+import torch.distributed as dist
+
+ROOT = Path(__file__).resolve().parent.parent
+sys.path.insert(0, str(ROOT))
+
+from oracle import moe as omoe  # noqa: E402
+
+RTOL, ATOL = 2e-2, 2e-3
+
+
+def make_rank_inputs(rank, tokens, hidden, experts, top_k, seed):
+    g = torch.Generator().manual_seed(seed * 100 + rank)
+    x = torch.randn(tokens, hidden, generator=g).bfloat16()
+    logits = torch.randn(tokens, experts, generator=g)
+    weights, ids = torch.topk(logits.softmax(-1), top_k, dim=-1)
+    grad = torch.randn(tokens, hidden, generator=g).bfloat16()
+    return x, ids, weights.contiguous(), grad
+
+
+def check(name, got, expected):
+    expected = expected.float()
+    scale = max(1.0, float(expected.abs().max())) if expected.numel() else 1.0
+    torch.testing.assert_close(got.detach().cpu().float(), expected, rtol=RTOL, atol=ATOL * scale,
+                               msg=lambda m: f"{name}: {m}")
+
+
+def scenario(module, rank, world, device, token_counts, hidden, inter, experts, top_k, seed, layout):
+    local = experts // world
+    gw = torch.Generator().manual_seed(seed)
+    w1_all = (torch.randn(experts, hidden, 2 * inter, generator=gw) * 0.05).bfloat16()
+    w2_all = (torch.randn(experts, inter, hidden, generator=gw) * 0.05).bfloat16()
+    per_rank = [make_rank_inputs(r, token_counts[r], hidden, experts, top_k, seed) for r in range(world)]
+    x, ids, probs, grad = per_rank[rank]
+    w1 = w1_all[rank * local:(rank + 1) * local]
+    w2 = w2_all[rank * local:(rank + 1) * local]
+    if layout == "EOI":
+        w1, w2 = w1.transpose(1, 2), w2.transpose(1, 2)
+    w1 = w1.contiguous().to(device).requires_grad_(True)
+    w2 = w2.contiguous().to(device).requires_grad_(True)
+    xd = x.to(device).requires_grad_(True)
+    pd = probs.to(device).requires_grad_(True)
+    out = module(xd, ids.to(device), pd, expert_weights=(w1, w2))
+    out.backward(grad.to(device))
+    module.check_status()
+    ref = omoe.experts_forward_backward(
+        torch.cat([p[0] for p in per_rank]), torch.cat([p[1] for p in per_rank]),
+        torch.cat([p[2] for p in per_rank]), w1_all, w2_all, torch.cat([p[3] for p in per_rank]))
+    start = sum(token_counts[:rank])
+    rows = slice(start, start + token_counts[rank])
+    check("output", out, ref["output"][rows])
+    check("grad_hidden", xd.grad, ref["grad_hidden"][rows])
+    check("grad_probs", pd.grad, ref["grad_probs"][rows])
+    gw1, gw2 = w1.grad, w2.grad
+    if layout == "EOI":
+        gw1, gw2 = gw1.transpose(1, 2), gw2.transpose(1, 2)
+    check("grad_w1", gw1, ref["grad_w1"][rank * local:(rank + 1) * local])
+    check("grad_w2", gw2, ref["grad_w2"][rank * local:(rank + 1) * local])
+
+
+def main():
+    from hyper_multicore_b200 import MegaMoeExperts
+
+    rank = int(os.environ["RANK"])
+    world = int(os.environ["WORLD_SIZE"])
+    device = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
+    torch.cuda.set_device(device)
+    dist.init_process_group("nccl", device_id=device)
+    hidden, inter, experts, top_k = 256, 128, 8 * world // 2 if world > 2 else 8, 2
+    for layout in ("EIO", "EOI"):
+        module = MegaMoeExperts(hidden_size=hidden, intermediate_size=inter, num_experts=experts, top_k=top_k,
+                                ep_group=dist.group.WORLD)
+        even = [96] * world
+        ragged = [40 + 57 * r for r in range(world)]
+        empty_first = [0] + [64] * (world - 1)
+        grown = [700] * world  # exceeds the first workspace: collective re-allocation
+        for index, counts in enumerate((even, ragged, even, empty_first, grown)):
+            scenario(module, rank, world, device, counts, hidden, inter, experts, top_k, seed=10 + index,
+                     layout=layout)
+        state = module.debug_state()
+        assert state["ep"] == world and state["generation"] >= 10, state
+        module.close()
+    dist.barrier()
+    if rank == 0:
+        print(f"EP={world} ok", flush=True)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

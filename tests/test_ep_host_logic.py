@@ -1,0 +1,111 @@
+"""CPU, two gloo ranks: the host-side expert-parallel logic (group handling, count exchange, offsets).
+
+Rows are moved with plain tensor indexing instead of peer stores; what is checked is that the
+offset descriptors every rank derives from the gathered count table describe one consistent
+lossless exchange, and that the module's group validation behaves like the reference's.
+"""
+
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import route as oroute
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank: int, world: int, port: int, failures) -> None:
+    try:
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        from hyper_multicore_b200 import MegaMoeExperts
+
+        with pytest.raises(ValueError, match="Pass ep_group explicitly"):
+            MegaMoeExperts(hidden_size=64, intermediate_size=64, num_experts=8, top_k=2)
+        with pytest.raises(ValueError, match="must be divisible by ep_size"):
+            MegaMoeExperts(hidden_size=64, intermediate_size=64, num_experts=7, top_k=2, ep_group=dist.group.WORLD)
+        module = MegaMoeExperts(hidden_size=64, intermediate_size=64, num_experts=8, top_k=2,
+                                ep_group=dist.group.WORLD)
+        assert module.ep_size == world and module.local_experts == 8 // world
+        assert len(module.state_dict()) == 0
+
+        experts, top_k, hidden = 8, 2, 4
+        local = experts // world
+        rng = np.random.default_rng(100 + rank)
+        tokens = 13 + 7 * rank
+        ids = np.stack([rng.choice(experts, size=top_k, replace=False) for _ in range(tokens)])
+        x = torch.arange(tokens * hidden, dtype=torch.float32).reshape(tokens, hidden) + 1000 * rank
+        counts = torch.from_numpy(oroute.counts(ids, experts))
+        gathered = [torch.empty_like(counts) for _ in range(world)]
+        dist.all_gather(gathered, counts)
+        table = torch.stack(gathered).numpy()
+        meta = oroute.route_metadata(table, world, rank)
+        mapping, source, row_experts = oroute.permutation(ids, experts)
+        routed = x[torch.from_numpy(source).long() // top_k]  # expert-major rows on the source
+        # every rank publishes its routed rows and its descriptors; each owner assembles its buffer
+        objects = [None] * world
+        dist.all_gather_object(objects, (routed, meta, row_experts))
+        capacity, _ = oroute.expert_capacity(table, world, rank)
+        buffer = torch.full((capacity, hidden), -1.0)
+        filled = torch.zeros(capacity, dtype=torch.int32)
+        for src, (src_rows, src_meta, src_experts) in enumerate(objects):
+            for j, e in enumerate(src_experts.tolist()):
+                if e // local != rank:
+                    continue
+                dest = int(src_meta["dispatch_target_off"][e]) + (j - int(src_meta["dispatch_src_off"][e]))
+                buffer[dest] = src_rows[j]
+                filled[dest] += 1
+        received = int(table[:, rank * local:(rank + 1) * local].sum())
+        assert filled[:received].eq(1).all() and filled[received:].eq(0).all(), "dispatch is not a bijection"
+        ends = meta["group_list"].tolist()
+        assert ends[-1] == received
+        # combine back: (source, local expert) segments return to the source's expert-major rows
+        returned = [None] * world
+        back = []
+        for src in range(world):
+            rows = []
+            for le in range(local):
+                start = int(meta["combine_src_off"][src * local + le])
+                size = int(meta["combine_size"][src * local + le])
+                rows.append((int(meta["combine_target_off"][src * local + le]), buffer[start:start + size]))
+            back.append(rows)
+        dist.all_gather_object(returned, back)
+        restored = torch.full_like(routed, -2.0)
+        for owner_rows in returned:
+            for target, rows in owner_rows[rank]:
+                restored[target:target + rows.shape[0]] = rows
+        assert torch.equal(restored, routed), "combine does not return every row to its source slot"
+        dist.barrier()
+        dist.destroy_process_group()
+    except BaseException as error:  # pylint: disable=broad-except
+        failures.put(f"rank {rank}: {type(error).__name__}: {error}")
+        raise
+
+
+def test_two_rank_route_exchange_is_lossless():
+    world = 2
+    ctx = mp.get_context("spawn")
+    failures = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(rank, world, port, failures)) for rank in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=120)
+    messages = []
+    while not failures.empty():
+        messages.append(failures.get())
+    for p in procs:
+        if p.is_alive():
+            p.kill()
+            messages.append("a rank did not finish")
+    assert not messages and all(p.exitcode == 0 for p in procs), messages
