@@ -335,7 +335,7 @@ def run_gpu(args) -> None:
             "layer_frac": flops_per_step / (ms_per_step * 1e-3) / 1e12 / peak_tflops,
         },
     }
-    if world == 1:
+    if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(sample_tokens=256, iterations=2)
     print(json.dumps(line), flush=True)
     if world > 1:
@@ -348,6 +348,8 @@ def main() -> None:
     parser.add_argument("--steps", type=int, default=20)
     parser.add_argument("--warmup", type=int, default=5)
     parser.add_argument("--impl", choices=("b200", "reference"), default="b200")
+    parser.add_argument("--no-cpu-baseline", action="store_true",
+                        help="skip the CPU baseline leg (used when the run is captured by a profiler)")
     args = parser.parse_args()
     if args.warmup < 3:
         args.warmup = 3
