@@ -36,9 +36,9 @@ UNIT = "tokens/s"
 # forward 6*K*H*I flops per token (two GEMMs), backward 12*K*H*I (four GEMMs)
 FLOPS_PER_TOKEN = 18 * TOP_K * HIDDEN * INTER
 
-# DRAM bytes (read + write) per step of the six grouped-GEMM launches, from an ncu capture of this
-# workload's kernels; None until a capture has been summarised under profiles/.
-GEMM_DRAM_BYTES_PER_STEP = None
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of the six grouped-GEMM launches of one
+# step at EP=1, from the ncu capture summarised in profiles/grouped_gemm_kernel_bench_moe_bf16_ep1.md.
+GEMM_DRAM_BYTES_PER_STEP = 4.98e9
 
 
 def make_inputs(rank: int, ep: int):
@@ -329,7 +329,7 @@ def run_gpu(args) -> None:
             "achieved": achieved, "peak": peak_tflops, "unit": "TFLOP/s", "frac": achieved / peak_tflops,
             "peak_source": peak_note,
             "traffic": (GEMM_DRAM_BYTES_PER_STEP / gemm_launches_per_step
-                        if GEMM_DRAM_BYTES_PER_STEP and gemm_launches_per_step else None),
+                        if world == 1 and gemm_launches_per_step else None),
             "gemm_ms_per_step": gemm_ms_per_step, "launches_per_step": gemm_launches_per_step,
             "algorithmic_flops_per_step": flops_per_step,
             "layer_frac": flops_per_step / (ms_per_step * 1e-3) / 1e12 / peak_tflops,

@@ -8,7 +8,8 @@
 // experts" rule (bf16_worker.h:62-75).
 //
 // One CTA per SM, 192 threads: warp 0 = TMA producer, warp 1 = MMA issuer (+TMEM owner),
-// warps 2..5 = epilogue (one TMEM lane quarter each). Tiles are 128 x 256 x 64.
+// warps 2..9 = epilogue (two warps per TMEM lane quarter, one column half each). Tiles are
+// 128 x 256 x 64. Weight-gradient tiles leave through shared memory and TMA stores.
 //
 //  RAGGED_M : C[r0:r1, :] = A[r0:r1, :] * B_g      rows of group g are [ends[g-1], ends[g])
 //  RAGGED_K : C_g = A[r0:r1, :]^T * B[r0:r1, :]    contraction over the group's rows
@@ -31,8 +32,10 @@ constexpr int A_TILE_BYTES = BM * BK * 2;  // 16 KiB
 constexpr int B_TILE_BYTES = BN * BK * 2;  // 32 KiB
 constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
 constexpr int CHUNK_BYTES = 64 * BK * 2;  // one 64-wide MN-major chunk: BK rows of 128 B
-constexpr int NUM_THREADS = 192;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+constexpr int EPI_WARPS = 8;
+constexpr int NUM_THREADS = 64 + EPI_WARPS * 32;
+constexpr int STORE_STAGE_BYTES = 32 * 128;  // one 32-row x 128-byte TMA store box per epilogue warp
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_WARPS * STORE_STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t SWIZZLE_128B = 2;
 
@@ -121,11 +124,12 @@ __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)
 template <int A_MAJOR, int B_MAJOR>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
-                    const Params p) {
+                    const __grid_constant__ CUtensorMap tm_c, const Params p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint8_t* store_stage = smem + STAGES * STAGE_BYTES;  // [EPI_WARPS][STORE_STAGE_BYTES], 1024-aligned
+  uint64_t* bars = reinterpret_cast<uint64_t*>(store_stage + EPI_WARPS * STORE_STAGE_BYTES);
   uint64_t* full_bar = bars;                                 // [STAGES]
   uint64_t* empty_bar = bars + STAGES;                       // [STAGES]
   uint64_t* acc_full_bar = bars + 2 * STAGES;                // [ACC_STAGES]
@@ -143,12 +147,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     }
     for (int s = 0; s < ACC_STAGES; ++s) {
       mbar_init(&acc_full_bar[s], 1);
-      mbar_init(&acc_empty_bar[s], 4);  // one arrival per epilogue warp
+      mbar_init(&acc_empty_bar[s], EPI_WARPS);  // one arrival per epilogue warp
     }
     *abort_word = 0;
     mbar_fence_init();
     prefetch_tensormap(&tm_a);
     prefetch_tensormap(&tm_b);
+    if (p.mode == HMC_GEMM_RAGGED_K) prefetch_tensormap(&tm_c);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, TMEM_COLS);
@@ -327,7 +332,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
-    const int quarter = warp & 3;  // TMEM lane quarter this warp may read
+    const int quarter = warp & 3;       // TMEM lane quarter this warp may read
+    const int half = (warp - 2) >> 2;   // which half of the tile's columns this warp handles
+    const int c_lo = half * (BN / 2);
+    const int c_hi = c_lo + BN / 2;
+    uint8_t* my_stage = store_stage + (warp - 2) * STORE_STAGE_BYTES;
+    bool store_pending = false;
     const int row_in_tile = quarter * 32 + lane;
     for (long long idx = blockIdx.x; ok && walker.get(idx, t); idx += gridDim.x) {
       const int kiters = k_iterations(p, t);
@@ -349,11 +359,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         if (row_ok) {
           if (p.epilogue == HMC_EPI_STORE_F32) {
             float* dst = static_cast<float*>(p.c) + out_row * p.ldc + col_base;
-            for (int c = 0; c < BN && col_base + c < p.n; c += 4)
+            for (int c = c_lo; c < c_hi && col_base + c < p.n; c += 4)
               *reinterpret_cast<float4*>(dst + c) = make_float4(0.f, 0.f, 0.f, 0.f);
           } else {
             __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.c) + out_row * p.ldc + col_base;
-            for (int c = 0; c < BN && col_base + c < p.n; c += 8)
+            for (int c = c_lo; c < c_hi && col_base + c < p.n; c += 8)
               *reinterpret_cast<uint4*>(dst + c) = make_uint4(0, 0, 0, 0);
           }
         }
@@ -367,10 +377,54 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                              static_cast<uint32_t>(acc * BN);
-      if (p.epilogue == HMC_EPI_STORE_BF16) {
+      if (p.mode == HMC_GEMM_RAGGED_K) {
+        // Weight-gradient tiles are regular [m, n] grids per group, so they leave through shared
+        // memory and TMA stores (full 128-byte lines, clipped at the m and n edges by the tensor
+        // map). Each warp stages a 32-row x 128-byte box: 64 BF16 or 32 FP32 columns per store.
+        const bool f32 = p.epilogue == HMC_EPI_STORE_F32;
+        const int step = f32 ? 32 : 64;
+        const int m0 = t.m_idx * BM + quarter * 32;
+#pragma unroll 1
+        for (int c = c_lo; c < c_hi; c += step) {
+          if (col_base + c >= p.n) break;
+          uint32_t v[32];
+          uint32_t w[32];
+          tmem_ld_32x32(taddr + c, v);
+          if (!f32) tmem_ld_32x32(taddr + c + 32, w);
+          tmem_ld_wait();
+          if (store_pending) {  // the previous box must have been read out of the stage
+            if (lane == 0) bulk_wait_read_all();
+            __syncwarp();
+          }
+          // 16-byte chunk q of row `lane` goes to chunk q ^ (lane & 7): the 128-byte swizzle the
+          // tensor map expects, which also spreads a warp's stores over all banks.
+          uint8_t* row_base = my_stage + lane * 128;
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            uint4 o;
+            if (f32) {
+              o = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+            } else {
+              const uint32_t* src = q < 4 ? v + 8 * q : w + 8 * (q - 4);
+              o.x = pack_bf16x2(__uint_as_float(src[0]), __uint_as_float(src[1]));
+              o.y = pack_bf16x2(__uint_as_float(src[2]), __uint_as_float(src[3]));
+              o.z = pack_bf16x2(__uint_as_float(src[4]), __uint_as_float(src[5]));
+              o.w = pack_bf16x2(__uint_as_float(src[6]), __uint_as_float(src[7]));
+            }
+            *reinterpret_cast<uint4*>(row_base + ((q ^ (lane & 7)) << 4)) = o;
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_3d(&tm_c, my_stage, col_base + c, m0, t.group);
+            bulk_commit_group();
+          }
+          store_pending = true;
+        }
+      } else if (p.epilogue == HMC_EPI_STORE_BF16) {
         __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.c) + out_row * p.ldc + col_base;
 #pragma unroll 1
-        for (int c = 0; c < BN; c += 32) {
+        for (int c = c_lo; c < c_hi; c += 32) {
           uint32_t v[32];
           tmem_ld_32x32(taddr + c, v);
           tmem_ld_wait();
@@ -391,7 +445,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       } else if (p.epilogue == HMC_EPI_STORE_F32) {
         float* dst = static_cast<float*>(p.c) + out_row * p.ldc + col_base;
 #pragma unroll 1
-        for (int c = 0; c < BN; c += 32) {
+        for (int c = c_lo; c < c_hi; c += 32) {
           uint32_t v[32];
           tmem_ld_32x32(taddr + c, v);
           tmem_ld_wait();
@@ -413,7 +467,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         __nv_bfloat16* u_dst = static_cast<__nv_bfloat16*>(p.c) + out_row * p.ldc + col_base;
         __nv_bfloat16* a_dst = static_cast<__nv_bfloat16*>(p.aux) + out_row * p.ld_aux + col_base;
 #pragma unroll 1
-        for (int c = 0; c < BN / 2; c += 32) {
+        for (int c = half * (BN / 4); c < (half + 1) * (BN / 4); c += 32) {
           uint32_t g[32], u[32];
           tmem_ld_32x32(taddr + c, g);
           tmem_ld_32x32(taddr + BN / 2 + c, u);
@@ -445,7 +499,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         const __nv_bfloat16* u_src = static_cast<const __nv_bfloat16*>(p.aux) + out_row * p.ld_aux + col_base;
         __nv_bfloat16* d_dst = static_cast<__nv_bfloat16*>(p.c) + out_row * p.ldc + col_base;
 #pragma unroll 1
-        for (int c = 0; c < BN; c += 32) {
+        for (int c = c_lo; c < c_hi; c += 32) {
           uint32_t v[32];
           tmem_ld_32x32(taddr + c, v);
           tmem_ld_wait();
@@ -485,6 +539,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         acc_phase ^= 1u;
       }
     }
+    if (store_pending && lane == 0) bulk_wait_all();  // this thread's stores are in global memory
   }
 
   // Teardown: everyone meets here (also after a time-out), then the allocating warp frees TMEM.
@@ -515,18 +570,20 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// BF16 tensor of `rank` dims (dims[0] innermost), box with a 64-element (128-byte) inner extent.
-int make_map(CUtensorMap* out, const void* base, int rank, const cuuint64_t* dims, const cuuint32_t* box) {
+// Tensor of `rank` dims (dims[0] innermost), box with a 128-byte inner extent, 128-byte swizzle.
+int make_map(CUtensorMap* out, const void* base, int rank, const cuuint64_t* dims, const cuuint32_t* box,
+             bool f32 = false) {
   EncodeTiledFn fn = encode_fn();
   HMC_REQUIRE(fn != nullptr, HMC_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
   cuuint64_t strides[4];
-  cuuint64_t acc = 2;
+  cuuint64_t acc = f32 ? 4 : 2;
   for (int i = 0; i + 1 < rank; ++i) {
     acc *= dims[i];
     strides[i] = acc;
   }
   cuuint32_t elem_strides[5] = {1, 1, 1, 1, 1};
-  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, static_cast<cuuint32_t>(rank),
+  CUresult r = fn(out, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
+                  static_cast<cuuint32_t>(rank),
                   const_cast<void*>(base), dims, strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -535,14 +592,15 @@ int make_map(CUtensorMap* out, const void* base, int rank, const cuuint64_t* dim
 }
 
 template <int A_MAJOR, int B_MAJOR>
-int launch(const CUtensorMap& ta, const CUtensorMap& tb, const Params& p, int grid, cudaStream_t stream) {
+int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const Params& p, int grid,
+           cudaStream_t stream) {
   static bool configured = false;
   auto kernel = grouped_gemm_kernel<A_MAJOR, B_MAJOR>;
   if (!configured) {
     HMC_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
     configured = true;
   }
-  kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, p);
+  kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, tc, p);
   HMC_LAUNCH_OK();
   return 0;
 }
@@ -584,7 +642,7 @@ extern "C" int hmc_grouped_gemm(const hmc_grouped_gemm_args* args, void* stream_
   p.status = a.status;
   p.n = static_cast<int>(a.n);
 
-  CUtensorMap ta, tb;
+  CUtensorMap ta, tb, tc;
   int rc;
   if (a.mode == HMC_GEMM_RAGGED_M) {
     HMC_REQUIRE(a.k > 0 && a.k % 8 == 0, HMC_ERR_INVALID,
@@ -642,15 +700,23 @@ extern "C" int hmc_grouped_gemm(const hmc_grouped_gemm_args* args, void* stream_
       cuuint32_t box[2] = {64, BK};
       if ((rc = make_map(&tb, a.b, 2, dims, box)) != 0) return rc;
     }
+    {  // C = [groups, m, n]: 32-row boxes, 128 bytes wide
+      const bool f32 = a.epilogue == HMC_EPI_STORE_F32;
+      cuuint64_t dims[3] = {static_cast<cuuint64_t>(a.n), static_cast<cuuint64_t>(a.m),
+                            static_cast<cuuint64_t>(a.groups)};
+      cuuint32_t box[3] = {f32 ? 32u : 64u, 32, 1};
+      if ((rc = make_map(&tc, a.c, 3, dims, box, f32)) != 0) return rc;
+    }
   }
+  if (a.mode == HMC_GEMM_RAGGED_M) tc = ta;  // unused by the kernel in this mode
 
   int grid = a.max_ctas > 0 ? a.max_ctas : sm_count();
   if (grid > sm_count()) grid = sm_count();
   if (a.mode == HMC_GEMM_RAGGED_K) {
     const long long tiles = static_cast<long long>(p.groups) * p.m_tiles * p.n_tiles;
     if (tiles < grid) grid = static_cast<int>(tiles);
-    return launch<HMC_MAJOR_MN, HMC_MAJOR_MN>(ta, tb, p, grid, stream);
+    return launch<HMC_MAJOR_MN, HMC_MAJOR_MN>(ta, tb, tc, p, grid, stream);
   }
-  if (a.b_major == HMC_MAJOR_MN) return launch<HMC_MAJOR_K, HMC_MAJOR_MN>(ta, tb, p, grid, stream);
-  return launch<HMC_MAJOR_K, HMC_MAJOR_K>(ta, tb, p, grid, stream);
+  if (a.b_major == HMC_MAJOR_MN) return launch<HMC_MAJOR_K, HMC_MAJOR_MN>(ta, tb, tc, p, grid, stream);
+  return launch<HMC_MAJOR_K, HMC_MAJOR_K>(ta, tb, tc, p, grid, stream);
 }
