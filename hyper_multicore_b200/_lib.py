@@ -152,6 +152,30 @@ class EpCombineArgs(ctypes.Structure):
     ]
 
 
+class MxGemmArgs(ctypes.Structure):
+    """Mirror of ``hmc_mx_gemm_args``."""
+
+    _fields_ = [
+        ("mode", c_int32), ("b_major", c_int32), ("epilogue", c_int32), ("groups", c_int32),
+        ("max_ctas", c_int32), ("reserved", c_int32),
+        ("rows", c_int64), ("pad_blocks", c_int64), ("m", c_int64), ("n", c_int64), ("k", c_int64),
+        ("a", c_void_p), ("a_scale", c_void_p), ("b", c_void_p), ("b_scale", c_void_p), ("c", c_void_p),
+        ("group_ends", c_void_p), ("status", c_void_p),
+    ]
+
+
+class MxQuantArgs(ctypes.Structure):
+    """Mirror of ``hmc_mx_quant_args``."""
+
+    _fields_ = [
+        ("kind", c_int32), ("groups", c_int32),
+        ("rows", c_int64), ("pad_blocks", c_int64), ("width", c_int64),
+        ("src", c_void_p), ("aux", c_void_p), ("group_ends", c_void_p),
+        ("row_data", c_void_p), ("row_scale", c_void_p), ("col_data", c_void_p), ("col_scale", c_void_p),
+        ("dense", c_void_p),
+    ]
+
+
 HMC_MAX_EP = 16
 HMC_CTRL_ARRIVAL = 0
 HMC_CTRL_COMBINE = 1024
@@ -174,6 +198,10 @@ SIGNATURES: dict[str, tuple] = {
     "hmc_mega_moe_transport_version": (_I, []),
     "hmc_worker_queue_layout_version": (_I, []),
     "hmc_grouped_gemm": (_I, [ctypes.POINTER(GroupedGemmArgs), _P]),
+    "hmc_mx_gemm": (_I, [ctypes.POINTER(MxGemmArgs), _P]),
+    "hmc_mx_quant": (_I, [ctypes.POINTER(MxQuantArgs), _P]),
+    "hmc_mx_quant_weight": (_I, [_P, _L, _L, _L, _P, _P, _P, _P, _P]),
+    "hmc_mx_pack_weight_scale": (_I, [_P, _I, _L, _L, _L, _P, _P]),
     "hmc_gate_route": (_I, [ctypes.POINTER(GateRouteArgs), _P]),
     "hmc_gate_route_grad": (_I, [ctypes.POINTER(GateRouteGradArgs), _P]),
     "hmc_gate_project": (_I, [_P, _I, _P, _I, _L, _L, _L, _P, _P]),

@@ -1,0 +1,372 @@
+// MXFP8 quantisers: BF16 -> E4M3 with one UE8M0 scale per 32 elements, along the row (for GEMMs
+// that contract over the feature axis) and down the rows (for the weight-gradient GEMMs that
+// contract over tokens), written in the padded expert-major layout the MX GEMM consumes.
+//
+// Replaces the reference's dual-axis MX quantiser tasks (hyper_multicore/ops/common/mega_moe/
+// adapters/arch35/quantization/dual_axis_mxfp8_worker.h:23-110): plain, fused SwiGLU + quant and
+// fused SwiGLUGrad + quant. The reference delegates the arithmetic to a third-party CANN operator
+// whose source is not part of that project; the rule used here is the OCP Microscaling one:
+//   shared exponent = floor(log2(max |x| of the block)) - 8   (8 = largest E4M3 exponent)
+//   element         = round-to-nearest-even(x / 2^exponent), saturating at +-448
+// with an all-zero block taking scale 1.
+#include <cuda_fp8.h>
+
+#include "common.cuh"
+
+namespace hmc {
+namespace {
+
+constexpr int TILE = 128;
+constexpr int LD = TILE + 1;  // shared-memory row stride in floats (conflict-free both ways)
+constexpr int THREADS = 256;
+
+__device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)); }
+
+// biased UE8M0 exponent of a block whose largest magnitude is `amax`
+__device__ __forceinline__ uint32_t block_exponent(float amax) {
+  if (!(amax > 0.f)) return 127u;
+  const int e = static_cast<int>((__float_as_uint(amax) >> 23) & 0xffu) - 8;
+  return static_cast<uint32_t>(min(max(e, 0), 254));
+}
+__device__ __forceinline__ float inverse_scale(uint32_t biased) { return __uint_as_float((254u - biased) << 23); }
+__device__ __forceinline__ uint8_t to_e4m3(float v) {
+  return static_cast<uint8_t>(__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3));
+}
+
+struct QuantParams {
+  int kind;
+  int groups;
+  long long rows;
+  int pad_blocks;
+  int width;  // columns of the quantised result
+  const __nv_bfloat16* src;
+  const __nv_bfloat16* aux;
+  const long long* group_ends;
+  uint8_t* row_data;
+  uint8_t* row_scale;
+  uint8_t* col_data;
+  uint8_t* col_scale;
+  __nv_bfloat16* dense;
+};
+
+// One CTA per (128-row padded block, 128-column block).
+__global__ void __launch_bounds__(THREADS) mx_quant_kernel(const QuantParams p) {
+  extern __shared__ float tile[];  // [TILE][LD]
+  __shared__ long long s_row0;
+  __shared__ int s_valid;
+  const int pb = blockIdx.x;
+  const int cb = blockIdx.y;
+  if (threadIdx.x == 0) {
+    // locate the padded block: groups own ceil(rows / 128) consecutive blocks each
+    int block = 0;
+    long long prev = 0;
+    s_valid = -1;
+    for (int g = 0; g < p.groups; ++g) {
+      const long long end = p.group_ends[g];
+      const int blocks = static_cast<int>((end - prev + 127) / 128);
+      if (pb < block + blocks) {
+        s_row0 = prev + static_cast<long long>(pb - block) * 128;
+        s_valid = static_cast<int>(min(static_cast<long long>(128), end - s_row0));
+        break;
+      }
+      block += blocks;
+      prev = end;
+    }
+  }
+  __syncthreads();
+  const int valid = s_valid;
+  if (valid < 0) return;  // a spare block past the last group: never read by the GEMM
+  const long long row0 = s_row0;
+  const int width = p.width;
+  const int c0 = cb * TILE;
+
+  // ---- load (and transform) the tile: 8 BF16 per access
+  for (int i = threadIdx.x; i < TILE * (TILE / 8); i += THREADS) {
+    const int r = i >> 4;
+    const int c = (i & 15) * 8;
+    float v[8];
+    if (r < valid) {
+      const long long row = row0 + r;
+      if (p.kind == HMC_MXQ_PLAIN) {
+        const uint4 q = ld_nc_16(p.src + row * width + c0 + c);
+        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = unpack_bf16x2(w[j]);
+          v[2 * j] = f.x;
+          v[2 * j + 1] = f.y;
+        }
+      } else if (p.kind == HMC_MXQ_SWIGLU) {
+        // src = U[rows, 2 * width] = [gate | up]
+        const uint4 gq = ld_nc_16(p.src + row * 2 * width + c0 + c);
+        const uint4 uq = ld_nc_16(p.src + row * 2 * width + width + c0 + c);
+        const uint32_t gw[4] = {gq.x, gq.y, gq.z, gq.w};
+        const uint32_t uw[4] = {uq.x, uq.y, uq.z, uq.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 g = unpack_bf16x2(gw[j]);
+          const float2 u = unpack_bf16x2(uw[j]);
+          v[2 * j] = bf16_round(silu_f(g.x) * u.x);
+          v[2 * j + 1] = bf16_round(silu_f(g.y) * u.y);
+        }
+      } else {
+        // src = dAct[rows, width / 2], aux = U[rows, width]; result = [dgate | dup]
+        const int inter = width / 2;
+        const int col = c0 + c;
+        const bool gate_half = col < inter;
+        const int ic = gate_half ? col : col - inter;
+        const uint4 dq = ld_nc_16(p.src + row * inter + ic);
+        const uint4 gq = ld_nc_16(p.aux + row * width + ic);
+        const uint4 uq = ld_nc_16(p.aux + row * width + inter + ic);
+        const uint32_t dw[4] = {dq.x, dq.y, dq.z, dq.w};
+        const uint32_t gw[4] = {gq.x, gq.y, gq.z, gq.w};
+        const uint32_t uw[4] = {uq.x, uq.y, uq.z, uq.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 d = unpack_bf16x2(dw[j]);
+          const float2 g = unpack_bf16x2(gw[j]);
+          const float2 u = unpack_bf16x2(uw[j]);
+          const float s0 = 1.0f / (1.0f + __expf(-g.x));
+          const float s1 = 1.0f / (1.0f + __expf(-g.y));
+          if (gate_half) {
+            v[2 * j] = bf16_round(d.x * u.x * s0 * (1.0f + g.x * (1.0f - s0)));
+            v[2 * j + 1] = bf16_round(d.y * u.y * s1 * (1.0f + g.y * (1.0f - s1)));
+          } else {
+            v[2 * j] = bf16_round(d.x * (g.x * s0));
+            v[2 * j + 1] = bf16_round(d.y * (g.y * s1));
+          }
+        }
+      }
+      if (p.dense != nullptr) {
+        uint4 o;
+        o.x = pack_bf16x2(v[0], v[1]);
+        o.y = pack_bf16x2(v[2], v[3]);
+        o.z = pack_bf16x2(v[4], v[5]);
+        o.w = pack_bf16x2(v[6], v[7]);
+        *reinterpret_cast<uint4*>(p.dense + row * width + c0 + c) = o;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) tile[r * LD + c + j] = v[j];
+  }
+  __syncthreads();
+
+  const long long pad_row0 = static_cast<long long>(pb) * TILE;
+  // ---- 32-element blocks along each row
+  if (p.row_data != nullptr) {
+    uint8_t* atom = p.row_scale + (static_cast<long long>(cb) * p.pad_blocks + pb) * 512;
+    for (int item = threadIdx.x; item < 4 * TILE; item += THREADS) {
+      const int r = item & (TILE - 1);  // a warp covers 32 different rows of one block column
+      const int j = item >> 7;
+      const float* src = tile + r * LD + 32 * j;
+      float amax = 0.f;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(src[i]));
+      const uint32_t e = block_exponent(amax);
+      const float inv = inverse_scale(e);
+      uint32_t packed[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        packed[i] = static_cast<uint32_t>(to_e4m3(src[4 * i] * inv)) |
+                    (static_cast<uint32_t>(to_e4m3(src[4 * i + 1] * inv)) << 8) |
+                    (static_cast<uint32_t>(to_e4m3(src[4 * i + 2] * inv)) << 16) |
+                    (static_cast<uint32_t>(to_e4m3(src[4 * i + 3] * inv)) << 24);
+      }
+      uint8_t* dst = p.row_data + (pad_row0 + r) * width + c0 + 32 * j;
+      *reinterpret_cast<uint4*>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+      *reinterpret_cast<uint4*>(dst + 16) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+      atom[(r & 31) * 16 + (r >> 5) * 4 + j] = static_cast<uint8_t>(e);
+    }
+  }
+  // ---- 32-element blocks down each column
+  if (p.col_data != nullptr) {
+    uint8_t* atom = p.col_scale + (static_cast<long long>(pb) * (width / TILE) + cb) * 512;
+    for (int item = threadIdx.x; item < 4 * TILE; item += THREADS) {
+      const int c = item & (TILE - 1);
+      const int jb = item >> 7;
+      const float* src = tile + (32 * jb) * LD + c;
+      float amax = 0.f;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(src[i * LD]));
+      const uint32_t e = block_exponent(amax);
+      const float inv = inverse_scale(e);
+      uint8_t* dst = p.col_data + (pad_row0 + 32 * jb) * width + c0 + c;
+#pragma unroll 4
+      for (int i = 0; i < 32; ++i) dst[static_cast<long long>(i) * width] = to_e4m3(src[i * LD] * inv);
+      atom[(c & 31) * 16 + (c >> 5) * 4 + jb] = static_cast<uint8_t>(e);
+    }
+  }
+}
+
+// Weights [experts, m, n] BF16 -> the reference's physical MX fields. One thread per 32-block.
+__global__ void mx_quant_weight_col_kernel(const __nv_bfloat16* __restrict__ w, long long experts, int m, int n,
+                                           uint8_t* __restrict__ data, uint8_t* __restrict__ scale) {
+  // blocks of 32 along m; scale[e, m/64, n, 2]
+  const long long total = experts * (m / 32) * n;
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const int col = static_cast<int>(i % n);
+  const int mb = static_cast<int>((i / n) % (m / 32));
+  const long long e = i / (static_cast<long long>(n) * (m / 32));
+  const __nv_bfloat16* src = w + (e * m + mb * 32) * n + col;
+  float v[32], amax = 0.f;
+#pragma unroll
+  for (int k = 0; k < 32; ++k) {
+    v[k] = __bfloat162float(src[static_cast<long long>(k) * n]);
+    amax = fmaxf(amax, fabsf(v[k]));
+  }
+  const uint32_t ex = block_exponent(amax);
+  const float inv = inverse_scale(ex);
+  uint8_t* dst = data + (e * m + mb * 32) * n + col;
+#pragma unroll
+  for (int k = 0; k < 32; ++k) dst[static_cast<long long>(k) * n] = to_e4m3(v[k] * inv);
+  scale[((e * (m / 64) + mb / 2) * n + col) * 2 + (mb & 1)] = static_cast<uint8_t>(ex);
+}
+
+__global__ void mx_quant_weight_row_kernel(const __nv_bfloat16* __restrict__ w, long long experts, int m, int n,
+                                           uint8_t* __restrict__ data, uint8_t* __restrict__ scale) {
+  // blocks of 32 along n; scale[e, m, n/64, 2]
+  const long long total = experts * m * (n / 32);
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const int nb = static_cast<int>(i % (n / 32));
+  const long long row = i / (n / 32);  // e * m + m_index
+  const __nv_bfloat16* src = w + row * n + nb * 32;
+  float v[32], amax = 0.f;
+#pragma unroll
+  for (int k = 0; k < 32; ++k) {
+    v[k] = __bfloat162float(src[k]);
+    amax = fmaxf(amax, fabsf(v[k]));
+  }
+  const uint32_t ex = block_exponent(amax);
+  const float inv = inverse_scale(ex);
+  uint8_t* dst = data + row * n + nb * 32;
+#pragma unroll
+  for (int k = 0; k < 32; ++k) dst[k] = to_e4m3(v[k] * inv);
+  scale[(row * (n / 64) + nb / 2) * 2 + (nb & 1)] = static_cast<uint8_t>(ex);
+}
+
+// Reference scale tensors -> 512-byte atoms. One thread per output byte.
+__global__ void mx_pack_weight_scale_kernel(const uint8_t* __restrict__ scale, int axis, long long experts, int m,
+                                            int n, uint8_t* __restrict__ atoms) {
+  const long long total = experts * (static_cast<long long>(m) * n / 32);
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const int within = static_cast<int>(i & 511);
+  const int r32 = within >> 4, r4 = (within >> 2) & 3, kk = within & 3;
+  const long long atom = i >> 9;
+  if (axis == 0) {
+    // atoms [e][m/128][n/128], atom row = n index, kk = 32-block of m inside the 128-block
+    const int nb = static_cast<int>(atom % (n / 128));
+    const int kb = static_cast<int>((atom / (n / 128)) % (m / 128));
+    const long long e = atom / (static_cast<long long>(n / 128) * (m / 128));
+    const int col = nb * 128 + r4 * 32 + r32;
+    atoms[i] = scale[((e * (m / 64) + kb * 2 + kk / 2) * n + col) * 2 + (kk & 1)];
+  } else {
+    // atoms [e][n/128][m/128], atom row = m index, kk = 32-block of n inside the 128-block
+    const int mb = static_cast<int>(atom % (m / 128));
+    const int kb = static_cast<int>((atom / (m / 128)) % (n / 128));
+    const long long e = atom / (static_cast<long long>(m / 128) * (n / 128));
+    const int row = mb * 128 + r4 * 32 + r32;
+    atoms[i] = scale[((e * m + row) * (n / 64) + kb * 2 + kk / 2) * 2 + (kk & 1)];
+  }
+}
+
+}  // namespace
+}  // namespace hmc
+
+using namespace hmc;
+
+extern "C" int hmc_mx_quant(const hmc_mx_quant_args* args, void* stream_ptr) {
+  HMC_REQUIRE(args != nullptr, HMC_ERR_INVALID, "hmc_mx_quant: null args");
+  const hmc_mx_quant_args& a = *args;
+  HMC_REQUIRE(a.kind >= HMC_MXQ_PLAIN && a.kind <= HMC_MXQ_SWIGLU_GRAD, HMC_ERR_INVALID, "hmc_mx_quant: unknown kind %d",
+              a.kind);
+  HMC_REQUIRE(a.groups > 0 && a.rows >= 0 && a.pad_blocks >= (a.rows + 127) / 128 && a.pad_blocks > 0 &&
+                  a.pad_blocks <= 65535 * 16,
+              HMC_ERR_INVALID, "hmc_mx_quant: bad group / row / pad_blocks arguments");
+  HMC_REQUIRE(a.width > 0 && a.width % 128 == 0 && a.width / 128 <= 65535, HMC_ERR_LIMIT,
+              "hmc_mx_quant: width (%lld) must be a positive multiple of 128", (long long)a.width);
+  HMC_REQUIRE(a.kind != HMC_MXQ_SWIGLU_GRAD || (a.width % 256 == 0 && a.aux != nullptr), HMC_ERR_INVALID,
+              "hmc_mx_quant: the SwiGLU-grad kind needs aux = U and a width that is a multiple of 256");
+  HMC_REQUIRE(a.src && a.group_ends, HMC_ERR_INVALID, "hmc_mx_quant: null tensor pointer");
+  HMC_REQUIRE((a.row_data == nullptr) == (a.row_scale == nullptr) && (a.col_data == nullptr) == (a.col_scale == nullptr),
+              HMC_ERR_INVALID, "hmc_mx_quant: data and scale outputs go together");
+  HMC_REQUIRE(aligned16(a.src) && (a.aux == nullptr || aligned16(a.aux)) && (a.row_data == nullptr || aligned16(a.row_data)) &&
+                  (a.dense == nullptr || aligned16(a.dense)),
+              HMC_ERR_INVALID, "hmc_mx_quant: tensors must be 16-byte aligned");
+  if (a.rows == 0) return 0;
+  QuantParams p{};
+  p.kind = a.kind;
+  p.groups = a.groups;
+  p.rows = a.rows;
+  p.pad_blocks = static_cast<int>(a.pad_blocks);
+  p.width = static_cast<int>(a.width);
+  p.src = static_cast<const __nv_bfloat16*>(a.src);
+  p.aux = static_cast<const __nv_bfloat16*>(a.aux);
+  p.group_ends = reinterpret_cast<const long long*>(a.group_ends);
+  p.row_data = static_cast<uint8_t*>(a.row_data);
+  p.row_scale = static_cast<uint8_t*>(a.row_scale);
+  p.col_data = static_cast<uint8_t*>(a.col_data);
+  p.col_scale = static_cast<uint8_t*>(a.col_scale);
+  p.dense = static_cast<__nv_bfloat16*>(a.dense);
+  static bool configured = false;
+  const int smem = TILE * LD * sizeof(float);
+  if (!configured) {
+    HMC_CUDA_OK(cudaFuncSetAttribute(mx_quant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    configured = true;
+  }
+  // only blocks that can hold rows are launched: ceil(rows / 128) + groups bounds them
+  long long blocks = (a.rows + 127) / 128 + a.groups;
+  if (blocks > a.pad_blocks) blocks = a.pad_blocks;
+  dim3 grid(static_cast<unsigned>(blocks), static_cast<unsigned>(a.width / 128));
+  mx_quant_kernel<<<grid, THREADS, smem, static_cast<cudaStream_t>(stream_ptr)>>>(p);
+  HMC_LAUNCH_OK();
+  return 0;
+}
+
+extern "C" int hmc_mx_quant_weight(const void* weight_bf16, int64_t experts, int64_t m, int64_t n, void* col_data,
+                                   void* col_scale, void* row_data, void* row_scale, void* stream_ptr) {
+  HMC_REQUIRE(weight_bf16 != nullptr && experts > 0, HMC_ERR_INVALID, "hmc_mx_quant_weight: bad arguments");
+  // the reference's contract: both matrix extents are multiples of 64 (docs/mega_moe.md:184)
+  HMC_REQUIRE(m > 0 && n > 0 && m % 64 == 0 && n % 64 == 0 && m < (1ll << 31) && n < (1ll << 31), HMC_ERR_INVALID,
+              "hmc_mx_quant_weight: m (%lld) and n (%lld) must be positive multiples of 64", (long long)m, (long long)n);
+  HMC_REQUIRE((col_data == nullptr) == (col_scale == nullptr) && (row_data == nullptr) == (row_scale == nullptr),
+              HMC_ERR_INVALID, "hmc_mx_quant_weight: data and scale outputs go together");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  const __nv_bfloat16* w = static_cast<const __nv_bfloat16*>(weight_bf16);
+  if (col_data != nullptr) {
+    const long long total = experts * (m / 32) * n;
+    mx_quant_weight_col_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(
+        w, experts, static_cast<int>(m), static_cast<int>(n), static_cast<uint8_t*>(col_data),
+        static_cast<uint8_t*>(col_scale));
+    HMC_LAUNCH_OK();
+  }
+  if (row_data != nullptr) {
+    const long long total = experts * m * (n / 32);
+    mx_quant_weight_row_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(
+        w, experts, static_cast<int>(m), static_cast<int>(n), static_cast<uint8_t*>(row_data),
+        static_cast<uint8_t*>(row_scale));
+    HMC_LAUNCH_OK();
+  }
+  return 0;
+}
+
+extern "C" int hmc_mx_pack_weight_scale(const void* scale, int axis, int64_t experts, int64_t m, int64_t n, void* atoms,
+                                        void* stream_ptr) {
+  HMC_REQUIRE(scale != nullptr && atoms != nullptr && experts > 0 && (axis == 0 || axis == 1), HMC_ERR_INVALID,
+              "hmc_mx_pack_weight_scale: bad arguments");
+  HMC_REQUIRE(m > 0 && n > 0 && m % 128 == 0 && n % 128 == 0, HMC_ERR_LIMIT,
+              "hmc_mx_pack_weight_scale: m (%lld) and n (%lld) must be multiples of 128 on this backend", (long long)m,
+              (long long)n);
+  const long long total = experts * (m * n / 32);
+  mx_pack_weight_scale_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0,
+                                static_cast<cudaStream_t>(stream_ptr)>>>(
+      static_cast<const uint8_t*>(scale), axis, experts, static_cast<int>(m), static_cast<int>(n),
+      static_cast<uint8_t*>(atoms));
+  HMC_LAUNCH_OK();
+  return 0;
+}

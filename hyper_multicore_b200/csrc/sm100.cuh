@@ -182,6 +182,39 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
                : "memory");
 }
 
+// ------------------------------------------------------------------ block-scaled FP8 (MX) MMA
+// Instruction descriptor of kind::mxf8f6f4.block_scale: E4M3 operands, UE8M0 scales, FP32
+// accumulation. `sf_id` picks which of the four scale bytes of a 32-bit TMEM column this K=32
+// instruction uses, for both operands.
+__host__ __device__ constexpr uint32_t make_idesc_mxf8(uint32_t m, uint32_t n, uint32_t a_major, uint32_t b_major,
+                                                       uint32_t sf_id) {
+  return (sf_id << 4) | (a_major << 15) | (b_major << 16) | ((n >> 3) << 17) | (1u << 23) | ((m >> 4) << 24) |
+         (sf_id << 29);
+}
+__device__ __forceinline__ void umma_mxf8(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                          uint32_t tmem_sfa, uint32_t tmem_sfb, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t"
+      "}\n" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb)
+      : "memory");
+}
+// Shared memory -> TMEM copy of one scale-factor atom: 32 rows x 16 bytes, replicated into all
+// four lane quarters. Issued by one thread; ordered before later MMAs of the same thread.
+__device__ __forceinline__ void tmem_cp_sf(uint32_t taddr, uint64_t smem_desc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(smem_desc) : "memory");
+}
+// Untiled bulk copy global -> shared, completing on an mbarrier (16-byte aligned, size % 16 == 0).
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(smem_dst)),
+               "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+
 // TMEM -> registers: 32 lanes x 32 consecutive 32-bit columns (one row per thread).
 __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(

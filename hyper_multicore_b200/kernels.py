@@ -365,3 +365,30 @@ KERNELS_PER_CALL = {
     "hmc_mega_mhc": 5, "hmc_mega_mhc_grad": 7, "hmc_ep_publish_ready": 1, "hmc_ep_dispatch": 1,
     "hmc_ep_combine": 1, "hmc_ep_wait": 1,
 }
+
+
+# ---------------------------------------------------------------------------------------- MXFP8
+HMC_MXQ_PLAIN, HMC_MXQ_SWIGLU, HMC_MXQ_SWIGLU_GRAD = 0, 1, 2
+KERNELS_PER_CALL.update({"hmc_mx_gemm": 1, "hmc_mx_quant": 1, "hmc_mx_quant_weight": 1,
+                         "hmc_mx_pack_weight_scale": 1})
+
+
+def mx_pad_blocks(rows: int, groups: int) -> int:
+    """Upper bound of the 128-row blocks of the padded expert-major layout."""
+    return (rows + 127) // 128 + groups
+
+
+def mx_gemm(a, a_scale, b, b_scale, c, group_ends, *, mode, rows, pad_blocks, n, k=0, m=0,
+            b_major=HMC_MAJOR_MN, epilogue=HMC_EPI_STORE_BF16, status=None, max_ctas=0) -> None:
+    """Block-scaled FP8 grouped GEMM; see ``hmc_mx_gemm_args`` for the operand layouts."""
+    device = _require_cuda(a, a_scale, b, b_scale, c, group_ends, status)
+    args = _lib.MxGemmArgs()
+    args.mode, args.b_major, args.epilogue = mode, b_major, epilogue
+    args.groups, args.max_ctas = group_ends.numel(), max_ctas
+    args.rows, args.pad_blocks, args.m, args.n, args.k = rows, pad_blocks, m, n, k
+    args.a, args.a_scale = a.data_ptr(), a_scale.data_ptr()
+    args.b, args.b_scale = b.data_ptr(), b_scale.data_ptr()
+    args.c = c.data_ptr()
+    args.group_ends = group_ends.data_ptr()
+    args.status = _lib.ptr(status)
+    _call("hmc_mx_gemm", device, ctypes.byref(args))

@@ -87,6 +87,82 @@ typedef struct hmc_grouped_gemm_args {
 int hmc_grouped_gemm(const hmc_grouped_gemm_args* args, void* stream);
 
 /* ------------------------------------------------------------------------------------------
+ * MXFP8 expert GEMM (tcgen05 kind::mxf8f6f4.block_scale) and its quantisers.
+ * Replaces the reference's MX GMM worker ExecuteMxGmmMatrix
+ * (hyper_multicore/ops/common/mega_moe/adapters/arch35/gmm/mxfp8_worker.h:15-159, descriptor
+ * contracts/mx_gmm_descriptor.h:18-87) and the dual-axis MX quantiser ExecuteMxQuantRange
+ * (adapters/arch35/quantization/dual_axis_mxfp8_worker.h:23-110, kinds plain / SwiGLU+quant /
+ * SwiGLUGrad+quant; graph hyper_multicore/modules/mega_moe/backends/mxfp8/graph.py:116-180).
+ *
+ * Operands are E4M3 with one UE8M0 scale per 32 elements along the contraction axis.
+ * Activations use a PADDED expert-major layout: the rows of group g start at 128 * (number of
+ * 128-row blocks of the groups before it), padding rows are zero, so that 128-row tiles, 32-row
+ * scale blocks and scale-factor atoms never straddle two experts.
+ * Scale factors are stored as 512-byte atoms covering 128 rows (or columns) x 4 consecutive
+ * 32-element blocks: byte (r % 32) * 16 + (r / 32) * 4 + kk, the layout tcgen05.cp expects.
+ *   row-quantised activations : atoms [k / 128][pad_blocks]        (contraction along the row)
+ *   col-quantised activations : atoms [pad_blocks][width / 128]     (contraction along the rows)
+ *   weights, forward          : atoms [groups][k / 128][n / 128]
+ * pad_blocks is the caller's upper bound ceil(rows / 128) + groups; buffers are sized with it.
+ * Limits: k, n (and m for RAGGED_K) multiples of 128.
+ * ------------------------------------------------------------------------------------------ */
+typedef struct hmc_mx_gemm_args {
+  int32_t mode;     /* HMC_GEMM_RAGGED_M or HMC_GEMM_RAGGED_K */
+  int32_t b_major;  /* RAGGED_M: MN = b[groups, k, n], K = b[groups, n, k]. RAGGED_K: ignored */
+  int32_t epilogue; /* HMC_EPI_STORE_BF16, or HMC_EPI_STORE_F32 (RAGGED_K only) */
+  int32_t groups;
+  int32_t max_ctas;
+  int32_t reserved;
+  int64_t rows;       /* un-padded rows (sum of the groups) */
+  int64_t pad_blocks; /* 128-row blocks the padded activation buffers hold */
+  int64_t m;          /* RAGGED_K only */
+  int64_t n;
+  int64_t k;          /* RAGGED_M only */
+  const void* a;      /* RAGGED_M: e4m3 [pad_blocks*128, k] row-quantised. RAGGED_K: e4m3 [pad_blocks*128, m] col-quantised */
+  const void* a_scale;
+  const void* b;      /* RAGGED_M: weight data. RAGGED_K: e4m3 [pad_blocks*128, n] col-quantised */
+  const void* b_scale;
+  void* c;            /* RAGGED_M: bf16 [rows, n] in the UN-padded layout. RAGGED_K: [groups, m, n] */
+  const int64_t* group_ends; /* device int64[groups], cumulative un-padded row ends */
+  int32_t* status;
+} hmc_mx_gemm_args;
+
+int hmc_mx_gemm(const hmc_mx_gemm_args* args, void* stream);
+
+#define HMC_MXQ_PLAIN 0       /* quantise src[rows, width] */
+#define HMC_MXQ_SWIGLU 1      /* src = U[rows, 2*width]; quantise bf16(silu(gate) * up) */
+#define HMC_MXQ_SWIGLU_GRAD 2 /* src = dAct[rows, width/2], aux = U[rows, width]; quantise dU = [dgate | dup] */
+
+typedef struct hmc_mx_quant_args {
+  int32_t kind;   /* HMC_MXQ_* */
+  int32_t groups;
+  int64_t rows;
+  int64_t pad_blocks;
+  int64_t width;  /* columns of the quantised result (multiple of 128) */
+  const void* src;            /* bf16, un-padded expert-major rows */
+  const void* aux;            /* bf16 U for HMC_MXQ_SWIGLU_GRAD */
+  const int64_t* group_ends;
+  void* row_data;             /* optional out: e4m3 [pad_blocks*128, width], 32-blocks along the row */
+  void* row_scale;            /* atoms [width/128][pad_blocks] */
+  void* col_data;             /* optional out: e4m3 [pad_blocks*128, width], 32-blocks down the rows */
+  void* col_scale;            /* atoms [pad_blocks][width/128] */
+  void* dense;                /* optional out: bf16 [rows, width] un-padded (the un-quantised result) */
+} hmc_mx_quant_args;
+
+int hmc_mx_quant(const hmc_mx_quant_args* args, void* stream);
+
+/* Weight helpers. hmc_mx_quant_weight produces the reference's physical fields
+ * (docs/mega_moe.md:169-200): col_data/col_scale [e, m/64, n, 2] (blocks along m) and
+ * row_data/row_scale [e, m, n/64, 2] (blocks along n) from a bf16 weight [e, m, n].
+ * hmc_mx_pack_weight_scale converts one of those scale tensors into the GEMM's atoms:
+ * axis 0 (col_scale): atoms [e][m/128][n/128] with the atom row = n; axis 1 (row_scale):
+ * atoms [e][n/128][m/128] with the atom row = m. */
+int hmc_mx_quant_weight(const void* weight_bf16, int64_t experts, int64_t m, int64_t n, void* col_data,
+                        void* col_scale, void* row_data, void* row_scale, void* stream);
+int hmc_mx_pack_weight_scale(const void* scale, int axis, int64_t experts, int64_t m, int64_t n, void* atoms,
+                             void* stream);
+
+/* ------------------------------------------------------------------------------------------
  * MegaGate.
  * hmc_gate_route replaces torch.ops.hyper_multicore.mega_gate_route(_out)
  * (hyper_multicore/torch/csrc/mega_gate_registration.cpp:10-27, checks mega_gate.cpp:40-61, device
