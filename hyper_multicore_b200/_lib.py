@@ -225,6 +225,7 @@ SIGNATURES: dict[str, tuple] = {
     "hmc_ep_dispatch": (_I, [ctypes.POINTER(EpDispatchArgs), _P]),
     "hmc_ep_combine": (_I, [ctypes.POINTER(EpCombineArgs), _P]),
     "hmc_ep_wait": (_I, [_P, _I, c_uint64, _P, _P]),
+    "hmc_ep_wait_groups": (_I, [_P, _P, _L, c_uint64, _P, _P]),
     "hmc_mega_mhc_workspace_bytes": (_L, [_L, _L]),
     "hmc_mega_mhc_grad_workspace_bytes": (_L, [_L, _L]),
     "hmc_mega_mhc": (_I, [ctypes.POINTER(MegaMhcArgs), _P]),

@@ -197,6 +197,18 @@ __global__ void ep_wait_kernel(const int* counter, int expected, unsigned long l
     report_status(status, HMC_STATUS_TIMEOUT_ARRIVAL, -1, expected, seen);
 }
 
+// One thread per group: bounded wait until the group's arrival counter covers its rows.
+__global__ void ep_wait_groups_kernel(const int* counters, const long long* group_ends, int groups,
+                                      unsigned long long budget_ns, int* status) {
+  const int g = blockIdx.x * blockDim.x + threadIdx.x;
+  if (g >= groups) return;
+  const long long prev = g == 0 ? 0 : group_ends[g - 1];
+  const int need = static_cast<int>(group_ends[g] - prev);
+  int seen = 0;
+  if (!wait_counter_ge(counters + g, need, budget_ns, &seen))
+    report_status(status, HMC_STATUS_TIMEOUT_ARRIVAL, g, need, seen);
+}
+
 int fill_peers(PeerTable* table, void* const* data, void* const* ctrl, int64_t ep) {
   HMC_REQUIRE(ep >= 1 && ep <= HMC_MAX_EP, HMC_ERR_LIMIT, "expert-parallel size must be in [1, %d], got %lld",
               HMC_MAX_EP, (long long)ep);
@@ -320,6 +332,17 @@ extern "C" int hmc_ep_wait(const int32_t* counter, int32_t expected, uint64_t bu
   HMC_REQUIRE(counter != nullptr, HMC_ERR_INVALID, "hmc_ep_wait: null counter");
   ep_wait_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream_ptr)>>>(
       counter, expected, budget_ns ? budget_ns : 10ull * 1000 * 1000 * 1000, status);
+  HMC_LAUNCH_OK();
+  return 0;
+}
+
+extern "C" int hmc_ep_wait_groups(const int32_t* counters, const int64_t* group_ends, int64_t groups,
+                                  uint64_t budget_ns, int32_t* status, void* stream_ptr) {
+  HMC_REQUIRE(counters != nullptr && group_ends != nullptr && groups > 0 && groups <= HMC_CTRL_MAX_LOCAL_EXPERTS,
+              HMC_ERR_INVALID, "hmc_ep_wait_groups: bad arguments");
+  ep_wait_groups_kernel<<<static_cast<unsigned>((groups + 127) / 128), 128, 0, static_cast<cudaStream_t>(stream_ptr)>>>(
+      counters, reinterpret_cast<const long long*>(group_ends), static_cast<int>(groups),
+      budget_ns ? budget_ns : 10ull * 1000 * 1000 * 1000, status);
   HMC_LAUNCH_OK();
   return 0;
 }

@@ -363,7 +363,7 @@ KERNELS_PER_CALL = {
     "hmc_moe_permute_from_mapping": 1, "hmc_moe_unpermute": 1, "hmc_moe_unpermute_grad": 1,
     "hmc_moe_token_permute_grad": 1, "hmc_zero_empty_expert_grad": 1, "hmc_route_offsets": 1,
     "hmc_mega_mhc": 5, "hmc_mega_mhc_grad": 7, "hmc_ep_publish_ready": 1, "hmc_ep_dispatch": 1,
-    "hmc_ep_combine": 1, "hmc_ep_wait": 1,
+    "hmc_ep_combine": 1, "hmc_ep_wait": 1, "hmc_ep_wait_groups": 1,
 }
 
 
@@ -392,3 +392,67 @@ def mx_gemm(a, a_scale, b, b_scale, c, group_ends, *, mode, rows, pad_blocks, n,
     args.group_ends = group_ends.data_ptr()
     args.status = _lib.ptr(status)
     _call("hmc_mx_gemm", device, ctypes.byref(args))
+
+
+def ep_wait_groups(counters: torch.Tensor, group_ends: torch.Tensor, status=None, budget_ns: int = 0) -> None:
+    """Stream-ordered bounded wait until every group's arrival counter covers its rows."""
+    device = _require_cuda(counters, group_ends)
+    _call("hmc_ep_wait_groups", device, counters.data_ptr(), group_ends.data_ptr(), group_ends.numel(), budget_ns,
+          _lib.ptr(status))
+
+
+class MxActivations:
+    """Quantised activations in the padded expert-major layout (see ``hmc_mx_quant_args``)."""
+
+    def __init__(self, rows: int, groups: int, width: int, device, *, want_row: bool, want_col: bool) -> None:
+        self.rows, self.width = rows, width
+        self.pad_blocks = mx_pad_blocks(rows, groups)
+        u8 = dict(dtype=torch.uint8, device=device)
+        pad_rows = self.pad_blocks * 128
+        atoms = self.pad_blocks * (width // 128) * 512
+        self.row_data = torch.empty((pad_rows, width), **u8) if want_row else None
+        self.row_scale = torch.empty(atoms, **u8) if want_row else None
+        self.col_data = torch.empty((pad_rows, width), **u8) if want_col else None
+        self.col_scale = torch.empty(atoms, **u8) if want_col else None
+
+
+def mx_quant(src, group_ends, width, *, kind=HMC_MXQ_PLAIN, aux=None, want_row=True, want_col=False,
+             dense=None) -> MxActivations:
+    """Quantise expert-major BF16 rows (optionally through SwiGLU / SwiGLU-grad) to MXFP8."""
+    device = _require_cuda(src, group_ends, aux, dense)
+    rows, groups = src.shape[0], group_ends.numel()
+    out = MxActivations(rows, groups, width, device, want_row=want_row, want_col=want_col)
+    args = _lib.MxQuantArgs()
+    args.kind, args.groups = kind, groups
+    args.rows, args.pad_blocks, args.width = rows, out.pad_blocks, width
+    args.src, args.aux, args.group_ends = src.data_ptr(), _lib.ptr(aux), group_ends.data_ptr()
+    args.row_data, args.row_scale = _lib.ptr(out.row_data), _lib.ptr(out.row_scale)
+    args.col_data, args.col_scale = _lib.ptr(out.col_data), _lib.ptr(out.col_scale)
+    args.dense = _lib.ptr(dense)
+    _call("hmc_mx_quant", device, ctypes.byref(args))
+    return out
+
+
+def mx_quant_weight(weight: torch.Tensor, *, want_col: bool = True, want_row: bool = True) -> dict:
+    """BF16 weight [e, m, n] -> the reference's physical MX fields (col_* blocks along m, row_* along n)."""
+    device = _require_cuda(weight)
+    experts, m, n = weight.shape
+    weight = weight.contiguous()
+    out = {}
+    if want_col:
+        out["col_data"] = torch.empty((experts, m, n), dtype=torch.float8_e4m3fn, device=device)
+        out["col_scale"] = torch.empty((experts, m // 64, n, 2), dtype=torch.uint8, device=device)
+    if want_row:
+        out["row_data"] = torch.empty((experts, m, n), dtype=torch.float8_e4m3fn, device=device)
+        out["row_scale"] = torch.empty((experts, m, n // 64, 2), dtype=torch.uint8, device=device)
+    _call("hmc_mx_quant_weight", device, weight.data_ptr(), experts, m, n, _lib.ptr(out.get("col_data")),
+          _lib.ptr(out.get("col_scale")), _lib.ptr(out.get("row_data")), _lib.ptr(out.get("row_scale")))
+    return out
+
+
+def mx_pack_weight_scale(scale: torch.Tensor, axis: int, experts: int, m: int, n: int) -> torch.Tensor:
+    """Reference scale tensor (col_scale: axis 0, row_scale: axis 1) -> scale-factor atoms for the GEMM."""
+    device = _require_cuda(scale)
+    atoms = torch.empty(experts * m * n // 32, dtype=torch.uint8, device=device)
+    _call("hmc_mx_pack_weight_scale", device, scale.data_ptr(), axis, experts, m, n, atoms.data_ptr())
+    return atoms

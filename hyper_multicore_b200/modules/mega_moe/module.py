@@ -129,17 +129,20 @@ class _MegaMoeFunction(torch.autograd.Function):
     def forward(ctx, hidden, probs, w1, w2, module, route: PreparedRoute):  # pylint: disable=arguments-differ
         ctx.module = module
         ctx.route = route
-        out, saved = module._run_forward(hidden, probs, w1, w2, route)  # pylint: disable=protected-access
+        # grad mode is off inside Function.forward: whether a backward can follow is what the inputs say
+        module._backward_expected = any(ctx.needs_input_grad[:4])  # pylint: disable=protected-access
+        run = module._run_forward_mx if module.precision == "mxfp8" else module._run_forward  # pylint: disable=protected-access
+        out, saved = run(hidden, probs, w1, w2, route)
         ctx.save_for_backward(hidden, probs, w1, w2, *saved)
         return out
 
     @staticmethod
     @torch.autograd.function.once_differentiable
     def backward(ctx, grad_output):  # pylint: disable=arguments-differ
-        hidden, probs, w1, w2, received, up_proj, activation, routed_out = ctx.saved_tensors
-        grads = ctx.module._run_backward(  # pylint: disable=protected-access
-            grad_output.contiguous(), hidden, probs, w1, w2, received, up_proj, activation, routed_out, ctx.route,
-            need_weight_grads=(ctx.needs_input_grad[2], ctx.needs_input_grad[3]))
+        hidden, probs, w1, w2, *saved = ctx.saved_tensors
+        run = ctx.module._run_backward_mx if ctx.module.precision == "mxfp8" else ctx.module._run_backward  # pylint: disable=protected-access
+        grads = run(grad_output.contiguous(), hidden, probs, w1, w2, *saved, ctx.route,
+                    need_weight_grads=(ctx.needs_input_grad[2], ctx.needs_input_grad[3]))
         grad_hidden, grad_probs, grad_w1, grad_w2 = grads
         return (grad_hidden if ctx.needs_input_grad[0] else None,
                 grad_probs if ctx.needs_input_grad[1] else None,
@@ -174,9 +177,9 @@ class MegaMoeExperts(torch.nn.Module):
                     f"{name} must be a positive integer multiple of {_COMMUNICATION_SPLIT}, got {split!r}.")
         if hidden_size % 8 or intermediate_size % 8:
             raise ValueError("hidden_size and intermediate_size must be multiples of 8 (16-byte BF16 rows)")
-        if precision == "mxfp8":
-            raise NotImplementedError(
-                "precision='mxfp8' is not available yet in the sm_100a backend; use precision='bf16'")
+        if precision == "mxfp8" and (hidden_size % 128 or intermediate_size % 128):
+            raise ValueError("precision='mxfp8' needs hidden_size and intermediate_size to be multiples of 128 "
+                             "on the sm_100a backend (the reference requires multiples of 64)")
         if tuning.dispatch_mode != "push":
             raise NotImplementedError("dispatch_mode='pull' is not available in the sm_100a backend; use 'push'")
         if numerics.swiglu_limit is not None or numerics.apply_probs_before_fc2:
@@ -194,6 +197,8 @@ class MegaMoeExperts(torch.nn.Module):
         self._numerics = numerics
         self._tuning = tuning
         self._layout: str | None = None
+        self._scale_atoms: dict = {}
+        self._backward_expected = False
         self._workspace: PeerWorkspace | _LocalWorkspace | None = None
         self._status: torch.Tensor | None = None
         local, hidden, inter = self.local_experts, hidden_size, intermediate_size
@@ -228,12 +233,44 @@ class MegaMoeExperts(torch.nn.Module):
             f"expert_weights must have EIO shapes {self._weight_shapes['EIO']} or EOI shapes "
             f"{self._weight_shapes['EOI']}, got {(shape1, shape2)}.")
 
+    def _validate_mx_weights(self, hidden: torch.Tensor, weight1, weight2) -> None:
+        """MXFP8 roots carry their physical fields as attributes (reference: backends/mxfp8/weights.py:36-86)."""
+        shapes = self._weight_shapes["EIO"]
+        for name, root, (experts, rows, cols) in (("gate_up_weight", weight1, shapes[0]), ("down_weight", weight2, shapes[1])):
+            if not isinstance(root, torch.Tensor):
+                raise _InvalidExpertWeightType("MegaMoE MXFP8 weights require an original tensor root with physical MX storage.")
+            if tuple(root.shape) not in ((experts, rows, cols), (experts * rows, cols)):
+                raise _InvalidExpertWeights(
+                    f"MegaMoE MXFP8 root shape {tuple(root.shape)} does not match expert shape {(experts, rows, cols)}.")
+            if root.device != hidden.device:
+                raise _InvalidExpertWeights("expert weights and hidden states must be on the same GPU.")
+            data, scale = getattr(root, "col_data", None), getattr(root, "col_scale", None)
+            if data is None or scale is None:
+                raise _InvalidExpertWeights(f"MegaMoE MXFP8 current root ({name}) is missing required col data/scale.")
+            self._check_mx_pair(data, scale, root, (experts, rows, cols), "col")
+        self._pending_layout = "EIO"
+
+    @staticmethod
+    def _check_mx_pair(data, scale, root, shape, direction):
+        experts, rows, cols = shape
+        if data.dtype != torch.float8_e4m3fn or scale.dtype != torch.uint8:
+            raise _InvalidExpertWeightType("MegaMoE MXFP8 physical storage requires E4M3FN data and packed uint8 E8M0 scales.")
+        if not data.is_contiguous() or not scale.is_contiguous():
+            raise _InvalidExpertWeights("MX physical data and scale must be contiguous; implicit copies are forbidden")
+        if data.device != root.device or scale.device != root.device:
+            raise _InvalidExpertWeights("MX physical data, scales and current root must share a device")
+        if data.numel() != experts * rows * cols or scale.numel() != experts * rows * cols // 32:
+            raise _InvalidExpertWeights(f"MX {direction} data/scale sizes do not match expert shape {shape}")
+
     def _validate_weights(self, hidden: torch.Tensor, expert_weights) -> None:
         try:
             weight1, weight2 = expert_weights
             shape1, shape2 = tuple(weight1.shape), tuple(weight2.shape)
         except (AttributeError, TypeError, ValueError) as error:
             raise _InvalidExpertWeights("expert_weights must contain two tensors") from error
+        if self._precision == "mxfp8":
+            self._validate_mx_weights(hidden, weight1, weight2)
+            return
         if self._layout is None:
             layout = self._infer_layout(shape1, shape2)
         else:
@@ -491,4 +528,150 @@ class MegaMoeExperts(torch.nn.Module):
             grad_w1 = grad_w1.to(w1.dtype)
         if grad_w2 is not None and grad_w2.dtype != w2.dtype:
             grad_w2 = grad_w2.to(w2.dtype)
+        return grad_hidden, grad_probs, grad_w1, grad_w2
+
+    # ------------------------------------------------------------------ MXFP8 backend
+    def _atoms(self, root: torch.Tensor, direction: str, shape) -> torch.Tensor:
+        """Scale-factor atoms of one weight axis, re-packed only when the scale tensor changed."""
+        scale = getattr(root, f"{direction}_scale", None)
+        data = getattr(root, f"{direction}_data", None)
+        if scale is None or data is None:
+            raise ValueError(f"MegaMoE MXFP8 current root is missing required {direction} data/scale.")
+        self._check_mx_pair(data, scale, root, shape, direction)
+        key = (id(root), direction)
+        stamp = (scale.data_ptr(), scale._version)  # pylint: disable=protected-access
+        cached = self._scale_atoms.get(key)
+        if cached is None or cached[0] != stamp:
+            experts, rows, cols = shape
+            atoms = kernels.mx_pack_weight_scale(scale, 0 if direction == "col" else 1, experts, rows, cols)
+            self._scale_atoms[key] = cached = (stamp, atoms)
+        return cached[1]
+
+    def _mx_exchange(self, source, source_of_row, route, generation_hint=None):
+        """Dispatch rows to their owners and wait until every local expert's rows have landed."""
+        workspace = self._workspace
+        device = source.device
+        received, routed_rows = route.received_rows, route.routed_rows
+        generation = workspace.begin_call()
+        if self.ep_size == 1:
+            expert_buffer = torch.empty(max(received, 1), self.hidden_size, dtype=torch.bfloat16, device=device)
+            capacity = expert_buffer.shape[0]
+        else:
+            expert_buffer = workspace.expert_buffer
+            capacity = workspace.capacity_rows
+        peer_expert, peer_routed, peer_ctrl = self._peer_tables(workspace, expert_buffer)
+        off = route.offsets
+        kernels.ep_dispatch(source, source_of_row, route.expert_of_row, off["dispatch_src_off"],
+                            off["dispatch_target_off"], rows=routed_rows, top_k=self.top_k, ep=self.ep_size,
+                            local_experts=self.local_experts, capacity_rows=capacity, peer_buffers=peer_expert,
+                            peer_ctrl=peer_ctrl, local_ctrl=workspace.ctrl, generation=generation,
+                            status=self._status)
+        arrival = workspace.ctrl[_lib.HMC_CTRL_ARRIVAL:_lib.HMC_CTRL_ARRIVAL + self.local_experts]
+        kernels.ep_wait_groups(arrival, off["group_list"], status=self._status)
+        return expert_buffer[:max(received, 1)], generation, peer_routed, peer_ctrl
+
+    def _mx_return(self, rows_tensor, route, generation, peer_routed, peer_ctrl):
+        """Combine result rows back to their sources (identity at ep_size == 1)."""
+        if self.ep_size == 1:
+            return rows_tensor
+        workspace = self._workspace
+        off = route.offsets
+        kernels.ep_combine(rows_tensor, off["recv_segment_start"], off["combine_target_off"], rows=route.received_rows,
+                           ep=self.ep_size, local_experts=self.local_experts,
+                           target_rows_limit=workspace.routed_rows, peer_buffers=peer_routed, peer_ctrl=peer_ctrl,
+                           local_ctrl=workspace.ctrl, generation=generation, status=self._status)
+        kernels.ep_wait(workspace.ctrl[_lib.HMC_CTRL_COMBINE:], route.routed_rows, status=self._status)
+        return workspace.routed_buffer
+
+    def _run_forward_mx(self, hidden, probs, root1, root2, route: PreparedRoute):
+        """dispatch -> quant X -> GEMM1 -> SwiGLU + quant -> GEMM2 -> combine -> K-sum
+        (reference graph: backends/mxfp8/graph.py:140-146)."""
+        device = hidden.device
+        inter, hid, local = self.intermediate_size, self.hidden_size, self.local_experts
+        received = route.received_rows
+        rows = max(received, 1)
+        bf16 = dict(dtype=torch.bfloat16, device=device)
+        ends = route.offsets["group_list"]
+        training = self._backward_expected
+        x_recv, generation, peer_routed, peer_ctrl = self._mx_exchange(hidden, route.source_of_row, route)
+        up_proj = torch.empty(rows, 2 * inter, **bf16)
+        down_proj = torch.empty(rows, hid, **bf16)
+        x_q = act_q = None
+        if received > 0:
+            x_q = kernels.mx_quant(x_recv[:received], ends, hid, want_row=True, want_col=training)
+            kernels.mx_gemm(x_q.row_data, x_q.row_scale, root1.col_data, self._atoms(root1, "col", (local, hid, 2 * inter)),
+                            up_proj, ends, mode=kernels.HMC_GEMM_RAGGED_M, rows=received, pad_blocks=x_q.pad_blocks,
+                            n=2 * inter, k=hid, b_major=kernels.HMC_MAJOR_MN, status=self._status)
+            act_q = kernels.mx_quant(up_proj[:received], ends, inter, kind=kernels.HMC_MXQ_SWIGLU, want_row=True,
+                                     want_col=training)
+            kernels.mx_gemm(act_q.row_data, act_q.row_scale, root2.col_data, self._atoms(root2, "col", (local, inter, hid)),
+                            down_proj, ends, mode=kernels.HMC_GEMM_RAGGED_M, rows=received, pad_blocks=act_q.pad_blocks,
+                            n=hid, k=inter, b_major=kernels.HMC_MAJOR_MN, status=self._status)
+        returned = self._mx_return(down_proj, route, generation, peer_routed, peer_ctrl)
+        routed_out = returned if self.ep_size == 1 else returned[:max(route.routed_rows, 1)].clone()
+        out = torch.empty(hidden.shape[0], hid, **bf16)
+        kernels.moe_unpermute(routed_out, route.mapping, probs, hidden.shape[0], self.top_k, out, status=self._status)
+        empty = torch.empty(0, dtype=torch.uint8, device=device)
+        saved = (up_proj, routed_out,
+                 x_q.col_data if x_q is not None and training else empty,
+                 x_q.col_scale if x_q is not None and training else empty,
+                 act_q.col_data if act_q is not None and training else empty,
+                 act_q.col_scale if act_q is not None and training else empty)
+        return out, saved
+
+    def _run_backward_mx(self, grad_output, hidden, probs, root1, root2, up_proj, routed_out, x_col, x_col_scale,
+                         act_col, act_col_scale, route: PreparedRoute, need_weight_grads):
+        """dispatch dY -> quant -> dA -> SwiGLU-grad + quant -> dX, dW2, dW1 -> combine
+        (reference graph: backends/mxfp8/graph.py:147-154)."""
+        device = hidden.device
+        inter, hid, local = self.intermediate_size, self.hidden_size, self.local_experts
+        received, routed_rows = route.received_rows, route.routed_rows
+        rows = max(received, 1)
+        tokens = hidden.shape[0]
+        bf16 = dict(dtype=torch.bfloat16, device=device)
+        ends = route.offsets["group_list"]
+        grad_routed = torch.empty(max(routed_rows, 1), hid, **bf16)
+        grad_probs = torch.empty(tokens, self.top_k, dtype=torch.float32, device=device)
+        kernels.moe_unpermute_grad(routed_out, grad_output, route.mapping, probs, self.top_k, grad_routed, grad_probs,
+                                   status=self._status)
+        dy_recv, generation, peer_routed, peer_ctrl = self._mx_exchange(grad_routed, None, route)
+        f32_partials = self._numerics.partial_weight_grad_dtype == "float32"
+        wdtype = torch.float32 if f32_partials else torch.bfloat16
+        wepi = kernels.HMC_EPI_STORE_F32 if f32_partials else kernels.HMC_EPI_STORE_BF16
+        shape1, shape2 = (local, hid, 2 * inter), (local, inter, hid)
+        grad_w1 = torch.empty(shape1, dtype=wdtype, device=device) if need_weight_grads[0] else None
+        grad_w2 = torch.empty(shape2, dtype=wdtype, device=device) if need_weight_grads[1] else None
+        grad_x_rows = torch.empty(rows, hid, **bf16)
+        if received > 0:
+            want_col = grad_w1 is not None or grad_w2 is not None
+            dy_q = kernels.mx_quant(dy_recv[:received], ends, hid, want_row=True, want_col=want_col)
+            grad_act = torch.empty(rows, inter, **bf16)
+            # W2 [e, I, H] row-quantised (blocks along H) is the K-major B of dA = dY . W2^T
+            kernels.mx_gemm(dy_q.row_data, dy_q.row_scale, root2.row_data, self._atoms(root2, "row", shape2), grad_act,
+                            ends, mode=kernels.HMC_GEMM_RAGGED_M, rows=received, pad_blocks=dy_q.pad_blocks, n=inter,
+                            k=hid, b_major=kernels.HMC_MAJOR_K, status=self._status)
+            du_q = kernels.mx_quant(grad_act[:received], ends, 2 * inter, kind=kernels.HMC_MXQ_SWIGLU_GRAD,
+                                    aux=up_proj[:received], want_row=True, want_col=want_col)
+            kernels.mx_gemm(du_q.row_data, du_q.row_scale, root1.row_data, self._atoms(root1, "row", shape1), grad_x_rows,
+                            ends, mode=kernels.HMC_GEMM_RAGGED_M, rows=received, pad_blocks=du_q.pad_blocks, n=hid,
+                            k=2 * inter, b_major=kernels.HMC_MAJOR_K, status=self._status)
+            if grad_w2 is not None:
+                kernels.mx_gemm(act_col, act_col_scale, dy_q.col_data, dy_q.col_scale, grad_w2, ends,
+                                mode=kernels.HMC_GEMM_RAGGED_K, rows=received, pad_blocks=dy_q.pad_blocks, m=inter, n=hid,
+                                epilogue=wepi, status=self._status)
+            if grad_w1 is not None:
+                kernels.mx_gemm(x_col, x_col_scale, du_q.col_data, du_q.col_scale, grad_w1, ends,
+                                mode=kernels.HMC_GEMM_RAGGED_K, rows=received, pad_blocks=du_q.pad_blocks, m=hid,
+                                n=2 * inter, epilogue=wepi, status=self._status)
+        else:
+            for grad in (grad_w1, grad_w2):
+                if grad is not None:
+                    grad.zero_()
+        returned = self._mx_return(grad_x_rows, route, generation, peer_routed, peer_ctrl)
+        grad_hidden = torch.empty(tokens, hid, **bf16)
+        kernels.moe_token_permute_grad(returned, route.mapping, tokens, self.top_k, grad_hidden, status=self._status)
+        if grad_w1 is not None:
+            grad_w1 = grad_w1.to(root1.dtype).reshape(root1.shape)
+        if grad_w2 is not None:
+            grad_w2 = grad_w2.to(root2.dtype).reshape(root2.shape)
         return grad_hidden, grad_probs, grad_w1, grad_w2

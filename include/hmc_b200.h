@@ -437,6 +437,10 @@ int hmc_ep_dispatch(const hmc_ep_dispatch_args* args, void* stream);
 int hmc_ep_combine(const hmc_ep_combine_args* args, void* stream);
 /* Bounded device-side wait until *counter >= expected; on time-out writes HMC_STATUS_TIMEOUT_ARRIVAL. */
 int hmc_ep_wait(const int32_t* counter, int32_t expected, uint64_t budget_ns, int32_t* status, void* stream);
+/* Bounded device-side wait until counters[g] >= rows of group g for every group (used where a
+ * kernel without its own arrival gating consumes dispatched rows, e.g. the MX quantiser). */
+int hmc_ep_wait_groups(const int32_t* counters, const int64_t* group_ends, int64_t groups, uint64_t budget_ns,
+                       int32_t* status, void* stream);
 
 #ifdef __cplusplus
 }
