@@ -37,6 +37,43 @@ def check(name, got, expected):
                                msg=lambda m: f"{name}: {m}")
 
 
+def scenario_mx(module, rank, world, device, token_counts, hidden, inter, experts, top_k, seed):
+    """MXFP8 backend across ranks against the MX oracle on the concatenated batch. Rows of one
+    expert arrive source-rank-major, which is the row order of the concatenated batch, so the
+    token-axis quantisation blocks of the weight gradients line up with the oracle's."""
+    from hyper_multicore_b200.mxfp8 import attach_mx_fields
+    from oracle import mxfp8 as omx
+    from tests.helpers import rel_l2
+
+    local = experts // world
+    gw = torch.Generator().manual_seed(seed)
+    w1_all = (torch.randn(experts, hidden, 2 * inter, generator=gw) * 0.05).bfloat16()
+    w2_all = (torch.randn(experts, inter, hidden, generator=gw) * 0.05).bfloat16()
+    per_rank = [make_rank_inputs(r, token_counts[r], hidden, experts, top_k, seed) for r in range(world)]
+    x, ids, probs, grad = per_rank[rank]
+    w1 = attach_mx_fields(w1_all[rank * local:(rank + 1) * local].contiguous().to(device).requires_grad_(True))
+    w2 = attach_mx_fields(w2_all[rank * local:(rank + 1) * local].contiguous().to(device).requires_grad_(True))
+    xd = x.to(device).requires_grad_(True)
+    pd = probs.to(device).requires_grad_(True)
+    out = module(xd, ids.to(device), pd, expert_weights=(w1, w2))
+    out.backward(grad.to(device))
+    module.check_status()
+    ref = omx.experts_forward_backward(
+        torch.cat([p[0] for p in per_rank]), torch.cat([p[1] for p in per_rank]),
+        torch.cat([p[2] for p in per_rank]), w1_all, w2_all, torch.cat([p[3] for p in per_rank]))
+    start = sum(token_counts[:rank])
+    rows = slice(start, start + token_counts[rank])
+    experts_slice = slice(rank * local, (rank + 1) * local)
+    for name, got, expected, limit in (
+            ("output", out, ref["output"][rows], 1e-2), ("grad_hidden", xd.grad, ref["grad_hidden"][rows], 3e-2),
+            ("grad_probs", pd.grad, ref["grad_probs"][rows], 3e-2),
+            ("grad_w1", w1.grad, ref["grad_w1"][experts_slice], 3e-2),
+            ("grad_w2", w2.grad, ref["grad_w2"][experts_slice], 3e-2)):
+        if expected.numel():
+            error = rel_l2(got.detach().cpu().float(), expected.float())
+            assert error <= limit, (name, error)
+
+
 def scenario(module, rank, world, device, token_counts, hidden, inter, experts, top_k, seed, layout):
     local = experts // world
     gw = torch.Generator().manual_seed(seed)
@@ -92,6 +129,11 @@ def main():
         state = module.debug_state()
         assert state["ep"] == world and state["generation"] >= 10, state
         module.close()
+    module = MegaMoeExperts(hidden_size=hidden, intermediate_size=inter, num_experts=experts, top_k=top_k,
+                            ep_group=dist.group.WORLD, precision="mxfp8")
+    for index, counts in enumerate(([96] * world, [40 + 57 * r for r in range(world)], [0] + [200] * (world - 1))):
+        scenario_mx(module, rank, world, device, counts, hidden, inter, experts, top_k, seed=30 + index)
+    module.close()
     dist.barrier()
     if rank == 0:
         print(f"EP={world} ok", flush=True)
