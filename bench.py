@@ -30,7 +30,27 @@ import torch
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
+# Default: the per-rank problem of the EP=2 BF16 configuration. "c3" is the per-rank problem of the
+# EP=8 MXFP8 configuration (32 experts per rank, Zipf(1.1) expert load); its expert count scales with
+# the number of ranks so that every rank keeps 32 local experts.
+SHAPES = {
+    "c2": dict(tokens=4096, hidden=4096, experts=32, top_k=4, inter=1536, experts_per_rank=None, zipf=None),
+    "c3": dict(tokens=8192, hidden=7168, experts=None, top_k=8, inter=2048, experts_per_rank=32, zipf=1.1),
+}
 TOKENS, HIDDEN, EXPERTS, TOP_K, INTER = 4096, 4096, 32, 4, 1536
+ZIPF = None
+PRECISION = "bf16"
+
+
+def select_shape(name: str, world: int, precision: str) -> None:
+    """Bind the module-level workload constants."""
+    global TOKENS, HIDDEN, EXPERTS, TOP_K, INTER, FLOPS_PER_TOKEN, ZIPF, PRECISION  # pylint: disable=global-statement
+    shape = SHAPES[name]
+    TOKENS, HIDDEN, TOP_K, INTER = shape["tokens"], shape["hidden"], shape["top_k"], shape["inter"]
+    EXPERTS = shape["experts"] if shape["experts"] is not None else shape["experts_per_rank"] * world
+    ZIPF = shape["zipf"]
+    PRECISION = precision
+    FLOPS_PER_TOKEN = 18 * TOP_K * HIDDEN * INTER
 METRIC = "moe_layer_fwd_bwd_tokens_per_s"
 UNIT = "tokens/s"
 # forward 6*K*H*I flops per token (two GEMMs), backward 12*K*H*I (four GEMMs)
@@ -41,25 +61,43 @@ FLOPS_PER_TOKEN = 18 * TOP_K * HIDDEN * INTER
 GEMM_DRAM_BYTES_PER_STEP = 4.98e9
 
 
-def make_inputs(rank: int, ep: int):
+def make_inputs(rank: int, ep: int, device=None):
     """Seeded synthetic inputs of the configuration's shapes and distributions (CPU, then copied)."""
     g = torch.Generator().manual_seed(1234 + rank)
     x = torch.randn(TOKENS, HIDDEN, generator=g).bfloat16()
     # "uniform-ish" router logits: U(-1, 1) plus small noise, softmax, top-4
     logits = torch.rand(TOKENS, EXPERTS, generator=g) * 2 - 1 + 0.01 * torch.randn(TOKENS, EXPERTS, generator=g)
-    weights, ids = torch.topk(logits.softmax(dim=-1), TOP_K, dim=-1)
+    if ZIPF is not None:
+        # skewed router logits: expert popularity follows Zipf(s) over a fixed random ranking (Gumbel top-k)
+        ranking = torch.randperm(EXPERTS, generator=torch.Generator().manual_seed(99))
+        popularity = torch.empty(EXPERTS)
+        popularity[ranking] = torch.arange(1, EXPERTS + 1, dtype=torch.float32).pow(-ZIPF)
+        gumbel = -torch.log(-torch.log(torch.rand(TOKENS, EXPERTS, generator=g).clamp_min(1e-9)))
+        logits = popularity.log() + gumbel
+        weights, ids = torch.topk(logits.sigmoid(), TOP_K, dim=-1)
+        weights = weights / weights.sum(dim=-1, keepdim=True)
+    else:
+        weights, ids = torch.topk(logits.softmax(dim=-1), TOP_K, dim=-1)
     grad_out = torch.randn(TOKENS, HIDDEN, generator=g).bfloat16()
     local = EXPERTS // ep
-    gw = torch.Generator().manual_seed(4321 + rank)
-    w1 = (torch.randn(local, HIDDEN, 2 * INTER, generator=gw) * 0.02).bfloat16()
-    w2 = (torch.randn(local, INTER, HIDDEN, generator=gw) * 0.02).bfloat16()
+    if device is not None:
+        # large shapes: draw the weights on the GPU (seeded), there is nothing to compare them with on the CPU
+        gw = torch.Generator(device=device).manual_seed(4321 + rank)
+        w1 = (torch.randn(local, HIDDEN, 2 * INTER, generator=gw, device=device) * 0.02).bfloat16()
+        w2 = (torch.randn(local, INTER, HIDDEN, generator=gw, device=device) * 0.02).bfloat16()
+    else:
+        gw = torch.Generator().manual_seed(4321 + rank)
+        w1 = (torch.randn(local, HIDDEN, 2 * INTER, generator=gw) * 0.02).bfloat16()
+        w2 = (torch.randn(local, INTER, HIDDEN, generator=gw) * 0.02).bfloat16()
     return x, ids, weights.contiguous(), grad_out, w1, w2
 
 
 def config(ep: int) -> dict:
     return {
-        "workload": (f"MegaMoE BF16 forward+backward, EP={ep}, {TOKENS} tokens/rank, hidden {HIDDEN}, "
-                     f"{EXPERTS} experts ({EXPERTS // ep}/rank), softmax top-{TOP_K}, SwiGLU intermediate {INTER}"),
+        "workload": (f"MegaMoE {PRECISION.upper()} forward+backward, EP={ep}, {TOKENS} tokens/rank, hidden {HIDDEN}, "
+                     f"{EXPERTS} experts ({EXPERTS // ep}/rank), "
+                     f"{'sigmoid top-' + str(TOP_K) + ' with Zipf(' + str(ZIPF) + ') load' if ZIPF else 'softmax top-' + str(TOP_K)}, "
+                     f"SwiGLU intermediate {INTER}"),
         "tokens_per_rank": TOKENS, "hidden": HIDDEN, "experts": EXPERTS, "top_k": TOP_K, "intermediate": INTER,
         "ep": ep, "layout": "EIO",
         "l2": "no flush: each step streams >1.4 GB of weights and activations through the 126 MB L2",
@@ -218,11 +256,16 @@ def run_gpu(args) -> None:
             dist.barrier()
         torch.cuda.synchronize()
 
-    x_h, ids_h, p_h, g_h, w1_h, w2_h = make_inputs(rank, world)
+    x_h, ids_h, p_h, g_h, w1_h, w2_h = make_inputs(rank, world, device if args.shape != "c2" else None)
     w1 = w1_h.to(device).requires_grad_(True)
     w2 = w2_h.to(device).requires_grad_(True)
+    if PRECISION == "mxfp8":
+        from hyper_multicore_b200.mxfp8 import attach_mx_fields
+
+        attach_mx_fields(w1)
+        attach_mx_fields(w2)
     module = MegaMoeExperts(hidden_size=HIDDEN, intermediate_size=INTER, num_experts=EXPERTS, top_k=TOP_K,
-                            ep_group=group)
+                            ep_group=group, precision=PRECISION)
 
     # device-resident inputs
     x_d = x_h.to(device).requires_grad_(True)
@@ -280,7 +323,8 @@ def run_gpu(args) -> None:
     module.check_status()
 
     # per-launch duration of the dominant kernel (the grouped GEMM), CUDA events on the launch stream
-    original = kernels.grouped_gemm
+    gemm_name = "mx_gemm" if PRECISION == "mxfp8" else "grouped_gemm"
+    original = getattr(kernels, gemm_name)
     pairs: list = []
 
     def instrumented(*a, **kw):
@@ -290,12 +334,12 @@ def run_gpu(args) -> None:
         e1.record()
         pairs.append((e0, e1))
 
-    kernels.grouped_gemm = instrumented
+    setattr(kernels, gemm_name, instrumented)
     profile_steps = min(args.steps, 5)
     for _ in range(profile_steps):
         step_resident()
     barrier()
-    kernels.grouped_gemm = original
+    setattr(kernels, gemm_name, original)
     gemm_ms_per_step = sum(a.elapsed_time(b) for a, b in pairs) / profile_steps
     gemm_launches_per_step = len(pairs) // profile_steps
 
@@ -311,6 +355,9 @@ def run_gpu(args) -> None:
         peak_tflops, peak_note = float(peaks["bf16_tflops_sustained"]), "of measured (sustained cuBLAS bf16)"
     else:
         peak_tflops, peak_note = 1400.0, "of fallback (sustained)"
+    if PRECISION == "mxfp8":
+        # no FP8 peak was measured on this pool: the dense FP8 rate is twice the BF16 one
+        peak_tflops, peak_note = 2 * peak_tflops, "2 x " + peak_note[3:] + " (no FP8 peak measured)"
     flops_per_step = FLOPS_PER_TOKEN * TOKENS  # per rank: every rank owns an equal share in expectation
     achieved = flops_per_step / (gemm_ms_per_step * 1e-3) / 1e12
     ms_per_step = total_ms / args.steps
@@ -318,24 +365,27 @@ def run_gpu(args) -> None:
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "bf16", "data": "synthetic", "config": config(world),
+        "dtype": "bf16" if PRECISION == "bf16" else "mxfp8 (e4m3 + ue8m0/32) operands, bf16 activations",
+        "data": "synthetic", "config": config(world),
         "clocks": clocks,
         "e2e": {"value": world * TOKENS / (e2e_ms / args.steps * 1e-3), "unit": UNIT,
                 "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes,
                 "ms_per_step": e2e_ms / args.steps},
         "gpu_launches": launches,
         "roofline": {
-            "bound": "tensor", "kernel": "grouped_gemm_kernel (tcgen05, 6 launches per step)",
+            "bound": "tensor",
+            "kernel": ("mx_gemm_kernel (tcgen05 block-scaled FP8" if PRECISION == "mxfp8" else "grouped_gemm_kernel (tcgen05") +
+                      f", {gemm_launches_per_step} launches per step)",
             "achieved": achieved, "peak": peak_tflops, "unit": "TFLOP/s", "frac": achieved / peak_tflops,
             "peak_source": peak_note,
             "traffic": (GEMM_DRAM_BYTES_PER_STEP / gemm_launches_per_step
-                        if world == 1 and gemm_launches_per_step else None),
+                        if world == 1 and gemm_launches_per_step and args.shape == "c2" and PRECISION == "bf16" else None),
             "gemm_ms_per_step": gemm_ms_per_step, "launches_per_step": gemm_launches_per_step,
             "algorithmic_flops_per_step": flops_per_step,
             "layer_frac": flops_per_step / (ms_per_step * 1e-3) / 1e12 / peak_tflops,
         },
     }
-    if world == 1 and not args.no_cpu_baseline:
+    if world == 1 and not args.no_cpu_baseline and args.shape == "c2":
         line["cpu_baseline"] = cpu_baseline(sample_tokens=256, iterations=2)
     print(json.dumps(line), flush=True)
     if world > 1:
@@ -350,9 +400,13 @@ def main() -> None:
     parser.add_argument("--impl", choices=("b200", "reference"), default="b200")
     parser.add_argument("--no-cpu-baseline", action="store_true",
                         help="skip the CPU baseline leg (used when the run is captured by a profiler)")
+    parser.add_argument("--shape", choices=tuple(SHAPES), default="c2",
+                        help="c2 = EP=2 BF16 configuration's per-rank problem (default); c3 = EP=8 MXFP8 configuration's")
+    parser.add_argument("--precision", choices=("bf16", "mxfp8"), default="bf16")
     args = parser.parse_args()
     if args.warmup < 3:
         args.warmup = 3
+    select_shape(args.shape, args.gpus, args.precision)
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -17,6 +17,7 @@ from __future__ import annotations
 
 import ctypes
 import math
+import os
 import struct
 from typing import Any
 
@@ -198,6 +199,9 @@ class MegaMoeExperts(torch.nn.Module):
         self._tuning = tuning
         self._layout: str | None = None
         self._scale_atoms: dict = {}
+        # Budget of every cross-rank device wait (ready flags, arrival and combine counters). A rank
+        # that is late by more than this makes its peers give up with a status word instead of hanging.
+        self._wait_budget_ns = int(float(os.environ.get("HMC_EP_WAIT_SECONDS", "60")) * 1e9)
         self._backward_expected = False
         self._workspace: PeerWorkspace | _LocalWorkspace | None = None
         self._status: torch.Tensor | None = None
@@ -425,7 +429,7 @@ class MegaMoeExperts(torch.nn.Module):
                             off["dispatch_target_off"], rows=routed_rows, top_k=self.top_k, ep=self.ep_size,
                             local_experts=self.local_experts, capacity_rows=capacity, peer_buffers=peer_expert,
                             peer_ctrl=peer_ctrl, local_ctrl=workspace.ctrl, generation=generation,
-                            status=self._status)
+                            status=self._status, budget_ns=self._wait_budget_ns)
         rows = max(received, 1)
         up_proj = torch.empty(rows, 2 * inter, **bf16)
         activation = torch.empty(rows, inter, **bf16)
@@ -435,7 +439,7 @@ class MegaMoeExperts(torch.nn.Module):
         if received > 0:
             kernels.grouped_gemm(x_recv, w1, up_proj, off["group_list"], mode=kernels.HMC_GEMM_RAGGED_M,
                                  b_major=b_major, epilogue=kernels.HMC_EPI_SWIGLU, aux=activation,
-                                 ready_counters=arrival, status=self._status)
+                                 ready_counters=arrival, ready_budget_ns=self._wait_budget_ns, status=self._status)
             kernels.grouped_gemm(activation, w2, down_proj, off["group_list"], mode=kernels.HMC_GEMM_RAGGED_M,
                                  b_major=b_major, status=self._status)
         if self.ep_size == 1:
@@ -446,8 +450,8 @@ class MegaMoeExperts(torch.nn.Module):
                                ep=self.ep_size, local_experts=self.local_experts,
                                target_rows_limit=workspace.routed_rows, peer_buffers=peer_routed,
                                peer_ctrl=peer_ctrl, local_ctrl=workspace.ctrl, generation=generation,
-                               status=self._status)
-            kernels.ep_wait(workspace.ctrl[_lib.HMC_CTRL_COMBINE:], routed_rows, status=self._status)
+                               status=self._status, budget_ns=self._wait_budget_ns)
+            kernels.ep_wait(workspace.ctrl[_lib.HMC_CTRL_COMBINE:], routed_rows, status=self._status, budget_ns=self._wait_budget_ns)
             # Owned copies: the symmetric buffers are rewritten by the next call on any rank
             # (reference: autograd.py:655-663 saves a dispatch copy and clones the combine output).
             routed_out = workspace.routed_buffer[:max(routed_rows, 1)].clone()
@@ -484,7 +488,7 @@ class MegaMoeExperts(torch.nn.Module):
                             off["dispatch_target_off"], rows=routed_rows, top_k=self.top_k, ep=self.ep_size,
                             local_experts=self.local_experts, capacity_rows=capacity, peer_buffers=peer_expert,
                             peer_ctrl=peer_ctrl, local_ctrl=workspace.ctrl, generation=generation,
-                            status=self._status)
+                            status=self._status, budget_ns=self._wait_budget_ns)
         rows = max(received, 1)
         dy_recv = expert_buffer[:rows]
         arrival = workspace.ctrl[_lib.HMC_CTRL_ARRIVAL:_lib.HMC_CTRL_ARRIVAL + self.local_experts]
@@ -500,7 +504,7 @@ class MegaMoeExperts(torch.nn.Module):
         if received > 0:
             kernels.grouped_gemm(dy_recv, w2, grad_up, off["group_list"], mode=kernels.HMC_GEMM_RAGGED_M,
                                  b_major=bt_major, epilogue=kernels.HMC_EPI_SWIGLU_GRAD, aux=up_proj,
-                                 ready_counters=arrival, status=self._status)
+                                 ready_counters=arrival, ready_budget_ns=self._wait_budget_ns, status=self._status)
             kernels.grouped_gemm(grad_up, w1, grad_x_rows, off["group_list"], mode=kernels.HMC_GEMM_RAGGED_M,
                                  b_major=bt_major, status=self._status)
         if grad_w2 is not None:
@@ -519,8 +523,8 @@ class MegaMoeExperts(torch.nn.Module):
                                ep=self.ep_size, local_experts=self.local_experts,
                                target_rows_limit=workspace.routed_rows, peer_buffers=peer_routed,
                                peer_ctrl=peer_ctrl, local_ctrl=workspace.ctrl, generation=generation,
-                               status=self._status)
-            kernels.ep_wait(workspace.ctrl[_lib.HMC_CTRL_COMBINE:], routed_rows, status=self._status)
+                               status=self._status, budget_ns=self._wait_budget_ns)
+            kernels.ep_wait(workspace.ctrl[_lib.HMC_CTRL_COMBINE:], routed_rows, status=self._status, budget_ns=self._wait_budget_ns)
             returned = workspace.routed_buffer
         grad_hidden = torch.empty(tokens, hid, **bf16)
         kernels.moe_token_permute_grad(returned, route.mapping, tokens, self.top_k, grad_hidden, status=self._status)
@@ -565,9 +569,9 @@ class MegaMoeExperts(torch.nn.Module):
                             off["dispatch_target_off"], rows=routed_rows, top_k=self.top_k, ep=self.ep_size,
                             local_experts=self.local_experts, capacity_rows=capacity, peer_buffers=peer_expert,
                             peer_ctrl=peer_ctrl, local_ctrl=workspace.ctrl, generation=generation,
-                            status=self._status)
+                            status=self._status, budget_ns=self._wait_budget_ns)
         arrival = workspace.ctrl[_lib.HMC_CTRL_ARRIVAL:_lib.HMC_CTRL_ARRIVAL + self.local_experts]
-        kernels.ep_wait_groups(arrival, off["group_list"], status=self._status)
+        kernels.ep_wait_groups(arrival, off["group_list"], status=self._status, budget_ns=self._wait_budget_ns)
         return expert_buffer[:max(received, 1)], generation, peer_routed, peer_ctrl
 
     def _mx_return(self, rows_tensor, route, generation, peer_routed, peer_ctrl):
@@ -579,8 +583,8 @@ class MegaMoeExperts(torch.nn.Module):
         kernels.ep_combine(rows_tensor, off["recv_segment_start"], off["combine_target_off"], rows=route.received_rows,
                            ep=self.ep_size, local_experts=self.local_experts,
                            target_rows_limit=workspace.routed_rows, peer_buffers=peer_routed, peer_ctrl=peer_ctrl,
-                           local_ctrl=workspace.ctrl, generation=generation, status=self._status)
-        kernels.ep_wait(workspace.ctrl[_lib.HMC_CTRL_COMBINE:], route.routed_rows, status=self._status)
+                           local_ctrl=workspace.ctrl, generation=generation, status=self._status, budget_ns=self._wait_budget_ns)
+        kernels.ep_wait(workspace.ctrl[_lib.HMC_CTRL_COMBINE:], route.routed_rows, status=self._status, budget_ns=self._wait_budget_ns)
         return workspace.routed_buffer
 
     def _run_forward_mx(self, hidden, probs, root1, root2, route: PreparedRoute):

@@ -51,6 +51,7 @@ def scenario_mx(module, rank, world, device, token_counts, hidden, inter, expert
     w2_all = (torch.randn(experts, inter, hidden, generator=gw) * 0.05).bfloat16()
     per_rank = [make_rank_inputs(r, token_counts[r], hidden, experts, top_k, seed) for r in range(world)]
     x, ids, probs, grad = per_rank[rank]
+    dist.barrier()  # the oracle below takes a different time on every rank; start the GPU call together
     w1 = attach_mx_fields(w1_all[rank * local:(rank + 1) * local].contiguous().to(device).requires_grad_(True))
     w2 = attach_mx_fields(w2_all[rank * local:(rank + 1) * local].contiguous().to(device).requires_grad_(True))
     xd = x.to(device).requires_grad_(True)
@@ -81,6 +82,7 @@ def scenario(module, rank, world, device, token_counts, hidden, inter, experts, 
     w2_all = (torch.randn(experts, inter, hidden, generator=gw) * 0.05).bfloat16()
     per_rank = [make_rank_inputs(r, token_counts[r], hidden, experts, top_k, seed) for r in range(world)]
     x, ids, probs, grad = per_rank[rank]
+    dist.barrier()  # the oracle below takes a different time on every rank; start the GPU call together
     w1 = w1_all[rank * local:(rank + 1) * local]
     w2 = w2_all[rank * local:(rank + 1) * local]
     if layout == "EOI":
@@ -115,6 +117,8 @@ def main():
     device = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
     torch.cuda.set_device(device)
     dist.init_process_group("nccl", device_id=device)
+    # the CPU oracle runs in every rank: share the host cores instead of oversubscribing them
+    torch.set_num_threads(max(1, (os.cpu_count() or 8) // world))
     hidden, inter, experts, top_k = 256, 128, 8 * world // 2 if world > 2 else 8, 2
     for layout in ("EIO", "EOI"):
         module = MegaMoeExperts(hidden_size=hidden, intermediate_size=inter, num_experts=experts, top_k=top_k,
@@ -141,4 +145,15 @@ def main():
 
 
 if __name__ == "__main__":
-    main()
+    try:
+        main()
+    except BaseException:  # pylint: disable=broad-except
+        import traceback
+
+        text = f"[rank {os.environ.get('RANK')}] " + traceback.format_exc()
+        print(text, flush=True)
+        log_dir = os.environ.get("HMC_TEST_LOG_DIR")
+        if log_dir:
+            Path(log_dir).mkdir(parents=True, exist_ok=True)
+            (Path(log_dir) / f"ep_worker_rank{os.environ.get('RANK')}.log").write_text(text)
+        raise

@@ -28,5 +28,5 @@ def test_expert_parallel_matches_oracle(world):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", str(_free_port()), str(ROOT / "tests" / "_ep_worker.py")]
     result = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
-    assert result.returncode == 0, result.stdout[-3000:] + result.stderr[-3000:]
+    assert result.returncode == 0, result.stdout[-6000:] + result.stderr[-1500:]
     assert f"EP={world} ok" in result.stdout
