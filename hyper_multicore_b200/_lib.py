@@ -48,6 +48,8 @@ class GroupedGemmArgs(ctypes.Structure):
         ("epilogue", c_int32),
         ("groups", c_int32),
         ("max_ctas", c_int32),
+        ("tile_mode", c_int32),
+        ("reserved", c_int32),
         ("rows", c_int64),
         ("m", c_int64),
         ("n", c_int64),
@@ -205,6 +207,8 @@ SIGNATURES: dict[str, tuple] = {
     "hmc_gate_route": (_I, [ctypes.POINTER(GateRouteArgs), _P]),
     "hmc_gate_route_grad": (_I, [ctypes.POINTER(GateRouteGradArgs), _P]),
     "hmc_gate_project": (_I, [_P, _I, _P, _I, _L, _L, _L, _P, _P]),
+    "hmc_gate_project_workspace_bytes": (_L, [_L, _L, _L]),
+    "hmc_gate_project_tc": (_I, [_P, _P, _I, _L, _L, _L, _P, _P, _L, _P]),
     "hmc_moe_sort_workspace_bytes": (_L, [_L, _L]),
     "hmc_moe_histogram": (_I, [_P, _I, _L, _L, _P, _P, _P]),
     "hmc_moe_sort_routes": (_I, [_P, _I, _L, _L, _P, _L, _P, _P, _P, _P, _P, _P, _P]),

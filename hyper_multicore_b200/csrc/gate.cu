@@ -280,6 +280,40 @@ gate_project_kernel(const TX* __restrict__ x, const TW* __restrict__ w, long lon
   }
 }
 
+// FP32 weight [E, H] -> three BF16 parts (hi, mid, lo; hi + mid + lo == w to 24 bits) stacked as
+// rows [0, E), [Epad, Epad + E), [2 Epad, 2 Epad + E) of a [3 Epad, H] matrix; other rows zero.
+__global__ void gate_split_weight_kernel(const void* __restrict__ w, int w_is_bf16, int experts, int epad, int parts,
+                                         long long hidden, __nv_bfloat16* __restrict__ split) {
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= static_cast<long long>(epad) * hidden) return;
+  const int e = static_cast<int>(i / hidden);
+  float v = 0.f;
+  if (e < experts)
+    v = w_is_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(w)[i]) : static_cast<const float*>(w)[i];
+  const __nv_bfloat16 hi = __float2bfloat16_rn(v);
+  split[i] = hi;
+  if (parts == 3) {
+    const float r1 = v - __bfloat162float(hi);
+    const __nv_bfloat16 mid = __float2bfloat16_rn(r1);
+    const __nv_bfloat16 lo = __float2bfloat16_rn(r1 - __bfloat162float(mid));
+    split[static_cast<long long>(epad) * hidden + i] = mid;
+    split[2ll * epad * hidden + i] = lo;
+  }
+}
+
+// logits[t, e] = sum of the partial products of the weight parts
+__global__ void gate_sum_parts_kernel(const float* __restrict__ partial, long long tokens, int experts, int epad,
+                                      int parts, float* __restrict__ logits) {
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= tokens * experts) return;
+  const long long t = i / experts;
+  const int e = static_cast<int>(i % experts);
+  const float* row = partial + t * parts * epad;
+  float v = row[e];
+  if (parts == 3) v = (v + row[epad + e]) + row[2 * epad + e];
+  logits[i] = v;
+}
+
 template <int NPL>
 void launch_route(const hmc_gate_route_args& a, cudaStream_t stream) {
   const unsigned grid = static_cast<unsigned>((a.tokens + WARPS_PER_BLOCK - 1) / WARPS_PER_BLOCK);
@@ -382,6 +416,61 @@ extern "C" int hmc_gate_project(const void* x, int x_is_bf16, const void* w, int
   else
     gate_project_kernel<float, float><<<grid, 256, 0, stream>>>(static_cast<const float*>(x),
                                                                 static_cast<const float*>(w), tokens, h, e, logits);
+  HMC_LAUNCH_OK();
+  return 0;
+}
+
+extern "C" int64_t hmc_gate_project_workspace_bytes(int64_t tokens, int64_t hidden, int64_t experts) {
+  const int64_t epad = (experts + 7) / 8 * 8;
+  return 3 * epad * hidden * 2 + tokens * 3 * epad * 4 + 512;
+}
+
+// Tensor-core projection for BF16 hidden states: the FP32 weight is split into three BF16 parts whose
+// sum reproduces it to 24 bits, the products with the (exact) BF16 activations accumulate in FP32 on
+// tcgen05, and the three partial results are added. FP32 hidden states use hmc_gate_project.
+extern "C" int hmc_gate_project_tc(const void* x_bf16, const void* w, int w_is_bf16, int64_t tokens, int64_t hidden,
+                                   int64_t experts, float* logits, void* workspace, int64_t workspace_bytes,
+                                   void* stream_ptr) {
+  using namespace hmc;
+  HMC_REQUIRE(x_bf16 && w && logits && workspace, HMC_ERR_INVALID, "hmc_gate_project_tc: null tensor pointer");
+  HMC_REQUIRE(tokens > 0 && experts > 0 && hidden > 0 && hidden % 8 == 0, HMC_ERR_INVALID,
+              "hmc_gate_project_tc: extents must be positive and hidden a multiple of 8");
+  HMC_REQUIRE(workspace_bytes >= hmc_gate_project_workspace_bytes(tokens, hidden, experts), HMC_ERR_INVALID,
+              "hmc_gate_project_tc: workspace holds %lld bytes, %lld needed", (long long)workspace_bytes,
+              (long long)hmc_gate_project_workspace_bytes(tokens, hidden, experts));
+  HMC_REQUIRE(aligned16(x_bf16) && aligned16(workspace), HMC_ERR_INVALID, "hmc_gate_project_tc: 16-byte alignment");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  const int epad = static_cast<int>((experts + 7) / 8 * 8);
+  const int parts = w_is_bf16 ? 1 : 3;
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  __nv_bfloat16* split = reinterpret_cast<__nv_bfloat16*>(ws);
+  float* partial = reinterpret_cast<float*>(ws + 3ll * epad * hidden * 2);
+  long long* ends = reinterpret_cast<long long*>(ws + 3ll * epad * hidden * 2 + tokens * 3ll * epad * 4);
+  ends = reinterpret_cast<long long*>((reinterpret_cast<uintptr_t>(ends) + 15) & ~static_cast<uintptr_t>(15));
+  const long long split_elems = static_cast<long long>(epad) * hidden;
+  gate_split_weight_kernel<<<static_cast<unsigned>((split_elems + 255) / 256), 256, 0, stream>>>(
+      w, w_is_bf16, static_cast<int>(experts), epad, parts, hidden, split);
+  HMC_LAUNCH_OK();
+  HMC_CUDA_OK(cudaMemcpyAsync(ends, &tokens, sizeof(long long), cudaMemcpyHostToDevice, stream));
+  hmc_grouped_gemm_args g{};
+  g.mode = HMC_GEMM_RAGGED_M;
+  g.a_major = HMC_MAJOR_K;
+  g.b_major = HMC_MAJOR_K;
+  g.epilogue = HMC_EPI_STORE_F32;
+  g.groups = 1;
+  g.tile_mode = HMC_TILE_SINGLE;
+  g.rows = tokens;
+  g.n = static_cast<int64_t>(parts) * epad;
+  g.k = hidden;
+  g.a = x_bf16;
+  g.b = split;
+  g.c = partial;
+  g.group_ends = reinterpret_cast<const int64_t*>(ends);
+  int rc = hmc_grouped_gemm(&g, stream);
+  if (rc != 0) return rc;
+  const long long total = tokens * experts;
+  gate_sum_parts_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(
+      partial, tokens, static_cast<int>(experts), epad, parts, logits);
   HMC_LAUNCH_OK();
   return 0;
 }

@@ -16,110 +16,16 @@
 #include <cuda.h>
 
 #include "common.cuh"
+#include "gemm_shared.cuh"
 #include "sm100.cuh"
 
 namespace hmc {
 namespace {
 
 using namespace sm100;
+using namespace gemm;
 
-constexpr int BM = 128;
-constexpr int BN = 256;
-constexpr int BK = 64;
-constexpr int STAGES = 4;
-constexpr int ACC_STAGES = 2;
-constexpr int A_TILE_BYTES = BM * BK * 2;  // 16 KiB
-constexpr int B_TILE_BYTES = BN * BK * 2;  // 32 KiB
-constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
-constexpr int CHUNK_BYTES = 64 * BK * 2;  // one 64-wide MN-major chunk: BK rows of 128 B
-constexpr int EPI_WARPS = 8;
-constexpr int NUM_THREADS = 64 + EPI_WARPS * 32;
-constexpr int STORE_STAGE_BYTES = 32 * 128;  // one 32-row x 128-byte TMA store box per epilogue warp
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_WARPS * STORE_STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
-constexpr uint32_t TMEM_COLS = 512;
-constexpr uint32_t SWIZZLE_128B = 2;
-
-constexpr uint64_t PIPE_BUDGET_NS = 4ull * 1000 * 1000 * 1000;  // intra-kernel barrier waits
-
-struct Params {
-  int mode;      // HMC_GEMM_RAGGED_M / HMC_GEMM_RAGGED_K
-  int epilogue;  // HMC_EPI_*
-  int groups;
-  int m;  // RAGGED_K: rows of C per group. RAGGED_M: unused
-  int n;  // logical N of the accumulator (SWIGLU: I, the width of one half)
-  int k;  // RAGGED_M: contraction length. RAGGED_K: unused
-  int n_tiles;
-  int m_tiles;  // RAGGED_K only
-  int ldc;      // row stride of C in elements
-  int ld_aux;   // row stride of aux in elements
-  long long rows;
-  const long long* group_ends;
-  void* c;
-  void* aux;
-  const int* ready_counters;  // optional, RAGGED_M: per-group arrival counters (rows landed)
-  unsigned long long ready_budget_ns;
-  int* status;
-};
-
-struct Tile {
-  int group;
-  int m_idx;
-  int n_idx;
-  long long row0;  // first row of the group in the ragged dimension
-  long long row1;  // one past the last row of the group
-};
-
-// Walks the static tile order. Tile indices only grow for a given CTA, so the group cursor only
-// moves forward and every role (producer, MMA, epilogue) reproduces the same sequence.
-struct TileWalker {
-  const Params& p;
-  int group = 0;
-  long long base = 0;  // first linear tile index of `group`
-  long long row0 = 0;
-  long long row1 = 0;
-  int tiles_in_group = 0;
-
-  __device__ explicit TileWalker(const Params& params) : p(params) { load_group(); }
-
-  __device__ void load_group() {
-    if (group >= p.groups) {
-      tiles_in_group = 0;
-      return;
-    }
-    row0 = group == 0 ? 0 : p.group_ends[group - 1];
-    row1 = p.group_ends[group];
-    if (p.mode == HMC_GEMM_RAGGED_M) {
-      long long rows = row1 - row0;
-      tiles_in_group = static_cast<int>((rows + BM - 1) / BM) * p.n_tiles;
-    } else {
-      tiles_in_group = p.m_tiles * p.n_tiles;
-    }
-  }
-
-  __device__ bool get(long long idx, Tile& t) {
-    while (group < p.groups && idx >= base + tiles_in_group) {
-      base += tiles_in_group;
-      ++group;
-      load_group();
-    }
-    if (group >= p.groups) return false;
-    int local = static_cast<int>(idx - base);
-    int mt = p.mode == HMC_GEMM_RAGGED_M ? tiles_in_group / p.n_tiles : p.m_tiles;
-    t.group = group;
-    t.m_idx = local % mt;
-    t.n_idx = local / mt;
-    t.row0 = row0;
-    t.row1 = row1;
-    return true;
-  }
-};
-
-__device__ __forceinline__ int k_iterations(const Params& p, const Tile& t) {
-  if (p.mode == HMC_GEMM_RAGGED_M) return (p.k + BK - 1) / BK;
-  return static_cast<int>((t.row1 - t.row0 + BK - 1) / BK);
-}
-
-__device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)); }
+using TileWalker = TileWalkerT<BM>;
 
 template <int A_MAJOR, int B_MAJOR>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
@@ -421,115 +327,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           }
           store_pending = true;
         }
-      } else if (p.epilogue == HMC_EPI_STORE_BF16) {
-        __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.c) + out_row * p.ldc + col_base;
-#pragma unroll 1
-        for (int c = c_lo; c < c_hi; c += 32) {
-          uint32_t v[32];
-          tmem_ld_32x32(taddr + c, v);
-          tmem_ld_wait();
-          if (row_ok) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              if (col_base + c + j < p.n) {
-                uint4 o;
-                o.x = pack_bf16x2(__uint_as_float(v[j + 0]), __uint_as_float(v[j + 1]));
-                o.y = pack_bf16x2(__uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
-                o.z = pack_bf16x2(__uint_as_float(v[j + 4]), __uint_as_float(v[j + 5]));
-                o.w = pack_bf16x2(__uint_as_float(v[j + 6]), __uint_as_float(v[j + 7]));
-                *reinterpret_cast<uint4*>(dst + c + j) = o;
-              }
-            }
-          }
-        }
-      } else if (p.epilogue == HMC_EPI_STORE_F32) {
-        float* dst = static_cast<float*>(p.c) + out_row * p.ldc + col_base;
-#pragma unroll 1
-        for (int c = c_lo; c < c_hi; c += 32) {
-          uint32_t v[32];
-          tmem_ld_32x32(taddr + c, v);
-          tmem_ld_wait();
-          if (row_ok) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 4) {
-              if (col_base + c + j < p.n) {
-                *reinterpret_cast<float4*>(dst + c + j) =
-                    make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
-                                __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
-              }
-            }
-          }
-        }
-      } else if (p.epilogue == HMC_EPI_SWIGLU) {
-        // U[row, col] = bf16(gate), U[row, I + col] = bf16(up), Act[row, col] =
-        // bf16(silu(gate_bf16) * up_bf16): the rounding points of the reference's golden
-        // (tests/common/multicore/fp32_expert_reference.py:22-25).
-        __nv_bfloat16* u_dst = static_cast<__nv_bfloat16*>(p.c) + out_row * p.ldc + col_base;
-        __nv_bfloat16* a_dst = static_cast<__nv_bfloat16*>(p.aux) + out_row * p.ld_aux + col_base;
-#pragma unroll 1
-        for (int c = half * (BN / 4); c < (half + 1) * (BN / 4); c += 32) {
-          uint32_t g[32], u[32];
-          tmem_ld_32x32(taddr + c, g);
-          tmem_ld_32x32(taddr + BN / 2 + c, u);
-          tmem_ld_wait();
-          if (row_ok) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              if (col_base + c + j < p.n) {
-                uint32_t go[4], uo[4], ao[4];
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                  go[q] = pack_bf16x2(__uint_as_float(g[j + 2 * q]), __uint_as_float(g[j + 2 * q + 1]));
-                  uo[q] = pack_bf16x2(__uint_as_float(u[j + 2 * q]), __uint_as_float(u[j + 2 * q + 1]));
-                  const float2 gf = unpack_bf16x2(go[q]);
-                  const float2 uf = unpack_bf16x2(uo[q]);
-                  ao[q] = pack_bf16x2(silu_f(gf.x) * uf.x, silu_f(gf.y) * uf.y);
-                }
-                *reinterpret_cast<uint4*>(u_dst + c + j) = make_uint4(go[0], go[1], go[2], go[3]);
-                *reinterpret_cast<uint4*>(u_dst + p.n + c + j) = make_uint4(uo[0], uo[1], uo[2], uo[3]);
-                *reinterpret_cast<uint4*>(a_dst + c + j) = make_uint4(ao[0], ao[1], ao[2], ao[3]);
-              }
-            }
-          }
-        }
-      } else {  // HMC_EPI_SWIGLU_GRAD
-        // acc = dAct tile. With saved U = [gate | up] (aux): dU[:, col] = bf16(dA*up*s*(1+g(1-s))),
-        // dU[:, I + col] = bf16(dA*silu(g)), dA rounded to BF16 first
-        // (tests/common/multicore/fp32_expert_reference.py:29-33).
-        const __nv_bfloat16* u_src = static_cast<const __nv_bfloat16*>(p.aux) + out_row * p.ld_aux + col_base;
-        __nv_bfloat16* d_dst = static_cast<__nv_bfloat16*>(p.c) + out_row * p.ldc + col_base;
-#pragma unroll 1
-        for (int c = c_lo; c < c_hi; c += 32) {
-          uint32_t v[32];
-          tmem_ld_32x32(taddr + c, v);
-          tmem_ld_wait();
-          if (row_ok) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              if (col_base + c + j < p.n) {
-                const uint4 gq = *reinterpret_cast<const uint4*>(u_src + c + j);
-                const uint4 uq = *reinterpret_cast<const uint4*>(u_src + p.n + c + j);
-                const uint32_t gw[4] = {gq.x, gq.y, gq.z, gq.w};
-                const uint32_t uw[4] = {uq.x, uq.y, uq.z, uq.w};
-                uint32_t dg[4], du[4];
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                  const float2 gf = unpack_bf16x2(gw[q]);
-                  const float2 uf = unpack_bf16x2(uw[q]);
-                  const float da0 = bf16_round(__uint_as_float(v[j + 2 * q]));
-                  const float da1 = bf16_round(__uint_as_float(v[j + 2 * q + 1]));
-                  const float s0 = 1.0f / (1.0f + __expf(-gf.x));
-                  const float s1 = 1.0f / (1.0f + __expf(-gf.y));
-                  dg[q] = pack_bf16x2(da0 * uf.x * s0 * (1.0f + gf.x * (1.0f - s0)),
-                                      da1 * uf.y * s1 * (1.0f + gf.y * (1.0f - s1)));
-                  du[q] = pack_bf16x2(da0 * (gf.x * s0), da1 * (gf.y * s1));
-                }
-                *reinterpret_cast<uint4*>(d_dst + c + j) = make_uint4(dg[0], dg[1], dg[2], dg[3]);
-                *reinterpret_cast<uint4*>(d_dst + p.n + c + j) = make_uint4(du[0], du[1], du[2], du[3]);
-              }
-            }
-          }
-        }
+      } else {
+        epilogue_rows(p, taddr, out_row, row_ok, col_base, half);
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -606,6 +405,10 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, 
 }
 
 }  // namespace
+
+int launch_grouped_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const gemm::Params& p, int b_major, int grid,
+                             cudaStream_t stream);
+
 }  // namespace hmc
 
 extern "C" int hmc_grouped_gemm(const hmc_grouped_gemm_args* args, void* stream_ptr) {
@@ -717,6 +520,12 @@ extern "C" int hmc_grouped_gemm(const hmc_grouped_gemm_args* args, void* stream_
     if (tiles < grid) grid = static_cast<int>(tiles);
     return launch<HMC_MAJOR_MN, HMC_MAJOR_MN>(ta, tb, tc, p, grid, stream);
   }
+  // CTA pairs work on 256-row tiles: worth it once the average group fills most of one
+  // and the epilogue is light (the SwiGLU-grad epilogue prefers the deeper overlap of 128-row tiles)
+  const bool use_pairs = a.tile_mode == HMC_TILE_PAIR || (a.tile_mode == HMC_TILE_AUTO && a.rows >= 192ll * a.groups &&
+                                                          a.epilogue != HMC_EPI_SWIGLU_GRAD);
+  if (use_pairs && a.k % 8 == 0 && sm_count() >= 2)
+    return launch_grouped_gemm_pair(ta, tb, p, a.b_major, grid, stream);
   if (a.b_major == HMC_MAJOR_MN) return launch<HMC_MAJOR_K, HMC_MAJOR_MN>(ta, tb, tc, p, grid, stream);
   return launch<HMC_MAJOR_K, HMC_MAJOR_K>(ta, tb, tc, p, grid, stream);
 }

@@ -58,6 +58,9 @@ int hmc_worker_queue_layout_version(void);
 #define HMC_GEMM_RAGGED_K 1 /* C_g[m, n] = A[rows_g, m]^T * B[rows_g, n] (weight gradients) */
 #define HMC_MAJOR_K 0       /* operand stored with the contraction index contiguous */
 #define HMC_MAJOR_MN 1      /* operand stored with the M/N index contiguous */
+#define HMC_TILE_AUTO 0
+#define HMC_TILE_SINGLE 1
+#define HMC_TILE_PAIR 2
 #define HMC_EPI_STORE_BF16 0
 #define HMC_EPI_STORE_F32 1   /* FP32 output (partial weight gradients, mHC projection) */
 #define HMC_EPI_SWIGLU 2      /* B has 2n columns [gate | up]; c = U[rows, 2n], aux = Act[rows, n] */
@@ -70,6 +73,8 @@ typedef struct hmc_grouped_gemm_args {
   int32_t epilogue;
   int32_t groups;
   int32_t max_ctas; /* 0 = one CTA per SM */
+  int32_t tile_mode; /* RAGGED_M: HMC_TILE_AUTO, _SINGLE (128-row tiles) or _PAIR (256-row CTA-pair tiles) */
+  int32_t reserved;
   int64_t rows;     /* extent of the ragged dimension of a (and of b for RAGGED_K) */
   int64_t m;        /* RAGGED_K only */
   int64_t n;
@@ -217,6 +222,11 @@ int hmc_gate_route(const hmc_gate_route_args* args, void* stream);
 int hmc_gate_route_grad(const hmc_gate_route_grad_args* args, void* stream);
 int hmc_gate_project(const void* x, int x_is_bf16, const void* w, int w_is_bf16, int64_t tokens, int64_t hidden,
                      int64_t experts, float* logits, void* stream);
+/* Same projection on tcgen05 for BF16 hidden states: the weight is split into three BF16 parts that
+ * sum to its FP32 value, so the result keeps FP32 accuracy. Scratch comes from the caller. */
+int64_t hmc_gate_project_workspace_bytes(int64_t tokens, int64_t hidden, int64_t experts);
+int hmc_gate_project_tc(const void* x_bf16, const void* w, int w_is_bf16, int64_t tokens, int64_t hidden,
+                        int64_t experts, float* logits, void* workspace, int64_t workspace_bytes, void* stream);
 
 /* ------------------------------------------------------------------------------------------
  * MoE route preparation and token (un)permutation.

@@ -146,6 +146,23 @@ def test_projection_is_fp32_accurate(cuda_device, x_dtype, w_dtype):
     ref = torch.nn.functional.linear(x.double(), w.double()).float()
     got = K.gate_project(x.to(cuda_device), w.to(cuda_device)).cpu()
     torch.testing.assert_close(got, ref, rtol=1e-5, atol=1e-6)
+    fast = K.gate_project(x.to(cuda_device), w.to(cuda_device), use_tensor_cores=True).cpu()
+    torch.testing.assert_close(fast, ref, rtol=1e-5, atol=1e-5 * float(ref.abs().max()))
     for case in load_cases("gate"):
         got = K.gate_project(case["hidden"].to(cuda_device), case["weight"].to(cuda_device)).cpu()
         torch.testing.assert_close(got, case["logits"], rtol=1e-5, atol=1e-6)
+
+
+def test_projection_at_the_multimodal_gate_shape(cuda_device):
+    """8192 tokens x hidden 4096 x 64 experts: the tensor-core path against a float64 reference."""
+    from hyper_multicore_b200 import kernels as K
+
+    torch.manual_seed(9)
+    x = torch.randn(8192, 4096, device=cuda_device).bfloat16()
+    x[6144:] = (x[6144:].float() * torch.empty(4096, device=cuda_device).uniform_(0.5, 2.0)).bfloat16()
+    w = torch.randn(64, 4096, device=cuda_device) * 0.02
+    ref = (x.double() @ w.double().T).float()
+    torch.testing.assert_close(K.gate_project(x, w), ref, rtol=1e-5, atol=1e-5)
+    # opt-in tcgen05 path: absolute error bounded relative to the largest logit
+    torch.testing.assert_close(K.gate_project(x, w, use_tensor_cores=True), ref, rtol=1e-5,
+                               atol=1e-5 * float(ref.abs().max()))

@@ -20,11 +20,12 @@ def _close(got, ref):
     torch.testing.assert_close(got.float(), ref.float(), rtol=RTOL, atol=ATOL * max(1.0, float(ref.abs().max())))
 
 
+@pytest.mark.parametrize("tile_mode", [1, 2])  # 128-row tiles on one CTA, 256-row tiles on a CTA pair
 @pytest.mark.parametrize("b_major", [0, 1])
 @pytest.mark.parametrize("counts,k,n", [([128], 64, 256), ([100, 0, 300, 129, 1], 512, 512),
                                         ([100, 0, 300, 129, 1], 200, 328), ([0, 0, 5], 64, 8),
                                         ([700, 1, 0, 900], 1024, 2048)])
-def test_ragged_m_plain(cuda_device, b_major, counts, k, n):
+def test_ragged_m_plain(cuda_device, tile_mode, b_major, counts, k, n):
     from hyper_multicore_b200 import _lib, kernels as K
 
     torch.manual_seed(sum(counts) + k)
@@ -35,7 +36,8 @@ def test_ragged_m_plain(cuda_device, b_major, counts, k, n):
     b = w if b_major == K.HMC_MAJOR_MN else w.transpose(1, 2).contiguous()
     c = torch.full((rows + guard, n), 7.0, device=dev, dtype=torch.bfloat16)
     status = _lib.new_status(dev)
-    K.grouped_gemm(a, b, c, _ends(counts, dev), mode=K.HMC_GEMM_RAGGED_M, b_major=b_major, status=status)
+    K.grouped_gemm(a, b, c, _ends(counts, dev), mode=K.HMC_GEMM_RAGGED_M, b_major=b_major, status=status,
+                   tile_mode=tile_mode)
     starts = _starts(counts)
     ref = torch.cat([a[starts[g]:starts[g + 1]].float() @ w[g].float() for g in range(groups)])
     _close(c[:rows], ref)
@@ -43,9 +45,10 @@ def test_ragged_m_plain(cuda_device, b_major, counts, k, n):
     _lib.raise_on_status(status, "grouped gemm")
 
 
+@pytest.mark.parametrize("tile_mode", [1, 2])
 @pytest.mark.parametrize("b_major", [0, 1])
 @pytest.mark.parametrize("inter", [384, 200])
-def test_ragged_m_swiglu_forward_and_backward_epilogues(cuda_device, b_major, inter):
+def test_ragged_m_swiglu_forward_and_backward_epilogues(cuda_device, tile_mode, b_major, inter):
     from hyper_multicore_b200 import kernels as K
 
     torch.manual_seed(inter)
@@ -59,7 +62,7 @@ def test_ragged_m_swiglu_forward_and_backward_epilogues(cuda_device, b_major, in
     u = torch.empty(rows, 2 * inter, device=dev, dtype=torch.bfloat16)
     act = torch.empty(rows, inter, device=dev, dtype=torch.bfloat16)
     K.grouped_gemm(a, b, u, _ends(counts, dev), mode=K.HMC_GEMM_RAGGED_M, b_major=b_major,
-                   epilogue=K.HMC_EPI_SWIGLU, aux=act)
+                   epilogue=K.HMC_EPI_SWIGLU, aux=act, tile_mode=tile_mode)
     ref_u = torch.cat([a[starts[g]:starts[g + 1]].float() @ w[g].float() for g in range(groups)])
     _close(u, ref_u)
     ub = u.float()  # activation is defined on the BF16-rounded projection
@@ -71,7 +74,7 @@ def test_ragged_m_swiglu_forward_and_backward_epilogues(cuda_device, b_major, in
     b2 = w2 if b_major == K.HMC_MAJOR_MN else w2.transpose(1, 2).contiguous()
     du = torch.empty(rows, 2 * inter, device=dev, dtype=torch.bfloat16)
     K.grouped_gemm(dy, b2, du, _ends(counts, dev), mode=K.HMC_GEMM_RAGGED_M, b_major=b_major,
-                   epilogue=K.HMC_EPI_SWIGLU_GRAD, aux=u)
+                   epilogue=K.HMC_EPI_SWIGLU_GRAD, aux=u, tile_mode=tile_mode)
     d_act = torch.cat([dy[starts[g]:starts[g + 1]].float() @ w2[g].float() for g in range(groups)]).bfloat16().float()
     gate, up = ub[:, :inter], ub[:, inter:]
     sig = torch.sigmoid(gate)
