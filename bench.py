@@ -403,9 +403,22 @@ def main() -> None:
     parser.add_argument("--shape", choices=tuple(SHAPES), default="c2",
                         help="c2 = EP=2 BF16 configuration's per-rank problem (default); c3 = EP=8 MXFP8 configuration's")
     parser.add_argument("--precision", choices=("bf16", "mxfp8"), default="bf16")
+    parser.add_argument("--workload", choices=("moe", "gate", "mhc"), default="moe",
+                        help="moe = the MoE layer (default, the headline metric); gate / mhc = the router and the "
+                             "four-stream residual mix, timed against the HBM roofline")
+    parser.add_argument("--tokens", type=int, default=None,
+                        help="gate / mhc workloads only: run a smaller case of the same kernels (profiler captures)")
     args = parser.parse_args()
     if args.warmup < 3:
         args.warmup = 3
+    if args.workload != "moe":
+        import bench_side
+
+        if args.impl == "reference":
+            bench_side.run_reference(args, args.workload)
+        else:
+            bench_side.run_gpu(args, args.workload, ClockSampler)
+        return
     select_shape(args.shape, args.gpus, args.precision)
     if args.impl == "reference":
         run_reference(args)

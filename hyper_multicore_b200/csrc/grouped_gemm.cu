@@ -188,23 +188,26 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         tc_fence_after_sync();
         uint8_t* a_src = smem + stage * STAGE_BYTES;
         uint8_t* b_src = a_src + A_TILE_BYTES;
+        int k_steps = BK / 16;
         if (p.mode == HMC_GEMM_RAGGED_K) {
           const long long left = t.row1 - (t.row0 + static_cast<long long>(kb) * BK);
           if (left < BK) {
-            // Rows past the end of this group belong to the next group (or are unwritten):
-            // clear them in both operands. A 128-byte row stays one 128-byte line under the
+            // Rows past the end of this group belong to the next group (or are unwritten). Only the
+            // 16-row MMA steps that hold valid rows are issued; the invalid rows of the last such
+            // step are cleared in both operands. A 128-byte row stays one 128-byte line under the
             // 128-byte swizzle, so whole lines can be cleared without undoing the swizzle.
             const int valid = static_cast<int>(left);
-            const int lines = (BK - valid) * 6;  // 2 A chunks + 4 B chunks per row
-            const uint4 zero = make_uint4(0, 0, 0, 0);
-            for (int i = lane; i < lines * 8; i += 32) {
-              const int line = i >> 3;
-              const int chunk = line / (BK - valid);
-              const int row = valid + line % (BK - valid);
-              uint8_t* base = chunk < 2 ? a_src + chunk * CHUNK_BYTES : b_src + (chunk - 2) * CHUNK_BYTES;
-              *reinterpret_cast<uint4*>(base + row * 128 + (i & 7) * 16) = zero;
+            k_steps = (valid + 15) >> 4;
+            const int vectors = (k_steps * 16 - valid) * 8;  // 16-byte vectors to clear per 64-wide chunk
+            if (vectors > 0) {
+              const uint4 zero = make_uint4(0, 0, 0, 0);
+#pragma unroll
+              for (int chunk = 0; chunk < 6; ++chunk) {  // 2 A chunks + 4 B chunks
+                uint8_t* base = (chunk < 2 ? a_src + chunk * CHUNK_BYTES : b_src + (chunk - 2) * CHUNK_BYTES) + valid * 128;
+                for (int i = lane; i < vectors; i += 32) *reinterpret_cast<uint4*>(base + i * 16) = zero;
+              }
+              fence_proxy_async_smem();
             }
-            fence_proxy_async_smem();
             __syncwarp();
           }
         }
@@ -213,7 +216,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           uint64_t db = make_smem_desc(smem_u32(b_src), B_LBO, 1024, SWIZZLE_128B);
 #pragma unroll
           for (int ks = 0; ks < BK / 16; ++ks) {
-            umma_bf16(tmem_d, da, db, idesc, (kb > 0 || ks > 0) ? 1u : 0u);
+            if (ks < k_steps) umma_bf16(tmem_d, da, db, idesc, (kb > 0 || ks > 0) ? 1u : 0u);
             da += A_KSTEP;
             db += B_KSTEP;
           }
