@@ -45,8 +45,9 @@ chunk_histogram_kernel(const void* __restrict__ indices, int is_i64, long long e
 // chunk_counts[c][e] becomes the first destination row of chunk c's entries for expert e.
 __global__ void __launch_bounds__(1024)
 chunk_scan_kernel(int* __restrict__ chunk_counts, int chunks, int experts, int* __restrict__ counts_out,
-                  long long* __restrict__ ends_out) {
+                  long long* __restrict__ ends_out, int* __restrict__ expert_of_row, long long entries) {
   extern __shared__ int totals[];  // [experts]
+  __shared__ int placed;
   for (int e = threadIdx.x; e < experts; e += blockDim.x) {
     int run = 0;
     for (int c = 0; c < chunks; ++c) {
@@ -68,8 +69,13 @@ chunk_scan_kernel(int* __restrict__ chunk_counts, int chunks, int experts, int* 
       run += v;
       if (ends_out != nullptr) ends_out[e] = run;
     }
+    placed = run;
   }
   __syncthreads();
+  // Rejected expert ids leave the last rows without an owner: mark them so that no consumer
+  // reads a stale expert or source there.
+  if (expert_of_row != nullptr)
+    for (long long r = placed + threadIdx.x; r < entries; r += blockDim.x) expert_of_row[r] = -1;
   for (int e = threadIdx.x; e < experts; e += blockDim.x) {
     const int base = totals[e];
     for (int c = 0; c < chunks; ++c) chunk_counts[static_cast<long long>(c) * experts + e] += base;
@@ -418,7 +424,7 @@ extern "C" int hmc_moe_sort_routes(const void* indices, int indices_are_i64, int
                                                                chunk_counts, status);
   HMC_LAUNCH_OK();
   chunk_scan_kernel<<<1, 1024, smem, stream>>>(chunk_counts, chunks, e, counts,
-                                               reinterpret_cast<long long*>(cumulative));
+                                               reinterpret_cast<long long*>(cumulative), expert_of_row, entries);
   HMC_LAUNCH_OK();
   chunk_rank_kernel<<<chunks, SORT_THREADS, smem, stream>>>(indices, indices_are_i64, entries, e, chunk_counts,
                                                           mapping, source_of_row, expert_of_row);

@@ -393,14 +393,20 @@ class MegaMoeExperts(torch.nn.Module):
                               invalid=weight_error is not None, status=self._status)
         if weight_error is not None:
             raise weight_error
-        # prepare_route just synchronised with the device, so earlier kernels' status words are final
-        self.check_status()
+        if route.pending is None:
+            # prepare_route just synchronised with the device, so earlier kernels' status words are final
+            self.check_status()
         if self._layout is None:
             self._layout = self._pending_layout
         self._ensure_workspace(device, route)
         weight1, weight2 = expert_weights
         probs = topk_weights if topk_weights.dtype == torch.float32 else topk_weights.float()
         out = _MegaMoeFunction.apply(hidden_flat, probs.contiguous(), weight1, weight2, self, route)
+        try:
+            route.finish()
+        except ValueError:
+            self._status.zero_()  # the rejected ids also set the status words; the call is over
+            raise
         return out.reshape(hidden_states.shape)
 
     def _peer_tables(self, workspace, expert_buffer: torch.Tensor):
@@ -476,22 +482,25 @@ class MegaMoeExperts(torch.nn.Module):
         grad_probs = torch.empty(tokens, self.top_k, dtype=torch.float32, device=device)
         kernels.moe_unpermute_grad(routed_out, grad_output, route.mapping, probs, self.top_k, grad_routed,
                                    grad_probs, status=self._status)
-        generation = workspace.begin_call()
-        if self.ep_size == 1:
-            expert_buffer = torch.empty(max(received, 1), hid, **bf16)
-            capacity = expert_buffer.shape[0]
-        else:
-            expert_buffer = workspace.expert_buffer
-            capacity = workspace.capacity_rows
-        peer_expert, peer_routed, peer_ctrl = self._peer_tables(workspace, expert_buffer)
-        kernels.ep_dispatch(grad_routed, None, route.expert_of_row, off["dispatch_src_off"],
-                            off["dispatch_target_off"], rows=routed_rows, top_k=self.top_k, ep=self.ep_size,
-                            local_experts=self.local_experts, capacity_rows=capacity, peer_buffers=peer_expert,
-                            peer_ctrl=peer_ctrl, local_ctrl=workspace.ctrl, generation=generation,
-                            status=self._status, budget_ns=self._wait_budget_ns)
         rows = max(received, 1)
-        dy_recv = expert_buffer[:rows]
-        arrival = workspace.ctrl[_lib.HMC_CTRL_ARRIVAL:_lib.HMC_CTRL_ARRIVAL + self.local_experts]
+        if self.ep_size == 1:
+            # One rank owns every expert: the source's expert-major order IS the owner's order
+            # (the reference short-circuits peer == self the same way, rma.h:205-208), so the
+            # rows are used in place and nothing has to arrive.
+            dy_recv = grad_routed[:rows]
+            arrival = None
+            generation = peer_routed = peer_ctrl = None
+        else:
+            generation = workspace.begin_call()
+            expert_buffer = workspace.expert_buffer
+            peer_expert, peer_routed, peer_ctrl = self._peer_tables(workspace, expert_buffer)
+            kernels.ep_dispatch(grad_routed, None, route.expert_of_row, off["dispatch_src_off"],
+                                off["dispatch_target_off"], rows=routed_rows, top_k=self.top_k, ep=self.ep_size,
+                                local_experts=self.local_experts, capacity_rows=workspace.capacity_rows,
+                                peer_buffers=peer_expert, peer_ctrl=peer_ctrl, local_ctrl=workspace.ctrl,
+                                generation=generation, status=self._status, budget_ns=self._wait_budget_ns)
+            dy_recv = expert_buffer[:rows]
+            arrival = workspace.ctrl[_lib.HMC_CTRL_ARRIVAL:_lib.HMC_CTRL_ARRIVAL + self.local_experts]
         grad_up = torch.empty(rows, 2 * inter, **bf16)
         grad_x_rows = torch.empty(rows, hid, **bf16)
         f32_partials = self._numerics.partial_weight_grad_dtype == "float32"
@@ -556,6 +565,8 @@ class MegaMoeExperts(torch.nn.Module):
         workspace = self._workspace
         device = source.device
         received, routed_rows = route.received_rows, route.routed_rows
+        if self.ep_size == 1 and source_of_row is None:
+            return source[:max(received, 1)], None, None, None  # already in the owner's order
         generation = workspace.begin_call()
         if self.ep_size == 1:
             expert_buffer = torch.empty(max(received, 1), self.hidden_size, dtype=torch.bfloat16, device=device)

@@ -18,6 +18,7 @@ import torch.distributed as dist
 from ... import kernels
 
 _HEADER = 3  # [invalid, local tokens, reserved] ahead of the per-expert counts
+_PINNED: dict = {}  # (device, experts) -> pinned int32 staging for single-rank validation
 
 
 @dataclass
@@ -27,12 +28,37 @@ class PreparedRoute:
     mapping: torch.Tensor          # [T*K] int32: destination row of flat (token, slot)
     source_of_row: torch.Tensor    # [T*K] int32: inverse permutation
     expert_of_row: torch.Tensor    # [T*K] int32
-    counts_by_source: list[list[int]]  # host copy of the gathered table
+    counts_by_source: Any          # host copy of the gathered table (None for single-rank calls)
     offsets: dict[str, torch.Tensor]
     routed_rows: int               # tokens * top_k on this rank
     received_rows: int             # rows this rank's experts receive
     max_received_rows: int         # over the group
     max_routed_rows: int           # over the group
+    pending: Any = None            # single-rank calls: (event, pinned counts + status words) checked by finish()
+
+    def finish(self, what: str = "MegaMoeExperts") -> None:
+        """Single-rank calls validate here, after the layer's kernels have been queued.
+
+        The counts and the status words were copied to pinned host memory right after the sort, so
+        waiting for that copy does not wait for the GEMMs queued behind it. Out-of-range expert ids
+        were dropped by the sort (mapping -1, no rows), so the queued kernels touched nothing bad.
+        """
+        if self.pending is None:
+            return
+        event, pinned, experts, expected = self.pending
+        self.pending = None
+        event.synchronize()
+        words = pinned.tolist()
+        routed = sum(words[:experts])
+        if routed != expected:
+            raise ValueError(
+                f"topk_ids must hold expert ids in [0, {experts}): {expected - routed} routes fell outside that range.")
+        status = words[experts:]
+        if status[0] != 0:
+            from ... import _lib
+
+            raise _lib.HmcError(f"{what}: device status {status[0]} ({_lib.STATUS_NAMES.get(status[0], '?')}), "
+                                f"detail {status[1:4]}")
 
 
 def validate_topk_inputs(hidden: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor) -> None:
@@ -51,6 +77,24 @@ def prepare_route(hidden: torch.Tensor, topk_ids: torch.Tensor, *, num_experts: 
     device = hidden.device
     tokens = hidden.shape[0]
     mapping, sources, row_experts, counts, _ = kernels.moe_sort_routes(topk_ids, num_experts, status=status)
+    if ep_size == 1 and status is not None:
+        # One rank owns every expert: every size the host needs is tokens * top_k, so nothing waits for
+        # the device here. Counts and status travel to pinned memory and are checked by finish().
+        table = counts.view(1, num_experts)
+        offsets = kernels.route_offsets(table, rank)
+        key = (device, num_experts)
+        pinned = _PINNED.get(key)
+        if pinned is None:
+            pinned = _PINNED[key] = torch.empty(num_experts + status.numel(), dtype=torch.int32).pin_memory()
+        pinned[:num_experts].copy_(counts, non_blocking=True)
+        pinned[num_experts:].copy_(status, non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        routed = tokens * top_k
+        return PreparedRoute(
+            mapping=mapping, source_of_row=sources, expert_of_row=row_experts, counts_by_source=None,
+            offsets=offsets, routed_rows=routed, received_rows=routed, max_received_rows=routed,
+            max_routed_rows=routed, pending=(event, pinned, num_experts, routed))
     payload = torch.empty(_HEADER + num_experts, dtype=torch.int32, device=device)
     payload[:_HEADER] = torch.tensor([int(invalid), tokens, 0], dtype=torch.int32, device=device) \
         if ep_size > 1 else 0
