@@ -24,6 +24,7 @@ HMC_EPI_STORE_F32 = 1
 HMC_EPI_SWIGLU = 2
 HMC_EPI_SWIGLU_GRAD = 3
 HMC_STATUS_WORDS = 8
+HMC_CLAMP_NONE, HMC_CLAMP_BEFORE_SILU, HMC_CLAMP_AFTER_SILU = 0, 1, 2
 
 STATUS_NAMES = {
     0: "ok",
@@ -49,7 +50,7 @@ class GroupedGemmArgs(ctypes.Structure):
         ("groups", c_int32),
         ("max_ctas", c_int32),
         ("tile_mode", c_int32),
-        ("reserved", c_int32),
+        ("swiglu_clamp", c_int32),
         ("rows", c_int64),
         ("m", c_int64),
         ("n", c_int64),
@@ -62,6 +63,10 @@ class GroupedGemmArgs(ctypes.Structure):
         ("ready_counters", c_void_p),
         ("ready_budget_ns", c_uint64),
         ("status", c_void_p),
+        ("swiglu_limit", c_float),
+        ("reserved", c_int32),
+        ("row_probs", c_void_p),
+        ("row_dot", c_void_p),
     ]
 
 
@@ -139,6 +144,7 @@ class EpDispatchArgs(ctypes.Structure):
         ("capacity_rows", c_int64),
         ("peer_buffers", c_void_p), ("peer_ctrl", c_void_p), ("local_ctrl", c_void_p),
         ("generation", c_int32), ("max_ctas", c_int32), ("budget_ns", c_uint64), ("status", c_void_p),
+        ("row_values", c_void_p), ("value_index", c_void_p), ("value_plane_offset", c_int64),
     ]
 
 
@@ -151,6 +157,7 @@ class EpCombineArgs(ctypes.Structure):
         ("target_rows_limit", c_int64),
         ("peer_buffers", c_void_p), ("peer_ctrl", c_void_p), ("local_ctrl", c_void_p),
         ("generation", c_int32), ("max_ctas", c_int32), ("budget_ns", c_uint64), ("status", c_void_p),
+        ("result_values", c_void_p), ("value_plane_offset", c_int64),
     ]
 
 

@@ -58,7 +58,8 @@ ep_dispatch_kernel(const uint4* __restrict__ tokens, const int* __restrict__ sou
                    const long long* __restrict__ dispatch_target_off, long long rows, int top_k, int vec_per_row,
                    int ep, int local_experts, long long capacity_rows, PeerTable peers,
                    const int* __restrict__ local_ctrl, int generation, unsigned long long budget_ns,
-                   int* __restrict__ status) {
+                   int* __restrict__ status, const float* __restrict__ row_values,
+                   const int* __restrict__ value_index, long long value_plane_offset) {
   __shared__ int seen[HMC_MAX_EP];
   __shared__ int chunk_expert[ROWS_PER_CHUNK];
   __shared__ int failed;
@@ -103,6 +104,12 @@ ep_dispatch_kernel(const uint4* __restrict__ tokens, const int* __restrict__ sou
       const uint4* src = tokens + src_row * vec_per_row;
       uint4* dst = static_cast<uint4*>(peers.data[e / local_experts]) + dest_row * vec_per_row;
       for (int v = lane; v < vec_per_row; v += 32) st_16(dst + v, ld_nc_16(src + v));
+      if (row_values != nullptr && lane == 0) {
+        // the row's scalar (its routing probability) lands in the float plane behind the rows
+        float* plane = reinterpret_cast<float*>(static_cast<unsigned char*>(peers.data[e / local_experts]) +
+                                                value_plane_offset);
+        plane[dest_row] = row_values[value_index != nullptr ? value_index[j] : j];
+      }
     }
     __syncthreads();
     // One release-add per run of equal experts in the chunk. The barrier above orders every
@@ -127,7 +134,8 @@ ep_combine_kernel(const uint4* __restrict__ results, const long long* __restrict
                   const long long* __restrict__ combine_target_off, long long rows, int vec_per_row, int ep,
                   int local_experts, long long target_rows_limit, PeerTable peers,
                   const int* __restrict__ local_ctrl, int generation, unsigned long long budget_ns,
-                  int* __restrict__ status) {
+                  int* __restrict__ status, const float* __restrict__ result_values,
+                  long long value_plane_offset) {
   __shared__ int seen[HMC_MAX_EP];
   __shared__ int chunk_source[ROWS_PER_CHUNK];
   __shared__ long long chunk_dest[ROWS_PER_CHUNK];
@@ -176,6 +184,10 @@ ep_combine_kernel(const uint4* __restrict__ results, const long long* __restrict
       const uint4* src = results + (r0 + r) * vec_per_row;
       uint4* dst = static_cast<uint4*>(peers.data[s]) + chunk_dest[r] * vec_per_row;
       for (int v = lane; v < vec_per_row; v += 32) st_16(dst + v, ld_nc_16(src + v));
+      if (result_values != nullptr && lane == 0) {
+        float* plane = reinterpret_cast<float*>(static_cast<unsigned char*>(peers.data[s]) + value_plane_offset);
+        plane[chunk_dest[r]] = result_values[r0 + r];
+      }
     }
     __syncthreads();
     if (threadIdx.x < count) {
@@ -287,6 +299,9 @@ extern "C" int hmc_ep_dispatch(const hmc_ep_dispatch_args* args, void* stream_pt
   HMC_REQUIRE(a.local_experts > 0 && a.local_experts <= HMC_CTRL_MAX_LOCAL_EXPERTS, HMC_ERR_LIMIT,
               "hmc_ep_dispatch: local experts must be in [1, %d]", HMC_CTRL_MAX_LOCAL_EXPERTS);
   HMC_REQUIRE(a.rows > 0 && a.rows < (1ll << 31) && a.top_k > 0, HMC_ERR_INVALID, "hmc_ep_dispatch: bad extents");
+  HMC_REQUIRE(a.row_values == nullptr || (a.value_plane_offset >= a.capacity_rows * a.hidden * 2 &&
+                                          a.value_plane_offset % 4 == 0),
+              HMC_ERR_INVALID, "hmc_ep_dispatch: the value plane must lie behind the rows of the receive buffer");
   const long long chunks = (a.rows + ROWS_PER_CHUNK - 1) / ROWS_PER_CHUNK;
   int grid = 4 * sm_count();
   if (a.max_ctas > 0 && grid > a.max_ctas) grid = a.max_ctas;
@@ -296,7 +311,8 @@ extern "C" int hmc_ep_dispatch(const hmc_ep_dispatch_args* args, void* stream_pt
       reinterpret_cast<const long long*>(a.dispatch_src_off), reinterpret_cast<const long long*>(a.dispatch_target_off),
       a.rows, static_cast<int>(a.top_k), static_cast<int>(a.hidden / 8), static_cast<int>(a.ep),
       static_cast<int>(a.local_experts), a.capacity_rows, table, a.local_ctrl, a.generation,
-      a.budget_ns ? a.budget_ns : 10ull * 1000 * 1000 * 1000, a.status);
+      a.budget_ns ? a.budget_ns : 10ull * 1000 * 1000 * 1000, a.status, a.row_values, a.value_index,
+      a.value_plane_offset);
   HMC_LAUNCH_OK();
   return 0;
 }
@@ -314,6 +330,9 @@ extern "C" int hmc_ep_combine(const hmc_ep_combine_args* args, void* stream_ptr)
               "hmc_ep_combine: rows must be 16-byte aligned multiples of 8 BF16 elements");
   HMC_REQUIRE(a.local_experts > 0 && a.rows > 0 && a.rows < (1ll << 31), HMC_ERR_INVALID,
               "hmc_ep_combine: bad extents");
+  HMC_REQUIRE(a.result_values == nullptr || (a.value_plane_offset >= a.target_rows_limit * a.hidden * 2 &&
+                                             a.value_plane_offset % 4 == 0),
+              HMC_ERR_INVALID, "hmc_ep_combine: the value plane must lie behind the rows of the routed buffer");
   const long long chunks = (a.rows + ROWS_PER_CHUNK - 1) / ROWS_PER_CHUNK;
   int grid = 4 * sm_count();
   if (a.max_ctas > 0 && grid > a.max_ctas) grid = a.max_ctas;
@@ -322,7 +341,8 @@ extern "C" int hmc_ep_combine(const hmc_ep_combine_args* args, void* stream_ptr)
       static_cast<const uint4*>(a.results), reinterpret_cast<const long long*>(a.segment_start),
       reinterpret_cast<const long long*>(a.combine_target_off), a.rows, static_cast<int>(a.hidden / 8),
       static_cast<int>(a.ep), static_cast<int>(a.local_experts), a.target_rows_limit, table, a.local_ctrl,
-      a.generation, a.budget_ns ? a.budget_ns : 10ull * 1000 * 1000 * 1000, a.status);
+      a.generation, a.budget_ns ? a.budget_ns : 10ull * 1000 * 1000 * 1000, a.status, a.result_values,
+      a.value_plane_offset);
   HMC_LAUNCH_OK();
   return 0;
 }

@@ -47,6 +47,10 @@ struct Params {
   const int* ready_counters;  // optional, RAGGED_M: per-group arrival counters (rows landed)
   unsigned long long ready_budget_ns;
   int* status;
+  int swiglu_clamp;        // HMC_CLAMP_*
+  float swiglu_limit;
+  const float* row_probs;  // optional per-row routing probability (weighting before FC2)
+  float* row_dot;          // SWIGLU_GRAD with row_probs: per-row probability gradient (atomic adds)
 };
 
 struct Tile {
@@ -110,6 +114,41 @@ __device__ __forceinline__ int k_iterations(const Params& p, const Tile& t) {
 
 __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)); }
 
+// SwiGLU with the optional clamp: the gate is clipped from above before or after SiLU, the up
+// projection to [-L, L]; a clipped branch passes its gradient while the clipped variable is within
+// the bound, equality included.
+struct SwigluTerms {
+  float act;    // value of the activation
+  float dgate;  // d act / d gate
+  float dup;    // d act / d up
+};
+
+__device__ __forceinline__ SwigluTerms swiglu_terms(float g, float u, int clamp, float limit) {
+  const float gx = clamp == HMC_CLAMP_BEFORE_SILU ? fminf(g, limit) : g;
+  const float s = 1.0f / (1.0f + __expf(-gx));
+  const float silu = gx * s;
+  const float dsilu = s * (1.0f + gx * (1.0f - s));
+  float gate_factor = silu;
+  float uc = u;
+  bool gate_pass = true;
+  bool up_pass = true;
+  if (clamp != HMC_CLAMP_NONE) {
+    uc = fminf(fmaxf(u, -limit), limit);
+    up_pass = u >= -limit && u <= limit;
+    if (clamp == HMC_CLAMP_BEFORE_SILU) {
+      gate_pass = g <= limit;
+    } else {
+      gate_pass = silu <= limit;
+      gate_factor = fminf(silu, limit);
+    }
+  }
+  SwigluTerms t;
+  t.act = gate_factor * uc;
+  t.dgate = gate_pass ? uc * dsilu : 0.0f;
+  t.dup = up_pass ? gate_factor : 0.0f;
+  return t;
+}
+
 // Row-major epilogues shared by the one-CTA and the CTA-pair kernels: the calling warp owns TMEM
 // lanes [32 * quarter, +32) and the column half `half` of a 128 x 256 accumulator; thread `lane`
 // owns output row `out_row` (written only when row_ok).
@@ -162,6 +201,8 @@ __device__ __forceinline__ void epilogue_rows(const Params& p, uint32_t taddr, l
     // (tests/common/multicore/fp32_expert_reference.py:22-25).
     __nv_bfloat16* u_dst = static_cast<__nv_bfloat16*>(p.c) + out_row * p.ldc + col_base;
     __nv_bfloat16* a_dst = static_cast<__nv_bfloat16*>(p.aux) + out_row * p.ld_aux + col_base;
+    const bool options = p.swiglu_clamp != HMC_CLAMP_NONE || p.row_probs != nullptr;
+    const float prob = (p.row_probs != nullptr && row_ok) ? p.row_probs[out_row] : 1.0f;
 #pragma unroll 1
     for (int c = half * (BN / 4); c < (half + 1) * (BN / 4); c += 32) {
       uint32_t g[32], u[32];
@@ -179,7 +220,18 @@ __device__ __forceinline__ void epilogue_rows(const Params& p, uint32_t taddr, l
               uo[q] = pack_bf16x2(__uint_as_float(u[j + 2 * q]), __uint_as_float(u[j + 2 * q + 1]));
               const float2 gf = unpack_bf16x2(go[q]);
               const float2 uf = unpack_bf16x2(uo[q]);
-              ao[q] = pack_bf16x2(silu_f(gf.x) * uf.x, silu_f(gf.y) * uf.y);
+              if (!options) {
+                ao[q] = pack_bf16x2(silu_f(gf.x) * uf.x, silu_f(gf.y) * uf.y);
+              } else {
+                float a0 = swiglu_terms(gf.x, uf.x, p.swiglu_clamp, p.swiglu_limit).act;
+                float a1 = swiglu_terms(gf.y, uf.y, p.swiglu_clamp, p.swiglu_limit).act;
+                if (p.row_probs != nullptr) {
+                  // two roundings: the activation first, then its product with the probability
+                  a0 = bf16_round(a0) * prob;
+                  a1 = bf16_round(a1) * prob;
+                }
+                ao[q] = pack_bf16x2(a0, a1);
+              }
             }
             *reinterpret_cast<uint4*>(u_dst + c + j) = make_uint4(go[0], go[1], go[2], go[3]);
             *reinterpret_cast<uint4*>(u_dst + p.n + c + j) = make_uint4(uo[0], uo[1], uo[2], uo[3]);
@@ -194,6 +246,9 @@ __device__ __forceinline__ void epilogue_rows(const Params& p, uint32_t taddr, l
     // (tests/common/multicore/fp32_expert_reference.py:29-33).
     const __nv_bfloat16* u_src = static_cast<const __nv_bfloat16*>(p.aux) + out_row * p.ld_aux + col_base;
     __nv_bfloat16* d_dst = static_cast<__nv_bfloat16*>(p.c) + out_row * p.ldc + col_base;
+    const bool options = p.swiglu_clamp != HMC_CLAMP_NONE || p.row_probs != nullptr;
+    const float prob = (p.row_probs != nullptr && row_ok) ? p.row_probs[out_row] : 1.0f;
+    float dot = 0.0f;
 #pragma unroll 1
     for (int c = c_lo; c < c_hi; c += 32) {
       uint32_t v[32];
@@ -212,13 +267,28 @@ __device__ __forceinline__ void epilogue_rows(const Params& p, uint32_t taddr, l
             for (int q = 0; q < 4; ++q) {
               const float2 gf = unpack_bf16x2(gw[q]);
               const float2 uf = unpack_bf16x2(uw[q]);
-              const float da0 = bf16_round(__uint_as_float(v[j + 2 * q]));
-              const float da1 = bf16_round(__uint_as_float(v[j + 2 * q + 1]));
-              const float s0 = 1.0f / (1.0f + __expf(-gf.x));
-              const float s1 = 1.0f / (1.0f + __expf(-gf.y));
-              dg[q] = pack_bf16x2(da0 * uf.x * s0 * (1.0f + gf.x * (1.0f - s0)),
-                                  da1 * uf.y * s1 * (1.0f + gf.y * (1.0f - s1)));
-              du[q] = pack_bf16x2(da0 * (gf.x * s0), da1 * (gf.y * s1));
+              float da0 = bf16_round(__uint_as_float(v[j + 2 * q]));
+              float da1 = bf16_round(__uint_as_float(v[j + 2 * q + 1]));
+              if (!options) {
+                const float s0 = 1.0f / (1.0f + __expf(-gf.x));
+                const float s1 = 1.0f / (1.0f + __expf(-gf.y));
+                dg[q] = pack_bf16x2(da0 * uf.x * s0 * (1.0f + gf.x * (1.0f - s0)),
+                                    da1 * uf.y * s1 * (1.0f + gf.y * (1.0f - s1)));
+                du[q] = pack_bf16x2(da0 * (gf.x * s0), da1 * (gf.y * s1));
+              } else {
+                const SwigluTerms t0 = swiglu_terms(gf.x, uf.x, p.swiglu_clamp, p.swiglu_limit);
+                const SwigluTerms t1 = swiglu_terms(gf.y, uf.y, p.swiglu_clamp, p.swiglu_limit);
+                if (p.row_probs != nullptr) {
+                  // the accumulator is the gradient of the weighted FC2 input: the probability
+                  // gradient uses the unweighted BF16 activation, the activation gradient is
+                  // rounded to BF16 after the multiplication
+                  dot += bf16_round(t0.act) * da0 + bf16_round(t1.act) * da1;
+                  da0 = bf16_round(da0 * prob);
+                  da1 = bf16_round(da1 * prob);
+                }
+                dg[q] = pack_bf16x2(da0 * t0.dgate, da1 * t1.dgate);
+                du[q] = pack_bf16x2(da0 * t0.dup, da1 * t1.dup);
+              }
             }
             *reinterpret_cast<uint4*>(d_dst + c + j) = make_uint4(dg[0], dg[1], dg[2], dg[3]);
             *reinterpret_cast<uint4*>(d_dst + p.n + c + j) = make_uint4(du[0], du[1], du[2], du[3]);
@@ -226,6 +296,7 @@ __device__ __forceinline__ void epilogue_rows(const Params& p, uint32_t taddr, l
         }
       }
     }
+    if (p.row_dot != nullptr && row_ok) atomicAdd(p.row_dot + out_row, dot);
   }
 }
 

@@ -447,6 +447,21 @@ extern "C" int hmc_grouped_gemm(const hmc_grouped_gemm_args* args, void* stream_
   p.ready_budget_ns = a.ready_budget_ns ? a.ready_budget_ns : 10ull * 1000 * 1000 * 1000;
   p.status = a.status;
   p.n = static_cast<int>(a.n);
+  {
+    const bool swiglu_family = a.epilogue == HMC_EPI_SWIGLU || a.epilogue == HMC_EPI_SWIGLU_GRAD;
+    HMC_REQUIRE(a.swiglu_clamp >= HMC_CLAMP_NONE && a.swiglu_clamp <= HMC_CLAMP_AFTER_SILU, HMC_ERR_INVALID,
+                "hmc_grouped_gemm: unknown swiglu_clamp %d", a.swiglu_clamp);
+    HMC_REQUIRE(swiglu_family || (a.swiglu_clamp == HMC_CLAMP_NONE && a.row_probs == nullptr && a.row_dot == nullptr),
+                HMC_ERR_INVALID, "hmc_grouped_gemm: clamp and row probabilities belong to the SwiGLU epilogues");
+    HMC_REQUIRE(a.swiglu_clamp == HMC_CLAMP_NONE || (a.swiglu_limit > 0.0f && a.swiglu_limit < 3.0e38f),
+                HMC_ERR_INVALID, "hmc_grouped_gemm: swiglu_limit must be positive and finite");
+    HMC_REQUIRE(a.row_dot == nullptr || (a.epilogue == HMC_EPI_SWIGLU_GRAD && a.row_probs != nullptr), HMC_ERR_INVALID,
+                "hmc_grouped_gemm: row_dot is an output of the SwiGLU-grad epilogue with row_probs");
+    p.swiglu_clamp = a.swiglu_clamp;
+    p.swiglu_limit = a.swiglu_limit;
+    p.row_probs = a.row_probs;
+    p.row_dot = a.row_dot;
+  }
 
   CUtensorMap ta, tb, tc;
   int rc;

@@ -45,13 +45,24 @@ def grouped_gemm(
     status: torch.Tensor | None = None,
     max_ctas: int = 0,
     tile_mode: int = 0,
+    swiglu_clamp: int = 0,
+    swiglu_limit: float = 0.0,
+    row_probs: torch.Tensor | None = None,
+    row_dot: torch.Tensor | None = None,
 ) -> None:
     """Launch the tcgen05 grouped GEMM.
+
+    ``swiglu_clamp`` / ``swiglu_limit`` select the clamped SwiGLU of the SwiGLU epilogues;
+    ``row_probs`` (float32 [rows]) weights the activation before FC2 and, in the SwiGLU-grad
+    epilogue, ``row_dot`` (float32 [rows], zeroed by the caller) receives the probability gradient.
 
     RAGGED_M: ``a`` [rows, k]; ``b`` [groups, k, n_cols] (MN) or [groups, n_cols, k] (K); ``c`` [rows, *].
     RAGGED_K: ``a`` [rows, m]; ``b`` [rows, n]; ``c`` [groups, m, n] BF16 or FP32.
     """
-    device = _require_cuda(a, b, c, group_ends, aux, ready_counters, status)
+    device = _require_cuda(a, b, c, group_ends, aux, ready_counters, status, row_probs, row_dot)
+    for name, plane in (("row_probs", row_probs), ("row_dot", row_dot)):
+        if plane is not None and (plane.dtype != torch.float32 or not plane.is_contiguous() or plane.numel() < a.shape[0]):
+            raise ValueError(f"{name} must be a contiguous float32 tensor with one entry per row")
     args = GroupedGemmArgs()
     args.mode = mode
     args.epilogue = epilogue
@@ -80,6 +91,10 @@ def grouped_gemm(
     args.ready_counters = _lib.ptr(ready_counters)
     args.ready_budget_ns = ready_budget_ns
     args.status = _lib.ptr(status)
+    args.swiglu_clamp = swiglu_clamp
+    args.swiglu_limit = swiglu_limit
+    args.row_probs = _lib.ptr(row_probs)
+    args.row_dot = _lib.ptr(row_dot)
     _count("hmc_grouped_gemm")
     with torch.cuda.device(device):
         _lib.check(_lib.load().hmc_grouped_gemm(ctypes.byref(args), _lib.stream_ptr(device)))
@@ -330,9 +345,16 @@ def mega_mhc_grad_out(tensors: dict, *, hc_eps: float, num_iters: int, status=No
 # --------------------------------------------------------------------------------- EP transport
 def ep_dispatch(tokens, source_of_row, expert_of_row, dispatch_src_off, dispatch_target_off, *, rows, top_k, ep,
                 local_experts, capacity_rows, peer_buffers, peer_ctrl, local_ctrl, generation, status=None,
-                budget_ns=0, max_ctas=0) -> None:
-    """Push expert-major rows (or gathered token rows) into their owners' receive buffers."""
-    device = _require_cuda(tokens, expert_of_row, dispatch_src_off, dispatch_target_off, local_ctrl)
+                budget_ns=0, max_ctas=0, row_values=None, value_index=None, value_plane_offset=0) -> None:
+    """Push expert-major rows (or gathered token rows) into their owners' receive buffers.
+
+    ``row_values`` (float32) adds one scalar per row, read at ``value_index[j]`` when an index is
+    given, and stored in the float plane ``value_plane_offset`` bytes into each owner's buffer.
+    """
+    device = _require_cuda(tokens, expert_of_row, dispatch_src_off, dispatch_target_off, local_ctrl, row_values,
+                           value_index)
+    if row_values is not None and (row_values.dtype != torch.float32 or not row_values.is_contiguous()):
+        raise ValueError("row_values must be a contiguous float32 tensor")
     args = _lib.EpDispatchArgs()
     args.tokens = tokens.data_ptr()
     args.source_of_row = _lib.ptr(source_of_row)
@@ -346,13 +368,18 @@ def ep_dispatch(tokens, source_of_row, expert_of_row, dispatch_src_off, dispatch
     args.local_ctrl = local_ctrl.data_ptr()
     args.generation, args.max_ctas, args.budget_ns = generation, max_ctas, budget_ns
     args.status = _lib.ptr(status)
+    args.row_values, args.value_index = _lib.ptr(row_values), _lib.ptr(value_index)
+    args.value_plane_offset = value_plane_offset
     _call("hmc_ep_dispatch", device, ctypes.byref(args))
 
 
 def ep_combine(results, segment_start, combine_target_off, *, rows, ep, local_experts, target_rows_limit,
-               peer_buffers, peer_ctrl, local_ctrl, generation, status=None, budget_ns=0, max_ctas=0) -> None:
-    """Return result rows to the routed buffers of their source ranks."""
-    device = _require_cuda(results, segment_start, combine_target_off, local_ctrl)
+               peer_buffers, peer_ctrl, local_ctrl, generation, status=None, budget_ns=0, max_ctas=0,
+               result_values=None, value_plane_offset=0) -> None:
+    """Return result rows (and optionally one float per row) to the routed buffers of their source ranks."""
+    device = _require_cuda(results, segment_start, combine_target_off, local_ctrl, result_values)
+    if result_values is not None and (result_values.dtype != torch.float32 or not result_values.is_contiguous()):
+        raise ValueError("result_values must be a contiguous float32 tensor")
     args = _lib.EpCombineArgs()
     args.results = results.data_ptr()
     args.segment_start = segment_start.data_ptr()
@@ -364,6 +391,8 @@ def ep_combine(results, segment_start, combine_target_off, *, rows, ep, local_ex
     args.local_ctrl = local_ctrl.data_ptr()
     args.generation, args.max_ctas, args.budget_ns = generation, max_ctas, budget_ns
     args.status = _lib.ptr(status)
+    args.result_values = _lib.ptr(result_values)
+    args.value_plane_offset = value_plane_offset
     _call("hmc_ep_combine", device, ctypes.byref(args))
 
 

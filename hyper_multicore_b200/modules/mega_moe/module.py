@@ -183,9 +183,6 @@ class MegaMoeExperts(torch.nn.Module):
                              "on the sm_100a backend (the reference requires multiples of 64)")
         if tuning.dispatch_mode != "push":
             raise NotImplementedError("dispatch_mode='pull' is not available in the sm_100a backend; use 'push'")
-        if numerics.swiglu_limit is not None or numerics.apply_probs_before_fc2:
-            raise NotImplementedError(
-                "swiglu_limit and apply_probs_before_fc2 are not available yet in the sm_100a backend")
         self.hidden_size = hidden_size
         self.intermediate_size = intermediate_size
         self.num_experts = num_experts
@@ -414,6 +411,21 @@ class MegaMoeExperts(torch.nn.Module):
             return workspace.peer_expert, workspace.peer_routed, workspace.peer_ctrl
         return (ctypes.c_void_p * 1)(expert_buffer.data_ptr()), None, workspace.peer_ctrl
 
+    def _swiglu_options(self) -> dict:
+        """Clamp arguments of the SwiGLU epilogues (reference: docs/mega_moe.md:258-272)."""
+        limit = self._numerics.swiglu_limit
+        if limit is None:
+            return {}
+        clamp = _lib.HMC_CLAMP_AFTER_SILU if self._numerics.clamp_after_silu else _lib.HMC_CLAMP_BEFORE_SILU
+        return {"swiglu_clamp": clamp, "swiglu_limit": float(limit)}
+
+    def _local_rows(self, rows: int, device: torch.device):
+        """Single-rank receive buffer: [rows, H] BF16 followed by one float per row."""
+        row_bytes = self.hidden_size * 2
+        raw = torch.empty(rows * (row_bytes + 4), dtype=torch.uint8, device=device)
+        return (raw[:rows * row_bytes].view(torch.bfloat16).view(rows, self.hidden_size),
+                raw[rows * row_bytes:].view(torch.float32), rows * row_bytes)
+
     def _run_forward(self, hidden, probs, w1, w2, route: PreparedRoute):
         workspace = self._workspace
         device = hidden.device
@@ -422,35 +434,41 @@ class MegaMoeExperts(torch.nn.Module):
         received, routed_rows = route.received_rows, route.routed_rows
         inter, hid = self.intermediate_size, self.hidden_size
         bf16 = dict(dtype=torch.bfloat16, device=device)
+        before_fc2 = self._numerics.apply_probs_before_fc2
         generation = workspace.begin_call()
         if self.ep_size == 1:
-            expert_buffer = torch.empty(max(received, 1), hid, **bf16)
+            expert_buffer, expert_values, plane_offset = self._local_rows(max(received, 1), device)
             capacity = expert_buffer.shape[0]
         else:
-            expert_buffer = workspace.expert_buffer
-            capacity = workspace.capacity_rows
+            expert_buffer, expert_values = workspace.expert_buffer, workspace.expert_values
+            capacity, plane_offset = workspace.capacity_rows, workspace.expert_plane_offset
         peer_expert, peer_routed, peer_ctrl = self._peer_tables(workspace, expert_buffer)
         off = route.offsets
+        travelling = dict(row_values=probs.reshape(-1), value_index=route.source_of_row,
+                          value_plane_offset=plane_offset) if before_fc2 else {}
         kernels.ep_dispatch(hidden, route.source_of_row, route.expert_of_row, off["dispatch_src_off"],
                             off["dispatch_target_off"], rows=routed_rows, top_k=self.top_k, ep=self.ep_size,
                             local_experts=self.local_experts, capacity_rows=capacity, peer_buffers=peer_expert,
                             peer_ctrl=peer_ctrl, local_ctrl=workspace.ctrl, generation=generation,
-                            status=self._status, budget_ns=self._wait_budget_ns)
+                            status=self._status, budget_ns=self._wait_budget_ns, **travelling)
         rows = max(received, 1)
         up_proj = torch.empty(rows, 2 * inter, **bf16)
         activation = torch.empty(rows, inter, **bf16)
         down_proj = torch.empty(rows, hid, **bf16)
         x_recv = expert_buffer[:rows]
+        row_probs = expert_values[:rows] if before_fc2 else None
         arrival = workspace.ctrl[_lib.HMC_CTRL_ARRIVAL:_lib.HMC_CTRL_ARRIVAL + self.local_experts]
         if received > 0:
             kernels.grouped_gemm(x_recv, w1, up_proj, off["group_list"], mode=kernels.HMC_GEMM_RAGGED_M,
                                  b_major=b_major, epilogue=kernels.HMC_EPI_SWIGLU, aux=activation,
-                                 ready_counters=arrival, ready_budget_ns=self._wait_budget_ns, status=self._status)
+                                 ready_counters=arrival, ready_budget_ns=self._wait_budget_ns, status=self._status,
+                                 row_probs=row_probs, **self._swiglu_options())
             kernels.grouped_gemm(activation, w2, down_proj, off["group_list"], mode=kernels.HMC_GEMM_RAGGED_M,
                                  b_major=b_major, status=self._status)
         if self.ep_size == 1:
             routed_out = down_proj
             saved_received = x_recv
+            saved_probs = row_probs
         else:
             kernels.ep_combine(down_proj, off["recv_segment_start"], off["combine_target_off"], rows=received,
                                ep=self.ep_size, local_experts=self.local_experts,
@@ -462,13 +480,24 @@ class MegaMoeExperts(torch.nn.Module):
             # (reference: autograd.py:655-663 saves a dispatch copy and clones the combine output).
             routed_out = workspace.routed_buffer[:max(routed_rows, 1)].clone()
             saved_received = x_recv.clone()
+            saved_probs = row_probs.clone() if before_fc2 else None
         out = torch.empty(hidden.shape[0], hid, **bf16)
-        kernels.moe_unpermute(routed_out, route.mapping, probs, hidden.shape[0], self.top_k, out,
-                              status=self._status)
-        return out, (saved_received, up_proj, activation, routed_out)
+        if before_fc2:
+            # The rows are already weighted: the Top-K rows of a token are summed as they are
+            # (reference: _restore_unweighted_output, backends/bf16/autograd.py:133-135).
+            kernels.moe_token_permute_grad(routed_out, route.mapping, hidden.shape[0], self.top_k, out,
+                                           status=self._status)
+            saved_last = saved_probs if saved_probs is not None else torch.empty(0, device=device)
+        else:
+            kernels.moe_unpermute(routed_out, route.mapping, probs, hidden.shape[0], self.top_k, out,
+                                  status=self._status)
+            saved_last = routed_out
+        return out, (saved_received, up_proj, activation, saved_last)
 
-    def _run_backward(self, grad_output, hidden, probs, w1, w2, received_x, up_proj, activation, routed_out,
+    def _run_backward(self, grad_output, hidden, probs, w1, w2, received_x, up_proj, activation, saved_last,
                       route: PreparedRoute, need_weight_grads):
+        """`saved_last` is the routed forward output (probabilities after FC2, needed for their
+        gradient) or the received per-row probabilities (probabilities before FC2)."""
         workspace = self._workspace
         device = hidden.device
         eio = self._layout == "EIO"
@@ -477,30 +506,53 @@ class MegaMoeExperts(torch.nn.Module):
         bf16 = dict(dtype=torch.bfloat16, device=device)
         off = route.offsets
         tokens = hidden.shape[0]
-        # dYe (source's expert-major order) and dProbs
-        grad_routed = torch.empty(max(routed_rows, 1), hid, **bf16)
-        grad_probs = torch.empty(tokens, self.top_k, dtype=torch.float32, device=device)
-        kernels.moe_unpermute_grad(routed_out, grad_output, route.mapping, probs, self.top_k, grad_routed,
-                                   grad_probs, status=self._status)
         rows = max(received, 1)
-        if self.ep_size == 1:
-            # One rank owns every expert: the source's expert-major order IS the owner's order
-            # (the reference short-circuits peer == self the same way, rma.h:205-208), so the
-            # rows are used in place and nothing has to arrive.
-            dy_recv = grad_routed[:rows]
-            arrival = None
-            generation = peer_routed = peer_ctrl = None
-        else:
+        before_fc2 = self._numerics.apply_probs_before_fc2
+        grad_probs = None
+        generation = peer_routed = peer_ctrl = None
+        if before_fc2:
+            # dYe rows are plain copies of the token gradients (reference: _stage_backward_source,
+            # backends/bf16/autograd.py:138-150); the gather is fused into the dispatch.
+            row_probs = saved_last
             generation = workspace.begin_call()
-            expert_buffer = workspace.expert_buffer
+            if self.ep_size == 1:
+                expert_buffer, _, _ = self._local_rows(rows, device)
+                capacity = rows
+            else:
+                expert_buffer, capacity = workspace.expert_buffer, workspace.capacity_rows
             peer_expert, peer_routed, peer_ctrl = self._peer_tables(workspace, expert_buffer)
-            kernels.ep_dispatch(grad_routed, None, route.expert_of_row, off["dispatch_src_off"],
+            kernels.ep_dispatch(grad_output, route.source_of_row, route.expert_of_row, off["dispatch_src_off"],
                                 off["dispatch_target_off"], rows=routed_rows, top_k=self.top_k, ep=self.ep_size,
-                                local_experts=self.local_experts, capacity_rows=workspace.capacity_rows,
-                                peer_buffers=peer_expert, peer_ctrl=peer_ctrl, local_ctrl=workspace.ctrl,
-                                generation=generation, status=self._status, budget_ns=self._wait_budget_ns)
+                                local_experts=self.local_experts, capacity_rows=capacity, peer_buffers=peer_expert,
+                                peer_ctrl=peer_ctrl, local_ctrl=workspace.ctrl, generation=generation,
+                                status=self._status, budget_ns=self._wait_budget_ns)
             dy_recv = expert_buffer[:rows]
             arrival = workspace.ctrl[_lib.HMC_CTRL_ARRIVAL:_lib.HMC_CTRL_ARRIVAL + self.local_experts]
+            row_dot = torch.zeros(rows, dtype=torch.float32, device=device)
+        else:
+            row_probs = row_dot = None
+            # dYe (source's expert-major order) and dProbs
+            grad_routed = torch.empty(max(routed_rows, 1), hid, **bf16)
+            grad_probs = torch.empty(tokens, self.top_k, dtype=torch.float32, device=device)
+            kernels.moe_unpermute_grad(saved_last, grad_output, route.mapping, probs, self.top_k, grad_routed,
+                                       grad_probs, status=self._status)
+            if self.ep_size == 1:
+                # One rank owns every expert: the source's expert-major order IS the owner's order
+                # (the reference short-circuits peer == self the same way, rma.h:205-208), so the
+                # rows are used in place and nothing has to arrive.
+                dy_recv = grad_routed[:rows]
+                arrival = None
+            else:
+                generation = workspace.begin_call()
+                expert_buffer = workspace.expert_buffer
+                peer_expert, peer_routed, peer_ctrl = self._peer_tables(workspace, expert_buffer)
+                kernels.ep_dispatch(grad_routed, None, route.expert_of_row, off["dispatch_src_off"],
+                                    off["dispatch_target_off"], rows=routed_rows, top_k=self.top_k, ep=self.ep_size,
+                                    local_experts=self.local_experts, capacity_rows=workspace.capacity_rows,
+                                    peer_buffers=peer_expert, peer_ctrl=peer_ctrl, local_ctrl=workspace.ctrl,
+                                    generation=generation, status=self._status, budget_ns=self._wait_budget_ns)
+                dy_recv = expert_buffer[:rows]
+                arrival = workspace.ctrl[_lib.HMC_CTRL_ARRIVAL:_lib.HMC_CTRL_ARRIVAL + self.local_experts]
         grad_up = torch.empty(rows, 2 * inter, **bf16)
         grad_x_rows = torch.empty(rows, hid, **bf16)
         f32_partials = self._numerics.partial_weight_grad_dtype == "float32"
@@ -513,11 +565,13 @@ class MegaMoeExperts(torch.nn.Module):
         if received > 0:
             kernels.grouped_gemm(dy_recv, w2, grad_up, off["group_list"], mode=kernels.HMC_GEMM_RAGGED_M,
                                  b_major=bt_major, epilogue=kernels.HMC_EPI_SWIGLU_GRAD, aux=up_proj,
-                                 ready_counters=arrival, ready_budget_ns=self._wait_budget_ns, status=self._status)
+                                 ready_counters=arrival, ready_budget_ns=self._wait_budget_ns, status=self._status,
+                                 row_probs=row_probs, row_dot=row_dot, **self._swiglu_options())
             kernels.grouped_gemm(grad_up, w1, grad_x_rows, off["group_list"], mode=kernels.HMC_GEMM_RAGGED_M,
                                  b_major=bt_major, status=self._status)
         if grad_w2 is not None:
             # The arrival wait of the dA GEMM above orders this kernel after the rows have landed.
+            # With probabilities before FC2, `activation` is the weighted input FC2 actually saw.
             a_op, b_op = (activation, dy_recv) if eio else (dy_recv, activation)
             kernels.grouped_gemm(a_op, b_op, grad_w2, off["group_list"], mode=kernels.HMC_GEMM_RAGGED_K, epilogue=wepi,
                                  status=self._status)
@@ -526,17 +580,22 @@ class MegaMoeExperts(torch.nn.Module):
             kernels.grouped_gemm(a_op, b_op, grad_w1, off["group_list"], mode=kernels.HMC_GEMM_RAGGED_K, epilogue=wepi,
                                  status=self._status)
         if self.ep_size == 1:
-            returned = grad_x_rows
+            returned, returned_dot = grad_x_rows, row_dot
         else:
+            returning = dict(result_values=row_dot, value_plane_offset=workspace.routed_plane_offset) if before_fc2 else {}
             kernels.ep_combine(grad_x_rows, off["recv_segment_start"], off["combine_target_off"], rows=received,
                                ep=self.ep_size, local_experts=self.local_experts,
                                target_rows_limit=workspace.routed_rows, peer_buffers=peer_routed,
                                peer_ctrl=peer_ctrl, local_ctrl=workspace.ctrl, generation=generation,
-                               status=self._status, budget_ns=self._wait_budget_ns)
+                               status=self._status, budget_ns=self._wait_budget_ns, **returning)
             kernels.ep_wait(workspace.ctrl[_lib.HMC_CTRL_COMBINE:], routed_rows, status=self._status, budget_ns=self._wait_budget_ns)
-            returned = workspace.routed_buffer
+            returned, returned_dot = workspace.routed_buffer, workspace.routed_values
         grad_hidden = torch.empty(tokens, hid, **bf16)
         kernels.moe_token_permute_grad(returned, route.mapping, tokens, self.top_k, grad_hidden, status=self._status)
+        if before_fc2:
+            # the probability gradient of route (t, k) sits at that route's row of the source order
+            # (reference: backends/bf16/autograd.py:725-730)
+            grad_probs = returned_dot.index_select(0, route.mapping.long()).view(tokens, self.top_k)
         if grad_w1 is not None and grad_w1.dtype != w1.dtype:
             grad_w1 = grad_w1.to(w1.dtype)
         if grad_w2 is not None and grad_w2.dtype != w2.dtype:

@@ -58,8 +58,12 @@ class PeerWorkspace:
         row_bytes = hidden_size * 2
         self._ctrl_bytes = _lib.HMC_CTRL_WORDS * 4
         self._expert_off = (self._ctrl_bytes + 1023) // 1024 * 1024
-        self._routed_off = self._expert_off + self.capacity_rows * row_bytes
-        self.nbytes = self._routed_off + self.routed_rows * row_bytes
+        # One float per row follows each buffer (routing probabilities travelling with dispatched rows,
+        # probability gradients travelling back with combined rows).
+        self.expert_plane_offset = self.capacity_rows * row_bytes
+        self.routed_plane_offset = self.routed_rows * row_bytes
+        self._routed_off = self._expert_off + self.expert_plane_offset + self.capacity_rows * 4
+        self.nbytes = self._routed_off + self.routed_plane_offset + self.routed_rows * 4
         lib = _lib.load()
         with torch.cuda.device(device):
             _lib.check(lib.hmc_symm_alloc(self.nbytes, ctypes.byref(self._base)))
@@ -67,10 +71,14 @@ class PeerWorkspace:
         span = torch.as_tensor(_DeviceSpan(self._base.value, self.nbytes, self), device=device)
         self._bytes = span
         self.ctrl = span[:self._ctrl_bytes].view(torch.int32)
-        self.expert_buffer = span[self._expert_off:self._routed_off].view(torch.bfloat16).view(
+        expert_end = self._expert_off + self.expert_plane_offset
+        routed_end = self._routed_off + self.routed_plane_offset
+        self.expert_buffer = span[self._expert_off:expert_end].view(torch.bfloat16).view(
             self.capacity_rows, hidden_size)
-        self.routed_buffer = span[self._routed_off:self.nbytes].view(torch.bfloat16).view(
+        self.expert_values = span[expert_end:self._routed_off].view(torch.float32)
+        self.routed_buffer = span[self._routed_off:routed_end].view(torch.bfloat16).view(
             self.routed_rows, hidden_size)
+        self.routed_values = span[routed_end:self.nbytes].view(torch.float32)
         pointer_array = ctypes.c_void_p * self.ep
         self.peer_ctrl = pointer_array(*self._peer_bases)
         self.peer_expert = pointer_array(*(base + self._expert_off for base in self._peer_bases))

@@ -65,6 +65,9 @@ int hmc_worker_queue_layout_version(void);
 #define HMC_EPI_STORE_F32 1   /* FP32 output (partial weight gradients, mHC projection) */
 #define HMC_EPI_SWIGLU 2      /* B has 2n columns [gate | up]; c = U[rows, 2n], aux = Act[rows, n] */
 #define HMC_EPI_SWIGLU_GRAD 3 /* acc = dAct[rows, n]; aux = U[rows, 2n] (input); c = dU[rows, 2n] */
+#define HMC_CLAMP_NONE 0
+#define HMC_CLAMP_BEFORE_SILU 1 /* silu(min(g, L)) * clamp(u, -L, L) */
+#define HMC_CLAMP_AFTER_SILU 2  /* min(silu(g), L) * clamp(u, -L, L) */
 
 typedef struct hmc_grouped_gemm_args {
   int32_t mode;
@@ -74,7 +77,7 @@ typedef struct hmc_grouped_gemm_args {
   int32_t groups;
   int32_t max_ctas; /* 0 = one CTA per SM */
   int32_t tile_mode; /* RAGGED_M: HMC_TILE_AUTO, _SINGLE (128-row tiles) or _PAIR (256-row CTA-pair tiles) */
-  int32_t reserved;
+  int32_t swiglu_clamp; /* HMC_CLAMP_*: SwiGLU / SwiGLU-grad epilogues only */
   int64_t rows;     /* extent of the ragged dimension of a (and of b for RAGGED_K) */
   int64_t m;        /* RAGGED_K only */
   int64_t n;
@@ -87,6 +90,15 @@ typedef struct hmc_grouped_gemm_args {
   const int32_t* ready_counters; /* optional device int32[groups]: rows landed per group */
   uint64_t ready_budget_ns;      /* 0 = 10 s */
   int32_t* status;               /* optional device int32[HMC_STATUS_WORDS] */
+  /* Numerics options of the reference (hyper_multicore/modules/mega_moe/numerics.py:21-50,
+   * docs/mega_moe.md:258-308; device math ops/common/mega_moe/routing_probabilities.h:19-108). */
+  float swiglu_limit;     /* L of the clamp: gate clipped from above, up clipped to [-L, L] */
+  int32_t reserved;
+  const float* row_probs; /* optional device float[rows]: routing probability of each row ("before FC2").
+                             SWIGLU: aux = bf16(fp32(bf16(act)) * p). SWIGLU_GRAD: the accumulator is the
+                             gradient of that weighted activation; dAct = bf16(fp32(bf16(acc)) * p) */
+  float* row_dot;         /* SWIGLU_GRAD with row_probs: row_dot[row] += sum_col bf16(act) * bf16(acc), the
+                             probability gradient; zeroed by the caller */
 } hmc_grouped_gemm_args;
 
 int hmc_grouped_gemm(const hmc_grouped_gemm_args* args, void* stream);
@@ -417,6 +429,13 @@ typedef struct hmc_ep_dispatch_args {
   int32_t max_ctas;              /* 0 = default */
   uint64_t budget_ns;            /* bound of the ready wait, 0 = 10 s */
   int32_t* status;
+  /* Optional scalar per row (the routing probability when probabilities are applied before FC2;
+   * reference: probability planes, ops/common/mega_moe/contracts/probability_abi.h:10-19). The value of
+   * row j, row_values[value_index ? value_index[j] : j], is stored as float at
+   * (char*)peer_buffer + value_plane_offset + 4 * destination_row on the owner. */
+  const float* row_values;
+  const int32_t* value_index;
+  int64_t value_plane_offset;    /* bytes; at least capacity_rows * hidden * 2 */
 } hmc_ep_dispatch_args;
 
 typedef struct hmc_ep_combine_args {
@@ -435,6 +454,8 @@ typedef struct hmc_ep_combine_args {
   int32_t max_ctas;
   uint64_t budget_ns;
   int32_t* status;
+  const float* result_values;    /* optional float[rows] (probability gradients), returned with the rows */
+  int64_t value_plane_offset;    /* bytes behind the source's routed buffer; at least target_rows_limit * hidden * 2 */
 } hmc_ep_combine_args;
 
 int hmc_symm_alloc(int64_t bytes, void** out); /* cudaMalloc + zero; set-up time only */

@@ -75,7 +75,7 @@ def scenario_mx(module, rank, world, device, token_counts, hidden, inter, expert
             assert error <= limit, (name, error)
 
 
-def scenario(module, rank, world, device, token_counts, hidden, inter, experts, top_k, seed, layout):
+def scenario(module, rank, world, device, token_counts, hidden, inter, experts, top_k, seed, layout, **options):
     local = experts // world
     gw = torch.Generator().manual_seed(seed)
     w1_all = (torch.randn(experts, hidden, 2 * inter, generator=gw) * 0.05).bfloat16()
@@ -96,7 +96,7 @@ def scenario(module, rank, world, device, token_counts, hidden, inter, experts, 
     module.check_status()
     ref = omoe.experts_forward_backward(
         torch.cat([p[0] for p in per_rank]), torch.cat([p[1] for p in per_rank]),
-        torch.cat([p[2] for p in per_rank]), w1_all, w2_all, torch.cat([p[3] for p in per_rank]))
+        torch.cat([p[2] for p in per_rank]), w1_all, w2_all, torch.cat([p[3] for p in per_rank]), **options)
     start = sum(token_counts[:rank])
     rows = slice(start, start + token_counts[rank])
     check("output", out, ref["output"][rows])
@@ -133,6 +133,16 @@ def main():
         state = module.debug_state()
         assert state["ep"] == world and state["generation"] >= 10, state
         module.close()
+    # numerics options: clamped SwiGLU with the probabilities travelling with the rows (before FC2)
+    from hyper_multicore_b200 import MegaMoeNumericsOptions
+
+    options = dict(swiglu_limit=0.5, clamp_after_silu=True, apply_probs_before_fc2=True)
+    module = MegaMoeExperts(hidden_size=hidden, intermediate_size=inter, num_experts=experts, top_k=top_k,
+                            ep_group=dist.group.WORLD, numerics_options=MegaMoeNumericsOptions(**options))
+    for index, counts in enumerate(([96] * world, [40 + 57 * r for r in range(world)], [0] + [64] * (world - 1))):
+        scenario(module, rank, world, device, counts, hidden, inter, experts, top_k, seed=50 + index, layout="EIO",
+                 **options)
+    module.close()
     module = MegaMoeExperts(hidden_size=hidden, intermediate_size=inter, num_experts=experts, top_k=top_k,
                             ep_group=dist.group.WORLD, precision="mxfp8")
     for index, counts in enumerate(([96] * world, [40 + 57 * r for r in range(world)], [0] + [200] * (world - 1))):

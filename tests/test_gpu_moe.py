@@ -36,11 +36,19 @@ def run_module(case, dev, layout="EIO", numerics=None):
             "grad_w1": grad_w1.cpu(), "grad_w2": grad_w2.cpu()}, module
 
 
-def check(got, ref):
+def check(got, ref, stray_fraction=0.0):
+    """`stray_fraction` > 0 admits that share of elements outside the tolerance (one-ulp BF16 differences
+    of K-term sums rounded once here and per addition in the golden), bounded by a relative L2 error."""
     for name in ("output", "grad_hidden", "grad_probs", "grad_w1", "grad_w2"):
         expected = ref[name].float()
+        actual = got[name].float()
         scale = max(1.0, float(expected.abs().max()))
-        torch.testing.assert_close(got[name].float(), expected, rtol=RTOL, atol=ATOL * scale, msg=lambda m, n=name: f"{n}: {m}")
+        if stray_fraction == 0.0:
+            torch.testing.assert_close(actual, expected, rtol=RTOL, atol=ATOL * scale, msg=lambda m, n=name: f"{n}: {m}")
+            continue
+        outside = (actual - expected).abs() > ATOL * scale + RTOL * expected.abs()
+        assert outside.float().mean().item() <= stray_fraction, f"{name}: {int(outside.sum())} elements outside the tolerance"
+        assert ((actual - expected).norm() / expected.norm().clamp_min(1e-12)).item() < 1e-2, f"{name}: relative L2 error"
 
 
 @pytest.mark.parametrize("layout", ["EIO", "EOI"])
@@ -86,6 +94,31 @@ def test_float32_partial_weight_gradients(cuda_device):
                                         case["w2"], case["grad_output"])
     got, module = run_module(case, cuda_device, numerics=MegaMoeNumericsOptions(partial_weight_grad_dtype="float32"))
     check(got, ref)
+
+
+@pytest.mark.parametrize("limit,after_silu,before_fc2", [(1.0, False, False), (1.0, True, False),
+                                                         (None, False, True), (1.25, False, True), (1.25, True, True)])
+@pytest.mark.parametrize("layout", ["EIO", "EOI"])
+def test_numerics_options(cuda_device, limit, after_silu, before_fc2, layout):
+    """SwiGLU clamp before / after SiLU and probabilities applied before FC2 (docs/mega_moe.md:258-308 of
+    the reference). Weights are five times larger than elsewhere so that outputs are O(1) and the limits
+    sit inside the spread of the gate / up values (std about 1.6): a large share of the entries is clipped."""
+    from hyper_multicore_b200 import MegaMoeNumericsOptions
+
+    case = make_case(300, 256, 128, 8, 3, seed=11, dead_expert=2)
+    case["w1"], case["w2"] = (case["w1"].float() * 5).bfloat16(), (case["w2"].float() * 5).bfloat16()
+    options = dict(swiglu_limit=limit, clamp_after_silu=after_silu, apply_probs_before_fc2=before_fc2)
+    ref = omoe.experts_forward_backward(case["hidden"], case["topk_ids"], case["topk_weights"], case["w1"],
+                                        case["w2"], case["grad_output"], **options)
+    plain = omoe.experts_forward_backward(case["hidden"], case["topk_ids"], case["topk_weights"], case["w1"],
+                                          case["w2"], case["grad_output"])
+    if limit is not None:
+        assert (ref["output"].float() - plain["output"].float()).abs().max() > 0.2, "the clamp must matter here"
+    got, module = run_module(case, cuda_device, layout, numerics=MegaMoeNumericsOptions(**options))
+    check(got, ref, stray_fraction=1e-3)
+    assert module.swiglu_limit == limit and module.clamp_after_silu == after_silu
+    assert module.apply_probs_before_fc2 == before_fc2
+    assert (got["grad_w1"][2] == 0).all() and (got["grad_w2"][2] == 0).all()
 
 
 def test_repeated_calls_and_activation_checkpoint(cuda_device):
