@@ -47,6 +47,7 @@ struct Params {
   const int* ready_counters;  // optional, RAGGED_M: per-group arrival counters (rows landed)
   unsigned long long ready_budget_ns;
   int* status;
+  int tma_store;           // RAGGED_M plain stores: full tiles leave through shared memory + TMA
   int swiglu_clamp;        // HMC_CLAMP_*
   float swiglu_limit;
   const float* row_probs;  // optional per-row routing probability (weighting before FC2)

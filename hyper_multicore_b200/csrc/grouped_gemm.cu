@@ -59,7 +59,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     mbar_fence_init();
     prefetch_tensormap(&tm_a);
     prefetch_tensormap(&tm_b);
-    if (p.mode == HMC_GEMM_RAGGED_K) prefetch_tensormap(&tm_c);
+    if (p.mode == HMC_GEMM_RAGGED_K || p.tma_store) prefetch_tensormap(&tm_c);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, TMEM_COLS);
@@ -286,13 +286,18 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                              static_cast<uint32_t>(acc * BN);
-      if (p.mode == HMC_GEMM_RAGGED_K) {
+      // A RAGGED_M tile whose 128 rows all belong to its group may use the same path: nothing past
+      // the group's last row is written.
+      const bool full_rows = p.tma_store && t.row0 + static_cast<long long>(t.m_idx + 1) * BM <= t.row1;
+      if (p.mode == HMC_GEMM_RAGGED_K || full_rows) {
         // Weight-gradient tiles are regular [m, n] grids per group, so they leave through shared
         // memory and TMA stores (full 128-byte lines, clipped at the m and n edges by the tensor
         // map). Each warp stages a 32-row x 128-byte box: 64 BF16 or 32 FP32 columns per store.
         const bool f32 = p.epilogue == HMC_EPI_STORE_F32;
         const int step = f32 ? 32 : 64;
-        const int m0 = t.m_idx * BM + quarter * 32;
+        const bool ragged_k = p.mode == HMC_GEMM_RAGGED_K;
+        const int m0 = (ragged_k ? t.m_idx * BM : static_cast<int>(t.row0) + t.m_idx * BM) + quarter * 32;
+        const int plane = ragged_k ? t.group : 0;
 #pragma unroll 1
         for (int c = c_lo; c < c_hi; c += step) {
           if (col_base + c >= p.n) break;
@@ -325,7 +330,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
-            tma_store_3d(&tm_c, my_stage, col_base + c, m0, t.group);
+            tma_store_3d(&tm_c, my_stage, col_base + c, m0, plane);
             bulk_commit_group();
           }
           store_pending = true;
@@ -529,7 +534,18 @@ extern "C" int hmc_grouped_gemm(const hmc_grouped_gemm_args* args, void* stream_
       if ((rc = make_map(&tc, a.c, 3, dims, box, f32)) != 0) return rc;
     }
   }
-  if (a.mode == HMC_GEMM_RAGGED_M) tc = ta;  // unused by the kernel in this mode
+  if (a.mode == HMC_GEMM_RAGGED_M) {
+    tc = ta;  // unused by the kernel unless the plain-store path below is on
+    const bool f32 = a.epilogue == HMC_EPI_STORE_F32;
+    const bool plain = f32 || a.epilogue == HMC_EPI_STORE_BF16;
+    if (plain && (a.n * (f32 ? 4 : 2)) % 16 == 0 && aligned16(a.c)) {
+      // C = [1, rows, n] seen through the same 32-row x 128-byte boxes as the weight gradients
+      cuuint64_t dims[3] = {static_cast<cuuint64_t>(a.n), static_cast<cuuint64_t>(a.rows), 1};
+      cuuint32_t box[3] = {f32 ? 32u : 64u, 32, 1};
+      if ((rc = make_map(&tc, a.c, 3, dims, box, f32)) != 0) return rc;
+      p.tma_store = 1;
+    }
+  }
 
   int grid = a.max_ctas > 0 ? a.max_ctas : sm_count();
   if (grid > sm_count()) grid = sm_count();

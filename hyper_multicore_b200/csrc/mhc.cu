@@ -33,7 +33,7 @@ __device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + expf
 // Forward, stage 1 (one warp per token): residual post-mix, both RMS statistics, BF16 input mix,
 // final RMSNorm. The token's mixed row is re-read from the cache line this lane wrote itself.
 // ---------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(WARPS * 32)
+__global__ void __launch_bounds__(WARPS * 32, 3)
 mhc_post_kernel(const uint4* __restrict__ prev_out, const uint4* __restrict__ residual,
                 const float* __restrict__ prev_pre, const float* __restrict__ prev_post,
                 const float* __restrict__ prev_mix, const uint4* __restrict__ norm_weight, long long tokens,
@@ -323,7 +323,7 @@ mhc_mapping_grad_kernel(const float* __restrict__ hc_before_norm, const float* _
 // ---------------------------------------------------------------------------------------------
 // Backward, stage 2 (one warp per token): everything that streams over the hidden dimension.
 // ---------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(WARPS * 32)
+__global__ void __launch_bounds__(WARPS * 32, 2)
 mhc_stream_grad_kernel(const uint4* __restrict__ grad_new_residual, const uint4* __restrict__ grad_block_input,
                        const uint4* __restrict__ new_residual, const uint4* __restrict__ mixed_input,
                        const uint4* __restrict__ residual, const uint4* __restrict__ prev_out,
@@ -333,11 +333,8 @@ mhc_stream_grad_kernel(const uint4* __restrict__ grad_new_residual, const uint4*
                        const float* __restrict__ rms_rstd, const float* __restrict__ rms_coef, long long tokens,
                        int hidden, uint4* __restrict__ grad_residual, uint4* __restrict__ grad_prev_out,
                        float* __restrict__ grad_prev_pre, float* __restrict__ grad_prev_post,
-                       float* __restrict__ grad_prev_mix, float* __restrict__ grad_norm_weight) {
-  extern __shared__ float norm_acc[];  // [hidden] per-CTA partial of d norm_weight
+                       float* __restrict__ grad_prev_mix) {
   const int vec = hidden / 8;
-  for (int h = threadIdx.x; h < hidden; h += blockDim.x) norm_acc[h] = 0.f;
-  __syncthreads();
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
   for (long long t = static_cast<long long>(blockIdx.x) * WARPS + warp; t < tokens;
@@ -379,10 +376,7 @@ mhc_stream_grad_kernel(const uint4* __restrict__ grad_new_residual, const uint4*
       unpack8(ld_16(norm_weight + v), w);
       unpack8(ld_16(mixed_row + v), m);
 #pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        d_mixed[e] = rstd * (gb[e] * w[e]) - m[e] * back;
-        atomicAdd(&norm_acc[v * 8 + e], gb[e] * m[e] * rstd);
-      }
+      for (int e = 0; e < 8; ++e) d_mixed[e] = rstd * (gb[e] * w[e]) - m[e] * back;
       float dR[STREAMS][8];
 #pragma unroll
       for (int i = 0; i < STREAMS; ++i) {
@@ -441,8 +435,41 @@ mhc_stream_grad_kernel(const uint4* __restrict__ grad_new_residual, const uint4*
       }
     }
   }
+}
+
+// d norm_weight[h] = sum_t grad_block_input[t, h] * mixed_input[t, h] * rstd[t]: a column reduction.
+// Block = 32 column vectors x 8 token lanes; every thread keeps 8 FP32 partial sums in registers.
+__global__ void __launch_bounds__(256)
+mhc_norm_weight_grad_kernel(const uint4* __restrict__ grad_block_input, const uint4* __restrict__ mixed_input,
+                            const float* __restrict__ rms_rstd, long long tokens, int vec,
+                            float* __restrict__ grad_norm_weight) {
+  __shared__ float red[8][32][9];
+  const int tx = threadIdx.x & 31;
+  const int ty = threadIdx.x >> 5;
+  const int v = blockIdx.x * 32 + tx;
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  if (v < vec) {
+    const long long step = static_cast<long long>(gridDim.y) * 8;
+#pragma unroll 4
+    for (long long t = static_cast<long long>(blockIdx.y) * 8 + ty; t < tokens; t += step) {
+      float gb[8], m[8];
+      unpack8(ld_nc_16(grad_block_input + t * vec + v), gb);
+      unpack8(ld_nc_16(mixed_input + t * vec + v), m);
+      const float r = rms_rstd[t];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] = fmaf(gb[e] * m[e], r, acc[e]);
+    }
+  }
+#pragma unroll
+  for (int e = 0; e < 8; ++e) red[ty][tx][e] = acc[e];
   __syncthreads();
-  for (int h = threadIdx.x; h < hidden; h += blockDim.x) atomicAdd(&grad_norm_weight[h], norm_acc[h]);
+  // thread (ty, tx) sums column e = ty of vector tx over the 8 token lanes
+  if (v < vec) {
+    float total = 0.f;
+#pragma unroll
+    for (int y = 0; y < 8; ++y) total += red[y][tx][ty];
+    atomicAdd(grad_norm_weight + static_cast<long long>(v) * 8 + ty, total);
+  }
 }
 
 // dphi[c, k] = parts[c, k] + parts[32 + c, k]
@@ -540,7 +567,7 @@ extern "C" int hmc_mega_mhc(const hmc_mega_mhc_args* args, void* stream_ptr) {
   g.status = a.status;
   rc = run_gemm(g, stream);
   if (rc != 0) return rc;
-  mhc_mapping_kernel<<<static_cast<unsigned>((a.tokens + 127) / 128), 128, 0, stream>>>(
+  mhc_mapping_kernel<<<static_cast<unsigned>((a.tokens + 31) / 32), 32, 0, stream>>>(
       q_parts, a.inv_rms, a.alpha, a.bias, a.tokens, a.hc_eps, a.num_iters, a.next_pre_mix, a.next_post_mix,
       a.next_residual_mix, a.hc_before_norm, a.need_backward ? a.sum_out : nullptr,
       a.need_backward ? a.norm_out : nullptr);
@@ -563,8 +590,6 @@ extern "C" int hmc_mega_mhc_grad(const hmc_mega_mhc_grad_args* args, void* strea
   HMC_REQUIRE(a.workspace_bytes >= hmc_mega_mhc_grad_workspace_bytes(a.tokens, a.hidden), HMC_ERR_INVALID,
               "hmc_mega_mhc_grad: workspace holds %lld bytes, %lld needed", (long long)a.workspace_bytes,
               (long long)hmc_mega_mhc_grad_workspace_bytes(a.tokens, a.hidden));
-  HMC_REQUIRE(a.hidden * 4 <= 200 * 1024, HMC_ERR_LIMIT,
-              "hmc_mega_mhc_grad: hidden size %lld exceeds the shared-memory accumulator (51200)", (long long)a.hidden);
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
   const int hidden = static_cast<int>(a.hidden);
   const long long k = 4ll * a.hidden;
@@ -593,7 +618,7 @@ extern "C" int hmc_mega_mhc_grad(const hmc_mega_mhc_grad_args* args, void* strea
   HMC_LAUNCH_OK();
   fill_i64_kernel<<<1, 1, 0, stream>>>(ends, T);
   HMC_LAUNCH_OK();
-  mhc_mapping_grad_kernel<<<static_cast<unsigned>((T + 127) / 128), 128, 0, stream>>>(
+  mhc_mapping_grad_kernel<<<static_cast<unsigned>((T + 31) / 32), 32, 0, stream>>>(
       a.hc_before_norm, a.inv_rms, a.alpha, a.bias, a.grad_next_pre_mix, a.grad_next_post_mix,
       a.grad_next_residual_mix, T, hidden, a.hc_eps, a.num_iters, dq_rows, dq_cols, rms_coef, a.grad_alpha,
       a.grad_bias);
@@ -608,6 +633,7 @@ extern "C" int hmc_mega_mhc_grad(const hmc_mega_mhc_grad_args* args, void* strea
     g.rows = T;
     g.n = k;
     g.k = 128;
+    g.tile_mode = HMC_TILE_SINGLE;  // two k-blocks per tile: the store path decides, and 128-row tiles store by TMA
     g.a = dq_rows;
     g.b = phi_split;
     g.c = proj_grad;
@@ -637,23 +663,23 @@ extern "C" int hmc_mega_mhc_grad(const hmc_mega_mhc_grad_args* args, void* strea
   mhc_combine_dphi_kernel<<<static_cast<unsigned>((k + 255) / 256), 256, 0, stream>>>(dphi_parts, k, a.grad_phi);
   HMC_LAUNCH_OK();
   {
-    static bool configured = false;
-    if (!configured) {
-      HMC_CUDA_OK(cudaFuncSetAttribute(mhc_stream_grad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       200 * 1024));
-      configured = true;
-    }
-    int grid = 2 * sm_count();
+    const int vec = hidden / 8;
+    dim3 grid_nw(static_cast<unsigned>((vec + 31) / 32), static_cast<unsigned>(T >= 4096 ? 64 : (T + 63) / 64));
+    mhc_norm_weight_grad_kernel<<<grid_nw, 256, 0, stream>>>(static_cast<const uint4*>(a.grad_block_input),
+                                                             static_cast<const uint4*>(a.mixed_input), a.rms_rstd, T,
+                                                             vec, a.grad_norm_weight);
+    HMC_LAUNCH_OK();
+    int grid = 4 * sm_count();
     const long long need = (T + WARPS - 1) / WARPS;
     if (need < grid) grid = static_cast<int>(need);
-    mhc_stream_grad_kernel<<<grid, WARPS * 32, a.hidden * sizeof(float), stream>>>(
+    mhc_stream_grad_kernel<<<grid, WARPS * 32, 0, stream>>>(
         static_cast<const uint4*>(a.grad_new_residual), static_cast<const uint4*>(a.grad_block_input),
         static_cast<const uint4*>(a.new_residual), static_cast<const uint4*>(a.mixed_input),
         static_cast<const uint4*>(a.residual), static_cast<const uint4*>(a.previous_output),
         reinterpret_cast<const uint4*>(proj_grad), static_cast<const uint4*>(a.norm_weight), a.previous_pre_mix,
         a.previous_post_mix, a.previous_residual_mix, a.rms_rstd, rms_coef, T, hidden,
         static_cast<uint4*>(a.grad_residual), static_cast<uint4*>(a.grad_previous_output),
-        a.grad_previous_pre_mix, a.grad_previous_post_mix, a.grad_previous_residual_mix, a.grad_norm_weight);
+        a.grad_previous_pre_mix, a.grad_previous_post_mix, a.grad_previous_residual_mix);
     HMC_LAUNCH_OK();
   }
   return 0;

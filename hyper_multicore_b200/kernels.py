@@ -409,7 +409,7 @@ KERNELS_PER_CALL = {
     "hmc_moe_histogram": 1, "hmc_moe_sort_routes": 3, "hmc_moe_gather_rows": 1,
     "hmc_moe_permute_from_mapping": 1, "hmc_moe_unpermute": 1, "hmc_moe_unpermute_grad": 1,
     "hmc_moe_token_permute_grad": 1, "hmc_zero_empty_expert_grad": 1, "hmc_route_offsets": 1,
-    "hmc_mega_mhc": 5, "hmc_mega_mhc_grad": 7, "hmc_ep_publish_ready": 1, "hmc_ep_dispatch": 1,
+    "hmc_mega_mhc": 5, "hmc_mega_mhc_grad": 8, "hmc_ep_publish_ready": 1, "hmc_ep_dispatch": 1,
     "hmc_ep_combine": 1, "hmc_ep_wait": 1, "hmc_ep_wait_groups": 1,
 }
 
