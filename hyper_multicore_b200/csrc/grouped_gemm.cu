@@ -555,9 +555,7 @@ extern "C" int hmc_grouped_gemm(const hmc_grouped_gemm_args* args, void* stream_
     return launch<HMC_MAJOR_MN, HMC_MAJOR_MN>(ta, tb, tc, p, grid, stream);
   }
   // CTA pairs work on 256-row tiles: worth it once the average group fills most of one
-  // and the epilogue is light (the SwiGLU-grad epilogue prefers the deeper overlap of 128-row tiles)
-  const bool use_pairs = a.tile_mode == HMC_TILE_PAIR || (a.tile_mode == HMC_TILE_AUTO && a.rows >= 192ll * a.groups &&
-                                                          a.epilogue != HMC_EPI_SWIGLU_GRAD);
+  const bool use_pairs = a.tile_mode == HMC_TILE_PAIR || (a.tile_mode == HMC_TILE_AUTO && a.rows >= 192ll * a.groups);
   if (use_pairs && a.k % 8 == 0 && sm_count() >= 2)
     return launch_grouped_gemm_pair(ta, tb, p, a.b_major, grid, stream);
   if (a.b_major == HMC_MAJOR_MN) return launch<HMC_MAJOR_K, HMC_MAJOR_MN>(ta, tb, tc, p, grid, stream);

@@ -33,7 +33,7 @@ __device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + expf
 // Forward, stage 1 (one warp per token): residual post-mix, both RMS statistics, BF16 input mix,
 // final RMSNorm. The token's mixed row is re-read from the cache line this lane wrote itself.
 // ---------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(WARPS * 32, 3)
+__global__ void __launch_bounds__(WARPS * 32, 2)
 mhc_post_kernel(const uint4* __restrict__ prev_out, const uint4* __restrict__ residual,
                 const float* __restrict__ prev_pre, const float* __restrict__ prev_post,
                 const float* __restrict__ prev_mix, const uint4* __restrict__ norm_weight, long long tokens,
@@ -56,6 +56,7 @@ mhc_post_kernel(const uint4* __restrict__ prev_out, const uint4* __restrict__ re
   uint4* new_row = new_residual + t * STREAMS * vec;
   uint4* mixed_row = mixed_input + t * vec;
   float sumsq = 0.f, sumsq_mixed = 0.f;
+#pragma unroll 2
   for (int v = lane; v < vec; v += 32) {
     float r[STREAMS][8], o[8];
 #pragma unroll
