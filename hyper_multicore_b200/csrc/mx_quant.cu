@@ -17,7 +17,7 @@ namespace hmc {
 namespace {
 
 constexpr int TILE = 128;
-constexpr int LD = TILE + 1;  // shared-memory row stride in floats (conflict-free both ways)
+constexpr int LDB = TILE + 8;  // shared-memory row stride in BF16 elements (16-byte rows, conflict-free both ways)
 constexpr int THREADS = 256;
 
 __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)); }
@@ -29,6 +29,10 @@ __device__ __forceinline__ uint32_t block_exponent(float amax) {
   return static_cast<uint32_t>(min(max(e, 0), 254));
 }
 __device__ __forceinline__ float inverse_scale(uint32_t biased) { return __uint_as_float((254u - biased) << 23); }
+// two values -> two E4M3 bytes (first value in the low byte), round to nearest even, saturating
+__device__ __forceinline__ uint32_t e4m3x2(float lo, float hi) {
+  return static_cast<uint32_t>(__nv_cvt_float2_to_fp8x2(make_float2(lo, hi), __NV_SATFINITE, __NV_E4M3));
+}
 __device__ __forceinline__ uint8_t to_e4m3(float v) {
   return static_cast<uint8_t>(__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3));
 }
@@ -50,8 +54,8 @@ struct QuantParams {
 };
 
 // One CTA per (128-row padded block, 128-column block).
-__global__ void __launch_bounds__(THREADS) mx_quant_kernel(const QuantParams p) {
-  extern __shared__ float tile[];  // [TILE][LD]
+__global__ void __launch_bounds__(THREADS, 3) mx_quant_kernel(const QuantParams p) {
+  extern __shared__ __align__(16) __nv_bfloat16 tile[];  // [TILE][LDB], BF16-exact values
   __shared__ long long s_row0;
   __shared__ int s_valid;
   const int pb = blockIdx.x;
@@ -80,7 +84,12 @@ __global__ void __launch_bounds__(THREADS) mx_quant_kernel(const QuantParams p) 
   const int width = p.width;
   const int c0 = cb * TILE;
 
-  // ---- load (and transform) the tile: 8 BF16 per access
+  // ---- load (and transform) the tile, 8 BF16 per access. Sixteen threads cover one row, so the four
+  // threads of a 32-column block are neighbours: the row-wise block maximum is two shuffles away and
+  // the row-quantised bytes leave straight from registers; only the column pass needs shared memory.
+  const long long pad_row0 = static_cast<long long>(pb) * TILE;
+  uint8_t* row_atom = p.row_data != nullptr ? p.row_scale + (static_cast<long long>(cb) * p.pad_blocks + pb) * 512 : nullptr;
+#pragma unroll 2
   for (int i = threadIdx.x; i < TILE * (TILE / 8); i += THREADS) {
     const int r = i >> 4;
     const int c = (i & 15) * 8;
@@ -137,67 +146,58 @@ __global__ void __launch_bounds__(THREADS) mx_quant_kernel(const QuantParams p) 
           }
         }
       }
-      if (p.dense != nullptr) {
-        uint4 o;
-        o.x = pack_bf16x2(v[0], v[1]);
-        o.y = pack_bf16x2(v[2], v[3]);
-        o.z = pack_bf16x2(v[4], v[5]);
-        o.w = pack_bf16x2(v[6], v[7]);
-        *reinterpret_cast<uint4*>(p.dense + row * width + c0 + c) = o;
-      }
     } else {
 #pragma unroll
       for (int j = 0; j < 8; ++j) v[j] = 0.f;
     }
-#pragma unroll
-    for (int j = 0; j < 8; ++j) tile[r * LD + c + j] = v[j];
-  }
-  __syncthreads();
-
-  const long long pad_row0 = static_cast<long long>(pb) * TILE;
-  // ---- 32-element blocks along each row
-  if (p.row_data != nullptr) {
-    uint8_t* atom = p.row_scale + (static_cast<long long>(cb) * p.pad_blocks + pb) * 512;
-    for (int item = threadIdx.x; item < 4 * TILE; item += THREADS) {
-      const int r = item & (TILE - 1);  // a warp covers 32 different rows of one block column
-      const int j = item >> 7;
-      const float* src = tile + r * LD + 32 * j;
+    // every value is BF16-exact here
+    const uint4 packed = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]),
+                                    pack_bf16x2(v[6], v[7]));
+    if (p.dense != nullptr && r < valid) *reinterpret_cast<uint4*>(p.dense + (row0 + r) * width + c0 + c) = packed;
+    if (p.col_data != nullptr) *reinterpret_cast<uint4*>(tile + r * LDB + c) = packed;
+    if (p.row_data != nullptr) {
       float amax = 0.f;
 #pragma unroll
-      for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(src[i]));
+      for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
       const uint32_t e = block_exponent(amax);
       const float inv = inverse_scale(e);
-      uint32_t packed[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        packed[i] = static_cast<uint32_t>(to_e4m3(src[4 * i] * inv)) |
-                    (static_cast<uint32_t>(to_e4m3(src[4 * i + 1] * inv)) << 8) |
-                    (static_cast<uint32_t>(to_e4m3(src[4 * i + 2] * inv)) << 16) |
-                    (static_cast<uint32_t>(to_e4m3(src[4 * i + 3] * inv)) << 24);
-      }
-      uint8_t* dst = p.row_data + (pad_row0 + r) * width + c0 + 32 * j;
-      *reinterpret_cast<uint4*>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-      *reinterpret_cast<uint4*>(dst + 16) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
-      atom[(r & 31) * 16 + (r >> 5) * 4 + j] = static_cast<uint8_t>(e);
+      uint2 q;
+      q.x = e4m3x2(v[0] * inv, v[1] * inv) | (e4m3x2(v[2] * inv, v[3] * inv) << 16);
+      q.y = e4m3x2(v[4] * inv, v[5] * inv) | (e4m3x2(v[6] * inv, v[7] * inv) << 16);
+      *reinterpret_cast<uint2*>(p.row_data + (pad_row0 + r) * width + c0 + c) = q;
+      if ((threadIdx.x & 3) == 0) row_atom[(r & 31) * 16 + (r >> 5) * 4 + (c >> 5)] = static_cast<uint8_t>(e);
     }
   }
-  // ---- 32-element blocks down each column
+  // ---- 32-element blocks down each column: one thread per (column pair, 32-row block)
   if (p.col_data != nullptr) {
+    __syncthreads();
     uint8_t* atom = p.col_scale + (static_cast<long long>(pb) * (width / TILE) + cb) * 512;
-    for (int item = threadIdx.x; item < 4 * TILE; item += THREADS) {
-      const int c = item & (TILE - 1);
-      const int jb = item >> 7;
-      const float* src = tile + (32 * jb) * LD + c;
-      float amax = 0.f;
+    const int cp = threadIdx.x & 63;
+    const int jb = threadIdx.x >> 6;
+    const uint32_t* src = reinterpret_cast<const uint32_t*>(tile + (32 * jb) * LDB + 2 * cp);
+    uint32_t w[32];
+    float amax0 = 0.f, amax1 = 0.f;
 #pragma unroll
-      for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(src[i * LD]));
-      const uint32_t e = block_exponent(amax);
-      const float inv = inverse_scale(e);
-      uint8_t* dst = p.col_data + (pad_row0 + 32 * jb) * width + c0 + c;
-#pragma unroll 4
-      for (int i = 0; i < 32; ++i) dst[static_cast<long long>(i) * width] = to_e4m3(src[i * LD] * inv);
-      atom[(c & 31) * 16 + (c >> 5) * 4 + jb] = static_cast<uint8_t>(e);
+    for (int i = 0; i < 32; ++i) {
+      w[i] = src[i * (LDB / 2)];
+      const float2 f = unpack_bf16x2(w[i]);
+      amax0 = fmaxf(amax0, fabsf(f.x));
+      amax1 = fmaxf(amax1, fabsf(f.y));
     }
+    const uint32_t e0 = block_exponent(amax0), e1 = block_exponent(amax1);
+    const float inv0 = inverse_scale(e0), inv1 = inverse_scale(e1);
+    uint8_t* dst = p.col_data + (pad_row0 + 32 * jb) * width + c0 + 2 * cp;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      const float2 f = unpack_bf16x2(w[i]);
+      *reinterpret_cast<uint16_t*>(dst + static_cast<long long>(i) * width) =
+          static_cast<uint16_t>(e4m3x2(f.x * inv0, f.y * inv1));
+    }
+    const int c_even = 2 * cp;
+    atom[(c_even & 31) * 16 + (c_even >> 5) * 4 + jb] = static_cast<uint8_t>(e0);
+    atom[((c_even + 1) & 31) * 16 + ((c_even + 1) >> 5) * 4 + jb] = static_cast<uint8_t>(e1);
   }
 }
 
@@ -314,7 +314,7 @@ extern "C" int hmc_mx_quant(const hmc_mx_quant_args* args, void* stream_ptr) {
   p.col_scale = static_cast<uint8_t*>(a.col_scale);
   p.dense = static_cast<__nv_bfloat16*>(a.dense);
   static bool configured = false;
-  const int smem = TILE * LD * sizeof(float);
+  const int smem = TILE * LDB * sizeof(__nv_bfloat16);
   if (!configured) {
     HMC_CUDA_OK(cudaFuncSetAttribute(mx_quant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     configured = true;
