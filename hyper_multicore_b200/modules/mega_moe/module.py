@@ -16,9 +16,11 @@ Backward mirrors it with dY / dX and the four gradient GEMMs (autograd.py:681-76
 from __future__ import annotations
 
 import ctypes
+import itertools
 import math
 import os
 import struct
+import weakref
 from typing import Any
 
 import torch
@@ -123,6 +125,51 @@ class _LocalWorkspace:
         """Nothing to release explicitly."""
 
 
+class _ResourceGroup:
+    """Workspace owned jointly by the serial modules of one group
+    (reference: _ExecutionResourceGroup, hyper_multicore/modules/module.py:262-345, 408-430)."""
+
+    def __init__(self, key: tuple) -> None:
+        self.key = key
+        self.members: set[int] = set()
+        self.workspace: Any | None = None
+        self.closed = False
+        self.shared = False
+        self.sequence = next(_GROUP_SEQUENCE)  # creation order: the same on every rank
+        _GROUPS.add(self)
+
+
+_GROUPS: "weakref.WeakSet[_ResourceGroup]" = weakref.WeakSet()
+_GROUP_SEQUENCE = itertools.count()
+_DESTROY_HOOKED = False
+
+
+def _close_all_groups() -> None:
+    """Release every live workspace; every rank reaches this in the same order."""
+    for group in sorted(_GROUPS, key=lambda g: g.sequence):
+        if group.workspace is not None and not group.closed:
+            group.workspace.close()
+            group.workspace = None
+            group.closed = True
+
+
+def _hook_process_group_destruction() -> None:
+    """Workspaces map peer memory through the process group's ranks: release them before the group
+    goes away (reference: hyper_multicore/_automatic.py:55-124, docs/mega_moe.md:348-356)."""
+    global _DESTROY_HOOKED  # pylint: disable=global-statement
+    if _DESTROY_HOOKED:
+        return
+    original = dist.destroy_process_group
+
+    def destroy_process_group(group=None):
+        if group is None or group is dist.group.WORLD:
+            _close_all_groups()
+        return original(group)
+
+    dist.destroy_process_group = destroy_process_group
+    _DESTROY_HOOKED = True
+
+
 class _MegaMoeFunction(torch.autograd.Function):
     """Forward / backward of the routed expert FFN on already prepared routes."""
 
@@ -200,8 +247,12 @@ class MegaMoeExperts(torch.nn.Module):
         # that is late by more than this makes its peers give up with a status word instead of hanging.
         self._wait_budget_ns = int(float(os.environ.get("HMC_EP_WAIT_SECONDS", "60")) * 1e9)
         self._backward_expected = False
-        self._workspace: PeerWorkspace | _LocalWorkspace | None = None
+        self._group = _ResourceGroup(self._compatibility_key())
+        self._group.members.add(id(self))
+        self._closed = False
         self._status: torch.Tensor | None = None
+        if ep_size > 1:
+            _hook_process_group_destruction()
         local, hidden, inter = self.local_experts, hidden_size, intermediate_size
         self._weight_shapes = {
             "EIO": ((local, hidden, inter * 2), (local, inter, hidden)),
@@ -224,6 +275,57 @@ class MegaMoeExperts(torch.nn.Module):
     @property
     def apply_probs_before_fc2(self) -> bool:
         return self._numerics.apply_probs_before_fc2
+
+    # ------------------------------------------------------------------ execution resources
+    @property
+    def _workspace(self):
+        return self._group.workspace
+
+    @_workspace.setter
+    def _workspace(self, value) -> None:
+        self._group.workspace = value
+
+    def _compatibility_key(self) -> tuple:
+        """Normalised configuration two modules must share to use one workspace: field values, not
+        option-object identity (reference: docs/mega_moe.md:337-342)."""
+        numerics, tuning = self._numerics, self._tuning
+        return (type(self).__name__, self.hidden_size, self.intermediate_size, self.num_experts, self.top_k,
+                self.ep_size, id(self._ep_group), self._precision,
+                (numerics.partial_weight_grad_dtype, numerics.swiglu_limit, numerics.clamp_after_silu,
+                 numerics.apply_probs_before_fc2),
+                (tuning.dispatch_mode, tuning.dispatch_split, tuning.combine_split, tuning.initial_capacity_factor,
+                 tuning.capacity_growth_factor))
+
+    @classmethod
+    def share_execution_resources(cls, modules) -> None:
+        """Share one workspace among compatible modules that execute serially; must be called
+        before any of them runs (reference: hyper_multicore/modules/module.py:262-323)."""
+        members = tuple(modules)
+        if not members:
+            raise ValueError("shared multicore execution requires at least one module.")
+        if len({id(member) for member in members}) != len(members):
+            raise ValueError("shared multicore execution cannot contain duplicate modules.")
+        if any(not isinstance(member, cls) for member in members):
+            raise TypeError(f"all shared modules must be {cls.__name__} instances, "
+                            f"got {[type(member).__name__ for member in members]}.")
+        if any(member._closed or member._group.closed for member in members):  # pylint: disable=protected-access
+            raise RuntimeError("closed multicore modules cannot share execution resources.")
+        if len({type(member) for member in members}) != 1:
+            raise TypeError("shared multicore execution requires one concrete module type.")
+        first = members[0]._group  # pylint: disable=protected-access
+        if all(member._group is first for member in members):  # pylint: disable=protected-access
+            return
+        for member in members:
+            group = member._group  # pylint: disable=protected-access
+            if group.key != first.key:
+                raise ValueError("shared multicore modules must have identical configuration and scope.")
+            if group.workspace is not None or len(group.members) != 1:
+                raise RuntimeError("execution resources must be shared before first use or previous grouping.")
+        first.shared = True
+        for member in members[1:]:
+            member._group.members.discard(id(member))  # pylint: disable=protected-access
+            member._group = first  # pylint: disable=protected-access
+            first.members.add(id(member))
 
     # ------------------------------------------------------------------ validation
     def _infer_layout(self, shape1, shape2) -> str:
@@ -339,16 +441,29 @@ class MegaMoeExperts(torch.nn.Module):
             generation = workspace.generation
             workspace.close()
         bound = self.ep_size * align_rows(need_routed)
+        if need_capacity > bound:
+            # cannot happen for real routes: a rank receives at most every rank's tokens * top_k rows
+            # (reference: _grow_receive_capacity, hyper_multicore/modules/mega_moe/spec.py:113-119)
+            raise ValueError("MegaMoe route exceeds the lossless token bound")
         capacity = max(need_capacity, min(capacity, bound))
         self._workspace = PeerWorkspace(self._ep_group, self.hidden_size, capacity, routed, device)
         self._workspace.generation = generation
         return self._workspace
 
     def close(self) -> None:
-        """Release the workspace. Collective over the EP group when ep_size > 1."""
-        if self._workspace is not None:
-            self._workspace.close()
-            self._workspace = None
+        """Release this member; the workspace goes with the last member of its group. Collective over
+        the EP group when ep_size > 1: every rank closes in the same order, with no call in flight
+        (reference: hyper_multicore/modules/module.py:408-430)."""
+        if self._closed:
+            return
+        group = self._group
+        group.members.discard(id(self))
+        if not group.members and not group.closed:
+            if group.workspace is not None:
+                group.workspace.close()
+                group.workspace = None
+            group.closed = True
+        self._closed = True
 
     def debug_state(self) -> dict:
         """Workspace sizes and the last device status words (synchronises)."""
@@ -363,6 +478,14 @@ class MegaMoeExperts(torch.nn.Module):
         """Raise if a bounded device wait ran out or an index was rejected (synchronises)."""
         if self._status is not None:
             _lib.raise_on_status(self._status, "MegaMoeExperts")
+
+    @staticmethod
+    def _takes_part_in_autograd(hidden_states, topk_weights, expert_weights) -> bool:
+        try:
+            tensors = (hidden_states, topk_weights, *expert_weights)
+        except TypeError:
+            tensors = (hidden_states, topk_weights)
+        return torch.is_grad_enabled() and any(isinstance(t, torch.Tensor) and t.requires_grad for t in tensors)
 
     # ------------------------------------------------------------------ forward
     def forward(self, hidden_states: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor, *,
@@ -380,6 +503,8 @@ class MegaMoeExperts(torch.nn.Module):
             # exchange, so that no peer is left waiting (reference: module.py:474-495).
             weight_error = error
             hidden_flat = hidden_states.reshape(-1, self.hidden_size).contiguous()
+        if self._closed or self._group.closed:
+            raise RuntimeError("closed multicore modules cannot execute.")
         if torch.cuda.is_current_stream_capturing():
             raise RuntimeError("MegaMoe dynamic tokens and workspace growth do not support graph capture")
         device = hidden_flat.device
@@ -387,7 +512,8 @@ class MegaMoeExperts(torch.nn.Module):
             self._status = _lib.new_status(device)
         route = prepare_route(hidden_flat, topk_ids.contiguous(), num_experts=self.num_experts, top_k=self.top_k,
                               ep_size=self.ep_size, rank=self._rank, group=self._ep_group,
-                              invalid=weight_error is not None, status=self._status)
+                              invalid=weight_error is not None, status=self._status,
+                              autograd=self._takes_part_in_autograd(hidden_states, topk_weights, expert_weights))
         if weight_error is not None:
             raise weight_error
         if route.pending is None:

@@ -17,7 +17,7 @@ import torch.distributed as dist
 
 from ... import kernels
 
-_HEADER = 3  # [invalid, local tokens, reserved] ahead of the per-expert counts
+_HEADER = 3  # [invalid, local tokens, takes part in autograd] ahead of the per-expert counts
 _PINNED: dict = {}  # (device, experts) -> pinned int32 staging for single-rank validation
 
 
@@ -72,7 +72,8 @@ def validate_topk_inputs(hidden: torch.Tensor, topk_ids: torch.Tensor, topk_weig
 
 
 def prepare_route(hidden: torch.Tensor, topk_ids: torch.Tensor, *, num_experts: int, top_k: int, ep_size: int,
-                  rank: int, group: Any | None, invalid: bool = False, status=None) -> PreparedRoute:
+                  rank: int, group: Any | None, invalid: bool = False, status=None,
+                  autograd: bool = False) -> PreparedRoute:
     """Sort the routes, exchange counts, derive offsets. Collective when ep_size > 1."""
     device = hidden.device
     tokens = hidden.shape[0]
@@ -96,8 +97,16 @@ def prepare_route(hidden: torch.Tensor, topk_ids: torch.Tensor, *, num_experts: 
             offsets=offsets, routed_rows=routed, received_rows=routed, max_received_rows=routed,
             max_routed_rows=routed, pending=(event, pinned, num_experts, routed))
     payload = torch.empty(_HEADER + num_experts, dtype=torch.int32, device=device)
-    payload[:_HEADER] = torch.tensor([int(invalid), tokens, 0], dtype=torch.int32, device=device) \
-        if ep_size > 1 else 0
+    if ep_size > 1:
+        # header staged in pinned memory: a plain torch.tensor(..., device=...) copies synchronously
+        key = ("header", device)
+        stage = _PINNED.get(key)
+        if stage is None:
+            stage = _PINNED[key] = torch.empty(_HEADER, dtype=torch.int32).pin_memory()
+        stage[0], stage[1], stage[2] = int(invalid), tokens, int(autograd)
+        payload[:_HEADER].copy_(stage, non_blocking=True)
+    else:
+        payload[:_HEADER] = 0
     payload[_HEADER:] = counts
     if ep_size > 1:
         gathered = torch.empty(ep_size * (_HEADER + num_experts), dtype=torch.int32, device=device)
@@ -112,6 +121,10 @@ def prepare_route(hidden: torch.Tensor, topk_ids: torch.Tensor, *, num_experts: 
     if any(row[0] for row in host):
         bad = [r for r, row in enumerate(host) if row[0]]
         raise ValueError(f"MegaMoeExperts received invalid inputs on EP rank(s) {bad}; all ranks reject the call.")
+    if len({row[2] for row in host}) != 1:
+        # a rank that skips backward would leave its peers waiting in theirs
+        # (reference: _validate_dynamic_rows, hyper_multicore/modules/mega_moe/route.py:585-593)
+        raise RuntimeError("MegaMoe autograd participation differs across EP ranks")
     host_counts = [row[_HEADER:] for row in host]
     if sum(host_counts[rank]) != tokens * top_k:
         raise ValueError(

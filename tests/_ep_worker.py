@@ -133,6 +133,17 @@ def main():
         state = module.debug_state()
         assert state["ep"] == world and state["generation"] >= 10, state
         module.close()
+    # two serial layers on one peer-mapped workspace
+    shared = [MegaMoeExperts(hidden_size=hidden, intermediate_size=inter, num_experts=experts, top_k=top_k,
+                             ep_group=dist.group.WORLD) for _ in range(2)]
+    MegaMoeExperts.share_execution_resources(shared)
+    for index, layer in enumerate(shared + shared):
+        scenario(layer, rank, world, device, [64 + 32 * index] * world, hidden, inter, experts, top_k,
+                 seed=70 + index, layout="EIO")
+    assert shared[0]._workspace is shared[1]._workspace
+    shared[0].close()
+    assert shared[1]._workspace is not None
+    shared[1].close()
     # numerics options: clamped SwiGLU with the probabilities travelling with the rows (before FC2)
     from hyper_multicore_b200 import MegaMoeNumericsOptions
 

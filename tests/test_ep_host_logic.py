@@ -109,3 +109,37 @@ def test_two_rank_route_exchange_is_lossless():
             p.kill()
             messages.append("a rank did not finish")
     assert not messages and all(p.exitcode == 0 for p in procs), messages
+
+
+def test_share_execution_resources_validation():
+    """Host rules of workspace sharing (reference: hyper_multicore/modules/module.py:262-323)."""
+    from hyper_multicore_b200 import MegaMoeExperts, MegaMoeNumericsOptions
+
+    def layer(**extra):
+        return MegaMoeExperts(hidden_size=64, intermediate_size=64, num_experts=4, top_k=2, **extra)
+
+    a, b, c = layer(), layer(numerics_options=MegaMoeNumericsOptions()), layer()
+    MegaMoeExperts.share_execution_resources([a, b, c])  # omitted and explicit default options are compatible
+    assert a._group is b._group is c._group and len(a._group.members) == 3 and a._group.shared
+    MegaMoeExperts.share_execution_resources([a, b])  # already grouped: nothing to do
+    with pytest.raises(ValueError, match="at least one module"):
+        MegaMoeExperts.share_execution_resources([])
+    with pytest.raises(ValueError, match="duplicate"):
+        MegaMoeExperts.share_execution_resources([a, a])
+    with pytest.raises(TypeError, match="must be MegaMoeExperts instances"):
+        MegaMoeExperts.share_execution_resources([a, object()])
+    other = layer(numerics_options=MegaMoeNumericsOptions(swiglu_limit=7.0))
+    with pytest.raises(ValueError, match="identical configuration"):
+        MegaMoeExperts.share_execution_resources([layer(), other])
+    with pytest.raises(RuntimeError, match="before first use or previous grouping"):
+        MegaMoeExperts.share_execution_resources([layer(), a])
+    # the workspace goes with the last member
+    a._group.workspace = sentinel = type("W", (), {"closed": False, "close": lambda self: setattr(self, "closed", True)})()
+    a.close()
+    b.close()
+    assert not sentinel.closed and not c._group.closed
+    c.close()
+    c.close()  # idempotent
+    assert sentinel.closed and c._group.closed and c._group.workspace is None
+    with pytest.raises(RuntimeError, match="closed multicore modules cannot share"):
+        MegaMoeExperts.share_execution_resources([layer(), a])

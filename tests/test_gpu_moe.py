@@ -150,6 +150,39 @@ def test_repeated_calls_and_activation_checkpoint(cuda_device):
     module.check_status()
 
 
+def test_shared_execution_resources(cuda_device):
+    """Two layers on one workspace, both forwards before either backward; a closed member cannot run and
+    the workspace goes with the last member (reference: docs/mega_moe.md:329-366)."""
+    from hyper_multicore_b200 import MegaMoeExperts
+
+    dev = cuda_device
+    cases = [make_case(120, 128, 64, 4, 2, seed=21), make_case(77, 128, 64, 4, 2, seed=22)]
+    layers = [MegaMoeExperts(hidden_size=128, intermediate_size=64, num_experts=4, top_k=2) for _ in cases]
+    MegaMoeExperts.share_execution_resources(layers)
+    state = []
+    for layer, case in zip(layers, cases):
+        x = case["hidden"].to(dev).requires_grad_(True)
+        p = case["topk_weights"].to(dev).requires_grad_(True)
+        w1 = case["w1"].to(dev).requires_grad_(True)
+        w2 = case["w2"].to(dev).requires_grad_(True)
+        out = layer(x, case["topk_ids"].to(dev), p, expert_weights=(w1, w2))
+        state.append((out, x, p, w1, w2))
+    assert layers[0]._workspace is layers[1]._workspace and layers[0]._workspace is not None
+    for (out, x, p, w1, w2), case in reversed(list(zip(state, cases))):
+        out.backward(case["grad_output"].to(dev))
+        ref = omoe.experts_forward_backward(case["hidden"], case["topk_ids"], case["topk_weights"], case["w1"],
+                                            case["w2"], case["grad_output"])
+        check({"output": out.detach().cpu(), "grad_hidden": x.grad.cpu(), "grad_probs": p.grad.cpu(),
+               "grad_w1": w1.grad.cpu(), "grad_w2": w2.grad.cpu()}, ref)
+    layers[0].check_status()
+    layers[0].close()
+    assert layers[1]._workspace is not None
+    with pytest.raises(RuntimeError, match="closed multicore modules cannot execute"):
+        layers[0](state[0][1], cases[0]["topk_ids"].to(dev), state[0][2], expert_weights=(state[0][3], state[0][4]))
+    layers[1].close()
+    assert layers[1]._group.closed
+
+
 def test_validation_errors(cuda_device):
     from hyper_multicore_b200 import MegaMoeExperts
 
