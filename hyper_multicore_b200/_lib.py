@@ -39,6 +39,16 @@ class HmcError(RuntimeError):
     """A check inside the native library failed."""
 
 
+class GemmCombine(ctypes.Structure):
+    """Mirror of ``hmc_gemm_combine``."""
+
+    _fields_ = [
+        ("segment_start", c_void_p), ("combine_target_off", c_void_p),
+        ("peer_buffers", c_void_p), ("peer_ctrl", c_void_p),
+        ("ep", c_int64), ("local_experts", c_int64), ("target_rows_limit", c_int64),
+    ]
+
+
 class GroupedGemmArgs(ctypes.Structure):
     """Mirror of ``hmc_grouped_gemm_args``."""
 
@@ -67,6 +77,7 @@ class GroupedGemmArgs(ctypes.Structure):
         ("reserved", c_int32),
         ("row_probs", c_void_p),
         ("row_dot", c_void_p),
+        ("combine", c_void_p),
     ]
 
 
@@ -207,6 +218,7 @@ SIGNATURES: dict[str, tuple] = {
     "hmc_mega_moe_transport_version": (_I, []),
     "hmc_worker_queue_layout_version": (_I, []),
     "hmc_grouped_gemm": (_I, [ctypes.POINTER(GroupedGemmArgs), _P]),
+    "hmc_grouped_gemm_combine_units": (_L, [_L]),
     "hmc_mx_gemm": (_I, [ctypes.POINTER(MxGemmArgs), _P]),
     "hmc_mx_quant": (_I, [ctypes.POINTER(MxQuantArgs), _P]),
     "hmc_mx_quant_weight": (_I, [_P, _L, _L, _L, _P, _P, _P, _P, _P]),

@@ -29,6 +29,17 @@ constexpr uint32_t SWIZZLE_128B = 2;
 
 constexpr uint64_t PIPE_BUDGET_NS = 4ull * 1000 * 1000 * 1000;  // intra-kernel barrier waits
 
+// Result rows that leave the epilogue for their source ranks (fused combine).
+struct CombineFuse {
+  const long long* segment_start;       // [local_experts * ep] first row of (local expert, source)
+  const long long* combine_target_off;  // [ep * local_experts]
+  void* peer_data[HMC_MAX_EP];          // routed buffer of every rank
+  int* peer_ctrl[HMC_MAX_EP];           // control block of every rank
+  long long target_rows_limit;
+  int ep;
+  int local_experts;
+};
+
 struct Params {
   int mode;      // HMC_GEMM_RAGGED_M / HMC_GEMM_RAGGED_K
   int epilogue;  // HMC_EPI_*
@@ -48,6 +59,8 @@ struct Params {
   unsigned long long ready_budget_ns;
   int* status;
   int tma_store;           // RAGGED_M plain stores: full tiles leave through shared memory + TMA
+  int combine_enabled;     // STORE_BF16 rows go to `combine` destinations instead of c
+  CombineFuse combine;
   int swiglu_clamp;        // HMC_CLAMP_*
   float swiglu_limit;
   const float* row_probs;  // optional per-row routing probability (weighting before FC2)

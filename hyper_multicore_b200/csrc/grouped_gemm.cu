@@ -335,6 +335,67 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           }
           store_pending = true;
         }
+      } else if (p.combine_enabled) {
+        // Fused combine: the rows go to the routed buffers of their source ranks. Each lane finds the
+        // destination of its own row; the tile is staged in shared memory so that every store
+        // instruction writes whole 128-byte pieces of four rows (NVLink-friendly), not 16 bytes of
+        // thirty-two rows.
+        const CombineFuse& cf = p.combine;
+        unsigned long long dst_bits = 0;
+        int source = -1;
+        if (row_ok) {
+          const long long* seg = cf.segment_start + static_cast<long long>(t.group) * cf.ep;
+          int s = 0;
+          for (int q = 1; q < cf.ep; ++q)
+            if (seg[q] <= out_row) s = q;
+          const long long dest = cf.combine_target_off[s * cf.local_experts + t.group] + (out_row - seg[s]);
+          if (dest >= 0 && dest < cf.target_rows_limit) {
+            source = s;
+            dst_bits = reinterpret_cast<unsigned long long>(static_cast<__nv_bfloat16*>(cf.peer_data[s]) +
+                                                            dest * p.ldc + col_base);
+          } else {
+            report_status(p.status, HMC_STATUS_BAD_INDEX, static_cast<int>(out_row), s, static_cast<int>(dest));
+          }
+        }
+        const int sub = lane >> 3;
+        const int piece = lane & 7;
+#pragma unroll 1
+        for (int c = c_lo; c < c_hi; c += 64) {
+          if (col_base + c >= p.n) break;
+          uint32_t v[32];
+          uint32_t w[32];
+          tmem_ld_32x32(taddr + c, v);
+          tmem_ld_32x32(taddr + c + 32, w);
+          tmem_ld_wait();
+          uint8_t* row_base = my_stage + lane * 128;
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            const uint32_t* src = q < 4 ? v + 8 * q : w + 8 * (q - 4);
+            uint4 o;
+            o.x = pack_bf16x2(__uint_as_float(src[0]), __uint_as_float(src[1]));
+            o.y = pack_bf16x2(__uint_as_float(src[2]), __uint_as_float(src[3]));
+            o.z = pack_bf16x2(__uint_as_float(src[4]), __uint_as_float(src[5]));
+            o.w = pack_bf16x2(__uint_as_float(src[6]), __uint_as_float(src[7]));
+            *reinterpret_cast<uint4*>(row_base + ((q ^ (lane & 7)) << 4)) = o;
+          }
+          __syncwarp();
+          const bool piece_ok = col_base + c + piece * 8 < p.n;
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            const int r = i + sub;
+            const unsigned long long base = __shfl_sync(0xffffffffu, dst_bits, r);
+            if (base != 0 && piece_ok) {
+              const uint4 val = *reinterpret_cast<const uint4*>(my_stage + r * 128 + ((piece ^ (r & 7)) << 4));
+              st_16(reinterpret_cast<uint8_t*>(base) + c * 2 + piece * 16, val);
+            }
+          }
+          __syncwarp();
+        }
+        // One release-add per destination per warp: the warp barrier orders every lane's stores
+        // before the leader's release, which publishes them to the acquiring rank.
+        const unsigned same = __match_any_sync(0xffffffffu, source);
+        if (source >= 0 && lane == __ffs(same) - 1)
+          red_release_sys_add(cf.peer_ctrl[source] + HMC_CTRL_COMBINE, __popc(same));
       } else {
         epilogue_rows(p, taddr, out_row, row_ok, col_base, half);
       }
@@ -419,6 +480,11 @@ int launch_grouped_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const
 
 }  // namespace hmc
 
+extern "C" int64_t hmc_grouped_gemm_combine_units(int64_t n) {
+  // every (32-row, half-tile) piece of every 256-column tile reports its rows once
+  return 2 * ((n + hmc::gemm::BN - 1) / hmc::gemm::BN);
+}
+
 extern "C" int hmc_grouped_gemm(const hmc_grouped_gemm_args* args, void* stream_ptr) {
   using namespace hmc;
   HMC_REQUIRE(args != nullptr, HMC_ERR_INVALID, "hmc_grouped_gemm: null args");
@@ -433,7 +499,8 @@ extern "C" int hmc_grouped_gemm(const hmc_grouped_gemm_args* args, void* stream_
               a.groups, (long long)a.n, (long long)a.rows);
   HMC_REQUIRE(a.rows < (1ll << 31) && a.n < (1ll << 31) && a.k < (1ll << 31) && a.m < (1ll << 31),
               HMC_ERR_INVALID, "hmc_grouped_gemm: extents must fit in int32");
-  HMC_REQUIRE(a.a && a.b && a.c && a.group_ends, HMC_ERR_INVALID, "hmc_grouped_gemm: null tensor pointer");
+  HMC_REQUIRE(a.a && a.b && (a.c || a.combine) && a.group_ends, HMC_ERR_INVALID,
+              "hmc_grouped_gemm: null tensor pointer");
   HMC_REQUIRE(aligned16(a.a) && aligned16(a.b) && aligned16(a.c), HMC_ERR_INVALID,
               "hmc_grouped_gemm: tensors must be 16-byte aligned");
   HMC_REQUIRE(a.n % 8 == 0, HMC_ERR_INVALID, "hmc_grouped_gemm: n (%lld) must be a multiple of 8",
@@ -466,6 +533,28 @@ extern "C" int hmc_grouped_gemm(const hmc_grouped_gemm_args* args, void* stream_
     p.swiglu_limit = a.swiglu_limit;
     p.row_probs = a.row_probs;
     p.row_dot = a.row_dot;
+  }
+  if (a.combine != nullptr) {
+    const hmc_gemm_combine& cb = *a.combine;
+    HMC_REQUIRE(a.mode == HMC_GEMM_RAGGED_M && a.epilogue == HMC_EPI_STORE_BF16, HMC_ERR_INVALID,
+                "hmc_grouped_gemm: the fused combine belongs to RAGGED_M GEMMs with BF16 stores");
+    HMC_REQUIRE(cb.ep >= 1 && cb.ep <= HMC_MAX_EP && cb.local_experts == a.groups, HMC_ERR_INVALID,
+                "hmc_grouped_gemm: combine needs 1 <= ep <= %d and local_experts == groups", HMC_MAX_EP);
+    HMC_REQUIRE(cb.segment_start && cb.combine_target_off && cb.peer_buffers && cb.peer_ctrl && cb.target_rows_limit > 0,
+                HMC_ERR_INVALID, "hmc_grouped_gemm: null combine table");
+    HMC_REQUIRE(a.n % 8 == 0, HMC_ERR_INVALID, "hmc_grouped_gemm: combined rows must be multiples of 16 bytes");
+    for (int r = 0; r < cb.ep; ++r) {
+      HMC_REQUIRE(cb.peer_buffers[r] != nullptr && cb.peer_ctrl[r] != nullptr && aligned16(cb.peer_buffers[r]),
+                  HMC_ERR_INVALID, "hmc_grouped_gemm: peer %d has no 16-byte aligned routed buffer / control block", r);
+      p.combine.peer_data[r] = cb.peer_buffers[r];
+      p.combine.peer_ctrl[r] = static_cast<int*>(cb.peer_ctrl[r]);
+    }
+    p.combine.segment_start = reinterpret_cast<const long long*>(cb.segment_start);
+    p.combine.combine_target_off = reinterpret_cast<const long long*>(cb.combine_target_off);
+    p.combine.target_rows_limit = cb.target_rows_limit;
+    p.combine.ep = static_cast<int>(cb.ep);
+    p.combine.local_experts = static_cast<int>(cb.local_experts);
+    p.combine_enabled = 1;
   }
 
   CUtensorMap ta, tb, tc;
@@ -538,7 +627,7 @@ extern "C" int hmc_grouped_gemm(const hmc_grouped_gemm_args* args, void* stream_
     tc = ta;  // unused by the kernel unless the plain-store path below is on
     const bool f32 = a.epilogue == HMC_EPI_STORE_F32;
     const bool plain = f32 || a.epilogue == HMC_EPI_STORE_BF16;
-    if (plain && (a.n * (f32 ? 4 : 2)) % 16 == 0 && aligned16(a.c)) {
+    if (plain && !p.combine_enabled && (a.n * (f32 ? 4 : 2)) % 16 == 0 && aligned16(a.c)) {
       // C = [1, rows, n] seen through the same 32-row x 128-byte boxes as the weight gradients
       cuuint64_t dims[3] = {static_cast<cuuint64_t>(a.n), static_cast<cuuint64_t>(a.rows), 1};
       cuuint32_t box[3] = {f32 ? 32u : 64u, 32, 1};
@@ -556,7 +645,7 @@ extern "C" int hmc_grouped_gemm(const hmc_grouped_gemm_args* args, void* stream_
   }
   // CTA pairs work on 256-row tiles: worth it once the average group fills most of one
   const bool use_pairs = a.tile_mode == HMC_TILE_PAIR || (a.tile_mode == HMC_TILE_AUTO && a.rows >= 192ll * a.groups);
-  if (use_pairs && a.k % 8 == 0 && sm_count() >= 2)
+  if (use_pairs && !p.combine_enabled && a.k % 8 == 0 && sm_count() >= 2)
     return launch_grouped_gemm_pair(ta, tb, p, a.b_major, grid, stream);
   if (a.b_major == HMC_MAJOR_MN) return launch<HMC_MAJOR_K, HMC_MAJOR_MN>(ta, tb, tc, p, grid, stream);
   return launch<HMC_MAJOR_K, HMC_MAJOR_K>(ta, tb, tc, p, grid, stream);

@@ -49,17 +49,23 @@ def grouped_gemm(
     swiglu_limit: float = 0.0,
     row_probs: torch.Tensor | None = None,
     row_dot: torch.Tensor | None = None,
+    combine: dict | None = None,
 ) -> None:
     """Launch the tcgen05 grouped GEMM.
 
     ``swiglu_clamp`` / ``swiglu_limit`` select the clamped SwiGLU of the SwiGLU epilogues;
     ``row_probs`` (float32 [rows]) weights the activation before FC2 and, in the SwiGLU-grad
     epilogue, ``row_dot`` (float32 [rows], zeroed by the caller) receives the probability gradient.
+    ``combine`` (RAGGED_M, BF16 stores) sends the result rows from the epilogue to the routed buffers of
+    their source ranks: keys segment_start, combine_target_off (device int64), peer_buffers, peer_ctrl
+    (ctypes pointer arrays), ep, local_experts, target_rows_limit; ``c`` may then be None.
 
     RAGGED_M: ``a`` [rows, k]; ``b`` [groups, k, n_cols] (MN) or [groups, n_cols, k] (K); ``c`` [rows, *].
     RAGGED_K: ``a`` [rows, m]; ``b`` [rows, n]; ``c`` [groups, m, n] BF16 or FP32.
     """
     device = _require_cuda(a, b, c, group_ends, aux, ready_counters, status, row_probs, row_dot)
+    if c is None and combine is None:
+        raise ValueError("grouped_gemm needs an output tensor unless its rows are combined to their sources")
     for name, plane in (("row_probs", row_probs), ("row_dot", row_dot)):
         if plane is not None and (plane.dtype != torch.float32 or not plane.is_contiguous() or plane.numel() < a.shape[0]):
             raise ValueError(f"{name} must be a contiguous float32 tensor with one entry per row")
@@ -85,7 +91,7 @@ def grouped_gemm(
         args.k = 0
     args.a = a.data_ptr()
     args.b = b.data_ptr()
-    args.c = c.data_ptr()
+    args.c = _lib.ptr(c)
     args.aux = _lib.ptr(aux)
     args.group_ends = group_ends.data_ptr()
     args.ready_counters = _lib.ptr(ready_counters)
@@ -95,9 +101,24 @@ def grouped_gemm(
     args.swiglu_limit = swiglu_limit
     args.row_probs = _lib.ptr(row_probs)
     args.row_dot = _lib.ptr(row_dot)
+    fused = None
+    if combine is not None:
+        fused = _lib.GemmCombine()
+        fused.segment_start = combine["segment_start"].data_ptr()
+        fused.combine_target_off = combine["combine_target_off"].data_ptr()
+        fused.peer_buffers = ctypes.cast(combine["peer_buffers"], ctypes.c_void_p)
+        fused.peer_ctrl = ctypes.cast(combine["peer_ctrl"], ctypes.c_void_p)
+        fused.ep, fused.local_experts = combine["ep"], combine["local_experts"]
+        fused.target_rows_limit = combine["target_rows_limit"]
+        args.combine = ctypes.cast(ctypes.pointer(fused), ctypes.c_void_p)
     _count("hmc_grouped_gemm")
     with torch.cuda.device(device):
         _lib.check(_lib.load().hmc_grouped_gemm(ctypes.byref(args), _lib.stream_ptr(device)))
+
+
+def grouped_gemm_combine_units(n: int) -> int:
+    """Counter increments per result row of a fused-combine GEMM with ``n`` output columns."""
+    return int(_lib.load().hmc_grouped_gemm_combine_units(n))
 
 
 LAUNCH_COUNT = 0  # kernels of this library launched so far in this process

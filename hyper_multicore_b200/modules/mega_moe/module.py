@@ -545,6 +545,14 @@ class MegaMoeExperts(torch.nn.Module):
         clamp = _lib.HMC_CLAMP_AFTER_SILU if self._numerics.clamp_after_silu else _lib.HMC_CLAMP_BEFORE_SILU
         return {"swiglu_clamp": clamp, "swiglu_limit": float(limit)}
 
+    def _fused_combine(self, workspace, off, peer_routed, peer_ctrl) -> dict | None:
+        """Arguments that make a GEMM's epilogue return its rows to their source ranks."""
+        if self.ep_size == 1:
+            return None
+        return {"segment_start": off["recv_segment_start"], "combine_target_off": off["combine_target_off"],
+                "peer_buffers": peer_routed, "peer_ctrl": peer_ctrl, "ep": self.ep_size,
+                "local_experts": self.local_experts, "target_rows_limit": workspace.routed_rows}
+
     def _local_rows(self, rows: int, device: torch.device):
         """Single-rank receive buffer: [rows, H] BF16 followed by one float per row."""
         row_bytes = self.hidden_size * 2
@@ -580,7 +588,7 @@ class MegaMoeExperts(torch.nn.Module):
         rows = max(received, 1)
         up_proj = torch.empty(rows, 2 * inter, **bf16)
         activation = torch.empty(rows, inter, **bf16)
-        down_proj = torch.empty(rows, hid, **bf16)
+        down_proj = torch.empty(rows, hid, **bf16) if self.ep_size == 1 else None
         x_recv = expert_buffer[:rows]
         row_probs = expert_values[:rows] if before_fc2 else None
         arrival = workspace.ctrl[_lib.HMC_CTRL_ARRIVAL:_lib.HMC_CTRL_ARRIVAL + self.local_experts]
@@ -589,19 +597,18 @@ class MegaMoeExperts(torch.nn.Module):
                                  b_major=b_major, epilogue=kernels.HMC_EPI_SWIGLU, aux=activation,
                                  ready_counters=arrival, ready_budget_ns=self._wait_budget_ns, status=self._status,
                                  row_probs=row_probs, **self._swiglu_options())
-            kernels.grouped_gemm(activation, w2, down_proj, off["group_list"], mode=kernels.HMC_GEMM_RAGGED_M,
-                                 b_major=b_major, status=self._status)
+            kernels.grouped_gemm(activation, w2, None if self.ep_size > 1 else down_proj, off["group_list"],
+                                 mode=kernels.HMC_GEMM_RAGGED_M, b_major=b_major, status=self._status,
+                                 combine=self._fused_combine(workspace, off, peer_routed, peer_ctrl))
         if self.ep_size == 1:
             routed_out = down_proj
             saved_received = x_recv
             saved_probs = row_probs
         else:
-            kernels.ep_combine(down_proj, off["recv_segment_start"], off["combine_target_off"], rows=received,
-                               ep=self.ep_size, local_experts=self.local_experts,
-                               target_rows_limit=workspace.routed_rows, peer_buffers=peer_routed,
-                               peer_ctrl=peer_ctrl, local_ctrl=workspace.ctrl, generation=generation,
-                               status=self._status, budget_ns=self._wait_budget_ns)
-            kernels.ep_wait(workspace.ctrl[_lib.HMC_CTRL_COMBINE:], routed_rows, status=self._status, budget_ns=self._wait_budget_ns)
+            # The result rows left the GEMM2 epilogue for their sources; wait for this rank's own.
+            kernels.ep_wait(workspace.ctrl[_lib.HMC_CTRL_COMBINE:],
+                            routed_rows * kernels.grouped_gemm_combine_units(hid), status=self._status,
+                            budget_ns=self._wait_budget_ns)
             # Owned copies: the symmetric buffers are rewritten by the next call on any rank
             # (reference: autograd.py:655-663 saves a dispatch copy and clones the combine output).
             routed_out = workspace.routed_buffer[:max(routed_rows, 1)].clone()
@@ -680,7 +687,10 @@ class MegaMoeExperts(torch.nn.Module):
                 dy_recv = expert_buffer[:rows]
                 arrival = workspace.ctrl[_lib.HMC_CTRL_ARRIVAL:_lib.HMC_CTRL_ARRIVAL + self.local_experts]
         grad_up = torch.empty(rows, 2 * inter, **bf16)
-        grad_x_rows = torch.empty(rows, hid, **bf16)
+        # With the probability gradient travelling back (before FC2) the rows return through the combine
+        # kernel, which carries the float plane; otherwise they leave from the dX GEMM's epilogue.
+        fused = None if (self.ep_size == 1 or before_fc2) else self._fused_combine(workspace, off, peer_routed, peer_ctrl)
+        grad_x_rows = torch.empty(rows, hid, **bf16) if fused is None else None
         f32_partials = self._numerics.partial_weight_grad_dtype == "float32"
         wdtype = torch.float32 if f32_partials else torch.bfloat16
         wepi = kernels.HMC_EPI_STORE_F32 if f32_partials else kernels.HMC_EPI_STORE_BF16
@@ -694,7 +704,7 @@ class MegaMoeExperts(torch.nn.Module):
                                  ready_counters=arrival, ready_budget_ns=self._wait_budget_ns, status=self._status,
                                  row_probs=row_probs, row_dot=row_dot, **self._swiglu_options())
             kernels.grouped_gemm(grad_up, w1, grad_x_rows, off["group_list"], mode=kernels.HMC_GEMM_RAGGED_M,
-                                 b_major=bt_major, status=self._status)
+                                 b_major=bt_major, status=self._status, combine=fused)
         if grad_w2 is not None:
             # The arrival wait of the dA GEMM above orders this kernel after the rows have landed.
             # With probabilities before FC2, `activation` is the weighted input FC2 actually saw.
@@ -707,13 +717,18 @@ class MegaMoeExperts(torch.nn.Module):
                                  status=self._status)
         if self.ep_size == 1:
             returned, returned_dot = grad_x_rows, row_dot
+        elif fused is not None:
+            kernels.ep_wait(workspace.ctrl[_lib.HMC_CTRL_COMBINE:],
+                            routed_rows * kernels.grouped_gemm_combine_units(hid), status=self._status,
+                            budget_ns=self._wait_budget_ns)
+            returned, returned_dot = workspace.routed_buffer, None
         else:
-            returning = dict(result_values=row_dot, value_plane_offset=workspace.routed_plane_offset) if before_fc2 else {}
             kernels.ep_combine(grad_x_rows, off["recv_segment_start"], off["combine_target_off"], rows=received,
                                ep=self.ep_size, local_experts=self.local_experts,
                                target_rows_limit=workspace.routed_rows, peer_buffers=peer_routed,
                                peer_ctrl=peer_ctrl, local_ctrl=workspace.ctrl, generation=generation,
-                               status=self._status, budget_ns=self._wait_budget_ns, **returning)
+                               status=self._status, budget_ns=self._wait_budget_ns, result_values=row_dot,
+                               value_plane_offset=workspace.routed_plane_offset)
             kernels.ep_wait(workspace.ctrl[_lib.HMC_CTRL_COMBINE:], routed_rows, status=self._status, budget_ns=self._wait_budget_ns)
             returned, returned_dot = workspace.routed_buffer, workspace.routed_values
         grad_hidden = torch.empty(tokens, hid, **bf16)

@@ -69,6 +69,24 @@ int hmc_worker_queue_layout_version(void);
 #define HMC_CLAMP_BEFORE_SILU 1 /* silu(min(g, L)) * clamp(u, -L, L) */
 #define HMC_CLAMP_AFTER_SILU 2  /* min(silu(g), L) * clamp(u, -L, L) */
 
+/* Optional: the result rows of a RAGGED_M / STORE_BF16 GEMM leave the epilogue straight for the routed
+ * buffers of their source ranks (the reference's combine stage, tasks/alltoall.py:90-157 and
+ * worker_kernel.cpp:301-366, fused into the GEMM that produces the rows). Row r of local expert g came
+ * from source s = last s with segment_start[g * ep + s] <= r and goes to row
+ * combine_target_off[s * local_experts + g] + (r - segment_start[g * ep + s]) of peer_buffers[s].
+ * Every (32-row, half-tile) piece adds its row count to the destination's HMC_CTRL_COMBINE counter with
+ * release semantics, so a source has all its rows once the counter reaches
+ * rows * hmc_grouped_gemm_combine_units(n). */
+typedef struct hmc_gemm_combine {
+  const int64_t* segment_start;      /* device [local_experts * ep], from hmc_route_offsets */
+  const int64_t* combine_target_off; /* device [ep * local_experts] */
+  void* const* peer_buffers;         /* host array [ep]: routed buffer of every rank, as mapped here */
+  void* const* peer_ctrl;            /* host array [ep]: control block of every rank */
+  int64_t ep;
+  int64_t local_experts;             /* must equal the GEMM's groups */
+  int64_t target_rows_limit;
+} hmc_gemm_combine;
+
 typedef struct hmc_grouped_gemm_args {
   int32_t mode;
   int32_t a_major; /* RAGGED_M: HMC_MAJOR_K. RAGGED_K: HMC_MAJOR_MN */
@@ -99,9 +117,12 @@ typedef struct hmc_grouped_gemm_args {
                              gradient of that weighted activation; dAct = bf16(fp32(bf16(acc)) * p) */
   float* row_dot;         /* SWIGLU_GRAD with row_probs: row_dot[row] += sum_col bf16(act) * bf16(acc), the
                              probability gradient; zeroed by the caller */
+  const hmc_gemm_combine* combine; /* optional, RAGGED_M + STORE_BF16: c is ignored, rows go to their sources */
 } hmc_grouped_gemm_args;
 
 int hmc_grouped_gemm(const hmc_grouped_gemm_args* args, void* stream);
+/* Counter increments per result row of a fused-combine GEMM with n output columns. */
+int64_t hmc_grouped_gemm_combine_units(int64_t n);
 
 /* ------------------------------------------------------------------------------------------
  * MXFP8 expert GEMM (tcgen05 kind::mxf8f6f4.block_scale) and its quantisers.

@@ -49,4 +49,4 @@ def test_argument_checks_fail_without_touching_a_device():
 
 def test_struct_sizes_match_the_header_layout():
     # 8 int32 + 4 int64 + 6 pointers + uint64 + pointer
-    assert ctypes.sizeof(_lib.GroupedGemmArgs) == 8 * 4 + 4 * 8 + 6 * 8 + 8 + 8 + 2 * 4 + 2 * 8
+    assert ctypes.sizeof(_lib.GroupedGemmArgs) == 8 * 4 + 4 * 8 + 6 * 8 + 8 + 8 + 2 * 4 + 3 * 8
