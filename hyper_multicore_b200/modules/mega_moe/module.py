@@ -553,6 +553,12 @@ class MegaMoeExperts(torch.nn.Module):
                 "peer_buffers": peer_routed, "peer_ctrl": peer_ctrl, "ep": self.ep_size,
                 "local_experts": self.local_experts, "target_rows_limit": workspace.routed_rows}
 
+    def _copy_stream(self, device: torch.device) -> torch.cuda.Stream:
+        stream = getattr(self, "_side_stream", None)
+        if stream is None or stream.device != device:
+            stream = self._side_stream = torch.cuda.Stream(device=device)
+        return stream
+
     def _local_rows(self, rows: int, device: torch.device):
         """Single-rank receive buffer: [rows, H] BF16 followed by one float per row."""
         row_bytes = self.hidden_size * 2
@@ -592,11 +598,19 @@ class MegaMoeExperts(torch.nn.Module):
         x_recv = expert_buffer[:rows]
         row_probs = expert_values[:rows] if before_fc2 else None
         arrival = workspace.ctrl[_lib.HMC_CTRL_ARRIVAL:_lib.HMC_CTRL_ARRIVAL + self.local_experts]
+        saved_received = torch.empty_like(x_recv) if self.ep_size > 1 else None
         if received > 0:
             kernels.grouped_gemm(x_recv, w1, up_proj, off["group_list"], mode=kernels.HMC_GEMM_RAGGED_M,
                                  b_major=b_major, epilogue=kernels.HMC_EPI_SWIGLU, aux=activation,
                                  ready_counters=arrival, ready_budget_ns=self._wait_budget_ns, status=self._status,
                                  row_probs=row_probs, **self._swiglu_options())
+            if self.ep_size > 1:
+                # GEMM1 has waited for every expert's rows: the owned copy of the received rows (the
+                # symmetric buffer is rewritten by the next call) runs on a side stream beside GEMM2.
+                side = self._copy_stream(device)
+                side.wait_stream(torch.cuda.current_stream(device))
+                with torch.cuda.stream(side):
+                    saved_received.copy_(x_recv)
             kernels.grouped_gemm(activation, w2, None if self.ep_size > 1 else down_proj, off["group_list"],
                                  mode=kernels.HMC_GEMM_RAGGED_M, b_major=b_major, status=self._status,
                                  combine=self._fused_combine(workspace, off, peer_routed, peer_ctrl))
@@ -611,20 +625,32 @@ class MegaMoeExperts(torch.nn.Module):
                             budget_ns=self._wait_budget_ns)
             # Owned copies: the symmetric buffers are rewritten by the next call on any rank
             # (reference: autograd.py:655-663 saves a dispatch copy and clones the combine output).
-            routed_out = workspace.routed_buffer[:max(routed_rows, 1)].clone()
-            saved_received = x_recv.clone()
-            saved_probs = row_probs.clone() if before_fc2 else None
+            # They are made on a side stream, beside the K-sum below; this stream joins it before
+            # the call returns.
+            live_routed = workspace.routed_buffer[:max(routed_rows, 1)]
+            routed_out = torch.empty_like(live_routed)
+            saved_probs = torch.empty_like(row_probs) if before_fc2 else None
+            main = torch.cuda.current_stream(device)
+            side = self._copy_stream(device)
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                routed_out.copy_(live_routed)
+                if before_fc2:
+                    saved_probs.copy_(row_probs)
         out = torch.empty(hidden.shape[0], hid, **bf16)
+        live = routed_out if self.ep_size == 1 else live_routed
         if before_fc2:
             # The rows are already weighted: the Top-K rows of a token are summed as they are
             # (reference: _restore_unweighted_output, backends/bf16/autograd.py:133-135).
-            kernels.moe_token_permute_grad(routed_out, route.mapping, hidden.shape[0], self.top_k, out,
+            kernels.moe_token_permute_grad(live, route.mapping, hidden.shape[0], self.top_k, out,
                                            status=self._status)
             saved_last = saved_probs if saved_probs is not None else torch.empty(0, device=device)
         else:
-            kernels.moe_unpermute(routed_out, route.mapping, probs, hidden.shape[0], self.top_k, out,
+            kernels.moe_unpermute(live, route.mapping, probs, hidden.shape[0], self.top_k, out,
                                   status=self._status)
             saved_last = routed_out
+        if self.ep_size > 1:
+            torch.cuda.current_stream(device).wait_stream(self._copy_stream(device))
         return out, (saved_received, up_proj, activation, saved_last)
 
     def _run_backward(self, grad_output, hidden, probs, w1, w2, received_x, up_proj, activation, saved_last,
