@@ -246,7 +246,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     const int c_lo = half * (BN / 2);
     const int c_hi = c_lo + BN / 2;
     uint8_t* my_stage = store_stage + (warp - 2) * STORE_STAGE_BYTES;
-    bool store_pending = false;
+    unsigned stores_issued = 0;
     const int row_in_tile = quarter * 32 + lane;
     for (long long idx = blockIdx.x; ok && walker.get(idx, t); idx += gridDim.x) {
       const int kiters = k_iterations(p, t);
@@ -291,49 +291,57 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       const bool full_rows = p.tma_store && t.row0 + static_cast<long long>(t.m_idx + 1) * BM <= t.row1;
       if (p.mode == HMC_GEMM_RAGGED_K || full_rows) {
         // Weight-gradient tiles are regular [m, n] grids per group, so they leave through shared
-        // memory and TMA stores (full 128-byte lines, clipped at the m and n edges by the tensor
-        // map). Each warp stages a 32-row x 128-byte box: 64 BF16 or 32 FP32 columns per store.
+        // memory and TMA stores (clipped at the m and n edges by the tensor map), 32 columns per box.
+        // FP32 boxes are 32 columns x 128 bytes in one 4 KiB stage. BF16 boxes are 32 columns x 64 bytes:
+        // the stage holds two of them, so the store of one box overlaps the packing of the next.
         const bool f32 = p.epilogue == HMC_EPI_STORE_F32;
-        const int step = f32 ? 32 : 64;
         const bool ragged_k = p.mode == HMC_GEMM_RAGGED_K;
         const int m0 = (ragged_k ? t.m_idx * BM : static_cast<int>(t.row0) + t.m_idx * BM) + quarter * 32;
         const int plane = ragged_k ? t.group : 0;
 #pragma unroll 1
-        for (int c = c_lo; c < c_hi; c += step) {
+        for (int c = c_lo; c < c_hi; c += 32) {
           if (col_base + c >= p.n) break;
           uint32_t v[32];
-          uint32_t w[32];
           tmem_ld_32x32(taddr + c, v);
-          if (!f32) tmem_ld_32x32(taddr + c + 32, w);
           tmem_ld_wait();
-          if (store_pending) {  // the previous box must have been read out of the stage
-            if (lane == 0) bulk_wait_read_all();
-            __syncwarp();
-          }
-          // 16-byte chunk q of row `lane` goes to chunk q ^ (lane & 7): the 128-byte swizzle the
-          // tensor map expects, which also spreads a warp's stores over all banks.
-          uint8_t* row_base = my_stage + lane * 128;
-#pragma unroll
-          for (int q = 0; q < 8; ++q) {
-            uint4 o;
-            if (f32) {
-              o = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-            } else {
-              const uint32_t* src = q < 4 ? v + 8 * q : w + 8 * (q - 4);
-              o.x = pack_bf16x2(__uint_as_float(src[0]), __uint_as_float(src[1]));
-              o.y = pack_bf16x2(__uint_as_float(src[2]), __uint_as_float(src[3]));
-              o.z = pack_bf16x2(__uint_as_float(src[4]), __uint_as_float(src[5]));
-              o.w = pack_bf16x2(__uint_as_float(src[6]), __uint_as_float(src[7]));
+          uint8_t* box = my_stage;
+          if (f32) {
+            if (stores_issued > 0) {  // the previous box must have been read out of the stage
+              if (lane == 0) bulk_wait_read_all();
+              __syncwarp();
             }
-            *reinterpret_cast<uint4*>(row_base + ((q ^ (lane & 7)) << 4)) = o;
+            // 16-byte chunk q of row `lane` goes to chunk q ^ (lane & 7): the 128-byte swizzle the
+            // tensor map expects, which also spreads a warp's stores over all banks.
+            uint8_t* row_base = box + lane * 128;
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+              *reinterpret_cast<uint4*>(row_base + ((q ^ (lane & 7)) << 4)) =
+                  make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+          } else {
+            box = my_stage + (stores_issued & 1) * (STORE_STAGE_BYTES / 2);
+            if (stores_issued > 1) {  // the box before the previous one used this half
+              if (lane == 0) bulk_wait_read_but_one();
+              __syncwarp();
+            }
+            // 64-byte rows under the 64-byte swizzle: chunk q of row r sits at q ^ ((r >> 1) & 3)
+            uint8_t* row_base = box + lane * 64;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint4 o;
+              o.x = pack_bf16x2(__uint_as_float(v[8 * q + 0]), __uint_as_float(v[8 * q + 1]));
+              o.y = pack_bf16x2(__uint_as_float(v[8 * q + 2]), __uint_as_float(v[8 * q + 3]));
+              o.z = pack_bf16x2(__uint_as_float(v[8 * q + 4]), __uint_as_float(v[8 * q + 5]));
+              o.w = pack_bf16x2(__uint_as_float(v[8 * q + 6]), __uint_as_float(v[8 * q + 7]));
+              *reinterpret_cast<uint4*>(row_base + ((q ^ ((lane >> 1) & 3)) << 4)) = o;
+            }
           }
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
-            tma_store_3d(&tm_c, my_stage, col_base + c, m0, plane);
+            tma_store_3d(&tm_c, box, col_base + c, m0, plane);
             bulk_commit_group();
           }
-          store_pending = true;
+          ++stores_issued;
         }
       } else if (p.combine_enabled) {
         // Fused combine: the rows go to the routed buffers of their source ranks. Each lane finds the
@@ -407,7 +415,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         acc_phase ^= 1u;
       }
     }
-    if (store_pending && lane == 0) bulk_wait_all();  // this thread's stores are in global memory
+    if (stores_issued > 0 && lane == 0) bulk_wait_all();  // this thread's stores are in global memory
   }
 
   // Teardown: everyone meets here (also after a time-out), then the allocating warp frees TMEM.
@@ -440,7 +448,7 @@ EncodeTiledFn encode_fn() {
 
 // Tensor of `rank` dims (dims[0] innermost), box with a 128-byte inner extent, 128-byte swizzle.
 int make_map(CUtensorMap* out, const void* base, int rank, const cuuint64_t* dims, const cuuint32_t* box,
-             bool f32 = false) {
+             bool f32 = false, bool swizzle64 = false) {
   EncodeTiledFn fn = encode_fn();
   HMC_REQUIRE(fn != nullptr, HMC_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
   cuuint64_t strides[4];
@@ -453,7 +461,7 @@ int make_map(CUtensorMap* out, const void* base, int rank, const cuuint64_t* dim
   CUresult r = fn(out, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
                   static_cast<cuuint32_t>(rank),
                   const_cast<void*>(base), dims, strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  swizzle64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   HMC_REQUIRE(r == CUDA_SUCCESS, HMC_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
   return 0;
@@ -619,8 +627,8 @@ extern "C" int hmc_grouped_gemm(const hmc_grouped_gemm_args* args, void* stream_
       const bool f32 = a.epilogue == HMC_EPI_STORE_F32;
       cuuint64_t dims[3] = {static_cast<cuuint64_t>(a.n), static_cast<cuuint64_t>(a.m),
                             static_cast<cuuint64_t>(a.groups)};
-      cuuint32_t box[3] = {f32 ? 32u : 64u, 32, 1};
-      if ((rc = make_map(&tc, a.c, 3, dims, box, f32)) != 0) return rc;
+      cuuint32_t box[3] = {32u, 32, 1};  // FP32: 128-byte rows; BF16: 64-byte rows, two boxes in flight
+      if ((rc = make_map(&tc, a.c, 3, dims, box, f32, !f32)) != 0) return rc;
     }
   }
   if (a.mode == HMC_GEMM_RAGGED_M) {
@@ -630,8 +638,8 @@ extern "C" int hmc_grouped_gemm(const hmc_grouped_gemm_args* args, void* stream_
     if (plain && !p.combine_enabled && (a.n * (f32 ? 4 : 2)) % 16 == 0 && aligned16(a.c)) {
       // C = [1, rows, n] seen through the same 32-row x 128-byte boxes as the weight gradients
       cuuint64_t dims[3] = {static_cast<cuuint64_t>(a.n), static_cast<cuuint64_t>(a.rows), 1};
-      cuuint32_t box[3] = {f32 ? 32u : 64u, 32, 1};
-      if ((rc = make_map(&tc, a.c, 3, dims, box, f32)) != 0) return rc;
+      cuuint32_t box[3] = {32u, 32, 1};
+      if ((rc = make_map(&tc, a.c, 3, dims, box, f32, !f32)) != 0) return rc;
       p.tma_store = 1;
     }
   }

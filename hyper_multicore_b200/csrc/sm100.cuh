@@ -105,6 +105,8 @@ __device__ __forceinline__ void tma_store_3d(const CUtensorMap* tm, const void* 
 __device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // All of this thread's bulk groups have finished READING shared memory (the source may be reused).
 __device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// All but the newest of this thread's bulk groups have finished reading shared memory.
+__device__ __forceinline__ void bulk_wait_read_but_one() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
 // All of this thread's bulk groups are complete (their global writes are done).
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
