@@ -58,7 +58,7 @@ FLOPS_PER_TOKEN = 18 * TOP_K * HIDDEN * INTER
 
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of the six grouped-GEMM launches of one
 # step at EP=1, from the ncu capture summarised in profiles/grouped_gemm_kernel_bench_moe_bf16_ep1.md.
-GEMM_DRAM_BYTES_PER_STEP = 4.98e9
+GEMM_DRAM_BYTES_PER_STEP = 5.02e9
 
 
 def make_inputs(rank: int, ep: int, device=None):
