@@ -74,7 +74,15 @@ def make_inputs(rank: int, ep: int, device=None):
         popularity[ranking] = torch.arange(1, EXPERTS + 1, dtype=torch.float32).pow(-ZIPF)
         gumbel = -torch.log(-torch.log(torch.rand(TOKENS, EXPERTS, generator=g).clamp_min(1e-9)))
         logits = popularity.log() + gumbel
-        weights, ids = torch.topk(logits.sigmoid(), TOP_K, dim=-1)
+        # group-limited selection of that configuration: 8 expert groups, the 4 best per token (group score =
+        # sum of the two largest scores of the group), then top-k inside them
+        scores = logits.sigmoid()
+        grouped = scores.view(TOKENS, 8, EXPERTS // 8)
+        best_groups = grouped.topk(2, dim=-1).values.sum(dim=-1).topk(4, dim=-1).indices
+        keep = torch.zeros(TOKENS, 8, dtype=torch.bool).scatter_(1, best_groups, True)
+        limited = scores.masked_fill(~keep.unsqueeze(-1).expand_as(grouped).reshape(TOKENS, EXPERTS), float("-inf"))
+        ids = torch.topk(limited, TOP_K, dim=-1).indices
+        weights = scores.gather(1, ids)
         weights = weights / weights.sum(dim=-1, keepdim=True)
     else:
         weights, ids = torch.topk(logits.softmax(dim=-1), TOP_K, dim=-1)
@@ -96,7 +104,7 @@ def config(ep: int) -> dict:
     return {
         "workload": (f"MegaMoE {PRECISION.upper()} forward+backward, EP={ep}, {TOKENS} tokens/rank, hidden {HIDDEN}, "
                      f"{EXPERTS} experts ({EXPERTS // ep}/rank), "
-                     f"{'sigmoid top-' + str(TOP_K) + ' with Zipf(' + str(ZIPF) + ') load' if ZIPF else 'softmax top-' + str(TOP_K)}, "
+                     f"{'sigmoid top-' + str(TOP_K) + ' in 4 of 8 expert groups, Zipf(' + str(ZIPF) + ') load' if ZIPF else 'softmax top-' + str(TOP_K)}, "
                      f"SwiGLU intermediate {INTER}"),
         "tokens_per_rank": TOKENS, "hidden": HIDDEN, "experts": EXPERTS, "top_k": TOP_K, "intermediate": INTER,
         "ep": ep, "layout": "EIO",

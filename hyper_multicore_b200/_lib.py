@@ -89,7 +89,7 @@ class GateRouteArgs(ctypes.Structure):
         ("use_vision_bias", c_int32), ("experts", c_int32), ("top_k", c_int32), ("scoring", c_int32),
         ("tokens", c_int64), ("scale", c_float),
         ("weights", c_void_p), ("indices", c_void_p), ("route_scores", c_void_p), ("selected", c_void_p),
-        ("denominator", c_void_p),
+        ("denominator", c_void_p), ("n_group", c_int32), ("topk_group", c_int32),
     ]
 
 

@@ -41,7 +41,8 @@ gate_route_kernel(const float* __restrict__ logits, const float* __restrict__ te
                   int use_vision_bias, long long tokens, int experts, int top_k, float scale,
                   int scoring, float* __restrict__ weights, long long* __restrict__ indices,
                   float* __restrict__ route_scores, float* __restrict__ selected,
-                  float* __restrict__ denominator) {
+                  float* __restrict__ denominator, int n_group, int topk_group) {
+  extern __shared__ float group_stage[];  // [WARPS_PER_BLOCK][experts], only with n_group > 0
   const int lane = threadIdx.x & 31;
   const long long token = static_cast<long long>(blockIdx.x) * WARPS_PER_BLOCK + (threadIdx.x >> 5);
   if (token >= tokens) return;
@@ -88,6 +89,45 @@ gate_route_kernel(const float* __restrict__ logits, const float* __restrict__ te
       biased[i] = score[i] + bias[e];
     } else {
       biased[i] = NEG_INF;
+    }
+  }
+
+  if (n_group > 0) {
+    // Group limit: lane g scores group g (sum of its two largest biased scores), the warp picks the
+    // topk_group best groups, experts of the other groups leave the selection.
+    float* mine = group_stage + (threadIdx.x >> 5) * experts;
+#pragma unroll
+    for (int i = 0; i < NPL; ++i) {
+      const int e = lane + 32 * i;
+      if (e < experts) mine[e] = biased[i];
+    }
+    __syncwarp();
+    const int group_size = experts / n_group;
+    float group_score = NEG_INF;
+    if (lane < n_group) {
+      float first = NEG_INF, second = NEG_INF;
+      for (int j = 0; j < group_size; ++j) {
+        const float v = mine[lane * group_size + j];
+        if (v > first) {
+          second = first;
+          first = v;
+        } else if (v > second) {
+          second = v;
+        }
+      }
+      group_score = group_size > 1 ? first + second : first;
+    }
+    uint32_t chosen = 0;
+    for (int k = 0; k < topk_group; ++k) {
+      float best = (lane < n_group && !((chosen >> lane) & 1u)) ? group_score : NEG_INF;
+      int best_idx = (lane < n_group && !((chosen >> lane) & 1u)) ? lane : 0x7fffffff;
+      warp_argmax(best, best_idx);
+      if (best_idx < 32) chosen |= 1u << best_idx;
+    }
+#pragma unroll
+    for (int i = 0; i < NPL; ++i) {
+      const int e = lane + 32 * i;
+      if (e < experts && !((chosen >> (e / group_size)) & 1u)) biased[i] = NEG_INF;
     }
   }
 
@@ -317,10 +357,11 @@ __global__ void gate_sum_parts_kernel(const float* __restrict__ partial, long lo
 template <int NPL>
 void launch_route(const hmc_gate_route_args& a, cudaStream_t stream) {
   const unsigned grid = static_cast<unsigned>((a.tokens + WARPS_PER_BLOCK - 1) / WARPS_PER_BLOCK);
-  gate_route_kernel<NPL><<<grid, WARPS_PER_BLOCK * 32, 0, stream>>>(
+  const size_t smem = a.n_group > 0 ? static_cast<size_t>(WARPS_PER_BLOCK) * a.experts * sizeof(float) : 0;
+  gate_route_kernel<NPL><<<grid, WARPS_PER_BLOCK * 32, smem, stream>>>(
       a.logits, a.text_bias, a.vision_bias, a.image_mask, a.use_vision_bias, a.tokens, a.experts, a.top_k,
       a.scale, a.scoring, a.weights, reinterpret_cast<long long*>(a.indices), a.route_scores, a.selected,
-      a.denominator);
+      a.denominator, a.n_group, a.topk_group);
 }
 
 template <int NPL>
@@ -362,6 +403,14 @@ extern "C" int hmc_gate_route(const hmc_gate_route_args* args, void* stream_ptr)
               HMC_ERR_INVALID, "hmc_gate_route: null tensor pointer");
   HMC_REQUIRE(!a.use_vision_bias || (a.vision_bias && a.image_mask), HMC_ERR_INVALID,
               "hmc_gate_route: vision routing needs vision_bias and image_mask");
+  if (a.n_group != 0) {
+    HMC_REQUIRE(a.n_group >= 1 && a.n_group <= 32 && a.experts % a.n_group == 0, HMC_ERR_INVALID,
+                "hmc_gate_route: n_group (%d) must be in [1, 32] and divide experts (%d)", a.n_group, a.experts);
+    HMC_REQUIRE(a.topk_group >= 1 && a.topk_group <= a.n_group, HMC_ERR_INVALID,
+                "hmc_gate_route: topk_group (%d) must be in [1, n_group]", a.topk_group);
+    HMC_REQUIRE(a.top_k <= a.topk_group * (a.experts / a.n_group), HMC_ERR_INVALID,
+                "hmc_gate_route: top_k (%d) exceeds the experts of %d groups", a.top_k, a.topk_group);
+  }
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
 #define CALL(N) launch_route<N>(a, stream)
   HMC_DISPATCH_NPL(a.experts, CALL);

@@ -166,8 +166,8 @@ def gate_project(x: torch.Tensor, weight: torch.Tensor, use_tensor_cores: bool |
 
 
 def gate_route_out(logits, text_bias, vision_bias, image_mask, use_vision_bias, top_k, scale, scoring,
-                   weights, indices, route_scores, selected, denominator) -> None:
-    """Top-k Route on FP32 logits into caller-owned outputs."""
+                   weights, indices, route_scores, selected, denominator, n_group=0, topk_group=0) -> None:
+    """Top-k Route on FP32 logits into caller-owned outputs (``n_group`` > 0: group-limited selection)."""
     device = _require_cuda(logits, text_bias, vision_bias, weights, indices, route_scores, selected, denominator)
     args = _lib.GateRouteArgs()
     args.logits = logits.data_ptr()
@@ -185,6 +185,7 @@ def gate_route_out(logits, text_bias, vision_bias, image_mask, use_vision_bias, 
     args.route_scores = route_scores.data_ptr()
     args.selected = selected.data_ptr()
     args.denominator = denominator.data_ptr()
+    args.n_group, args.topk_group = n_group, topk_group
     _call("hmc_gate_route", device, ctypes.byref(args))
 
 

@@ -21,7 +21,8 @@ from ._precision import preserve_fp32_parameters
 _SCORING = ("sqrtsoftplus", "softmax", "sigmoid")
 
 
-def route(logits, text_bias, vision_bias, image_mask, use_vision_bias, top_k, scale, scoring):
+def route(logits, text_bias, vision_bias, image_mask, use_vision_bias, top_k, scale, scoring, n_group=0,
+          topk_group=0):
     """Allocate the five Route outputs and launch (mirror of ops._mega_gate_route)."""
     tokens, experts = logits.shape
     device = logits.device
@@ -31,7 +32,7 @@ def route(logits, text_bias, vision_bias, image_mask, use_vision_bias, top_k, sc
     selected = torch.empty((tokens, top_k), dtype=torch.float32, device=device)
     denominator = torch.empty((tokens, 1), dtype=torch.float32, device=device)
     kernels.gate_route_out(logits, text_bias, vision_bias, image_mask, use_vision_bias, top_k, scale, scoring,
-                           weights, indices, scores, selected, denominator)
+                           weights, indices, scores, selected, denominator, n_group, topk_group)
     return weights, indices, scores, selected, denominator
 
 
@@ -58,10 +59,12 @@ class _RouteFunction(torch.autograd.Function):
     """Differentiate Route with respect to the logits only; first order (function.py:96-160)."""
 
     @staticmethod
-    def forward(ctx, logits, text_bias, vision_bias, image_mask, use_vision_bias, top_k, scale, scoring):  # pylint: disable=arguments-differ
+    def forward(ctx, logits, text_bias, vision_bias, image_mask, use_vision_bias, top_k, scale, scoring,  # pylint: disable=arguments-differ
+                n_group=0, topk_group=0):
         ctx.set_materialize_grads(False)
         weights, indices, scores, selected, denominator = route(
-            logits, text_bias.detach(), vision_bias.detach(), image_mask, use_vision_bias, top_k, scale, scoring)
+            logits, text_bias.detach(), vision_bias.detach(), image_mask, use_vision_bias, top_k, scale, scoring,
+            n_group, topk_group)
         ctx.save_for_backward(logits, indices, scores, selected, denominator)
         ctx.config = (top_k, scale, scoring)
         ctx.mark_non_differentiable(indices)
@@ -72,13 +75,13 @@ class _RouteFunction(torch.autograd.Function):
     def backward(ctx, grad_weights, grad_indices):  # pylint: disable=arguments-differ
         del grad_indices
         if grad_weights is None or not ctx.needs_input_grad[0]:
-            return (None,) * 8
+            return (None,) * 10
         logits, indices, scores, selected, denominator = ctx.saved_tensors
         top_k, scale, scoring = ctx.config
         grad_logits = torch.empty_like(logits)
         kernels.gate_route_grad_out(logits, scores, selected, denominator, indices, grad_weights.contiguous().float(),
                                     top_k, scale, scoring, grad_logits)
-        return (grad_logits,) + (None,) * 7
+        return (grad_logits,) + (None,) * 9
 
 
 class MegaGate(torch.nn.Module):
@@ -86,8 +89,20 @@ class MegaGate(torch.nn.Module):
 
     def __init__(self, *, hidden_size: int, num_experts: int, top_k: int, scoring_func: str,
                  routed_scaling_factor: float, vision_enabled: bool = False,
-                 initializer_range: float = 0.02) -> None:
+                 initializer_range: float = 0.02, n_group: int | None = None, topk_group: int | None = None) -> None:
+        """``n_group`` / ``topk_group`` are an extension the reference does not have: each token may only
+        select experts from the ``topk_group`` best of ``n_group`` equal contiguous expert groups (group
+        score = sum of the two largest biased scores of the group)."""
         super().__init__()
+        if (n_group is None) != (topk_group is None):
+            raise ValueError("n_group and topk_group go together")
+        if n_group is not None:
+            if not 1 <= n_group <= 32 or num_experts % n_group:
+                raise ValueError("n_group must be in [1, 32] and divide num_experts")
+            if not 1 <= topk_group <= n_group or top_k > topk_group * (num_experts // n_group):
+                raise ValueError("topk_group must be in [1, n_group] and leave at least top_k experts")
+        self.n_group = int(n_group or 0)
+        self.topk_group = int(topk_group or 0)
         if hidden_size <= 0 or num_experts <= 0:
             raise ValueError("hidden_size and num_experts must be positive")
         if top_k <= 0 or top_k > num_experts:
@@ -183,8 +198,10 @@ class MegaGate(torch.nn.Module):
         vision_bias = self.bias_vl.detach().float() if use_vision else text_bias
         if needs_grad:
             weights, indices = _RouteFunction.apply(logits, text_bias, vision_bias, mask, use_vision, self.top_k,
-                                                    self.routed_scaling_factor, self.scoring_func)
+                                                    self.routed_scaling_factor, self.scoring_func, self.n_group,
+                                                    self.topk_group)
         else:
             weights, indices = route(logits, text_bias, vision_bias, mask, use_vision, self.top_k,
-                                     self.routed_scaling_factor, self.scoring_func)[:2]
+                                     self.routed_scaling_factor, self.scoring_func, self.n_group,
+                                     self.topk_group)[:2]
         return logits, weights, indices

@@ -232,6 +232,13 @@ typedef struct hmc_gate_route_args {
   float* route_scores; /* out [tokens, experts] unbiased scores (saved for backward) */
   float* selected;     /* out [tokens, top_k] unbiased scores of the winners */
   float* denominator;  /* out [tokens, 1] sum(selected) + 1e-20 */
+  /* Group-limited selection. NOT part of the reference (it has no expert groups); an extension for
+   * routers that restrict each token to a few expert groups. experts are split into n_group equal,
+   * contiguous groups; a group's score is the sum of its two largest biased scores (its largest one
+   * for groups of one expert); only experts of the topk_group best groups (ties to the lower group)
+   * take part in the top-k. n_group == 0 switches the limit off. n_group <= 32. */
+  int32_t n_group;
+  int32_t topk_group;
 } hmc_gate_route_args;
 
 typedef struct hmc_gate_route_grad_args {

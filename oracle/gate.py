@@ -21,13 +21,28 @@ def scores_from_logits(logits: torch.Tensor, scoring: str) -> torch.Tensor:
     raise ValueError(f"unsupported scoring_func: {scoring!r}")
 
 
-def route_from_logits(logits, bias, bias_vl, image_mask, top_k, scoring, scale):
+def group_limit(biased: torch.Tensor, n_group: int, topk_group: int) -> torch.Tensor:
+    """Extension with no counterpart in the reference (it has no expert groups): keep only the experts
+    of the `topk_group` best of `n_group` equal contiguous groups; a group's score is the sum of its two
+    largest biased scores (the largest for single-expert groups); ties go to the lower group."""
+    tokens, experts = biased.shape
+    grouped = biased.view(tokens, n_group, experts // n_group)
+    group_scores = grouped.topk(min(2, grouped.shape[-1]), dim=-1).values.sum(dim=-1)
+    # stable descending order = ties to the lower group index
+    order = torch.sort(group_scores, dim=-1, descending=True, stable=True).indices[:, :topk_group]
+    keep = torch.zeros(tokens, n_group, dtype=torch.bool).scatter_(1, order, True)
+    return biased.masked_fill(~keep.unsqueeze(-1).expand_as(grouped).reshape(tokens, experts), float("-inf"))
+
+
+def route_from_logits(logits, bias, bias_vl, image_mask, top_k, scoring, scale, n_group=0, topk_group=0):
     """module.py:208-227: bias only selects; weights come from the unbiased scores."""
     scores = scores_from_logits(logits.float(), scoring)
     correction = bias.float()
     if image_mask is not None and bias_vl is not None:
         correction = torch.where(image_mask.reshape(-1, 1), bias_vl.float().unsqueeze(0), bias.float().unsqueeze(0))
     biased = scores + correction
+    if n_group:
+        biased = group_limit(biased, n_group, topk_group)
     indices = torch.topk(biased, top_k, dim=-1, sorted=False).indices
     selected = scores.gather(1, indices)
     denominator = selected.sum(dim=-1, keepdim=True) + 1.0e-20
@@ -42,10 +57,10 @@ def route_from_logits(logits, bias, bias_vl, image_mask, top_k, scoring, scale):
     }
 
 
-def gate_forward(hidden, weight, bias, bias_vl, image_mask, top_k, scoring, scale):
+def gate_forward(hidden, weight, bias, bias_vl, image_mask, top_k, scoring, scale, n_group=0, topk_group=0):
     """module.py:195-198 projection + route."""
     logits = F.linear(hidden.reshape(-1, hidden.shape[-1]).float(), weight.float())
-    out = route_from_logits(logits, bias, bias_vl, image_mask, top_k, scoring, scale)
+    out = route_from_logits(logits, bias, bias_vl, image_mask, top_k, scoring, scale, n_group, topk_group)
     out["logits"] = logits
     return out
 

@@ -166,3 +166,44 @@ def test_projection_at_the_multimodal_gate_shape(cuda_device):
     # opt-in tcgen05 path: absolute error bounded relative to the largest logit
     torch.testing.assert_close(K.gate_project(x, w, use_tensor_cores=True), ref, rtol=1e-5,
                                atol=1e-5 * float(ref.abs().max()))
+
+
+@pytest.mark.parametrize("experts,n_group,topk_group,top_k,scoring", [(256, 8, 4, 8, "sigmoid"), (64, 4, 2, 6, "softmax"),
+                                                                      (48, 16, 5, 3, "sqrtsoftplus"), (32, 32, 8, 8, "sigmoid")])
+def test_group_limited_routing(cuda_device, experts, n_group, topk_group, top_k, scoring):
+    """Group-limited selection (an extension: the reference has no expert groups): 256 experts in 8 groups,
+    4 groups per token, top-8 is the expert-parallel MXFP8 configuration's router. Checked against the
+    oracle's restatement; every selected expert must lie in one of the chosen groups."""
+    from hyper_multicore_b200 import MegaGate, kernels as K
+
+    g = torch.Generator().manual_seed(experts + n_group)
+    tokens = 777
+    logits = torch.randn(tokens, experts, generator=g) * 2
+    bias = torch.randn(experts, generator=g) * 0.1
+    ref = ogate.route_from_logits(logits, bias, None, None, top_k, scoring, 2.5, n_group, topk_group)
+    dev = cuda_device
+    out = dict(
+        weights=torch.empty(tokens, top_k, device=dev), indices=torch.empty(tokens, top_k, dtype=torch.int64, device=dev),
+        route_scores=torch.empty(tokens, experts, device=dev), selected=torch.empty(tokens, top_k, device=dev),
+        denominator=torch.empty(tokens, 1, device=dev))
+    K.gate_route_out(logits.to(dev), bias.to(dev), bias.to(dev), None, False, top_k, 2.5, scoring, **out,
+                     n_group=n_group, topk_group=topk_group)
+    got_idx, got_w = sorted_sets(out["indices"].cpu(), out["weights"].cpu())
+    ref_idx, ref_w = sorted_sets(ref["indices"], ref["weights"])
+    # rows whose group choice or top-k boundary is a near tie may legitimately differ between CPU and GPU exp()
+    flips = (got_idx != ref_idx).any(dim=-1)
+    assert flips.float().mean() < 0.01, f"{int(flips.sum())} of {tokens} rows differ"
+    torch.testing.assert_close(got_w[~flips], ref_w[~flips], rtol=1e-5, atol=1e-6)
+    groups_per_row = torch.tensor([len(set((row // (experts // n_group)).tolist())) for row in out["indices"].cpu()])
+    assert (groups_per_row <= topk_group).all()
+    # module level: the extension arguments reach the kernel, validation rejects impossible settings
+    gate = MegaGate(hidden_size=64, num_experts=experts, top_k=top_k, scoring_func=scoring, routed_scaling_factor=1.0,
+                    n_group=n_group, topk_group=topk_group).to(dev)
+    _, _, idx = gate(torch.randn(2, 50, 64, device=dev).bfloat16())
+    assert ((idx // (experts // n_group)).sort(dim=-1).values.diff(dim=-1) != 0).sum(dim=-1).max() < topk_group
+    with pytest.raises(ValueError):
+        MegaGate(hidden_size=64, num_experts=experts, top_k=top_k, scoring_func=scoring, routed_scaling_factor=1.0,
+                 n_group=n_group)
+    with pytest.raises(ValueError):
+        MegaGate(hidden_size=64, num_experts=experts, top_k=top_k, scoring_func=scoring, routed_scaling_factor=1.0,
+                 n_group=7, topk_group=1)
