@@ -272,8 +272,11 @@ def run_gpu(args) -> None:
 
         attach_mx_fields(w1)
         attach_mx_fields(w2)
+    from hyper_multicore_b200 import MegaMoeTuningOptions
+
     module = MegaMoeExperts(hidden_size=HIDDEN, intermediate_size=INTER, num_experts=EXPERTS, top_k=TOP_K,
-                            ep_group=group, precision=PRECISION)
+                            ep_group=group, precision=PRECISION,
+                            tuning_options=MegaMoeTuningOptions(dispatch_mode=args.dispatch))
 
     # device-resident inputs
     x_d = x_h.to(device).requires_grad_(True)
@@ -411,6 +414,8 @@ def main() -> None:
     parser.add_argument("--shape", choices=tuple(SHAPES), default="c2",
                         help="c2 = EP=2 BF16 configuration's per-rank problem (default); c3 = EP=8 MXFP8 configuration's")
     parser.add_argument("--precision", choices=("bf16", "mxfp8"), default="bf16")
+    parser.add_argument("--dispatch", choices=("push", "pull"), default="push",
+                        help="EP > 1: sources store rows into the owners' buffers (push, default) or owners fetch them (pull)")
     parser.add_argument("--workload", choices=("moe", "gate", "mhc"), default="moe",
                         help="moe = the MoE layer (default, the headline metric); gate / mhc = the router and the "
                              "four-stream residual mix, timed against the HBM roofline")

@@ -24,6 +24,7 @@ HMC_EPI_STORE_F32 = 1
 HMC_EPI_SWIGLU = 2
 HMC_EPI_SWIGLU_GRAD = 3
 HMC_STATUS_WORDS = 8
+HMC_CTRL_SOURCE = 1296
 HMC_CLAMP_NONE, HMC_CLAMP_BEFORE_SILU, HMC_CLAMP_AFTER_SILU = 0, 1, 2
 
 STATUS_NAMES = {
@@ -172,6 +173,19 @@ class EpCombineArgs(ctypes.Structure):
     ]
 
 
+class EpPullArgs(ctypes.Structure):
+    """Mirror of ``hmc_ep_pull_args``."""
+
+    _fields_ = [
+        ("peer_sources", c_void_p), ("source_row_off", c_void_p), ("segment_start", c_void_p),
+        ("out", c_void_p), ("out_values", c_void_p),
+        ("rows", c_int64), ("hidden", c_int64), ("ep", c_int64), ("local_experts", c_int64),
+        ("source_rows_limit", c_int64), ("value_plane_offset", c_int64),
+        ("local_ctrl", c_void_p), ("generation", c_int32), ("max_ctas", c_int32), ("budget_ns", c_uint64),
+        ("status", c_void_p),
+    ]
+
+
 class MxGemmArgs(ctypes.Structure):
     """Mirror of ``hmc_mx_gemm_args``."""
 
@@ -245,6 +259,8 @@ SIGNATURES: dict[str, tuple] = {
     "hmc_ipc_open_handle": (_I, [_P, ctypes.POINTER(c_void_p)]),
     "hmc_ipc_close_handle": (_I, [_P]),
     "hmc_ep_publish_ready": (_I, [_P, _L, _L, _I, _P]),
+    "hmc_ep_publish_source": (_I, [_P, _L, _L, _I, _P]),
+    "hmc_ep_pull": (_I, [ctypes.POINTER(EpPullArgs), _P]),
     "hmc_ep_dispatch": (_I, [ctypes.POINTER(EpDispatchArgs), _P]),
     "hmc_ep_combine": (_I, [ctypes.POINTER(EpCombineArgs), _P]),
     "hmc_ep_wait": (_I, [_P, _I, c_uint64, _P, _P]),

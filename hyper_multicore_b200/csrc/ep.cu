@@ -203,6 +203,85 @@ ep_combine_kernel(const uint4* __restrict__ results, const long long* __restrict
   }
 }
 
+__global__ void ep_publish_source_kernel(PeerTable peers, int ep, int rank, int generation) {
+  const int p = threadIdx.x;
+  if (p < ep) st_release_sys(peers.ctrl[p] + HMC_CTRL_SOURCE + rank * HMC_CTRL_READY_STRIDE, generation);
+}
+
+// Pull: row r of this rank's receive layout (local-expert-major, then source rank) is fetched from the
+// source's expert-major buffer. Plain (coherent) loads: the rows were written by another GPU during
+// this call and become visible through the acquire of the source's flag.
+__global__ void __launch_bounds__(THREADS)
+ep_pull_kernel(PeerTable sources, const long long* __restrict__ source_row_off,
+               const long long* __restrict__ segment_start, uint4* __restrict__ out, float* __restrict__ out_values,
+               long long rows, int vec_per_row, int ep, int local_experts, long long source_rows_limit,
+               long long value_plane_offset, const int* __restrict__ local_ctrl, int generation,
+               unsigned long long budget_ns, int* __restrict__ status) {
+  __shared__ int seen[HMC_MAX_EP];
+  __shared__ int chunk_source[ROWS_PER_CHUNK];
+  __shared__ long long chunk_row[ROWS_PER_CHUNK];
+  __shared__ int failed;
+  if (threadIdx.x < HMC_MAX_EP) seen[threadIdx.x] = -1;
+  if (threadIdx.x == 0) failed = 0;
+  __syncthreads();
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int segments = ep * local_experts;
+  const long long chunks = (rows + ROWS_PER_CHUNK - 1) / ROWS_PER_CHUNK;
+  for (long long chunk = blockIdx.x; chunk < chunks; chunk += gridDim.x) {
+    const long long r0 = chunk * ROWS_PER_CHUNK;
+    const int count = static_cast<int>(min(static_cast<long long>(ROWS_PER_CHUNK), rows - r0));
+    if (threadIdx.x < count) {
+      const long long r = r0 + threadIdx.x;
+      int lo = 0, hi = segments - 1;
+      while (lo < hi) {  // last segment (local expert * ep + source) that starts at or before r
+        const int mid = (lo + hi + 1) >> 1;
+        if (segment_start[mid] <= r) lo = mid; else hi = mid - 1;
+      }
+      const int le = lo / ep;
+      const int s = lo % ep;
+      const long long src = source_row_off[s * local_experts + le] + (r - segment_start[lo]);
+      if (src < 0 || src >= source_rows_limit) {
+        report_status(status, HMC_STATUS_BAD_INDEX, static_cast<int>(r), lo, static_cast<int>(src));
+        chunk_source[threadIdx.x] = -1;
+      } else {
+        chunk_source[threadIdx.x] = s;
+      }
+      chunk_row[threadIdx.x] = src;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      for (int r = 0; r < count; ++r) {
+        const int s = chunk_source[r];
+        if (s < 0 || seen[s] >= generation) continue;
+        int observed = 0;
+        if (!wait_counter_ge(local_ctrl + HMC_CTRL_SOURCE + s * HMC_CTRL_READY_STRIDE, generation, budget_ns,
+                             &observed)) {
+          report_status(status, HMC_STATUS_TIMEOUT_READY, s, generation, observed);
+          failed = 1;
+          break;
+        }
+        seen[s] = observed;
+      }
+    }
+    __syncthreads();
+    if (failed) return;
+    for (int r = warp; r < count; r += THREADS / 32) {
+      const int s = chunk_source[r];
+      if (s < 0) continue;
+      const uint4* src = static_cast<const uint4*>(sources.data[s]) + chunk_row[r] * vec_per_row;
+      uint4* dst = out + (r0 + r) * vec_per_row;
+      for (int v = lane; v < vec_per_row; v += 32) st_16(dst + v, ld_16(src + v));
+      if (out_values != nullptr && lane == 0) {
+        const float* plane = reinterpret_cast<const float*>(static_cast<const unsigned char*>(sources.data[s]) +
+                                                           value_plane_offset);
+        out_values[r0 + r] = plane[chunk_row[r]];
+      }
+    }
+    __syncthreads();
+  }
+}
+
 __global__ void ep_wait_kernel(const int* counter, int expected, unsigned long long budget_ns, int* status) {
   int seen = 0;
   if (!wait_counter_ge(counter, expected, budget_ns, &seen))
@@ -281,6 +360,49 @@ extern "C" int hmc_ep_publish_ready(void* const* peer_ctrl, int64_t ep, int64_t 
   HMC_REQUIRE(rank >= 0 && rank < ep, HMC_ERR_INVALID, "hmc_ep_publish_ready: rank out of range");
   ep_publish_ready_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream_ptr)>>>(table, static_cast<int>(ep),
                                                                               static_cast<int>(rank), generation);
+  HMC_LAUNCH_OK();
+  return 0;
+}
+
+extern "C" int hmc_ep_publish_source(void* const* peer_ctrl, int64_t ep, int64_t rank, int32_t generation,
+                                     void* stream_ptr) {
+  PeerTable table;
+  int rc = fill_peers(&table, peer_ctrl, peer_ctrl, ep);
+  if (rc != 0) return rc;
+  HMC_REQUIRE(rank >= 0 && rank < ep, HMC_ERR_INVALID, "hmc_ep_publish_source: rank out of range");
+  ep_publish_source_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream_ptr)>>>(table, static_cast<int>(ep),
+                                                                               static_cast<int>(rank), generation);
+  HMC_LAUNCH_OK();
+  return 0;
+}
+
+extern "C" int hmc_ep_pull(const hmc_ep_pull_args* args, void* stream_ptr) {
+  HMC_REQUIRE(args != nullptr, HMC_ERR_INVALID, "hmc_ep_pull: null args");
+  const hmc_ep_pull_args& a = *args;
+  if (a.rows == 0) return 0;
+  PeerTable table;
+  int rc = fill_peers(&table, a.peer_sources, a.peer_sources, a.ep);
+  if (rc != 0) return rc;
+  HMC_REQUIRE(a.source_row_off && a.segment_start && a.out && a.local_ctrl, HMC_ERR_INVALID,
+              "hmc_ep_pull: null tensor pointer");
+  HMC_REQUIRE(a.hidden > 0 && a.hidden % 8 == 0 && aligned16(a.out), HMC_ERR_INVALID,
+              "hmc_ep_pull: rows must be 16-byte aligned multiples of 8 BF16 elements");
+  HMC_REQUIRE(a.local_experts > 0 && a.rows > 0 && a.rows < (1ll << 31) && a.source_rows_limit > 0, HMC_ERR_INVALID,
+              "hmc_ep_pull: bad extents");
+  HMC_REQUIRE(a.out_values == nullptr || (a.value_plane_offset >= a.source_rows_limit * a.hidden * 2 &&
+                                          a.value_plane_offset % 4 == 0),
+              HMC_ERR_INVALID, "hmc_ep_pull: the value plane must lie behind the rows of the source buffer");
+  for (int p = 0; p < a.ep; ++p)
+    HMC_REQUIRE(aligned16(a.peer_sources[p]), HMC_ERR_INVALID, "hmc_ep_pull: source buffer %d is not 16-byte aligned", p);
+  const long long chunks = (a.rows + ROWS_PER_CHUNK - 1) / ROWS_PER_CHUNK;
+  int grid = 4 * sm_count();
+  if (a.max_ctas > 0 && grid > a.max_ctas) grid = a.max_ctas;
+  if (chunks < grid) grid = static_cast<int>(chunks);
+  ep_pull_kernel<<<grid, THREADS, 0, static_cast<cudaStream_t>(stream_ptr)>>>(
+      table, reinterpret_cast<const long long*>(a.source_row_off), reinterpret_cast<const long long*>(a.segment_start),
+      static_cast<uint4*>(a.out), a.out_values, a.rows, static_cast<int>(a.hidden / 8), static_cast<int>(a.ep),
+      static_cast<int>(a.local_experts), a.source_rows_limit, a.value_plane_offset, a.local_ctrl, a.generation,
+      a.budget_ns ? a.budget_ns : 10ull * 1000 * 1000 * 1000, a.status);
   HMC_LAUNCH_OK();
   return 0;
 }

@@ -418,6 +418,30 @@ def ep_combine(results, segment_start, combine_target_off, *, rows, ep, local_ex
     _call("hmc_ep_combine", device, ctypes.byref(args))
 
 
+def ep_publish_source(peer_ctrl, ep: int, rank: int, generation: int, device: torch.device) -> None:
+    """Tell every peer that this rank's source buffer holds the rows of ``generation`` (pull dispatch)."""
+    _call("hmc_ep_publish_source", device, peer_ctrl, ep, rank, generation)
+
+
+def ep_pull(out, segment_start, source_row_off, *, rows, ep, local_experts, source_rows_limit, peer_sources,
+            local_ctrl, generation, status=None, budget_ns=0, max_ctas=0, out_values=None,
+            value_plane_offset=0) -> None:
+    """Fetch this rank's rows from the published source buffers of their source ranks."""
+    device = _require_cuda(out, segment_start, source_row_off, local_ctrl, out_values)
+    args = _lib.EpPullArgs()
+    args.peer_sources = ctypes.cast(peer_sources, ctypes.c_void_p)
+    args.source_row_off = source_row_off.data_ptr()
+    args.segment_start = segment_start.data_ptr()
+    args.out = out.data_ptr()
+    args.out_values = _lib.ptr(out_values)
+    args.rows, args.hidden, args.ep, args.local_experts = rows, out.shape[1], ep, local_experts
+    args.source_rows_limit, args.value_plane_offset = source_rows_limit, value_plane_offset
+    args.local_ctrl = local_ctrl.data_ptr()
+    args.generation, args.max_ctas, args.budget_ns = generation, max_ctas, budget_ns
+    args.status = _lib.ptr(status)
+    _call("hmc_ep_pull", device, ctypes.byref(args))
+
+
 def ep_wait(counter: torch.Tensor, expected: int, status=None, budget_ns: int = 0) -> None:
     """Stream-ordered bounded wait until ``counter[0] >= expected``."""
     device = _require_cuda(counter)
@@ -432,7 +456,7 @@ KERNELS_PER_CALL = {
     "hmc_moe_permute_from_mapping": 1, "hmc_moe_unpermute": 1, "hmc_moe_unpermute_grad": 1,
     "hmc_moe_token_permute_grad": 1, "hmc_zero_empty_expert_grad": 1, "hmc_route_offsets": 1,
     "hmc_mega_mhc": 5, "hmc_mega_mhc_grad": 8, "hmc_ep_publish_ready": 1, "hmc_ep_dispatch": 1,
-    "hmc_ep_combine": 1, "hmc_ep_wait": 1, "hmc_ep_wait_groups": 1,
+    "hmc_ep_combine": 1, "hmc_ep_wait": 1, "hmc_ep_wait_groups": 1, "hmc_ep_publish_source": 1, "hmc_ep_pull": 1,
 }
 
 

@@ -228,8 +228,6 @@ class MegaMoeExperts(torch.nn.Module):
         if precision == "mxfp8" and (hidden_size % 128 or intermediate_size % 128):
             raise ValueError("precision='mxfp8' needs hidden_size and intermediate_size to be multiples of 128 "
                              "on the sm_100a backend (the reference requires multiples of 64)")
-        if tuning.dispatch_mode != "push":
-            raise NotImplementedError("dispatch_mode='pull' is not available in the sm_100a backend; use 'push'")
         self.hidden_size = hidden_size
         self.intermediate_size = intermediate_size
         self.num_experts = num_experts
@@ -241,6 +239,7 @@ class MegaMoeExperts(torch.nn.Module):
         self._precision = precision
         self._numerics = numerics
         self._tuning = tuning
+        self._pull = tuning.dispatch_mode == "pull" and ep_size > 1
         self._layout: str | None = None
         self._scale_atoms: dict = {}
         # Budget of every cross-rank device wait (ready flags, arrival and combine counters). A rank
@@ -426,6 +425,18 @@ class MegaMoeExperts(torch.nn.Module):
             return self._workspace
         need_capacity, need_routed = route.max_received_rows, route.max_routed_rows
         workspace = self._workspace
+        if self._pull:
+            # Owners fetch into plain local tensors: the peer-mapped memory holds each rank's own rows
+            # (source buffer + routed buffer), so a hot expert never makes it grow.
+            if workspace is None or need_routed > workspace.routed_rows:
+                generation = 0
+                if workspace is not None:
+                    generation = workspace.generation
+                    workspace.close()
+                self._workspace = PeerWorkspace(self._ep_group, self.hidden_size, need_routed, need_routed, device,
+                                                pull=True)
+                self._workspace.generation = generation
+            return self._workspace
         if workspace is not None and need_capacity <= workspace.capacity_rows and need_routed <= workspace.routed_rows:
             return workspace
         # Every rank sees the same gathered table, so every rank takes this branch together.
@@ -545,6 +556,29 @@ class MegaMoeExperts(torch.nn.Module):
         clamp = _lib.HMC_CLAMP_AFTER_SILU if self._numerics.clamp_after_silu else _lib.HMC_CLAMP_BEFORE_SILU
         return {"swiglu_clamp": clamp, "swiglu_limit": float(limit)}
 
+    def _pull_rows(self, workspace, route: PreparedRoute, generation: int, fill, values=None):
+        """Pull dispatch: `fill(rows)` writes this rank's expert-major rows into its source buffer, the
+        buffer is published, and this rank fetches the rows of its own experts from every source
+        (reference: owner-initiated GET, docs/design/mega_moe_design.md:33-35). Returns the received
+        rows (a local tensor of exactly the received size) and, with `values`, their per-row scalars."""
+        device = workspace.device
+        routed = route.routed_rows
+        if routed > 0:
+            fill(workspace.source_buffer[:routed])
+            if values is not None:
+                workspace.source_values[:routed].copy_(values)
+        kernels.ep_publish_source(workspace.peer_ctrl, self.ep_size, self._rank, generation, device)
+        rows = max(route.received_rows, 1)
+        out = torch.empty(rows, self.hidden_size, dtype=torch.bfloat16, device=device)
+        out_values = torch.empty(rows, dtype=torch.float32, device=device) if values is not None else None
+        off = route.offsets
+        kernels.ep_pull(out, off["recv_segment_start"], off["combine_target_off"], rows=route.received_rows,
+                        ep=self.ep_size, local_experts=self.local_experts, source_rows_limit=workspace.routed_rows,
+                        peer_sources=workspace.peer_source, local_ctrl=workspace.ctrl, generation=generation,
+                        status=self._status, budget_ns=self._wait_budget_ns, out_values=out_values,
+                        value_plane_offset=workspace.source_plane_offset)
+        return out, out_values
+
     def _fused_combine(self, workspace, off, peer_routed, peer_ctrl) -> dict | None:
         """Arguments that make a GEMM's epilogue return its rows to their source ranks."""
         if self.ep_size == 1:
@@ -576,35 +610,45 @@ class MegaMoeExperts(torch.nn.Module):
         bf16 = dict(dtype=torch.bfloat16, device=device)
         before_fc2 = self._numerics.apply_probs_before_fc2
         generation = workspace.begin_call()
-        if self.ep_size == 1:
-            expert_buffer, expert_values, plane_offset = self._local_rows(max(received, 1), device)
-            capacity = expert_buffer.shape[0]
-        else:
-            expert_buffer, expert_values = workspace.expert_buffer, workspace.expert_values
-            capacity, plane_offset = workspace.capacity_rows, workspace.expert_plane_offset
-        peer_expert, peer_routed, peer_ctrl = self._peer_tables(workspace, expert_buffer)
         off = route.offsets
-        travelling = dict(row_values=probs.reshape(-1), value_index=route.source_of_row,
-                          value_plane_offset=plane_offset) if before_fc2 else {}
-        kernels.ep_dispatch(hidden, route.source_of_row, route.expert_of_row, off["dispatch_src_off"],
-                            off["dispatch_target_off"], rows=routed_rows, top_k=self.top_k, ep=self.ep_size,
-                            local_experts=self.local_experts, capacity_rows=capacity, peer_buffers=peer_expert,
-                            peer_ctrl=peer_ctrl, local_ctrl=workspace.ctrl, generation=generation,
-                            status=self._status, budget_ns=self._wait_budget_ns, **travelling)
+        pull = self._pull
+        if pull:
+            sorted_probs = probs.reshape(-1).index_select(0, route.source_of_row.long()) if before_fc2 else None
+            expert_buffer, expert_values = self._pull_rows(
+                workspace, route, generation,
+                lambda rows_out: kernels.moe_gather_rows(hidden, route.source_of_row, self.top_k, rows_out),
+                values=sorted_probs)
+            _, peer_routed, peer_ctrl = self._peer_tables(workspace, expert_buffer)
+        else:
+            if self.ep_size == 1:
+                expert_buffer, expert_values, plane_offset = self._local_rows(max(received, 1), device)
+                capacity = expert_buffer.shape[0]
+            else:
+                expert_buffer, expert_values = workspace.expert_buffer, workspace.expert_values
+                capacity, plane_offset = workspace.capacity_rows, workspace.expert_plane_offset
+            peer_expert, peer_routed, peer_ctrl = self._peer_tables(workspace, expert_buffer)
+            travelling = dict(row_values=probs.reshape(-1), value_index=route.source_of_row,
+                              value_plane_offset=plane_offset) if before_fc2 else {}
+            kernels.ep_dispatch(hidden, route.source_of_row, route.expert_of_row, off["dispatch_src_off"],
+                                off["dispatch_target_off"], rows=routed_rows, top_k=self.top_k, ep=self.ep_size,
+                                local_experts=self.local_experts, capacity_rows=capacity, peer_buffers=peer_expert,
+                                peer_ctrl=peer_ctrl, local_ctrl=workspace.ctrl, generation=generation,
+                                status=self._status, budget_ns=self._wait_budget_ns, **travelling)
         rows = max(received, 1)
         up_proj = torch.empty(rows, 2 * inter, **bf16)
         activation = torch.empty(rows, inter, **bf16)
         down_proj = torch.empty(rows, hid, **bf16) if self.ep_size == 1 else None
         x_recv = expert_buffer[:rows]
         row_probs = expert_values[:rows] if before_fc2 else None
-        arrival = workspace.ctrl[_lib.HMC_CTRL_ARRIVAL:_lib.HMC_CTRL_ARRIVAL + self.local_experts]
-        saved_received = torch.empty_like(x_recv) if self.ep_size > 1 else None
+        # pulled rows are complete in stream order and live in a tensor of their own
+        arrival = None if pull else workspace.ctrl[_lib.HMC_CTRL_ARRIVAL:_lib.HMC_CTRL_ARRIVAL + self.local_experts]
+        saved_received = torch.empty_like(x_recv) if (self.ep_size > 1 and not pull) else x_recv
         if received > 0:
             kernels.grouped_gemm(x_recv, w1, up_proj, off["group_list"], mode=kernels.HMC_GEMM_RAGGED_M,
                                  b_major=b_major, epilogue=kernels.HMC_EPI_SWIGLU, aux=activation,
                                  ready_counters=arrival, ready_budget_ns=self._wait_budget_ns, status=self._status,
                                  row_probs=row_probs, **self._swiglu_options())
-            if self.ep_size > 1:
+            if self.ep_size > 1 and not pull:
                 # GEMM1 has waited for every expert's rows: the owned copy of the received rows (the
                 # symmetric buffer is rewritten by the next call) runs on a side stream beside GEMM2.
                 side = self._copy_stream(device)
@@ -629,13 +673,13 @@ class MegaMoeExperts(torch.nn.Module):
             # the call returns.
             live_routed = workspace.routed_buffer[:max(routed_rows, 1)]
             routed_out = torch.empty_like(live_routed)
-            saved_probs = torch.empty_like(row_probs) if before_fc2 else None
+            saved_probs = (row_probs if pull else torch.empty_like(row_probs)) if before_fc2 else None
             main = torch.cuda.current_stream(device)
             side = self._copy_stream(device)
             side.wait_stream(main)
             with torch.cuda.stream(side):
                 routed_out.copy_(live_routed)
-                if before_fc2:
+                if before_fc2 and not pull:
                     saved_probs.copy_(row_probs)
         out = torch.empty(hidden.shape[0], hid, **bf16)
         live = routed_out if self.ep_size == 1 else live_routed
@@ -674,28 +718,48 @@ class MegaMoeExperts(torch.nn.Module):
             # backends/bf16/autograd.py:138-150); the gather is fused into the dispatch.
             row_probs = saved_last
             generation = workspace.begin_call()
-            if self.ep_size == 1:
-                expert_buffer, _, _ = self._local_rows(rows, device)
-                capacity = rows
+            if self._pull:
+                dy_recv, _ = self._pull_rows(
+                    workspace, route, generation,
+                    lambda rows_out: kernels.moe_gather_rows(grad_output, route.source_of_row, self.top_k, rows_out))
+                _, peer_routed, peer_ctrl = self._peer_tables(workspace, dy_recv)
+                arrival = None
             else:
-                expert_buffer, capacity = workspace.expert_buffer, workspace.capacity_rows
-            peer_expert, peer_routed, peer_ctrl = self._peer_tables(workspace, expert_buffer)
-            kernels.ep_dispatch(grad_output, route.source_of_row, route.expert_of_row, off["dispatch_src_off"],
-                                off["dispatch_target_off"], rows=routed_rows, top_k=self.top_k, ep=self.ep_size,
-                                local_experts=self.local_experts, capacity_rows=capacity, peer_buffers=peer_expert,
-                                peer_ctrl=peer_ctrl, local_ctrl=workspace.ctrl, generation=generation,
-                                status=self._status, budget_ns=self._wait_budget_ns)
-            dy_recv = expert_buffer[:rows]
-            arrival = workspace.ctrl[_lib.HMC_CTRL_ARRIVAL:_lib.HMC_CTRL_ARRIVAL + self.local_experts]
+                if self.ep_size == 1:
+                    expert_buffer, _, _ = self._local_rows(rows, device)
+                    capacity = rows
+                else:
+                    expert_buffer, capacity = workspace.expert_buffer, workspace.capacity_rows
+                peer_expert, peer_routed, peer_ctrl = self._peer_tables(workspace, expert_buffer)
+                kernels.ep_dispatch(grad_output, route.source_of_row, route.expert_of_row, off["dispatch_src_off"],
+                                    off["dispatch_target_off"], rows=routed_rows, top_k=self.top_k, ep=self.ep_size,
+                                    local_experts=self.local_experts, capacity_rows=capacity,
+                                    peer_buffers=peer_expert, peer_ctrl=peer_ctrl, local_ctrl=workspace.ctrl,
+                                    generation=generation, status=self._status, budget_ns=self._wait_budget_ns)
+                dy_recv = expert_buffer[:rows]
+                arrival = workspace.ctrl[_lib.HMC_CTRL_ARRIVAL:_lib.HMC_CTRL_ARRIVAL + self.local_experts]
             row_dot = torch.zeros(rows, dtype=torch.float32, device=device)
         else:
             row_probs = row_dot = None
-            # dYe (source's expert-major order) and dProbs
-            grad_routed = torch.empty(max(routed_rows, 1), hid, **bf16)
             grad_probs = torch.empty(tokens, self.top_k, dtype=torch.float32, device=device)
-            kernels.moe_unpermute_grad(saved_last, grad_output, route.mapping, probs, self.top_k, grad_routed,
-                                       grad_probs, status=self._status)
-            if self.ep_size == 1:
+            if self._pull:
+                # dYe is written straight into the published source buffer; the owners fetch it
+                generation = workspace.begin_call()
+                dy_recv, _ = self._pull_rows(
+                    workspace, route, generation,
+                    lambda rows_out: kernels.moe_unpermute_grad(saved_last, grad_output, route.mapping, probs,
+                                                                self.top_k, rows_out, grad_probs,
+                                                                status=self._status))
+                _, peer_routed, peer_ctrl = self._peer_tables(workspace, dy_recv)
+                arrival = None
+            else:
+                # dYe (source's expert-major order) and dProbs
+                grad_routed = torch.empty(max(routed_rows, 1), hid, **bf16)
+                kernels.moe_unpermute_grad(saved_last, grad_output, route.mapping, probs, self.top_k, grad_routed,
+                                           grad_probs, status=self._status)
+            if self._pull:
+                pass
+            elif self.ep_size == 1:
                 # One rank owns every expert: the source's expert-major order IS the owner's order
                 # (the reference short-circuits peer == self the same way, rma.h:205-208), so the
                 # rows are used in place and nothing has to arrive.
@@ -794,6 +858,14 @@ class MegaMoeExperts(torch.nn.Module):
         if self.ep_size == 1 and source_of_row is None:
             return source[:max(received, 1)], None, None, None  # already in the owner's order
         generation = workspace.begin_call()
+        if self._pull:
+            if source_of_row is not None:
+                fill = lambda rows_out: kernels.moe_gather_rows(source, source_of_row, self.top_k, rows_out)  # noqa: E731
+            else:
+                fill = lambda rows_out: rows_out.copy_(source[:rows_out.shape[0]])  # noqa: E731
+            rows_in, _ = self._pull_rows(workspace, route, generation, fill)
+            _, peer_routed, peer_ctrl = self._peer_tables(workspace, rows_in)
+            return rows_in, generation, peer_routed, peer_ctrl
         if self.ep_size == 1:
             expert_buffer = torch.empty(max(received, 1), self.hidden_size, dtype=torch.bfloat16, device=device)
             capacity = expert_buffer.shape[0]

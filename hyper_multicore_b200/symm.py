@@ -40,7 +40,9 @@ class PeerWorkspace:
     """Symmetric allocation of one EP group member, with every peer's copy mapped locally."""
 
     def __init__(self, group: Any | None, hidden_size: int, capacity_rows: int, routed_rows: int,
-                 device: torch.device) -> None:
+                 device: torch.device, pull: bool = False) -> None:
+        """``pull``: the first buffer is this rank's SOURCE buffer (its own rows in expert-major order,
+        read by the owners), so it holds ``routed_rows`` rows and no receive capacity is needed."""
         self.group = group
         self.device = device
         self.hidden_size = hidden_size
@@ -48,8 +50,9 @@ class PeerWorkspace:
         self.rank = dist.get_rank(group) if group is not None else 0
         if self.ep > _lib.HMC_MAX_EP:
             raise ValueError(f"expert-parallel size {self.ep} exceeds the supported maximum {_lib.HMC_MAX_EP}")
-        self.capacity_rows = align_rows(capacity_rows)
+        self.pull = pull
         self.routed_rows = align_rows(routed_rows)
+        self.capacity_rows = self.routed_rows if pull else align_rows(capacity_rows)
         self.generation = 0
         self._base = ctypes.c_void_p()
         self._peer_bases: list[int] = []
@@ -79,10 +82,14 @@ class PeerWorkspace:
         self.routed_buffer = span[self._routed_off:routed_end].view(torch.bfloat16).view(
             self.routed_rows, hidden_size)
         self.routed_values = span[routed_end:self.nbytes].view(torch.float32)
+        # pull mode reads the same memory under the names of its role
+        self.source_buffer, self.source_values = self.expert_buffer, self.expert_values
+        self.source_plane_offset = self.expert_plane_offset
         pointer_array = ctypes.c_void_p * self.ep
         self.peer_ctrl = pointer_array(*self._peer_bases)
         self.peer_expert = pointer_array(*(base + self._expert_off for base in self._peer_bases))
         self.peer_routed = pointer_array(*(base + self._routed_off for base in self._peer_bases))
+        self.peer_source = self.peer_expert
 
     def _exchange_handles(self, lib: ctypes.CDLL) -> None:
         if self.ep == 1:

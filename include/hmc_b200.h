@@ -436,6 +436,7 @@ int hmc_mega_mhc_grad(const hmc_mega_mhc_grad_args* args, void* stream);
 #define HMC_CTRL_COMBINE 1024
 #define HMC_CTRL_READY 1040
 #define HMC_CTRL_READY_STRIDE 16
+#define HMC_CTRL_SOURCE 1296 /* + p * STRIDE: last generation peer p published its source buffer for (pull) */
 #define HMC_CTRL_WORDS 2048
 
 typedef struct hmc_ep_dispatch_args {
@@ -493,6 +494,36 @@ int hmc_ipc_open_handle(const void* handle_64_bytes, void** out);
 int hmc_ipc_close_handle(void* ptr);
 int hmc_ep_publish_ready(void* const* peer_ctrl, int64_t ep, int64_t rank, int32_t generation, void* stream);
 int hmc_ep_dispatch(const hmc_ep_dispatch_args* args, void* stream);
+
+/* Pull dispatch: the owner fetches its rows from the sources' published, expert-major source buffers
+ * (the reference's pull mode: docs/design/mega_moe_design.md:33-35, transport.h:12-42; the source buffer
+ * of hyper_multicore/modules/mega_moe/workspace.py:48-75). A source publishes with
+ * hmc_ep_publish_source once its buffer is written; the owner's kernel waits (bounded) for that flag,
+ * then copies segment (local expert, source) = source rows [source_row_off[s * local_experts + e], +n)
+ * into its own rows starting at segment_start[e * ep + s]. The receive buffer is a plain local
+ * allocation of exactly `rows` rows: pull needs no receive capacity in peer-mapped memory. The source
+ * may rewrite its buffer once its own result rows are back (every owner has read before it combines). */
+typedef struct hmc_ep_pull_args {
+  void* const* peer_sources;       /* host array [ep]: source buffer of every rank, as mapped here */
+  const int64_t* source_row_off;   /* device [ep * local_experts]: combine_target_off of hmc_route_offsets */
+  const int64_t* segment_start;    /* device [local_experts * ep]: recv_segment_start of hmc_route_offsets */
+  void* out;                       /* [rows, hidden] bf16, local */
+  float* out_values;               /* optional float[rows]: the per-row scalars of the sources */
+  int64_t rows;                    /* rows this rank receives */
+  int64_t hidden;
+  int64_t ep;
+  int64_t local_experts;
+  int64_t source_rows_limit;       /* rows of every source buffer */
+  int64_t value_plane_offset;      /* bytes from a source buffer to its float plane (with out_values) */
+  const int32_t* local_ctrl;
+  int32_t generation;
+  int32_t max_ctas;
+  uint64_t budget_ns;
+  int32_t* status;
+} hmc_ep_pull_args;
+
+int hmc_ep_publish_source(void* const* peer_ctrl, int64_t ep, int64_t rank, int32_t generation, void* stream);
+int hmc_ep_pull(const hmc_ep_pull_args* args, void* stream);
 int hmc_ep_combine(const hmc_ep_combine_args* args, void* stream);
 /* Bounded device-side wait until *counter >= expected; on time-out writes HMC_STATUS_TIMEOUT_ARRIVAL. */
 int hmc_ep_wait(const int32_t* counter, int32_t expected, uint64_t budget_ns, int32_t* status, void* stream);

@@ -144,8 +144,26 @@ def main():
     shared[0].close()
     assert shared[1]._workspace is not None
     shared[1].close()
+    # pull dispatch: owners fetch their rows from the sources' published buffers
+    from hyper_multicore_b200 import MegaMoeNumericsOptions, MegaMoeTuningOptions
+
+    pull = MegaMoeTuningOptions(dispatch_mode="pull")
+    module = MegaMoeExperts(hidden_size=hidden, intermediate_size=inter, num_experts=experts, top_k=top_k,
+                            ep_group=dist.group.WORLD, tuning_options=pull)
+    for index, counts in enumerate(([96] * world, [40 + 57 * r for r in range(world)], [0] + [64] * (world - 1),
+                                    [500] * world)):
+        scenario(module, rank, world, device, counts, hidden, inter, experts, top_k, seed=80 + index, layout="EIO")
+    assert module._workspace.pull
+    module.close()
+    before = dict(swiglu_limit=0.5, clamp_after_silu=False, apply_probs_before_fc2=True)
+    module = MegaMoeExperts(hidden_size=hidden, intermediate_size=inter, num_experts=experts, top_k=top_k,
+                            ep_group=dist.group.WORLD, tuning_options=pull,
+                            numerics_options=MegaMoeNumericsOptions(**before))
+    for index, counts in enumerate(([96] * world, [40 + 57 * r for r in range(world)])):
+        scenario(module, rank, world, device, counts, hidden, inter, experts, top_k, seed=90 + index, layout="EOI",
+                 **before)
+    module.close()
     # numerics options: clamped SwiGLU with the probabilities travelling with the rows (before FC2)
-    from hyper_multicore_b200 import MegaMoeNumericsOptions
 
     options = dict(swiglu_limit=0.5, clamp_after_silu=True, apply_probs_before_fc2=True)
     module = MegaMoeExperts(hidden_size=hidden, intermediate_size=inter, num_experts=experts, top_k=top_k,
@@ -158,6 +176,10 @@ def main():
                             ep_group=dist.group.WORLD, precision="mxfp8")
     for index, counts in enumerate(([96] * world, [40 + 57 * r for r in range(world)], [0] + [200] * (world - 1))):
         scenario_mx(module, rank, world, device, counts, hidden, inter, experts, top_k, seed=30 + index)
+    module.close()
+    module = MegaMoeExperts(hidden_size=hidden, intermediate_size=inter, num_experts=experts, top_k=top_k,
+                            ep_group=dist.group.WORLD, precision="mxfp8", tuning_options=pull)
+    scenario_mx(module, rank, world, device, [40 + 57 * r for r in range(world)], hidden, inter, experts, top_k, seed=33)
     module.close()
     dist.barrier()
     if rank == 0:
