@@ -25,6 +25,7 @@ HMC_EPI_SWIGLU = 2
 HMC_EPI_SWIGLU_GRAD = 3
 HMC_STATUS_WORDS = 8
 HMC_CTRL_SOURCE = 1296
+HMC_CTRL_COUNTS = 1552
 HMC_CLAMP_NONE, HMC_CLAMP_BEFORE_SILU, HMC_CLAMP_AFTER_SILU = 0, 1, 2
 
 STATUS_NAMES = {
@@ -173,6 +174,16 @@ class EpCombineArgs(ctypes.Structure):
     ]
 
 
+class EpExchangeArgs(ctypes.Structure):
+    """Mirror of ``hmc_ep_exchange_args``."""
+
+    _fields_ = [
+        ("counts", c_void_p), ("header", c_int32 * 4), ("peer_tables", c_void_p), ("peer_ctrl", c_void_p),
+        ("local_ctrl", c_void_p), ("ep", c_int64), ("rank", c_int64), ("experts", c_int64),
+        ("exchange", c_int32), ("reserved", c_int32), ("budget_ns", c_uint64), ("status", c_void_p),
+    ]
+
+
 class EpPullArgs(ctypes.Structure):
     """Mirror of ``hmc_ep_pull_args``."""
 
@@ -260,6 +271,8 @@ SIGNATURES: dict[str, tuple] = {
     "hmc_ipc_close_handle": (_I, [_P]),
     "hmc_ep_publish_ready": (_I, [_P, _L, _L, _I, _P]),
     "hmc_ep_publish_source": (_I, [_P, _L, _L, _I, _P]),
+    "hmc_ep_exchange_table_bytes": (_L, [_L, _L]),
+    "hmc_ep_exchange_counts": (_I, [ctypes.POINTER(EpExchangeArgs), _P]),
     "hmc_ep_pull": (_I, [ctypes.POINTER(EpPullArgs), _P]),
     "hmc_ep_dispatch": (_I, [ctypes.POINTER(EpDispatchArgs), _P]),
     "hmc_ep_combine": (_I, [ctypes.POINTER(EpCombineArgs), _P]),

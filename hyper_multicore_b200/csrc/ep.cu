@@ -203,6 +203,32 @@ ep_combine_kernel(const uint4* __restrict__ results, const long long* __restrict
   }
 }
 
+// Count exchange: every rank stores its row into every peer's table, then waits for all rows.
+__global__ void __launch_bounds__(256)
+ep_exchange_counts_kernel(const int* __restrict__ counts, int h0, int h1, int h2, int h3, PeerTable peers,
+                          const int* __restrict__ local_ctrl, int ep, int rank, int experts, int exchange,
+                          unsigned long long budget_ns, int* __restrict__ status) {
+  const long long half_words = static_cast<long long>(ep) * (experts + 4);
+  const long long base = (exchange & 1) * half_words;
+  for (int p = 0; p < ep; ++p) {
+    int* table = static_cast<int*>(peers.data[p]) + base;
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) table[static_cast<long long>(rank) * experts + e] = counts[e];
+    if (threadIdx.x < 4) {
+      const int h = threadIdx.x == 0 ? h0 : threadIdx.x == 1 ? h1 : threadIdx.x == 2 ? h2 : h3;
+      table[static_cast<long long>(ep) * experts + rank * 4 + threadIdx.x] = h;
+    }
+  }
+  __syncthreads();  // every store of this CTA is ordered before the releases below
+  if (threadIdx.x < ep)
+    st_release_sys(peers.ctrl[threadIdx.x] + HMC_CTRL_COUNTS + rank * HMC_CTRL_READY_STRIDE, exchange);
+  if (threadIdx.x < ep) {
+    int observed = 0;
+    if (!wait_counter_ge(local_ctrl + HMC_CTRL_COUNTS + threadIdx.x * HMC_CTRL_READY_STRIDE, exchange, budget_ns,
+                         &observed))
+      report_status(status, HMC_STATUS_TIMEOUT_READY, threadIdx.x, exchange, observed);
+  }
+}
+
 __global__ void ep_publish_source_kernel(PeerTable peers, int ep, int rank, int generation) {
   const int p = threadIdx.x;
   if (p < ep) st_release_sys(peers.ctrl[p] + HMC_CTRL_SOURCE + rank * HMC_CTRL_READY_STRIDE, generation);
@@ -360,6 +386,28 @@ extern "C" int hmc_ep_publish_ready(void* const* peer_ctrl, int64_t ep, int64_t 
   HMC_REQUIRE(rank >= 0 && rank < ep, HMC_ERR_INVALID, "hmc_ep_publish_ready: rank out of range");
   ep_publish_ready_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream_ptr)>>>(table, static_cast<int>(ep),
                                                                               static_cast<int>(rank), generation);
+  HMC_LAUNCH_OK();
+  return 0;
+}
+
+extern "C" int64_t hmc_ep_exchange_table_bytes(int64_t ep, int64_t experts) {
+  return 2 * ep * (experts + 4) * static_cast<int64_t>(sizeof(int));
+}
+
+extern "C" int hmc_ep_exchange_counts(const hmc_ep_exchange_args* args, void* stream_ptr) {
+  HMC_REQUIRE(args != nullptr, HMC_ERR_INVALID, "hmc_ep_exchange_counts: null args");
+  const hmc_ep_exchange_args& a = *args;
+  PeerTable table;
+  int rc = fill_peers(&table, a.peer_tables, a.peer_ctrl, a.ep);
+  if (rc != 0) return rc;
+  HMC_REQUIRE(a.counts && a.local_ctrl, HMC_ERR_INVALID, "hmc_ep_exchange_counts: null tensor pointer");
+  HMC_REQUIRE(a.rank >= 0 && a.rank < a.ep && a.experts > 0 && a.experts <= 4096, HMC_ERR_INVALID,
+              "hmc_ep_exchange_counts: bad rank or expert count");
+  HMC_REQUIRE(a.exchange > 0, HMC_ERR_INVALID, "hmc_ep_exchange_counts: exchanges are numbered from 1");
+  ep_exchange_counts_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream_ptr)>>>(
+      a.counts, a.header[0], a.header[1], a.header[2], a.header[3], table, a.local_ctrl, static_cast<int>(a.ep),
+      static_cast<int>(a.rank), static_cast<int>(a.experts), a.exchange,
+      a.budget_ns ? a.budget_ns : 10ull * 1000 * 1000 * 1000, a.status);
   HMC_LAUNCH_OK();
   return 0;
 }

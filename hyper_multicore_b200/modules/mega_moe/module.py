@@ -133,6 +133,7 @@ class _ResourceGroup:
         self.key = key
         self.members: set[int] = set()
         self.workspace: Any | None = None
+        self.control: Any | None = None  # PeerControl of an EP group: control block + count-exchange table
         self.closed = False
         self.shared = False
         self.sequence = next(_GROUP_SEQUENCE)  # creation order: the same on every rank
@@ -147,9 +148,13 @@ _DESTROY_HOOKED = False
 def _close_all_groups() -> None:
     """Release every live workspace; every rank reaches this in the same order."""
     for group in sorted(_GROUPS, key=lambda g: g.sequence):
-        if group.workspace is not None and not group.closed:
-            group.workspace.close()
-            group.workspace = None
+        if not group.closed and (group.workspace is not None or group.control is not None):
+            if group.workspace is not None:
+                group.workspace.close()
+                group.workspace = None
+            if group.control is not None:
+                group.control.close()
+                group.control = None
             group.closed = True
 
 
@@ -434,7 +439,7 @@ class MegaMoeExperts(torch.nn.Module):
                     generation = workspace.generation
                     workspace.close()
                 self._workspace = PeerWorkspace(self._ep_group, self.hidden_size, need_routed, need_routed, device,
-                                                pull=True)
+                                                pull=True, control=self._group.control)
                 self._workspace.generation = generation
             return self._workspace
         if workspace is not None and need_capacity <= workspace.capacity_rows and need_routed <= workspace.routed_rows:
@@ -457,7 +462,8 @@ class MegaMoeExperts(torch.nn.Module):
             # (reference: _grow_receive_capacity, hyper_multicore/modules/mega_moe/spec.py:113-119)
             raise ValueError("MegaMoe route exceeds the lossless token bound")
         capacity = max(need_capacity, min(capacity, bound))
-        self._workspace = PeerWorkspace(self._ep_group, self.hidden_size, capacity, routed, device)
+        self._workspace = PeerWorkspace(self._ep_group, self.hidden_size, capacity, routed, device,
+                                        control=self._group.control)
         self._workspace.generation = generation
         return self._workspace
 
@@ -473,6 +479,9 @@ class MegaMoeExperts(torch.nn.Module):
             if group.workspace is not None:
                 group.workspace.close()
                 group.workspace = None
+            if group.control is not None:
+                group.control.close()
+                group.control = None
             group.closed = True
         self._closed = True
 
@@ -521,10 +530,15 @@ class MegaMoeExperts(torch.nn.Module):
         device = hidden_flat.device
         if self._status is None:
             self._status = _lib.new_status(device)
+        if self.ep_size > 1 and self._group.control is None and os.environ.get("HMC_COUNT_EXCHANGE", "device") != "nccl":
+            from ...symm import PeerControl  # pylint: disable=import-outside-toplevel
+
+            self._group.control = PeerControl(self._ep_group, self.num_experts, device)  # collective, once
         route = prepare_route(hidden_flat, topk_ids.contiguous(), num_experts=self.num_experts, top_k=self.top_k,
                               ep_size=self.ep_size, rank=self._rank, group=self._ep_group,
                               invalid=weight_error is not None, status=self._status,
-                              autograd=self._takes_part_in_autograd(hidden_states, topk_weights, expert_weights))
+                              autograd=self._takes_part_in_autograd(hidden_states, topk_weights, expert_weights),
+                              control=self._group.control, budget_ns=self._wait_budget_ns)
         if weight_error is not None:
             raise weight_error
         if route.pending is None:

@@ -73,7 +73,7 @@ def validate_topk_inputs(hidden: torch.Tensor, topk_ids: torch.Tensor, topk_weig
 
 def prepare_route(hidden: torch.Tensor, topk_ids: torch.Tensor, *, num_experts: int, top_k: int, ep_size: int,
                   rank: int, group: Any | None, invalid: bool = False, status=None,
-                  autograd: bool = False) -> PreparedRoute:
+                  autograd: bool = False, control: Any | None = None, budget_ns: int = 0) -> PreparedRoute:
     """Sort the routes, exchange counts, derive offsets. Collective when ep_size > 1."""
     device = hidden.device
     tokens = hidden.shape[0]
@@ -96,28 +96,38 @@ def prepare_route(hidden: torch.Tensor, topk_ids: torch.Tensor, *, num_experts: 
             mapping=mapping, source_of_row=sources, expert_of_row=row_experts, counts_by_source=None,
             offsets=offsets, routed_rows=routed, received_rows=routed, max_received_rows=routed,
             max_routed_rows=routed, pending=(event, pinned, num_experts, routed))
-    payload = torch.empty(_HEADER + num_experts, dtype=torch.int32, device=device)
-    if ep_size > 1:
-        # header staged in pinned memory: a plain torch.tensor(..., device=...) copies synchronously
-        key = ("header", device)
-        stage = _PINNED.get(key)
-        if stage is None:
-            stage = _PINNED[key] = torch.empty(_HEADER, dtype=torch.int32).pin_memory()
-        stage[0], stage[1], stage[2] = int(invalid), tokens, int(autograd)
-        payload[:_HEADER].copy_(stage, non_blocking=True)
+    if control is not None:
+        # Device-initiated exchange through the peer-mapped count table: one kernel instead of staging a
+        # payload and enqueueing a host collective; the header words travel as kernel arguments.
+        table, block = control.exchange(counts, (int(invalid), tokens, int(autograd)), status, budget_ns)
+        offsets = kernels.route_offsets(table, rank)
+        flat = block.tolist()  # the one host synchronisation of the call
+        body = ep_size * num_experts
+        host = [flat[body + 4 * r: body + 4 * r + _HEADER] + flat[r * num_experts:(r + 1) * num_experts]
+                for r in range(ep_size)]
     else:
-        payload[:_HEADER] = 0
-    payload[_HEADER:] = counts
-    if ep_size > 1:
-        gathered = torch.empty(ep_size * (_HEADER + num_experts), dtype=torch.int32, device=device)
-        work = dist.all_gather_into_tensor(gathered, payload, group=group, async_op=True)
-        work.wait()
-        table_with_header = gathered.view(ep_size, _HEADER + num_experts)
-    else:
-        table_with_header = payload.view(1, _HEADER + num_experts)
-    table = table_with_header[:, _HEADER:].contiguous()
-    offsets = kernels.route_offsets(table, rank)
-    host = table_with_header.tolist()  # the one host synchronisation of the call
+        payload = torch.empty(_HEADER + num_experts, dtype=torch.int32, device=device)
+        if ep_size > 1:
+            # header staged in pinned memory: a plain torch.tensor(..., device=...) copies synchronously
+            key = ("header", device)
+            stage = _PINNED.get(key)
+            if stage is None:
+                stage = _PINNED[key] = torch.empty(_HEADER, dtype=torch.int32).pin_memory()
+            stage[0], stage[1], stage[2] = int(invalid), tokens, int(autograd)
+            payload[:_HEADER].copy_(stage, non_blocking=True)
+        else:
+            payload[:_HEADER] = 0
+        payload[_HEADER:] = counts
+        if ep_size > 1:
+            gathered = torch.empty(ep_size * (_HEADER + num_experts), dtype=torch.int32, device=device)
+            work = dist.all_gather_into_tensor(gathered, payload, group=group, async_op=True)
+            work.wait()
+            table_with_header = gathered.view(ep_size, _HEADER + num_experts)
+        else:
+            table_with_header = payload.view(1, _HEADER + num_experts)
+        table = table_with_header[:, _HEADER:].contiguous()
+        offsets = kernels.route_offsets(table, rank)
+        host = table_with_header.tolist()  # the one host synchronisation of the call
     if any(row[0] for row in host):
         bad = [r for r, row in enumerate(host) if row[0]]
         raise ValueError(f"MegaMoeExperts received invalid inputs on EP rank(s) {bad}; all ranks reject the call.")

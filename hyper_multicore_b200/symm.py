@@ -36,11 +36,102 @@ class _DeviceSpan:
         }
 
 
+def _map_peers(lib, base: ctypes.c_void_p, nbytes: int, group: Any, ep: int, rank: int):
+    """Exchange CUDA-IPC handles of one allocation; returns (addresses of every rank's copy, opened)."""
+    if ep == 1:
+        return [base.value], []
+    handle = (ctypes.c_ubyte * 64)()
+    _lib.check(lib.hmc_ipc_get_handle(base, handle))
+    gathered: list[Any] = [None] * ep
+    dist.all_gather_object(gathered, (bytes(handle), nbytes), group=group)
+    bases, opened = [], []
+    for peer, (peer_handle, peer_bytes) in enumerate(gathered):
+        if peer_bytes != nbytes:
+            raise RuntimeError("EP ranks disagree on the size of a peer-mapped allocation")
+        if peer == rank:
+            bases.append(base.value)
+            continue
+        mapped = ctypes.c_void_p()
+        raw = (ctypes.c_ubyte * 64).from_buffer_copy(peer_handle)
+        _lib.check(lib.hmc_ipc_open_handle(raw, ctypes.byref(mapped)))
+        bases.append(mapped.value)
+        opened.append(mapped.value)
+    dist.barrier(group=group)  # every rank has mapped every peer before anyone may write remotely
+    return bases, opened
+
+
+class PeerControl:
+    """The part of the peer-mapped state that outlives workspace growth: the control block and the
+    table of the count exchange. Created collectively at the first call of an EP group member
+    (the reference keeps its signal arena and route header in the symmetric heap the same way,
+    hyper_multicore/modules/mega_moe/workspace.py:409-470)."""
+
+    def __init__(self, group: Any, experts: int, device: torch.device) -> None:
+        self.group, self.device, self.experts = group, device, experts
+        self.ep = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        if self.ep > _lib.HMC_MAX_EP:
+            raise ValueError(f"expert-parallel size {self.ep} exceeds the supported maximum {_lib.HMC_MAX_EP}")
+        lib = _lib.load()
+        self._ctrl_bytes = _lib.HMC_CTRL_WORDS * 4
+        self._table_off = (self._ctrl_bytes + 1023) // 1024 * 1024
+        self._table_bytes = int(lib.hmc_ep_exchange_table_bytes(self.ep, experts))
+        self.nbytes = self._table_off + self._table_bytes
+        self._base = ctypes.c_void_p()
+        self._closed = False
+        self.generation = 0   # operator calls (dispatch / combine phases)
+        self.exchanges = 0    # count exchanges
+        with torch.cuda.device(device):
+            _lib.check(lib.hmc_symm_alloc(self.nbytes, ctypes.byref(self._base)))
+            self._peer_bases, self._opened = _map_peers(lib, self._base, self.nbytes, group, self.ep, self.rank)
+        span = torch.as_tensor(_DeviceSpan(self._base.value, self.nbytes, self), device=device)
+        self.ctrl = span[:self._ctrl_bytes].view(torch.int32)
+        self.table = span[self._table_off:self.nbytes].view(torch.int32).view(2, self.ep * (experts + 4))
+        pointer_array = ctypes.c_void_p * self.ep
+        self.peer_ctrl = pointer_array(*self._peer_bases)
+        self.peer_tables = pointer_array(*(base + self._table_off for base in self._peer_bases))
+
+    def exchange(self, counts: torch.Tensor, header: tuple[int, int, int], status, budget_ns: int):
+        """Returns (counts [ep, experts], raw block [ep * (experts + 4)]) of this exchange, on the device."""
+        from . import kernels  # pylint: disable=import-outside-toplevel
+
+        self.exchanges += 1
+        args = _lib.EpExchangeArgs()
+        args.counts = counts.data_ptr()
+        args.header[0], args.header[1], args.header[2], args.header[3] = header[0], header[1], header[2], 0
+        args.peer_tables = ctypes.cast(self.peer_tables, ctypes.c_void_p)
+        args.peer_ctrl = ctypes.cast(self.peer_ctrl, ctypes.c_void_p)
+        args.local_ctrl = self.ctrl.data_ptr()
+        args.ep, args.rank, args.experts = self.ep, self.rank, self.experts
+        args.exchange, args.budget_ns = self.exchanges, budget_ns
+        args.status = _lib.ptr(status)
+        kernels._call("hmc_ep_exchange_counts", self.device, ctypes.byref(args))  # pylint: disable=protected-access
+        block = self.table[self.exchanges & 1]
+        return block[:self.ep * self.experts].view(self.ep, self.experts), block
+
+    def close(self) -> None:
+        """Collective: unmap peers and free."""
+        if self._closed:
+            return
+        self._closed = True
+        lib = _lib.load()
+        with torch.cuda.device(self.device):
+            torch.cuda.synchronize(self.device)
+            if dist.is_initialized():
+                dist.barrier(group=self.group)
+            for mapped in self._opened:
+                lib.hmc_ipc_close_handle(ctypes.c_void_p(mapped))
+            if dist.is_initialized():
+                dist.barrier(group=self.group)
+            lib.hmc_symm_free(self._base)
+        self._opened = []
+
+
 class PeerWorkspace:
     """Symmetric allocation of one EP group member, with every peer's copy mapped locally."""
 
     def __init__(self, group: Any | None, hidden_size: int, capacity_rows: int, routed_rows: int,
-                 device: torch.device, pull: bool = False) -> None:
+                 device: torch.device, pull: bool = False, control: "PeerControl | None" = None) -> None:
         """``pull``: the first buffer is this rank's SOURCE buffer (its own rows in expert-major order,
         read by the owners), so it holds ``routed_rows`` rows and no receive capacity is needed."""
         self.group = group
@@ -87,6 +178,10 @@ class PeerWorkspace:
         self.source_plane_offset = self.expert_plane_offset
         pointer_array = ctypes.c_void_p * self.ep
         self.peer_ctrl = pointer_array(*self._peer_bases)
+        self.control = control
+        if control is not None:
+            # the control block (and the generation counter) outlive this buffer allocation
+            self.ctrl, self.peer_ctrl = control.ctrl, control.peer_ctrl
         self.peer_expert = pointer_array(*(base + self._expert_off for base in self._peer_bases))
         self.peer_routed = pointer_array(*(base + self._routed_off for base in self._peer_bases))
         self.peer_source = self.peer_expert
@@ -115,6 +210,10 @@ class PeerWorkspace:
 
     def next_generation(self) -> int:
         """Generation number of the next operator call (same sequence on every rank)."""
+        if self.control is not None:
+            self.control.generation += 1
+            self.generation = self.control.generation
+            return self.generation
         self.generation += 1
         return self.generation
 

@@ -437,6 +437,7 @@ int hmc_mega_mhc_grad(const hmc_mega_mhc_grad_args* args, void* stream);
 #define HMC_CTRL_READY 1040
 #define HMC_CTRL_READY_STRIDE 16
 #define HMC_CTRL_SOURCE 1296 /* + p * STRIDE: last generation peer p published its source buffer for (pull) */
+#define HMC_CTRL_COUNTS 1552 /* + p * STRIDE: last count exchange peer p has written its row for */
 #define HMC_CTRL_WORDS 2048
 
 typedef struct hmc_ep_dispatch_args {
@@ -522,6 +523,29 @@ typedef struct hmc_ep_pull_args {
   int32_t* status;
 } hmc_ep_pull_args;
 
+/* Count exchange without a host collective (replaces the all_gather of the route header and the
+ * per-expert counts, hyper_multicore/modules/mega_moe/route.py:214-245, 850-878): one kernel stores this
+ * rank's row {counts[experts], header[4]} into slot `rank` of every peer's table, publishes
+ * HMC_CTRL_COUNTS with release semantics and waits (bounded) until every peer's row of this exchange has
+ * arrived. A table holds two exchanges (parity = exchange & 1): {int32 counts[ep][experts];
+ * int32 header[ep][4]} each, so a fast rank never overwrites rows a slow rank still reads. */
+typedef struct hmc_ep_exchange_args {
+  const int32_t* counts;      /* device [experts]: this rank's per-expert route counts */
+  int32_t header[4];          /* this rank's header words (validity, tokens, autograd, reserved) */
+  void* const* peer_tables;   /* host array [ep]: count table of every rank, as mapped here */
+  void* const* peer_ctrl;
+  const int32_t* local_ctrl;
+  int64_t ep;
+  int64_t rank;
+  int64_t experts;
+  int32_t exchange;           /* 1, 2, 3, ...: the same sequence on every rank */
+  int32_t reserved;
+  uint64_t budget_ns;
+  int32_t* status;
+} hmc_ep_exchange_args;
+
+int64_t hmc_ep_exchange_table_bytes(int64_t ep, int64_t experts);
+int hmc_ep_exchange_counts(const hmc_ep_exchange_args* args, void* stream);
 int hmc_ep_publish_source(void* const* peer_ctrl, int64_t ep, int64_t rank, int32_t generation, void* stream);
 int hmc_ep_pull(const hmc_ep_pull_args* args, void* stream);
 int hmc_ep_combine(const hmc_ep_combine_args* args, void* stream);
