@@ -18,7 +18,9 @@ import numpy as np
 import torch
 
 HERE = Path(__file__).resolve().parent
-REFERENCE_ROOT = os.environ.get("REFERENCE_ROOT", "/root/reference")
+REFERENCE_ROOT = os.environ.get("REFERENCE_ROOT")
+if not REFERENCE_ROOT:
+    raise SystemExit("set REFERENCE_ROOT to a checkout of the reference project")
 sys.path.insert(0, REFERENCE_ROOT)
 
 from hyper_multicore.modules.mega_gate.module import MegaGate  # noqa: E402  pylint: disable=wrong-import-position
