@@ -45,7 +45,8 @@ chunk_histogram_kernel(const void* __restrict__ indices, int is_i64, long long e
 // chunk_counts[c][e] becomes the first destination row of chunk c's entries for expert e.
 __global__ void __launch_bounds__(1024)
 chunk_scan_kernel(int* __restrict__ chunk_counts, int chunks, int experts, int* __restrict__ counts_out,
-                  long long* __restrict__ ends_out, int* __restrict__ expert_of_row, long long entries) {
+                  long long* __restrict__ ends_out, int* __restrict__ expert_of_row,
+                  int* __restrict__ source_of_row, long long entries) {
   extern __shared__ int totals[];  // [experts]
   __shared__ int placed;
   for (int e = threadIdx.x; e < experts; e += blockDim.x) {
@@ -74,8 +75,10 @@ chunk_scan_kernel(int* __restrict__ chunk_counts, int chunks, int experts, int* 
   __syncthreads();
   // Rejected expert ids leave the last rows without an owner: mark them so that no consumer
   // reads a stale expert or source there.
-  if (expert_of_row != nullptr)
-    for (long long r = placed + threadIdx.x; r < entries; r += blockDim.x) expert_of_row[r] = -1;
+  for (long long r = placed + threadIdx.x; r < entries; r += blockDim.x) {
+    if (expert_of_row != nullptr) expert_of_row[r] = -1;
+    if (source_of_row != nullptr) source_of_row[r] = -1;
+  }
   for (int e = threadIdx.x; e < experts; e += blockDim.x) {
     const int base = totals[e];
     for (int c = 0; c < chunks; ++c) chunk_counts[static_cast<long long>(c) * experts + e] += base;
@@ -133,9 +136,13 @@ gather_rows_kernel(const uint4* __restrict__ tokens, const int* __restrict__ sou
   const long long row = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
   if (row >= rows) return;
   const int lane = threadIdx.x & 31;
-  const long long src = source_of_row[row] / top_k;
-  const uint4* s = tokens + src * vec_per_row;
+  const int flat = source_of_row[row];
   uint4* d = out + row * vec_per_row;
+  if (flat < 0) {  // a row without an owner (its route named no valid expert): defined contents, no read
+    for (int v = lane; v < vec_per_row; v += 32) st_cs_16(d + v, make_uint4(0, 0, 0, 0));
+    return;
+  }
+  const uint4* s = tokens + static_cast<long long>(flat / top_k) * vec_per_row;
   for (int v = lane; v < vec_per_row; v += 32) st_cs_16(d + v, ld_16(s + v));
 }
 
@@ -191,17 +198,25 @@ unpermute_kernel(const uint4* __restrict__ y, const int* __restrict__ mapping, c
   __syncthreads();
   for (int v = threadIdx.x; v < vec_per_row; v += blockDim.x) {
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    for (int k = 0; k < top_k; ++k) {
-      const int r = rows[k];
-      if (r < 0) continue;
-      const uint4 q = ld_nc_16(y + static_cast<long long>(r) * vec_per_row + v);
-      const float w = weight[k];
-      const uint32_t words[4] = {q.x, q.y, q.z, q.w};
+    for (int k0 = 0; k0 < top_k; k0 += 4) {
+      // four rows in flight: the loads do not depend on the running sum
+      uint4 q[4];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 f = unpack_bf16x2(words[j]);
-        acc[2 * j] = bf16_round(acc[2 * j] + bf16_round(f.x * w));
-        acc[2 * j + 1] = bf16_round(acc[2 * j + 1] + bf16_round(f.y * w));
+      for (int i = 0; i < 4; ++i) {
+        const int r = k0 + i < top_k ? rows[k0 + i] : -1;
+        q[i] = r >= 0 ? ld_nc_16(y + static_cast<long long>(r) * vec_per_row + v) : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        if (k0 + i >= top_k || rows[k0 + i] < 0) continue;
+        const float w = weight[k0 + i];
+        const uint32_t words[4] = {q[i].x, q[i].y, q[i].z, q[i].w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = unpack_bf16x2(words[j]);
+          acc[2 * j] = bf16_round(acc[2 * j] + bf16_round(f.x * w));
+          acc[2 * j + 1] = bf16_round(acc[2 * j + 1] + bf16_round(f.y * w));
+        }
       }
     }
     uint4 o;
@@ -424,7 +439,8 @@ extern "C" int hmc_moe_sort_routes(const void* indices, int indices_are_i64, int
                                                                chunk_counts, status);
   HMC_LAUNCH_OK();
   chunk_scan_kernel<<<1, 1024, smem, stream>>>(chunk_counts, chunks, e, counts,
-                                               reinterpret_cast<long long*>(cumulative), expert_of_row, entries);
+                                               reinterpret_cast<long long*>(cumulative), expert_of_row, source_of_row,
+                                               entries);
   HMC_LAUNCH_OK();
   chunk_rank_kernel<<<chunks, SORT_THREADS, smem, stream>>>(indices, indices_are_i64, entries, e, chunk_counts,
                                                           mapping, source_of_row, expert_of_row);

@@ -623,10 +623,19 @@ class MegaMoeExperts(torch.nn.Module):
         inter, hid = self.intermediate_size, self.hidden_size
         bf16 = dict(dtype=torch.bfloat16, device=device)
         before_fc2 = self._numerics.apply_probs_before_fc2
-        generation = workspace.begin_call()
         off = route.offsets
         pull = self._pull
-        if pull:
+        generation = workspace.begin_call() if self.ep_size > 1 else 0
+        if self.ep_size == 1 and not before_fc2:
+            # One rank owns every expert: the owner's order is the source's expert-major order, so the
+            # dispatch is a local gather with nothing to wait for (the reference short-circuits
+            # peer == self to a local copy the same way, rma.h:205-208).
+            expert_buffer = torch.empty(max(received, 1), hid, **bf16)
+            expert_values = None
+            if routed_rows > 0:
+                kernels.moe_gather_rows(hidden, route.source_of_row, self.top_k, expert_buffer[:routed_rows])
+            peer_routed = peer_ctrl = None
+        elif pull:
             sorted_probs = probs.reshape(-1).index_select(0, route.source_of_row.long()) if before_fc2 else None
             expert_buffer, expert_values = self._pull_rows(
                 workspace, route, generation,
@@ -635,6 +644,7 @@ class MegaMoeExperts(torch.nn.Module):
             _, peer_routed, peer_ctrl = self._peer_tables(workspace, expert_buffer)
         else:
             if self.ep_size == 1:
+                generation = workspace.begin_call()
                 expert_buffer, expert_values, plane_offset = self._local_rows(max(received, 1), device)
                 capacity = expert_buffer.shape[0]
             else:
@@ -654,8 +664,10 @@ class MegaMoeExperts(torch.nn.Module):
         down_proj = torch.empty(rows, hid, **bf16) if self.ep_size == 1 else None
         x_recv = expert_buffer[:rows]
         row_probs = expert_values[:rows] if before_fc2 else None
-        # pulled rows are complete in stream order and live in a tensor of their own
-        arrival = None if pull else workspace.ctrl[_lib.HMC_CTRL_ARRIVAL:_lib.HMC_CTRL_ARRIVAL + self.local_experts]
+        # pulled / locally gathered rows are complete in stream order and live in a tensor of their own
+        local_gather = self.ep_size == 1 and not before_fc2
+        arrival = None if (pull or local_gather) else \
+            workspace.ctrl[_lib.HMC_CTRL_ARRIVAL:_lib.HMC_CTRL_ARRIVAL + self.local_experts]
         saved_received = torch.empty_like(x_recv) if (self.ep_size > 1 and not pull) else x_recv
         if received > 0:
             kernels.grouped_gemm(x_recv, w1, up_proj, off["group_list"], mode=kernels.HMC_GEMM_RAGGED_M,

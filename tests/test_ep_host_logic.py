@@ -68,6 +68,16 @@ def _worker(rank: int, world: int, port: int, failures) -> None:
         assert filled[:received].eq(1).all() and filled[received:].eq(0).all(), "dispatch is not a bijection"
         ends = meta["group_list"].tolist()
         assert ends[-1] == received
+        # pull dispatch: the owner fetches segment (local expert, source) from the source's published rows at the
+        # offsets the push combine uses as targets; the result must be the buffer the push dispatch built
+        pulled = torch.full((capacity, hidden), -1.0)
+        for le in range(local):
+            for src, (src_rows, _, _) in enumerate(objects):
+                start = int(meta["combine_src_off"][src * local + le])
+                size = int(meta["combine_size"][src * local + le])
+                first = int(meta["combine_target_off"][src * local + le])
+                pulled[start:start + size] = src_rows[first:first + size]
+        assert torch.equal(pulled, buffer), "pull and push dispatch disagree on the receive layout"
         # combine back: (source, local expert) segments return to the source's expert-major rows
         returned = [None] * world
         back = []
