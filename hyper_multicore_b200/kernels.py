@@ -116,6 +116,17 @@ def grouped_gemm(
         _lib.check(_lib.load().hmc_grouped_gemm(ctypes.byref(args), _lib.stream_ptr(device)))
 
 
+def store_words(dst: torch.Tensor, src: torch.Tensor) -> None:
+    """dst[:] = src for int32 tensors, by a kernel. ``dst`` may be pinned host memory: the read-back then
+    does not wait behind bulk device-to-host copies queued in a copy engine."""
+    if dst.dtype != torch.int32 or src.dtype != torch.int32 or dst.numel() < src.numel():
+        raise ValueError("store_words copies int32 words into a tensor at least as large")
+    if not (dst.is_cuda or dst.is_pinned()):
+        raise ValueError("store_words writes device or pinned host memory")
+    device = _require_cuda(src)
+    _call("hmc_store_words", device, dst.data_ptr(), src.data_ptr(), src.numel())
+
+
 def grouped_gemm_combine_units(n: int) -> int:
     """Counter increments per result row of a fused-combine GEMM with ``n`` output columns."""
     return int(_lib.load().hmc_grouped_gemm_combine_units(n))
@@ -456,7 +467,7 @@ KERNELS_PER_CALL = {
     "hmc_moe_permute_from_mapping": 1, "hmc_moe_unpermute": 1, "hmc_moe_unpermute_grad": 1,
     "hmc_moe_token_permute_grad": 1, "hmc_zero_empty_expert_grad": 1, "hmc_route_offsets": 1,
     "hmc_mega_mhc": 5, "hmc_mega_mhc_grad": 8, "hmc_ep_publish_ready": 1, "hmc_ep_dispatch": 1,
-    "hmc_ep_combine": 1, "hmc_ep_wait": 1, "hmc_ep_wait_groups": 1, "hmc_ep_publish_source": 1, "hmc_ep_pull": 1,
+    "hmc_ep_combine": 1, "hmc_ep_wait": 1, "hmc_ep_wait_groups": 1, "hmc_ep_publish_source": 1, "hmc_ep_pull": 1, "hmc_store_words": 1,
 }
 
 

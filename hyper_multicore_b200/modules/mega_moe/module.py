@@ -541,7 +541,13 @@ class MegaMoeExperts(torch.nn.Module):
                               control=self._group.control, budget_ns=self._wait_budget_ns)
         if weight_error is not None:
             raise weight_error
-        if route.pending is None:
+        if route.status_words is not None:
+            # read together with the count table: earlier kernels' status words are final
+            if route.status_words[0] != 0:
+                code = route.status_words[0]
+                raise _lib.HmcError(f"MegaMoeExperts: device status {code} ({_lib.STATUS_NAMES.get(code, '?')}), "
+                                    f"detail {route.status_words[1:4]}")
+        elif route.pending is None:
             # prepare_route just synchronised with the device, so earlier kernels' status words are final
             self.check_status()
         if self._layout is None:

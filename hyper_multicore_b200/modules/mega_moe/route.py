@@ -35,6 +35,7 @@ class PreparedRoute:
     max_received_rows: int         # over the group
     max_routed_rows: int           # over the group
     pending: Any = None            # single-rank calls: (event, pinned counts + status words) checked by finish()
+    status_words: Any = None       # multi-rank calls with the device exchange: status words read with the table
 
     def finish(self, what: str = "MegaMoeExperts") -> None:
         """Single-rank calls validate here, after the layer's kernels have been queued.
@@ -87,8 +88,10 @@ def prepare_route(hidden: torch.Tensor, topk_ids: torch.Tensor, *, num_experts: 
         pinned = _PINNED.get(key)
         if pinned is None:
             pinned = _PINNED[key] = torch.empty(num_experts + status.numel(), dtype=torch.int32).pin_memory()
-        pinned[:num_experts].copy_(counts, non_blocking=True)
-        pinned[num_experts:].copy_(status, non_blocking=True)
+        # written by kernels, not by a copy engine: this read-back must not queue behind the caller's
+        # own bulk device-to-host copies
+        kernels.store_words(pinned[:num_experts], counts)
+        kernels.store_words(pinned[num_experts:], status)
         event = torch.cuda.Event()
         event.record()
         routed = tokens * top_k
@@ -101,11 +104,22 @@ def prepare_route(hidden: torch.Tensor, topk_ids: torch.Tensor, *, num_experts: 
         # payload and enqueueing a host collective; the header words travel as kernel arguments.
         table, block = control.exchange(counts, (int(invalid), tokens, int(autograd)), status, budget_ns)
         offsets = kernels.route_offsets(table, rank)
-        flat = block.tolist()  # the one host synchronisation of the call
+        words = status.numel() if status is not None else 0
+        key = ("table", device, block.numel() + words)
+        staged = _PINNED.get(key)
+        if staged is None:
+            staged = _PINNED[key] = torch.empty(block.numel() + words, dtype=torch.int32).pin_memory()
+        kernels.store_words(staged[:block.numel()], block)
+        if words:
+            kernels.store_words(staged[block.numel():], status)
+        torch.cuda.current_stream(device).synchronize()  # the one host synchronisation of the call
+        flat = staged.tolist()
+        read_status = flat[block.numel():] if words else None
         body = ep_size * num_experts
         host = [flat[body + 4 * r: body + 4 * r + _HEADER] + flat[r * num_experts:(r + 1) * num_experts]
                 for r in range(ep_size)]
     else:
+        read_status = None
         payload = torch.empty(_HEADER + num_experts, dtype=torch.int32, device=device)
         if ep_size > 1:
             # header staged in pinned memory: a plain torch.tensor(..., device=...) copies synchronously
@@ -146,4 +160,4 @@ def prepare_route(hidden: torch.Tensor, topk_ids: torch.Tensor, *, num_experts: 
     return PreparedRoute(
         mapping=mapping, source_of_row=sources, expert_of_row=row_experts, counts_by_source=host_counts,
         offsets=offsets, routed_rows=tokens * top_k, received_rows=received[rank],
-        max_received_rows=max(received), max_routed_rows=max(routed))
+        max_received_rows=max(received), max_routed_rows=max(routed), status_words=read_status)

@@ -546,6 +546,10 @@ typedef struct hmc_ep_exchange_args {
 
 int64_t hmc_ep_exchange_table_bytes(int64_t ep, int64_t experts);
 int hmc_ep_exchange_counts(const hmc_ep_exchange_args* args, void* stream);
+/* Copies `words` int32 from device memory to `dst` with a kernel (plain stores). `dst` may be pinned host
+ * memory (device-accessible under unified addressing): small read-backs such as the route counts then do
+ * not queue behind bulk device-to-host copies in a copy engine. No counterpart in the reference. */
+int hmc_store_words(int32_t* dst, const int32_t* src, int64_t words, void* stream);
 int hmc_ep_publish_source(void* const* peer_ctrl, int64_t ep, int64_t rank, int32_t generation, void* stream);
 int hmc_ep_pull(const hmc_ep_pull_args* args, void* stream);
 int hmc_ep_combine(const hmc_ep_combine_args* args, void* stream);
