@@ -323,13 +323,15 @@ def run_gpu(args) -> None:
             load(slot)
         main.wait_event(slot["loaded"])
         main.wait_event(slot["stored"])  # the results of the step that used this slot before are out
+        # queued before this step's kernels (the host waits for the device inside the module's route
+        # preparation): the next step's inputs travel while this step computes
+        load(other)
         w1.grad = w2.grad = None
         x = slot["in"][0].detach().requires_grad_(True)
         p = slot["in"][2].detach().requires_grad_(True)
         out = module(x, slot["in"][1], p, expert_weights=(w1, w2))
         out.backward(slot["in"][3])
         slot["computed"].record(main)
-        load(other)  # next step's inputs travel while this step computes
         results = (out.detach(), x.grad, p.grad)
         with torch.cuda.stream(copy_out):
             copy_out.wait_event(slot["computed"])
