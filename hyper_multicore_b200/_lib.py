@@ -205,7 +205,7 @@ class MxGemmArgs(ctypes.Structure):
         ("max_ctas", c_int32), ("reserved", c_int32),
         ("rows", c_int64), ("pad_blocks", c_int64), ("m", c_int64), ("n", c_int64), ("k", c_int64),
         ("a", c_void_p), ("a_scale", c_void_p), ("b", c_void_p), ("b_scale", c_void_p), ("c", c_void_p),
-        ("group_ends", c_void_p), ("status", c_void_p),
+        ("group_ends", c_void_p), ("status", c_void_p), ("combine", c_void_p),
     ]
 
 
@@ -245,6 +245,7 @@ SIGNATURES: dict[str, tuple] = {
     "hmc_grouped_gemm": (_I, [ctypes.POINTER(GroupedGemmArgs), _P]),
     "hmc_grouped_gemm_combine_units": (_L, [_L]),
     "hmc_mx_gemm": (_I, [ctypes.POINTER(MxGemmArgs), _P]),
+    "hmc_mx_gemm_combine_units": (_L, [_L]),
     "hmc_mx_quant": (_I, [ctypes.POINTER(MxQuantArgs), _P]),
     "hmc_mx_quant_weight": (_I, [_P, _L, _L, _L, _P, _P, _P, _P, _P]),
     "hmc_mx_pack_weight_scale": (_I, [_P, _I, _L, _L, _L, _P, _P]),

@@ -164,4 +164,16 @@ __device__ __forceinline__ bool wait_counter_ge(const int* counter, int expected
 
 #endif  // __CUDACC__
 
+// Result rows that leave the epilogue for their source ranks (fused combine).
+struct CombineFuse {
+  const long long* segment_start;       // [local_experts * ep] first row of (local expert, source)
+  const long long* combine_target_off;  // [ep * local_experts]
+  void* peer_data[HMC_MAX_EP];          // routed buffer of every rank
+  int* peer_ctrl[HMC_MAX_EP];           // control block of every rank
+  long long target_rows_limit;
+  int ep;
+  int local_experts;
+};
+
+
 }  // namespace hmc

@@ -29,17 +29,6 @@ constexpr uint32_t SWIZZLE_128B = 2;
 
 constexpr uint64_t PIPE_BUDGET_NS = 4ull * 1000 * 1000 * 1000;  // intra-kernel barrier waits
 
-// Result rows that leave the epilogue for their source ranks (fused combine).
-struct CombineFuse {
-  const long long* segment_start;       // [local_experts * ep] first row of (local expert, source)
-  const long long* combine_target_off;  // [ep * local_experts]
-  void* peer_data[HMC_MAX_EP];          // routed buffer of every rank
-  int* peer_ctrl[HMC_MAX_EP];           // control block of every rank
-  long long target_rows_limit;
-  int ep;
-  int local_experts;
-};
-
 struct Params {
   int mode;      // HMC_GEMM_RAGGED_M / HMC_GEMM_RAGGED_K
   int epilogue;  // HMC_EPI_*

@@ -56,6 +56,8 @@ struct Params {
   const uint8_t* b_scale;
   void* c;
   int* status;
+  int combine_enabled;  // RAGGED_M: rows go to `combine` destinations instead of c
+  CombineFuse combine;
 };
 
 struct Tile {
@@ -349,28 +351,75 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
           store_pending = true;
         }
       } else {
-        // rows are written in the un-padded layout; rows of the tile past the group's end are padding
+        // Rows are written in the un-padded layout (rows of the tile past the group's end are padding),
+        // either into c or - fused combine - into the routed buffers of their source ranks. Each lane
+        // finds the destination of its own row; the 32 x 64-column piece is staged in shared memory so
+        // that every store instruction writes whole 128-byte pieces of four rows.
         const long long out_row = t.row0 + static_cast<long long>(t.m_idx) * BM + row_in_tile;
         const bool row_ok = out_row < t.row1;
-        __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.c) + out_row * p.n + col_base;
-#pragma unroll 1
-        for (int c = c_lo; c < c_hi; c += 32) {
+        unsigned long long dst_bits = 0;
+        int source = -1;
+        if (row_ok) {
+          if (p.combine_enabled) {
+            const CombineFuse& cf = p.combine;
+            const long long* seg = cf.segment_start + static_cast<long long>(t.group) * cf.ep;
+            int s = 0;
+            for (int q = 1; q < cf.ep; ++q)
+              if (seg[q] <= out_row) s = q;
+            const long long dest = cf.combine_target_off[s * cf.local_experts + t.group] + (out_row - seg[s]);
+            if (dest >= 0 && dest < cf.target_rows_limit) {
+              source = s;
+              dst_bits = reinterpret_cast<unsigned long long>(static_cast<__nv_bfloat16*>(cf.peer_data[s]) +
+                                                              dest * p.n + col_base);
+            } else {
+              report_status(p.status, HMC_STATUS_BAD_INDEX, static_cast<int>(out_row), s, static_cast<int>(dest));
+            }
+          } else {
+            dst_bits = reinterpret_cast<unsigned long long>(static_cast<__nv_bfloat16*>(p.c) + out_row * p.n + col_base);
+          }
+        }
+        if (store_pending) {  // an earlier weight-gradient tile may still be reading the stage
+          if (lane == 0) bulk_wait_read_all();
+          __syncwarp();
+          store_pending = false;
+        }
+        {
+          const int c = c_lo;  // one 64-column step per warp
           uint32_t v[32];
+          uint32_t w[32];
           tmem_ld_32x32(taddr + c, v);
+          tmem_ld_32x32(taddr + c + 32, w);
           tmem_ld_wait();
-          if (row_ok) {
+          uint8_t* row_base = my_stage + lane * 128;
 #pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              if (col_base + c + j < p.n) {
-                uint4 o;
-                o.x = pack_bf16x2(__uint_as_float(v[j + 0]), __uint_as_float(v[j + 1]));
-                o.y = pack_bf16x2(__uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
-                o.z = pack_bf16x2(__uint_as_float(v[j + 4]), __uint_as_float(v[j + 5]));
-                o.w = pack_bf16x2(__uint_as_float(v[j + 6]), __uint_as_float(v[j + 7]));
-                *reinterpret_cast<uint4*>(dst + c + j) = o;
-              }
+          for (int q = 0; q < 8; ++q) {
+            const uint32_t* src = q < 4 ? v + 8 * q : w + 8 * (q - 4);
+            uint4 o;
+            o.x = pack_bf16x2(__uint_as_float(src[0]), __uint_as_float(src[1]));
+            o.y = pack_bf16x2(__uint_as_float(src[2]), __uint_as_float(src[3]));
+            o.z = pack_bf16x2(__uint_as_float(src[4]), __uint_as_float(src[5]));
+            o.w = pack_bf16x2(__uint_as_float(src[6]), __uint_as_float(src[7]));
+            *reinterpret_cast<uint4*>(row_base + ((q ^ (lane & 7)) << 4)) = o;
+          }
+          __syncwarp();
+          const int sub = lane >> 3;
+          const int piece = lane & 7;
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            const int r = i + sub;
+            const unsigned long long base = __shfl_sync(0xffffffffu, dst_bits, r);
+            if (base != 0) {
+              const uint4 val = *reinterpret_cast<const uint4*>(my_stage + r * 128 + ((piece ^ (r & 7)) << 4));
+              st_16(reinterpret_cast<uint8_t*>(base) + c * 2 + piece * 16, val);
             }
           }
+          __syncwarp();
+        }
+        if (p.combine_enabled) {
+          // one release-add per destination per warp; the warp barrier above orders the lanes' stores
+          const unsigned same = __match_any_sync(0xffffffffu, source);
+          if (source >= 0 && lane == __ffs(same) - 1)
+            red_release_sys_add(p.combine.peer_ctrl[source] + HMC_CTRL_COMBINE, __popc(same));
         }
       }
       tc_fence_before_sync();
@@ -449,6 +498,11 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, 
 }  // namespace
 }  // namespace hmc
 
+extern "C" int64_t hmc_mx_gemm_combine_units(int64_t n) {
+  // every (32-row, half-tile) piece of every 128-column tile reports its rows once
+  return 2 * ((n + 127) / 128);
+}
+
 extern "C" int hmc_mx_gemm(const hmc_mx_gemm_args* args, void* stream_ptr) {
   using namespace hmc;
   HMC_REQUIRE(args != nullptr, HMC_ERR_INVALID, "hmc_mx_gemm: null args");
@@ -460,7 +514,7 @@ extern "C" int hmc_mx_gemm(const hmc_mx_gemm_args* args, void* stream_ptr) {
               "hmc_mx_gemm: groups and pad_blocks must be positive, rows non-negative");
   HMC_REQUIRE(a.pad_blocks >= (a.rows + 127) / 128 && a.pad_blocks * 128 < (1ll << 31), HMC_ERR_INVALID,
               "hmc_mx_gemm: pad_blocks (%lld) cannot hold %lld rows", (long long)a.pad_blocks, (long long)a.rows);
-  HMC_REQUIRE(a.a && a.b && a.c && a.a_scale && a.b_scale && a.group_ends, HMC_ERR_INVALID,
+  HMC_REQUIRE(a.a && a.b && (a.c || a.combine) && a.a_scale && a.b_scale && a.group_ends, HMC_ERR_INVALID,
               "hmc_mx_gemm: null tensor pointer");
   HMC_REQUIRE(aligned16(a.a) && aligned16(a.b) && aligned16(a.c) && aligned16(a.a_scale) && aligned16(a.b_scale),
               HMC_ERR_INVALID, "hmc_mx_gemm: tensors must be 16-byte aligned");
@@ -481,6 +535,26 @@ extern "C" int hmc_mx_gemm(const hmc_mx_gemm_args* args, void* stream_ptr) {
   p.status = a.status;
   p.n = static_cast<int>(a.n);
   p.n_tiles = static_cast<int>(a.n / BN);
+  if (a.combine != nullptr) {
+    const hmc_gemm_combine& cb = *a.combine;
+    HMC_REQUIRE(a.mode == HMC_GEMM_RAGGED_M, HMC_ERR_INVALID, "hmc_mx_gemm: the fused combine belongs to RAGGED_M GEMMs");
+    HMC_REQUIRE(cb.ep >= 1 && cb.ep <= HMC_MAX_EP && cb.local_experts == a.groups, HMC_ERR_INVALID,
+                "hmc_mx_gemm: combine needs 1 <= ep <= %d and local_experts == groups", HMC_MAX_EP);
+    HMC_REQUIRE(cb.segment_start && cb.combine_target_off && cb.peer_buffers && cb.peer_ctrl && cb.target_rows_limit > 0,
+                HMC_ERR_INVALID, "hmc_mx_gemm: null combine table");
+    for (int r = 0; r < cb.ep; ++r) {
+      HMC_REQUIRE(cb.peer_buffers[r] != nullptr && cb.peer_ctrl[r] != nullptr && aligned16(cb.peer_buffers[r]),
+                  HMC_ERR_INVALID, "hmc_mx_gemm: peer %d has no 16-byte aligned routed buffer / control block", r);
+      p.combine.peer_data[r] = cb.peer_buffers[r];
+      p.combine.peer_ctrl[r] = static_cast<int*>(cb.peer_ctrl[r]);
+    }
+    p.combine.segment_start = reinterpret_cast<const long long*>(cb.segment_start);
+    p.combine.combine_target_off = reinterpret_cast<const long long*>(cb.combine_target_off);
+    p.combine.target_rows_limit = cb.target_rows_limit;
+    p.combine.ep = static_cast<int>(cb.ep);
+    p.combine.local_experts = static_cast<int>(cb.local_experts);
+    p.combine_enabled = 1;
+  }
   const cuuint64_t pad_rows = static_cast<cuuint64_t>(a.pad_blocks) * 128;
 
   CUtensorMap ta, tb, tc;

@@ -482,9 +482,26 @@ def mx_pad_blocks(rows: int, groups: int) -> int:
     return (rows + 127) // 128 + groups
 
 
+def _combine_struct(combine: dict):
+    fused = _lib.GemmCombine()
+    fused.segment_start = combine["segment_start"].data_ptr()
+    fused.combine_target_off = combine["combine_target_off"].data_ptr()
+    fused.peer_buffers = ctypes.cast(combine["peer_buffers"], ctypes.c_void_p)
+    fused.peer_ctrl = ctypes.cast(combine["peer_ctrl"], ctypes.c_void_p)
+    fused.ep, fused.local_experts = combine["ep"], combine["local_experts"]
+    fused.target_rows_limit = combine["target_rows_limit"]
+    return fused
+
+
+def mx_gemm_combine_units(n: int) -> int:
+    """Counter increments per result row of a fused-combine MX GEMM with ``n`` output columns."""
+    return int(_lib.load().hmc_mx_gemm_combine_units(n))
+
+
 def mx_gemm(a, a_scale, b, b_scale, c, group_ends, *, mode, rows, pad_blocks, n, k=0, m=0,
-            b_major=HMC_MAJOR_MN, epilogue=HMC_EPI_STORE_BF16, status=None, max_ctas=0) -> None:
-    """Block-scaled FP8 grouped GEMM; see ``hmc_mx_gemm_args`` for the operand layouts."""
+            b_major=HMC_MAJOR_MN, epilogue=HMC_EPI_STORE_BF16, status=None, max_ctas=0, combine=None) -> None:
+    """Block-scaled FP8 grouped GEMM; see ``hmc_mx_gemm_args`` for the operand layouts. ``combine`` as in
+    ``grouped_gemm``: the rows leave the epilogue for their source ranks and ``c`` may be None."""
     device = _require_cuda(a, a_scale, b, b_scale, c, group_ends, status)
     args = _lib.MxGemmArgs()
     args.mode, args.b_major, args.epilogue = mode, b_major, epilogue
@@ -492,9 +509,13 @@ def mx_gemm(a, a_scale, b, b_scale, c, group_ends, *, mode, rows, pad_blocks, n,
     args.rows, args.pad_blocks, args.m, args.n, args.k = rows, pad_blocks, m, n, k
     args.a, args.a_scale = a.data_ptr(), a_scale.data_ptr()
     args.b, args.b_scale = b.data_ptr(), b_scale.data_ptr()
-    args.c = c.data_ptr()
+    args.c = _lib.ptr(c)
     args.group_ends = group_ends.data_ptr()
     args.status = _lib.ptr(status)
+    fused = None
+    if combine is not None:
+        fused = _combine_struct(combine)
+        args.combine = ctypes.cast(ctypes.pointer(fused), ctypes.c_void_p)
     _call("hmc_mx_gemm", device, ctypes.byref(args))
 
 

@@ -915,12 +915,19 @@ class MegaMoeExperts(torch.nn.Module):
         kernels.ep_wait_groups(arrival, off["group_list"], status=self._status, budget_ns=self._wait_budget_ns)
         return expert_buffer[:max(received, 1)], generation, peer_routed, peer_ctrl
 
-    def _mx_return(self, rows_tensor, route, generation, peer_routed, peer_ctrl):
-        """Combine result rows back to their sources (identity at ep_size == 1)."""
+    def _mx_return(self, rows_tensor, route, generation, peer_routed, peer_ctrl, width=None):
+        """Combine result rows back to their sources (identity at ep_size == 1). With `rows_tensor` None
+        the rows already left from the producing GEMM's epilogue (`width` columns): only wait for this
+        rank's own rows."""
         if self.ep_size == 1:
             return rows_tensor
         workspace = self._workspace
         off = route.offsets
+        if rows_tensor is None:
+            kernels.ep_wait(workspace.ctrl[_lib.HMC_CTRL_COMBINE:],
+                            route.routed_rows * kernels.mx_gemm_combine_units(width), status=self._status,
+                            budget_ns=self._wait_budget_ns)
+            return workspace.routed_buffer
         kernels.ep_combine(rows_tensor, off["recv_segment_start"], off["combine_target_off"], rows=route.received_rows,
                            ep=self.ep_size, local_experts=self.local_experts,
                            target_rows_limit=workspace.routed_rows, peer_buffers=peer_routed, peer_ctrl=peer_ctrl,
@@ -940,7 +947,8 @@ class MegaMoeExperts(torch.nn.Module):
         training = self._backward_expected
         x_recv, generation, peer_routed, peer_ctrl = self._mx_exchange(hidden, route.source_of_row, route)
         up_proj = torch.empty(rows, 2 * inter, **bf16)
-        down_proj = torch.empty(rows, hid, **bf16)
+        fused = self._fused_combine(self._workspace, route.offsets, peer_routed, peer_ctrl)
+        down_proj = torch.empty(rows, hid, **bf16) if fused is None else None
         x_q = act_q = None
         if received > 0:
             x_q = kernels.mx_quant(x_recv[:received], ends, hid, want_row=True, want_col=training)
@@ -951,8 +959,8 @@ class MegaMoeExperts(torch.nn.Module):
                                      want_col=training)
             kernels.mx_gemm(act_q.row_data, act_q.row_scale, root2.col_data, self._atoms(root2, "col", (local, inter, hid)),
                             down_proj, ends, mode=kernels.HMC_GEMM_RAGGED_M, rows=received, pad_blocks=act_q.pad_blocks,
-                            n=hid, k=inter, b_major=kernels.HMC_MAJOR_MN, status=self._status)
-        returned = self._mx_return(down_proj, route, generation, peer_routed, peer_ctrl)
+                            n=hid, k=inter, b_major=kernels.HMC_MAJOR_MN, status=self._status, combine=fused)
+        returned = self._mx_return(down_proj, route, generation, peer_routed, peer_ctrl, width=hid)
         routed_out = returned if self.ep_size == 1 else returned[:max(route.routed_rows, 1)].clone()
         out = torch.empty(hidden.shape[0], hid, **bf16)
         kernels.moe_unpermute(routed_out, route.mapping, probs, hidden.shape[0], self.top_k, out, status=self._status)
@@ -986,7 +994,8 @@ class MegaMoeExperts(torch.nn.Module):
         shape1, shape2 = (local, hid, 2 * inter), (local, inter, hid)
         grad_w1 = torch.empty(shape1, dtype=wdtype, device=device) if need_weight_grads[0] else None
         grad_w2 = torch.empty(shape2, dtype=wdtype, device=device) if need_weight_grads[1] else None
-        grad_x_rows = torch.empty(rows, hid, **bf16)
+        fused = self._fused_combine(self._workspace, route.offsets, peer_routed, peer_ctrl)
+        grad_x_rows = torch.empty(rows, hid, **bf16) if fused is None else None
         if received > 0:
             want_col = grad_w1 is not None or grad_w2 is not None
             dy_q = kernels.mx_quant(dy_recv[:received], ends, hid, want_row=True, want_col=want_col)
@@ -999,7 +1008,7 @@ class MegaMoeExperts(torch.nn.Module):
                                     aux=up_proj[:received], want_row=True, want_col=want_col)
             kernels.mx_gemm(du_q.row_data, du_q.row_scale, root1.row_data, self._atoms(root1, "row", shape1), grad_x_rows,
                             ends, mode=kernels.HMC_GEMM_RAGGED_M, rows=received, pad_blocks=du_q.pad_blocks, n=hid,
-                            k=2 * inter, b_major=kernels.HMC_MAJOR_K, status=self._status)
+                            k=2 * inter, b_major=kernels.HMC_MAJOR_K, status=self._status, combine=fused)
             if grad_w2 is not None:
                 kernels.mx_gemm(act_col, act_col_scale, dy_q.col_data, dy_q.col_scale, grad_w2, ends,
                                 mode=kernels.HMC_GEMM_RAGGED_K, rows=received, pad_blocks=dy_q.pad_blocks, m=inter, n=hid,
@@ -1012,7 +1021,7 @@ class MegaMoeExperts(torch.nn.Module):
             for grad in (grad_w1, grad_w2):
                 if grad is not None:
                     grad.zero_()
-        returned = self._mx_return(grad_x_rows, route, generation, peer_routed, peer_ctrl)
+        returned = self._mx_return(grad_x_rows, route, generation, peer_routed, peer_ctrl, width=hid)
         grad_hidden = torch.empty(tokens, hid, **bf16)
         kernels.moe_token_permute_grad(returned, route.mapping, tokens, self.top_k, grad_hidden, status=self._status)
         if grad_w1 is not None:

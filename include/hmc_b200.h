@@ -163,9 +163,12 @@ typedef struct hmc_mx_gemm_args {
   void* c;            /* RAGGED_M: bf16 [rows, n] in the UN-padded layout. RAGGED_K: [groups, m, n] */
   const int64_t* group_ends; /* device int64[groups], cumulative un-padded row ends */
   int32_t* status;
+  const hmc_gemm_combine* combine; /* optional, RAGGED_M: rows go to their source ranks (see hmc_gemm_combine);
+                                      c may then be NULL; counter units per row: hmc_mx_gemm_combine_units(n) */
 } hmc_mx_gemm_args;
 
 int hmc_mx_gemm(const hmc_mx_gemm_args* args, void* stream);
+int64_t hmc_mx_gemm_combine_units(int64_t n);
 
 #define HMC_MXQ_PLAIN 0       /* quantise src[rows, width] */
 #define HMC_MXQ_SWIGLU 1      /* src = U[rows, 2*width]; quantise bf16(silu(gate) * up) */
