@@ -249,6 +249,8 @@ SIGNATURES: dict[str, tuple] = {
     "hmc_mx_quant": (_I, [ctypes.POINTER(MxQuantArgs), _P]),
     "hmc_mx_quant_weight": (_I, [_P, _L, _L, _L, _P, _P, _P, _P, _P]),
     "hmc_mx_pack_weight_scale": (_I, [_P, _I, _L, _L, _L, _P, _P]),
+    "hmc_gate_project_promoted_workspace_bytes": (_L, [_L, _L]),
+    "hmc_gate_project_promoted": (_I, [_P, _P, _I, _L, _L, _L, _P, _P, _L, _P, _P]),
     "hmc_gate_route": (_I, [ctypes.POINTER(GateRouteArgs), _P]),
     "hmc_gate_route_grad": (_I, [ctypes.POINTER(GateRouteGradArgs), _P]),
     "hmc_gate_project": (_I, [_P, _I, _P, _I, _L, _L, _L, _P, _P]),

@@ -1,0 +1,363 @@
+// Router projection logits[T, E] = float(x[T, H]) . W[E, H]^T on tcgen05 with FP32-level accuracy.
+//
+// Replaces the FP32 projection of MegaGate (hyper_multicore/modules/mega_gate/function.py:175-178,
+// module.py:195-198) for BF16 hidden states. x is exact in BF16; the FP32 weight is split into three
+// BF16 parts hi + mid + lo that reproduce it to 24 bits, so every product is exact in FP32 and the
+// only error left is the accumulation inside the tensor core, which grows with the length of the
+// accumulation chain. The chain of the dominant (hi) part is therefore cut every 128 elements of K:
+// two TMEM accumulators alternate, and while the tensor core fills one, the epilogue warps add the
+// other into FP32 registers (round-to-nearest adds on the CUDA cores). The mid and lo parts are
+// 2^-8 and 2^-16 of the result, so their single long chain adds nothing measurable.
+//
+// One CTA per 128 tokens x 64 experts (x K-slice): warp 0 = TMA producer, warp 1 = MMA issuer and TMEM
+// owner, warps 2..5 = promotion + epilogue (one per TMEM lane quarter).
+#include <cuda.h>
+
+#include "common.cuh"
+#include "sm100.cuh"
+
+namespace hmc {
+namespace {
+
+using namespace sm100;
+
+constexpr int GM = 128;                      // tokens per CTA
+constexpr int GN = 64;                       // experts per CTA
+constexpr int GK = 64;                       // K elements per pipeline stage (128-byte rows)
+constexpr int G_STAGES = 4;
+constexpr int G_PROMOTE = 2;                 // stages per accumulation chain of the hi part (128 K elements)
+constexpr int A_BYTES = GM * GK * 2;         // 16 KiB
+constexpr int B_BYTES = GN * GK * 2;         // 8 KiB per weight part
+constexpr int G_STAGE_BYTES = A_BYTES + 3 * B_BYTES;
+constexpr int G_THREADS = 6 * 32;
+constexpr int G_SMEM_BYTES = G_STAGES * G_STAGE_BYTES + 1024 + 256;
+constexpr uint32_t G_TMEM_COLS = 256;        // hi[0] @0, hi[1] @64, mid+lo @128
+constexpr uint32_t SWIZZLE_128B = 2;
+constexpr uint64_t G_BUDGET_NS = 4ull * 1000 * 1000 * 1000;
+
+struct GateParams {
+  long long tokens;
+  int hidden;
+  int experts;
+  int epad;        // experts rounded up to GN: row pitch between the weight parts
+  int parts;       // 3 for FP32 weights, 1 for BF16 weights
+  int k_blocks;    // ceil(hidden / GK)
+  int k_per_slice; // k-blocks per K-slice (gridDim.z slices)
+  float* logits;
+  int* status;
+};
+
+// FP32 (or BF16) weight [E, H] -> BF16 parts stacked as rows [part * epad + e] of a [parts * epad, H] matrix
+__global__ void gate_split_parts_kernel(const void* __restrict__ w, int w_is_bf16, int experts, int epad, int parts,
+                                        long long hidden, __nv_bfloat16* __restrict__ split) {
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= static_cast<long long>(epad) * hidden) return;
+  const int e = static_cast<int>(i / hidden);
+  float v = 0.f;
+  if (e < experts)
+    v = w_is_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(w)[i]) : static_cast<const float*>(w)[i];
+  const __nv_bfloat16 hi = __float2bfloat16_rn(v);
+  split[i] = hi;
+  if (parts == 3) {
+    const float r1 = v - __bfloat162float(hi);
+    const __nv_bfloat16 mid = __float2bfloat16_rn(r1);
+    split[static_cast<long long>(epad) * hidden + i] = mid;
+    split[2ll * epad * hidden + i] = __float2bfloat16_rn(r1 - __bfloat162float(mid));
+  }
+}
+
+__global__ void __launch_bounds__(G_THREADS, 1)
+gate_project_promoted_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
+                             const GateParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + G_STAGES * G_STAGE_BYTES);
+  uint64_t* full_bar = bars;                       // [G_STAGES]
+  uint64_t* empty_bar = bars + G_STAGES;           // [G_STAGES]
+  uint64_t* hi_full_bar = bars + 2 * G_STAGES;     // [2]
+  uint64_t* hi_empty_bar = bars + 2 * G_STAGES + 2;  // [2]
+  uint64_t* ml_full_bar = bars + 2 * G_STAGES + 4;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * G_STAGES + 5);
+  volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int m0 = blockIdx.x * GM;
+  const int e0 = blockIdx.y * GN;
+  const int kb_begin = blockIdx.z * p.k_per_slice;
+  const int kb_end = min(p.k_blocks, kb_begin + p.k_per_slice);
+  const int nkb = kb_end - kb_begin;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < G_STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&hi_full_bar[b], 1);
+      mbar_init(&hi_empty_bar[b], 4);  // one arrival per promotion warp
+    }
+    mbar_init(ml_full_bar, 1);
+    *abort_word = 0;
+    mbar_fence_init();
+    prefetch_tensormap(&tm_x);
+    prefetch_tensormap(&tm_w);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, G_TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ======================================================================== TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      const uint32_t bytes = A_BYTES + p.parts * B_BYTES;
+      for (int kb = kb_begin; kb < kb_end; ++kb) {
+        if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_word, G_BUDGET_NS)) {
+          report_status(p.status, HMC_STATUS_TIMEOUT_PIPELINE, 0, stage, kb);
+          break;
+        }
+        uint8_t* a_dst = smem + stage * G_STAGE_BYTES;
+        mbar_arrive_expect_tx(&full_bar[stage], bytes);
+        tma_load_2d(a_dst, &tm_x, &full_bar[stage], kb * GK, m0);
+        for (int part = 0; part < p.parts; ++part)
+          tma_load_2d(a_dst + A_BYTES + part * B_BYTES, &tm_w, &full_bar[stage], kb * GK, part * p.epad + e0);
+        if (++stage == G_STAGES) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ======================================================================== MMA issuer
+    int stage = 0;
+    uint32_t phase = 0;
+    uint32_t empty_phase[2] = {0, 0};
+    constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((GN >> 3) << 17) | ((GM >> 4) << 24);
+    bool ok = true;
+    for (int i = 0; ok && i < nkb; ++i) {
+      const int buf = (i / G_PROMOTE) & 1;
+      const bool chain_start = i % G_PROMOTE == 0;
+      const bool chain_end = i % G_PROMOTE == G_PROMOTE - 1 || i == nkb - 1;
+      if (chain_start) {
+        if (!mbar_wait(&hi_empty_bar[buf], empty_phase[buf] ^ 1u, abort_word, G_BUDGET_NS)) {
+          if (lane == 0) report_status(p.status, HMC_STATUS_TIMEOUT_PIPELINE, 1, buf, i);
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+      }
+      if (!mbar_wait(&full_bar[stage], phase, abort_word, G_BUDGET_NS)) {
+        if (lane == 0) report_status(p.status, HMC_STATUS_TIMEOUT_PIPELINE, 2, stage, i);
+        ok = false;
+        break;
+      }
+      tc_fence_after_sync();
+      if (lane == 0) {
+        const uint32_t a_addr = smem_u32(smem + stage * G_STAGE_BYTES);
+        const uint64_t da = make_smem_desc(a_addr, 16, 1024, SWIZZLE_128B);
+        const uint64_t db_hi = make_smem_desc(a_addr + A_BYTES, 16, 1024, SWIZZLE_128B);
+        const uint32_t tm_hi = tmem_base + static_cast<uint32_t>(buf * GN);
+        const uint32_t tm_ml = tmem_base + 2 * GN;
+#pragma unroll
+        for (int ks = 0; ks < GK / 16; ++ks)
+          umma_bf16(tm_hi, da + 2 * ks, db_hi + 2 * ks, idesc, (!chain_start || ks > 0) ? 1u : 0u);
+        if (p.parts == 3) {
+          const uint64_t db_mid = make_smem_desc(a_addr + A_BYTES + B_BYTES, 16, 1024, SWIZZLE_128B);
+          const uint64_t db_lo = make_smem_desc(a_addr + A_BYTES + 2 * B_BYTES, 16, 1024, SWIZZLE_128B);
+#pragma unroll
+          for (int ks = 0; ks < GK / 16; ++ks)
+            umma_bf16(tm_ml, da + 2 * ks, db_mid + 2 * ks, idesc, (i > 0 || ks > 0) ? 1u : 0u);
+#pragma unroll
+          for (int ks = 0; ks < GK / 16; ++ks) umma_bf16(tm_ml, da + 2 * ks, db_lo + 2 * ks, idesc, 1u);
+        }
+        umma_commit(&empty_bar[stage]);
+        if (chain_end) umma_commit(&hi_full_bar[buf]);
+        if (i == nkb - 1) umma_commit(ml_full_bar);
+      }
+      __syncwarp();
+      if (chain_end) empty_phase[buf] ^= 1u;
+      if (++stage == G_STAGES) {
+        stage = 0;
+        phase ^= 1u;
+      }
+    }
+  } else {
+    // ======================================================================== promotion + epilogue
+    const int quarter = warp & 3;
+    const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+    float sum[GN];
+#pragma unroll
+    for (int c = 0; c < GN; ++c) sum[c] = 0.f;
+    uint32_t full_phase[2] = {0, 0};
+    const int chains = (nkb + G_PROMOTE - 1) / G_PROMOTE;
+    bool ok = true;
+    for (int it = 0; ok && it < chains; ++it) {
+      const int buf = it & 1;
+      if (!mbar_wait(&hi_full_bar[buf], full_phase[buf], abort_word, G_BUDGET_NS)) {
+        if (lane == 0) report_status(p.status, HMC_STATUS_TIMEOUT_PIPELINE, 3, buf, it);
+        ok = false;
+        break;
+      }
+      tc_fence_after_sync();
+      uint32_t v[32], w[32];
+      tmem_ld_32x32(tmem_base + lane_base + static_cast<uint32_t>(buf * GN), v);
+      tmem_ld_32x32(tmem_base + lane_base + static_cast<uint32_t>(buf * GN + 32), w);
+      tmem_ld_wait();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&hi_empty_bar[buf]);  // the tensor core may start the next chain here
+#pragma unroll
+      for (int c = 0; c < 32; ++c) {
+        sum[c] += __uint_as_float(v[c]);
+        sum[32 + c] += __uint_as_float(w[c]);
+      }
+      full_phase[buf] ^= 1u;
+    }
+    if (ok && p.parts == 3 && nkb > 0) {
+      if (!mbar_wait(ml_full_bar, 0u, abort_word, G_BUDGET_NS)) {
+        if (lane == 0) report_status(p.status, HMC_STATUS_TIMEOUT_PIPELINE, 4, 0, 0);
+        ok = false;
+      } else {
+        tc_fence_after_sync();
+        uint32_t v[32], w[32];
+        tmem_ld_32x32(tmem_base + lane_base + 2 * GN, v);
+        tmem_ld_32x32(tmem_base + lane_base + 2 * GN + 32, w);
+        tmem_ld_wait();
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          sum[c] += __uint_as_float(v[c]);
+          sum[32 + c] += __uint_as_float(w[c]);
+        }
+      }
+    }
+    const long long row = static_cast<long long>(m0) + quarter * 32 + lane;
+    if (ok && row < p.tokens && nkb > 0) {
+      float* dst = p.logits + row * p.experts + e0;
+      if (gridDim.z == 1) {
+        if (p.experts % 4 == 0) {
+#pragma unroll
+          for (int c = 0; c < GN; c += 4)
+            if (e0 + c < p.experts) *reinterpret_cast<float4*>(dst + c) = make_float4(sum[c], sum[c + 1], sum[c + 2], sum[c + 3]);
+        } else {
+#pragma unroll
+          for (int c = 0; c < GN; ++c)
+            if (e0 + c < p.experts) dst[c] = sum[c];
+        }
+      } else {
+        // two K-slices: 0 + a + b is the same number in either order, so the result stays deterministic
+#pragma unroll
+        for (int c = 0; c < GN; ++c)
+          if (e0 + c < p.experts) atomicAdd(dst + c, sum[c]);
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, G_TMEM_COLS);
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+EncodeTiledFn gate_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) == cudaSuccess &&
+        result == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+int gate_make_map(CUtensorMap* out, const void* base, long long inner, long long outer, int box_inner, int box_outer) {
+  EncodeTiledFn fn = gate_encode_fn();
+  HMC_REQUIRE(fn != nullptr, HMC_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(outer)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(inner) * 2};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(box_inner), static_cast<cuuint32_t>(box_outer)};
+  cuuint32_t elem_strides[2] = {1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem_strides,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  HMC_REQUIRE(r == CUDA_SUCCESS, HMC_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return 0;
+}
+
+}  // namespace
+}  // namespace hmc
+
+extern "C" int64_t hmc_gate_project_promoted_workspace_bytes(int64_t hidden, int64_t experts) {
+  const int64_t epad = (experts + hmc::GN - 1) / hmc::GN * hmc::GN;
+  return 3 * epad * hidden * 2;
+}
+
+extern "C" int hmc_gate_project_promoted(const void* x_bf16, const void* w, int w_is_bf16, int64_t tokens,
+                                         int64_t hidden, int64_t experts, float* logits, void* workspace,
+                                         int64_t workspace_bytes, int32_t* status, void* stream_ptr) {
+  using namespace hmc;
+  HMC_REQUIRE(x_bf16 && w && logits && workspace, HMC_ERR_INVALID, "hmc_gate_project_promoted: null tensor pointer");
+  HMC_REQUIRE(tokens > 0 && experts > 0 && hidden > 0 && hidden % 8 == 0, HMC_ERR_INVALID,
+              "hmc_gate_project_promoted: extents must be positive and hidden a multiple of 8");
+  HMC_REQUIRE(tokens < (1ll << 31) && hidden < (1ll << 31) && experts <= 65536, HMC_ERR_LIMIT,
+              "hmc_gate_project_promoted: extent too large");
+  HMC_REQUIRE(workspace_bytes >= hmc_gate_project_promoted_workspace_bytes(hidden, experts), HMC_ERR_INVALID,
+              "hmc_gate_project_promoted: workspace holds %lld bytes, %lld needed", (long long)workspace_bytes,
+              (long long)hmc_gate_project_promoted_workspace_bytes(hidden, experts));
+  HMC_REQUIRE(aligned16(x_bf16) && aligned16(workspace) && aligned16(logits), HMC_ERR_INVALID,
+              "hmc_gate_project_promoted: 16-byte alignment");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  const int epad = static_cast<int>((experts + GN - 1) / GN * GN);
+  const int parts = w_is_bf16 ? 1 : 3;
+  __nv_bfloat16* split = static_cast<__nv_bfloat16*>(workspace);
+  const long long split_elems = static_cast<long long>(epad) * hidden;
+  gate_split_parts_kernel<<<static_cast<unsigned>((split_elems + 255) / 256), 256, 0, stream>>>(
+      w, w_is_bf16, static_cast<int>(experts), epad, parts, hidden, split);
+  HMC_LAUNCH_OK();
+
+  CUtensorMap tx, tw;
+  int rc;
+  if ((rc = gate_make_map(&tx, x_bf16, hidden, tokens, GK, GM)) != 0) return rc;
+  if ((rc = gate_make_map(&tw, split, hidden, static_cast<long long>(parts) * epad, GK, GN)) != 0) return rc;
+
+  GateParams p{};
+  p.tokens = tokens;
+  p.hidden = static_cast<int>(hidden);
+  p.experts = static_cast<int>(experts);
+  p.epad = epad;
+  p.parts = parts;
+  p.k_blocks = static_cast<int>((hidden + GK - 1) / GK);
+  p.logits = logits;
+  p.status = status;
+  const unsigned m_tiles = static_cast<unsigned>((tokens + GM - 1) / GM);
+  const unsigned n_tiles = static_cast<unsigned>(epad / GN);
+  // a second K-slice when one slice per tile would leave most SMs idle
+  const int slices = (static_cast<long long>(m_tiles) * n_tiles * 2 <= 2ll * sm_count() && p.k_blocks >= 4 * G_PROMOTE) ? 2 : 1;
+  p.k_per_slice = ((p.k_blocks + slices - 1) / slices + G_PROMOTE - 1) / G_PROMOTE * G_PROMOTE;
+  if (slices > 1) HMC_CUDA_OK(cudaMemsetAsync(logits, 0, sizeof(float) * tokens * experts, stream));
+  static bool configured = false;
+  if (!configured) {
+    HMC_CUDA_OK(cudaFuncSetAttribute(gate_project_promoted_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     G_SMEM_BYTES));
+    configured = true;
+  }
+  dim3 grid(m_tiles, n_tiles, static_cast<unsigned>(slices));
+  gate_project_promoted_kernel<<<grid, G_THREADS, G_SMEM_BYTES, stream>>>(tx, tw, p);
+  HMC_LAUNCH_OK();
+  return 0;
+}

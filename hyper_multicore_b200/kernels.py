@@ -147,17 +147,21 @@ def _call(name: str, device: torch.device, *args) -> None:
 
 
 # ------------------------------------------------------------------------------------------- gate
-def gate_project(x: torch.Tensor, weight: torch.Tensor, use_tensor_cores: bool | None = None) -> torch.Tensor:
+_GATE_DEFAULT = "0"  # "1": promoted tcgen05 projection by default for eligible inputs
+
+
+def gate_project(x: torch.Tensor, weight: torch.Tensor, use_tensor_cores: bool | str | None = None) -> torch.Tensor:
     """FP32 logits [T, E] = float(x [T, H]) @ float(weight [E, H]).T.
 
-    The default path accumulates with FP32 FMAs (within 1e-5 / 1e-6 of the FP32 reference). With
-    ``use_tensor_cores=True`` (or HMC_GATE_TENSOR_CORES=1) BF16 hidden states go through tcgen05 with the
-    weight split into three BF16 parts: five times faster at 8192 x 4096 x 64, but the tensor core's
-    FP32 accumulation leaves an absolute error of about 3e-6 of the largest logit, above the
-    reference's logits tolerance, so it is opt-in.
+    BF16 hidden states (at least 128 tokens, H a multiple of 8) go through tcgen05 with the weight split
+    into three BF16 parts and the accumulation chain of the dominant part cut every 128 elements of K
+    ("promoted"); everything else, or ``use_tensor_cores=False`` / HMC_GATE_TENSOR_CORES=0, takes the FP32-FMA
+    kernel. ``use_tensor_cores="unpromoted"`` (HMC_GATE_TENSOR_CORES=unpromoted) is the three-GEMM variant
+    whose full-length accumulation leaves about 2e-5 absolute error at H = 4096.
     """
     if use_tensor_cores is None:
-        use_tensor_cores = os.environ.get("HMC_GATE_TENSOR_CORES", "0") == "1"
+        use_tensor_cores = {"0": False, "1": True}.get(os.environ.get("HMC_GATE_TENSOR_CORES", _GATE_DEFAULT),
+                                                       os.environ.get("HMC_GATE_TENSOR_CORES"))
     device = _require_cuda(x, weight)
     for name, tensor in (("hidden states", x), ("weight", weight)):
         if tensor.dtype not in (torch.bfloat16, torch.float32):
@@ -165,11 +169,18 @@ def gate_project(x: torch.Tensor, weight: torch.Tensor, use_tensor_cores: bool |
     x = x.contiguous()
     weight = weight.contiguous()
     logits = torch.empty((x.shape[0], weight.shape[0]), dtype=torch.float32, device=device)
-    if x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and x.shape[0] >= 128 and use_tensor_cores:
+    eligible = x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and x.shape[0] >= 128
+    if eligible and use_tensor_cores == "unpromoted":
         need = _lib.load().hmc_gate_project_workspace_bytes(x.shape[0], x.shape[1], weight.shape[0])
         workspace = torch.empty(need, dtype=torch.uint8, device=device)
         _call("hmc_gate_project_tc", device, x.data_ptr(), weight.data_ptr(), int(weight.dtype == torch.bfloat16),
               x.shape[0], x.shape[1], weight.shape[0], logits.data_ptr(), workspace.data_ptr(), need)
+        return logits
+    if eligible and use_tensor_cores:
+        need = _lib.load().hmc_gate_project_promoted_workspace_bytes(x.shape[1], weight.shape[0])
+        workspace = torch.empty(need, dtype=torch.uint8, device=device)
+        _call("hmc_gate_project_promoted", device, x.data_ptr(), weight.data_ptr(), int(weight.dtype == torch.bfloat16),
+              x.shape[0], x.shape[1], weight.shape[0], logits.data_ptr(), workspace.data_ptr(), need, None)
         return logits
     _call("hmc_gate_project", device, x.data_ptr(), int(x.dtype == torch.bfloat16), weight.data_ptr(),
           int(weight.dtype == torch.bfloat16), x.shape[0], x.shape[1], weight.shape[0], logits.data_ptr())
@@ -462,7 +473,7 @@ def ep_wait(counter: torch.Tensor, expected: int, status=None, budget_ns: int = 
 # ------------------------------------------------------------------------------ launch accounting
 # Kernels launched per C-ABI call, for callers that report how many device launches a step made.
 KERNELS_PER_CALL = {
-    "hmc_grouped_gemm": 1, "hmc_gate_project_tc": 3, "hmc_gate_route": 1, "hmc_gate_route_grad": 1, "hmc_gate_project": 1,
+    "hmc_grouped_gemm": 1, "hmc_gate_project_tc": 3, "hmc_gate_project_promoted": 2, "hmc_gate_route": 1, "hmc_gate_route_grad": 1, "hmc_gate_project": 1,
     "hmc_moe_histogram": 1, "hmc_moe_sort_routes": 3, "hmc_moe_gather_rows": 1,
     "hmc_moe_permute_from_mapping": 1, "hmc_moe_unpermute": 1, "hmc_moe_unpermute_grad": 1,
     "hmc_moe_token_permute_grad": 1, "hmc_zero_empty_expert_grad": 1, "hmc_route_offsets": 1,
