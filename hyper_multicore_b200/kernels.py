@@ -147,7 +147,7 @@ def _call(name: str, device: torch.device, *args) -> None:
 
 
 # ------------------------------------------------------------------------------------------- gate
-_GATE_DEFAULT = "0"  # "1": promoted tcgen05 projection by default for eligible inputs
+_GATE_DEFAULT = "1"  # promoted tcgen05 projection for eligible inputs; HMC_GATE_TENSOR_CORES=0 selects FP32 FMAs
 
 
 def gate_project(x: torch.Tensor, weight: torch.Tensor, use_tensor_cores: bool | str | None = None) -> torch.Tensor:
