@@ -46,13 +46,22 @@ chunk_histogram_kernel(const void* __restrict__ indices, int is_i64, long long e
 __global__ void __launch_bounds__(1024)
 chunk_scan_kernel(int* __restrict__ chunk_counts, int chunks, int experts, int* __restrict__ counts_out,
                   long long* __restrict__ ends_out, int* __restrict__ expert_of_row,
-                  int* __restrict__ source_of_row, long long entries) {
-  extern __shared__ int totals[];  // [experts]
+                  int* __restrict__ source_of_row, long long entries, int stage_table) {
+  extern __shared__ int totals[];  // [experts] (+ [chunks * experts] when the table is staged)
   __shared__ int placed;
+  // Small tables are scanned in shared memory: the serial walk over the chunks then costs shared-memory
+  // latencies instead of one global round trip per chunk.
+  const long long cells = static_cast<long long>(chunks) * experts;
+  int* staged = stage_table ? totals + experts : nullptr;
+  if (staged != nullptr) {
+    for (long long i = threadIdx.x; i < cells; i += blockDim.x) staged[i] = chunk_counts[i];
+    __syncthreads();
+  }
+  int* table = staged != nullptr ? staged : chunk_counts;
   for (int e = threadIdx.x; e < experts; e += blockDim.x) {
     int run = 0;
     for (int c = 0; c < chunks; ++c) {
-      int* slot = chunk_counts + static_cast<long long>(c) * experts + e;
+      int* slot = table + static_cast<long long>(c) * experts + e;
       const int v = *slot;
       *slot = run;
       run += v;
@@ -79,9 +88,14 @@ chunk_scan_kernel(int* __restrict__ chunk_counts, int chunks, int experts, int* 
     if (expert_of_row != nullptr) expert_of_row[r] = -1;
     if (source_of_row != nullptr) source_of_row[r] = -1;
   }
-  for (int e = threadIdx.x; e < experts; e += blockDim.x) {
-    const int base = totals[e];
-    for (int c = 0; c < chunks; ++c) chunk_counts[static_cast<long long>(c) * experts + e] += base;
+  if (staged != nullptr) {
+    for (long long i = threadIdx.x; i < cells; i += blockDim.x)
+      chunk_counts[i] = staged[i] + totals[static_cast<int>(i % experts)];
+  } else {
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) {
+      const int base = totals[e];
+      for (int c = 0; c < chunks; ++c) chunk_counts[static_cast<long long>(c) * experts + e] += base;
+    }
   }
 }
 
@@ -438,9 +452,14 @@ extern "C" int hmc_moe_sort_routes(const void* indices, int indices_are_i64, int
   chunk_histogram_kernel<<<chunks, SORT_THREADS, smem, stream>>>(indices, indices_are_i64, entries, e,
                                                                chunk_counts, status);
   HMC_LAUNCH_OK();
-  chunk_scan_kernel<<<1, 1024, smem, stream>>>(chunk_counts, chunks, e, counts,
-                                               reinterpret_cast<long long*>(cumulative), expert_of_row, source_of_row,
-                                               entries);
+  {
+    // stage the chunk table in shared memory when it fits the default 48 KiB
+    const size_t staged_bytes = smem + static_cast<size_t>(chunks) * experts * sizeof(int);
+    const int stage_table = staged_bytes <= 48 * 1024;
+    chunk_scan_kernel<<<1, 1024, stage_table ? staged_bytes : smem, stream>>>(
+        chunk_counts, chunks, e, counts, reinterpret_cast<long long*>(cumulative), expert_of_row, source_of_row,
+        entries, stage_table);
+  }
   HMC_LAUNCH_OK();
   chunk_rank_kernel<<<chunks, SORT_THREADS, smem, stream>>>(indices, indices_are_i64, entries, e, chunk_counts,
                                                           mapping, source_of_row, expert_of_row);
