@@ -225,7 +225,10 @@ def run_gpu(args, workload: str, clock_sampler_cls) -> None:
         d2h = sum(t.numel() * t.element_size() for t in outs_h)
         t, h, e, k = tokens, GATE["hidden"], GATE["experts"], GATE["top_k"]
         algorithmic_bytes = t * h * 2 + e * h * 4 + t * e * 4 + t * k * 4 + t * k * 8 + e * 4 + t * k * 4
-        kernel_note = "gate_project_kernel + gate_route_kernel + 3 sort kernels"
+        kernel_note = "gate_split_parts_kernel + gate_project_promoted_kernel (tcgen05) + gate_route_kernel + 3 sort kernels"
+        # DRAM bytes of the projection, split and route kernels of one step at the default size, from the ncu
+        # capture summarised in profiles/gate_kernels_bench_gate.md
+        traffic = 75.7e6 if not getattr(args, "tokens", None) else None
         dtype = "f32 (bf16 activations, int32/int64 indices)"
     else:
         tokens, hidden = MHC["tokens"], MHC["hidden"]
@@ -271,6 +274,7 @@ def run_gpu(args, workload: str, clock_sampler_cls) -> None:
         # previous_output; write grad_residual (4TH), grad_previous_output.
         algorithmic_bytes = (4 + 1 + 4 + 1 + 1) * th + (12 + 3 + 4 + 1) * th
         kernel_note = "mhc_post_kernel, mhc_mapping_kernel, mhc_mapping_grad_kernel, mhc_stream_grad_kernel + 3 tcgen05 contractions"
+        traffic = None
         dtype = "f32 math on bf16 activations"
 
     def timed(step, steps, warmup):
@@ -337,7 +341,7 @@ def run_gpu(args, workload: str, clock_sampler_cls) -> None:
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / args.steps},
         "gpu_launches": launches,
         "roofline": {"bound": "hbm", "kernel": kernel_note, "achieved": achieved, "peak": peak, "unit": "GB/s",
-                     "frac": achieved / peak, "peak_source": note, "traffic": None,
+                     "frac": achieved / peak, "peak_source": note, "traffic": traffic,
                      "algorithmic_bytes_per_step": algorithmic_bytes, "stage_ms": stage_ms},
     }
     if world == 1 and not args.no_cpu_baseline:
