@@ -60,21 +60,28 @@ __global__ void __launch_bounds__(THREADS, 3) mx_quant_kernel(const QuantParams 
   __shared__ int s_valid;
   const int pb = blockIdx.x;
   const int cb = blockIdx.y;
+  // locate the padded block: groups own ceil(rows / 128) consecutive blocks each. The group ends are
+  // fetched by all threads at once (one memory latency), then one thread walks the block counts.
+  __shared__ int s_blocks[HMC_CTRL_MAX_LOCAL_EXPERTS];
+  for (int g = threadIdx.x; g < p.groups; g += THREADS) {
+    const long long end = p.group_ends[g];
+    const long long prev = g > 0 ? p.group_ends[g - 1] : 0;
+    s_blocks[g] = static_cast<int>((end - prev + 127) / 128);
+  }
+  __syncthreads();
   if (threadIdx.x == 0) {
-    // locate the padded block: groups own ceil(rows / 128) consecutive blocks each
     int block = 0;
-    long long prev = 0;
     s_valid = -1;
     for (int g = 0; g < p.groups; ++g) {
-      const long long end = p.group_ends[g];
-      const int blocks = static_cast<int>((end - prev + 127) / 128);
+      const int blocks = s_blocks[g];
       if (pb < block + blocks) {
+        const long long prev = g > 0 ? p.group_ends[g - 1] : 0;
+        const long long end = p.group_ends[g];
         s_row0 = prev + static_cast<long long>(pb - block) * 128;
         s_valid = static_cast<int>(min(static_cast<long long>(128), end - s_row0));
         break;
       }
       block += blocks;
-      prev = end;
     }
   }
   __syncthreads();
