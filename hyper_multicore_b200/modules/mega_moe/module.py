@@ -889,6 +889,12 @@ class MegaMoeExperts(torch.nn.Module):
         received, routed_rows = route.received_rows, route.routed_rows
         if self.ep_size == 1 and source_of_row is None:
             return source[:max(received, 1)], None, None, None  # already in the owner's order
+        if self.ep_size == 1:
+            # one rank owns every expert: the dispatch is a local gather into the owner's (= the source's) order
+            rows_in = torch.empty(max(received, 1), self.hidden_size, dtype=torch.bfloat16, device=device)
+            if routed_rows > 0:
+                kernels.moe_gather_rows(source, source_of_row, self.top_k, rows_in[:routed_rows])
+            return rows_in, None, None, None
         generation = workspace.begin_call()
         if self._pull:
             if source_of_row is not None:
