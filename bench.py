@@ -365,7 +365,7 @@ def run_gpu(args) -> None:
         sampler.start()
     total_ms, launches = timed(step_resident, args.steps, args.warmup)
     clocks = sampler.stop() if rank == 0 else None
-    e2e_ms, _ = timed(step_host, args.steps, max(2, args.warmup // 2), join=(copy_in, copy_out))
+    e2e_ms, _ = timed(step_host, args.steps, max(3, args.warmup), join=(copy_in, copy_out))
     module.check_status()
 
     # per-launch duration of the dominant kernel (the grouped GEMM), CUDA events on the launch stream
