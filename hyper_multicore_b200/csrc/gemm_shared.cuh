@@ -152,6 +152,82 @@ __device__ __forceinline__ SwigluTerms swiglu_terms(float g, float u, int clamp,
   return t;
 }
 
+// RAGGED_K tail block: rows past the end of the group belong to the next group (or are unwritten).
+// Only the 16-row MMA steps that hold valid rows are issued; the invalid rows of the last such step
+// are cleared in every 64-wide MN-major chunk of the stage. A 128-byte row stays one 128-byte line
+// under the 128-byte swizzle, so whole lines can be cleared without undoing the swizzle.
+// Returns the number of 16-row steps to issue; the whole warp calls it.
+__device__ __forceinline__ int clear_tail_rows(uint8_t* stage_base, int chunks, int valid, int lane) {
+  const int k_steps = (valid + 15) >> 4;
+  const int vectors = (k_steps * 16 - valid) * 8;  // 16-byte vectors to clear per chunk
+  if (vectors > 0) {
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+    for (int chunk = 0; chunk < chunks; ++chunk) {
+      uint8_t* base = stage_base + chunk * CHUNK_BYTES + valid * 128;
+      for (int i = lane; i < vectors; i += 32) *reinterpret_cast<uint4*>(base + i * 16) = zero;
+    }
+    fence_proxy_async_smem();
+  }
+  __syncwarp();
+  return k_steps;
+}
+
+// Regular [rows, n] output tiles leave through shared memory and TMA stores (clipped at the row and
+// column edges by the tensor map): the calling warp writes its 32 accumulator rows x columns
+// [c_lo, c_hi) as 32-column boxes at rows m0.. of plane `plane`. FP32 boxes are 32 rows x 128 bytes in
+// one 4 KiB stage. BF16 boxes are 32 rows x 64 bytes: the stage holds two of them, so the store of
+// one box overlaps the packing of the next. `stores_issued` counts this warp's boxes across tiles.
+__device__ __forceinline__ void epilogue_tma_boxes(const Params& p, const CUtensorMap* tm_c, uint32_t taddr,
+                                                   uint8_t* my_stage, unsigned& stores_issued, int m0, int plane,
+                                                   int col_base, int c_lo, int c_hi, int lane) {
+  const bool f32 = p.epilogue == HMC_EPI_STORE_F32;
+#pragma unroll 1
+  for (int c = c_lo; c < c_hi; c += 32) {
+    if (col_base + c >= p.n) break;
+    uint32_t v[32];
+    tmem_ld_32x32(taddr + c, v);
+    tmem_ld_wait();
+    uint8_t* box = my_stage;
+    if (f32) {
+      if (stores_issued > 0) {  // the previous box must have been read out of the stage
+        if (lane == 0) bulk_wait_read_all();
+        __syncwarp();
+      }
+      // 16-byte chunk q of row `lane` goes to chunk q ^ (lane & 7): the 128-byte swizzle the
+      // tensor map expects, which also spreads a warp's stores over all banks.
+      uint8_t* row_base = box + lane * 128;
+#pragma unroll
+      for (int q = 0; q < 8; ++q)
+        *reinterpret_cast<uint4*>(row_base + ((q ^ (lane & 7)) << 4)) =
+            make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+    } else {
+      box = my_stage + (stores_issued & 1) * (STORE_STAGE_BYTES / 2);
+      if (stores_issued > 1) {  // the box before the previous one used this half
+        if (lane == 0) bulk_wait_read_but_one();
+        __syncwarp();
+      }
+      // 64-byte rows under the 64-byte swizzle: chunk q of row r sits at q ^ ((r >> 1) & 3)
+      uint8_t* row_base = box + lane * 64;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        uint4 o;
+        o.x = pack_bf16x2(__uint_as_float(v[8 * q + 0]), __uint_as_float(v[8 * q + 1]));
+        o.y = pack_bf16x2(__uint_as_float(v[8 * q + 2]), __uint_as_float(v[8 * q + 3]));
+        o.z = pack_bf16x2(__uint_as_float(v[8 * q + 4]), __uint_as_float(v[8 * q + 5]));
+        o.w = pack_bf16x2(__uint_as_float(v[8 * q + 6]), __uint_as_float(v[8 * q + 7]));
+        *reinterpret_cast<uint4*>(row_base + ((q ^ ((lane >> 1) & 3)) << 4)) = o;
+      }
+    }
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+      tma_store_3d(tm_c, box, col_base + c, m0, plane);
+      bulk_commit_group();
+    }
+    ++stores_issued;
+  }
+}
+
 // Row-major epilogues shared by the one-CTA and the CTA-pair kernels: the calling warp owns TMEM
 // lanes [32 * quarter, +32) and the column half `half` of a 128 x 256 accumulator; thread `lane`
 // owns output row `out_row` (written only when row_ok).

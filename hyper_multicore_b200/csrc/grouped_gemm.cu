@@ -191,25 +191,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         int k_steps = BK / 16;
         if (p.mode == HMC_GEMM_RAGGED_K) {
           const long long left = t.row1 - (t.row0 + static_cast<long long>(kb) * BK);
-          if (left < BK) {
-            // Rows past the end of this group belong to the next group (or are unwritten). Only the
-            // 16-row MMA steps that hold valid rows are issued; the invalid rows of the last such
-            // step are cleared in both operands. A 128-byte row stays one 128-byte line under the
-            // 128-byte swizzle, so whole lines can be cleared without undoing the swizzle.
-            const int valid = static_cast<int>(left);
-            k_steps = (valid + 15) >> 4;
-            const int vectors = (k_steps * 16 - valid) * 8;  // 16-byte vectors to clear per 64-wide chunk
-            if (vectors > 0) {
-              const uint4 zero = make_uint4(0, 0, 0, 0);
-#pragma unroll
-              for (int chunk = 0; chunk < 6; ++chunk) {  // 2 A chunks + 4 B chunks
-                uint8_t* base = (chunk < 2 ? a_src + chunk * CHUNK_BYTES : b_src + (chunk - 2) * CHUNK_BYTES) + valid * 128;
-                for (int i = lane; i < vectors; i += 32) *reinterpret_cast<uint4*>(base + i * 16) = zero;
-              }
-              fence_proxy_async_smem();
-            }
-            __syncwarp();
-          }
+          // the stage holds 2 A chunks followed by 4 B chunks
+          if (left < BK) k_steps = clear_tail_rows(a_src, 6, static_cast<int>(left), lane);
         }
         if (lane == 0) {
           uint64_t da = make_smem_desc(smem_u32(a_src), A_LBO, 1024, SWIZZLE_128B);
@@ -294,55 +277,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         // memory and TMA stores (clipped at the m and n edges by the tensor map), 32 columns per box.
         // FP32 boxes are 32 columns x 128 bytes in one 4 KiB stage. BF16 boxes are 32 columns x 64 bytes:
         // the stage holds two of them, so the store of one box overlaps the packing of the next.
-        const bool f32 = p.epilogue == HMC_EPI_STORE_F32;
         const bool ragged_k = p.mode == HMC_GEMM_RAGGED_K;
         const int m0 = (ragged_k ? t.m_idx * BM : static_cast<int>(t.row0) + t.m_idx * BM) + quarter * 32;
         const int plane = ragged_k ? t.group : 0;
-#pragma unroll 1
-        for (int c = c_lo; c < c_hi; c += 32) {
-          if (col_base + c >= p.n) break;
-          uint32_t v[32];
-          tmem_ld_32x32(taddr + c, v);
-          tmem_ld_wait();
-          uint8_t* box = my_stage;
-          if (f32) {
-            if (stores_issued > 0) {  // the previous box must have been read out of the stage
-              if (lane == 0) bulk_wait_read_all();
-              __syncwarp();
-            }
-            // 16-byte chunk q of row `lane` goes to chunk q ^ (lane & 7): the 128-byte swizzle the
-            // tensor map expects, which also spreads a warp's stores over all banks.
-            uint8_t* row_base = box + lane * 128;
-#pragma unroll
-            for (int q = 0; q < 8; ++q)
-              *reinterpret_cast<uint4*>(row_base + ((q ^ (lane & 7)) << 4)) =
-                  make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-          } else {
-            box = my_stage + (stores_issued & 1) * (STORE_STAGE_BYTES / 2);
-            if (stores_issued > 1) {  // the box before the previous one used this half
-              if (lane == 0) bulk_wait_read_but_one();
-              __syncwarp();
-            }
-            // 64-byte rows under the 64-byte swizzle: chunk q of row r sits at q ^ ((r >> 1) & 3)
-            uint8_t* row_base = box + lane * 64;
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              uint4 o;
-              o.x = pack_bf16x2(__uint_as_float(v[8 * q + 0]), __uint_as_float(v[8 * q + 1]));
-              o.y = pack_bf16x2(__uint_as_float(v[8 * q + 2]), __uint_as_float(v[8 * q + 3]));
-              o.z = pack_bf16x2(__uint_as_float(v[8 * q + 4]), __uint_as_float(v[8 * q + 5]));
-              o.w = pack_bf16x2(__uint_as_float(v[8 * q + 6]), __uint_as_float(v[8 * q + 7]));
-              *reinterpret_cast<uint4*>(row_base + ((q ^ ((lane >> 1) & 3)) << 4)) = o;
-            }
-          }
-          fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) {
-            tma_store_3d(&tm_c, box, col_base + c, m0, plane);
-            bulk_commit_group();
-          }
-          ++stores_issued;
-        }
+        epilogue_tma_boxes(p, &tm_c, taddr, my_stage, stores_issued, m0, plane, col_base, c_lo, c_hi, lane);
       } else if (p.combine_enabled) {
         // Fused combine: the rows go to the routed buffers of their source ranks. Each lane finds the
         // destination of its own row; the tile is staged in shared memory so that every store

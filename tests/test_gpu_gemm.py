@@ -84,7 +84,9 @@ def test_ragged_m_swiglu_forward_and_backward_epilogues(cuda_device, tile_mode, 
 
 @pytest.mark.parametrize("f32", [False, True])
 @pytest.mark.parametrize("counts,m,n", [([64], 128, 256), ([128, 0, 65, 1, 300], 256, 512),
-                                        ([128, 0, 65, 1, 300], 200, 328), ([0, 0], 128, 256)])
+                                        ([128, 0, 65, 1, 300], 200, 328), ([0, 0], 128, 256),
+                                        ([128, 0, 65, 1, 300], 256, 328), ([0, 0, 0], 512, 256),
+                                        ([77, 16, 0, 500, 33, 7], 512, 768), ([399] * 24 + [0, 1000], 1024, 1280)])
 def test_ragged_k_weight_gradient(cuda_device, f32, counts, m, n):
     from hyper_multicore_b200 import kernels as K
 
