@@ -423,6 +423,8 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, 
 
 int launch_grouped_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const gemm::Params& p, int b_major, int grid,
                              cudaStream_t stream);
+int launch_grouped_gemm_pair_dw(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const gemm::Params& p,
+                                int grid, cudaStream_t stream);
 
 }  // namespace hmc
 
@@ -585,6 +587,13 @@ extern "C" int hmc_grouped_gemm(const hmc_grouped_gemm_args* args, void* stream_
   int grid = a.max_ctas > 0 ? a.max_ctas : sm_count();
   if (grid > sm_count()) grid = sm_count();
   if (a.mode == HMC_GEMM_RAGGED_K) {
+    // CTA pairs on 256 x 256 tiles move two thirds of the operand bytes: taken whenever m splits into them
+    if (a.tile_mode != HMC_TILE_SINGLE && a.m % (2 * BM) == 0 && sm_count() >= 2) {
+      p.m_tiles = static_cast<int>(a.m / (2 * BM));
+      const long long pair_tiles = static_cast<long long>(p.groups) * p.m_tiles * p.n_tiles;
+      if (2 * pair_tiles < grid) grid = static_cast<int>(2 * pair_tiles);
+      return launch_grouped_gemm_pair_dw(ta, tb, tc, p, grid, stream);
+    }
     const long long tiles = static_cast<long long>(p.groups) * p.m_tiles * p.n_tiles;
     if (tiles < grid) grid = static_cast<int>(tiles);
     return launch<HMC_MAJOR_MN, HMC_MAJOR_MN>(ta, tb, tc, p, grid, stream);

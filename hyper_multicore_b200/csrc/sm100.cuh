@@ -204,6 +204,37 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t local_smem_addr, uint32_
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
+// Bounded wait with cluster-scope acquire: for barriers whose arrivals come from the other CTA of the
+// pair and publish that CTA's shared-memory writes.
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, volatile int* abort_word,
+                                                  uint64_t budget_ns) {
+  if (mbar_try_wait_cluster(bar, parity)) return true;
+  const uint64_t t0 = global_timer_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 256; ++i) {
+      if (mbar_try_wait_cluster(bar, parity)) return true;
+    }
+    if (*abort_word != 0) return false;
+    if (global_timer_ns() - t0 > budget_ns) {
+      *abort_word = 1;
+      return false;
+    }
+  }
+}
 constexpr uint32_t PEER_BIT_MASK = 0xFEFFFFFFu;  // clears the CTA-rank bit: the pair's leader
 // TMA loads of a CTA pair (each CTA fetches its own tiles): data lands in the issuing CTA, bytes are counted on the
 // LEADER's barrier (the barrier address has its peer bit cleared).

@@ -94,7 +94,7 @@ typedef struct hmc_grouped_gemm_args {
   int32_t epilogue;
   int32_t groups;
   int32_t max_ctas; /* 0 = one CTA per SM */
-  int32_t tile_mode; /* RAGGED_M: HMC_TILE_AUTO, _SINGLE (128-row tiles) or _PAIR (256-row CTA-pair tiles) */
+  int32_t tile_mode; /* HMC_TILE_AUTO, _SINGLE (128-row tiles) or _PAIR (256-row CTA-pair tiles; RAGGED_K: where m % 256 == 0) */
   int32_t swiglu_clamp; /* HMC_CLAMP_*: SwiGLU / SwiGLU-grad epilogues only */
   int64_t rows;     /* extent of the ragged dimension of a (and of b for RAGGED_K) */
   int64_t m;        /* RAGGED_K only */

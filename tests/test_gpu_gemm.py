@@ -82,12 +82,13 @@ def test_ragged_m_swiglu_forward_and_backward_epilogues(cuda_device, tile_mode, 
     _close(du, ref_du)
 
 
+@pytest.mark.parametrize("tile_mode", [0, 1])  # 1: one-CTA tiles; otherwise CTA pairs on 256 x 256 tiles where m % 256 == 0
 @pytest.mark.parametrize("f32", [False, True])
 @pytest.mark.parametrize("counts,m,n", [([64], 128, 256), ([128, 0, 65, 1, 300], 256, 512),
                                         ([128, 0, 65, 1, 300], 200, 328), ([0, 0], 128, 256),
                                         ([128, 0, 65, 1, 300], 256, 328), ([0, 0, 0], 512, 256),
                                         ([77, 16, 0, 500, 33, 7], 512, 768), ([399] * 24 + [0, 1000], 1024, 1280)])
-def test_ragged_k_weight_gradient(cuda_device, f32, counts, m, n):
+def test_ragged_k_weight_gradient(cuda_device, f32, counts, m, n, tile_mode):
     from hyper_multicore_b200 import kernels as K
 
     torch.manual_seed(m + n)
@@ -99,7 +100,7 @@ def test_ragged_k_weight_gradient(cuda_device, f32, counts, m, n):
     b[rows:] = float("nan")
     c = torch.full((groups, m, n), 3.0, device=dev, dtype=torch.float32 if f32 else torch.bfloat16)
     K.grouped_gemm(a, b, c, _ends(counts, dev), mode=K.HMC_GEMM_RAGGED_K,
-                   epilogue=K.HMC_EPI_STORE_F32 if f32 else K.HMC_EPI_STORE_BF16)
+                   epilogue=K.HMC_EPI_STORE_F32 if f32 else K.HMC_EPI_STORE_BF16, tile_mode=tile_mode)
     starts = _starts(counts)
     ref = torch.stack([a[starts[g]:starts[g + 1]].float().T @ b[starts[g]:starts[g + 1]].float() for g in range(groups)])
     _close(c, ref)
