@@ -873,14 +873,18 @@ class MegaMoeExperts(torch.nn.Module):
         if scale is None or data is None:
             raise ValueError(f"MegaMoE MXFP8 current root is missing required {direction} data/scale.")
         self._check_mx_pair(data, scale, root, shape, direction)
-        key = (id(root), direction)
-        stamp = (scale.data_ptr(), scale._version)  # pylint: disable=protected-access
+        # An entry is valid only for the very tensor object it was packed from (held weakly: an id() or a
+        # data_ptr() can come back for new weights once the old ones are freed) at the same version.
+        key = (id(scale), direction)
+        version = scale._version  # pylint: disable=protected-access
         cached = self._scale_atoms.get(key)
-        if cached is None or cached[0] != stamp:
+        if cached is None or cached[0]() is not scale or cached[1] != version:
+            for stale in [k for k, entry in self._scale_atoms.items() if entry[0]() is None]:
+                del self._scale_atoms[stale]
             experts, rows, cols = shape
             atoms = kernels.mx_pack_weight_scale(scale, 0 if direction == "col" else 1, experts, rows, cols)
-            self._scale_atoms[key] = cached = (stamp, atoms)
-        return cached[1]
+            self._scale_atoms[key] = cached = (weakref.ref(scale), version, atoms)
+        return cached[2]
 
     def _mx_exchange(self, source, source_of_row, route, generation_hint=None):
         """Dispatch rows to their owners and wait until every local expert's rows have landed."""

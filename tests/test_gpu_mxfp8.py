@@ -159,6 +159,44 @@ def test_mxfp8_experts_forward_backward(cuda_device, tokens, hidden, inter, expe
     assert (w1.grad[1] == 0).all() and (w2.grad[1] == 0).all(), "cold expert gradients must be exact zeros"
 
 
+def test_requantised_weights_replace_cached_scale_factors(cuda_device):
+    """One module, weights updated in place and re-quantised between calls (an optimiser step): the new
+    field tensors tend to land in the memory the old ones just freed, and fresh weights may even get a
+    recycled id(). The packed scale factors must follow the new fields, not a cache entry."""
+    from hyper_multicore_b200 import MegaMoeExperts
+    from hyper_multicore_b200.mxfp8 import attach_mx_fields
+
+    dev = cuda_device
+    tokens, hidden, inter, experts, top_k = 96, 256, 128, 4, 2
+    module = MegaMoeExperts(hidden_size=hidden, intermediate_size=inter, num_experts=experts, top_k=top_k,
+                            precision="mxfp8")
+    w1 = w2 = None
+    for seed in (30, 31, 32, 33):
+        case = make_case(tokens, hidden, inter, experts, top_k, seed=seed)
+        case["w1"] = (case["w1"].float() * (1.0 + seed % 3)).bfloat16()  # different scale factors every round
+        ref = omx.experts_forward_backward(case["hidden"], case["topk_ids"], case["topk_weights"], case["w1"],
+                                           case["w2"], case["grad_output"])
+        if seed % 2 == 0 or w1 is None:  # fresh tensors ...
+            w1 = case["w1"].to(dev).requires_grad_(True)
+            w2 = case["w2"].to(dev).requires_grad_(True)
+        else:  # ... or the same tensors updated in place
+            with torch.no_grad():
+                w1.copy_(case["w1"].to(dev))
+                w2.copy_(case["w2"].to(dev))
+            w1.grad = w2.grad = None
+        attach_mx_fields(w1)
+        attach_mx_fields(w2)
+        x = case["hidden"].to(dev).requires_grad_(True)
+        p = case["topk_weights"].to(dev).requires_grad_(True)
+        out = module(x, case["topk_ids"].to(dev), p, expert_weights=(w1, w2))
+        out.backward(case["grad_output"].to(dev))
+        module.check_status()
+        for name, value, limit in (("output", out, 1e-2), ("grad_hidden", x.grad, 3e-2), ("grad_w1", w1.grad, 3e-2)):
+            error = rel_l2(value.detach().cpu().float(), ref[name].float())
+            assert error <= limit, (seed, name, error)
+        del x, p, out
+
+
 def test_mxfp8_validation(cuda_device):
     from hyper_multicore_b200 import MegaMoeExperts, MegaMoeNumericsOptions
 
