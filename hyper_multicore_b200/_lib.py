@@ -80,6 +80,7 @@ class GroupedGemmArgs(ctypes.Structure):
         ("row_probs", c_void_p),
         ("row_dot", c_void_p),
         ("combine", c_void_p),
+        ("pipe_budget_ns", c_uint64),
     ]
 
 

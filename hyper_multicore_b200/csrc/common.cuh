@@ -47,6 +47,25 @@ void set_error(const char* fmt, ...);
 
 int sm_count();  // number of SMs on the current device (cached per device)
 
+// cudaFuncAttributeMaxDynamicSharedMemorySize belongs to a (kernel, device) pair: every launch site keeps one
+// PerDeviceFlag and raises the limit the first time it launches on each device ordinal.
+constexpr int HMC_MAX_DEVICES = 64;
+struct PerDeviceFlag {
+  bool done[HMC_MAX_DEVICES];
+};
+
+template <typename Kernel>
+static inline int allow_dynamic_smem(Kernel kernel, int bytes, PerDeviceFlag& flag) {
+  int dev = 0;
+  HMC_CUDA_OK(cudaGetDevice(&dev));
+  const bool tracked = dev >= 0 && dev < HMC_MAX_DEVICES;
+  if (!tracked || !flag.done[dev]) {
+    HMC_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+    if (tracked) flag.done[dev] = true;
+  }
+  return 0;
+}
+
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // ---------------------------------------------------------------------------------------------

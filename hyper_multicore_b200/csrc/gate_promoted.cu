@@ -350,12 +350,8 @@ extern "C" int hmc_gate_project_promoted(const void* x_bf16, const void* w, int 
   const int slices = (static_cast<long long>(m_tiles) * n_tiles * 2 <= 2ll * sm_count() && p.k_blocks >= 4 * G_PROMOTE) ? 2 : 1;
   p.k_per_slice = ((p.k_blocks + slices - 1) / slices + G_PROMOTE - 1) / G_PROMOTE * G_PROMOTE;
   if (slices > 1) HMC_CUDA_OK(cudaMemsetAsync(logits, 0, sizeof(float) * tokens * experts, stream));
-  static bool configured = false;
-  if (!configured) {
-    HMC_CUDA_OK(cudaFuncSetAttribute(gate_project_promoted_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     G_SMEM_BYTES));
-    configured = true;
-  }
+  static PerDeviceFlag configured{};
+  if (int rc = allow_dynamic_smem(gate_project_promoted_kernel, G_SMEM_BYTES, configured)) return rc;
   dim3 grid(m_tiles, n_tiles, static_cast<unsigned>(slices));
   gate_project_promoted_kernel<<<grid, G_THREADS, G_SMEM_BYTES, stream>>>(tx, tw, p);
   HMC_LAUNCH_OK();

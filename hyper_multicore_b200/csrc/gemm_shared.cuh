@@ -27,7 +27,7 @@ constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_WARPS * STORE_STAGE_BYTES 
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t SWIZZLE_128B = 2;
 
-constexpr uint64_t PIPE_BUDGET_NS = 4ull * 1000 * 1000 * 1000;  // intra-kernel barrier waits
+constexpr uint64_t PIPE_BUDGET_NS = 4ull * 1000 * 1000 * 1000;  // default budget of intra-kernel barrier waits
 
 struct Params {
   int mode;      // HMC_GEMM_RAGGED_M / HMC_GEMM_RAGGED_K
@@ -46,6 +46,7 @@ struct Params {
   void* aux;
   const int* ready_counters;  // optional, RAGGED_M: per-group arrival counters (rows landed)
   unsigned long long ready_budget_ns;
+  unsigned long long pipe_budget_ns;  // intra-kernel barrier waits; covers the arrival budget when rows are awaited
   int* status;
   int tma_store;           // RAGGED_M plain stores: full tiles leave through shared memory + TMA
   int combine_enabled;     // STORE_BF16 rows go to `combine` destinations instead of c

@@ -96,7 +96,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           ready_group = t.group;
         }
         for (int kb = 0; kb < kiters; ++kb) {
-          if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_word, PIPE_BUDGET_NS)) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_word, p.pipe_budget_ns)) {
             report_status(p.status, HMC_STATUS_TIMEOUT_PIPELINE, 0, stage, kb);
             ok = false;
             break;
@@ -172,7 +172,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     for (long long idx = blockIdx.x; ok && walker.get(idx, t); idx += gridDim.x) {
       const int kiters = k_iterations(p, t);
       if (kiters == 0) continue;  // RAGGED_K cold group: the epilogue writes zeros on its own
-      if (!mbar_wait(&acc_empty_bar[acc], acc_phase ^ 1u, abort_word, PIPE_BUDGET_NS)) {
+      if (!mbar_wait(&acc_empty_bar[acc], acc_phase ^ 1u, abort_word, p.pipe_budget_ns)) {
         if (lane == 0) report_status(p.status, HMC_STATUS_TIMEOUT_PIPELINE, 1, acc, 0);
         ok = false;
         break;
@@ -180,7 +180,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       tc_fence_after_sync();
       const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * BN);
       for (int kb = 0; kb < kiters; ++kb) {
-        if (!mbar_wait(&full_bar[stage], phase, abort_word, PIPE_BUDGET_NS)) {
+        if (!mbar_wait(&full_bar[stage], phase, abort_word, p.pipe_budget_ns)) {
           if (lane == 0) report_status(p.status, HMC_STATUS_TIMEOUT_PIPELINE, 2, stage, kb);
           ok = false;
           break;
@@ -261,7 +261,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         }
         continue;
       }
-      if (!mbar_wait(&acc_full_bar[acc], acc_phase, abort_word, PIPE_BUDGET_NS)) {
+      if (!mbar_wait(&acc_full_bar[acc], acc_phase, abort_word, p.pipe_budget_ns)) {
         if (lane == 0) report_status(p.status, HMC_STATUS_TIMEOUT_PIPELINE, 3, acc, 0);
         ok = false;
         break;
@@ -408,12 +408,9 @@ int make_map(CUtensorMap* out, const void* base, int rank, const cuuint64_t* dim
 template <int A_MAJOR, int B_MAJOR>
 int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const Params& p, int grid,
            cudaStream_t stream) {
-  static bool configured = false;
+  static PerDeviceFlag configured{};
   auto kernel = grouped_gemm_kernel<A_MAJOR, B_MAJOR>;
-  if (!configured) {
-    HMC_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-    configured = true;
-  }
+  if (int rc = allow_dynamic_smem(kernel, SMEM_BYTES, configured)) return rc;
   kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, tc, p);
   HMC_LAUNCH_OK();
   return 0;
@@ -465,6 +462,9 @@ extern "C" int hmc_grouped_gemm(const hmc_grouped_gemm_args* args, void* stream_
   p.aux = a.aux;
   p.ready_counters = a.ready_counters;
   p.ready_budget_ns = a.ready_budget_ns ? a.ready_budget_ns : 10ull * 1000 * 1000 * 1000;
+  // The producer may wait for late rows for the whole arrival budget: the MMA and epilogue warps behind
+  // it get that time on top of their own, so that a slow peer never shows up as a pipeline time-out.
+  p.pipe_budget_ns = (a.pipe_budget_ns ? a.pipe_budget_ns : PIPE_BUDGET_NS) + (a.ready_counters ? p.ready_budget_ns : 0);
   p.status = a.status;
   p.n = static_cast<int>(a.n);
   {

@@ -99,7 +99,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
         const int n0 = p.epilogue == HMC_EPI_SWIGLU ? (rank == 0 ? t.n_idx * (BN / 2) : p.n + t.n_idx * (BN / 2))
                                                     : t.n_idx * BN + static_cast<int>(rank) * (BN / 2);
         for (int kb = 0; kb < kiters; ++kb) {
-          if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_word, PIPE_BUDGET_NS)) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_word, p.pipe_budget_ns)) {
             report_status(p.status, HMC_STATUS_TIMEOUT_PIPELINE, 0, stage, kb);
             ok = false;
             break;
@@ -137,7 +137,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
       constexpr uint32_t B_KSTEP = B_MAJOR == HMC_MAJOR_MN ? (16 * 128) >> 4 : 32 >> 4;
       const int kiters = (p.k + BK - 1) / BK;
       for (long long idx = pair; ok && walker.get(idx, t); idx += pairs) {
-        if (!mbar_wait(&acc_empty_bar[acc], acc_phase ^ 1u, abort_word, PIPE_BUDGET_NS)) {
+        if (!mbar_wait(&acc_empty_bar[acc], acc_phase ^ 1u, abort_word, p.pipe_budget_ns)) {
           if (lane == 0) report_status(p.status, HMC_STATUS_TIMEOUT_PIPELINE, 1, acc, 0);
           ok = false;
           break;
@@ -145,7 +145,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
         tc_fence_after_sync();
         const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * BN);
         for (int kb = 0; kb < kiters; ++kb) {
-          if (!mbar_wait(&full_bar[stage], phase, abort_word, PIPE_BUDGET_NS)) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_word, p.pipe_budget_ns)) {
             if (lane == 0) report_status(p.status, HMC_STATUS_TIMEOUT_PIPELINE, 2, stage, kb);
             ok = false;
             break;
@@ -191,7 +191,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
           t.row0 + static_cast<long long>(t.m_idx) * PAIR_ROWS + static_cast<long long>(rank) * BM + row_in_tile;
       const bool row_ok = out_row < t.row1;
       const int col_base = p.epilogue == HMC_EPI_SWIGLU ? t.n_idx * (BN / 2) : t.n_idx * BN;
-      if (!mbar_wait(&acc_full_bar[acc], acc_phase, abort_word, PIPE_BUDGET_NS)) {
+      if (!mbar_wait(&acc_full_bar[acc], acc_phase, abort_word, p.pipe_budget_ns)) {
         if (lane == 0) report_status(p.status, HMC_STATUS_TIMEOUT_PIPELINE, 3, acc, 0);
         ok = false;
         break;
@@ -222,12 +222,9 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
 
 template <int B_MAJOR>
 int launch_pair_impl(const CUtensorMap& ta, const CUtensorMap& tb, const Params& p, int grid, cudaStream_t stream) {
-  static bool configured = false;
+  static PerDeviceFlag configured{};
   auto kernel = grouped_gemm_pair_kernel<B_MAJOR>;
-  if (!configured) {
-    HMC_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM_BYTES));
-    configured = true;
-  }
+  if (int rc = allow_dynamic_smem(kernel, PAIR_SMEM_BYTES, configured)) return rc;
   kernel<<<grid, NUM_THREADS, PAIR_SMEM_BYTES, stream>>>(ta, tb, p);
   HMC_LAUNCH_OK();
   return 0;

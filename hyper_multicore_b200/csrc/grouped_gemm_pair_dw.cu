@@ -97,7 +97,7 @@ grouped_gemm_pair_dw_kernel(const __grid_constant__ CUtensorMap tm_a, const __gr
         const int m0 = t.m_idx * DW_PAIR_M + static_cast<int>(rank) * BM;      // this CTA's 128 rows of C
         const int n0 = t.n_idx * BN + static_cast<int>(rank) * (BN / 2);       // this CTA's 128 columns of B
         for (int kb = 0; kb < kiters; ++kb) {
-          if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_word, PIPE_BUDGET_NS)) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_word, p.pipe_budget_ns)) {
             report_status(p.status, HMC_STATUS_TIMEOUT_PIPELINE, 0, stage, kb);
             ok = false;
             break;
@@ -158,7 +158,7 @@ grouped_gemm_pair_dw_kernel(const __grid_constant__ CUtensorMap tm_a, const __gr
           const long long left = t.row1 - (t.row0 + static_cast<long long>(kb) * BK);
           if (block_needs_clearing(left)) {
             const uint32_t bit = 1u << stage;
-            if (!mbar_wait(&tail_full_bar[stage], (tail_parity & bit) ? 1u : 0u, abort_word, PIPE_BUDGET_NS)) {
+            if (!mbar_wait(&tail_full_bar[stage], (tail_parity & bit) ? 1u : 0u, abort_word, p.pipe_budget_ns)) {
               if (lane == 0) report_status(p.status, HMC_STATUS_TIMEOUT_PIPELINE, 5, stage, kb);
               ok = false;
               break;
@@ -174,7 +174,7 @@ grouped_gemm_pair_dw_kernel(const __grid_constant__ CUtensorMap tm_a, const __gr
       for (long long idx = pair; ok && walker.get(idx, t); idx += pairs) {
         const int kiters = k_iterations(p, t);
         if (kiters == 0) continue;  // cold group: the epilogue writes zeros on its own
-        if (!mbar_wait(&acc_empty_bar[acc], acc_phase ^ 1u, abort_word, PIPE_BUDGET_NS)) {
+        if (!mbar_wait(&acc_empty_bar[acc], acc_phase ^ 1u, abort_word, p.pipe_budget_ns)) {
           if (lane == 0) report_status(p.status, HMC_STATUS_TIMEOUT_PIPELINE, 1, acc, 0);
           ok = false;
           break;
@@ -182,7 +182,7 @@ grouped_gemm_pair_dw_kernel(const __grid_constant__ CUtensorMap tm_a, const __gr
         tc_fence_after_sync();
         const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * BN);
         for (int kb = 0; kb < kiters; ++kb) {
-          if (!mbar_wait(&full_bar[stage], phase, abort_word, PIPE_BUDGET_NS)) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_word, p.pipe_budget_ns)) {
             if (lane == 0) report_status(p.status, HMC_STATUS_TIMEOUT_PIPELINE, 2, stage, kb);
             ok = false;
             break;
@@ -194,7 +194,7 @@ grouped_gemm_pair_dw_kernel(const __grid_constant__ CUtensorMap tm_a, const __gr
           if (block_needs_clearing(left)) {
             clear_tail_rows(src, 4, static_cast<int>(left), lane);
             const uint32_t bit = 1u << stage;
-            if (!mbar_wait_cluster(&peer_bar[stage], (tail_parity & bit) ? 1u : 0u, abort_word, PIPE_BUDGET_NS)) {
+            if (!mbar_wait_cluster(&peer_bar[stage], (tail_parity & bit) ? 1u : 0u, abort_word, p.pipe_budget_ns)) {
               if (lane == 0) report_status(p.status, HMC_STATUS_TIMEOUT_PIPELINE, 4, stage, kb);
               ok = false;
               break;
@@ -261,7 +261,7 @@ grouped_gemm_pair_dw_kernel(const __grid_constant__ CUtensorMap tm_a, const __gr
         }
         continue;
       }
-      if (!mbar_wait(&acc_full_bar[acc], acc_phase, abort_word, PIPE_BUDGET_NS)) {
+      if (!mbar_wait(&acc_full_bar[acc], acc_phase, abort_word, p.pipe_budget_ns)) {
         if (lane == 0) report_status(p.status, HMC_STATUS_TIMEOUT_PIPELINE, 3, acc, 0);
         ok = false;
         break;
@@ -297,12 +297,8 @@ grouped_gemm_pair_dw_kernel(const __grid_constant__ CUtensorMap tm_a, const __gr
 // 256-row tiles.
 int launch_grouped_gemm_pair_dw(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const gemm::Params& p,
                                 int grid, cudaStream_t stream) {
-  static bool configured = false;
-  if (!configured) {
-    HMC_CUDA_OK(cudaFuncSetAttribute(grouped_gemm_pair_dw_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     DW_SMEM_BYTES));
-    configured = true;
-  }
+  static PerDeviceFlag configured{};
+  if (int rc = allow_dynamic_smem(grouped_gemm_pair_dw_kernel, DW_SMEM_BYTES, configured)) return rc;
   grid &= ~1;  // whole pairs
   if (grid < 2) grid = 2;
   grouped_gemm_pair_dw_kernel<<<grid, NUM_THREADS, DW_SMEM_BYTES, stream>>>(ta, tb, tc, p);

@@ -484,12 +484,9 @@ int make_map(CUtensorMap* out, const void* base, int rank, const cuuint64_t* dim
 template <int A_MAJOR, int B_MAJOR>
 int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const Params& p, int grid,
            cudaStream_t stream) {
-  static bool configured = false;
+  static PerDeviceFlag configured{};
   auto kernel = mx_gemm_kernel<A_MAJOR, B_MAJOR>;
-  if (!configured) {
-    HMC_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-    configured = true;
-  }
+  if (int rc = allow_dynamic_smem(kernel, SMEM_BYTES, configured)) return rc;
   kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, tc, p);
   HMC_LAUNCH_OK();
   return 0;

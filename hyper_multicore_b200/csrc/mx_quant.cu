@@ -334,12 +334,9 @@ extern "C" int hmc_mx_quant(const hmc_mx_quant_args* args, void* stream_ptr) {
   p.col_data = static_cast<uint8_t*>(a.col_data);
   p.col_scale = static_cast<uint8_t*>(a.col_scale);
   p.dense = static_cast<__nv_bfloat16*>(a.dense);
-  static bool configured = false;
+  static PerDeviceFlag configured{};
   const int smem = TILE * LDB * sizeof(__nv_bfloat16);
-  if (!configured) {
-    HMC_CUDA_OK(cudaFuncSetAttribute(mx_quant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    configured = true;
-  }
+  if (int rc = allow_dynamic_smem(mx_quant_kernel, smem, configured)) return rc;
   // only blocks that can hold rows are launched: ceil(rows / 128) + groups bounds them
   long long blocks = (a.rows + 127) / 128 + a.groups;
   if (blocks > a.pad_blocks) blocks = a.pad_blocks;

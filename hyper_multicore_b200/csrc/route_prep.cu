@@ -248,7 +248,7 @@ unpermute_kernel(const uint4* __restrict__ y, const int* __restrict__ mapping, c
 __global__ void __launch_bounds__(128)
 unpermute_grad_kernel(const uint4* __restrict__ y, const uint4* __restrict__ grad_out,
                       const int* __restrict__ mapping, const float* __restrict__ probs, long long tokens,
-                      int top_k, int vec_per_row, uint4* __restrict__ grad_permuted,
+                      int top_k, int vec_per_row, long long permuted_rows, uint4* __restrict__ grad_permuted,
                       float* __restrict__ grad_probs, int* __restrict__ status) {
   __shared__ float partial[4];
   const long long t = blockIdx.x;
@@ -258,7 +258,7 @@ unpermute_grad_kernel(const uint4* __restrict__ y, const uint4* __restrict__ gra
     const int r = mapping[t * top_k + k];
     const float w = probs[t * top_k + k];
     float dot = 0.f;
-    if (r >= 0) {
+    if (r >= 0 && r < permuted_rows) {
       for (int v = threadIdx.x; v < vec_per_row; v += blockDim.x) {
         const uint4 g = ld_16(grad_out + t * vec_per_row + v);
         const uint32_t gw[4] = {g.x, g.y, g.z, g.w};
@@ -292,27 +292,53 @@ unpermute_grad_kernel(const uint4* __restrict__ y, const uint4* __restrict__ gra
   }
 }
 
-// dX[t] = sum_k dXe[row(t,k)] with one FP32 accumulation and a single BF16 rounding.
+// dX[t] = sum over the token's routes of dXe[row(t,k)], added the way the golden's autograd adds them:
+// every expert's index_select hands the token one BF16 row, the engine accumulates those rows as the
+// per-expert backward nodes run, last expert first, and every addition rounds to BF16
+// (tests/common/multicore/moe_reference.py:170-181 under torch.autograd). Rows are expert-major, so
+// "last expert first" is descending row order. One CTA of 128 threads per token.
 __global__ void __launch_bounds__(128)
 permute_grad_kernel(const uint4* __restrict__ grad_permuted, const int* __restrict__ mapping, long long tokens,
                     int top_k, int vec_per_row, long long rows, uint4* __restrict__ grad_tokens,
                     int* __restrict__ status) {
+  __shared__ int order[MAX_TOP_K];
   const long long t = blockIdx.x;
+  if (threadIdx.x == 0) {
+    // insertion sort by descending row; rejected entries (-1) sink to the end
+    for (int k = 0; k < top_k; ++k) {
+      int r = mapping[t * top_k + k];
+      if (r < 0 || r >= rows) {
+        report_status(status, HMC_STATUS_BAD_INDEX, static_cast<int>(t), k, r);
+        r = -1;
+      }
+      int j = k;
+      while (j > 0 && order[j - 1] < r) {
+        order[j] = order[j - 1];
+        --j;
+      }
+      order[j] = r;
+    }
+  }
+  __syncthreads();
   for (int v = threadIdx.x; v < vec_per_row; v += blockDim.x) {
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    for (int k = 0; k < top_k; ++k) {
-      const int r = mapping[t * top_k + k];
-      if (r < 0 || r >= rows) {
-        if (v == 0) report_status(status, HMC_STATUS_BAD_INDEX, static_cast<int>(t), k, r);
-        continue;
-      }
-      const uint4 q = ld_nc_16(grad_permuted + static_cast<long long>(r) * vec_per_row + v);
-      const uint32_t words[4] = {q.x, q.y, q.z, q.w};
+    for (int k0 = 0; k0 < top_k; k0 += 4) {
+      uint4 q[4];  // four rows in flight: the loads do not depend on the running sum
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 f = unpack_bf16x2(words[j]);
-        acc[2 * j] += f.x;
-        acc[2 * j + 1] += f.y;
+      for (int i = 0; i < 4; ++i) {
+        const int r = k0 + i < top_k ? order[k0 + i] : -1;
+        q[i] = r >= 0 ? ld_nc_16(grad_permuted + static_cast<long long>(r) * vec_per_row + v) : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        if (k0 + i >= top_k || order[k0 + i] < 0) continue;
+        const uint32_t words[4] = {q[i].x, q[i].y, q[i].z, q[i].w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = unpack_bf16x2(words[j]);
+          acc[2 * j] = bf16_round(acc[2 * j] + f.x);  // the first row passes unchanged: 0 + x is exact
+          acc[2 * j + 1] = bf16_round(acc[2 * j + 1] + f.y);
+        }
       }
     }
     uint4 o;
@@ -540,7 +566,8 @@ extern "C" int hmc_moe_unpermute_grad(const void* permuted, const void* grad_out
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
   unpermute_grad_kernel<<<static_cast<unsigned>(num_tokens), 128, 0, stream>>>(
       static_cast<const uint4*>(permuted), static_cast<const uint4*>(grad_out), mapping, probs, num_tokens,
-      static_cast<int>(top_k), static_cast<int>(hidden / 8), static_cast<uint4*>(grad_permuted), grad_probs, status);
+      static_cast<int>(top_k), static_cast<int>(hidden / 8), num_tokens * top_k, static_cast<uint4*>(grad_permuted),
+      grad_probs, status);
   HMC_LAUNCH_OK();
   return 0;
 }
@@ -552,6 +579,7 @@ extern "C" int hmc_moe_token_permute_grad(const void* grad_permuted, const int32
   int rc = check_rows("hmc_moe_token_permute_grad", grad_permuted, grad_tokens, hidden);
   if (rc != 0) return rc;
   HMC_REQUIRE(mapping != nullptr && top_k > 0, HMC_ERR_INVALID, "hmc_moe_token_permute_grad: bad arguments");
+  HMC_REQUIRE(top_k <= MAX_TOP_K, HMC_ERR_LIMIT, "hmc_moe_token_permute_grad: top_k must be in [1, %d]", MAX_TOP_K);
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
   permute_grad_kernel<<<static_cast<unsigned>(num_tokens), 128, 0, stream>>>(
       static_cast<const uint4*>(grad_permuted), mapping, num_tokens, static_cast<int>(top_k),
@@ -616,7 +644,10 @@ extern "C" int hmc_route_offsets(const int32_t* counts, int64_t ep, int64_t expe
 static __device__ __align__(256) int g_sort_scratch[HMC_SORT_STATIC_BYTES / sizeof(int)];
 
 // In host code the array's name is only a handle; the device address comes from
-// cudaGetSymbolAddress, asked once per device with that device current.
+// cudaGetSymbolAddress, asked once per device with that device current. The cache is indexed by the
+// CURRENT device (the stream passed in must belong to it), is written without a lock (two host threads
+// making the first call store the same value, which is harmless) and is not dropped by cudaDeviceReset:
+// a process that resets a device must not call this entry point on it again.
 static int* g_sort_scratch_address[64];
 
 extern "C" int hmc_moe_sort_routes_static(const void* indices, int indices_are_i64, int64_t entries,

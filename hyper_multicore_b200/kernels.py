@@ -50,6 +50,7 @@ def grouped_gemm(
     row_probs: torch.Tensor | None = None,
     row_dot: torch.Tensor | None = None,
     combine: dict | None = None,
+    pipe_budget_ns: int = 0,
 ) -> None:
     """Launch the tcgen05 grouped GEMM.
 
@@ -63,7 +64,9 @@ def grouped_gemm(
     RAGGED_M: ``a`` [rows, k]; ``b`` [groups, k, n_cols] (MN) or [groups, n_cols, k] (K); ``c`` [rows, *].
     RAGGED_K: ``a`` [rows, m]; ``b`` [rows, n]; ``c`` [groups, m, n] BF16 or FP32.
     """
-    device = _require_cuda(a, b, c, group_ends, aux, ready_counters, status, row_probs, row_dot)
+    device = _require_cuda(a, b, c, group_ends, aux, status, row_probs, row_dot)
+    if ready_counters is not None and not (ready_counters.is_cuda or ready_counters.is_pinned()):
+        raise ValueError("ready_counters must live in device memory or in pinned (device-visible) host memory")
     if c is None and combine is None:
         raise ValueError("grouped_gemm needs an output tensor unless its rows are combined to their sources")
     for name, plane in (("row_probs", row_probs), ("row_dot", row_dot)):
@@ -101,6 +104,7 @@ def grouped_gemm(
     args.swiglu_limit = swiglu_limit
     args.row_probs = _lib.ptr(row_probs)
     args.row_dot = _lib.ptr(row_dot)
+    args.pipe_budget_ns = pipe_budget_ns
     fused = None
     if combine is not None:
         fused = _lib.GemmCombine()

@@ -718,8 +718,8 @@ class MegaMoeExperts(torch.nn.Module):
         if before_fc2:
             # The rows are already weighted: the Top-K rows of a token are summed as they are
             # (reference: _restore_unweighted_output, backends/bf16/autograd.py:133-135).
-            kernels.moe_token_permute_grad(live, route.mapping, hidden.shape[0], self.top_k, out,
-                                           status=self._status)
+            # in ascending expert order with a BF16 rounding per addition, like the golden's index_add
+            kernels.moe_unpermute(live, route.mapping, None, hidden.shape[0], self.top_k, out, status=self._status)
             saved_last = saved_probs if saved_probs is not None else torch.empty(0, device=device)
         else:
             kernels.moe_unpermute(live, route.mapping, probs, hidden.shape[0], self.top_k, out,

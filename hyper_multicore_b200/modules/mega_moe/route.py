@@ -72,6 +72,32 @@ def validate_topk_inputs(hidden: torch.Tensor, topk_ids: torch.Tensor, topk_weig
         raise ValueError("hidden_states, topk_ids and topk_weights must be on one device.")
 
 
+def check_gathered_rows(host: list[list[int]], top_k: int, num_experts: int) -> list[list[int]]:
+    """Validate the gathered table [invalid, local tokens, autograd, counts...] of every EP rank.
+
+    Every rank holds the same rows, so every rank takes the same decision and raises the same error
+    together: nobody is left waiting in a collective or in a device wait
+    (reference: _validate_dynamic_rows, hyper_multicore/modules/mega_moe/route.py:585-593, and the
+    validity header of 850-868). Returns the per-rank count rows. Pure host logic: runs on plain lists.
+    """
+    if any(row[0] for row in host):
+        bad = [r for r, row in enumerate(host) if row[0]]
+        raise ValueError(f"MegaMoeExperts received invalid inputs on EP rank(s) {bad}; all ranks reject the call.")
+    if len({row[2] for row in host}) != 1:
+        # a rank that skips backward would leave its peers waiting in theirs
+        raise RuntimeError("MegaMoe autograd participation differs across EP ranks")
+    host_counts = [row[_HEADER:] for row in host]
+    # A rank whose counts do not add up to its tokens * top_k dropped out-of-range expert ids, and ALL
+    # ranks reject the call (a peer that went on would wait for rows that never come).
+    short = [r for r, row in enumerate(host) if sum(host_counts[r]) != row[1] * top_k]
+    if short:
+        missing = sum(host[r][1] * top_k - sum(host_counts[r]) for r in short)
+        raise ValueError(
+            f"topk_ids must hold expert ids in [0, {num_experts}): {missing} routes fell outside that range "
+            f"on EP rank(s) {short}; all ranks reject the call.")
+    return host_counts
+
+
 def prepare_route(hidden: torch.Tensor, topk_ids: torch.Tensor, *, num_experts: int, top_k: int, ep_size: int,
                   rank: int, group: Any | None, invalid: bool = False, status=None,
                   autograd: bool = False, control: Any | None = None, budget_ns: int = 0) -> PreparedRoute:
@@ -142,18 +168,7 @@ def prepare_route(hidden: torch.Tensor, topk_ids: torch.Tensor, *, num_experts: 
         table = table_with_header[:, _HEADER:].contiguous()
         offsets = kernels.route_offsets(table, rank)
         host = table_with_header.tolist()  # the one host synchronisation of the call
-    if any(row[0] for row in host):
-        bad = [r for r, row in enumerate(host) if row[0]]
-        raise ValueError(f"MegaMoeExperts received invalid inputs on EP rank(s) {bad}; all ranks reject the call.")
-    if len({row[2] for row in host}) != 1:
-        # a rank that skips backward would leave its peers waiting in theirs
-        # (reference: _validate_dynamic_rows, hyper_multicore/modules/mega_moe/route.py:585-593)
-        raise RuntimeError("MegaMoe autograd participation differs across EP ranks")
-    host_counts = [row[_HEADER:] for row in host]
-    if sum(host_counts[rank]) != tokens * top_k:
-        raise ValueError(
-            f"topk_ids must hold expert ids in [0, {num_experts}): {tokens * top_k - sum(host_counts[rank])} "
-            "routes fell outside that range.")
+    host_counts = check_gathered_rows(host, top_k, num_experts)
     local = num_experts // ep_size
     received = [sum(sum(row[d * local:(d + 1) * local]) for row in host_counts) for d in range(ep_size)]
     routed = [sum(row) for row in host_counts]

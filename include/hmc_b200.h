@@ -118,6 +118,9 @@ typedef struct hmc_grouped_gemm_args {
   float* row_dot;         /* SWIGLU_GRAD with row_probs: row_dot[row] += sum_col bf16(act) * bf16(acc), the
                              probability gradient; zeroed by the caller */
   const hmc_gemm_combine* combine; /* optional, RAGGED_M + STORE_BF16: c is ignored, rows go to their sources */
+  uint64_t pipe_budget_ns;         /* bound of the kernel's internal barrier waits, 0 = 4 s. With ready_counters the
+                                      consumer-side waits add ready_budget_ns to it: while the producer is allowed to
+                                      wait for late rows, the warps behind it must not give up first */
 } hmc_grouped_gemm_args;
 
 int hmc_grouped_gemm(const hmc_grouped_gemm_args* args, void* stream);
@@ -294,7 +297,10 @@ int hmc_gate_project_promoted(const void* x_bf16, const void* w, int w_is_bf16, 
  * hmc_moe_unpermute         : restore_topk_output (route.py:1029-1051), rounding as in the golden
  *                             (tests/common/multicore/moe_reference.py:179-180)
  * hmc_moe_unpermute_grad    : mega_moe_unpermute_grad_out (torch/csrc/mega_moe_unpermute.cpp:56-65)
- * hmc_moe_token_permute_grad: moe_token_permute_grad (torch/csrc/moe_token_permute_grad.cpp:29-38)
+ * hmc_moe_token_permute_grad: moe_token_permute_grad (torch/csrc/moe_token_permute_grad.cpp:29-38); a token's
+ *                             rows are added in descending row (= expert) order with a BF16 rounding per
+ *                             addition, the order torch.autograd gives the golden
+ *                             (tests/common/multicore/moe_reference.py:170-181)
  * hmc_zero_empty_expert_grad: zero_empty_expert_grad_ (torch/csrc/mega_moe_utilities.cpp:64-92)
  * hmc_route_offsets         : route_offsets / _compute_route_metadata, push mode
  *                             (route.py:309-390, utilities.asc:89-151); row units. totals =
@@ -315,7 +321,10 @@ int hmc_moe_sort_routes(const void* indices, int indices_are_i64, int64_t entrie
  *    ceil(entries / 1024) * experts <= 1 Mi (for example 1 Mi routes over 1024 experts); larger
  *    problems return HMC_ERR_LIMIT and must use hmc_moe_sort_routes;
  *  - the first call on each device looks up the array's device address (with that device current);
- *    make that first call before any stream capture begins;
+ *    make that first call before any stream capture begins. The address is remembered per CURRENT
+ *    device: `stream` must belong to the current device. The first calls of two host threads may both
+ *    do the look-up (they store the same value). The remembered address does not survive
+ *    cudaDeviceReset: do not call this entry point on a device after resetting it;
  *  - all calls on a device share the array: two calls whose kernels overlap on the GPU (different
  *    streams, no ordering) race on it. Calls ordered on one stream are safe, and nothing needs
  *    clearing between them;

@@ -94,6 +94,26 @@ def _worker(rank: int, world: int, port: int, failures) -> None:
             for target, rows in owner_rows[rank]:
                 restored[target:target + rows.shape[0]] = rows
         assert torch.equal(restored, routed), "combine does not return every row to its source slot"
+        # failure convergence: the validity header travels with the counts, every rank validates the same
+        # gathered rows and so every rank raises together (nobody goes on into a wait the other never joins)
+        from hyper_multicore_b200.modules.mega_moe.route import check_gathered_rows
+
+        def gather_rows(invalid: bool, autograd: bool, dropped: int = 0):
+            counts_row = oroute.counts(ids, experts).tolist()
+            if dropped:  # routes the sort dropped as out of range
+                counts_row[next(i for i, c in enumerate(counts_row) if c >= dropped)] -= dropped
+            payload = torch.tensor([int(invalid), tokens, int(autograd)] + counts_row, dtype=torch.int32)
+            rows = [torch.empty_like(payload) for _ in range(world)]
+            dist.all_gather(rows, payload)
+            return [row.tolist() for row in rows]
+
+        assert check_gathered_rows(gather_rows(False, True), top_k, experts) == table.tolist()
+        with pytest.raises(ValueError, match=r"invalid inputs on EP rank\(s\) \[1\]; all ranks reject"):
+            check_gathered_rows(gather_rows(rank == 1, True), top_k, experts)
+        with pytest.raises(RuntimeError, match="autograd participation differs"):
+            check_gathered_rows(gather_rows(False, rank == 0), top_k, experts)
+        with pytest.raises(ValueError, match=r"outside that range on EP rank\(s\) \[0\]; all ranks reject"):
+            check_gathered_rows(gather_rows(False, True, dropped=1 if rank == 0 else 0), top_k, experts)
         dist.barrier()
         dist.destroy_process_group()
     except BaseException as error:  # pylint: disable=broad-except

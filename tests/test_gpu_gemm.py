@@ -160,3 +160,69 @@ def test_arrival_counters_gate_the_groups(cuda_device):
     K.grouped_gemm(a, w, c, _ends(counts, dev), mode=K.HMC_GEMM_RAGGED_M, ready_counters=ready, status=status)
     torch.cuda.synchronize()
     assert status.tolist()[0] == 0
+
+
+def test_late_rows_do_not_look_like_a_pipeline_fault(cuda_device):
+    """The producer may wait for a peer's rows for the whole arrival budget; the MMA and epilogue warps
+    behind it must outlast that wait. Here the internal barrier budget (20 ms) runs out long before the
+    missing row "arrives" (the host advances the counter, which lives in pinned host memory, after
+    0.3 s) and well inside the arrival budget (5 s): the GEMM must finish with a clean status."""
+    import time
+
+    from hyper_multicore_b200 import _lib, kernels as K
+
+    dev = cuda_device
+    counts = [130, 70]
+    a = torch.randn(200, 64, device=dev).bfloat16()
+    w = torch.randn(2, 64, 256, device=dev).bfloat16()
+    for tile_mode in (1, 2):
+        c = torch.zeros(200, 256, device=dev, dtype=torch.bfloat16)
+        ready = torch.tensor([130, 69], dtype=torch.int32).pin_memory()
+        status = _lib.new_status(dev)
+        torch.cuda.synchronize()
+        K.grouped_gemm(a, w, c, _ends(counts, dev), mode=K.HMC_GEMM_RAGGED_M, ready_counters=ready, status=status,
+                       ready_budget_ns=5_000_000_000, pipe_budget_ns=20_000_000, tile_mode=tile_mode)
+        time.sleep(0.3)
+        ready[1] = 70
+        torch.cuda.synchronize()
+        assert status.tolist()[0] == 0, status.tolist()
+        _close(c[130:], a[130:].float() @ w[1].float())
+
+
+def test_ready_flag_that_nobody_publishes_times_out(cuda_device):
+    """A dispatch towards a generation no peer has declared itself ready for gives up after its budget with
+    HMC_STATUS_TIMEOUT_READY {peer, expected, seen}; the kernel returns, and the next, published, call
+    on the same control block is healthy."""
+    import ctypes
+
+    from hyper_multicore_b200 import _lib, kernels as K
+
+    dev = cuda_device
+    rows, hidden, experts = 64, 128, 4
+    tokens = torch.randn(rows, hidden, device=dev).bfloat16()
+    expert_of_row = torch.arange(rows, device=dev, dtype=torch.int32) // (rows // experts)
+    counts = torch.full((1, experts), rows // experts, dtype=torch.int32, device=dev)
+    off = K.route_offsets(counts, 0)
+    ctrl = torch.zeros(_lib.HMC_CTRL_WORDS, dtype=torch.int32, device=dev)
+    received = torch.zeros(rows, hidden, device=dev, dtype=torch.bfloat16)
+    peers = (ctypes.c_void_p * 1)(received.data_ptr())
+    peer_ctrl = (ctypes.c_void_p * 1)(ctrl.data_ptr())
+    status = _lib.new_status(dev)
+
+    def dispatch(generation):
+        K.ep_dispatch(tokens, None, expert_of_row, off["dispatch_src_off"], off["dispatch_target_off"], rows=rows,
+                      top_k=1, ep=1, local_experts=experts, capacity_rows=rows, peer_buffers=peers,
+                      peer_ctrl=peer_ctrl, local_ctrl=ctrl, generation=generation, status=status,
+                      budget_ns=20_000_000)
+        torch.cuda.synchronize()
+
+    dispatch(5)  # the ready word still holds 0
+    words = status.tolist()
+    assert words[0] == 3 and words[1:4] == [0, 5, 0], words
+    assert not received.any(), "no row may be stored towards a peer that is not ready"
+    status.zero_()
+    K._call("hmc_ep_publish_ready", dev, peer_ctrl, 1, 0, 5)
+    dispatch(5)
+    assert status.tolist()[0] == 0
+    assert torch.equal(received, tokens)
+    assert ctrl[:experts].tolist() == [rows // experts] * experts
