@@ -27,6 +27,8 @@ HMC_STATUS_WORDS = 8
 HMC_CTRL_SOURCE = 1296
 HMC_CTRL_COUNTS = 1552
 HMC_CLAMP_NONE, HMC_CLAMP_BEFORE_SILU, HMC_CLAMP_AFTER_SILU = 0, 1, 2
+HMC_MOE_LAYOUT = {"EIO": 0, "EOI": 1}
+HMC_MOE_DISPATCH = {"push": 0, "pull": 1}
 
 STATUS_NAMES = {
     0: "ok",
@@ -81,6 +83,7 @@ class GroupedGemmArgs(ctypes.Structure):
         ("row_dot", c_void_p),
         ("combine", c_void_p),
         ("pipe_budget_ns", c_uint64),
+        ("dispatch", c_void_p),
     ]
 
 
@@ -159,6 +162,7 @@ class EpDispatchArgs(ctypes.Structure):
         ("peer_buffers", c_void_p), ("peer_ctrl", c_void_p), ("local_ctrl", c_void_p),
         ("generation", c_int32), ("max_ctas", c_int32), ("budget_ns", c_uint64), ("status", c_void_p),
         ("row_values", c_void_p), ("value_index", c_void_p), ("value_plane_offset", c_int64),
+        ("rank", c_int64),
     ]
 
 
@@ -221,6 +225,100 @@ class MxQuantArgs(ctypes.Structure):
         ("dense", c_void_p),
     ]
 
+
+class MoeTransport(ctypes.Structure):
+    """Mirror of ``hmc_moe_transport``."""
+
+    _fields_ = [
+        ("ep", c_int64), ("rank", c_int64), ("peer_dispatch", c_void_p), ("peer_combine", c_void_p),
+        ("peer_ctrl", c_void_p), ("dispatch_rows_limit", c_int64), ("combine_rows_limit", c_int64),
+        ("dispatch_plane_offset", c_int64), ("combine_plane_offset", c_int64), ("generation", c_int32),
+        ("dispatch_mode", c_int32), ("wait_budget_ns", c_uint64), ("copy_stream", c_void_p),
+    ]
+
+
+class MegaMoeArgs(ctypes.Structure):
+    """Mirror of ``hmc_mega_moe_args``."""
+
+    _fields_ = [
+        ("dispatch_target", c_void_p), ("dispatch_target_off", c_void_p), ("dispatch_src", c_void_p),
+        ("dispatch_src_off", c_void_p), ("dispatch_size", c_void_p), ("up_proj_weight", c_void_p),
+        ("up_proj_glist", c_void_p), ("up_proj_y", c_void_p), ("swiglu_out", c_void_p),
+        ("down_proj_weight", c_void_p), ("down_proj_glist", c_void_p), ("down_proj_y", c_void_p),
+        ("combine_target", c_void_p), ("combine_target_off", c_void_p), ("combine_src_off", c_void_p),
+        ("combine_size", c_void_p), ("all_event_counters", c_void_p), ("diagnostic_buffer", c_void_p),
+        ("rank_id", c_int64), ("ep", c_int64), ("expert_num", c_int64), ("hidden_size", c_int64),
+        ("seq_size", c_int64), ("intermediate_size", c_int64), ("top_k", c_int64), ("routed_rows", c_int64),
+        ("received_rows", c_int64), ("weight_layout", c_int32), ("swiglu_clamp", c_int32),
+        ("swiglu_limit", c_float), ("fuse_dispatch", c_int32), ("dispatch_src_index", c_void_p),
+        ("expert_of_row", c_void_p), ("recv_segment_start", c_void_p), ("route_probs", c_void_p),
+        ("row_probs", c_void_p), ("transport", c_void_p), ("saved_dispatch", c_void_p),
+        ("saved_combine", c_void_p), ("saved_row_probs", c_void_p), ("mapping", c_void_p),
+        ("topk_probs", c_void_p), ("output", c_void_p),
+    ]
+
+
+class MegaMoeGradArgs(ctypes.Structure):
+    """Mirror of ``hmc_mega_moe_grad_args``."""
+
+    _fields_ = [
+        ("dispatch_target", c_void_p), ("dispatch_target_off", c_void_p), ("dy", c_void_p),
+        ("dispatch_src_off", c_void_p), ("dispatch_size", c_void_p), ("hidden", c_void_p), ("hidden_dw", c_void_p),
+        ("w2", c_void_p), ("act_grad_y", c_void_p), ("gate", c_void_p), ("grad_gate", c_void_p), ("w1", c_void_p),
+        ("gate_dx", c_void_p), ("grad_x", c_void_p), ("combine_target_off", c_void_p),
+        ("combine_src_off", c_void_p), ("combine_size", c_void_p), ("permute_out", c_void_p),
+        ("gate_dw", c_void_p), ("group_list", c_void_p), ("all_event_counters", c_void_p),
+        ("diagnostic_buffer", c_void_p), ("rank_id", c_int64), ("ep", c_int64), ("expert_num", c_int64),
+        ("hidden_size", c_int64), ("seq_size", c_int64), ("intermediate_size", c_int64), ("top_k", c_int64),
+        ("routed_rows", c_int64), ("received_rows", c_int64), ("weight_layout", c_int32),
+        ("swiglu_clamp", c_int32), ("swiglu_limit", c_float), ("fuse_dispatch", c_int32),
+        ("weight_grad_f32", c_int32), ("reserved", c_int32), ("dispatch_src_index", c_void_p),
+        ("expert_of_row", c_void_p), ("recv_segment_start", c_void_p), ("row_probs", c_void_p),
+        ("row_dot", c_void_p), ("transport", c_void_p), ("grad_output", c_void_p), ("saved_combine", c_void_p),
+        ("mapping", c_void_p), ("topk_probs", c_void_p), ("grad_probs", c_void_p), ("grad_hidden", c_void_p),
+    ]
+
+
+class MegaMoeMxfp8Args(ctypes.Structure):
+    """Mirror of ``hmc_mega_moe_mxfp8_args``."""
+
+    _fields_ = [
+        ("dispatch_buffer", c_void_p), ("dispatch_target_off", c_void_p), ("source_buffer", c_void_p),
+        ("dispatch_src_off", c_void_p), ("dispatch_size", c_void_p), ("w1_col_data", c_void_p),
+        ("group_list", c_void_p), ("up", c_void_p), ("a_row", c_void_p), ("w2_col_data", c_void_p),
+        ("group_list2", c_void_p), ("down", c_void_p), ("routed_buffer", c_void_p),
+        ("combine_target_off", c_void_p), ("combine_src_off", c_void_p), ("combine_size", c_void_p),
+        ("x_row", c_void_p), ("x_scale", c_void_p), ("x_col", c_void_p), ("x_col_scale", c_void_p),
+        ("a_scale", c_void_p), ("a_col", c_void_p), ("a_col_scale", c_void_p), ("w1_col_scale", c_void_p),
+        ("w2_col_scale", c_void_p), ("all_event_counters", c_void_p), ("diagnostic_buffer", c_void_p),
+        ("rank_id", c_int64), ("ep", c_int64), ("expert_num", c_int64), ("hidden_size", c_int64),
+        ("seq_size", c_int64), ("intermediate_size", c_int64), ("top_k", c_int64), ("routed_rows", c_int64),
+        ("received_rows", c_int64), ("pad_blocks", c_int64), ("dispatch_src_index", c_void_p),
+        ("expert_of_row", c_void_p), ("recv_segment_start", c_void_p), ("transport", c_void_p),
+        ("saved_combine", c_void_p), ("mapping", c_void_p), ("topk_probs", c_void_p), ("output", c_void_p),
+    ]
+
+
+class MegaMoeMxfp8GradArgs(ctypes.Structure):
+    """Mirror of ``hmc_mega_moe_mxfp8_grad_args``."""
+
+    _fields_ = [
+        ("dispatch", c_void_p), ("dispatch_target_off", c_void_p), ("source", c_void_p),
+        ("dispatch_src_off", c_void_p), ("dispatch_size", c_void_p), ("a_col", c_void_p), ("dw2", c_void_p),
+        ("w2_row_data", c_void_p), ("da", c_void_p), ("up", c_void_p), ("du_row", c_void_p),
+        ("w1_row_data", c_void_p), ("dx", c_void_p), ("routed_buffer", c_void_p), ("combine_target_off", c_void_p),
+        ("combine_src_off", c_void_p), ("combine_size", c_void_p), ("x_col", c_void_p), ("dw1", c_void_p),
+        ("group_list", c_void_p), ("dy_row", c_void_p), ("dy_scale", c_void_p), ("dy_col", c_void_p),
+        ("dy_col_scale", c_void_p), ("a_col_scale", c_void_p), ("w2_row_scale", c_void_p), ("du_scale", c_void_p),
+        ("du_col", c_void_p), ("du_col_scale", c_void_p), ("w1_row_scale", c_void_p), ("x_col_scale", c_void_p),
+        ("all_event_counters", c_void_p), ("diagnostic_buffer", c_void_p), ("rank_id", c_int64), ("ep", c_int64),
+        ("expert_num", c_int64), ("hidden_size", c_int64), ("seq_size", c_int64), ("intermediate_size", c_int64),
+        ("top_k", c_int64), ("routed_rows", c_int64), ("received_rows", c_int64), ("pad_blocks", c_int64),
+        ("weight_grad_f32", c_int32), ("reserved", c_int32), ("recv_segment_start", c_void_p),
+        ("expert_of_row", c_void_p), ("transport", c_void_p), ("grad_output", c_void_p),
+        ("saved_combine", c_void_p), ("mapping", c_void_p), ("topk_probs", c_void_p), ("grad_probs", c_void_p),
+        ("grad_hidden", c_void_p),
+    ]
 
 HMC_MAX_EP = 16
 HMC_CTRL_ARRIVAL = 0
@@ -287,6 +385,11 @@ SIGNATURES: dict[str, tuple] = {
     "hmc_mega_mhc_grad_workspace_bytes": (_L, [_L, _L]),
     "hmc_mega_mhc": (_I, [ctypes.POINTER(MegaMhcArgs), _P]),
     "hmc_mega_mhc_grad": (_I, [ctypes.POINTER(MegaMhcGradArgs), _P]),
+    "hmc_mega_moe": (_I, [ctypes.POINTER(MegaMoeArgs), _P]),
+    "hmc_mega_moe_grad": (_I, [ctypes.POINTER(MegaMoeGradArgs), _P]),
+    "hmc_mega_moe_mxfp8": (_I, [ctypes.POINTER(MegaMoeMxfp8Args), _P]),
+    "hmc_mega_moe_mxfp8_grad": (_I, [ctypes.POINTER(MegaMoeMxfp8GradArgs), _P]),
+    "hmc_mega_moe_mxfp8_abi_version": (_I, []),
 }
 
 

@@ -157,8 +157,10 @@ __device__ __forceinline__ void report_status(int* status, int code, int a, int 
 }
 
 // Bounded poll on a local counter that peers (or other CTAs) advance. Returns false on time-out.
+// With `status`, the wait also ends (false) as soon as the status words carry an error: whoever was to
+// advance the counter may be the one that failed.
 __device__ __forceinline__ bool wait_counter_ge(const int* counter, int expected, uint64_t budget_ns,
-                                                int* observed) {
+                                                int* observed, const int* status = nullptr) {
   int v = ld_acquire_sys(counter);
   if (v >= expected) {
     *observed = v;
@@ -176,6 +178,7 @@ __device__ __forceinline__ bool wait_counter_ge(const int* counter, int expected
       __nanosleep(64);
     }
     if (global_timer_ns() - t0 > budget_ns) break;
+    if (status != nullptr && *reinterpret_cast<const volatile int*>(status) != 0) break;
   }
   *observed = v;
   return false;

@@ -19,6 +19,7 @@
 #include <string.h>
 
 #include "common.cuh"
+#include "ep_device.cuh"
 
 namespace hmc {
 namespace {
@@ -340,6 +341,51 @@ int fill_peers(PeerTable* table, void* const* data, void* const* ctrl, int64_t e
 }
 
 }  // namespace
+
+// Checks an hmc_ep_dispatch_args and turns it into the device-side description used by the dispatch
+// warps of the grouped GEMM (declared in grouped_gemm.cu).
+int fill_dispatch(DispatchFuse* out, const hmc_ep_dispatch_args& a, const char* who) {
+  PeerTable table;
+  int rc = fill_peers(&table, a.peer_buffers, a.peer_ctrl, a.ep);
+  if (rc != 0) return rc;
+  HMC_REQUIRE(a.tokens && a.expert_of_row && a.dispatch_src_off && a.dispatch_target_off && a.local_ctrl,
+              HMC_ERR_INVALID, "%s: null tensor pointer in the dispatch description", who);
+  HMC_REQUIRE(a.hidden > 0 && a.hidden % 8 == 0 && aligned16(a.tokens), HMC_ERR_INVALID,
+              "%s: dispatched rows must be 16-byte aligned multiples of 8 BF16 elements", who);
+  HMC_REQUIRE(a.local_experts > 0 && a.local_experts <= HMC_CTRL_MAX_LOCAL_EXPERTS, HMC_ERR_LIMIT,
+              "%s: local experts must be in [1, %d]", who, HMC_CTRL_MAX_LOCAL_EXPERTS);
+  HMC_REQUIRE(a.rows >= 0 && a.rows < (1ll << 31) && a.top_k > 0, HMC_ERR_INVALID, "%s: bad dispatch extents", who);
+  HMC_REQUIRE(a.rank >= 0 && a.rank < a.ep, HMC_ERR_INVALID, "%s: dispatch rank %lld outside [0, %lld)", who,
+              (long long)a.rank, (long long)a.ep);
+  HMC_REQUIRE(a.row_values == nullptr || (a.value_plane_offset >= a.capacity_rows * a.hidden * 2 &&
+                                          a.value_plane_offset % 4 == 0),
+              HMC_ERR_INVALID, "%s: the value plane must lie behind the rows of the receive buffer", who);
+  for (int p = 0; p < a.ep; ++p) {
+    HMC_REQUIRE(aligned16(a.peer_buffers[p]), HMC_ERR_INVALID, "%s: receive buffer %d is not 16-byte aligned", who, p);
+    out->peer_data[p] = table.data[p];
+    out->peer_ctrl[p] = table.ctrl[p];
+  }
+  out->tokens = static_cast<const uint4*>(a.tokens);
+  out->source_of_row = a.source_of_row;
+  out->expert_of_row = a.expert_of_row;
+  out->dispatch_src_off = reinterpret_cast<const long long*>(a.dispatch_src_off);
+  out->dispatch_target_off = reinterpret_cast<const long long*>(a.dispatch_target_off);
+  out->rows = a.rows;
+  out->capacity_rows = a.capacity_rows;
+  out->local_ctrl = a.local_ctrl;
+  out->row_values = a.row_values;
+  out->value_index = a.value_index;
+  out->value_plane_offset = a.value_plane_offset;
+  out->budget_ns = a.budget_ns ? a.budget_ns : 10ull * 1000 * 1000 * 1000;
+  out->top_k = static_cast<int>(a.top_k);
+  out->vec_per_row = static_cast<int>(a.hidden / 8);
+  out->ep = static_cast<int>(a.ep);
+  out->rank = static_cast<int>(a.rank);
+  out->local_experts = static_cast<int>(a.local_experts);
+  out->generation = a.generation;
+  return 0;
+}
+
 }  // namespace hmc
 
 using namespace hmc;

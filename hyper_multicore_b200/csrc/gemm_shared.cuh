@@ -4,6 +4,7 @@
 #include <cuda.h>
 
 #include "common.cuh"
+#include "ep_device.cuh"
 #include "sm100.cuh"
 
 namespace hmc {
@@ -55,6 +56,8 @@ struct Params {
   float swiglu_limit;
   const float* row_probs;  // optional per-row routing probability (weighting before FC2)
   float* row_dot;          // SWIGLU_GRAD with row_probs: per-row probability gradient (atomic adds)
+  int dispatch_enabled;    // extra warps of this kernel send this rank's rows to their owners (RAGGED_M, gated)
+  DispatchFuse dispatch;
 };
 
 struct Tile {

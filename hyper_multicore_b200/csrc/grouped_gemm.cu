@@ -7,9 +7,13 @@
 // (ops/hyper_mega_moe_grad/op_kernel/worker_kernel.cpp:164-195), and the "zero dW of cold
 // experts" rule (bf16_worker.h:62-75).
 //
-// One CTA per SM, 192 threads: warp 0 = TMA producer, warp 1 = MMA issuer (+TMEM owner),
+// One CTA per SM, 320 threads: warp 0 = TMA producer, warp 1 = MMA issuer (+TMEM owner),
 // warps 2..9 = epilogue (two warps per TMEM lane quarter, one column half each). Tiles are
 // 128 x 256 x 64. Weight-gradient tiles leave through shared memory and TMA stores.
+// With DISPATCH_WARPS > 0 the CTA carries extra warps that send this rank's rows to their owners
+// (peer stores + arrival counters) while the producer waits, per expert, for the rows this rank
+// receives: dispatch and the first tiles overlap inside one launch, as the reference's dispatch PUT
+// tasks and GMM1 do (ops/hyper_mega_moe/op_kernel/worker_kernel.cpp:301-366).
 //
 //  RAGGED_M : C[r0:r1, :] = A[r0:r1, :] * B_g      rows of group g are [ends[g-1], ends[g])
 //  RAGGED_K : C_g = A[r0:r1, :]^T * B[r0:r1, :]    contraction over the group's rows
@@ -27,8 +31,8 @@ using namespace gemm;
 
 using TileWalker = TileWalkerT<BM>;
 
-template <int A_MAJOR, int B_MAJOR>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+template <int A_MAJOR, int B_MAJOR, int DISPATCH_WARPS>
+__global__ void __launch_bounds__(NUM_THREADS + 32 * DISPATCH_WARPS, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                     const __grid_constant__ CUtensorMap tm_c, const Params p) {
   extern __shared__ uint8_t smem_raw[];
@@ -86,7 +90,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           // order the async-proxy (TMA) reads after the acquire.
           int seen = 0;
           const int need = static_cast<int>(t.row1 - t.row0);
-          if (!wait_counter_ge(p.ready_counters + t.group, need, p.ready_budget_ns, &seen)) {
+          if (!wait_counter_ge(p.ready_counters + t.group, need, p.ready_budget_ns, &seen, p.status)) {
             report_status(p.status, HMC_STATUS_TIMEOUT_ARRIVAL, t.group, need, seen);
             *abort_word = 1;
             ok = false;
@@ -217,6 +221,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         acc_phase ^= 1u;
       }
     }
+  } else if (DISPATCH_WARPS > 0 && warp >= 2 + EPI_WARPS) {
+    // ======================================================================== dispatch warps
+    if (p.dispatch_enabled)
+      dispatch_rows_warp(p.dispatch, static_cast<int>(blockIdx.x) * DISPATCH_WARPS + (warp - 2 - EPI_WARPS),
+                         static_cast<int>(gridDim.x) * DISPATCH_WARPS, lane, p.status);
   } else {
     // ======================================================================== epilogue
     TileWalker walker(p);
@@ -405,13 +414,15 @@ int make_map(CUtensorMap* out, const void* base, int rank, const cuuint64_t* dim
   return 0;
 }
 
-template <int A_MAJOR, int B_MAJOR>
+constexpr int SINGLE_DISPATCH_WARPS = 2;  // 384 threads x 168 registers still fit the register file
+
+template <int A_MAJOR, int B_MAJOR, int DISPATCH_WARPS = 0>
 int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const Params& p, int grid,
            cudaStream_t stream) {
   static PerDeviceFlag configured{};
-  auto kernel = grouped_gemm_kernel<A_MAJOR, B_MAJOR>;
+  auto kernel = grouped_gemm_kernel<A_MAJOR, B_MAJOR, DISPATCH_WARPS>;
   if (int rc = allow_dynamic_smem(kernel, SMEM_BYTES, configured)) return rc;
-  kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, tc, p);
+  kernel<<<grid, NUM_THREADS + 32 * DISPATCH_WARPS, SMEM_BYTES, stream>>>(ta, tb, tc, p);
   HMC_LAUNCH_OK();
   return 0;
 }
@@ -420,6 +431,7 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, 
 
 int launch_grouped_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const gemm::Params& p, int b_major, int grid,
                              cudaStream_t stream);
+int fill_dispatch(DispatchFuse* out, const hmc_ep_dispatch_args& a, const char* who);  // ep.cu
 int launch_grouped_gemm_pair_dw(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const gemm::Params& p,
                                 int grid, cudaStream_t stream);
 
@@ -450,7 +462,7 @@ extern "C" int hmc_grouped_gemm(const hmc_grouped_gemm_args* args, void* stream_
               "hmc_grouped_gemm: tensors must be 16-byte aligned");
   HMC_REQUIRE(a.n % 8 == 0, HMC_ERR_INVALID, "hmc_grouped_gemm: n (%lld) must be a multiple of 8",
               (long long)a.n);
-  if (a.rows == 0 && a.mode == HMC_GEMM_RAGGED_M) return 0;
+  if (a.rows == 0 && a.mode == HMC_GEMM_RAGGED_M && (a.dispatch == nullptr || a.dispatch->rows == 0)) return 0;
 
   Params p{};
   p.mode = a.mode;
@@ -505,6 +517,20 @@ extern "C" int hmc_grouped_gemm(const hmc_grouped_gemm_args* args, void* stream_
     p.combine_enabled = 1;
   }
 
+  if (a.dispatch != nullptr) {
+    const hmc_ep_dispatch_args& d = *a.dispatch;
+    HMC_REQUIRE(a.mode == HMC_GEMM_RAGGED_M && a.ready_counters != nullptr, HMC_ERR_INVALID,
+                "hmc_grouped_gemm: a fused dispatch belongs to a RAGGED_M GEMM gated by arrival counters");
+    int drc = fill_dispatch(&p.dispatch, d, "hmc_grouped_gemm");
+    if (drc != 0) return drc;
+    HMC_REQUIRE(d.local_experts == a.groups && d.hidden == a.k, HMC_ERR_INVALID,
+                "hmc_grouped_gemm: the fused dispatch must send rows of this GEMM's k (%lld) to groups (%d) experts per rank",
+                (long long)a.k, a.groups);
+    HMC_REQUIRE(d.peer_buffers[d.rank] == a.a, HMC_ERR_INVALID,
+                "hmc_grouped_gemm: with a fused dispatch, a must be this rank's own receive buffer");
+    p.dispatch_enabled = d.rows > 0 ? 1 : 0;
+  }
+
   CUtensorMap ta, tb, tc;
   int rc;
   if (a.mode == HMC_GEMM_RAGGED_M) {
@@ -522,7 +548,8 @@ extern "C" int hmc_grouped_gemm(const hmc_grouped_gemm_args* args, void* stream_
     p.ldc = static_cast<int>((swiglu || grad) ? 2 * a.n : a.n);
     p.ld_aux = static_cast<int>(swiglu ? a.n : 2 * a.n);
     {
-      cuuint64_t dims[2] = {static_cast<cuuint64_t>(a.k), static_cast<cuuint64_t>(a.rows)};
+      // a rank that receives nothing still launches when it has rows to send: one row keeps the map valid
+      cuuint64_t dims[2] = {static_cast<cuuint64_t>(a.k), static_cast<cuuint64_t>(a.rows > 0 ? a.rows : 1)};
       cuuint32_t box[2] = {64, BM};
       if ((rc = make_map(&ta, a.a, 2, dims, box)) != 0) return rc;
     }
@@ -577,7 +604,7 @@ extern "C" int hmc_grouped_gemm(const hmc_grouped_gemm_args* args, void* stream_
     const bool plain = f32 || a.epilogue == HMC_EPI_STORE_BF16;
     if (plain && !p.combine_enabled && (a.n * (f32 ? 4 : 2)) % 16 == 0 && aligned16(a.c)) {
       // C = [1, rows, n] seen through the same 32-row x 128-byte boxes as the weight gradients
-      cuuint64_t dims[3] = {static_cast<cuuint64_t>(a.n), static_cast<cuuint64_t>(a.rows), 1};
+      cuuint64_t dims[3] = {static_cast<cuuint64_t>(a.n), static_cast<cuuint64_t>(a.rows > 0 ? a.rows : 1), 1};
       cuuint32_t box[3] = {32u, 32, 1};
       if ((rc = make_map(&tc, a.c, 3, dims, box, f32, !f32)) != 0) return rc;
       p.tma_store = 1;
@@ -602,6 +629,11 @@ extern "C" int hmc_grouped_gemm(const hmc_grouped_gemm_args* args, void* stream_
   const bool use_pairs = a.tile_mode == HMC_TILE_PAIR || (a.tile_mode == HMC_TILE_AUTO && a.rows >= 192ll * a.groups);
   if (use_pairs && !p.combine_enabled && a.k % 8 == 0 && sm_count() >= 2)
     return launch_grouped_gemm_pair(ta, tb, p, a.b_major, grid, stream);
+  if (p.dispatch_enabled) {
+    if (a.b_major == HMC_MAJOR_MN)
+      return launch<HMC_MAJOR_K, HMC_MAJOR_MN, SINGLE_DISPATCH_WARPS>(ta, tb, tc, p, grid, stream);
+    return launch<HMC_MAJOR_K, HMC_MAJOR_K, SINGLE_DISPATCH_WARPS>(ta, tb, tc, p, grid, stream);
+  }
   if (a.b_major == HMC_MAJOR_MN) return launch<HMC_MAJOR_K, HMC_MAJOR_MN>(ta, tb, tc, p, grid, stream);
   return launch<HMC_MAJOR_K, HMC_MAJOR_K>(ta, tb, tc, p, grid, stream);
 }

@@ -26,8 +26,10 @@ constexpr int PAIR_STAGES = 6;
 constexpr int PAIR_SMEM_BYTES = PAIR_STAGES * PAIR_STAGE_BYTES + 1024 + 256;
 using PairWalker = TileWalkerT<PAIR_ROWS>;
 
-template <int B_MAJOR>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+// With DISPATCH_WARPS > 0 every CTA carries extra warps that send this rank's rows to their owners while
+// the producers wait, per expert, for the rows this rank receives (see grouped_gemm.cu).
+template <int B_MAJOR, int DISPATCH_WARPS>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS + 32 * DISPATCH_WARPS, 1)
 grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                          const Params p) {
   extern __shared__ uint8_t smem_raw[];
@@ -85,7 +87,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
         if (p.ready_counters != nullptr && t.group != ready_group) {
           int seen = 0;
           const int need = static_cast<int>(t.row1 - t.row0);
-          if (!wait_counter_ge(p.ready_counters + t.group, need, p.ready_budget_ns, &seen)) {
+          if (!wait_counter_ge(p.ready_counters + t.group, need, p.ready_budget_ns, &seen, p.status)) {
             report_status(p.status, HMC_STATUS_TIMEOUT_ARRIVAL, t.group, need, seen);
             *abort_word = 1;
             ok = false;
@@ -176,6 +178,11 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
         }
       }
     }
+  } else if (DISPATCH_WARPS > 0 && warp >= 2 + EPI_WARPS) {
+    // ======================================================================== dispatch warps (both CTAs)
+    if (p.dispatch_enabled)
+      dispatch_rows_warp(p.dispatch, static_cast<int>(blockIdx.x) * DISPATCH_WARPS + (warp - 2 - EPI_WARPS),
+                         static_cast<int>(gridDim.x) * DISPATCH_WARPS, lane, p.status);
   } else {
     // ======================================================================== epilogue (both CTAs)
     PairWalker walker(p);
@@ -220,12 +227,14 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
   }
 }
 
-template <int B_MAJOR>
+constexpr int PAIR_DISPATCH_WARPS = 4;  // 448 threads x 124 registers fit the register file
+
+template <int B_MAJOR, int DISPATCH_WARPS>
 int launch_pair_impl(const CUtensorMap& ta, const CUtensorMap& tb, const Params& p, int grid, cudaStream_t stream) {
   static PerDeviceFlag configured{};
-  auto kernel = grouped_gemm_pair_kernel<B_MAJOR>;
+  auto kernel = grouped_gemm_pair_kernel<B_MAJOR, DISPATCH_WARPS>;
   if (int rc = allow_dynamic_smem(kernel, PAIR_SMEM_BYTES, configured)) return rc;
-  kernel<<<grid, NUM_THREADS, PAIR_SMEM_BYTES, stream>>>(ta, tb, p);
+  kernel<<<grid, NUM_THREADS + 32 * DISPATCH_WARPS, PAIR_SMEM_BYTES, stream>>>(ta, tb, p);
   HMC_LAUNCH_OK();
   return 0;
 }
@@ -237,8 +246,12 @@ int launch_grouped_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const
                              cudaStream_t stream) {
   grid &= ~1;  // whole pairs
   if (grid < 2) grid = 2;
-  if (b_major == HMC_MAJOR_MN) return launch_pair_impl<HMC_MAJOR_MN>(ta, tb, p, grid, stream);
-  return launch_pair_impl<HMC_MAJOR_K>(ta, tb, p, grid, stream);
+  if (p.dispatch_enabled) {
+    if (b_major == HMC_MAJOR_MN) return launch_pair_impl<HMC_MAJOR_MN, PAIR_DISPATCH_WARPS>(ta, tb, p, grid, stream);
+    return launch_pair_impl<HMC_MAJOR_K, PAIR_DISPATCH_WARPS>(ta, tb, p, grid, stream);
+  }
+  if (b_major == HMC_MAJOR_MN) return launch_pair_impl<HMC_MAJOR_MN, 0>(ta, tb, p, grid, stream);
+  return launch_pair_impl<HMC_MAJOR_K, 0>(ta, tb, p, grid, stream);
 }
 
 }  // namespace hmc

@@ -51,6 +51,7 @@ def grouped_gemm(
     row_dot: torch.Tensor | None = None,
     combine: dict | None = None,
     pipe_budget_ns: int = 0,
+    dispatch: dict | None = None,
 ) -> None:
     """Launch the tcgen05 grouped GEMM.
 
@@ -60,6 +61,9 @@ def grouped_gemm(
     ``combine`` (RAGGED_M, BF16 stores) sends the result rows from the epilogue to the routed buffers of
     their source ranks: keys segment_start, combine_target_off (device int64), peer_buffers, peer_ctrl
     (ctypes pointer arrays), ep, local_experts, target_rows_limit; ``c`` may then be None.
+
+    ``dispatch`` (RAGGED_M with ``ready_counters``): the keyword arguments of ``ep_dispatch`` plus ``rank``;
+    extra warps of the GEMM then send this rank's rows while its tiles wait for the rows it receives.
 
     RAGGED_M: ``a`` [rows, k]; ``b`` [groups, k, n_cols] (MN) or [groups, n_cols, k] (K); ``c`` [rows, *].
     RAGGED_K: ``a`` [rows, m]; ``b`` [rows, n]; ``c`` [groups, m, n] BF16 or FP32.
@@ -115,6 +119,10 @@ def grouped_gemm(
         fused.ep, fused.local_experts = combine["ep"], combine["local_experts"]
         fused.target_rows_limit = combine["target_rows_limit"]
         args.combine = ctypes.cast(ctypes.pointer(fused), ctypes.c_void_p)
+    sending = None
+    if dispatch is not None:
+        sending = _dispatch_struct(**dispatch)
+        args.dispatch = ctypes.cast(ctypes.pointer(sending), ctypes.c_void_p)
     _count("hmc_grouped_gemm")
     with torch.cuda.device(device):
         _lib.check(_lib.load().hmc_grouped_gemm(ctypes.byref(args), _lib.stream_ptr(device)))
@@ -401,6 +409,18 @@ def ep_dispatch(tokens, source_of_row, expert_of_row, dispatch_src_off, dispatch
     """
     device = _require_cuda(tokens, expert_of_row, dispatch_src_off, dispatch_target_off, local_ctrl, row_values,
                            value_index)
+    args = _dispatch_struct(tokens, source_of_row, expert_of_row, dispatch_src_off, dispatch_target_off, rows=rows,
+                            top_k=top_k, ep=ep, local_experts=local_experts, capacity_rows=capacity_rows,
+                            peer_buffers=peer_buffers, peer_ctrl=peer_ctrl, local_ctrl=local_ctrl,
+                            generation=generation, status=status, budget_ns=budget_ns, max_ctas=max_ctas,
+                            row_values=row_values, value_index=value_index, value_plane_offset=value_plane_offset)
+    _call("hmc_ep_dispatch", device, ctypes.byref(args))
+
+
+def _dispatch_struct(tokens, source_of_row, expert_of_row, dispatch_src_off, dispatch_target_off, *, rows, top_k, ep,
+                     local_experts, capacity_rows, peer_buffers, peer_ctrl, local_ctrl, generation, status=None,
+                     budget_ns=0, max_ctas=0, row_values=None, value_index=None, value_plane_offset=0, rank=0):
+    """``hmc_ep_dispatch_args`` from tensors (``rank`` matters only when the dispatch rides inside a GEMM)."""
     if row_values is not None and (row_values.dtype != torch.float32 or not row_values.is_contiguous()):
         raise ValueError("row_values must be a contiguous float32 tensor")
     args = _lib.EpDispatchArgs()
@@ -418,7 +438,8 @@ def ep_dispatch(tokens, source_of_row, expert_of_row, dispatch_src_off, dispatch
     args.status = _lib.ptr(status)
     args.row_values, args.value_index = _lib.ptr(row_values), _lib.ptr(value_index)
     args.value_plane_offset = value_plane_offset
-    _call("hmc_ep_dispatch", device, ctypes.byref(args))
+    args.rank = rank
+    return args
 
 
 def ep_combine(results, segment_start, combine_target_off, *, rows, ep, local_experts, target_rows_limit,

@@ -26,7 +26,7 @@ from typing import Any
 import torch
 import torch.distributed as dist
 
-from ... import _lib, kernels
+from ... import _lib, kernels, ops
 from ...symm import PeerWorkspace, align_rows
 from .numerics import MegaMoeNumericsOptions, MegaMoeSchedulerOptions, MegaMoeTuningOptions
 from .route import PreparedRoute, prepare_route, validate_topk_inputs
@@ -115,10 +115,9 @@ class _LocalWorkspace:
         self.peer_ctrl = (ctypes.c_void_p * 1)(self.ctrl.data_ptr())
         self.generation = 0
 
-    def begin_call(self) -> int:
+    def next_generation(self) -> int:
+        """Generation of the next operator call (the operator clears the counters and publishes it)."""
         self.generation += 1
-        self.ctrl[:_lib.HMC_CTRL_READY].zero_()
-        kernels._call("hmc_ep_publish_ready", self.device, self.peer_ctrl, 1, 0, self.generation)  # pylint: disable=protected-access
         return self.generation
 
     def close(self) -> None:
@@ -251,6 +250,9 @@ class MegaMoeExperts(torch.nn.Module):
         # that is late by more than this makes its peers give up with a status word instead of hanging.
         self._wait_budget_ns = int(float(os.environ.get("HMC_EP_WAIT_SECONDS", "60")) * 1e9)
         self._backward_expected = False
+        # push dispatch rides inside the GEMM that consumes the rows; HMC_MOE_FUSED_DISPATCH=0 launches the
+        # stand-alone dispatch kernel ahead of it instead
+        self._fuse_dispatch = os.environ.get("HMC_MOE_FUSED_DISPATCH", "1") != "0"
         self._group = _ResourceGroup(self._compatibility_key())
         self._group.members.add(id(self))
         self._closed = False
@@ -563,11 +565,6 @@ class MegaMoeExperts(torch.nn.Module):
             raise
         return out.reshape(hidden_states.shape)
 
-    def _peer_tables(self, workspace, expert_buffer: torch.Tensor):
-        if isinstance(workspace, PeerWorkspace):
-            return workspace.peer_expert, workspace.peer_routed, workspace.peer_ctrl
-        return (ctypes.c_void_p * 1)(expert_buffer.data_ptr()), None, workspace.peer_ctrl
-
     def _swiglu_options(self) -> dict:
         """Clamp arguments of the SwiGLU epilogues (reference: docs/mega_moe.md:258-272)."""
         limit = self._numerics.swiglu_limit
@@ -575,37 +572,6 @@ class MegaMoeExperts(torch.nn.Module):
             return {}
         clamp = _lib.HMC_CLAMP_AFTER_SILU if self._numerics.clamp_after_silu else _lib.HMC_CLAMP_BEFORE_SILU
         return {"swiglu_clamp": clamp, "swiglu_limit": float(limit)}
-
-    def _pull_rows(self, workspace, route: PreparedRoute, generation: int, fill, values=None):
-        """Pull dispatch: `fill(rows)` writes this rank's expert-major rows into its source buffer, the
-        buffer is published, and this rank fetches the rows of its own experts from every source
-        (reference: owner-initiated GET, docs/design/mega_moe_design.md:33-35). Returns the received
-        rows (a local tensor of exactly the received size) and, with `values`, their per-row scalars."""
-        device = workspace.device
-        routed = route.routed_rows
-        if routed > 0:
-            fill(workspace.source_buffer[:routed])
-            if values is not None:
-                workspace.source_values[:routed].copy_(values)
-        kernels.ep_publish_source(workspace.peer_ctrl, self.ep_size, self._rank, generation, device)
-        rows = max(route.received_rows, 1)
-        out = torch.empty(rows, self.hidden_size, dtype=torch.bfloat16, device=device)
-        out_values = torch.empty(rows, dtype=torch.float32, device=device) if values is not None else None
-        off = route.offsets
-        kernels.ep_pull(out, off["recv_segment_start"], off["combine_target_off"], rows=route.received_rows,
-                        ep=self.ep_size, local_experts=self.local_experts, source_rows_limit=workspace.routed_rows,
-                        peer_sources=workspace.peer_source, local_ctrl=workspace.ctrl, generation=generation,
-                        status=self._status, budget_ns=self._wait_budget_ns, out_values=out_values,
-                        value_plane_offset=workspace.source_plane_offset)
-        return out, out_values
-
-    def _fused_combine(self, workspace, off, peer_routed, peer_ctrl) -> dict | None:
-        """Arguments that make a GEMM's epilogue return its rows to their source ranks."""
-        if self.ep_size == 1:
-            return None
-        return {"segment_start": off["recv_segment_start"], "combine_target_off": off["combine_target_off"],
-                "peer_buffers": peer_routed, "peer_ctrl": peer_ctrl, "ep": self.ep_size,
-                "local_experts": self.local_experts, "target_rows_limit": workspace.routed_rows}
 
     def _copy_stream(self, device: torch.device) -> torch.cuda.Stream:
         stream = getattr(self, "_side_stream", None)
@@ -620,122 +586,102 @@ class MegaMoeExperts(torch.nn.Module):
         return (raw[:rows * row_bytes].view(torch.bfloat16).view(rows, self.hidden_size),
                 raw[rows * row_bytes:].view(torch.float32), rows * row_bytes)
 
+    def _transport(self, workspace, generation: int, device: torch.device, local_buffer: torch.Tensor | None = None,
+                   local_plane_offset: int = 0) -> ops.MoeTransport:
+        """Endpoints of this call: the peer-mapped workspace of an EP group, or, on a single rank, the
+        call's own receive buffer standing in for "the owner's buffer"."""
+        if self.ep_size == 1:
+            return ops.MoeTransport(
+                ep=1, rank=0, peer_dispatch=(ctypes.c_void_p * 1)(_lib.ptr(local_buffer)), peer_combine=None,
+                peer_ctrl=workspace.peer_ctrl, dispatch_rows_limit=0 if local_buffer is None else local_buffer.shape[0],
+                dispatch_plane_offset=local_plane_offset, generation=generation, wait_budget_ns=self._wait_budget_ns)
+        pull = self._pull
+        return ops.MoeTransport(
+            ep=self.ep_size, rank=self._rank, peer_dispatch=workspace.peer_source if pull else workspace.peer_expert,
+            peer_combine=workspace.peer_routed, peer_ctrl=workspace.peer_ctrl,
+            dispatch_rows_limit=workspace.routed_rows if pull else workspace.capacity_rows,
+            combine_rows_limit=workspace.routed_rows,
+            dispatch_plane_offset=workspace.source_plane_offset if pull else workspace.expert_plane_offset,
+            combine_plane_offset=workspace.routed_plane_offset, generation=generation,
+            dispatch_mode="pull" if pull else "push", wait_budget_ns=self._wait_budget_ns,
+            copy_stream=self._copy_stream(device))
+
+    def _launch(self, route: PreparedRoute, transport: ops.MoeTransport, **fields) -> ops.MegaMoeLaunch:
+        off = route.offsets
+        return ops.MegaMoeLaunch(
+            transport=transport, intermediate_size=self.intermediate_size, top_k=self.top_k,
+            routed_rows=route.routed_rows, received_rows=route.received_rows, weight_layout=self._layout or "EIO",
+            fuse_dispatch=self._fuse_dispatch, status=self._status, expert_of_row=route.expert_of_row,
+            recv_segment_start=off["recv_segment_start"], mapping=route.mapping, **self._swiglu_options(), **fields)
+
     def _run_forward(self, hidden, probs, w1, w2, route: PreparedRoute):
+        """One call of the forward operator (reference: ops.mega_moe, torch/ops.py:554-649, issued by
+        backends/bf16/autograd.py:576-679): dispatch, GEMM1 + SwiGLU, GEMM2, combine, and the Top-K sum."""
         workspace = self._workspace
         device = hidden.device
-        eio = self._layout == "EIO"
-        b_major = kernels.HMC_MAJOR_MN if eio else kernels.HMC_MAJOR_K
         received, routed_rows = route.received_rows, route.routed_rows
         inter, hid = self.intermediate_size, self.hidden_size
         bf16 = dict(dtype=torch.bfloat16, device=device)
         before_fc2 = self._numerics.apply_probs_before_fc2
+        ep1, pull = self.ep_size == 1, self._pull
         off = route.offsets
-        pull = self._pull
-        generation = workspace.begin_call() if self.ep_size > 1 else 0
-        if self.ep_size == 1 and not before_fc2:
-            # One rank owns every expert: the owner's order is the source's expert-major order, so the
-            # dispatch is a local gather with nothing to wait for (the reference short-circuits
-            # peer == self to a local copy the same way, rma.h:205-208).
-            expert_buffer = torch.empty(max(received, 1), hid, **bf16)
-            expert_values = None
-            if routed_rows > 0:
-                kernels.moe_gather_rows(hidden, route.source_of_row, self.top_k, expert_buffer[:routed_rows])
-            peer_routed = peer_ctrl = None
-        elif pull:
-            sorted_probs = probs.reshape(-1).index_select(0, route.source_of_row.long()) if before_fc2 else None
-            expert_buffer, expert_values = self._pull_rows(
-                workspace, route, generation,
-                lambda rows_out: kernels.moe_gather_rows(hidden, route.source_of_row, self.top_k, rows_out),
-                values=sorted_probs)
-            _, peer_routed, peer_ctrl = self._peer_tables(workspace, expert_buffer)
-        else:
-            if self.ep_size == 1:
-                generation = workspace.begin_call()
-                expert_buffer, expert_values, plane_offset = self._local_rows(max(received, 1), device)
-                capacity = expert_buffer.shape[0]
-            else:
-                expert_buffer, expert_values = workspace.expert_buffer, workspace.expert_values
-                capacity, plane_offset = workspace.capacity_rows, workspace.expert_plane_offset
-            peer_expert, peer_routed, peer_ctrl = self._peer_tables(workspace, expert_buffer)
-            travelling = dict(row_values=probs.reshape(-1), value_index=route.source_of_row,
-                              value_plane_offset=plane_offset) if before_fc2 else {}
-            kernels.ep_dispatch(hidden, route.source_of_row, route.expert_of_row, off["dispatch_src_off"],
-                                off["dispatch_target_off"], rows=routed_rows, top_k=self.top_k, ep=self.ep_size,
-                                local_experts=self.local_experts, capacity_rows=capacity, peer_buffers=peer_expert,
-                                peer_ctrl=peer_ctrl, local_ctrl=workspace.ctrl, generation=generation,
-                                status=self._status, budget_ns=self._wait_budget_ns, **travelling)
         rows = max(received, 1)
+        # One rank owns every expert and nothing travels with the rows: the dispatch is a local gather with
+        # nothing to wait for (the reference short-circuits peer == self the same way, rma.h:205-208).
+        local_gather = ep1 and not before_fc2
+        generation = 0 if local_gather else workspace.next_generation()
+        row_probs = None
+        if ep1:
+            if before_fc2:
+                dispatch_target, row_probs, plane = self._local_rows(rows, device)
+            else:
+                dispatch_target, plane = torch.empty(rows, hid, **bf16), 0
+            transport = self._transport(workspace, generation, device, dispatch_target, plane)
+        else:
+            transport = self._transport(workspace, generation, device)
+            if pull:
+                # owners fetch into a plain local tensor of exactly the received size
+                dispatch_target = torch.empty(rows, hid, **bf16)
+                row_probs = torch.empty(rows, dtype=torch.float32, device=device) if before_fc2 else None
+            else:
+                dispatch_target = workspace.expert_buffer
+                row_probs = workspace.expert_values if before_fc2 else None
         up_proj = torch.empty(rows, 2 * inter, **bf16)
         activation = torch.empty(rows, inter, **bf16)
-        down_proj = torch.empty(rows, hid, **bf16) if self.ep_size == 1 else None
-        x_recv = expert_buffer[:rows]
-        row_probs = expert_values[:rows] if before_fc2 else None
-        # pulled / locally gathered rows are complete in stream order and live in a tensor of their own
-        local_gather = self.ep_size == 1 and not before_fc2
-        arrival = None if (pull or local_gather) else \
-            workspace.ctrl[_lib.HMC_CTRL_ARRIVAL:_lib.HMC_CTRL_ARRIVAL + self.local_experts]
-        saved_received = torch.empty_like(x_recv) if (self.ep_size > 1 and not pull) else x_recv
-        if received > 0:
-            kernels.grouped_gemm(x_recv, w1, up_proj, off["group_list"], mode=kernels.HMC_GEMM_RAGGED_M,
-                                 b_major=b_major, epilogue=kernels.HMC_EPI_SWIGLU, aux=activation,
-                                 ready_counters=arrival, ready_budget_ns=self._wait_budget_ns, status=self._status,
-                                 row_probs=row_probs, **self._swiglu_options())
-            if self.ep_size > 1 and not pull:
-                # GEMM1 has waited for every expert's rows: the owned copy of the received rows (the
-                # symmetric buffer is rewritten by the next call) runs on a side stream beside GEMM2.
-                side = self._copy_stream(device)
-                side.wait_stream(torch.cuda.current_stream(device))
-                with torch.cuda.stream(side):
-                    saved_received.copy_(x_recv)
-            kernels.grouped_gemm(activation, w2, None if self.ep_size > 1 else down_proj, off["group_list"],
-                                 mode=kernels.HMC_GEMM_RAGGED_M, b_major=b_major, status=self._status,
-                                 combine=self._fused_combine(workspace, off, peer_routed, peer_ctrl))
-        if self.ep_size == 1:
-            routed_out = down_proj
-            saved_received = x_recv
-            saved_probs = row_probs
-        else:
-            # The result rows left the GEMM2 epilogue for their sources; wait for this rank's own.
-            kernels.ep_wait(workspace.ctrl[_lib.HMC_CTRL_COMBINE:],
-                            routed_rows * kernels.grouped_gemm_combine_units(hid), status=self._status,
-                            budget_ns=self._wait_budget_ns)
-            # Owned copies: the symmetric buffers are rewritten by the next call on any rank
-            # (reference: autograd.py:655-663 saves a dispatch copy and clones the combine output).
-            # They are made on a side stream, beside the K-sum below; this stream joins it before
-            # the call returns.
-            live_routed = workspace.routed_buffer[:max(routed_rows, 1)]
-            routed_out = torch.empty_like(live_routed)
-            saved_probs = (row_probs if pull else torch.empty_like(row_probs)) if before_fc2 else None
-            main = torch.cuda.current_stream(device)
-            side = self._copy_stream(device)
-            side.wait_stream(main)
-            with torch.cuda.stream(side):
-                routed_out.copy_(live_routed)
-                if before_fc2 and not pull:
-                    saved_probs.copy_(row_probs)
+        down_proj = torch.empty(rows, hid, **bf16) if ep1 else None
         out = torch.empty(hidden.shape[0], hid, **bf16)
-        live = routed_out if self.ep_size == 1 else live_routed
+        # Owned copies: the peer-mapped buffers are rewritten by the next call on any rank
+        # (reference: autograd.py:655-663 saves a dispatch copy and clones the combine output).
+        push_ep = not ep1 and not pull
+        saved_received = torch.empty(rows, hid, **bf16) if push_ep else dispatch_target[:rows]
+        routed_out = down_proj if ep1 else torch.empty(max(routed_rows, 1), hid, **bf16)
+        saved_probs = None
         if before_fc2:
-            # The rows are already weighted: the Top-K rows of a token are summed as they are
-            # (reference: _restore_unweighted_output, backends/bf16/autograd.py:133-135).
-            # in ascending expert order with a BF16 rounding per addition, like the golden's index_add
-            kernels.moe_unpermute(live, route.mapping, None, hidden.shape[0], self.top_k, out, status=self._status)
+            saved_probs = torch.empty(rows, dtype=torch.float32, device=device) if push_ep else row_probs[:rows]
+        launch = self._launch(
+            route, transport, dispatch_src_index=route.source_of_row,
+            route_probs=probs.reshape(-1) if before_fc2 else None, row_probs=row_probs,
+            saved_dispatch=saved_received if push_ep else None, saved_combine=None if ep1 else routed_out,
+            saved_row_probs=saved_probs if (before_fc2 and push_ep) else None,
+            topk_probs=None if before_fc2 else probs, output=out)
+        ops.mega_moe(dispatch_target, off["dispatch_target_off"], hidden, off["dispatch_src_off"], off["dispatch_size"],
+                     w1, off["group_list"], up_proj, activation, w2, off["group_list"], down_proj,
+                     None if ep1 else workspace.routed_buffer, off["combine_target_off"], off["combine_src_off"],
+                     off["combine_size"], None, None, None, None, None, workspace.ctrl, self._rank, self.ep_size,
+                     self.num_experts, hid, hidden.shape[0], launch=launch)
+        if before_fc2:
             saved_last = saved_probs if saved_probs is not None else torch.empty(0, device=device)
         else:
-            kernels.moe_unpermute(live, route.mapping, probs, hidden.shape[0], self.top_k, out,
-                                  status=self._status)
             saved_last = routed_out
-        if self.ep_size > 1:
-            torch.cuda.current_stream(device).wait_stream(self._copy_stream(device))
         return out, (saved_received, up_proj, activation, saved_last)
 
     def _run_backward(self, grad_output, hidden, probs, w1, w2, received_x, up_proj, activation, saved_last,
                       route: PreparedRoute, need_weight_grads):
-        """`saved_last` is the routed forward output (probabilities after FC2, needed for their
-        gradient) or the received per-row probabilities (probabilities before FC2)."""
+        """One call of the backward operator (reference: ops.mega_moe_grad, torch/ops.py:652-737, issued by
+        backends/bf16/autograd.py:681-763). `saved_last` is the routed forward output (probabilities after
+        FC2, needed for their gradient) or the received per-row probabilities (probabilities before FC2)."""
         workspace = self._workspace
         device = hidden.device
-        eio = self._layout == "EIO"
         received, routed_rows = route.received_rows, route.routed_rows
         inter, hid = self.intermediate_size, self.hidden_size
         bf16 = dict(dtype=torch.bfloat16, device=device)
@@ -743,122 +689,50 @@ class MegaMoeExperts(torch.nn.Module):
         tokens = hidden.shape[0]
         rows = max(received, 1)
         before_fc2 = self._numerics.apply_probs_before_fc2
-        grad_probs = None
-        generation = peer_routed = peer_ctrl = None
-        if before_fc2:
-            # dYe rows are plain copies of the token gradients (reference: _stage_backward_source,
-            # backends/bf16/autograd.py:138-150); the gather is fused into the dispatch.
-            row_probs = saved_last
-            generation = workspace.begin_call()
-            if self._pull:
-                dy_recv, _ = self._pull_rows(
-                    workspace, route, generation,
-                    lambda rows_out: kernels.moe_gather_rows(grad_output, route.source_of_row, self.top_k, rows_out))
-                _, peer_routed, peer_ctrl = self._peer_tables(workspace, dy_recv)
-                arrival = None
-            else:
-                if self.ep_size == 1:
-                    expert_buffer, _, _ = self._local_rows(rows, device)
-                    capacity = rows
-                else:
-                    expert_buffer, capacity = workspace.expert_buffer, workspace.capacity_rows
-                peer_expert, peer_routed, peer_ctrl = self._peer_tables(workspace, expert_buffer)
-                kernels.ep_dispatch(grad_output, route.source_of_row, route.expert_of_row, off["dispatch_src_off"],
-                                    off["dispatch_target_off"], rows=routed_rows, top_k=self.top_k, ep=self.ep_size,
-                                    local_experts=self.local_experts, capacity_rows=capacity,
-                                    peer_buffers=peer_expert, peer_ctrl=peer_ctrl, local_ctrl=workspace.ctrl,
-                                    generation=generation, status=self._status, budget_ns=self._wait_budget_ns)
-                dy_recv = expert_buffer[:rows]
-                arrival = workspace.ctrl[_lib.HMC_CTRL_ARRIVAL:_lib.HMC_CTRL_ARRIVAL + self.local_experts]
-            row_dot = torch.zeros(rows, dtype=torch.float32, device=device)
-        else:
-            row_probs = row_dot = None
-            grad_probs = torch.empty(tokens, self.top_k, dtype=torch.float32, device=device)
-            if self._pull:
-                # dYe is written straight into the published source buffer; the owners fetch it
-                generation = workspace.begin_call()
-                dy_recv, _ = self._pull_rows(
-                    workspace, route, generation,
-                    lambda rows_out: kernels.moe_unpermute_grad(saved_last, grad_output, route.mapping, probs,
-                                                                self.top_k, rows_out, grad_probs,
-                                                                status=self._status))
-                _, peer_routed, peer_ctrl = self._peer_tables(workspace, dy_recv)
-                arrival = None
-            else:
-                # dYe (source's expert-major order) and dProbs
-                grad_routed = torch.empty(max(routed_rows, 1), hid, **bf16)
-                kernels.moe_unpermute_grad(saved_last, grad_output, route.mapping, probs, self.top_k, grad_routed,
-                                           grad_probs, status=self._status)
-            if self._pull:
-                pass
-            elif self.ep_size == 1:
-                # One rank owns every expert: the source's expert-major order IS the owner's order
-                # (the reference short-circuits peer == self the same way, rma.h:205-208), so the
-                # rows are used in place and nothing has to arrive.
-                dy_recv = grad_routed[:rows]
-                arrival = None
-            else:
-                generation = workspace.begin_call()
-                expert_buffer = workspace.expert_buffer
-                peer_expert, peer_routed, peer_ctrl = self._peer_tables(workspace, expert_buffer)
-                kernels.ep_dispatch(grad_routed, None, route.expert_of_row, off["dispatch_src_off"],
-                                    off["dispatch_target_off"], rows=routed_rows, top_k=self.top_k, ep=self.ep_size,
-                                    local_experts=self.local_experts, capacity_rows=workspace.capacity_rows,
-                                    peer_buffers=peer_expert, peer_ctrl=peer_ctrl, local_ctrl=workspace.ctrl,
-                                    generation=generation, status=self._status, budget_ns=self._wait_budget_ns)
-                dy_recv = expert_buffer[:rows]
-                arrival = workspace.ctrl[_lib.HMC_CTRL_ARRIVAL:_lib.HMC_CTRL_ARRIVAL + self.local_experts]
-        grad_up = torch.empty(rows, 2 * inter, **bf16)
-        # With the probability gradient travelling back (before FC2) the rows return through the combine
-        # kernel, which carries the float plane; otherwise they leave from the dX GEMM's epilogue.
-        fused = None if (self.ep_size == 1 or before_fc2) else self._fused_combine(workspace, off, peer_routed, peer_ctrl)
-        grad_x_rows = torch.empty(rows, hid, **bf16) if fused is None else None
+        ep1, pull = self.ep_size == 1, self._pull
         f32_partials = self._numerics.partial_weight_grad_dtype == "float32"
         wdtype = torch.float32 if f32_partials else torch.bfloat16
-        wepi = kernels.HMC_EPI_STORE_F32 if f32_partials else kernels.HMC_EPI_STORE_BF16
         grad_w1 = torch.empty(w1.shape, dtype=wdtype, device=device) if need_weight_grads[0] else None
         grad_w2 = torch.empty(w2.shape, dtype=wdtype, device=device) if need_weight_grads[1] else None
-        # Transposed use of the weights: EIO W2 [e, I, H] is the K-major B of dA = dY . W2^T; EOI the reverse.
-        bt_major = kernels.HMC_MAJOR_K if eio else kernels.HMC_MAJOR_MN
-        if received > 0:
-            kernels.grouped_gemm(dy_recv, w2, grad_up, off["group_list"], mode=kernels.HMC_GEMM_RAGGED_M,
-                                 b_major=bt_major, epilogue=kernels.HMC_EPI_SWIGLU_GRAD, aux=up_proj,
-                                 ready_counters=arrival, ready_budget_ns=self._wait_budget_ns, status=self._status,
-                                 row_probs=row_probs, row_dot=row_dot, **self._swiglu_options())
-            kernels.grouped_gemm(grad_up, w1, grad_x_rows, off["group_list"], mode=kernels.HMC_GEMM_RAGGED_M,
-                                 b_major=bt_major, status=self._status, combine=fused)
-        if grad_w2 is not None:
-            # The arrival wait of the dA GEMM above orders this kernel after the rows have landed.
-            # With probabilities before FC2, `activation` is the weighted input FC2 actually saw.
-            a_op, b_op = (activation, dy_recv) if eio else (dy_recv, activation)
-            kernels.grouped_gemm(a_op, b_op, grad_w2, off["group_list"], mode=kernels.HMC_GEMM_RAGGED_K, epilogue=wepi,
-                                 status=self._status)
-        if grad_w1 is not None:
-            a_op, b_op = (received_x, grad_up) if eio else (grad_up, received_x)
-            kernels.grouped_gemm(a_op, b_op, grad_w1, off["group_list"], mode=kernels.HMC_GEMM_RAGGED_K, epilogue=wepi,
-                                 status=self._status)
-        if self.ep_size == 1:
-            returned, returned_dot = grad_x_rows, row_dot
-        elif fused is not None:
-            kernels.ep_wait(workspace.ctrl[_lib.HMC_CTRL_COMBINE:],
-                            routed_rows * kernels.grouped_gemm_combine_units(hid), status=self._status,
-                            budget_ns=self._wait_budget_ns)
-            returned, returned_dot = workspace.routed_buffer, None
-        else:
-            kernels.ep_combine(grad_x_rows, off["recv_segment_start"], off["combine_target_off"], rows=received,
-                               ep=self.ep_size, local_experts=self.local_experts,
-                               target_rows_limit=workspace.routed_rows, peer_buffers=peer_routed,
-                               peer_ctrl=peer_ctrl, local_ctrl=workspace.ctrl, generation=generation,
-                               status=self._status, budget_ns=self._wait_budget_ns, result_values=row_dot,
-                               value_plane_offset=workspace.routed_plane_offset)
-            kernels.ep_wait(workspace.ctrl[_lib.HMC_CTRL_COMBINE:], routed_rows, status=self._status, budget_ns=self._wait_budget_ns)
-            returned, returned_dot = workspace.routed_buffer, workspace.routed_values
+        grad_up = torch.empty(rows, 2 * inter, **bf16)
         grad_hidden = torch.empty(tokens, hid, **bf16)
-        kernels.moe_token_permute_grad(returned, route.mapping, tokens, self.top_k, grad_hidden, status=self._status)
+        grad_probs = torch.empty(tokens, self.top_k, dtype=torch.float32, device=device)
+        # With the probability gradient travelling back (before FC2) the rows return through the combine
+        # kernel, which carries the float plane; otherwise they leave from the dX GEMM's epilogue.
+        fused_combine = not ep1 and not before_fc2
+        grad_x_rows = None if fused_combine else torch.empty(rows, hid, **bf16)
+        fields = dict(weight_grad_f32=f32_partials, grad_probs=grad_probs, grad_hidden=grad_hidden)
+        plane = 0
         if before_fc2:
-            # the probability gradient of route (t, k) sits at that route's row of the source order
-            # (reference: backends/bf16/autograd.py:725-730)
-            grad_probs = returned_dot.index_select(0, route.mapping.long()).view(tokens, self.top_k)
+            # dY rows are plain copies of the token gradients (reference: _stage_backward_source,
+            # backends/bf16/autograd.py:138-150); the gather is fused into the dispatch.
+            generation = workspace.next_generation()
+            dy_source = grad_output
+            fields.update(dispatch_src_index=route.source_of_row, row_probs=saved_last,
+                          row_dot=torch.empty(rows, dtype=torch.float32, device=device))
+            if ep1:
+                dispatch_target, _, plane = self._local_rows(rows, device)
+            else:
+                dispatch_target = torch.empty(rows, hid, **bf16) if pull else workspace.expert_buffer
+        else:
+            fields.update(grad_output=grad_output, saved_combine=saved_last, topk_probs=probs)
+            if ep1:
+                # the source's expert-major order IS the owner's order: the dY rows are used in place
+                generation = 0
+                dy_source = dispatch_target = torch.empty(max(routed_rows, 1), hid, **bf16)
+            else:
+                generation = workspace.next_generation()
+                # pull: dY is written straight into the published source buffer; the owners fetch it
+                dy_source = workspace.source_buffer if pull else torch.empty(max(routed_rows, 1), hid, **bf16)
+                dispatch_target = torch.empty(rows, hid, **bf16) if pull else workspace.expert_buffer
+        transport = self._transport(workspace, generation, device, dispatch_target if ep1 else None, plane)
+        launch = self._launch(route, transport, **fields)
+        ops.mega_moe_grad(dispatch_target, off["dispatch_target_off"], dy_source, off["dispatch_src_off"],
+                          off["dispatch_size"], activation, grad_w2, w2, None, up_proj, grad_up, w1, grad_x_rows,
+                          None if ep1 else workspace.routed_buffer, off["combine_target_off"], off["combine_src_off"],
+                          off["combine_size"], received_x, grad_w1, off["group_list"], None, None, None, None, None,
+                          None, None, None, workspace.ctrl, self._rank, self.ep_size, self.num_experts, hid, tokens,
+                          launch=launch)
         if grad_w1 is not None and grad_w1.dtype != w1.dtype:
             grad_w1 = grad_w1.to(w1.dtype)
         if grad_w2 is not None and grad_w2.dtype != w2.dtype:
@@ -886,154 +760,105 @@ class MegaMoeExperts(torch.nn.Module):
             self._scale_atoms[key] = cached = (weakref.ref(scale), version, atoms)
         return cached[2]
 
-    def _mx_exchange(self, source, source_of_row, route, generation_hint=None):
-        """Dispatch rows to their owners and wait until every local expert's rows have landed."""
-        workspace = self._workspace
-        device = source.device
-        received, routed_rows = route.received_rows, route.routed_rows
-        if self.ep_size == 1 and source_of_row is None:
-            return source[:max(received, 1)], None, None, None  # already in the owner's order
-        if self.ep_size == 1:
-            # one rank owns every expert: the dispatch is a local gather into the owner's (= the source's) order
-            rows_in = torch.empty(max(received, 1), self.hidden_size, dtype=torch.bfloat16, device=device)
-            if routed_rows > 0:
-                kernels.moe_gather_rows(source, source_of_row, self.top_k, rows_in[:routed_rows])
-            return rows_in, None, None, None
-        generation = workspace.begin_call()
-        if self._pull:
-            if source_of_row is not None:
-                fill = lambda rows_out: kernels.moe_gather_rows(source, source_of_row, self.top_k, rows_out)  # noqa: E731
-            else:
-                fill = lambda rows_out: rows_out.copy_(source[:rows_out.shape[0]])  # noqa: E731
-            rows_in, _ = self._pull_rows(workspace, route, generation, fill)
-            _, peer_routed, peer_ctrl = self._peer_tables(workspace, rows_in)
-            return rows_in, generation, peer_routed, peer_ctrl
-        if self.ep_size == 1:
-            expert_buffer = torch.empty(max(received, 1), self.hidden_size, dtype=torch.bfloat16, device=device)
-            capacity = expert_buffer.shape[0]
-        else:
-            expert_buffer = workspace.expert_buffer
-            capacity = workspace.capacity_rows
-        peer_expert, peer_routed, peer_ctrl = self._peer_tables(workspace, expert_buffer)
-        off = route.offsets
-        kernels.ep_dispatch(source, source_of_row, route.expert_of_row, off["dispatch_src_off"],
-                            off["dispatch_target_off"], rows=routed_rows, top_k=self.top_k, ep=self.ep_size,
-                            local_experts=self.local_experts, capacity_rows=capacity, peer_buffers=peer_expert,
-                            peer_ctrl=peer_ctrl, local_ctrl=workspace.ctrl, generation=generation,
-                            status=self._status, budget_ns=self._wait_budget_ns)
-        arrival = workspace.ctrl[_lib.HMC_CTRL_ARRIVAL:_lib.HMC_CTRL_ARRIVAL + self.local_experts]
-        kernels.ep_wait_groups(arrival, off["group_list"], status=self._status, budget_ns=self._wait_budget_ns)
-        return expert_buffer[:max(received, 1)], generation, peer_routed, peer_ctrl
+    def _mx_buffers(self, rows: int, groups: int, width: int, device, *, want_col: bool):
+        """Row- and (optionally) column-quantised planes of one activation in the padded expert-major layout."""
+        pad_blocks = kernels.mx_pad_blocks(rows, groups)
+        acts = kernels.MxActivations(rows, groups, width, device, want_row=True, want_col=want_col)
+        assert acts.pad_blocks == pad_blocks
+        return acts
 
-    def _mx_return(self, rows_tensor, route, generation, peer_routed, peer_ctrl, width=None):
-        """Combine result rows back to their sources (identity at ep_size == 1). With `rows_tensor` None
-        the rows already left from the producing GEMM's epilogue (`width` columns): only wait for this
-        rank's own rows."""
-        if self.ep_size == 1:
-            return rows_tensor
-        workspace = self._workspace
-        off = route.offsets
-        if rows_tensor is None:
-            kernels.ep_wait(workspace.ctrl[_lib.HMC_CTRL_COMBINE:],
-                            route.routed_rows * kernels.mx_gemm_combine_units(width), status=self._status,
-                            budget_ns=self._wait_budget_ns)
-            return workspace.routed_buffer
-        kernels.ep_combine(rows_tensor, off["recv_segment_start"], off["combine_target_off"], rows=route.received_rows,
-                           ep=self.ep_size, local_experts=self.local_experts,
-                           target_rows_limit=workspace.routed_rows, peer_buffers=peer_routed, peer_ctrl=peer_ctrl,
-                           local_ctrl=workspace.ctrl, generation=generation, status=self._status, budget_ns=self._wait_budget_ns)
-        kernels.ep_wait(workspace.ctrl[_lib.HMC_CTRL_COMBINE:], route.routed_rows, status=self._status, budget_ns=self._wait_budget_ns)
-        return workspace.routed_buffer
+    def _mx_transport(self, workspace, route: PreparedRoute, device, local_buffer):
+        ep1 = self.ep_size == 1
+        generation = 0 if ep1 else workspace.next_generation()
+        return self._transport(workspace, generation, device, local_buffer if ep1 else None)
 
     def _run_forward_mx(self, hidden, probs, root1, root2, route: PreparedRoute):
-        """dispatch -> quant X -> GEMM1 -> SwiGLU + quant -> GEMM2 -> combine -> K-sum
-        (reference graph: backends/mxfp8/graph.py:140-146)."""
+        """One call of the MXFP8 forward operator: dispatch -> quant X -> GEMM1 -> SwiGLU + quant -> GEMM2 ->
+        combine -> K-sum (reference: ops.mega_moe_mxfp8 issued by backends/mxfp8/execution.py:64-118, graph
+        backends/mxfp8/graph.py:140-146)."""
+        workspace = self._workspace
         device = hidden.device
         inter, hid, local = self.intermediate_size, self.hidden_size, self.local_experts
-        received = route.received_rows
+        received, routed_rows = route.received_rows, route.routed_rows
         rows = max(received, 1)
         bf16 = dict(dtype=torch.bfloat16, device=device)
-        ends = route.offsets["group_list"]
+        off = route.offsets
         training = self._backward_expected
-        x_recv, generation, peer_routed, peer_ctrl = self._mx_exchange(hidden, route.source_of_row, route)
+        ep1, pull = self.ep_size == 1, self._pull
+        dispatch_buffer = workspace.expert_buffer if (not ep1 and not pull) else torch.empty(rows, hid, **bf16)
+        transport = self._mx_transport(workspace, route, device, dispatch_buffer)
         up_proj = torch.empty(rows, 2 * inter, **bf16)
-        fused = self._fused_combine(self._workspace, route.offsets, peer_routed, peer_ctrl)
-        down_proj = torch.empty(rows, hid, **bf16) if fused is None else None
-        x_q = act_q = None
-        if received > 0:
-            x_q = kernels.mx_quant(x_recv[:received], ends, hid, want_row=True, want_col=training)
-            kernels.mx_gemm(x_q.row_data, x_q.row_scale, root1.col_data, self._atoms(root1, "col", (local, hid, 2 * inter)),
-                            up_proj, ends, mode=kernels.HMC_GEMM_RAGGED_M, rows=received, pad_blocks=x_q.pad_blocks,
-                            n=2 * inter, k=hid, b_major=kernels.HMC_MAJOR_MN, status=self._status)
-            act_q = kernels.mx_quant(up_proj[:received], ends, inter, kind=kernels.HMC_MXQ_SWIGLU, want_row=True,
-                                     want_col=training)
-            kernels.mx_gemm(act_q.row_data, act_q.row_scale, root2.col_data, self._atoms(root2, "col", (local, inter, hid)),
-                            down_proj, ends, mode=kernels.HMC_GEMM_RAGGED_M, rows=received, pad_blocks=act_q.pad_blocks,
-                            n=hid, k=inter, b_major=kernels.HMC_MAJOR_MN, status=self._status, combine=fused)
-        returned = self._mx_return(down_proj, route, generation, peer_routed, peer_ctrl, width=hid)
-        routed_out = returned if self.ep_size == 1 else returned[:max(route.routed_rows, 1)].clone()
+        down_proj = torch.empty(rows, hid, **bf16) if ep1 else None
+        x_q = self._mx_buffers(received, local, hid, device, want_col=training)
+        act_q = self._mx_buffers(received, local, inter, device, want_col=training)
+        routed_out = down_proj if ep1 else torch.empty(max(routed_rows, 1), hid, **bf16)
         out = torch.empty(hidden.shape[0], hid, **bf16)
-        kernels.moe_unpermute(routed_out, route.mapping, probs, hidden.shape[0], self.top_k, out, status=self._status)
+        launch = self._launch(route, transport, dispatch_src_index=route.source_of_row, pad_blocks=x_q.pad_blocks,
+                              saved_combine=None if ep1 else routed_out, topk_probs=probs, output=out)
+        buffers = [
+            dispatch_buffer, off["dispatch_target_off"], hidden, off["dispatch_src_off"], off["dispatch_size"],
+            root1.col_data, off["group_list"], up_proj, act_q.row_data, root2.col_data, off["group_list"], down_proj,
+            None if ep1 else workspace.routed_buffer, off["combine_target_off"], off["combine_src_off"],
+            off["combine_size"], x_q.row_data, x_q.row_scale, x_q.col_data, x_q.col_scale, act_q.row_scale,
+            act_q.col_data, act_q.col_scale, self._atoms(root1, "col", (local, hid, 2 * inter)),
+            self._atoms(root2, "col", (local, inter, hid)),
+        ]
+        ops.mega_moe_mxfp8(buffers, None, workspace.ctrl, None, None, rank_id=self._rank, ep=self.ep_size,
+                           expert_num=self.num_experts, hidden_size=hid, seq_size=hidden.shape[0], launch=launch)
         empty = torch.empty(0, dtype=torch.uint8, device=device)
+        keep = training and received > 0
         saved = (up_proj, routed_out,
-                 x_q.col_data if x_q is not None and training else empty,
-                 x_q.col_scale if x_q is not None and training else empty,
-                 act_q.col_data if act_q is not None and training else empty,
-                 act_q.col_scale if act_q is not None and training else empty)
+                 x_q.col_data if keep else empty, x_q.col_scale if keep else empty,
+                 act_q.col_data if keep else empty, act_q.col_scale if keep else empty)
         return out, saved
 
     def _run_backward_mx(self, grad_output, hidden, probs, root1, root2, up_proj, routed_out, x_col, x_col_scale,
                          act_col, act_col_scale, route: PreparedRoute, need_weight_grads):
-        """dispatch dY -> quant -> dA -> SwiGLU-grad + quant -> dX, dW2, dW1 -> combine
-        (reference graph: backends/mxfp8/graph.py:147-154)."""
+        """One call of the MXFP8 backward operator: dY rows -> dispatch -> quant -> dA -> SwiGLU-grad + quant ->
+        dX, dW2, dW1 -> combine -> K-sum (reference: ops.mega_moe_mxfp8_grad issued by
+        backends/mxfp8/execution.py:120-164, graph backends/mxfp8/graph.py:147-154)."""
+        workspace = self._workspace
         device = hidden.device
         inter, hid, local = self.intermediate_size, self.hidden_size, self.local_experts
         received, routed_rows = route.received_rows, route.routed_rows
         rows = max(received, 1)
         tokens = hidden.shape[0]
         bf16 = dict(dtype=torch.bfloat16, device=device)
-        ends = route.offsets["group_list"]
+        off = route.offsets
+        ep1, pull = self.ep_size == 1, self._pull
         grad_routed = torch.empty(max(routed_rows, 1), hid, **bf16)
         grad_probs = torch.empty(tokens, self.top_k, dtype=torch.float32, device=device)
-        kernels.moe_unpermute_grad(routed_out, grad_output, route.mapping, probs, self.top_k, grad_routed, grad_probs,
-                                   status=self._status)
-        dy_recv, generation, peer_routed, peer_ctrl = self._mx_exchange(grad_routed, None, route)
+        grad_hidden = torch.empty(tokens, hid, **bf16)
         f32_partials = self._numerics.partial_weight_grad_dtype == "float32"
         wdtype = torch.float32 if f32_partials else torch.bfloat16
-        wepi = kernels.HMC_EPI_STORE_F32 if f32_partials else kernels.HMC_EPI_STORE_BF16
         shape1, shape2 = (local, hid, 2 * inter), (local, inter, hid)
         grad_w1 = torch.empty(shape1, dtype=wdtype, device=device) if need_weight_grads[0] else None
         grad_w2 = torch.empty(shape2, dtype=wdtype, device=device) if need_weight_grads[1] else None
-        fused = self._fused_combine(self._workspace, route.offsets, peer_routed, peer_ctrl)
-        grad_x_rows = torch.empty(rows, hid, **bf16) if fused is None else None
-        if received > 0:
-            want_col = grad_w1 is not None or grad_w2 is not None
-            dy_q = kernels.mx_quant(dy_recv[:received], ends, hid, want_row=True, want_col=want_col)
-            grad_act = torch.empty(rows, inter, **bf16)
-            # W2 [e, I, H] row-quantised (blocks along H) is the K-major B of dA = dY . W2^T
-            kernels.mx_gemm(dy_q.row_data, dy_q.row_scale, root2.row_data, self._atoms(root2, "row", shape2), grad_act,
-                            ends, mode=kernels.HMC_GEMM_RAGGED_M, rows=received, pad_blocks=dy_q.pad_blocks, n=inter,
-                            k=hid, b_major=kernels.HMC_MAJOR_K, status=self._status)
-            du_q = kernels.mx_quant(grad_act[:received], ends, 2 * inter, kind=kernels.HMC_MXQ_SWIGLU_GRAD,
-                                    aux=up_proj[:received], want_row=True, want_col=want_col)
-            kernels.mx_gemm(du_q.row_data, du_q.row_scale, root1.row_data, self._atoms(root1, "row", shape1), grad_x_rows,
-                            ends, mode=kernels.HMC_GEMM_RAGGED_M, rows=received, pad_blocks=du_q.pad_blocks, n=hid,
-                            k=2 * inter, b_major=kernels.HMC_MAJOR_K, status=self._status, combine=fused)
-            if grad_w2 is not None:
-                kernels.mx_gemm(act_col, act_col_scale, dy_q.col_data, dy_q.col_scale, grad_w2, ends,
-                                mode=kernels.HMC_GEMM_RAGGED_K, rows=received, pad_blocks=dy_q.pad_blocks, m=inter, n=hid,
-                                epilogue=wepi, status=self._status)
-            if grad_w1 is not None:
-                kernels.mx_gemm(x_col, x_col_scale, du_q.col_data, du_q.col_scale, grad_w1, ends,
-                                mode=kernels.HMC_GEMM_RAGGED_K, rows=received, pad_blocks=du_q.pad_blocks, m=hid,
-                                n=2 * inter, epilogue=wepi, status=self._status)
+        want_col = grad_w1 is not None or grad_w2 is not None
+        if ep1:
+            dispatch = grad_routed  # already in the owner's (= the source's) order
         else:
-            for grad in (grad_w1, grad_w2):
-                if grad is not None:
-                    grad.zero_()
-        returned = self._mx_return(grad_x_rows, route, generation, peer_routed, peer_ctrl, width=hid)
-        grad_hidden = torch.empty(tokens, hid, **bf16)
-        kernels.moe_token_permute_grad(returned, route.mapping, tokens, self.top_k, grad_hidden, status=self._status)
+            dispatch = torch.empty(rows, hid, **bf16) if pull else workspace.expert_buffer
+        transport = self._mx_transport(workspace, route, device, dispatch)
+        dy_q = self._mx_buffers(received, local, hid, device, want_col=want_col)
+        du_q = self._mx_buffers(received, local, 2 * inter, device, want_col=want_col)
+        grad_act = torch.empty(rows, inter, **bf16)
+        grad_x_rows = torch.empty(rows, hid, **bf16) if ep1 else None
+        launch = self._launch(route, transport, pad_blocks=dy_q.pad_blocks, weight_grad_f32=f32_partials,
+                              grad_output=grad_output, saved_combine=routed_out, topk_probs=probs, grad_probs=grad_probs,
+                              grad_hidden=grad_hidden)
+        have_saved = received > 0
+        buffers = [
+            dispatch, off["dispatch_target_off"], grad_routed, off["dispatch_src_off"], off["dispatch_size"],
+            act_col if have_saved else None, grad_w2, root2.row_data, grad_act, up_proj, du_q.row_data, root1.row_data,
+            grad_x_rows, None if ep1 else workspace.routed_buffer, off["combine_target_off"], off["combine_src_off"],
+            off["combine_size"], x_col if have_saved else None, grad_w1, off["group_list"], dy_q.row_data, dy_q.row_scale,
+            dy_q.col_data, dy_q.col_scale, act_col_scale if have_saved else None, self._atoms(root2, "row", shape2),
+            du_q.row_scale, du_q.col_data, du_q.col_scale, self._atoms(root1, "row", shape1),
+            x_col_scale if have_saved else None,
+        ]
+        ops.mega_moe_mxfp8_grad(buffers, None, workspace.ctrl, None, None, rank_id=self._rank, ep=self.ep_size,
+                                expert_num=self.num_experts, hidden_size=hid, seq_size=tokens, launch=launch)
         if grad_w1 is not None:
             grad_w1 = grad_w1.to(root1.dtype).reshape(root1.shape)
         if grad_w2 is not None:

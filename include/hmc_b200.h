@@ -87,6 +87,8 @@ typedef struct hmc_gemm_combine {
   int64_t target_rows_limit;
 } hmc_gemm_combine;
 
+struct hmc_ep_dispatch_args; /* defined with the expert-parallel transport below */
+
 typedef struct hmc_grouped_gemm_args {
   int32_t mode;
   int32_t a_major; /* RAGGED_M: HMC_MAJOR_K. RAGGED_K: HMC_MAJOR_MN */
@@ -121,6 +123,15 @@ typedef struct hmc_grouped_gemm_args {
   uint64_t pipe_budget_ns;         /* bound of the kernel's internal barrier waits, 0 = 4 s. With ready_counters the
                                       consumer-side waits add ready_budget_ns to it: while the producer is allowed to
                                       wait for late rows, the warps behind it must not give up first */
+  /* Optional, RAGGED_M with ready_counters: this launch also SENDS this rank's rows. Extra warps of every CTA
+   * execute the push dispatch described here (peer stores + arrival counters, exactly what hmc_ep_dispatch
+   * does) while the tile producer waits per expert for the rows this rank receives, so the NVLink transfer
+   * overlaps the first tiles instead of preceding them: the reference runs its dispatch PUT tasks and GMM1
+   * inside one launch the same way (ops/hyper_mega_moe/op_kernel/worker_kernel.cpp:301-366,
+   * tasks/gmm.py:154-160). `a` must be this rank's own receive buffer, ready_counters its arrival counters,
+   * dispatch->local_experts == groups and dispatch->hidden == k. Every CTA of the launch is resident at once
+   * (one per SM), so a CTA waiting for rows never keeps another CTA's dispatch warps from running. */
+  const struct hmc_ep_dispatch_args* dispatch;
 } hmc_grouped_gemm_args;
 
 int hmc_grouped_gemm(const hmc_grouped_gemm_args* args, void* stream);
@@ -488,6 +499,10 @@ typedef struct hmc_ep_dispatch_args {
   const float* row_values;
   const int32_t* value_index;
   int64_t value_plane_offset;    /* bytes; at least capacity_rows * hidden * 2 */
+  int64_t rank;                  /* this rank (0 <= rank < ep). Used when the dispatch rides inside a grouped GEMM
+                                    (hmc_grouped_gemm_args.dispatch): rows are then sent in rank-rotated order,
+                                    those owned by rank + 1 first, this rank's own last
+                                    (hyper_multicore/scheduler/scheduler.py:27-53) */
 } hmc_ep_dispatch_args;
 
 typedef struct hmc_ep_combine_args {
@@ -581,6 +596,271 @@ int hmc_ep_wait(const int32_t* counter, int32_t expected, uint64_t budget_ns, in
  * kernel without its own arrival gating consumes dispatched rows, e.g. the MX quantiser). */
 int hmc_ep_wait_groups(const int32_t* counters, const int64_t* group_ends, int64_t groups, uint64_t budget_ns,
                        int32_t* status, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * MegaMoE operators: one call per direction, every buffer allocated by the caller.
+ * hmc_mega_moe             replaces torch.ops.hyper_multicore.mega_moe
+ *                          (hyper_multicore/torch/csrc/registration.cpp:30-60, wrapper torch/ops.py:554-649)
+ * hmc_mega_moe_grad        replaces mega_moe_grad (registration.cpp:70-107, torch/ops.py:652-737)
+ * hmc_mega_moe_mxfp8(_grad) replace mega_moe_mxfp8 / mega_moe_mxfp8_grad
+ *                          (hyper_multicore/torch/csrc/mega_moe_mxfp8.cpp:36-42; buffer order of
+ *                          hyper_multicore/modules/mega_moe/backends/mxfp8/execution.py:88-96, 147-155)
+ * Each struct lists the reference op's tensors first, under the reference's names and in its order
+ * (offsets are in ROWS here, the reference multiplies them by the hidden size), then the fields that
+ * stand for what the reference passes as tiling tensors, workspaces and RuntimeConfig blobs (this
+ * implementation schedules tiles on the device and needs no host task graph).
+ *
+ * One call enqueues the whole operator on `stream`: per-call counters cleared and "ready"
+ * published, dispatch (push: peer stores issued by extra warps of the first GEMM, so the transfer
+ * overlaps its tiles; pull: published source buffer + owner-side fetch; one rank: a local gather),
+ * the grouped GEMMs with their fused SwiGLU / SwiGLU-grad epilogues, combine (result rows leave the
+ * epilogue of the last row-ragged GEMM for their source ranks), the bounded wait for this rank's own
+ * rows, and the owned copies of buffers the next call rewrites. Optional prologue / epilogue fields
+ * fold the token-order steps of the reference's autograd function into the same call
+ * (restore_topk_output, mega_moe_unpermute_grad_out, moe_token_permute_grad).
+ * The first call on a device creates two CUDA events there (used to order the copy stream); make it
+ * outside stream capture.
+ * ------------------------------------------------------------------------------------------ */
+#define HMC_MOE_LAYOUT_EIO 0 /* W1 [e, H, 2I], W2 [e, I, H] */
+#define HMC_MOE_LAYOUT_EOI 1 /* W1 [e, 2I, H], W2 [e, H, I] */
+#define HMC_MOE_DISPATCH_PUSH 0
+#define HMC_MOE_DISPATCH_PULL 1
+
+/* Transport endpoints of one expert-parallel group member (the reference's symmetric workspace,
+ * hyper_multicore/modules/mega_moe/workspace.py:48-75, as peer-mapped pointers). */
+typedef struct hmc_moe_transport {
+  int64_t ep;
+  int64_t rank;
+  void* const* peer_dispatch;    /* host [ep]: receive buffer of every rank (pull: its published source buffer) */
+  void* const* peer_combine;     /* host [ep]: routed buffer of every rank; NULL when ep == 1 */
+  void* const* peer_ctrl;        /* host [ep]: control block of every rank (this rank's = all_event_counters) */
+  int64_t dispatch_rows_limit;   /* rows every peer_dispatch buffer holds */
+  int64_t combine_rows_limit;    /* rows every peer_combine buffer holds */
+  int64_t dispatch_plane_offset; /* bytes from a dispatch buffer to its float-per-row plane */
+  int64_t combine_plane_offset;  /* bytes from a routed buffer to its float-per-row plane */
+  int32_t generation;            /* of this call: grows by one per operator call, the same on every rank */
+  int32_t dispatch_mode;         /* HMC_MOE_DISPATCH_* */
+  uint64_t wait_budget_ns;       /* bound of every cross-rank device wait, 0 = 10 s */
+  void* copy_stream;             /* optional second stream for the owned copies; NULL = on `stream` */
+} hmc_moe_transport;
+
+typedef struct hmc_mega_moe_args {
+  /* --- the reference op's tensors, in its order --- */
+  void* dispatch_target;              /* [>= received_rows, H] bf16: this rank's receive buffer */
+  const int64_t* dispatch_target_off; /* [experts] */
+  const void* dispatch_src;           /* expert-major rows [routed_rows, H], or the tokens [seq, H] when
+                                         dispatch_src_index is given (the permutation is then fused) */
+  const int64_t* dispatch_src_off;    /* [experts] */
+  const int32_t* dispatch_size;       /* [experts]; not read (sizes follow from the offsets) */
+  const void* up_proj_weight;
+  const int64_t* up_proj_glist;       /* [experts / ep] cumulative received rows */
+  void* up_proj_y;                    /* [rows, 2I] bf16 out */
+  void* swiglu_out;                   /* [rows, I] bf16 out */
+  const void* down_proj_weight;
+  const int64_t* down_proj_glist;     /* the same tensor as up_proj_glist */
+  void* down_proj_y;                  /* [rows, H] bf16 out; only written when ep == 1 (with ep > 1 the rows
+                                         leave the epilogue for combine_target on their source ranks) */
+  void* combine_target;               /* this rank's routed buffer [routed_rows, H]; NULL when ep == 1 */
+  const int64_t* combine_target_off;  /* [ep * experts / ep] */
+  const int64_t* combine_src_off;     /* not read (recv_segment_start carries the same rows in buffer order) */
+  const int32_t* combine_size;        /* not read */
+  int32_t* all_event_counters;        /* this rank's control block (HMC_CTRL_WORDS) */
+  int32_t* diagnostic_buffer;         /* device status words (HMC_STATUS_WORDS) or NULL */
+  int64_t rank_id;
+  int64_t ep;
+  int64_t expert_num;                 /* global */
+  int64_t hidden_size;
+  int64_t seq_size;                   /* tokens of this rank */
+  /* --- in place of tiling tensors / RuntimeConfig --- */
+  int64_t intermediate_size;
+  int64_t top_k;
+  int64_t routed_rows;                /* seq_size * top_k */
+  int64_t received_rows;              /* rows this rank's experts receive */
+  int32_t weight_layout;              /* HMC_MOE_LAYOUT_* */
+  int32_t swiglu_clamp;               /* HMC_CLAMP_* */
+  float swiglu_limit;
+  int32_t fuse_dispatch;              /* push with ep > 1: 1 = dispatch warps inside GEMM1 (default choice of the
+                                         module), 0 = the stand-alone dispatch kernel first */
+  const int32_t* dispatch_src_index;  /* [routed_rows] flat (token * top_k + slot) of each expert-major row, or NULL */
+  const int32_t* expert_of_row;       /* [routed_rows] global expert of each expert-major row */
+  const int64_t* recv_segment_start;  /* [experts / ep * ep], from hmc_route_offsets */
+  const float* route_probs;           /* [seq * top_k]: set ONLY for "probabilities before FC2"; they then travel
+                                         with the rows and weight the activation */
+  float* row_probs;                   /* before FC2: where the received per-row probabilities are (push: the float
+                                         plane of dispatch_target; pull: a caller tensor of received_rows floats) */
+  const hmc_moe_transport* transport;
+  /* owned copies of what the next call rewrites (ep > 1); each may be NULL */
+  void* saved_dispatch;               /* [received_rows, H] <- dispatch_target (push only) */
+  void* saved_combine;                /* [routed_rows, H] <- combine_target */
+  float* saved_row_probs;             /* [received_rows] <- row_probs (push, before FC2) */
+  /* optional epilogue: the weighted Top-K sum back to token order (restore_topk_output,
+   * hyper_multicore/modules/mega_moe/route.py:1029-1051) */
+  const int32_t* mapping;             /* [seq * top_k] destination row of every (token, slot) */
+  const float* topk_probs;            /* [seq * top_k]; not used with route_probs (rows are already weighted) */
+  void* output;                       /* [seq, H] bf16, or NULL to skip the epilogue */
+} hmc_mega_moe_args;
+
+typedef struct hmc_mega_moe_grad_args {
+  /* --- the reference op's tensors, in its order --- */
+  void* dispatch_target;              /* [>= received_rows, H]: received dY rows */
+  const int64_t* dispatch_target_off;
+  const void* dy;                     /* dispatch source: expert-major dY rows [routed_rows, H] (written by the
+                                         prologue when grad_output is given), or the token gradients [seq, H]
+                                         with dispatch_src_index (probabilities before FC2) */
+  const int64_t* dispatch_src_off;
+  const int32_t* dispatch_size;       /* not read */
+  const void* hidden;                 /* saved swiglu_out [rows, I] */
+  void* hidden_dw;                    /* dW2 in the layout of w2, bf16 or f32; NULL = not needed */
+  const void* w2;
+  void* act_grad_y;                   /* not written: dAct stays in the accumulator of the fused SwiGLU-grad epilogue */
+  const void* gate;                   /* saved up_proj_y [rows, 2I] */
+  void* grad_gate;                    /* dU [rows, 2I] bf16 out */
+  const void* w1;
+  void* gate_dx;                      /* dX rows [rows, H]; NULL when they leave the epilogue for grad_x (ep > 1,
+                                         probabilities after FC2) */
+  void* grad_x;                       /* this rank's routed buffer (combine target); NULL when ep == 1 */
+  const int64_t* combine_target_off;
+  const int64_t* combine_src_off;     /* not read */
+  const int32_t* combine_size;        /* not read */
+  const void* permute_out;            /* saved received X rows [rows, H] (for dW1) */
+  void* gate_dw;                      /* dW1 in the layout of w1; NULL = not needed */
+  const int64_t* group_list;
+  int32_t* all_event_counters;
+  int32_t* diagnostic_buffer;
+  int64_t rank_id;
+  int64_t ep;
+  int64_t expert_num;
+  int64_t hidden_size;
+  int64_t seq_size;
+  /* --- in place of tiling tensors / RuntimeConfig --- */
+  int64_t intermediate_size;
+  int64_t top_k;
+  int64_t routed_rows;
+  int64_t received_rows;
+  int32_t weight_layout;
+  int32_t swiglu_clamp;
+  float swiglu_limit;
+  int32_t fuse_dispatch;
+  int32_t weight_grad_f32;            /* 1: hidden_dw / gate_dw are FP32 partial gradients (numerics.py:32-34) */
+  int32_t reserved;
+  const int32_t* dispatch_src_index;  /* before FC2 only */
+  const int32_t* expert_of_row;
+  const int64_t* recv_segment_start;
+  const float* row_probs;             /* before FC2: received per-row probabilities saved by forward */
+  float* row_dot;                     /* before FC2: scratch float[rows] for the per-row probability gradient */
+  const hmc_moe_transport* transport;
+  /* optional prologue (probabilities after FC2): dY rows and the probability gradient from the token
+   * gradients (mega_moe_unpermute_grad_out, hyper_multicore/torch/csrc/mega_moe_unpermute.cpp:56-65) */
+  const void* grad_output;            /* [seq, H] bf16, or NULL */
+  const void* saved_combine;          /* routed forward output saved by hmc_mega_moe */
+  const int32_t* mapping;
+  const float* topk_probs;
+  float* grad_probs;                  /* [seq * top_k] out (before FC2: gathered from the returned per-row values) */
+  /* optional epilogue: dX[t] = sum of the token's returned rows (moe_token_permute_grad,
+   * hyper_multicore/torch/csrc/moe_token_permute_grad.cpp:29-38) */
+  void* grad_hidden;                  /* [seq, H] bf16, or NULL */
+} hmc_mega_moe_grad_args;
+
+typedef struct hmc_mega_moe_mxfp8_args {
+  /* --- the reference's buffer list, in its order (execution.py:88-96) --- */
+  void* dispatch_buffer;              /* [>= received_rows, H] bf16 */
+  const int64_t* dispatch_target_off;
+  const void* source_buffer;          /* tokens [seq, H] with dispatch_src_index, or expert-major rows */
+  const int64_t* dispatch_src_off;
+  const int32_t* dispatch_size;       /* not read */
+  const void* w1_col_data;            /* e4m3 [e, H, 2I] */
+  const int64_t* group_list;
+  void* up;                           /* [rows, 2I] bf16 out */
+  void* a_row;                        /* quantised activation: row data (see `a` for the other planes) */
+  const void* w2_col_data;            /* e4m3 [e, I, H] */
+  const int64_t* group_list2;         /* the same tensor as group_list */
+  void* down;                         /* [rows, H] bf16 out (ep == 1 only) */
+  void* routed_buffer;                /* combine target; NULL when ep == 1 */
+  const int64_t* combine_target_off;
+  const int64_t* combine_src_off;     /* not read */
+  const int32_t* combine_size;        /* not read */
+  void* x_row;
+  void* x_scale;
+  void* x_col;                        /* NULL unless a backward follows */
+  void* x_col_scale;
+  void* a_scale;
+  void* a_col;
+  void* a_col_scale;
+  const void* w1_col_scale;           /* scale-factor ATOMS of W1 (hmc_mx_pack_weight_scale, axis 0) */
+  const void* w2_col_scale;           /* scale-factor atoms of W2 */
+  int32_t* all_event_counters;
+  int32_t* diagnostic_buffer;
+  /* --- in place of the launch metadata blob --- */
+  int64_t rank_id, ep, expert_num, hidden_size, seq_size, intermediate_size, top_k, routed_rows, received_rows;
+  int64_t pad_blocks;                 /* 128-row blocks the quantised buffers hold (>= ceil(rows/128) + groups) */
+  const int32_t* dispatch_src_index;
+  const int32_t* expert_of_row;
+  const int64_t* recv_segment_start;
+  const hmc_moe_transport* transport;
+  void* saved_combine;                /* [routed_rows, H] <- routed_buffer (ep > 1) */
+  const int32_t* mapping;             /* optional epilogue as in hmc_mega_moe_args */
+  const float* topk_probs;
+  void* output;
+} hmc_mega_moe_mxfp8_args;
+
+typedef struct hmc_mega_moe_mxfp8_grad_args {
+  /* --- the reference's buffer list, in its order (execution.py:147-155) --- */
+  void* dispatch;                     /* [>= received_rows, H] bf16: received dY rows */
+  const int64_t* dispatch_target_off;
+  void* source;                       /* [routed_rows, H] bf16 expert-major dY rows (written by the prologue) */
+  const int64_t* dispatch_src_off;
+  const int32_t* dispatch_size;       /* not read */
+  const void* a_col;                  /* saved by forward */
+  void* dw2;                          /* [e, I, H] bf16 or f32; NULL = not needed */
+  const void* w2_row_data;            /* e4m3 [e, I, H], blocks along H */
+  void* da;                           /* [rows, I] bf16 out */
+  const void* up;                     /* saved by forward */
+  void* du_row;
+  const void* w1_row_data;            /* e4m3 [e, H, 2I], blocks along 2I */
+  void* dx;                           /* [rows, H] bf16 out (ep == 1 only) */
+  void* routed_buffer;                /* combine target; NULL when ep == 1 */
+  const int64_t* combine_target_off;
+  const int64_t* combine_src_off;     /* not read */
+  const int32_t* combine_size;        /* not read */
+  const void* x_col;                  /* saved by forward */
+  void* dw1;                          /* [e, H, 2I]; NULL = not needed */
+  const int64_t* group_list;
+  void* dy_row;
+  void* dy_scale;
+  void* dy_col;
+  void* dy_col_scale;
+  const void* a_col_scale;
+  const void* w2_row_scale;           /* scale-factor atoms (hmc_mx_pack_weight_scale, axis 1) */
+  void* du_scale;
+  void* du_col;
+  void* du_col_scale;
+  const void* w1_row_scale;           /* scale-factor atoms */
+  const void* x_col_scale;
+  int32_t* all_event_counters;
+  int32_t* diagnostic_buffer;
+  /* --- in place of the launch metadata blob --- */
+  int64_t rank_id, ep, expert_num, hidden_size, seq_size, intermediate_size, top_k, routed_rows, received_rows;
+  int64_t pad_blocks;
+  int32_t weight_grad_f32;
+  int32_t reserved;
+  const int64_t* recv_segment_start;
+  const int32_t* expert_of_row;
+  const hmc_moe_transport* transport;
+  /* prologue / epilogue as in hmc_mega_moe_grad_args */
+  const void* grad_output;
+  const void* saved_combine;
+  const int32_t* mapping;
+  const float* topk_probs;
+  float* grad_probs;
+  void* grad_hidden;
+} hmc_mega_moe_mxfp8_grad_args;
+
+int hmc_mega_moe(const hmc_mega_moe_args* args, void* stream);
+int hmc_mega_moe_grad(const hmc_mega_moe_grad_args* args, void* stream);
+int hmc_mega_moe_mxfp8(const hmc_mega_moe_mxfp8_args* args, void* stream);
+int hmc_mega_moe_mxfp8_grad(const hmc_mega_moe_mxfp8_grad_args* args, void* stream);
+/* ABI version of the MXFP8 operator pair the reference's loader asserts (mega_moe_mxfp8.cpp: == 3). */
+int hmc_mega_moe_mxfp8_abi_version(void);
 
 #ifdef __cplusplus
 }

@@ -47,6 +47,43 @@ def test_argument_checks_fail_without_touching_a_device():
     assert lib.hmc_route_offsets(None, 2, 5, 0, None, None, None, None, None, None, None, None, None, None) == -1
 
 
-def test_struct_sizes_match_the_header_layout():
-    # 8 int32 + 4 int64 + 6 pointers + uint64 + pointer
-    assert ctypes.sizeof(_lib.GroupedGemmArgs) == 8 * 4 + 4 * 8 + 6 * 8 + 8 + 8 + 2 * 4 + 3 * 8
+STRUCTS = {
+    "hmc_gemm_combine": "GemmCombine", "hmc_grouped_gemm_args": "GroupedGemmArgs", "hmc_mx_gemm_args": "MxGemmArgs",
+    "hmc_mx_quant_args": "MxQuantArgs", "hmc_gate_route_args": "GateRouteArgs",
+    "hmc_gate_route_grad_args": "GateRouteGradArgs", "hmc_mega_mhc_args": "MegaMhcArgs",
+    "hmc_mega_mhc_grad_args": "MegaMhcGradArgs", "hmc_ep_dispatch_args": "EpDispatchArgs",
+    "hmc_ep_combine_args": "EpCombineArgs", "hmc_ep_pull_args": "EpPullArgs", "hmc_ep_exchange_args": "EpExchangeArgs",
+    "hmc_moe_transport": "MoeTransport", "hmc_mega_moe_args": "MegaMoeArgs", "hmc_mega_moe_grad_args": "MegaMoeGradArgs",
+    "hmc_mega_moe_mxfp8_args": "MegaMoeMxfp8Args", "hmc_mega_moe_mxfp8_grad_args": "MegaMoeMxfp8GradArgs",
+}
+
+
+def test_struct_layouts_match_the_header(tmp_path):
+    """The header compiles as plain C, and every ctypes mirror has the size and the field offsets the C
+    compiler gives the struct it mirrors (field names are the same on both sides)."""
+    import shutil
+    import subprocess
+
+    if shutil.which("gcc") is None:
+        import pytest
+
+        pytest.skip("no C compiler")
+    header = (ROOT / "include" / "hmc_b200.h").read_text()
+    declared = set(re.findall(r"^} (hmc_[a-z0-9_]+);", header, flags=re.M))
+    assert declared == set(STRUCTS), "every struct of the header needs a ctypes mirror listed here"
+    lines = ['#include <stdio.h>', '#include <stddef.h>', f'#include "{ROOT / "include" / "hmc_b200.h"}"', "int main(void) {"]
+    for c_name, py_name in STRUCTS.items():
+        lines.append(f'  printf("{c_name} size %zu\\n", sizeof({c_name}));')
+        for field, _ in getattr(_lib, py_name)._fields_:  # pylint: disable=protected-access
+            lines.append(f'  printf("{c_name} {field} %zu\\n", offsetof({c_name}, {field}));')
+    lines += ["  return 0;", "}"]
+    source = tmp_path / "layout.c"
+    source.write_text("\n".join(lines))
+    binary = tmp_path / "layout"
+    subprocess.run(["gcc", "-std=c99", "-Wall", "-Werror", "-o", str(binary), str(source)], check=True)
+    output = subprocess.run([str(binary)], check=True, capture_output=True, text=True).stdout
+    for line in output.splitlines():
+        c_name, field, value = line.split()
+        mirror = getattr(_lib, STRUCTS[c_name])
+        expected = ctypes.sizeof(mirror) if field == "size" else getattr(mirror, field).offset
+        assert int(value) == expected, f"{c_name}.{field}: header {value}, ctypes {expected}"

@@ -226,3 +226,45 @@ def test_ready_flag_that_nobody_publishes_times_out(cuda_device):
     assert status.tolist()[0] == 0
     assert torch.equal(received, tokens)
     assert ctrl[:experts].tolist() == [rows // experts] * experts
+
+
+@pytest.mark.parametrize("tile_mode", [1, 2])
+@pytest.mark.parametrize("hidden", [256, 1000])
+def test_dispatch_warps_feed_the_gemm_that_carries_them(cuda_device, tile_mode, hidden):
+    """A row-ragged GEMM with a fused dispatch: extra warps of the same launch gather this rank's rows into
+    the receive buffer and advance the arrival counters its tile producers wait on. One rank stands for
+    the group (every expert is local), so rows, counters and results can be checked exactly."""
+    import ctypes
+
+    from hyper_multicore_b200 import _lib, kernels as K
+
+    torch.manual_seed(hidden + tile_mode)
+    dev = cuda_device
+    tokens, top_k, experts, n = 300, 2, 4, 256
+    x = torch.randn(tokens, hidden, device=dev).bfloat16()
+    ids = torch.stack([torch.randperm(experts, device=dev)[:top_k] for _ in range(tokens)]).int()
+    mapping, sources, row_experts, counts, _ = K.moe_sort_routes(ids, experts)
+    off = K.route_offsets(counts.view(1, experts), 0)
+    rows = tokens * top_k
+    w = (torch.randn(experts, hidden, n, device=dev) * 0.05).bfloat16()
+    received = torch.zeros(rows, hidden, device=dev, dtype=torch.bfloat16)
+    c = torch.zeros(rows, n, device=dev, dtype=torch.bfloat16)
+    ctrl = torch.zeros(_lib.HMC_CTRL_WORDS, dtype=torch.int32, device=dev)
+    peers = (ctypes.c_void_p * 1)(received.data_ptr())
+    peer_ctrl = (ctypes.c_void_p * 1)(ctrl.data_ptr())
+    status = _lib.new_status(dev)
+    K._call("hmc_ep_publish_ready", dev, peer_ctrl, 1, 0, 1)
+    sending = dict(tokens=x, source_of_row=sources, expert_of_row=row_experts, dispatch_src_off=off["dispatch_src_off"],
+                   dispatch_target_off=off["dispatch_target_off"], rows=rows, top_k=top_k, ep=1, local_experts=experts,
+                   capacity_rows=rows, peer_buffers=peers, peer_ctrl=peer_ctrl, local_ctrl=ctrl, generation=1,
+                   status=status, budget_ns=2_000_000_000, rank=0)
+    K.grouped_gemm(received, w, c, off["group_list"], mode=K.HMC_GEMM_RAGGED_M, ready_counters=ctrl[:experts],
+                   ready_budget_ns=2_000_000_000, status=status, tile_mode=tile_mode, dispatch=sending)
+    torch.cuda.synchronize()
+    assert status.tolist()[0] == 0, status.tolist()
+    expected_rows = x[(sources // top_k).long()]
+    assert torch.equal(received, expected_rows), "the dispatch warps must deliver every row to its slot"
+    assert ctrl[:experts].tolist() == counts.tolist(), "every expert's arrival counter must reach its row count"
+    starts = [0] + counts.cumsum(0).tolist()
+    ref = torch.cat([expected_rows[starts[g]:starts[g + 1]].float() @ w[g].float() for g in range(experts)])
+    _close(c, ref)
