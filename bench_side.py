@@ -284,7 +284,7 @@ def run_gpu(args, workload: str, clock_sampler_cls) -> None:
         if flush is not None:
             # per-step events so that the L2 flush between steps stays outside the measured time
             pairs = []
-            launches_before = kernels.LAUNCH_COUNT
+            launches_before = _lib.launch_count()
             for _ in range(steps):
                 flush.zero_()
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -296,7 +296,7 @@ def run_gpu(args, workload: str, clock_sampler_cls) -> None:
             total = sum(a.elapsed_time(b) for a, b in pairs)
         else:
             start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            launches_before = kernels.LAUNCH_COUNT
+            launches_before = _lib.launch_count()
             start.record()
             for _ in range(steps):
                 step()
@@ -306,7 +306,7 @@ def run_gpu(args, workload: str, clock_sampler_cls) -> None:
         ms = torch.tensor([total], device=device)
         if world > 1:
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-        return float(ms.item()), kernels.LAUNCH_COUNT - launches_before
+        return float(ms.item()), _lib.launch_count() - launches_before
 
     sampler = clock_sampler_cls(local_rank)
     if rank == 0:

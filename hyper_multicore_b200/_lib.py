@@ -27,6 +27,7 @@ HMC_STATUS_WORDS = 8
 HMC_CTRL_SOURCE = 1296
 HMC_CTRL_COUNTS = 1552
 HMC_CLAMP_NONE, HMC_CLAMP_BEFORE_SILU, HMC_CLAMP_AFTER_SILU = 0, 1, 2
+HMC_PROFILE_KINDS = ("grouped_gemm", "mx_gemm", "mx_quant", "ep")
 HMC_MOE_LAYOUT = {"EIO": 0, "EOI": 1}
 HMC_MOE_DISPATCH = {"push": 0, "pull": 1}
 
@@ -250,7 +251,8 @@ class MegaMoeArgs(ctypes.Structure):
         ("rank_id", c_int64), ("ep", c_int64), ("expert_num", c_int64), ("hidden_size", c_int64),
         ("seq_size", c_int64), ("intermediate_size", c_int64), ("top_k", c_int64), ("routed_rows", c_int64),
         ("received_rows", c_int64), ("weight_layout", c_int32), ("swiglu_clamp", c_int32),
-        ("swiglu_limit", c_float), ("fuse_dispatch", c_int32), ("dispatch_src_index", c_void_p),
+        ("swiglu_limit", c_float), ("fuse_dispatch", c_int32), ("probs_before_fc2", c_int32), ("reserved", c_int32),
+        ("dispatch_src_index", c_void_p),
         ("expert_of_row", c_void_p), ("recv_segment_start", c_void_p), ("route_probs", c_void_p),
         ("row_probs", c_void_p), ("transport", c_void_p), ("saved_dispatch", c_void_p),
         ("saved_combine", c_void_p), ("saved_row_probs", c_void_p), ("mapping", c_void_p),
@@ -272,7 +274,7 @@ class MegaMoeGradArgs(ctypes.Structure):
         ("hidden_size", c_int64), ("seq_size", c_int64), ("intermediate_size", c_int64), ("top_k", c_int64),
         ("routed_rows", c_int64), ("received_rows", c_int64), ("weight_layout", c_int32),
         ("swiglu_clamp", c_int32), ("swiglu_limit", c_float), ("fuse_dispatch", c_int32),
-        ("weight_grad_f32", c_int32), ("reserved", c_int32), ("dispatch_src_index", c_void_p),
+        ("weight_grad_f32", c_int32), ("probs_before_fc2", c_int32), ("dispatch_src_index", c_void_p),
         ("expert_of_row", c_void_p), ("recv_segment_start", c_void_p), ("row_probs", c_void_p),
         ("row_dot", c_void_p), ("transport", c_void_p), ("grad_output", c_void_p), ("saved_combine", c_void_p),
         ("mapping", c_void_p), ("topk_probs", c_void_p), ("grad_probs", c_void_p), ("grad_hidden", c_void_p),
@@ -341,6 +343,9 @@ SIGNATURES: dict[str, tuple] = {
     "hmc_abi_version": (_I, []),
     "hmc_mega_moe_transport_version": (_I, []),
     "hmc_worker_queue_layout_version": (_I, []),
+    "hmc_launch_count": (_L, []),
+    "hmc_profile_enable": (_I, [_I]),
+    "hmc_profile_collect": (_I, [ctypes.POINTER(c_double), ctypes.POINTER(c_int64), _I]),
     "hmc_grouped_gemm": (_I, [ctypes.POINTER(GroupedGemmArgs), _P]),
     "hmc_grouped_gemm_combine_units": (_L, [_L]),
     "hmc_mx_gemm": (_I, [ctypes.POINTER(MxGemmArgs), _P]),
@@ -439,3 +444,31 @@ def raise_on_status(status: torch.Tensor, what: str) -> None:
     words = status.tolist()
     if words[0] != 0:
         raise HmcError(f"{what}: device status {words[0]} ({STATUS_NAMES.get(words[0], '?')}), detail {words[1:4]}")
+
+
+def launch_count() -> int:
+    """Kernels this library has launched in this process (counted where they are launched, in C)."""
+    return int(load().hmc_launch_count())
+
+
+class profile:  # pylint: disable=invalid-name
+    """Context manager: device time and call counts per kind of entry point while it is active.
+
+    ``with profile() as p: ...`` then ``p.ms["grouped_gemm"]``, ``p.calls["grouped_gemm"]`` (synchronises at exit).
+    """
+
+    def __enter__(self):
+        self.ms, self.calls = {}, {}
+        check(load().hmc_profile_enable(1))
+        return self
+
+    def __exit__(self, *exc):
+        lib = load()
+        lib.hmc_profile_enable(0)
+        kinds = len(HMC_PROFILE_KINDS)
+        ms = (c_double * kinds)()
+        calls = (c_int64 * kinds)()
+        check(lib.hmc_profile_collect(ms, calls, kinds))
+        self.ms = dict(zip(HMC_PROFILE_KINDS, ms))
+        self.calls = dict(zip(HMC_PROFILE_KINDS, calls))
+        return False

@@ -43,7 +43,21 @@ void set_error(const char* fmt, ...);
                        __FILE__, __LINE__);                                          \
       return HMC_ERR_CUDA;                                                           \
     }                                                                                \
+    ::hmc::count_launch();                                                           \
   } while (0)
+
+void count_launch();  // one more kernel of this library launched (hmc_launch_count)
+
+// Brackets the launches of one entry point with CUDA events while profiling is on (hmc_profile_enable):
+// per-kind device time for callers that report where a step's time goes. Does nothing when it is off.
+struct ProfileScope {
+  ProfileScope(int kind, cudaStream_t stream);
+  ~ProfileScope();
+  int kind_;
+  cudaStream_t stream_;
+  cudaEvent_t start_;
+  bool active_;
+};
 
 int sm_count();  // number of SMs on the current device (cached per device)
 

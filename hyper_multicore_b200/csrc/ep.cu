@@ -473,6 +473,7 @@ extern "C" int hmc_ep_publish_source(void* const* peer_ctrl, int64_t ep, int64_t
 extern "C" int hmc_ep_pull(const hmc_ep_pull_args* args, void* stream_ptr) {
   HMC_REQUIRE(args != nullptr, HMC_ERR_INVALID, "hmc_ep_pull: null args");
   const hmc_ep_pull_args& a = *args;
+  ProfileScope profile(HMC_PROFILE_EP, static_cast<cudaStream_t>(stream_ptr));
   if (a.rows == 0) return 0;
   PeerTable table;
   int rc = fill_peers(&table, a.peer_sources, a.peer_sources, a.ep);
@@ -504,6 +505,7 @@ extern "C" int hmc_ep_pull(const hmc_ep_pull_args* args, void* stream_ptr) {
 extern "C" int hmc_ep_dispatch(const hmc_ep_dispatch_args* args, void* stream_ptr) {
   HMC_REQUIRE(args != nullptr, HMC_ERR_INVALID, "hmc_ep_dispatch: null args");
   const hmc_ep_dispatch_args& a = *args;
+  ProfileScope profile(HMC_PROFILE_EP, static_cast<cudaStream_t>(stream_ptr));
   if (a.rows == 0) return 0;
   PeerTable table;
   int rc = fill_peers(&table, a.peer_buffers, a.peer_ctrl, a.ep);
@@ -536,6 +538,7 @@ extern "C" int hmc_ep_dispatch(const hmc_ep_dispatch_args* args, void* stream_pt
 extern "C" int hmc_ep_combine(const hmc_ep_combine_args* args, void* stream_ptr) {
   HMC_REQUIRE(args != nullptr, HMC_ERR_INVALID, "hmc_ep_combine: null args");
   const hmc_ep_combine_args& a = *args;
+  ProfileScope profile(HMC_PROFILE_EP, static_cast<cudaStream_t>(stream_ptr));
   if (a.rows == 0) return 0;
   PeerTable table;
   int rc = fill_peers(&table, a.peer_buffers, a.peer_ctrl, a.ep);
@@ -566,6 +569,7 @@ extern "C" int hmc_ep_combine(const hmc_ep_combine_args* args, void* stream_ptr)
 extern "C" int hmc_ep_wait(const int32_t* counter, int32_t expected, uint64_t budget_ns, int32_t* status,
                            void* stream_ptr) {
   HMC_REQUIRE(counter != nullptr, HMC_ERR_INVALID, "hmc_ep_wait: null counter");
+  ProfileScope profile(HMC_PROFILE_EP, static_cast<cudaStream_t>(stream_ptr));
   ep_wait_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream_ptr)>>>(
       counter, expected, budget_ns ? budget_ns : 10ull * 1000 * 1000 * 1000, status);
   HMC_LAUNCH_OK();
@@ -576,6 +580,7 @@ extern "C" int hmc_ep_wait_groups(const int32_t* counters, const int64_t* group_
                                   uint64_t budget_ns, int32_t* status, void* stream_ptr) {
   HMC_REQUIRE(counters != nullptr && group_ends != nullptr && groups > 0 && groups <= HMC_CTRL_MAX_LOCAL_EXPERTS,
               HMC_ERR_INVALID, "hmc_ep_wait_groups: bad arguments");
+  ProfileScope profile(HMC_PROFILE_EP, static_cast<cudaStream_t>(stream_ptr));
   ep_wait_groups_kernel<<<static_cast<unsigned>((groups + 127) / 128), 128, 0, static_cast<cudaStream_t>(stream_ptr)>>>(
       counters, reinterpret_cast<const long long*>(group_ends), static_cast<int>(groups),
       budget_ns ? budget_ns : 10ull * 1000 * 1000 * 1000, status);

@@ -285,7 +285,9 @@ __device__ __forceinline__ void epilogue_rows(const Params& p, uint32_t taddr, l
     __nv_bfloat16* u_dst = static_cast<__nv_bfloat16*>(p.c) + out_row * p.ldc + col_base;
     __nv_bfloat16* a_dst = static_cast<__nv_bfloat16*>(p.aux) + out_row * p.ld_aux + col_base;
     const bool options = p.swiglu_clamp != HMC_CLAMP_NONE || p.row_probs != nullptr;
-    const float prob = (p.row_probs != nullptr && row_ok) ? p.row_probs[out_row] : 1.0f;
+    // Read past L1: with the dispatch riding in this kernel, a neighbouring row's probability can have been
+    // cached (same 128-byte line) before this row's value arrived from its source rank.
+    const float prob = (p.row_probs != nullptr && row_ok) ? __ldcg(p.row_probs + out_row) : 1.0f;
 #pragma unroll 1
     for (int c = half * (BN / 4); c < (half + 1) * (BN / 4); c += 32) {
       uint32_t g[32], u[32];
@@ -330,7 +332,9 @@ __device__ __forceinline__ void epilogue_rows(const Params& p, uint32_t taddr, l
     const __nv_bfloat16* u_src = static_cast<const __nv_bfloat16*>(p.aux) + out_row * p.ld_aux + col_base;
     __nv_bfloat16* d_dst = static_cast<__nv_bfloat16*>(p.c) + out_row * p.ldc + col_base;
     const bool options = p.swiglu_clamp != HMC_CLAMP_NONE || p.row_probs != nullptr;
-    const float prob = (p.row_probs != nullptr && row_ok) ? p.row_probs[out_row] : 1.0f;
+    // Read past L1: with the dispatch riding in this kernel, a neighbouring row's probability can have been
+    // cached (same 128-byte line) before this row's value arrived from its source rank.
+    const float prob = (p.row_probs != nullptr && row_ok) ? __ldcg(p.row_probs + out_row) : 1.0f;
     float dot = 0.0f;
 #pragma unroll 1
     for (int c = c_lo; c < c_hi; c += 32) {

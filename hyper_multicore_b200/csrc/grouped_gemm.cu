@@ -447,6 +447,7 @@ extern "C" int hmc_grouped_gemm(const hmc_grouped_gemm_args* args, void* stream_
   HMC_REQUIRE(args != nullptr, HMC_ERR_INVALID, "hmc_grouped_gemm: null args");
   const hmc_grouped_gemm_args& a = *args;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  ProfileScope profile(HMC_PROFILE_GROUPED_GEMM, stream);
   HMC_REQUIRE(a.mode == HMC_GEMM_RAGGED_M || a.mode == HMC_GEMM_RAGGED_K, HMC_ERR_INVALID,
               "hmc_grouped_gemm: unknown mode %d", a.mode);
   HMC_REQUIRE(a.epilogue >= HMC_EPI_STORE_BF16 && a.epilogue <= HMC_EPI_SWIGLU_GRAD, HMC_ERR_INVALID,
@@ -517,7 +518,7 @@ extern "C" int hmc_grouped_gemm(const hmc_grouped_gemm_args* args, void* stream_
     p.combine_enabled = 1;
   }
 
-  if (a.dispatch != nullptr) {
+  if (a.dispatch != nullptr && a.dispatch->rows > 0) {  // a rank without rows has nothing to send
     const hmc_ep_dispatch_args& d = *a.dispatch;
     HMC_REQUIRE(a.mode == HMC_GEMM_RAGGED_M && a.ready_counters != nullptr, HMC_ERR_INVALID,
                 "hmc_grouped_gemm: a fused dispatch belongs to a RAGGED_M GEMM gated by arrival counters");
@@ -528,7 +529,7 @@ extern "C" int hmc_grouped_gemm(const hmc_grouped_gemm_args* args, void* stream_
                 (long long)a.k, a.groups);
     HMC_REQUIRE(d.peer_buffers[d.rank] == a.a, HMC_ERR_INVALID,
                 "hmc_grouped_gemm: with a fused dispatch, a must be this rank's own receive buffer");
-    p.dispatch_enabled = d.rows > 0 ? 1 : 0;
+    p.dispatch_enabled = 1;
   }
 
   CUtensorMap ta, tb, tc;

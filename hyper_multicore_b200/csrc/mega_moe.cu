@@ -288,18 +288,20 @@ extern "C" int hmc_mega_moe(const hmc_mega_moe_args* args, void* stream_ptr) {
   const bool ep1 = a.ep == 1;
   HMC_TRY(check_transport(a.transport, "hmc_mega_moe", a.ep, a.rank_id, a.all_event_counters, !ep1));
   const hmc_moe_transport& t = *a.transport;
-  const bool before_fc2 = a.route_probs != nullptr;
+  const bool before_fc2 = a.probs_before_fc2 != 0;
   const bool pull = !ep1 && t.dispatch_mode == HMC_MOE_DISPATCH_PULL;
   const bool local_gather = ep1 && !before_fc2;  // one rank owns every expert: a gather, nothing to wait for
   HMC_REQUIRE(ep1 ? a.down_proj_y != nullptr : a.combine_target != nullptr, HMC_ERR_INVALID,
               "hmc_mega_moe: down_proj_y (one rank) or combine_target (expert parallel) is required");
-  HMC_REQUIRE(local_gather || (a.expert_of_row && a.dispatch_src_off && a.dispatch_target_off), HMC_ERR_INVALID,
+  HMC_REQUIRE(local_gather || ((a.expert_of_row || s.routed == 0) && a.dispatch_src_off && a.dispatch_target_off),
+              HMC_ERR_INVALID,
               "hmc_mega_moe: dispatch needs expert_of_row and the dispatch offsets");
   HMC_REQUIRE(ep1 || (a.recv_segment_start && a.combine_target_off), HMC_ERR_INVALID,
               "hmc_mega_moe: combine needs recv_segment_start and combine_target_off");
-  HMC_REQUIRE(!before_fc2 || (a.row_probs != nullptr && a.dispatch_src_index != nullptr), HMC_ERR_INVALID,
-              "hmc_mega_moe: probabilities before FC2 need row_probs for the received rows and dispatch_src_index");
-  HMC_REQUIRE(!local_gather || a.dispatch_src_index != nullptr || a.dispatch_src == a.dispatch_target, HMC_ERR_INVALID,
+  HMC_REQUIRE(!before_fc2 || (a.row_probs != nullptr && ((a.dispatch_src_index && a.route_probs) || s.routed == 0)),
+              HMC_ERR_INVALID, "hmc_mega_moe: probabilities before FC2 need row_probs for the received rows and dispatch_src_index");
+  HMC_REQUIRE(!local_gather || a.dispatch_src_index != nullptr || a.dispatch_src == a.dispatch_target || s.routed == 0,
+              HMC_ERR_INVALID,
               "hmc_mega_moe: a single rank gathers its rows through dispatch_src_index");
   HMC_REQUIRE(a.output == nullptr || (a.mapping != nullptr && (before_fc2 || a.topk_probs != nullptr)), HMC_ERR_INVALID,
               "hmc_mega_moe: the Top-K sum needs mapping and topk_probs");
@@ -419,16 +421,19 @@ extern "C" int hmc_mega_moe_grad(const hmc_mega_moe_grad_args* args, void* strea
   const bool ep1 = a.ep == 1;
   HMC_TRY(check_transport(a.transport, "hmc_mega_moe_grad", a.ep, a.rank_id, a.all_event_counters, !ep1));
   const hmc_moe_transport& t = *a.transport;
-  const bool before_fc2 = a.row_probs != nullptr;
+  const bool before_fc2 = a.probs_before_fc2 != 0;
   const bool pull = !ep1 && t.dispatch_mode == HMC_MOE_DISPATCH_PULL;
   const bool eio = a.weight_layout == HMC_MOE_LAYOUT_EIO;
-  HMC_REQUIRE(!before_fc2 || (a.row_dot != nullptr && a.dispatch_src_index != nullptr), HMC_ERR_INVALID,
+  HMC_REQUIRE(!before_fc2 || (a.row_dot != nullptr && a.row_probs != nullptr && (a.dispatch_src_index != nullptr || s.routed == 0)),
+              HMC_ERR_INVALID,
               "hmc_mega_moe_grad: probabilities before FC2 need row_dot scratch and dispatch_src_index");
-  HMC_REQUIRE(before_fc2 || a.grad_output == nullptr || (a.mapping && a.topk_probs && a.grad_probs && a.saved_combine),
+  HMC_REQUIRE(before_fc2 || a.grad_output == nullptr || s.tokens == 0 ||
+                  (a.mapping && a.topk_probs && a.grad_probs && a.saved_combine),
               HMC_ERR_INVALID, "hmc_mega_moe_grad: the prologue needs mapping, topk_probs, grad_probs and saved_combine");
-  HMC_REQUIRE(a.grad_hidden == nullptr || a.mapping != nullptr, HMC_ERR_INVALID,
+  HMC_REQUIRE(a.grad_hidden == nullptr || a.mapping != nullptr || s.tokens == 0, HMC_ERR_INVALID,
               "hmc_mega_moe_grad: the Top-K sum of dX needs mapping");
-  HMC_REQUIRE(ep1 || (a.grad_x && a.recv_segment_start && a.combine_target_off && a.expert_of_row), HMC_ERR_INVALID,
+  HMC_REQUIRE(ep1 || (a.grad_x && a.recv_segment_start && a.combine_target_off && (a.expert_of_row || s.routed == 0)),
+              HMC_ERR_INVALID,
               "hmc_mega_moe_grad: expert parallelism needs grad_x, the combine tables and expert_of_row");
   const bool fused_combine = !ep1 && !before_fc2;  // with the probability gradient travelling back the rows
                                                    // return through the combine kernel, which carries it
@@ -689,8 +694,8 @@ extern "C" int hmc_mega_moe_mxfp8(const hmc_mega_moe_mxfp8_args* args, void* str
   const bool ep1 = a.ep == 1;
   HMC_TRY(check_transport(a.transport, "hmc_mega_moe_mxfp8", a.ep, a.rank_id, a.all_event_counters, !ep1));
   const hmc_moe_transport& t = *a.transport;
-  HMC_REQUIRE(ep1 ? a.down != nullptr : (a.routed_buffer && a.recv_segment_start && a.combine_target_off && a.expert_of_row &&
-                                         a.dispatch_buffer),
+  HMC_REQUIRE(ep1 ? a.down != nullptr : (a.routed_buffer && a.recv_segment_start && a.combine_target_off &&
+                                         (a.expert_of_row || s.routed == 0) && a.dispatch_buffer),
               HMC_ERR_INVALID, "hmc_mega_moe_mxfp8: missing output or combine tables");
   HMC_REQUIRE(a.pad_blocks >= (s.received + 127) / 128, HMC_ERR_INVALID, "hmc_mega_moe_mxfp8: pad_blocks too small");
   HMC_REQUIRE(a.output == nullptr || (a.mapping && a.topk_probs), HMC_ERR_INVALID,
@@ -764,8 +769,8 @@ extern "C" int hmc_mega_moe_mxfp8_grad(const hmc_mega_moe_mxfp8_grad_args* args,
   const bool ep1 = a.ep == 1;
   HMC_TRY(check_transport(a.transport, "hmc_mega_moe_mxfp8_grad", a.ep, a.rank_id, a.all_event_counters, !ep1));
   const hmc_moe_transport& t = *a.transport;
-  HMC_REQUIRE(ep1 ? a.dx != nullptr : (a.routed_buffer && a.recv_segment_start && a.combine_target_off && a.expert_of_row &&
-                                       a.dispatch),
+  HMC_REQUIRE(ep1 ? a.dx != nullptr : (a.routed_buffer && a.recv_segment_start && a.combine_target_off &&
+                                       (a.expert_of_row || s.routed == 0) && a.dispatch),
               HMC_ERR_INVALID, "hmc_mega_moe_mxfp8_grad: missing output or combine tables");
   HMC_REQUIRE(a.grad_output == nullptr || (a.mapping && a.topk_probs && a.grad_probs && a.saved_combine), HMC_ERR_INVALID,
               "hmc_mega_moe_mxfp8_grad: the prologue needs mapping, topk_probs, grad_probs and saved_combine");

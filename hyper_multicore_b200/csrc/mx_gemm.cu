@@ -505,6 +505,7 @@ extern "C" int hmc_mx_gemm(const hmc_mx_gemm_args* args, void* stream_ptr) {
   HMC_REQUIRE(args != nullptr, HMC_ERR_INVALID, "hmc_mx_gemm: null args");
   const hmc_mx_gemm_args& a = *args;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  ProfileScope profile(HMC_PROFILE_MX_GEMM, stream);
   HMC_REQUIRE(a.mode == HMC_GEMM_RAGGED_M || a.mode == HMC_GEMM_RAGGED_K, HMC_ERR_INVALID,
               "hmc_mx_gemm: unknown mode %d", a.mode);
   HMC_REQUIRE(a.groups > 0 && a.rows >= 0 && a.pad_blocks > 0, HMC_ERR_INVALID,

@@ -304,6 +304,7 @@ using namespace hmc;
 extern "C" int hmc_mx_quant(const hmc_mx_quant_args* args, void* stream_ptr) {
   HMC_REQUIRE(args != nullptr, HMC_ERR_INVALID, "hmc_mx_quant: null args");
   const hmc_mx_quant_args& a = *args;
+  ProfileScope profile(HMC_PROFILE_MX_QUANT, static_cast<cudaStream_t>(stream_ptr));
   HMC_REQUIRE(a.kind >= HMC_MXQ_PLAIN && a.kind <= HMC_MXQ_SWIGLU_GRAD, HMC_ERR_INVALID, "hmc_mx_quant: unknown kind %d",
               a.kind);
   HMC_REQUIRE(a.groups > 0 && a.rows >= 0 && a.pad_blocks >= (a.rows + 127) / 128 && a.pad_blocks > 0 &&

@@ -1,9 +1,47 @@
 // Process-level pieces of the hmc_* C ABI: thread-local error text, device queries, versions.
 #include <string.h>
 
+#include <atomic>
+#include <mutex>
+#include <vector>
+
 #include "common.cuh"
 
 namespace hmc {
+
+static std::atomic<long long> g_launches{0};
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+
+// ------------------------------------------------------------------------------------- profiling
+struct ProfileRecord {
+  cudaEvent_t start, stop;
+  int kind;
+};
+static std::atomic<int> g_profile_on{0};
+static std::mutex g_profile_mutex;
+static std::vector<ProfileRecord> g_profile_records;
+
+ProfileScope::ProfileScope(int kind, cudaStream_t stream) : kind_(kind), stream_(stream), start_(nullptr), active_(false) {
+  if (g_profile_on.load(std::memory_order_relaxed) == 0) return;
+  if (cudaEventCreate(&start_) != cudaSuccess) return;
+  if (cudaEventRecord(start_, stream_) != cudaSuccess) {
+    cudaEventDestroy(start_);
+    return;
+  }
+  active_ = true;
+}
+
+ProfileScope::~ProfileScope() {
+  if (!active_) return;
+  cudaEvent_t stop = nullptr;
+  if (cudaEventCreate(&stop) != cudaSuccess || cudaEventRecord(stop, stream_) != cudaSuccess) {
+    cudaEventDestroy(start_);
+    if (stop != nullptr) cudaEventDestroy(stop);
+    return;
+  }
+  std::lock_guard<std::mutex> lock(g_profile_mutex);
+  g_profile_records.push_back({start_, stop, kind_});
+}
 
 static thread_local char g_error[512] = "";
 
@@ -32,6 +70,41 @@ extern "C" const char* hmc_last_error(void) { return hmc::g_error; }
 extern "C" int hmc_abi_version(void) { return HMC_ABI_VERSION; }
 extern "C" int hmc_mega_moe_transport_version(void) { return 2; }
 extern "C" int hmc_worker_queue_layout_version(void) { return 2; }
+extern "C" int64_t hmc_launch_count(void) { return hmc::g_launches.load(std::memory_order_relaxed); }
+
+extern "C" int hmc_profile_enable(int on) {
+  hmc::g_profile_on.store(on ? 1 : 0, std::memory_order_relaxed);
+  return 0;
+}
+
+extern "C" int hmc_profile_collect(double* ms_by_kind, int64_t* calls_by_kind, int kinds) {
+  using namespace hmc;
+  HMC_REQUIRE(ms_by_kind != nullptr && calls_by_kind != nullptr && kinds > 0, HMC_ERR_INVALID,
+              "hmc_profile_collect: bad arguments");
+  for (int k = 0; k < kinds; ++k) {
+    ms_by_kind[k] = 0.0;
+    calls_by_kind[k] = 0;
+  }
+  std::vector<ProfileRecord> records;
+  {
+    std::lock_guard<std::mutex> lock(g_profile_mutex);
+    records.swap(g_profile_records);
+  }
+  int rc = 0;
+  for (const ProfileRecord& r : records) {
+    float ms = 0.0f;
+    if (cudaEventSynchronize(r.stop) != cudaSuccess || cudaEventElapsedTime(&ms, r.start, r.stop) != cudaSuccess) {
+      rc = HMC_ERR_CUDA;
+    } else if (r.kind >= 0 && r.kind < kinds) {
+      ms_by_kind[r.kind] += ms;
+      calls_by_kind[r.kind] += 1;
+    }
+    cudaEventDestroy(r.start);
+    cudaEventDestroy(r.stop);
+  }
+  if (rc != 0) set_error("hmc_profile_collect: an event could not be read");
+  return rc;
+}
 
 namespace {
 __global__ void store_words_kernel(int* __restrict__ dst, const int* __restrict__ src, long long words) {

@@ -123,7 +123,6 @@ def grouped_gemm(
     if dispatch is not None:
         sending = _dispatch_struct(**dispatch)
         args.dispatch = ctypes.cast(ctypes.pointer(sending), ctypes.c_void_p)
-    _count("hmc_grouped_gemm")
     with torch.cuda.device(device):
         _lib.check(_lib.load().hmc_grouped_gemm(ctypes.byref(args), _lib.stream_ptr(device)))
 
@@ -144,16 +143,7 @@ def grouped_gemm_combine_units(n: int) -> int:
     return int(_lib.load().hmc_grouped_gemm_combine_units(n))
 
 
-LAUNCH_COUNT = 0  # kernels of this library launched so far in this process
-
-
-def _count(name: str) -> None:
-    global LAUNCH_COUNT  # pylint: disable=global-statement
-    LAUNCH_COUNT += KERNELS_PER_CALL.get(name, 1)
-
-
 def _call(name: str, device: torch.device, *args) -> None:
-    _count(name)
     with torch.cuda.device(device):
         _lib.check(getattr(_lib.load(), name)(*args, _lib.stream_ptr(device)))
 
@@ -495,22 +485,8 @@ def ep_wait(counter: torch.Tensor, expected: int, status=None, budget_ns: int = 
     _call("hmc_ep_wait", device, counter.data_ptr(), expected, budget_ns, _lib.ptr(status))
 
 
-# ------------------------------------------------------------------------------ launch accounting
-# Kernels launched per C-ABI call, for callers that report how many device launches a step made.
-KERNELS_PER_CALL = {
-    "hmc_grouped_gemm": 1, "hmc_gate_project_tc": 3, "hmc_gate_project_promoted": 2, "hmc_gate_route": 1, "hmc_gate_route_grad": 1, "hmc_gate_project": 1,
-    "hmc_moe_histogram": 1, "hmc_moe_sort_routes": 3, "hmc_moe_gather_rows": 1,
-    "hmc_moe_permute_from_mapping": 1, "hmc_moe_unpermute": 1, "hmc_moe_unpermute_grad": 1,
-    "hmc_moe_token_permute_grad": 1, "hmc_zero_empty_expert_grad": 1, "hmc_route_offsets": 1,
-    "hmc_mega_mhc": 5, "hmc_mega_mhc_grad": 8, "hmc_ep_publish_ready": 1, "hmc_ep_dispatch": 1,
-    "hmc_ep_combine": 1, "hmc_ep_wait": 1, "hmc_ep_wait_groups": 1, "hmc_ep_publish_source": 1, "hmc_ep_pull": 1, "hmc_store_words": 1,
-}
-
-
 # ---------------------------------------------------------------------------------------- MXFP8
 HMC_MXQ_PLAIN, HMC_MXQ_SWIGLU, HMC_MXQ_SWIGLU_GRAD = 0, 1, 2
-KERNELS_PER_CALL.update({"hmc_mx_gemm": 1, "hmc_mx_quant": 1, "hmc_mx_quant_weight": 1,
-                         "hmc_mx_pack_weight_scale": 1})
 
 
 def mx_pad_blocks(rows: int, groups: int) -> int:

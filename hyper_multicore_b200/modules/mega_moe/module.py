@@ -611,7 +611,8 @@ class MegaMoeExperts(torch.nn.Module):
         return ops.MegaMoeLaunch(
             transport=transport, intermediate_size=self.intermediate_size, top_k=self.top_k,
             routed_rows=route.routed_rows, received_rows=route.received_rows, weight_layout=self._layout or "EIO",
-            fuse_dispatch=self._fuse_dispatch, status=self._status, expert_of_row=route.expert_of_row,
+            fuse_dispatch=self._fuse_dispatch, probs_before_fc2=self._numerics.apply_probs_before_fc2,
+            status=self._status, expert_of_row=route.expert_of_row,
             recv_segment_start=off["recv_segment_start"], mapping=route.mapping, **self._swiglu_options(), **fields)
 
     def _run_forward(self, hidden, probs, w1, w2, route: PreparedRoute):

@@ -233,6 +233,7 @@ class MegaMoeLaunch:
     swiglu_clamp: int = 0
     swiglu_limit: float = 0.0
     fuse_dispatch: bool = True
+    probs_before_fc2: bool = False
     status: torch.Tensor | None = None
     dispatch_src_index: torch.Tensor | None = None
     expert_of_row: torch.Tensor | None = None
@@ -268,7 +269,7 @@ def _check_rows(name: str, tensor: torch.Tensor | None, width: int, dtype=torch.
 
 
 def _launch_native(name: str, args, device: torch.device, launches: int) -> None:
-    kernels.LAUNCH_COUNT += launches
+    del launches  # counted by the native library itself
     with torch.cuda.device(device):
         _lib.check(getattr(_lib.load(), name)(ctypes.byref(args), _lib.stream_ptr(device)))
 
@@ -318,7 +319,7 @@ def mega_moe(dispatch_target, dispatch_target_off, dispatch_src, dispatch_src_of
     args.routed_rows, args.received_rows = launch.routed_rows, launch.received_rows
     args.weight_layout = _lib.HMC_MOE_LAYOUT[launch.weight_layout]
     args.swiglu_clamp, args.swiglu_limit = launch.swiglu_clamp, launch.swiglu_limit
-    args.fuse_dispatch = int(launch.fuse_dispatch)
+    args.fuse_dispatch, args.probs_before_fc2 = int(launch.fuse_dispatch), int(launch.probs_before_fc2)
     args.dispatch_src_index, args.expert_of_row = _ptr(launch.dispatch_src_index), _ptr(launch.expert_of_row)
     args.recv_segment_start = _ptr(launch.recv_segment_start)
     args.route_probs, args.row_probs = _ptr(launch.route_probs), _ptr(launch.row_probs)
@@ -379,6 +380,7 @@ def mega_moe_grad(dispatch_target, dispatch_target_off, dy, dispatch_src_off, di
     args.weight_layout = _lib.HMC_MOE_LAYOUT[launch.weight_layout]
     args.swiglu_clamp, args.swiglu_limit = launch.swiglu_clamp, launch.swiglu_limit
     args.fuse_dispatch, args.weight_grad_f32 = int(launch.fuse_dispatch), int(launch.weight_grad_f32)
+    args.probs_before_fc2 = int(launch.probs_before_fc2)
     args.dispatch_src_index, args.expert_of_row = _ptr(launch.dispatch_src_index), _ptr(launch.expert_of_row)
     args.recv_segment_start = _ptr(launch.recv_segment_start)
     args.row_probs, args.row_dot = _ptr(launch.row_probs), _ptr(launch.row_dot)

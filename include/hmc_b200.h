@@ -45,6 +45,18 @@ int hmc_abi_version(void);
  * (hyper_multicore/torch/csrc/registration.cpp:21-22). */
 int hmc_mega_moe_transport_version(void);
 int hmc_worker_queue_layout_version(void);
+/* Measurement helpers, no counterpart in the reference. hmc_launch_count: kernels this library has launched
+ * in this process. While hmc_profile_enable(1) is in force, every call of the entry points listed below is
+ * bracketed by two CUDA events on its stream; hmc_profile_collect waits for them, adds the device time and the
+ * number of calls per kind into ms_by_kind / calls_by_kind [kinds] and forgets them (it synchronises). */
+#define HMC_PROFILE_GROUPED_GEMM 0 /* hmc_grouped_gemm */
+#define HMC_PROFILE_MX_GEMM 1      /* hmc_mx_gemm */
+#define HMC_PROFILE_MX_QUANT 2     /* hmc_mx_quant */
+#define HMC_PROFILE_EP 3           /* hmc_ep_dispatch, hmc_ep_pull, hmc_ep_combine, hmc_ep_wait(_groups) */
+#define HMC_PROFILE_KINDS 4
+int64_t hmc_launch_count(void);
+int hmc_profile_enable(int on);
+int hmc_profile_collect(double* ms_by_kind, int64_t* calls_by_kind, int kinds);
 
 /* ------------------------------------------------------------------------------------------
  * Grouped expert GEMM (tcgen05 + TMA + TMEM).
@@ -681,11 +693,13 @@ typedef struct hmc_mega_moe_args {
   float swiglu_limit;
   int32_t fuse_dispatch;              /* push with ep > 1: 1 = dispatch warps inside GEMM1 (default choice of the
                                          module), 0 = the stand-alone dispatch kernel first */
+  int32_t probs_before_fc2;           /* 1: the routing probabilities travel with the rows and weight the activation
+                                         (numerics.py:21-50 apply_probs_before_fc2); the same on every rank */
+  int32_t reserved;
   const int32_t* dispatch_src_index;  /* [routed_rows] flat (token * top_k + slot) of each expert-major row, or NULL */
   const int32_t* expert_of_row;       /* [routed_rows] global expert of each expert-major row */
   const int64_t* recv_segment_start;  /* [experts / ep * ep], from hmc_route_offsets */
-  const float* route_probs;           /* [seq * top_k]: set ONLY for "probabilities before FC2"; they then travel
-                                         with the rows and weight the activation */
+  const float* route_probs;           /* [seq * top_k], read with probs_before_fc2 (may be NULL on a rank without tokens) */
   float* row_probs;                   /* before FC2: where the received per-row probabilities are (push: the float
                                          plane of dispatch_target; pull: a caller tensor of received_rows floats) */
   const hmc_moe_transport* transport;
@@ -742,7 +756,7 @@ typedef struct hmc_mega_moe_grad_args {
   float swiglu_limit;
   int32_t fuse_dispatch;
   int32_t weight_grad_f32;            /* 1: hidden_dw / gate_dw are FP32 partial gradients (numerics.py:32-34) */
-  int32_t reserved;
+  int32_t probs_before_fc2;           /* as in hmc_mega_moe_args */
   const int32_t* dispatch_src_index;  /* before FC2 only */
   const int32_t* expert_of_row;
   const int64_t* recv_segment_start;
