@@ -147,33 +147,19 @@ def _peak_hbm():
     return 6650.0, "of fallback"
 
 
-def run_gpu(args, workload: str, clock_sampler_cls) -> None:
-    import torch.distributed as dist
-
+def measure(workload: str, rank: int, world: int, device, steps: int, warmup: int, *, barrier, tokens=None,
+            with_e2e: bool = True, max_over_ranks=None) -> dict:
+    """Time one side workload on this rank's device: device-resident steps, optionally the host-buffer
+    steps, and a per-stage breakdown (CUDA events on the launch stream). Returns plain numbers."""
     from hyper_multicore_b200 import MegaGate, MegaMhc, _lib, kernels
 
-    _lib.load()
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if world != args.gpus:
-        raise SystemExit(f"--gpus {args.gpus} needs WORLD_SIZE={args.gpus}; got {world}")
-    device = torch.device("cuda", local_rank)
-    torch.cuda.set_device(device)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=device)
-
-    def barrier() -> None:
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    if getattr(args, "tokens", None):
+    if tokens:
         # a smaller case of the same kernels (used for profiler captures)
         if workload == "gate":
-            GATE["text"], GATE["vision"] = args.tokens * 3 // 4, args.tokens - args.tokens * 3 // 4
+            GATE["text"], GATE["vision"] = tokens * 3 // 4, tokens - tokens * 3 // 4
         else:
-            MHC["tokens"] = args.tokens
+            MHC["tokens"] = tokens
+    reduce_max = max_over_ranks or (lambda value: value)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=device) if workload == "gate" else None
     stages: dict[str, list] = {}
 
@@ -225,10 +211,7 @@ def run_gpu(args, workload: str, clock_sampler_cls) -> None:
         d2h = sum(t.numel() * t.element_size() for t in outs_h)
         t, h, e, k = tokens, GATE["hidden"], GATE["experts"], GATE["top_k"]
         algorithmic_bytes = t * h * 2 + e * h * 4 + t * e * 4 + t * k * 4 + t * k * 8 + e * 4 + t * k * 4
-        kernel_note = "gate_split_parts_kernel + gate_project_promoted_kernel (tcgen05) + gate_route_kernel + 3 sort kernels"
-        # DRAM bytes of the projection, split and route kernels of one step at the default size, from the ncu
-        # capture summarised in profiles/gate_kernels_bench_gate.md
-        traffic = 75.7e6 if not getattr(args, "tokens", None) else None
+        kernel_note = "gate_project_promoted_kernel (tcgen05) + gate_route_kernel + sort kernels"
         dtype = "f32 (bf16 activations, int32/int64 indices)"
     else:
         tokens, hidden = MHC["tokens"], MHC["hidden"]
@@ -240,10 +223,13 @@ def run_gpu(args, workload: str, clock_sampler_cls) -> None:
             module.bias.copy_(inputs[7])
             module.norm_weight.copy_(inputs[8])
         acts_d = [t.detach().requires_grad_(True) for t in inputs[:5]]
-        acts_h = [t.detach().cpu().pin_memory() for t in inputs[:5]]
-        grads_h = [g.cpu().pin_memory() for g in grads]
-        outs_h = [torch.empty_like(t) for t in acts_h] + [torch.empty(tokens, hidden, dtype=torch.bfloat16).pin_memory(),
-                                                          torch.empty(tokens, 4, hidden, dtype=torch.bfloat16).pin_memory()]
+        if with_e2e:
+            acts_h = [t.detach().cpu().pin_memory() for t in inputs[:5]]
+            grads_h = [g.cpu().pin_memory() for g in grads]
+            outs_h = [torch.empty_like(t) for t in acts_h] + [torch.empty(tokens, hidden, dtype=torch.bfloat16).pin_memory(),
+                                                              torch.empty(tokens, 4, hidden, dtype=torch.bfloat16).pin_memory()]
+        else:
+            acts_h, grads_h, outs_h = [], [], []
 
         def run(acts, upstream):
             for p in module.parameters():
@@ -274,18 +260,17 @@ def run_gpu(args, workload: str, clock_sampler_cls) -> None:
         # previous_output; write grad_residual (4TH), grad_previous_output.
         algorithmic_bytes = (4 + 1 + 4 + 1 + 1) * th + (12 + 3 + 4 + 1) * th
         kernel_note = "mhc_post_kernel, mhc_mapping_kernel, mhc_mapping_grad_kernel, mhc_stream_grad_kernel + 3 tcgen05 contractions"
-        traffic = None
         dtype = "f32 math on bf16 activations"
 
-    def timed(step, steps, warmup):
-        for _ in range(warmup):
+    def timed(step, count, warm):
+        for _ in range(warm):
             step()
         barrier()
         if flush is not None:
             # per-step events so that the L2 flush between steps stays outside the measured time
             pairs = []
             launches_before = _lib.launch_count()
-            for _ in range(steps):
+            for _ in range(count):
                 flush.zero_()
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record()
@@ -298,25 +283,18 @@ def run_gpu(args, workload: str, clock_sampler_cls) -> None:
             start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             launches_before = _lib.launch_count()
             start.record()
-            for _ in range(steps):
+            for _ in range(count):
                 step()
             stop.record()
             barrier()
             total = start.elapsed_time(stop)
-        ms = torch.tensor([total], device=device)
-        if world > 1:
-            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-        return float(ms.item()), _lib.launch_count() - launches_before
+        return reduce_max(total), _lib.launch_count() - launches_before
 
-    sampler = clock_sampler_cls(local_rank)
-    if rank == 0:
-        sampler.start()
-    total_ms, launches = timed(step_resident, args.steps, args.warmup)
-    clocks = sampler.stop() if rank == 0 else None
-    e2e_ms, _ = timed(step_host, args.steps, 3)
+    total_ms, launches = timed(step_resident, steps, warmup)
+    e2e_ms = timed(step_host, steps, 3)[0] if with_e2e else None
 
     collecting[0] = True
-    profile_steps = min(args.steps, 5)
+    profile_steps = min(steps, 5)
     for _ in range(profile_steps):
         if flush is not None:
             flush.zero_()
@@ -324,25 +302,66 @@ def run_gpu(args, workload: str, clock_sampler_cls) -> None:
     barrier()
     collecting[0] = False
     stage_ms = {name: sum(a.elapsed_time(b) for a, b in pairs) / profile_steps for name, pairs in stages.items()}
+    return {"tokens": tokens, "ms_per_step": total_ms / steps, "launches": launches,
+            "e2e_ms_per_step": e2e_ms / steps if e2e_ms is not None else None, "h2d": h2d, "d2h": d2h,
+            "algorithmic_bytes": algorithmic_bytes, "kernel_note": kernel_note, "dtype": dtype, "stage_ms": stage_ms}
 
+
+def run_gpu(args, workload: str, clock_sampler_cls) -> None:
+    import torch.distributed as dist
+
+    from hyper_multicore_b200 import _lib
+
+    _lib.load()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} needs WORLD_SIZE={args.gpus}; got {world}")
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+
+    def barrier() -> None:
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(value: float) -> float:
+        if world == 1:
+            return value
+        ms = torch.tensor([value], device=device)
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    sampler = clock_sampler_cls(local_rank)
+    if rank == 0:
+        sampler.start()
+    result = measure(workload, rank, world, device, args.steps, args.warmup, barrier=barrier,
+                     tokens=getattr(args, "tokens", None), max_over_ranks=max_over_ranks)
+    clocks = sampler.stop() if rank == 0 else None
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
         return
     peak, note = _peak_hbm()
-    ms_per_step = total_ms / args.steps
-    achieved = algorithmic_bytes / (ms_per_step * 1e-3) / 1e9
+    tokens, ms_per_step = result["tokens"], result["ms_per_step"]
+    achieved = result["algorithmic_bytes"] / (ms_per_step * 1e-3) / 1e9
     line = {
         "metric": f"{workload}_tokens_per_s", "value": world * tokens / (ms_per_step * 1e-3), "unit": "tokens/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
-        "higher_is_better": True, "scaling": "weak (independent replicas)", "vs_baseline": None, "dtype": dtype,
+        "higher_is_better": True, "scaling": "weak (independent replicas)", "vs_baseline": None, "dtype": result["dtype"],
         "data": "synthetic", "config": workload_config(workload), "clocks": clocks,
-        "e2e": {"value": world * tokens / (e2e_ms / args.steps * 1e-3), "unit": "tokens/s",
-                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / args.steps},
-        "gpu_launches": launches,
-        "roofline": {"bound": "hbm", "kernel": kernel_note, "achieved": achieved, "peak": peak, "unit": "GB/s",
-                     "frac": achieved / peak, "peak_source": note, "traffic": traffic,
-                     "algorithmic_bytes_per_step": algorithmic_bytes, "stage_ms": stage_ms},
+        "e2e": {"value": world * tokens / (result["e2e_ms_per_step"] * 1e-3), "unit": "tokens/s",
+                "h2d_bytes_per_step": result["h2d"], "d2h_bytes_per_step": result["d2h"],
+                "ms_per_step": result["e2e_ms_per_step"]},
+        "gpu_launches": result["launches"],
+        "roofline": {"bound": "hbm", "kernel": result["kernel_note"], "achieved": achieved, "peak": peak, "unit": "GB/s",
+                     "frac": achieved / peak, "peak_source": note,
+                     "traffic": result["algorithmic_bytes"],
+                     "traffic_note": "algorithmic bytes per step",
+                     "algorithmic_bytes_per_step": result["algorithmic_bytes"], "stage_ms": result["stage_ms"]},
     }
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_leg(workload, budget_s=20.0)

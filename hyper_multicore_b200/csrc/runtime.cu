@@ -21,9 +21,27 @@ static std::atomic<int> g_profile_on{0};
 static std::mutex g_profile_mutex;
 static std::vector<ProfileRecord> g_profile_records;
 
+// Events are created when profiling is switched on, not inside the measured call sequence: creating one
+// costs the host microseconds the GPU would spend idle between two launches.
+static std::vector<cudaEvent_t> g_profile_pool;
+
+static cudaEvent_t take_event() {
+  {
+    std::lock_guard<std::mutex> lock(g_profile_mutex);
+    if (!g_profile_pool.empty()) {
+      cudaEvent_t e = g_profile_pool.back();
+      g_profile_pool.pop_back();
+      return e;
+    }
+  }
+  cudaEvent_t e = nullptr;
+  return cudaEventCreate(&e) == cudaSuccess ? e : nullptr;
+}
+
 ProfileScope::ProfileScope(int kind, cudaStream_t stream) : kind_(kind), stream_(stream), start_(nullptr), active_(false) {
   if (g_profile_on.load(std::memory_order_relaxed) == 0) return;
-  if (cudaEventCreate(&start_) != cudaSuccess) return;
+  start_ = take_event();
+  if (start_ == nullptr) return;
   if (cudaEventRecord(start_, stream_) != cudaSuccess) {
     cudaEventDestroy(start_);
     return;
@@ -33,8 +51,8 @@ ProfileScope::ProfileScope(int kind, cudaStream_t stream) : kind_(kind), stream_
 
 ProfileScope::~ProfileScope() {
   if (!active_) return;
-  cudaEvent_t stop = nullptr;
-  if (cudaEventCreate(&stop) != cudaSuccess || cudaEventRecord(stop, stream_) != cudaSuccess) {
+  cudaEvent_t stop = take_event();
+  if (stop == nullptr || cudaEventRecord(stop, stream_) != cudaSuccess) {
     cudaEventDestroy(start_);
     if (stop != nullptr) cudaEventDestroy(stop);
     return;
@@ -73,7 +91,16 @@ extern "C" int hmc_worker_queue_layout_version(void) { return 2; }
 extern "C" int64_t hmc_launch_count(void) { return hmc::g_launches.load(std::memory_order_relaxed); }
 
 extern "C" int hmc_profile_enable(int on) {
-  hmc::g_profile_on.store(on ? 1 : 0, std::memory_order_relaxed);
+  using namespace hmc;
+  if (on) {
+    std::lock_guard<std::mutex> lock(g_profile_mutex);
+    while (g_profile_pool.size() < 1024) {
+      cudaEvent_t e = nullptr;
+      if (cudaEventCreate(&e) != cudaSuccess) break;
+      g_profile_pool.push_back(e);
+    }
+  }
+  g_profile_on.store(on ? 1 : 0, std::memory_order_relaxed);
   return 0;
 }
 
@@ -99,8 +126,9 @@ extern "C" int hmc_profile_collect(double* ms_by_kind, int64_t* calls_by_kind, i
       ms_by_kind[r.kind] += ms;
       calls_by_kind[r.kind] += 1;
     }
-    cudaEventDestroy(r.start);
-    cudaEventDestroy(r.stop);
+    std::lock_guard<std::mutex> lock(g_profile_mutex);
+    g_profile_pool.push_back(r.start);
+    g_profile_pool.push_back(r.stop);
   }
   if (rc != 0) set_error("hmc_profile_collect: an event could not be read");
   return rc;

@@ -34,10 +34,10 @@ def run_module(case, dev, layout="EIO", numerics=None):
             "grad_w1": grad_w1.cpu(), "grad_w2": grad_w2.cpu()}, module
 
 
-def check(got, ref):
+def check(got, ref, **allowance):
     """The reference's tolerance with the one documented allowance (oracle/compare.py)."""
     for name in ("output", "grad_hidden", "grad_probs", "grad_w1", "grad_w2"):
-        compare.check(name, got[name], ref[name])
+        compare.check(name, got[name], ref[name], **allowance)
 
 
 @pytest.mark.parametrize("layout", ["EIO", "EOI"])
@@ -104,7 +104,9 @@ def test_numerics_options(cuda_device, limit, after_silu, before_fc2, layout):
     if limit is not None:
         assert (ref["output"].float() - plain["output"].float()).abs().max() > 0.2, "the clamp must matter here"
     got, module = run_module(case, cuda_device, layout, numerics=MegaMoeNumericsOptions(**options))
-    check(got, ref)
+    # five times larger weights: dX terms of several units, whose BF16 ulp (0.03) is ten times the absolute
+    # tolerance, so more sums that cancel miss it (seen: 21 to 41 of 76800 elements, worst 2.0 x the bound)
+    check(got, ref, stray_fraction=1e-3)
     assert module.swiglu_limit == limit and module.clamp_after_silu == after_silu
     assert module.apply_probs_before_fc2 == before_fc2
     assert (got["grad_w1"][2] == 0).all() and (got["grad_w2"][2] == 0).all()
