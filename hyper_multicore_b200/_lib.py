@@ -27,7 +27,7 @@ HMC_STATUS_WORDS = 8
 HMC_CTRL_SOURCE = 1296
 HMC_CTRL_COUNTS = 1552
 HMC_CLAMP_NONE, HMC_CLAMP_BEFORE_SILU, HMC_CLAMP_AFTER_SILU = 0, 1, 2
-HMC_PROFILE_KINDS = ("grouped_gemm", "mx_gemm", "mx_quant", "ep")
+HMC_PROFILE_KINDS = ("grouped_gemm", "mx_gemm", "mx_quant", "ep", "route")
 HMC_MOE_LAYOUT = {"EIO": 0, "EOI": 1}
 HMC_MOE_DISPATCH = {"push": 0, "pull": 1}
 
@@ -85,6 +85,7 @@ class GroupedGemmArgs(ctypes.Structure):
         ("combine", c_void_p),
         ("pipe_budget_ns", c_uint64),
         ("dispatch", c_void_p),
+        ("skip_flag", c_void_p),
     ]
 
 
@@ -163,7 +164,7 @@ class EpDispatchArgs(ctypes.Structure):
         ("peer_buffers", c_void_p), ("peer_ctrl", c_void_p), ("local_ctrl", c_void_p),
         ("generation", c_int32), ("max_ctas", c_int32), ("budget_ns", c_uint64), ("status", c_void_p),
         ("row_values", c_void_p), ("value_index", c_void_p), ("value_plane_offset", c_int64),
-        ("rank", c_int64),
+        ("rank", c_int64), ("send_order_start", c_void_p), ("skip_flag", c_void_p),
     ]
 
 
@@ -253,10 +254,10 @@ class MegaMoeArgs(ctypes.Structure):
         ("received_rows", c_int64), ("weight_layout", c_int32), ("swiglu_clamp", c_int32),
         ("swiglu_limit", c_float), ("fuse_dispatch", c_int32), ("probs_before_fc2", c_int32), ("reserved", c_int32),
         ("dispatch_src_index", c_void_p),
-        ("expert_of_row", c_void_p), ("recv_segment_start", c_void_p), ("route_probs", c_void_p),
+        ("expert_of_row", c_void_p), ("recv_segment_start", c_void_p), ("send_order_start", c_void_p), ("route_probs", c_void_p),
         ("row_probs", c_void_p), ("transport", c_void_p), ("saved_dispatch", c_void_p),
         ("saved_combine", c_void_p), ("saved_row_probs", c_void_p), ("mapping", c_void_p),
-        ("topk_probs", c_void_p), ("output", c_void_p),
+        ("topk_probs", c_void_p), ("output", c_void_p), ("skip_flag", c_void_p),
     ]
 
 
@@ -275,7 +276,7 @@ class MegaMoeGradArgs(ctypes.Structure):
         ("routed_rows", c_int64), ("received_rows", c_int64), ("weight_layout", c_int32),
         ("swiglu_clamp", c_int32), ("swiglu_limit", c_float), ("fuse_dispatch", c_int32),
         ("weight_grad_f32", c_int32), ("probs_before_fc2", c_int32), ("dispatch_src_index", c_void_p),
-        ("expert_of_row", c_void_p), ("recv_segment_start", c_void_p), ("row_probs", c_void_p),
+        ("expert_of_row", c_void_p), ("recv_segment_start", c_void_p), ("send_order_start", c_void_p), ("row_probs", c_void_p),
         ("row_dot", c_void_p), ("transport", c_void_p), ("grad_output", c_void_p), ("saved_combine", c_void_p),
         ("mapping", c_void_p), ("topk_probs", c_void_p), ("grad_probs", c_void_p), ("grad_hidden", c_void_p),
     ]
@@ -346,6 +347,7 @@ SIGNATURES: dict[str, tuple] = {
     "hmc_launch_count": (_L, []),
     "hmc_profile_enable": (_I, [_I]),
     "hmc_profile_collect": (_I, [ctypes.POINTER(c_double), ctypes.POINTER(c_int64), _I]),
+    "hmc_profile_dump": (_I, [ctypes.POINTER(c_int32), ctypes.POINTER(c_double), ctypes.POINTER(c_double), _I]),
     "hmc_grouped_gemm": (_I, [ctypes.POINTER(GroupedGemmArgs), _P]),
     "hmc_grouped_gemm_combine_units": (_L, [_L]),
     "hmc_mx_gemm": (_I, [ctypes.POINTER(MxGemmArgs), _P]),
@@ -370,7 +372,7 @@ SIGNATURES: dict[str, tuple] = {
     "hmc_moe_unpermute_grad": (_I, [_P, _P, _P, _P, _L, _L, _L, _P, _P, _P, _P]),
     "hmc_moe_token_permute_grad": (_I, [_P, _P, _L, _L, _L, _P, _P, _P]),
     "hmc_zero_empty_expert_grad": (_I, [_P, _L, _P, _L, _P, _L, _P]),
-    "hmc_route_offsets": (_I, [_P, _L, _L, _L, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
+    "hmc_route_offsets": (_I, [_P, _L, _L, _L, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
     "hmc_symm_alloc": (_I, [_L, ctypes.POINTER(c_void_p)]),
     "hmc_symm_free": (_I, [_P]),
     "hmc_ipc_get_handle": (_I, [_P, _P]),
@@ -385,6 +387,8 @@ SIGNATURES: dict[str, tuple] = {
     "hmc_ep_dispatch": (_I, [ctypes.POINTER(EpDispatchArgs), _P]),
     "hmc_ep_combine": (_I, [ctypes.POINTER(EpCombineArgs), _P]),
     "hmc_ep_wait": (_I, [_P, _I, c_uint64, _P, _P]),
+    "hmc_ep_wait_unless": (_I, [_P, _I, c_uint64, _P, _P, _P]),
+    "hmc_route_guard": (_I, [_P, _L, _L, _L, _L, _P, _P, _P, _P]),
     "hmc_ep_wait_groups": (_I, [_P, _P, _L, c_uint64, _P, _P]),
     "hmc_mega_mhc_workspace_bytes": (_L, [_L, _L]),
     "hmc_mega_mhc_grad_workspace_bytes": (_L, [_L, _L]),

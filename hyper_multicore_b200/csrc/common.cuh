@@ -60,6 +60,9 @@ struct ProfileScope {
 };
 
 int sm_count();  // number of SMs on the current device (cached per device)
+int moe_unpermute_unless(const void* permuted, const int32_t* mapping, const float* probs, int64_t num_tokens,
+                         int64_t top_k, int64_t hidden, int64_t permuted_rows, void* out, int32_t* status,
+                         const int32_t* skip_flag, void* stream);  // route_prep.cu
 
 // cudaFuncAttributeMaxDynamicSharedMemorySize belongs to a (kernel, device) pair: every launch site keeps one
 // PerDeviceFlag and raises the limit the first time it launches on each device ordinal.

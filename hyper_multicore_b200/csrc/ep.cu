@@ -60,10 +60,11 @@ ep_dispatch_kernel(const uint4* __restrict__ tokens, const int* __restrict__ sou
                    int ep, int local_experts, long long capacity_rows, PeerTable peers,
                    const int* __restrict__ local_ctrl, int generation, unsigned long long budget_ns,
                    int* __restrict__ status, const float* __restrict__ row_values,
-                   const int* __restrict__ value_index, long long value_plane_offset) {
+                   const int* __restrict__ value_index, long long value_plane_offset, const int* __restrict__ skip_flag) {
   __shared__ int seen[HMC_MAX_EP];
   __shared__ int chunk_expert[ROWS_PER_CHUNK];
   __shared__ int failed;
+  if (skip_flag != nullptr && *reinterpret_cast<const volatile int*>(skip_flag) != 0) return;
   if (threadIdx.x < HMC_MAX_EP) seen[threadIdx.x] = -1;
   if (threadIdx.x == 0) failed = 0;
   __syncthreads();
@@ -309,7 +310,9 @@ ep_pull_kernel(PeerTable sources, const long long* __restrict__ source_row_off,
   }
 }
 
-__global__ void ep_wait_kernel(const int* counter, int expected, unsigned long long budget_ns, int* status) {
+__global__ void ep_wait_kernel(const int* counter, int expected, unsigned long long budget_ns, int* status,
+                               const int* skip_flag) {
+  if (skip_flag != nullptr && *reinterpret_cast<const volatile int*>(skip_flag) != 0) return;
   int seen = 0;
   if (!wait_counter_ge(counter, expected, budget_ns, &seen))
     report_status(status, HMC_STATUS_TIMEOUT_ARRIVAL, -1, expected, seen);
@@ -370,6 +373,7 @@ int fill_dispatch(DispatchFuse* out, const hmc_ep_dispatch_args& a, const char* 
   out->expert_of_row = a.expert_of_row;
   out->dispatch_src_off = reinterpret_cast<const long long*>(a.dispatch_src_off);
   out->dispatch_target_off = reinterpret_cast<const long long*>(a.dispatch_target_off);
+  out->send_order_start = reinterpret_cast<const long long*>(a.send_order_start);
   out->rows = a.rows;
   out->capacity_rows = a.capacity_rows;
   out->local_ctrl = a.local_ctrl;
@@ -385,6 +389,7 @@ int fill_dispatch(DispatchFuse* out, const hmc_ep_dispatch_args& a, const char* 
   out->generation = a.generation;
   return 0;
 }
+
 
 }  // namespace hmc
 
@@ -443,6 +448,7 @@ extern "C" int64_t hmc_ep_exchange_table_bytes(int64_t ep, int64_t experts) {
 extern "C" int hmc_ep_exchange_counts(const hmc_ep_exchange_args* args, void* stream_ptr) {
   HMC_REQUIRE(args != nullptr, HMC_ERR_INVALID, "hmc_ep_exchange_counts: null args");
   const hmc_ep_exchange_args& a = *args;
+  ProfileScope profile(HMC_PROFILE_EP, static_cast<cudaStream_t>(stream_ptr));
   PeerTable table;
   int rc = fill_peers(&table, a.peer_tables, a.peer_ctrl, a.ep);
   if (rc != 0) return rc;
@@ -530,7 +536,7 @@ extern "C" int hmc_ep_dispatch(const hmc_ep_dispatch_args* args, void* stream_pt
       a.rows, static_cast<int>(a.top_k), static_cast<int>(a.hidden / 8), static_cast<int>(a.ep),
       static_cast<int>(a.local_experts), a.capacity_rows, table, a.local_ctrl, a.generation,
       a.budget_ns ? a.budget_ns : 10ull * 1000 * 1000 * 1000, a.status, a.row_values, a.value_index,
-      a.value_plane_offset);
+      a.value_plane_offset, a.skip_flag);
   HMC_LAUNCH_OK();
   return 0;
 }
@@ -566,12 +572,66 @@ extern "C" int hmc_ep_combine(const hmc_ep_combine_args* args, void* stream_ptr)
   return 0;
 }
 
-extern "C" int hmc_ep_wait(const int32_t* counter, int32_t expected, uint64_t budget_ns, int32_t* status,
-                           void* stream_ptr) {
+extern "C" int hmc_ep_wait_unless(const int32_t* counter, int32_t expected, uint64_t budget_ns, int32_t* status,
+                                  const int32_t* skip_flag, void* stream_ptr) {
   HMC_REQUIRE(counter != nullptr, HMC_ERR_INVALID, "hmc_ep_wait: null counter");
   ProfileScope profile(HMC_PROFILE_EP, static_cast<cudaStream_t>(stream_ptr));
   ep_wait_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream_ptr)>>>(
-      counter, expected, budget_ns ? budget_ns : 10ull * 1000 * 1000 * 1000, status);
+      counter, expected, budget_ns ? budget_ns : 10ull * 1000 * 1000 * 1000, status, skip_flag);
+  HMC_LAUNCH_OK();
+  return 0;
+}
+
+extern "C" int hmc_ep_wait(const int32_t* counter, int32_t expected, uint64_t budget_ns, int32_t* status,
+                           void* stream_ptr) {
+  return hmc_ep_wait_unless(counter, expected, budget_ns, status, nullptr, stream_ptr);
+}
+
+namespace hmc {
+namespace {
+// One CTA. Threads r < ep add up what rank r receives and what it routes; any excess, or any rank's
+// "invalid" header word, sets the flag. Then the table, the status words and the flag go to the host mirror.
+__global__ void __launch_bounds__(256)
+route_guard_kernel(const int* __restrict__ table, int ep, int experts, long long capacity_rows, long long routed_limit,
+                   const int* __restrict__ status_words, int* __restrict__ skip_flag, int* __restrict__ host_mirror) {
+  __shared__ int flag;
+  if (threadIdx.x == 0) flag = 0;
+  __syncthreads();
+  const int local = experts / ep;
+  const int* header = table + static_cast<long long>(ep) * experts;
+  for (int r = threadIdx.x; r < ep; r += blockDim.x) {
+    long long received = 0, routed = 0;
+    for (int s = 0; s < ep; ++s)
+      for (int le = 0; le < local; ++le) received += table[static_cast<long long>(s) * experts + r * local + le];
+    for (int e = 0; e < experts; ++e) routed += table[static_cast<long long>(r) * experts + e];
+    if (received > capacity_rows || routed > routed_limit || header[r * 4] != 0) atomicOr(&flag, 1);
+  }
+  __syncthreads();
+  const int value = flag;
+  if (threadIdx.x == 0) *skip_flag = value;
+  if (host_mirror != nullptr) {
+    const int table_words = ep * (experts + 4);
+    for (int i = threadIdx.x; i < table_words; i += blockDim.x) host_mirror[i] = table[i];
+    if (threadIdx.x < HMC_STATUS_WORDS)
+      host_mirror[table_words + threadIdx.x] = status_words != nullptr ? status_words[threadIdx.x] : 0;
+    if (threadIdx.x == 0) host_mirror[table_words + HMC_STATUS_WORDS] = value;
+    __threadfence_system();
+  }
+}
+}  // namespace
+}  // namespace hmc
+
+extern "C" int hmc_route_guard(const int32_t* table, int64_t ep, int64_t experts, int64_t capacity_rows,
+                               int64_t routed_limit, const int32_t* status_words, int32_t* skip_flag,
+                               int32_t* host_mirror, void* stream_ptr) {
+  HMC_REQUIRE(table != nullptr && skip_flag != nullptr, HMC_ERR_INVALID, "hmc_route_guard: null tensor pointer");
+  HMC_REQUIRE(ep >= 1 && ep <= HMC_MAX_EP && experts > 0 && experts % ep == 0 && experts <= 65536, HMC_ERR_INVALID,
+              "hmc_route_guard: experts (%lld) must be a positive multiple of ep (%lld)", (long long)experts, (long long)ep);
+  HMC_REQUIRE(capacity_rows >= 0 && routed_limit >= 0, HMC_ERR_INVALID, "hmc_route_guard: negative limits");
+  ProfileScope profile(HMC_PROFILE_EP, static_cast<cudaStream_t>(stream_ptr));
+  hmc::route_guard_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream_ptr)>>>(
+      table, static_cast<int>(ep), static_cast<int>(experts), capacity_rows, routed_limit, status_words, skip_flag,
+      host_mirror);
   HMC_LAUNCH_OK();
   return 0;
 }

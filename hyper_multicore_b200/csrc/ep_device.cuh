@@ -19,6 +19,7 @@ struct DispatchFuse {
   const int* expert_of_row;             // global expert of each expert-major row
   const long long* dispatch_src_off;    // [experts] first source row of each expert
   const long long* dispatch_target_off; // [experts] first row of this rank's segment on the owner
+  const long long* send_order_start;    // [experts + 1] prefix of the segments in sending order, or null
   long long rows;
   long long capacity_rows;
   void* peer_data[HMC_MAX_EP];          // receive buffer of every rank
@@ -38,20 +39,20 @@ struct DispatchFuse {
 
 #ifdef __CUDACC__
 
-constexpr int DISPATCH_WARP_ROWS = 8;  // rows one warp sends between two counter updates
+// Rows one warp sends between two counter updates. Small on purpose: the first tile of the carrying GEMM
+// cannot start before one whole round of groups has been sent, and that round lasts as long as one warp
+// needs for its group.
+constexpr int DISPATCH_WARP_ROWS = 2;
 
 // One warp sends its share of the rows: worker `worker` of `workers` takes every workers-th group of
-// DISPATCH_WARP_ROWS rows. Rows are visited in rank-rotated order: first those owned by rank + 1, then
-// rank + 2, ..., this rank's own last, so that every owner's early experts fill first and remote
-// transfers start before local copies. After each group one release-add per run of equal experts
+// DISPATCH_WARP_ROWS rows of the sending order (send_order_start: local expert 0 of every destination,
+// remote destinations first, then local expert 1, ...), so that every owner's early experts are complete
+// early and their tiles overlap the rest of the transfer. After each group one release-add per expert
 // advances the owners' arrival counters. Returns false when a peer never became ready (status set).
 __device__ __forceinline__ bool dispatch_rows_warp(const DispatchFuse& d, int worker, int workers, int lane,
                                                    int* status) {
   if (d.rows <= 0) return true;
   const int experts = d.ep * d.local_experts;
-  long long start = 0;
-  if (d.ep > 1) start = d.dispatch_src_off[((d.rank + 1) % d.ep) * d.local_experts];
-  if (start >= d.rows) start = 0;
   unsigned ready_mask = 0;  // peers seen ready for this generation (warp-uniform)
   const long long groups = (d.rows + DISPATCH_WARP_ROWS - 1) / DISPATCH_WARP_ROWS;
   for (long long group = worker; group < groups; group += workers) {
@@ -61,9 +62,19 @@ __device__ __forceinline__ bool dispatch_rows_warp(const DispatchFuse& d, int wo
     int e = -1;
     long long j = 0, dest_row = 0, src_row = 0;
     if (lane < count) {
-      j = start + i0 + lane;
-      if (j >= d.rows) j -= d.rows;
-      e = d.expert_of_row[j];
+      j = i0 + lane;
+      if (d.send_order_start != nullptr) {
+        // position j of the sending order lies in segment q = le * ep + dd: the last q whose start is <= j
+        int lo = 0, hi = experts - 1;
+        while (lo < hi) {
+          const int mid = (lo + hi + 1) >> 1;
+          if (d.send_order_start[mid] <= j) lo = mid; else hi = mid - 1;
+        }
+        const int owner_of = (d.rank + 1 + lo % d.ep) % d.ep;
+        const int segment_expert = owner_of * d.local_experts + lo / d.ep;
+        j = d.dispatch_src_off[segment_expert] + (j - d.send_order_start[lo]);
+      }
+      e = (j >= 0 && j < d.rows) ? d.expert_of_row[j] : -1;
       if (e < 0 || e >= experts) {
         report_status(status, HMC_STATUS_BAD_INDEX, static_cast<int>(j), e, 0);
         e = -1;
@@ -109,15 +120,19 @@ __device__ __forceinline__ bool dispatch_rows_warp(const DispatchFuse& d, int wo
       const uint4* src = d.tokens + sr * d.vec_per_row;
       uint4* dst = static_cast<uint4*>(d.peer_data[o]) + dr * d.vec_per_row;
       int v = lane;
-      for (; v + 96 < d.vec_per_row; v += 128) {  // four loads in flight per lane
-        const uint4 q0 = ld_nc_16(src + v);
-        const uint4 q1 = ld_nc_16(src + v + 32);
-        const uint4 q2 = ld_nc_16(src + v + 64);
-        const uint4 q3 = ld_nc_16(src + v + 96);
-        st_16(dst + v, q0);
-        st_16(dst + v + 32, q1);
-        st_16(dst + v + 64, q2);
-        st_16(dst + v + 96, q3);
+      for (; v + 224 < d.vec_per_row; v += 256) {  // eight loads in flight per lane
+        uint4 q[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) q[u] = ld_nc_16(src + v + 32 * u);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) st_16(dst + v + 32 * u, q[u]);
+      }
+      for (; v + 96 < d.vec_per_row; v += 128) {
+        uint4 q[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) q[u] = ld_nc_16(src + v + 32 * u);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) st_16(dst + v + 32 * u, q[u]);
       }
       for (; v < d.vec_per_row; v += 32) st_16(dst + v, ld_nc_16(src + v));
     }

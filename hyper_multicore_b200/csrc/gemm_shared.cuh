@@ -58,7 +58,12 @@ struct Params {
   float* row_dot;          // SWIGLU_GRAD with row_probs: per-row probability gradient (atomic adds)
   int dispatch_enabled;    // extra warps of this kernel send this rank's rows to their owners (RAGGED_M, gated)
   DispatchFuse dispatch;
+  const int* skip_flag;    // optional: a non-zero value turns the launch into a no-op
 };
+
+__device__ __forceinline__ bool launch_skipped(const Params& p) {
+  return p.skip_flag != nullptr && *reinterpret_cast<const volatile int*>(p.skip_flag) != 0;
+}
 
 struct Tile {
   int group;
@@ -79,7 +84,10 @@ struct TileWalkerT {
   long long row1 = 0;
   int tiles_in_group = 0;
 
-  __device__ explicit TileWalkerT(const Params& params) : p(params) { load_group(); }
+  __device__ explicit TileWalkerT(const Params& params) : p(params) {
+    if (p.skip_flag != nullptr && *reinterpret_cast<const volatile int*>(p.skip_flag) != 0) group = p.groups;  // no tiles
+    load_group();
+  }
 
   __device__ void load_group() {
     if (group >= p.groups) {

@@ -223,7 +223,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     }
   } else if (DISPATCH_WARPS > 0 && warp >= 2 + EPI_WARPS) {
     // ======================================================================== dispatch warps
-    if (p.dispatch_enabled)
+    if (p.dispatch_enabled && !launch_skipped(p))
       dispatch_rows_warp(p.dispatch, static_cast<int>(blockIdx.x) * DISPATCH_WARPS + (warp - 2 - EPI_WARPS),
                          static_cast<int>(gridDim.x) * DISPATCH_WARPS, lane, p.status);
   } else {
@@ -479,6 +479,7 @@ extern "C" int hmc_grouped_gemm(const hmc_grouped_gemm_args* args, void* stream_
   // it get that time on top of their own, so that a slow peer never shows up as a pipeline time-out.
   p.pipe_budget_ns = (a.pipe_budget_ns ? a.pipe_budget_ns : PIPE_BUDGET_NS) + (a.ready_counters ? p.ready_budget_ns : 0);
   p.status = a.status;
+  p.skip_flag = a.skip_flag;
   p.n = static_cast<int>(a.n);
   {
     const bool swiglu_family = a.epilogue == HMC_EPI_SWIGLU || a.epilogue == HMC_EPI_SWIGLU_GRAD;

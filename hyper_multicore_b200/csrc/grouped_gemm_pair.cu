@@ -180,7 +180,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
     }
   } else if (DISPATCH_WARPS > 0 && warp >= 2 + EPI_WARPS) {
     // ======================================================================== dispatch warps (both CTAs)
-    if (p.dispatch_enabled)
+    if (p.dispatch_enabled && !launch_skipped(p))
       dispatch_rows_warp(p.dispatch, static_cast<int>(blockIdx.x) * DISPATCH_WARPS + (warp - 2 - EPI_WARPS),
                          static_cast<int>(gridDim.x) * DISPATCH_WARPS, lane, p.status);
   } else {

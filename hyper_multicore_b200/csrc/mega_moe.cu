@@ -150,7 +150,8 @@ hmc_gemm_combine make_combine(const hmc_moe_transport& t, const int64_t* segment
 
 hmc_ep_dispatch_args make_dispatch(const hmc_moe_transport& t, const void* src, const int32_t* src_index,
                                    const int32_t* expert_of_row, const int64_t* src_off, const int64_t* target_off,
-                                   const Shape& s, int32_t* ctrl, int32_t* status) {
+                                   const Shape& s, int32_t* ctrl, int32_t* status, const int64_t* send_order = nullptr,
+                                   const int32_t* skip_flag = nullptr) {
   hmc_ep_dispatch_args d;
   memset(&d, 0, sizeof(d));
   d.tokens = src;
@@ -171,6 +172,8 @@ hmc_ep_dispatch_args make_dispatch(const hmc_moe_transport& t, const void* src, 
   d.budget_ns = t.wait_budget_ns;
   d.status = status;
   d.rank = t.rank;
+  d.send_order_start = send_order;
+  d.skip_flag = skip_flag;
   return d;
 }
 
@@ -339,7 +342,7 @@ extern "C" int hmc_mega_moe(const hmc_mega_moe_args* args, void* stream_ptr) {
                         before_fc2 ? a.row_probs : nullptr, ctrl, status, stream));
     } else {
       dispatch = make_dispatch(t, a.dispatch_src, a.dispatch_src_index, a.expert_of_row, a.dispatch_src_off,
-                               a.dispatch_target_off, s, ctrl, status);
+                               a.dispatch_target_off, s, ctrl, status, a.send_order_start, a.skip_flag);
       if (before_fc2) {
         dispatch.row_values = a.route_probs;
         dispatch.value_index = a.dispatch_src_index;
@@ -364,6 +367,7 @@ extern "C" int hmc_mega_moe(const hmc_mega_moe_args* args, void* stream_ptr) {
     g.swiglu_limit = a.swiglu_limit;
     g.row_probs = row_probs;
     g.dispatch = fused_dispatch ? &dispatch : nullptr;
+    g.skip_flag = a.skip_flag;
     HMC_TRY(hmc_grouped_gemm(&g, stream));
   }
   if (!ep1 && !pull && a.saved_dispatch != nullptr && s.received > 0) {
@@ -380,18 +384,21 @@ extern "C" int hmc_mega_moe(const hmc_mega_moe_args* args, void* stream_ptr) {
       combine = make_combine(t, a.recv_segment_start, a.combine_target_off, s.local);
       g.combine = &combine;
     }
+    g.skip_flag = a.skip_flag;
     HMC_TRY(hmc_grouped_gemm(&g, stream));
   }
   const void* routed_rows_ptr = a.down_proj_y;
   if (!ep1) {
     // the result rows left the GEMM2 epilogue for their sources; wait for this rank's own
-    HMC_TRY(hmc_ep_wait(ctrl + HMC_CTRL_COMBINE,
-                        static_cast<int32_t>(s.routed * hmc_grouped_gemm_combine_units(s.hidden)), t.wait_budget_ns,
-                        status, stream));
+    HMC_TRY(hmc_ep_wait_unless(ctrl + HMC_CTRL_COMBINE,
+                               static_cast<int32_t>(s.routed * hmc_grouped_gemm_combine_units(s.hidden)),
+                               t.wait_budget_ns, status, a.skip_flag, stream));
     routed_rows_ptr = a.combine_target;
     if (a.saved_combine != nullptr || (before_fc2 && !pull && a.saved_row_probs != nullptr)) {
       HMC_TRY(copies.begin());
-      HMC_TRY(copies.copy(a.saved_combine, a.combine_target, static_cast<size_t>(s.routed) * s.hidden * 2));
+      // (a call that does not fit the workspace is a no-op on the device: copy no more than the buffer holds)
+      const int64_t held = s.routed < t.combine_rows_limit ? s.routed : t.combine_rows_limit;
+      HMC_TRY(copies.copy(a.saved_combine, a.combine_target, static_cast<size_t>(held) * s.hidden * 2));
       if (before_fc2 && !pull)
         HMC_TRY(copies.copy(a.saved_row_probs, a.row_probs, static_cast<size_t>(s.received) * sizeof(float)));
     }
@@ -399,8 +406,8 @@ extern "C" int hmc_mega_moe(const hmc_mega_moe_args* args, void* stream_ptr) {
   if (a.output != nullptr && s.tokens > 0) {
     // before FC2 the rows are already weighted: summed as they are (backends/bf16/autograd.py:133-135)
     const int64_t available = ep1 ? s.rows : t.combine_rows_limit;
-    HMC_TRY(hmc_moe_unpermute(routed_rows_ptr, a.mapping, before_fc2 ? nullptr : a.topk_probs, s.tokens, s.top_k,
-                              s.hidden, available, a.output, status, stream));
+    HMC_TRY(moe_unpermute_unless(routed_rows_ptr, a.mapping, before_fc2 ? nullptr : a.topk_probs, s.tokens, s.top_k,
+                                 s.hidden, available, a.output, status, a.skip_flag, stream));
   }
   return copies.end();
 }
@@ -459,7 +466,7 @@ extern "C" int hmc_mega_moe_grad(const hmc_mega_moe_grad_args* args, void* strea
       HMC_TRY(pull_rows(t, s, a.recv_segment_start, a.combine_target_off, a.dispatch_target, nullptr, ctrl, status, stream));
     } else {
       dispatch = make_dispatch(t, a.dy, a.dispatch_src_index, a.expert_of_row, a.dispatch_src_off, a.dispatch_target_off,
-                               s, ctrl, status);
+                               s, ctrl, status, a.send_order_start);
       HMC_REQUIRE(t.peer_dispatch[t.rank] == a.dispatch_target, HMC_ERR_INVALID,
                   "hmc_mega_moe_grad: dispatch_target must be this rank's entry of transport.peer_dispatch");
       fused_dispatch = a.fuse_dispatch != 0;
@@ -486,7 +493,7 @@ extern "C" int hmc_mega_moe_grad(const hmc_mega_moe_grad_args* args, void* strea
       HMC_REQUIRE(a.dispatch_target != nullptr, HMC_ERR_INVALID, "hmc_mega_moe_grad: dispatch_target is required");
       HMC_TRY(begin_call(t, ctrl, stream));
       dispatch = make_dispatch(t, a.dy, nullptr, a.expert_of_row, a.dispatch_src_off, a.dispatch_target_off, s, ctrl,
-                               status);
+                               status, a.send_order_start);
       HMC_REQUIRE(t.peer_dispatch[t.rank] == a.dispatch_target, HMC_ERR_INVALID,
                   "hmc_mega_moe_grad: dispatch_target must be this rank's entry of transport.peer_dispatch");
       fused_dispatch = a.fuse_dispatch != 0;

@@ -186,9 +186,10 @@ constexpr int MAX_TOP_K = 64;
 __global__ void __launch_bounds__(128)
 unpermute_kernel(const uint4* __restrict__ y, const int* __restrict__ mapping, const float* __restrict__ probs,
                  long long tokens, int top_k, int vec_per_row, long long y_rows, uint4* __restrict__ out,
-                 int* __restrict__ status) {
+                 int* __restrict__ status, const int* __restrict__ skip_flag) {
   __shared__ int rows[MAX_TOP_K];
   __shared__ float weight[MAX_TOP_K];
+  if (skip_flag != nullptr && *reinterpret_cast<const volatile int*>(skip_flag) != 0) return;  // uniform per launch
   const long long t = blockIdx.x;
   if (threadIdx.x == 0) {
     // insertion sort of the (row, weight) pairs by row; top_k is small
@@ -374,8 +375,24 @@ route_offsets_kernel(const int* __restrict__ counts, int ep, int experts, int ra
                      int* __restrict__ dispatch_size, long long* __restrict__ combine_src_off,
                      long long* __restrict__ combine_target_off, int* __restrict__ combine_size,
                      long long* __restrict__ group_list, long long* __restrict__ totals,
-                     long long* __restrict__ recv_segment_start) {
+                     long long* __restrict__ recv_segment_start, long long* __restrict__ send_order_start) {
   const int local = experts / ep;
+  if (threadIdx.x == 0 && send_order_start != nullptr) {
+    // Order in which this rank sends its rows when the dispatch rides inside the consuming GEMM: local
+    // expert 0 of every destination first (destinations rank + 1, rank + 2, ..., this rank last), then
+    // local expert 1, ... so that on every owner expert 0 completes after 1 / local of the transfer and
+    // its tiles run while the later experts' rows still travel. Entry q = le * ep + dd holds the first
+    // position of segment (destination (rank + 1 + dd) % ep, local expert le) in that order.
+    long long run = 0;
+    for (int le = 0; le < local; ++le) {
+      for (int dd = 0; dd < ep; ++dd) {
+        const int d = (rank + 1 + dd) % ep;
+        send_order_start[le * ep + dd] = run;
+        run += counts[rank * experts + d * local + le];
+      }
+    }
+    send_order_start[experts] = run;
+  }
   for (int s = threadIdx.x; s < ep; s += blockDim.x) {
     // source_prefix[s][e]: first row of expert e in source s's expert-major routed buffer
     long long run = 0;
@@ -439,6 +456,7 @@ extern "C" int64_t hmc_moe_sort_workspace_bytes(int64_t entries, int64_t experts
 
 extern "C" int hmc_moe_histogram(const void* indices, int indices_are_i64, int64_t entries, int64_t experts,
                                  int32_t* counts, int32_t* status, void* stream_ptr) {
+  ProfileScope profile(HMC_PROFILE_ROUTE, static_cast<cudaStream_t>(stream_ptr));
   HMC_REQUIRE(counts != nullptr && (entries == 0 || indices != nullptr), HMC_ERR_INVALID,
               "hmc_moe_histogram: null tensor pointer");
   HMC_REQUIRE(experts > 0 && experts <= 4096, HMC_ERR_LIMIT, "hmc_moe_histogram: experts must be in [1, 4096]");
@@ -458,6 +476,7 @@ extern "C" int hmc_moe_sort_routes(const void* indices, int indices_are_i64, int
                                    void* workspace, int64_t workspace_bytes, int32_t* mapping,
                                    int32_t* source_of_row, int32_t* expert_of_row, int32_t* counts,
                                    int64_t* cumulative, int32_t* status, void* stream_ptr) {
+  ProfileScope profile(HMC_PROFILE_ROUTE, static_cast<cudaStream_t>(stream_ptr));
   HMC_REQUIRE(experts > 0 && experts <= 4096, HMC_ERR_LIMIT, "hmc_moe_sort_routes: experts must be in [1, 4096]");
   HMC_REQUIRE(entries >= 0 && entries < (1ll << 31), HMC_ERR_LIMIT,
               "hmc_moe_sort_routes: tokens * top_k must fit in int32");
@@ -503,6 +522,7 @@ static int check_rows(const char* what, const void* a, const void* b, int64_t hi
 
 extern "C" int hmc_moe_gather_rows(const void* tokens, const int32_t* source_of_row, int64_t rows, int64_t top_k,
                                    int64_t hidden, void* out, void* stream_ptr) {
+  ProfileScope profile(HMC_PROFILE_ROUTE, static_cast<cudaStream_t>(stream_ptr));
   if (rows == 0) return 0;
   int rc = check_rows("hmc_moe_gather_rows", tokens, out, hidden);
   if (rc != 0) return rc;
@@ -518,6 +538,7 @@ extern "C" int hmc_moe_gather_rows(const void* tokens, const int32_t* source_of_
 extern "C" int hmc_moe_permute_from_mapping(const void* tokens, const int32_t* mapping, const float* probs,
                                             int64_t num_tokens, int64_t top_k, int64_t hidden, void* out,
                                             float* out_probs, int32_t* status, void* stream_ptr) {
+  ProfileScope profile(HMC_PROFILE_ROUTE, static_cast<cudaStream_t>(stream_ptr));
   if (num_tokens == 0) return 0;
   int rc = check_rows("hmc_moe_permute_from_mapping", tokens, out, hidden);
   if (rc != 0) return rc;
@@ -537,6 +558,15 @@ extern "C" int hmc_moe_permute_from_mapping(const void* tokens, const int32_t* m
 extern "C" int hmc_moe_unpermute(const void* permuted, const int32_t* mapping, const float* probs,
                                  int64_t num_tokens, int64_t top_k, int64_t hidden, int64_t permuted_rows,
                                  void* out, int32_t* status, void* stream_ptr) {
+  return hmc::moe_unpermute_unless(permuted, mapping, probs, num_tokens, top_k, hidden, permuted_rows, out, status, nullptr,
+                                   stream_ptr);
+}
+
+// hmc_moe_unpermute that does nothing when *skip_flag is non-zero on the device (used by hmc_mega_moe).
+int hmc::moe_unpermute_unless(const void* permuted, const int32_t* mapping, const float* probs, int64_t num_tokens,
+                              int64_t top_k, int64_t hidden, int64_t permuted_rows, void* out, int32_t* status,
+                              const int32_t* skip_flag, void* stream_ptr) {
+  ProfileScope profile(HMC_PROFILE_ROUTE, static_cast<cudaStream_t>(stream_ptr));
   if (num_tokens == 0) return 0;
   int rc = check_rows("hmc_moe_unpermute", permuted, out, hidden);
   if (rc != 0) return rc;
@@ -546,7 +576,7 @@ extern "C" int hmc_moe_unpermute(const void* permuted, const int32_t* mapping, c
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
   unpermute_kernel<<<static_cast<unsigned>(num_tokens), 128, 0, stream>>>(
       static_cast<const uint4*>(permuted), mapping, probs, num_tokens, static_cast<int>(top_k),
-      static_cast<int>(hidden / 8), permuted_rows, static_cast<uint4*>(out), status);
+      static_cast<int>(hidden / 8), permuted_rows, static_cast<uint4*>(out), status, skip_flag);
   HMC_LAUNCH_OK();
   return 0;
 }
@@ -555,6 +585,7 @@ extern "C" int hmc_moe_unpermute_grad(const void* permuted, const void* grad_out
                                       const float* probs, int64_t num_tokens, int64_t top_k, int64_t hidden,
                                       void* grad_permuted, float* grad_probs, int32_t* status,
                                       void* stream_ptr) {
+  ProfileScope profile(HMC_PROFILE_ROUTE, static_cast<cudaStream_t>(stream_ptr));
   if (num_tokens == 0) return 0;
   int rc = check_rows("hmc_moe_unpermute_grad", grad_out, grad_permuted, hidden);
   if (rc != 0) return rc;
@@ -575,6 +606,7 @@ extern "C" int hmc_moe_unpermute_grad(const void* permuted, const void* grad_out
 extern "C" int hmc_moe_token_permute_grad(const void* grad_permuted, const int32_t* mapping, int64_t num_tokens,
                                           int64_t top_k, int64_t hidden, void* grad_tokens, int32_t* status,
                                           void* stream_ptr) {
+  ProfileScope profile(HMC_PROFILE_ROUTE, static_cast<cudaStream_t>(stream_ptr));
   if (num_tokens == 0) return 0;
   int rc = check_rows("hmc_moe_token_permute_grad", grad_permuted, grad_tokens, hidden);
   if (rc != 0) return rc;
@@ -611,7 +643,8 @@ extern "C" int hmc_route_offsets(const int32_t* counts, int64_t ep, int64_t expe
                                  int64_t* dispatch_src_off, int64_t* dispatch_target_off, int32_t* dispatch_size,
                                  int64_t* combine_src_off, int64_t* combine_target_off, int32_t* combine_size,
                                  int64_t* group_list, int64_t* totals, int64_t* recv_segment_start,
-                                 void* stream_ptr) {
+                                 int64_t* send_order_start, void* stream_ptr) {
+  ProfileScope profile(HMC_PROFILE_ROUTE, static_cast<cudaStream_t>(stream_ptr));
   HMC_REQUIRE(counts && dispatch_src_off && dispatch_target_off && dispatch_size && combine_src_off &&
                   combine_target_off && combine_size && group_list,
               HMC_ERR_INVALID, "hmc_route_offsets: null tensor pointer");
@@ -626,7 +659,7 @@ extern "C" int hmc_route_offsets(const int32_t* counts, int64_t ep, int64_t expe
       reinterpret_cast<long long*>(dispatch_src_off), reinterpret_cast<long long*>(dispatch_target_off),
       dispatch_size, reinterpret_cast<long long*>(combine_src_off), reinterpret_cast<long long*>(combine_target_off),
       combine_size, reinterpret_cast<long long*>(group_list), reinterpret_cast<long long*>(totals),
-      reinterpret_cast<long long*>(recv_segment_start));
+      reinterpret_cast<long long*>(recv_segment_start), reinterpret_cast<long long*>(send_order_start));
   HMC_LAUNCH_OK();
   return 0;
 }

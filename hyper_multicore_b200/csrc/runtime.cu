@@ -104,6 +104,34 @@ extern "C" int hmc_profile_enable(int on) {
   return 0;
 }
 
+extern "C" int hmc_profile_dump(int32_t* kinds, double* start_ms, double* duration_ms, int capacity) {
+  using namespace hmc;
+  std::vector<ProfileRecord> records;
+  {
+    std::lock_guard<std::mutex> lock(g_profile_mutex);
+    records.swap(g_profile_records);
+  }
+  int written = 0;
+  for (size_t i = 0; i < records.size(); ++i) {
+    const ProfileRecord& r = records[i];
+    float since = 0.0f, ms = 0.0f;
+    if (kinds != nullptr && written < capacity && cudaEventSynchronize(r.stop) == cudaSuccess &&
+        cudaEventElapsedTime(&ms, r.start, r.stop) == cudaSuccess &&
+        cudaEventElapsedTime(&since, records[0].start, r.start) == cudaSuccess) {
+      kinds[written] = r.kind;
+      start_ms[written] = since;
+      duration_ms[written] = ms;
+      ++written;
+    }
+  }
+  std::lock_guard<std::mutex> lock(g_profile_mutex);
+  for (const ProfileRecord& r : records) {
+    g_profile_pool.push_back(r.start);
+    g_profile_pool.push_back(r.stop);
+  }
+  return written;
+}
+
 extern "C" int hmc_profile_collect(double* ms_by_kind, int64_t* calls_by_kind, int kinds) {
   using namespace hmc;
   HMC_REQUIRE(ms_by_kind != nullptr && calls_by_kind != nullptr && kinds > 0, HMC_ERR_INVALID,
@@ -144,6 +172,7 @@ __global__ void store_words_kernel(int* __restrict__ dst, const int* __restrict_
 
 extern "C" int hmc_store_words(int32_t* dst, const int32_t* src, int64_t words, void* stream_ptr) {
   HMC_REQUIRE(dst != nullptr && src != nullptr && words >= 0, HMC_ERR_INVALID, "hmc_store_words: bad arguments");
+  hmc::ProfileScope profile(HMC_PROFILE_ROUTE, static_cast<cudaStream_t>(stream_ptr));
   if (words == 0) return 0;
   const int blocks = static_cast<int>(words < 256 * 64 ? (words + 255) / 256 : 64);
   store_words_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream_ptr)>>>(dst, src, words);

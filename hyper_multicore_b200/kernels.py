@@ -332,11 +332,12 @@ def route_offsets(counts_by_source: torch.Tensor, rank: int):
         "group_list": torch.empty(local, **i64),
         "totals": torch.empty(2, **i64),
         "recv_segment_start": torch.empty(ep * local, **i64),
+        "send_order_start": torch.empty(experts + 1, **i64),
     }
     _call("hmc_route_offsets", device, counts_by_source.contiguous().data_ptr(), ep, experts, rank,
           *(out[k].data_ptr() for k in ("dispatch_src_off", "dispatch_target_off", "dispatch_size",
                                         "combine_src_off", "combine_target_off", "combine_size", "group_list",
-                                        "totals", "recv_segment_start")))
+                                        "totals", "recv_segment_start", "send_order_start")))
     return out
 
 
@@ -409,7 +410,8 @@ def ep_dispatch(tokens, source_of_row, expert_of_row, dispatch_src_off, dispatch
 
 def _dispatch_struct(tokens, source_of_row, expert_of_row, dispatch_src_off, dispatch_target_off, *, rows, top_k, ep,
                      local_experts, capacity_rows, peer_buffers, peer_ctrl, local_ctrl, generation, status=None,
-                     budget_ns=0, max_ctas=0, row_values=None, value_index=None, value_plane_offset=0, rank=0):
+                     budget_ns=0, max_ctas=0, row_values=None, value_index=None, value_plane_offset=0, rank=0,
+                     send_order_start=None):
     """``hmc_ep_dispatch_args`` from tensors (``rank`` matters only when the dispatch rides inside a GEMM)."""
     if row_values is not None and (row_values.dtype != torch.float32 or not row_values.is_contiguous()):
         raise ValueError("row_values must be a contiguous float32 tensor")
@@ -429,6 +431,7 @@ def _dispatch_struct(tokens, source_of_row, expert_of_row, dispatch_src_off, dis
     args.row_values, args.value_index = _lib.ptr(row_values), _lib.ptr(value_index)
     args.value_plane_offset = value_plane_offset
     args.rank = rank
+    args.send_order_start = _lib.ptr(send_order_start)
     return args
 
 
@@ -477,6 +480,17 @@ def ep_pull(out, segment_start, source_row_off, *, rows, ep, local_experts, sour
     args.generation, args.max_ctas, args.budget_ns = generation, max_ctas, budget_ns
     args.status = _lib.ptr(status)
     _call("hmc_ep_pull", device, ctypes.byref(args))
+
+
+def route_guard(table_block: torch.Tensor, ep: int, experts: int, capacity_rows: int, routed_limit: int, status,
+                skip_flag: torch.Tensor, host_mirror: torch.Tensor) -> None:
+    """Device-side admission check of one expert-parallel call + mirror of table, status words and decision
+    to pinned host memory (``hmc_route_guard``)."""
+    device = _require_cuda(table_block, skip_flag, status)
+    if not host_mirror.is_pinned() or host_mirror.numel() < ep * (experts + 4) + _lib.HMC_STATUS_WORDS + 1:
+        raise ValueError("host_mirror must be pinned int32 memory of ep * (experts + 4) + 9 words")
+    _call("hmc_route_guard", device, table_block.data_ptr(), ep, experts, capacity_rows, routed_limit, _lib.ptr(status),
+          skip_flag.data_ptr(), host_mirror.data_ptr())
 
 
 def ep_wait(counter: torch.Tensor, expected: int, status=None, budget_ns: int = 0) -> None:

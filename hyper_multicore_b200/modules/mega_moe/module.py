@@ -253,6 +253,8 @@ class MegaMoeExperts(torch.nn.Module):
         # push dispatch rides inside the GEMM that consumes the rows; HMC_MOE_FUSED_DISPATCH=0 launches the
         # stand-alone dispatch kernel ahead of it instead
         self._fuse_dispatch = os.environ.get("HMC_MOE_FUSED_DISPATCH", "1") != "0"
+        # queue the operator ahead of the count-table read-back (HMC_MOE_DEFERRED_ROUTE=0: read it first)
+        self._defer_route = os.environ.get("HMC_MOE_DEFERRED_ROUTE", "1") != "0"
         self._group = _ResourceGroup(self._compatibility_key())
         self._group.members.add(id(self))
         self._closed = False
@@ -536,12 +538,24 @@ class MegaMoeExperts(torch.nn.Module):
             from ...symm import PeerControl  # pylint: disable=import-outside-toplevel
 
             self._group.control = PeerControl(self._ep_group, self.num_experts, device)  # collective, once
+        # Steady state of a BF16 push group: the operator is queued WITHOUT waiting for the count table. The
+        # route guard decides on the device whether the call fits the live workspace; the table is validated
+        # below, once everything is queued (the first call, pull dispatch and MXFP8 size buffers from the table).
+        workspace = self._workspace
+        defer = None
+        if (self._defer_route and self.ep_size > 1 and not self._pull and self._precision == "bf16"
+                and isinstance(workspace, PeerWorkspace) and self._group.control is not None):
+            defer = (workspace.capacity_rows, workspace.routed_rows)
         route = prepare_route(hidden_flat, topk_ids.contiguous(), num_experts=self.num_experts, top_k=self.top_k,
                               ep_size=self.ep_size, rank=self._rank, group=self._ep_group,
                               invalid=weight_error is not None, status=self._status,
                               autograd=self._takes_part_in_autograd(hidden_states, topk_weights, expert_weights),
-                              control=self._group.control, budget_ns=self._wait_budget_ns)
+                              control=self._group.control, budget_ns=self._wait_budget_ns, defer_limits=defer)
         if weight_error is not None:
+            if route.deferred is not None:
+                # the peers have queued this call (as a no-op: the route guard saw this rank's flag) and moved on
+                # to the next generation; keep step with them
+                workspace.next_generation()
             raise weight_error
         if route.status_words is not None:
             # read together with the count table: earlier kernels' status words are final
@@ -549,15 +563,21 @@ class MegaMoeExperts(torch.nn.Module):
                 code = route.status_words[0]
                 raise _lib.HmcError(f"MegaMoeExperts: device status {code} ({_lib.STATUS_NAMES.get(code, '?')}), "
                                     f"detail {route.status_words[1:4]}")
-        elif route.pending is None:
+        elif route.pending is None and route.deferred is None:
             # prepare_route just synchronised with the device, so earlier kernels' status words are final
             self.check_status()
         if self._layout is None:
             self._layout = self._pending_layout
-        self._ensure_workspace(device, route)
+        if route.deferred is None:
+            self._ensure_workspace(device, route)
         weight1, weight2 = expert_weights
         probs = topk_weights if topk_weights.dtype == torch.float32 else topk_weights.float()
         out = _MegaMoeFunction.apply(hidden_flat, probs.contiguous(), weight1, weight2, self, route)
+        if route.deferred is not None and route.resolve():
+            # the call did not fit the workspace: it was a no-op on every rank; grow together and run it again
+            route.skip_flag = None
+            self._ensure_workspace(device, route)
+            out = _MegaMoeFunction.apply(hidden_flat, probs.contiguous(), weight1, weight2, self, route)
         try:
             route.finish()
         except ValueError:
@@ -613,7 +633,8 @@ class MegaMoeExperts(torch.nn.Module):
             routed_rows=route.routed_rows, received_rows=route.received_rows, weight_layout=self._layout or "EIO",
             fuse_dispatch=self._fuse_dispatch, probs_before_fc2=self._numerics.apply_probs_before_fc2,
             status=self._status, expert_of_row=route.expert_of_row,
-            recv_segment_start=off["recv_segment_start"], mapping=route.mapping, **self._swiglu_options(), **fields)
+            recv_segment_start=off["recv_segment_start"], send_order_start=off["send_order_start"],
+            mapping=route.mapping, **self._swiglu_options(), **fields)
 
     def _run_forward(self, hidden, probs, w1, w2, route: PreparedRoute):
         """One call of the forward operator (reference: ops.mega_moe, torch/ops.py:554-649, issued by
@@ -664,7 +685,7 @@ class MegaMoeExperts(torch.nn.Module):
             route_probs=probs.reshape(-1) if before_fc2 else None, row_probs=row_probs,
             saved_dispatch=saved_received if push_ep else None, saved_combine=None if ep1 else routed_out,
             saved_row_probs=saved_probs if (before_fc2 and push_ep) else None,
-            topk_probs=None if before_fc2 else probs, output=out)
+            topk_probs=None if before_fc2 else probs, output=out, skip_flag=route.skip_flag)
         ops.mega_moe(dispatch_target, off["dispatch_target_off"], hidden, off["dispatch_src_off"], off["dispatch_size"],
                      w1, off["group_list"], up_proj, activation, w2, off["group_list"], down_proj,
                      None if ep1 else workspace.routed_buffer, off["combine_target_off"], off["combine_src_off"],

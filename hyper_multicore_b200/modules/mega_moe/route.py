@@ -36,6 +36,44 @@ class PreparedRoute:
     max_routed_rows: int           # over the group
     pending: Any = None            # single-rank calls: (event, pinned counts + status words) checked by finish()
     status_words: Any = None       # multi-rank calls with the device exchange: status words read with the table
+    deferred: Any = None           # multi-rank calls queued ahead of the table read-back: see resolve()
+    skip_flag: Any = None          # device int32 the operator's kernels honour (set by the route guard)
+
+    def resolve(self, what: str = "MegaMoeExperts") -> bool:
+        """Deferred multi-rank calls validate here, after the operator has been queued.
+
+        The route guard decided on the device, identically on every rank, whether the call may run (no rank
+        flagged invalid inputs, nobody receives or routes more rows than the workspace holds) and mirrored the
+        count table, the status words and its decision to pinned host memory. Waiting for that copy does not
+        wait for the GEMMs queued behind it. Every rank reads the same table, so every rank raises the same
+        error here, or learns together that the workspace must grow (returns True: the queued operator was a
+        no-op on every rank and the caller runs the call again after growing).
+        """
+        if self.deferred is None:
+            return False
+        event, mirror, ep_size, num_experts, top_k, rank = self.deferred
+        self.deferred = None
+        event.synchronize()
+        flat = mirror.tolist()
+        body = ep_size * num_experts
+        host = [flat[body + 4 * r: body + 4 * r + _HEADER] + flat[r * num_experts:(r + 1) * num_experts]
+                for r in range(ep_size)]
+        table_words = ep_size * (num_experts + 4)
+        status = flat[table_words:table_words + 8]
+        skipped = bool(flat[table_words + 8])
+        if status[0] != 0:
+            from ... import _lib
+
+            raise _lib.HmcError(f"{what}: device status {status[0]} ({_lib.STATUS_NAMES.get(status[0], '?')}), "
+                                f"detail {status[1:4]}")
+        host_counts = check_gathered_rows(host, top_k, num_experts)  # raises on every rank together
+        local = num_experts // ep_size
+        received = [sum(sum(row[d * local:(d + 1) * local]) for row in host_counts) for d in range(ep_size)]
+        routed = [sum(row) for row in host_counts]
+        self.counts_by_source = host_counts
+        self.received_rows = received[rank]
+        self.max_received_rows, self.max_routed_rows = max(received), max(routed)
+        return skipped
 
     def finish(self, what: str = "MegaMoeExperts") -> None:
         """Single-rank calls validate here, after the layer's kernels have been queued.
@@ -100,8 +138,13 @@ def check_gathered_rows(host: list[list[int]], top_k: int, num_experts: int) -> 
 
 def prepare_route(hidden: torch.Tensor, topk_ids: torch.Tensor, *, num_experts: int, top_k: int, ep_size: int,
                   rank: int, group: Any | None, invalid: bool = False, status=None,
-                  autograd: bool = False, control: Any | None = None, budget_ns: int = 0) -> PreparedRoute:
-    """Sort the routes, exchange counts, derive offsets. Collective when ep_size > 1."""
+                  autograd: bool = False, control: Any | None = None, budget_ns: int = 0,
+                  defer_limits: tuple[int, int] | None = None) -> PreparedRoute:
+    """Sort the routes, exchange counts, derive offsets. Collective when ep_size > 1.
+
+    ``defer_limits`` = (receive capacity, routed capacity) of the live workspace: the host does not wait for the
+    count table. The route guard takes the admission decision on the device, `received_rows` of the result is the
+    capacity (an upper bound), and `resolve()` validates the mirrored table once the operator has been queued."""
     device = hidden.device
     tokens = hidden.shape[0]
     mapping, sources, row_experts, counts, _ = kernels.moe_sort_routes(topk_ids, num_experts, status=status)
@@ -130,6 +173,24 @@ def prepare_route(hidden: torch.Tensor, topk_ids: torch.Tensor, *, num_experts: 
         # payload and enqueueing a host collective; the header words travel as kernel arguments.
         table, block = control.exchange(counts, (int(invalid), tokens, int(autograd)), status, budget_ns)
         offsets = kernels.route_offsets(table, rank)
+        if defer_limits is not None:
+            words = block.numel() + 8 + 1
+            key = ("mirror", device, words)
+            slot = _PINNED.get(key)
+            if slot is None:
+                # two mirrors in turn: a call's mirror is read by resolve() before the call after next writes it
+                slot = _PINNED[key] = [torch.empty(words, dtype=torch.int32).pin_memory() for _ in range(2)] + [0]
+            slot[2] ^= 1
+            mirror = slot[slot[2]]
+            flag = control.skip_flag
+            kernels.route_guard(block, ep_size, num_experts, defer_limits[0], defer_limits[1], status, flag, mirror)
+            event = torch.cuda.Event()
+            event.record()
+            return PreparedRoute(
+                mapping=mapping, source_of_row=sources, expert_of_row=row_experts, counts_by_source=None,
+                offsets=offsets, routed_rows=tokens * top_k, received_rows=defer_limits[0],
+                max_received_rows=defer_limits[0], max_routed_rows=tokens * top_k,
+                deferred=(event, mirror, ep_size, num_experts, top_k, rank), skip_flag=flag)
         words = status.numel() if status is not None else 0
         key = ("table", device, block.numel() + words)
         staged = _PINNED.get(key)

@@ -238,6 +238,7 @@ class MegaMoeLaunch:
     dispatch_src_index: torch.Tensor | None = None
     expert_of_row: torch.Tensor | None = None
     recv_segment_start: torch.Tensor | None = None
+    send_order_start: torch.Tensor | None = None
     mapping: torch.Tensor | None = None
     topk_probs: torch.Tensor | None = None
     # forward
@@ -247,6 +248,7 @@ class MegaMoeLaunch:
     saved_combine: torch.Tensor | None = None
     saved_row_probs: torch.Tensor | None = None
     output: torch.Tensor | None = None
+    skip_flag: torch.Tensor | None = None
     # backward
     weight_grad_f32: bool = False
     row_dot: torch.Tensor | None = None
@@ -321,12 +323,13 @@ def mega_moe(dispatch_target, dispatch_target_off, dispatch_src, dispatch_src_of
     args.swiglu_clamp, args.swiglu_limit = launch.swiglu_clamp, launch.swiglu_limit
     args.fuse_dispatch, args.probs_before_fc2 = int(launch.fuse_dispatch), int(launch.probs_before_fc2)
     args.dispatch_src_index, args.expert_of_row = _ptr(launch.dispatch_src_index), _ptr(launch.expert_of_row)
-    args.recv_segment_start = _ptr(launch.recv_segment_start)
+    args.recv_segment_start, args.send_order_start = _ptr(launch.recv_segment_start), _ptr(launch.send_order_start)
     args.route_probs, args.row_probs = _ptr(launch.route_probs), _ptr(launch.row_probs)
     args.transport = ctypes.cast(ctypes.pointer(transport), ctypes.c_void_p)
     args.saved_dispatch, args.saved_combine = _ptr(launch.saved_dispatch), _ptr(launch.saved_combine)
     args.saved_row_probs = _ptr(launch.saved_row_probs)
     args.mapping, args.topk_probs, args.output = _ptr(launch.mapping), _ptr(launch.topk_probs), _ptr(launch.output)
+    args.skip_flag = _ptr(launch.skip_flag)
     _launch_native("hmc_mega_moe", args, dispatch_target.device, 6)
 
 
@@ -382,7 +385,7 @@ def mega_moe_grad(dispatch_target, dispatch_target_off, dy, dispatch_src_off, di
     args.fuse_dispatch, args.weight_grad_f32 = int(launch.fuse_dispatch), int(launch.weight_grad_f32)
     args.probs_before_fc2 = int(launch.probs_before_fc2)
     args.dispatch_src_index, args.expert_of_row = _ptr(launch.dispatch_src_index), _ptr(launch.expert_of_row)
-    args.recv_segment_start = _ptr(launch.recv_segment_start)
+    args.recv_segment_start, args.send_order_start = _ptr(launch.recv_segment_start), _ptr(launch.send_order_start)
     args.row_probs, args.row_dot = _ptr(launch.row_probs), _ptr(launch.row_dot)
     args.transport = ctypes.cast(ctypes.pointer(transport), ctypes.c_void_p)
     args.grad_output, args.saved_combine = _ptr(launch.grad_output), _ptr(launch.saved_combine)

@@ -87,6 +87,9 @@ class PeerControl:
         span = torch.as_tensor(_DeviceSpan(self._base.value, self.nbytes, self), device=device)
         self.ctrl = span[:self._ctrl_bytes].view(torch.int32)
         self.table = span[self._table_off:self.nbytes].view(torch.int32).view(2, self.ep * (experts + 4))
+        # the route guard's decision, one word per exchange parity: a call's kernels may still read theirs
+        # while the next call's guard writes the other
+        self._skip_flags = torch.zeros(2, dtype=torch.int32, device=device)
         pointer_array = ctypes.c_void_p * self.ep
         self.peer_ctrl = pointer_array(*self._peer_bases)
         self.peer_tables = pointer_array(*(base + self._table_off for base in self._peer_bases))
@@ -108,6 +111,11 @@ class PeerControl:
         kernels._call("hmc_ep_exchange_counts", self.device, ctypes.byref(args))  # pylint: disable=protected-access
         block = self.table[self.exchanges & 1]
         return block[:self.ep * self.experts].view(self.ep, self.experts), block
+
+    @property
+    def skip_flag(self) -> torch.Tensor:
+        """Device word of the current exchange that the operator's kernels consult."""
+        return self._skip_flags[self.exchanges & 1:(self.exchanges & 1) + 1]
 
     def close(self) -> None:
         """Collective: unmap peers and free."""

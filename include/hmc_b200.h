@@ -52,11 +52,15 @@ int hmc_worker_queue_layout_version(void);
 #define HMC_PROFILE_GROUPED_GEMM 0 /* hmc_grouped_gemm */
 #define HMC_PROFILE_MX_GEMM 1      /* hmc_mx_gemm */
 #define HMC_PROFILE_MX_QUANT 2     /* hmc_mx_quant */
-#define HMC_PROFILE_EP 3           /* hmc_ep_dispatch, hmc_ep_pull, hmc_ep_combine, hmc_ep_wait(_groups) */
-#define HMC_PROFILE_KINDS 4
+#define HMC_PROFILE_EP 3           /* hmc_ep_dispatch, hmc_ep_pull, hmc_ep_combine, hmc_ep_wait(_groups), count exchange */
+#define HMC_PROFILE_ROUTE 4        /* route preparation and token (un)permutation entry points */
+#define HMC_PROFILE_KINDS 5
 int64_t hmc_launch_count(void);
 int hmc_profile_enable(int on);
 int hmc_profile_collect(double* ms_by_kind, int64_t* calls_by_kind, int kinds);
+/* Like hmc_profile_collect, but returns the calls one by one in the order they were made: kind, start (ms after
+ * the first call's start) and duration of up to `capacity` calls. Returns the number of calls written. */
+int hmc_profile_dump(int32_t* kinds, double* start_ms, double* duration_ms, int capacity);
 
 /* ------------------------------------------------------------------------------------------
  * Grouped expert GEMM (tcgen05 + TMA + TMEM).
@@ -144,6 +148,9 @@ typedef struct hmc_grouped_gemm_args {
    * dispatch->local_experts == groups and dispatch->hidden == k. Every CTA of the launch is resident at once
    * (one per SM), so a CTA waiting for rows never keeps another CTA's dispatch warps from running. */
   const struct hmc_ep_dispatch_args* dispatch;
+  const int32_t* skip_flag;        /* optional device int32: when it holds a non-zero value as the kernel starts, the
+                                      launch does nothing (no tiles, no dispatch). Set by hmc_route_guard when the
+                                      call it belongs to must not run (see there) */
 } hmc_grouped_gemm_args;
 
 int hmc_grouped_gemm(const hmc_grouped_gemm_args* args, void* stream);
@@ -328,7 +335,11 @@ int hmc_gate_project_promoted(const void* x_bf16, const void* w, int w_is_bf16, 
  * hmc_route_offsets         : route_offsets / _compute_route_metadata, push mode
  *                             (route.py:309-390, utilities.asc:89-151); row units. totals =
  *                             {rows routed by this rank, rows received by this rank};
- *                             recv_segment_start[le * ep + s] = first received row of (le, s)
+ *                             recv_segment_start[le * ep + s] = first received row of (le, s);
+ *                             send_order_start[experts + 1] (optional) = prefix of this rank's segments in the
+ *                             order a GEMM-carried dispatch sends them: local expert 0 of every destination
+ *                             (rank + 1 first, this rank last), then local expert 1, ...
+ *                             (the reference rotates destinations the same way, scheduler/scheduler.py:27-53)
  * ------------------------------------------------------------------------------------------ */
 int64_t hmc_moe_sort_workspace_bytes(int64_t entries, int64_t experts);
 int hmc_moe_histogram(const void* indices, int indices_are_i64, int64_t entries, int64_t experts, int32_t* counts,
@@ -375,7 +386,7 @@ int hmc_zero_empty_expert_grad(void* first, int64_t first_bytes_per_expert, void
 int hmc_route_offsets(const int32_t* counts, int64_t ep, int64_t experts, int64_t rank, int64_t* dispatch_src_off,
                       int64_t* dispatch_target_off, int32_t* dispatch_size, int64_t* combine_src_off,
                       int64_t* combine_target_off, int32_t* combine_size, int64_t* group_list, int64_t* totals,
-                      int64_t* recv_segment_start, void* stream);
+                      int64_t* recv_segment_start, int64_t* send_order_start, void* stream);
 
 /* ------------------------------------------------------------------------------------------
  * MegaMHC.
@@ -511,10 +522,13 @@ typedef struct hmc_ep_dispatch_args {
   const float* row_values;
   const int32_t* value_index;
   int64_t value_plane_offset;    /* bytes; at least capacity_rows * hidden * 2 */
-  int64_t rank;                  /* this rank (0 <= rank < ep). Used when the dispatch rides inside a grouped GEMM
-                                    (hmc_grouped_gemm_args.dispatch): rows are then sent in rank-rotated order,
-                                    those owned by rank + 1 first, this rank's own last
-                                    (hyper_multicore/scheduler/scheduler.py:27-53) */
+  int64_t rank;                  /* this rank (0 <= rank < ep); used with send_order_start */
+  const int64_t* send_order_start; /* optional device [ep * local_experts + 1], from hmc_route_offsets: when the
+                                    dispatch rides inside a grouped GEMM (hmc_grouped_gemm_args.dispatch) the rows
+                                    are sent local-expert-major across the destinations (rank + 1 first, this rank
+                                    last), so every owner's first experts complete first and their tiles overlap
+                                    the rest of the transfer. NULL = source row order */
+  const int32_t* skip_flag;      /* optional: as in hmc_grouped_gemm_args */
 } hmc_ep_dispatch_args;
 
 typedef struct hmc_ep_combine_args {
@@ -604,6 +618,21 @@ int hmc_ep_pull(const hmc_ep_pull_args* args, void* stream);
 int hmc_ep_combine(const hmc_ep_combine_args* args, void* stream);
 /* Bounded device-side wait until *counter >= expected; on time-out writes HMC_STATUS_TIMEOUT_ARRIVAL. */
 int hmc_ep_wait(const int32_t* counter, int32_t expected, uint64_t budget_ns, int32_t* status, void* stream);
+/* The same wait, skipped when *skip_flag is non-zero (skip_flag may be NULL). */
+int hmc_ep_wait_unless(const int32_t* counter, int32_t expected, uint64_t budget_ns, int32_t* status,
+                       const int32_t* skip_flag, void* stream);
+/* Admission check of one expert-parallel call ON THE DEVICE, so that the host need not wait for the count table
+ * before it queues the operator (the reference reads the table back and validates on the host before every
+ * launch, hyper_multicore/modules/mega_moe/route.py:585-622; here the same decision is taken by every rank's
+ * device from the same table, and the host validates the mirrored table afterwards, off the critical path).
+ * table = {int32 counts[ep][experts]; int32 header[ep][4]} as written by hmc_ep_exchange_counts. *skip_flag is set
+ * to 1 when any rank flagged its inputs invalid (header word 0), when any rank would receive more than
+ * capacity_rows rows, or when any rank routes more than routed_limit rows; else to 0. Every rank computes the
+ * same value, and kernels given the flag do nothing when it is set: nobody stores, nobody waits. The table, the
+ * status words (HMC_STATUS_WORDS, may be NULL) and the flag are then copied to host_mirror (pinned host memory,
+ * ep * (experts + 4) + HMC_STATUS_WORDS + 1 words) by the kernel itself. */
+int hmc_route_guard(const int32_t* table, int64_t ep, int64_t experts, int64_t capacity_rows, int64_t routed_limit,
+                    const int32_t* status_words, int32_t* skip_flag, int32_t* host_mirror, void* stream);
 /* Bounded device-side wait until counters[g] >= rows of group g for every group (used where a
  * kernel without its own arrival gating consumes dispatched rows, e.g. the MX quantiser). */
 int hmc_ep_wait_groups(const int32_t* counters, const int64_t* group_ends, int64_t groups, uint64_t budget_ns,
@@ -699,6 +728,7 @@ typedef struct hmc_mega_moe_args {
   const int32_t* dispatch_src_index;  /* [routed_rows] flat (token * top_k + slot) of each expert-major row, or NULL */
   const int32_t* expert_of_row;       /* [routed_rows] global expert of each expert-major row */
   const int64_t* recv_segment_start;  /* [experts / ep * ep], from hmc_route_offsets */
+  const int64_t* send_order_start;    /* [experts + 1], from hmc_route_offsets: order of a GEMM-carried dispatch; or NULL */
   const float* route_probs;           /* [seq * top_k], read with probs_before_fc2 (may be NULL on a rank without tokens) */
   float* row_probs;                   /* before FC2: where the received per-row probabilities are (push: the float
                                          plane of dispatch_target; pull: a caller tensor of received_rows floats) */
@@ -712,6 +742,9 @@ typedef struct hmc_mega_moe_args {
   const int32_t* mapping;             /* [seq * top_k] destination row of every (token, slot) */
   const float* topk_probs;            /* [seq * top_k]; not used with route_probs (rows are already weighted) */
   void* output;                       /* [seq, H] bf16, or NULL to skip the epilogue */
+  const int32_t* skip_flag;           /* optional, from hmc_route_guard: when set on the device the whole operator is a
+                                         no-op there. received_rows may then be an UPPER BOUND (the receive capacity)
+                                         instead of the exact count: tiles follow the device-side group list */
 } hmc_mega_moe_args;
 
 typedef struct hmc_mega_moe_grad_args {
@@ -760,6 +793,7 @@ typedef struct hmc_mega_moe_grad_args {
   const int32_t* dispatch_src_index;  /* before FC2 only */
   const int32_t* expert_of_row;
   const int64_t* recv_segment_start;
+  const int64_t* send_order_start;    /* as in hmc_mega_moe_args */
   const float* row_probs;             /* before FC2: received per-row probabilities saved by forward */
   float* row_dot;                     /* before FC2: scratch float[rows] for the per-row probability gradient */
   const hmc_moe_transport* transport;

@@ -129,6 +129,28 @@ def main():
         state = module.debug_state()
         assert state["ep"] == world and state["generation"] >= 10, state
         module.close()
+    # Failure convergence with the operator queued ahead of the table read-back: one rank brings expert weights of
+    # the wrong shape. It raises its own error; every other rank learns of it from the validity header, its queued
+    # kernels do nothing (the route guard saw the flag on the device) and it raises too. The next call is healthy.
+    module = MegaMoeExperts(hidden_size=hidden, intermediate_size=inter, num_experts=experts, top_k=top_k,
+                            ep_group=dist.group.WORLD)
+    scenario(module, rank, world, device, [96] * world, hidden, inter, experts, top_k, seed=40, layout="EIO")
+    x, ids, probs, _ = make_rank_inputs(rank, 96, hidden, experts, top_k, 41)
+    local = experts // world
+    good = (torch.zeros(local, hidden, 2 * inter, dtype=torch.bfloat16, device=device),
+            torch.zeros(local, inter, hidden, dtype=torch.bfloat16, device=device))
+    bad = (good[0][:, :, :inter].contiguous(), good[1])
+    try:
+        module(x.to(device), ids.to(device), probs.to(device), expert_weights=bad if rank == world - 1 else good)
+    except ValueError as error:
+        expected = "gate_up_weight must have shape" if rank == world - 1 else "invalid inputs on EP rank"
+        assert expected in str(error), str(error)
+    else:
+        raise AssertionError("every rank must reject a call with invalid inputs on one rank")
+    torch.cuda.synchronize()
+    module.check_status()
+    scenario(module, rank, world, device, [80] * world, hidden, inter, experts, top_k, seed=42, layout="EIO")
+    module.close()
     # two serial layers on one peer-mapped workspace
     shared = [MegaMoeExperts(hidden_size=hidden, intermediate_size=inter, num_experts=experts, top_k=top_k,
                              ep_group=dist.group.WORLD) for _ in range(2)]

@@ -44,7 +44,7 @@ def test_argument_checks_fail_without_touching_a_device():
     args.tokens = 0
     assert lib.hmc_gate_route(ctypes.byref(args), None) == -1
     assert b"tokens must be positive" in lib.hmc_last_error()
-    assert lib.hmc_route_offsets(None, 2, 5, 0, None, None, None, None, None, None, None, None, None, None) == -1
+    assert lib.hmc_route_offsets(None, 2, 5, 0, None, None, None, None, None, None, None, None, None, None, None) == -1
 
 
 STRUCTS = {

@@ -257,7 +257,7 @@ def test_dispatch_warps_feed_the_gemm_that_carries_them(cuda_device, tile_mode, 
     sending = dict(tokens=x, source_of_row=sources, expert_of_row=row_experts, dispatch_src_off=off["dispatch_src_off"],
                    dispatch_target_off=off["dispatch_target_off"], rows=rows, top_k=top_k, ep=1, local_experts=experts,
                    capacity_rows=rows, peer_buffers=peers, peer_ctrl=peer_ctrl, local_ctrl=ctrl, generation=1,
-                   status=status, budget_ns=2_000_000_000, rank=0)
+                   status=status, budget_ns=2_000_000_000, rank=0, send_order_start=off["send_order_start"])
     K.grouped_gemm(received, w, c, off["group_list"], mode=K.HMC_GEMM_RAGGED_M, ready_counters=ctrl[:experts],
                    ready_budget_ns=2_000_000_000, status=status, tile_mode=tile_mode, dispatch=sending)
     torch.cuda.synchronize()

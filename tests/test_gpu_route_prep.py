@@ -128,3 +128,24 @@ def test_zero_empty_expert_gradients(cuda_device):
     K.zero_empty_expert_grad(first, second, cumulative)
     assert first.sum(dim=(1, 2)).cpu().tolist() == [0, 128, 0, 128]
     assert second.sum(dim=(1, 2)).cpu().tolist() == [0, 128, 0, 128]
+
+
+@pytest.mark.parametrize("ep,experts", [(1, 4), (2, 8), (4, 32), (8, 256)])
+def test_send_order_visits_local_expert_zero_of_every_destination_first(cuda_device, ep, experts):
+    """Prefix of a rank's segments in the order a GEMM-carried dispatch sends them: local expert le of the
+    destinations rank + 1, rank + 2, ..., rank, for le = 0, 1, ... (every owner's first experts complete first)."""
+    from hyper_multicore_b200 import kernels as K
+
+    rng = np.random.default_rng(ep * 1000 + experts)
+    table = rng.integers(0, 50, size=(ep, experts), dtype=np.int32)
+    local = experts // ep
+    for rank in range(ep):
+        off = K.route_offsets(torch.from_numpy(table).to(cuda_device), rank)
+        expected, run = [], 0
+        for le in range(local):
+            for dd in range(ep):
+                expected.append(run)
+                run += int(table[rank, ((rank + 1 + dd) % ep) * local + le])
+        expected.append(run)
+        assert off["send_order_start"].cpu().tolist() == expected
+        assert run == int(table[rank].sum())
