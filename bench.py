@@ -332,6 +332,13 @@ class MoeLayerRun:
         self.ids = ids_h.to(device)
         self.p = p_h.to(device).requires_grad_(True)
         self.g = g_h.to(device)
+        # rows every rank's experts receive (skewed routing loads the ranks unevenly: the step lasts as long as
+        # the most loaded rank, so that rank's rows set the work the roofline is computed from)
+        local = shape.num_experts(ctx.world) // ctx.world
+        received = torch.bincount(ids_h.reshape(-1) // local, minlength=ctx.world).to(device)
+        if ctx.world > 1:
+            ctx.dist.all_reduce(received)
+        self.received_rows = [int(v) for v in received.tolist()]
 
     def step(self) -> None:
         self.w1.grad = self.w2.grad = self.x.grad = self.p.grad = None
@@ -363,13 +370,15 @@ class MoeLayerRun:
         gemm_ms = ctx.max_over_ranks(prof.ms[kind] / profile_steps)
         quant_ms = ctx.max_over_ranks(prof.ms["mx_quant"] / profile_steps)
         ms_per_step = total_ms / steps
-        flops = shape.flops_per_token * shape.tokens  # per rank: every rank owns an equal share in expectation
+        rows_max = max(self.received_rows)
+        flops = shape.flops_per_token // shape.top_k * rows_max  # 18*H*I per routed row, on the most loaded rank
         return {
             "ms_per_step": ms_per_step, "tokens_per_s": ctx.world * shape.tokens / (ms_per_step * 1e-3),
             "launches": launches, "gemm_ms_per_step": gemm_ms, "gemm_launches_per_step": prof.calls[kind] // profile_steps,
             "quant_ms_per_step": quant_ms, "non_gemm_ms_per_step": ms_per_step - gemm_ms,
             "gemm_tflops": flops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else None,
             "layer_tflops": flops / (ms_per_step * 1e-3) / 1e12, "flops_per_step": flops,
+            "received_rows_max_rank": rows_max, "received_rows_mean": sum(self.received_rows) / len(self.received_rows),
         }
 
     def close(self) -> None:
@@ -645,6 +654,46 @@ def nccl_layer_measure(ctx: Context, run: MoeLayerRun, steps: int, warmup: int) 
                     "grouped GEMMs; the baseline of the reference's examples (AllToAllTokenDispatcher)"}
 
 
+def write_timeline(ctx: Context, run: MoeLayerRun, path: str) -> None:
+    """Call-by-call device timeline of one forward + backward step (CUDA events around every entry point of
+    the native library, on its stream): kind, start, duration and the gap to the previous call. Rank 0 writes it."""
+    import ctypes
+
+    from hyper_multicore_b200 import _lib
+
+    lib = _lib.load()
+    steps = 3
+    for _ in range(3):
+        run.step()
+    ctx.barrier()
+    lib.hmc_profile_enable(1)
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        run.step()
+    stop.record()
+    ctx.barrier()
+    lib.hmc_profile_enable(0)
+    capacity = 4096
+    kinds, begins, lengths = (ctypes.c_int32 * capacity)(), (ctypes.c_double * capacity)(), (ctypes.c_double * capacity)()
+    count = lib.hmc_profile_dump(kinds, begins, lengths, capacity)
+    if ctx.rank != 0:
+        return
+    per_step = count // steps
+    first = (steps - 1) * per_step
+    lines = [f"# one step of {steps} (the last), rank 0 of {ctx.world}; {config(run.shape, ctx.world, run.precision)['workload']}",
+             f"# step time over the {steps} profiled steps: {start.elapsed_time(stop) / steps * 1e3:.1f} us",
+             "#   start us    gap us  call kind        duration us"]
+    previous_end, totals = begins[first], {}
+    for i in range(first, count):
+        name = _lib.HMC_PROFILE_KINDS[kinds[i]]
+        lines.append(f"{1e3 * (begins[i] - begins[first]):12.1f} {1e3 * (begins[i] - previous_end):9.1f}  {name:14s} {1e3 * lengths[i]:12.1f}")
+        previous_end = begins[i] + lengths[i]
+        totals[name] = totals.get(name, 0.0) + lengths[i]
+    lines.append("# per kind (us): " + ", ".join(f"{k} {1e3 * v:.1f}" for k, v in totals.items()))
+    Path(path).write_text("\n".join(lines) + "\n")
+
+
 def side_workload(ctx: Context, workload: str, steps: int, warmup: int, peaks: dict) -> dict:
     import bench_side
 
@@ -673,6 +722,8 @@ def run_gpu(args) -> None:
         sampler.start()
     main = run.measure(args.steps, args.warmup, peaks)
     clocks = sampler.stop() if ctx.rank == 0 else None
+    if args.timeline:
+        write_timeline(ctx, run, args.timeline)
     e2e = e2e_measure(ctx, run, args.steps, args.warmup)
     parity = {"checked": False, "why": "--no-parity"} if args.no_parity or args.shape != "c2" else parity_check(ctx, run)
 
@@ -701,6 +752,9 @@ def run_gpu(args) -> None:
                 "workload": config(leg_shape, ctx.world, "mxfp8")["workload"], "ms_per_step": result["ms_per_step"],
                 "tokens_per_s": result["tokens_per_s"], "gemm_ms_per_step": result["gemm_ms_per_step"],
                 "quant_ms_per_step": result["quant_ms_per_step"], "gemm_tflops": result["gemm_tflops"],
+                "received_rows_max_rank": result["received_rows_max_rank"],
+                "received_rows_mean": result["received_rows_mean"],
+                "flops_note": "18*H*I flop per routed row x the rows of the most loaded rank (the step lasts as long as that rank)",
                 "frac_fp8": result["gemm_tflops"] / fp8_peak if result["gemm_tflops"] else None,
                 "layer_frac_fp8": result["layer_tflops"] / fp8_peak,
                 "fp8_peak_tflops": fp8_peak,
@@ -763,6 +817,7 @@ def run_gpu(args) -> None:
             "gemm_ms_per_step": main["gemm_ms_per_step"], "launches_per_step": main["gemm_launches_per_step"],
             "non_gemm_ms_per_step": main["non_gemm_ms_per_step"],
             "algorithmic_flops_per_step": main["flops_per_step"],
+            "received_rows_max_rank": main["received_rows_max_rank"], "received_rows_mean": main["received_rows_mean"],
             "layer_frac": main["layer_tflops"] / burst, "layer_frac_sustained": main["layer_tflops"] / sustained,
         },
         "extra": extra,
@@ -793,6 +848,8 @@ def main() -> None:
     parser.add_argument("--workload", choices=("moe", "gate", "mhc"), default="moe",
                         help="moe = the MoE layer (default, the headline metric); gate / mhc = the router and the "
                              "four-stream residual mix, timed against the HBM roofline")
+    parser.add_argument("--timeline", default=None, metavar="FILE",
+                        help="also write a call-by-call device timeline of one step (CUDA events) to FILE")
     parser.add_argument("--tokens", type=int, default=None,
                         help="gate / mhc workloads only: run a smaller case of the same kernels (profiler captures)")
     args = parser.parse_args()

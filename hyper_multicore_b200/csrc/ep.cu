@@ -105,7 +105,7 @@ ep_dispatch_kernel(const uint4* __restrict__ tokens, const int* __restrict__ sou
       const long long src_row = source_of_row != nullptr ? source_of_row[j] / top_k : j;
       const uint4* src = tokens + src_row * vec_per_row;
       uint4* dst = static_cast<uint4*>(peers.data[e / local_experts]) + dest_row * vec_per_row;
-      for (int v = lane; v < vec_per_row; v += 32) st_16(dst + v, ld_nc_16(src + v));
+      copy_row_warp(dst, src, vec_per_row, lane);
       if (row_values != nullptr && lane == 0) {
         // the row's scalar (its routing probability) lands in the float plane behind the rows
         float* plane = reinterpret_cast<float*>(static_cast<unsigned char*>(peers.data[e / local_experts]) +
@@ -185,7 +185,7 @@ ep_combine_kernel(const uint4* __restrict__ results, const long long* __restrict
       if (s < 0) continue;
       const uint4* src = results + (r0 + r) * vec_per_row;
       uint4* dst = static_cast<uint4*>(peers.data[s]) + chunk_dest[r] * vec_per_row;
-      for (int v = lane; v < vec_per_row; v += 32) st_16(dst + v, ld_nc_16(src + v));
+      copy_row_warp(dst, src, vec_per_row, lane);
       if (result_values != nullptr && lane == 0) {
         float* plane = reinterpret_cast<float*>(static_cast<unsigned char*>(peers.data[s]) + value_plane_offset);
         plane[chunk_dest[r]] = result_values[r0 + r];

@@ -39,6 +39,28 @@ struct DispatchFuse {
 
 #ifdef __CUDACC__
 
+// One warp copies one row of `vec_per_row` 16-byte vectors, eight (then four) loads in flight per lane: the
+// stores are posted writes (over NVLink for a remote owner), so the bytes in flight are set by the loads.
+__device__ __forceinline__ void copy_row_warp(uint4* __restrict__ dst, const uint4* __restrict__ src, int vec_per_row,
+                                              int lane) {
+  int v = lane;
+  for (; v + 224 < vec_per_row; v += 256) {
+    uint4 q[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) q[u] = ld_nc_16(src + v + 32 * u);
+#pragma unroll
+    for (int u = 0; u < 8; ++u) st_16(dst + v + 32 * u, q[u]);
+  }
+  for (; v + 96 < vec_per_row; v += 128) {
+    uint4 q[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) q[u] = ld_nc_16(src + v + 32 * u);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) st_16(dst + v + 32 * u, q[u]);
+  }
+  for (; v < vec_per_row; v += 32) st_16(dst + v, ld_nc_16(src + v));
+}
+
 // Rows one warp sends between two counter updates. Small on purpose: the first tile of the carrying GEMM
 // cannot start before one whole round of groups has been sent, and that round lasts as long as one warp
 // needs for its group.
@@ -119,22 +141,7 @@ __device__ __forceinline__ bool dispatch_rows_warp(const DispatchFuse& d, int wo
       const int o = er / d.local_experts;
       const uint4* src = d.tokens + sr * d.vec_per_row;
       uint4* dst = static_cast<uint4*>(d.peer_data[o]) + dr * d.vec_per_row;
-      int v = lane;
-      for (; v + 224 < d.vec_per_row; v += 256) {  // eight loads in flight per lane
-        uint4 q[8];
-#pragma unroll
-        for (int u = 0; u < 8; ++u) q[u] = ld_nc_16(src + v + 32 * u);
-#pragma unroll
-        for (int u = 0; u < 8; ++u) st_16(dst + v + 32 * u, q[u]);
-      }
-      for (; v + 96 < d.vec_per_row; v += 128) {
-        uint4 q[4];
-#pragma unroll
-        for (int u = 0; u < 4; ++u) q[u] = ld_nc_16(src + v + 32 * u);
-#pragma unroll
-        for (int u = 0; u < 4; ++u) st_16(dst + v + 32 * u, q[u]);
-      }
-      for (; v < d.vec_per_row; v += 32) st_16(dst + v, ld_nc_16(src + v));
+      copy_row_warp(dst, src, d.vec_per_row, lane);
     }
     if (d.row_values != nullptr && e >= 0) {
       // the row's scalar (its routing probability) lands in the float plane behind the owner's rows
