@@ -380,6 +380,7 @@ SIGNATURES: dict[str, tuple] = {
     "hmc_ipc_close_handle": (_I, [_P]),
     "hmc_ep_publish_ready": (_I, [_P, _L, _L, _I, _P]),
     "hmc_store_words": (_I, [_P, _P, _L, _P]),
+    "hmc_store_words_pair": (_I, [_P, _P, _L, _P, _L, _P]),
     "hmc_ep_publish_source": (_I, [_P, _L, _L, _I, _P]),
     "hmc_ep_exchange_table_bytes": (_L, [_L, _L]),
     "hmc_ep_exchange_counts": (_I, [ctypes.POINTER(EpExchangeArgs), _P]),

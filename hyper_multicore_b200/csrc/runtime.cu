@@ -170,6 +170,30 @@ __global__ void store_words_kernel(int* __restrict__ dst, const int* __restrict_
 }
 }  // namespace
 
+namespace {
+__global__ void store_words_pair_kernel(int* __restrict__ dst, const int* __restrict__ first, long long first_words,
+                                        const int* __restrict__ second, long long second_words) {
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < first_words + second_words; i += stride)
+    dst[i] = i < first_words ? first[i] : second[i - first_words];
+  __threadfence_system();
+}
+}  // namespace
+
+extern "C" int hmc_store_words_pair(int32_t* dst, const int32_t* first, int64_t first_words, const int32_t* second,
+                                    int64_t second_words, void* stream_ptr) {
+  HMC_REQUIRE(dst != nullptr && first != nullptr && second != nullptr && first_words >= 0 && second_words >= 0,
+              HMC_ERR_INVALID, "hmc_store_words_pair: bad arguments");
+  const long long words = first_words + second_words;
+  if (words == 0) return 0;
+  hmc::ProfileScope profile(HMC_PROFILE_ROUTE, static_cast<cudaStream_t>(stream_ptr));
+  const int blocks = static_cast<int>(words < 256 * 64 ? (words + 255) / 256 : 64);
+  store_words_pair_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream_ptr)>>>(dst, first, first_words, second,
+                                                                                   second_words);
+  HMC_LAUNCH_OK();
+  return 0;
+}
+
 extern "C" int hmc_store_words(int32_t* dst, const int32_t* src, int64_t words, void* stream_ptr) {
   HMC_REQUIRE(dst != nullptr && src != nullptr && words >= 0, HMC_ERR_INVALID, "hmc_store_words: bad arguments");
   hmc::ProfileScope profile(HMC_PROFILE_ROUTE, static_cast<cudaStream_t>(stream_ptr));

@@ -138,6 +138,16 @@ def store_words(dst: torch.Tensor, src: torch.Tensor) -> None:
     _call("hmc_store_words", device, dst.data_ptr(), src.data_ptr(), src.numel())
 
 
+def store_words_pair(dst: torch.Tensor, first: torch.Tensor, second: torch.Tensor) -> None:
+    """dst = [first | second] for int32 tensors, by ONE kernel (see ``store_words``)."""
+    if any(t.dtype != torch.int32 for t in (dst, first, second)) or dst.numel() < first.numel() + second.numel():
+        raise ValueError("store_words_pair copies int32 words into a tensor at least as large")
+    if not (dst.is_cuda or dst.is_pinned()):
+        raise ValueError("store_words_pair writes device or pinned host memory")
+    device = _require_cuda(first, second)
+    _call("hmc_store_words_pair", device, dst.data_ptr(), first.data_ptr(), first.numel(), second.data_ptr(), second.numel())
+
+
 def grouped_gemm_combine_units(n: int) -> int:
     """Counter increments per result row of a fused-combine GEMM with ``n`` output columns."""
     return int(_lib.load().hmc_grouped_gemm_combine_units(n))

@@ -159,8 +159,7 @@ def prepare_route(hidden: torch.Tensor, topk_ids: torch.Tensor, *, num_experts: 
             pinned = _PINNED[key] = torch.empty(num_experts + status.numel(), dtype=torch.int32).pin_memory()
         # written by kernels, not by a copy engine: this read-back must not queue behind the caller's
         # own bulk device-to-host copies
-        kernels.store_words(pinned[:num_experts], counts)
-        kernels.store_words(pinned[num_experts:], status)
+        kernels.store_words_pair(pinned, counts, status)
         event = torch.cuda.Event()
         event.record()
         routed = tokens * top_k

@@ -613,6 +613,9 @@ int hmc_ep_exchange_counts(const hmc_ep_exchange_args* args, void* stream);
  * memory (device-accessible under unified addressing): small read-backs such as the route counts then do
  * not queue behind bulk device-to-host copies in a copy engine. No counterpart in the reference. */
 int hmc_store_words(int32_t* dst, const int32_t* src, int64_t words, void* stream);
+/* The same for two sources in one launch: dst[0 .. first_words) = first, then second behind it. */
+int hmc_store_words_pair(int32_t* dst, const int32_t* first, int64_t first_words, const int32_t* second,
+                         int64_t second_words, void* stream);
 int hmc_ep_publish_source(void* const* peer_ctrl, int64_t ep, int64_t rank, int32_t generation, void* stream);
 int hmc_ep_pull(const hmc_ep_pull_args* args, void* stream);
 int hmc_ep_combine(const hmc_ep_combine_args* args, void* stream);
