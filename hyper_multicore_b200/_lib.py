@@ -209,7 +209,7 @@ class MxGemmArgs(ctypes.Structure):
 
     _fields_ = [
         ("mode", c_int32), ("b_major", c_int32), ("epilogue", c_int32), ("groups", c_int32),
-        ("max_ctas", c_int32), ("reserved", c_int32),
+        ("max_ctas", c_int32), ("tile_mode", c_int32),
         ("rows", c_int64), ("pad_blocks", c_int64), ("m", c_int64), ("n", c_int64), ("k", c_int64),
         ("a", c_void_p), ("a_scale", c_void_p), ("b", c_void_p), ("b_scale", c_void_p), ("c", c_void_p),
         ("group_ends", c_void_p), ("status", c_void_p), ("combine", c_void_p),

@@ -14,109 +14,24 @@
 #include <cuda.h>
 
 #include "common.cuh"
+#include "mx_gemm_shared.cuh"
 #include "sm100.cuh"
 
 namespace hmc {
 namespace {
 
 using namespace sm100;
+using namespace mx;
 
 constexpr int BM = 128;
 constexpr int BN = 128;
-constexpr int BK = 128;
 constexpr int STAGES = 5;
 constexpr int ACC_STAGES = 2;
-constexpr int TILE_BYTES = 128 * 128;  // one operand tile, 16 KiB
-constexpr int ATOM_BYTES = 512;        // scale factors of 128 rows x 4 blocks of 32
 constexpr int STAGE_BYTES = 2 * TILE_BYTES;
-constexpr int EPI_WARPS = 8;
-constexpr int NUM_THREADS = 64 + EPI_WARPS * 32;
-constexpr int STORE_STAGE_BYTES = 32 * 128;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_WARPS * STORE_STAGE_BYTES + STAGES * 2 * ATOM_BYTES + 1024 + 256;
-constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t TMEM_SFA_COL = ACC_STAGES * BN;  // 4 columns
 constexpr uint32_t TMEM_SFB_COL = TMEM_SFA_COL + 4;
-constexpr uint32_t SWIZZLE_128B = 2;
-constexpr uint64_t PIPE_BUDGET_NS = 4ull * 1000 * 1000 * 1000;
-
-struct Params {
-  int mode;
-  int epilogue;
-  int groups;
-  int m;        // RAGGED_K: rows of C per group
-  int n;
-  int k;        // RAGGED_M: contraction length
-  int n_tiles;
-  int m_tiles;  // RAGGED_K
-  int k_blocks; // RAGGED_M: k / 128
-  int pad_blocks;
-  long long rows;
-  const long long* group_ends;
-  const uint8_t* a_scale;
-  const uint8_t* b_scale;
-  void* c;
-  int* status;
-  int combine_enabled;  // RAGGED_M: rows go to `combine` destinations instead of c
-  CombineFuse combine;
-};
-
-struct Tile {
-  int group;
-  int m_idx;
-  int n_idx;
-  long long row0;     // un-padded first row of the group
-  long long row1;
-  int pad_block0;     // first 128-row block of the group in the padded layout
-  int blocks;         // 128-row blocks of the group
-};
-
-struct TileWalker {
-  const Params& p;
-  int group = 0;
-  long long base = 0;
-  long long row0 = 0;
-  long long row1 = 0;
-  int pad_block0 = 0;
-  int blocks = 0;
-  int tiles_in_group = 0;
-
-  __device__ explicit TileWalker(const Params& params) : p(params) { load_group(); }
-
-  __device__ void load_group() {
-    if (group >= p.groups) {
-      tiles_in_group = 0;
-      return;
-    }
-    row0 = group == 0 ? 0 : p.group_ends[group - 1];
-    row1 = p.group_ends[group];
-    blocks = static_cast<int>((row1 - row0 + 127) / 128);
-    tiles_in_group = p.mode == HMC_GEMM_RAGGED_M ? blocks * p.n_tiles : p.m_tiles * p.n_tiles;
-  }
-
-  __device__ bool get(long long idx, Tile& t) {
-    while (group < p.groups && idx >= base + tiles_in_group) {
-      base += tiles_in_group;
-      pad_block0 += blocks;
-      ++group;
-      load_group();
-    }
-    if (group >= p.groups) return false;
-    const int local = static_cast<int>(idx - base);
-    const int mt = p.mode == HMC_GEMM_RAGGED_M ? blocks : p.m_tiles;
-    t.group = group;
-    t.m_idx = local % mt;
-    t.n_idx = local / mt;
-    t.row0 = row0;
-    t.row1 = row1;
-    t.pad_block0 = pad_block0;
-    t.blocks = blocks;
-    return true;
-  }
-};
-
-__device__ __forceinline__ int k_iterations(const Params& p, const Tile& t) {
-  return p.mode == HMC_GEMM_RAGGED_M ? p.k_blocks : t.blocks;
-}
+using TileWalker = TileWalkerT<1>;
 
 template <int A_MAJOR, int B_MAJOR>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
@@ -356,28 +271,8 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         // finds the destination of its own row; the 32 x 64-column piece is staged in shared memory so
         // that every store instruction writes whole 128-byte pieces of four rows.
         const long long out_row = t.row0 + static_cast<long long>(t.m_idx) * BM + row_in_tile;
-        const bool row_ok = out_row < t.row1;
-        unsigned long long dst_bits = 0;
         int source = -1;
-        if (row_ok) {
-          if (p.combine_enabled) {
-            const CombineFuse& cf = p.combine;
-            const long long* seg = cf.segment_start + static_cast<long long>(t.group) * cf.ep;
-            int s = 0;
-            for (int q = 1; q < cf.ep; ++q)
-              if (seg[q] <= out_row) s = q;
-            const long long dest = cf.combine_target_off[s * cf.local_experts + t.group] + (out_row - seg[s]);
-            if (dest >= 0 && dest < cf.target_rows_limit) {
-              source = s;
-              dst_bits = reinterpret_cast<unsigned long long>(static_cast<__nv_bfloat16*>(cf.peer_data[s]) +
-                                                              dest * p.n + col_base);
-            } else {
-              report_status(p.status, HMC_STATUS_BAD_INDEX, static_cast<int>(out_row), s, static_cast<int>(dest));
-            }
-          } else {
-            dst_bits = reinterpret_cast<unsigned long long>(static_cast<__nv_bfloat16*>(p.c) + out_row * p.n + col_base);
-          }
-        }
+        const unsigned long long dst_bits = mx_row_destination(p, t, out_row, col_base, source);
         if (store_pending) {  // an earlier weight-gradient tile may still be reading the stage
           if (lane == 0) bulk_wait_read_all();
           __syncwarp();
@@ -442,45 +337,6 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
 }
 
 // ----------------------------------------------------------------------------- host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
-                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
-                                  CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (fn == nullptr) {
-    void* sym = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
-        qres == cudaDriverEntryPointSuccess) {
-      fn = reinterpret_cast<EncodeTiledFn>(sym);
-    }
-  }
-  return fn;
-}
-
-// elem: 1 = uint8 (E4M3 payload), 2 = bf16, 4 = f32. dims[0] innermost; 128-byte swizzle.
-int make_map(CUtensorMap* out, const void* base, int rank, const cuuint64_t* dims, const cuuint32_t* box, int elem) {
-  EncodeTiledFn fn = encode_fn();
-  HMC_REQUIRE(fn != nullptr, HMC_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
-  cuuint64_t strides[4];
-  cuuint64_t acc = static_cast<cuuint64_t>(elem);
-  for (int i = 0; i + 1 < rank; ++i) {
-    acc *= dims[i];
-    strides[i] = acc;
-  }
-  cuuint32_t elem_strides[5] = {1, 1, 1, 1, 1};
-  const CUtensorMapDataType type = elem == 1   ? CU_TENSOR_MAP_DATA_TYPE_UINT8
-                                   : elem == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
-                                               : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
-  CUresult r = fn(out, type, static_cast<cuuint32_t>(rank), const_cast<void*>(base), dims, strides, box, elem_strides,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  HMC_REQUIRE(r == CUDA_SUCCESS, HMC_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
-  return 0;
-}
-
 template <int A_MAJOR, int B_MAJOR>
 int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const Params& p, int grid,
            cudaStream_t stream) {
@@ -502,6 +358,7 @@ extern "C" int64_t hmc_mx_gemm_combine_units(int64_t n) {
 
 extern "C" int hmc_mx_gemm(const hmc_mx_gemm_args* args, void* stream_ptr) {
   using namespace hmc;
+  using namespace hmc::mx;
   HMC_REQUIRE(args != nullptr, HMC_ERR_INVALID, "hmc_mx_gemm: null args");
   const hmc_mx_gemm_args& a = *args;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
@@ -533,6 +390,14 @@ extern "C" int hmc_mx_gemm(const hmc_mx_gemm_args* args, void* stream_ptr) {
   p.status = a.status;
   p.n = static_cast<int>(a.n);
   p.n_tiles = static_cast<int>(a.n / BN);
+  p.n_atoms = p.n_tiles;
+  HMC_REQUIRE(a.tile_mode == HMC_TILE_AUTO || a.tile_mode == HMC_TILE_SINGLE || a.tile_mode == HMC_TILE_PAIR, HMC_ERR_INVALID,
+              "hmc_mx_gemm: unknown tile_mode %d", a.tile_mode);
+  // CTA pairs work on 256 x 256 tiles: twice the flops per operand byte brought into shared memory.
+  const bool pair_shape = a.n % 256 == 0 && (a.mode == HMC_GEMM_RAGGED_M || a.m % 256 == 0) && sm_count() >= 2;
+  HMC_REQUIRE(a.tile_mode != HMC_TILE_PAIR || pair_shape, HMC_ERR_LIMIT,
+              "hmc_mx_gemm: CTA-pair tiles need n (and m for RAGGED_K) to be multiples of 256");
+  const bool use_pairs = pair_shape && a.tile_mode != HMC_TILE_SINGLE;
   if (a.combine != nullptr) {
     const hmc_gemm_combine& cb = *a.combine;
     HMC_REQUIRE(a.mode == HMC_GEMM_RAGGED_M, HMC_ERR_INVALID, "hmc_mx_gemm: the fused combine belongs to RAGGED_M GEMMs");
@@ -585,6 +450,7 @@ extern "C" int hmc_mx_gemm(const hmc_mx_gemm_args* args, void* stream_ptr) {
                 "hmc_mx_gemm: m (%lld) must be a positive multiple of 128", (long long)a.m);
     p.m = static_cast<int>(a.m);
     p.m_tiles = static_cast<int>(a.m / BM);
+    p.m_atoms = p.m_tiles;
     {
       cuuint64_t dims[2] = {static_cast<cuuint64_t>(a.m), pad_rows};
       cuuint32_t box[2] = {128, 128};
@@ -604,6 +470,20 @@ extern "C" int hmc_mx_gemm(const hmc_mx_gemm_args* args, void* stream_ptr) {
   }
   int grid = a.max_ctas > 0 ? a.max_ctas : sm_count();
   if (grid > sm_count()) grid = sm_count();
+  if (use_pairs) {
+    CUtensorMap tsa, tsb;
+    const long long a_atoms = a.mode == HMC_GEMM_RAGGED_M ? static_cast<long long>(p.k_blocks) * p.pad_blocks
+                                                          : static_cast<long long>(p.pad_blocks) * p.m_atoms;
+    const long long b_atoms = a.mode == HMC_GEMM_RAGGED_M ? static_cast<long long>(p.groups) * p.k_blocks * p.n_atoms
+                                                          : static_cast<long long>(p.pad_blocks) * p.n_atoms;
+    if ((rc = make_atom_map(&tsa, a.a_scale, a_atoms, 1)) != 0) return rc;
+    if ((rc = make_atom_map(&tsb, a.b_scale, b_atoms, 2)) != 0) return rc;
+    p.n_tiles = p.n_atoms / 2;
+    p.m_tiles = p.m_atoms / 2;
+    const int a_major = a.mode == HMC_GEMM_RAGGED_K ? HMC_MAJOR_MN : HMC_MAJOR_K;
+    const int b_major = a.mode == HMC_GEMM_RAGGED_K ? HMC_MAJOR_MN : a.b_major;
+    return launch_mx_gemm_pair(ta, tb, tc, tsa, tsb, p, a_major, b_major, grid, stream);
+  }
   if (a.mode == HMC_GEMM_RAGGED_K) {
     const long long tiles = static_cast<long long>(p.groups) * p.m_tiles * p.n_tiles;
     if (tiles < grid) grid = static_cast<int>(tiles);

@@ -1,0 +1,393 @@
+// CTA-pair variant of the block-scaled FP8 grouped GEMM: two CTAs of a cluster share one 256 x 256 tile
+// (tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale, M = 256, N = 256, K = 32 per instruction).
+//
+// Per 128-element k-block each CTA brings 16 KiB of A (its own 128 rows), 16 KiB of B (its own 128 of the
+// tile's 256 columns), the scale atom of its A rows and the two atoms of all 256 B columns into shared
+// memory: half the operand bytes per flop of the 128 x 128 one-CTA kernel, whose tensor pipe idles two
+// thirds of the time behind the L2 -> shared-memory stream.
+//
+// The 256 accumulator columns plus the scale columns leave no room for a second accumulator in the 512
+// columns of tensor memory. The epilogue therefore drains the whole accumulator into registers first
+// (128 values per thread), hands the tensor memory back to the MMA issuer, and only then converts and
+// stores, so the next tile's MMAs overlap the stores.
+//
+// Roles as in the other pair kernels: warp 0 = TMA producer (both CTAs), warp 1 = MMA issuer (leader) and
+// TMEM owner, warps 2..9 = epilogue (both CTAs, each on its own 128 accumulator rows).
+//
+// Replaces the reference's MX GMM worker (hyper_multicore/ops/common/mega_moe/adapters/arch35/gmm/
+// mxfp8_worker.h:15-159; layouts NN forward, NT for dA / dX, TN for dW: tasks/gmm_mxfp8.py).
+#include <cuda.h>
+
+#include "common.cuh"
+#include "mx_gemm_shared.cuh"
+#include "sm100.cuh"
+
+namespace hmc {
+namespace mx {
+namespace {
+
+using namespace sm100;
+
+constexpr int PAIR_N = 256;
+constexpr int PAIR_STAGES = 5;
+constexpr int PAIR_DATA_BYTES = 2 * TILE_BYTES;  // this CTA's A rows and B columns of one k-block
+constexpr int PAIR_SF_BYTES = 3 * ATOM_BYTES;    // scale atoms: own A rows, then both halves of B
+constexpr int PAIR_SMEM_BYTES =
+    PAIR_STAGES * PAIR_DATA_BYTES + EPI_WARPS * STORE_STAGE_BYTES + PAIR_STAGES * PAIR_SF_BYTES + 1024 + 256;
+// Tensor memory: accumulator in columns [0, 256); four rotating 16-column scale slots behind it
+// (A scales in the first 4 columns of a slot, B scales in its last 8).
+constexpr uint32_t TMEM_SF_COL = PAIR_N;
+constexpr uint32_t SF_SLOT_COLS = 16;
+constexpr int SF_SLOTS = 4;
+using PairWalker = TileWalkerT<2>;
+
+template <int A_MAJOR, int B_MAJOR>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                    const __grid_constant__ CUtensorMap tm_c, const __grid_constant__ CUtensorMap tm_sa,
+                    const __grid_constant__ CUtensorMap tm_sb, const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* store_stage = smem + PAIR_STAGES * PAIR_DATA_BYTES;
+  uint8_t* sf_stage = store_stage + EPI_WARPS * STORE_STAGE_BYTES;  // [PAIR_STAGES][3][ATOM_BYTES]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sf_stage + PAIR_STAGES * PAIR_SF_BYTES);
+  uint64_t* full_bar = bars;                      // leader only: loads of both CTAs
+  uint64_t* empty_bar = bars + PAIR_STAGES;       // one set per CTA
+  uint64_t* acc_full_bar = bars + 2 * PAIR_STAGES;      // one per CTA
+  uint64_t* acc_empty_bar = bars + 2 * PAIR_STAGES + 1;  // leader only
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * PAIR_STAGES + 2);
+  volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();  // 0 = leader
+  const long long pair = blockIdx.x >> 1;
+  const long long pairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < PAIR_STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(acc_full_bar, 1);
+    mbar_init(acc_empty_bar, 2 * EPI_WARPS);  // every epilogue warp of both CTAs
+    *abort_word = 0;
+    mbar_fence_init();
+    prefetch_tensormap(&tm_a);
+    prefetch_tensormap(&tm_b);
+    prefetch_tensormap(&tm_sa);
+    prefetch_tensormap(&tm_sb);
+    if (p.mode == HMC_GEMM_RAGGED_K) prefetch_tensormap(&tm_c);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();  // both CTAs' barriers exist before any cross-CTA signal
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ======================================================================== TMA producer (both CTAs)
+    if (lane == 0) {
+      PairWalker walker(p);
+      Tile t;
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (long long idx = pair; ok && walker.get(idx, t); idx += pairs) {
+        const int kiters = k_iterations(p, t);
+        // RAGGED_M: this CTA's 128-row block of the tile. The second CTA of a group's last, half-empty tile
+        // repeats the group's last block; its rows lie past the group's end and are never stored.
+        int block = 2 * t.m_idx + static_cast<int>(rank);
+        if (block >= t.blocks) block = t.blocks - 1;
+        const int n0 = t.n_idx * PAIR_N + static_cast<int>(rank) * 128;  // this CTA's columns of B
+        for (int kb = 0; kb < kiters; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_word, PIPE_BUDGET_NS)) {
+            report_status(p.status, HMC_STATUS_TIMEOUT_PIPELINE, 0, stage, kb);
+            ok = false;
+            break;
+          }
+          uint8_t* a_dst = smem + stage * PAIR_DATA_BYTES;
+          uint8_t* b_dst = a_dst + TILE_BYTES;
+          uint8_t* sfa_dst = sf_stage + stage * PAIR_SF_BYTES;
+          uint8_t* sfb_dst = sfa_dst + ATOM_BYTES;
+          // the leader's barrier counts the bytes of both CTAs
+          if (rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * (PAIR_DATA_BYTES + PAIR_SF_BYTES));
+          if (p.mode == HMC_GEMM_RAGGED_M) {
+            const int pad_block = t.pad_block0 + block;
+            tma_load_2d_pair(a_dst, &tm_a, &full_bar[stage], kb * BK, pad_block * 128);
+            if (B_MAJOR == HMC_MAJOR_MN) tma_load_3d_pair(b_dst, &tm_b, &full_bar[stage], n0, kb * BK, t.group);
+            else tma_load_3d_pair(b_dst, &tm_b, &full_bar[stage], kb * BK, n0, t.group);
+            tma_load_2d_pair(sfa_dst, &tm_sa, &full_bar[stage], 0, kb * p.pad_blocks + pad_block);
+            tma_load_2d_pair(sfb_dst, &tm_sb, &full_bar[stage], 0, (t.group * p.k_blocks + kb) * p.n_atoms + 2 * t.n_idx);
+          } else {
+            const int pad_block = t.pad_block0 + kb;
+            const int m0 = t.m_idx * 256 + static_cast<int>(rank) * 128;
+            tma_load_2d_pair(a_dst, &tm_a, &full_bar[stage], m0, pad_block * 128);
+            tma_load_2d_pair(b_dst, &tm_b, &full_bar[stage], n0, pad_block * 128);
+            tma_load_2d_pair(sfa_dst, &tm_sa, &full_bar[stage], 0, pad_block * p.m_atoms + 2 * t.m_idx + static_cast<int>(rank));
+            tma_load_2d_pair(sfb_dst, &tm_sb, &full_bar[stage], 0, pad_block * p.n_atoms + 2 * t.n_idx);
+          }
+          if (++stage == PAIR_STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ======================================================================== MMA issuer (leader only)
+    if (rank == 0) {
+      PairWalker walker(p);
+      Tile t;
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t acc_phase = 0;
+      int sf_slot = 0;
+      bool ok = true;
+      // K-major: a K=32 step is 32 bytes along the 128-byte row. MN-major: 32 k-rows of 128 bytes.
+      constexpr uint32_t A_KSTEP = A_MAJOR == HMC_MAJOR_MN ? (32 * 128) >> 4 : 32 >> 4;
+      constexpr uint32_t B_KSTEP = B_MAJOR == HMC_MAJOR_MN ? (32 * 128) >> 4 : 32 >> 4;
+      for (long long idx = pair; ok && walker.get(idx, t); idx += pairs) {
+        const int kiters = k_iterations(p, t);
+        if (kiters == 0) continue;  // cold group: the epilogue writes zeros on its own
+        if (!mbar_wait(acc_empty_bar, acc_phase ^ 1u, abort_word, PIPE_BUDGET_NS)) {
+          if (lane == 0) report_status(p.status, HMC_STATUS_TIMEOUT_PIPELINE, 1, 0, 0);
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        for (int kb = 0; kb < kiters; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_word, PIPE_BUDGET_NS)) {
+            if (lane == 0) report_status(p.status, HMC_STATUS_TIMEOUT_PIPELINE, 2, stage, kb);
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          if (lane == 0) {
+            uint8_t* a_src = smem + stage * PAIR_DATA_BYTES;
+            uint8_t* b_src = a_src + TILE_BYTES;
+            uint8_t* sf_src = sf_stage + stage * PAIR_SF_BYTES;
+            const uint32_t tmem_sfa = tmem_base + TMEM_SF_COL + static_cast<uint32_t>(sf_slot) * SF_SLOT_COLS;
+            const uint32_t tmem_sfb = tmem_sfa + 8;
+            // scale atoms: un-swizzled, 8-row groups of 16 bytes are 128 bytes apart
+            tmem_cp_sf_pair(tmem_sfa, make_smem_desc(smem_u32(sf_src), 0, 128, 0));
+            tmem_cp_sf_pair(tmem_sfb, make_smem_desc(smem_u32(sf_src + ATOM_BYTES), 0, 128, 0));
+            tmem_cp_sf_pair(tmem_sfb + 4, make_smem_desc(smem_u32(sf_src + 2 * ATOM_BYTES), 0, 128, 0));
+            uint64_t da = make_smem_desc(smem_u32(a_src), A_MAJOR == HMC_MAJOR_MN ? TILE_BYTES : 16, 1024, SWIZZLE_128B);
+            uint64_t db = make_smem_desc(smem_u32(b_src), B_MAJOR == HMC_MAJOR_MN ? TILE_BYTES : 16, 1024, SWIZZLE_128B);
+#pragma unroll
+            for (int ks = 0; ks < BK / 32; ++ks) {
+              umma_mxf8_pair(tmem_base, da, db, make_idesc_mxf8(256, PAIR_N, A_MAJOR, B_MAJOR, ks), tmem_sfa, tmem_sfb,
+                             (kb > 0 || ks > 0) ? 1u : 0u);
+              da += A_KSTEP;
+              db += B_KSTEP;
+            }
+            umma_commit_pair(&empty_bar[stage]);  // frees the slot in both CTAs
+            if (kb == kiters - 1) umma_commit_pair(acc_full_bar);
+          }
+          __syncwarp();
+          sf_slot = (sf_slot + 1) & (SF_SLOTS - 1);
+          if (++stage == PAIR_STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        acc_phase ^= 1u;
+      }
+    }
+  } else {
+    // ======================================================================== epilogue (both CTAs)
+    PairWalker walker(p);
+    Tile t;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    const int quarter = warp & 3;       // TMEM lane quarter this warp may read
+    const int half = (warp - 2) >> 2;   // which 128 of the tile's 256 columns this warp handles
+    const int row_in_cta = quarter * 32 + lane;
+    uint8_t* my_stage = store_stage + (warp - 2) * STORE_STAGE_BYTES;
+    const uint32_t leader_acc_empty = map_to_cta(smem_u32(acc_empty_bar), 0);
+    bool store_pending = false;
+    for (long long idx = pair; ok && walker.get(idx, t); idx += pairs) {
+      const int kiters = k_iterations(p, t);
+      const int col_base = t.n_idx * PAIR_N + half * 128;
+      if (kiters == 0) {
+        // cold group of a weight-gradient GEMM: exact zeros, no accumulator involved
+        const int m = t.m_idx * 256 + static_cast<int>(rank) * 128 + row_in_cta;
+        if (m < p.m) {
+          const long long out_row = static_cast<long long>(t.group) * p.m + m;
+          if (p.epilogue == HMC_EPI_STORE_F32) {
+            float* dst = static_cast<float*>(p.c) + out_row * p.n + col_base;
+            for (int c = 0; c < 128; c += 4) *reinterpret_cast<float4*>(dst + c) = make_float4(0.f, 0.f, 0.f, 0.f);
+          } else {
+            __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.c) + out_row * p.n + col_base;
+            for (int c = 0; c < 128; c += 8) *reinterpret_cast<uint4*>(dst + c) = make_uint4(0, 0, 0, 0);
+          }
+        }
+        continue;
+      }
+      if (!mbar_wait(acc_full_bar, acc_phase, abort_word, PIPE_BUDGET_NS)) {
+        if (lane == 0) report_status(p.status, HMC_STATUS_TIMEOUT_PIPELINE, 3, 0, 0);
+        ok = false;
+        break;
+      }
+      acc_phase ^= 1u;
+      tc_fence_after_sync();
+      // The warp's 32 rows x 128 columns leave tensor memory in one go; the accumulator is then free again.
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(half * 128);
+      uint32_t v[4][32];
+      tmem_ld_32x32(taddr, v[0]);
+      tmem_ld_32x32(taddr + 32, v[1]);
+      tmem_ld_32x32(taddr + 64, v[2]);
+      tmem_ld_32x32(taddr + 96, v[3]);
+      tmem_ld_wait();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(leader_acc_empty);  // the MMA issuer lives in the leader
+
+      uint8_t* row_base = my_stage + lane * 128;
+      if (p.mode == HMC_GEMM_RAGGED_K) {
+        const bool f32 = p.epilogue == HMC_EPI_STORE_F32;
+        const int m0 = t.m_idx * 256 + static_cast<int>(rank) * 128 + quarter * 32;
+        if (f32) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {  // four boxes of 32 rows x 32 floats
+            if (store_pending) {
+              if (lane == 0) bulk_wait_read_all();
+              __syncwarp();
+            }
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+              *reinterpret_cast<uint4*>(row_base + ((q ^ (lane & 7)) << 4)) =
+                  make_uint4(v[j][4 * q], v[j][4 * q + 1], v[j][4 * q + 2], v[j][4 * q + 3]);
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_3d(&tm_c, my_stage, col_base + 32 * j, m0, t.group);
+              bulk_commit_group();
+            }
+            store_pending = true;
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {  // two boxes of 32 rows x 64 bf16
+            if (store_pending) {
+              if (lane == 0) bulk_wait_read_all();
+              __syncwarp();
+            }
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              const uint32_t* src = v[2 * j + (q >> 2)] + 8 * (q & 3);
+              uint4 o;
+              o.x = pack_bf16x2(__uint_as_float(src[0]), __uint_as_float(src[1]));
+              o.y = pack_bf16x2(__uint_as_float(src[2]), __uint_as_float(src[3]));
+              o.z = pack_bf16x2(__uint_as_float(src[4]), __uint_as_float(src[5]));
+              o.w = pack_bf16x2(__uint_as_float(src[6]), __uint_as_float(src[7]));
+              *reinterpret_cast<uint4*>(row_base + ((q ^ (lane & 7)) << 4)) = o;
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_3d(&tm_c, my_stage, col_base + 64 * j, m0, t.group);
+              bulk_commit_group();
+            }
+            store_pending = true;
+          }
+        }
+      } else {
+        // Rows go out in the un-padded layout (rows of the tile past the group's end are padding), into c
+        // or - fused combine - into the routed buffers of their source ranks. Each lane finds the
+        // destination of its own row; 64-column pieces are staged in shared memory so that every store
+        // instruction writes whole 128-byte pieces of four rows.
+        const long long out_row =
+            t.row0 + (2ll * t.m_idx + static_cast<long long>(rank)) * 128 + row_in_cta;
+        int source = -1;
+        const unsigned long long dst_bits = mx_row_destination(p, t, out_row, col_base, source);
+        if (store_pending) {  // an earlier weight-gradient tile may still be reading the stage
+          if (lane == 0) bulk_wait_read_all();
+          __syncwarp();
+          store_pending = false;
+        }
+        const int sub = lane >> 3;
+        const int piece = lane & 7;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            const uint32_t* src = v[2 * j + (q >> 2)] + 8 * (q & 3);
+            uint4 o;
+            o.x = pack_bf16x2(__uint_as_float(src[0]), __uint_as_float(src[1]));
+            o.y = pack_bf16x2(__uint_as_float(src[2]), __uint_as_float(src[3]));
+            o.z = pack_bf16x2(__uint_as_float(src[4]), __uint_as_float(src[5]));
+            o.w = pack_bf16x2(__uint_as_float(src[6]), __uint_as_float(src[7]));
+            *reinterpret_cast<uint4*>(row_base + ((q ^ (lane & 7)) << 4)) = o;
+          }
+          __syncwarp();
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            const int r = i + sub;
+            const unsigned long long base = __shfl_sync(0xffffffffu, dst_bits, r);
+            if (base != 0) {
+              const uint4 val = *reinterpret_cast<const uint4*>(my_stage + r * 128 + ((piece ^ (r & 7)) << 4));
+              st_16(reinterpret_cast<uint8_t*>(base) + j * 128 + piece * 16, val);
+            }
+          }
+          __syncwarp();
+        }
+        if (p.combine_enabled) {
+          // One release-add per destination per warp; the warp barrier above orders the lanes' stores. A warp
+          // covers 128 columns, which count as two of the 64-column units the receiver waits for.
+          const unsigned same = __match_any_sync(0xffffffffu, source);
+          if (source >= 0 && lane == __ffs(same) - 1)
+            red_release_sys_add(p.combine.peer_ctrl[source] + HMC_CTRL_COMBINE, 2 * __popc(same));
+        }
+      }
+    }
+    if (store_pending && lane == 0) bulk_wait_all();  // this thread's stores are in global memory
+  }
+
+  // Teardown: no CTA may leave while its partner can still reach into its shared memory or TMEM.
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc_pair(tmem_base, TMEM_COLS);
+  }
+}
+
+template <int A_MAJOR, int B_MAJOR>
+int launch_impl(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& tsa,
+                const CUtensorMap& tsb, const Params& p, int grid, cudaStream_t stream) {
+  static PerDeviceFlag configured{};
+  auto kernel = mx_gemm_pair_kernel<A_MAJOR, B_MAJOR>;
+  if (int rc = allow_dynamic_smem(kernel, PAIR_SMEM_BYTES, configured)) return rc;
+  kernel<<<grid, NUM_THREADS, PAIR_SMEM_BYTES, stream>>>(ta, tb, tc, tsa, tsb, p);
+  HMC_LAUNCH_OK();
+  return 0;
+}
+
+}  // namespace
+
+// Called by hmc_mx_gemm when n (and m for RAGGED_K) are multiples of 256. `p.n_tiles` and `p.m_tiles` count
+// 256-wide tiles; the scale atoms are still indexed by 128 (`p.n_atoms`, `p.m_atoms`).
+int launch_mx_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& tsa,
+                        const CUtensorMap& tsb, const Params& p, int a_major, int b_major, int grid, cudaStream_t stream) {
+  grid &= ~1;  // whole pairs
+  if (grid < 2) grid = 2;
+  if (p.mode == HMC_GEMM_RAGGED_K) {
+    const long long tiles = static_cast<long long>(p.groups) * p.m_tiles * p.n_tiles;
+    if (2 * tiles < grid) grid = static_cast<int>(2 * tiles);
+    return launch_impl<HMC_MAJOR_MN, HMC_MAJOR_MN>(ta, tb, tc, tsa, tsb, p, grid, stream);
+  }
+  (void)a_major;
+  if (b_major == HMC_MAJOR_MN) return launch_impl<HMC_MAJOR_K, HMC_MAJOR_MN>(ta, tb, tc, tsa, tsb, p, grid, stream);
+  return launch_impl<HMC_MAJOR_K, HMC_MAJOR_K>(ta, tb, tc, tsa, tsb, p, grid, stream);
+}
+
+}  // namespace mx
+}  // namespace hmc

@@ -311,6 +311,22 @@ __device__ __forceinline__ void umma_mxf8(uint32_t tmem_d, uint64_t desc_a, uint
 __device__ __forceinline__ void tmem_cp_sf(uint32_t taddr, uint64_t smem_desc) {
   asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(smem_desc) : "memory");
 }
+// CTA-pair forms, issued by one thread of the leader. The MMA takes A, B and both scale sets from the same
+// offsets in each CTA's shared / tensor memory; the copy moves each CTA's own atom into its own TMEM.
+__device__ __forceinline__ void umma_mxf8_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                               uint32_t tmem_sfa, uint32_t tmem_sfb, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t"
+      "}\n" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_cp_sf_pair(uint32_t taddr, uint64_t smem_desc) {
+  asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(smem_desc) : "memory");
+}
 // Untiled bulk copy global -> shared, completing on an mbarrier (16-byte aligned, size % 16 == 0).
 __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(

@@ -535,13 +535,15 @@ def mx_gemm_combine_units(n: int) -> int:
 
 
 def mx_gemm(a, a_scale, b, b_scale, c, group_ends, *, mode, rows, pad_blocks, n, k=0, m=0,
-            b_major=HMC_MAJOR_MN, epilogue=HMC_EPI_STORE_BF16, status=None, max_ctas=0, combine=None) -> None:
+            b_major=HMC_MAJOR_MN, epilogue=HMC_EPI_STORE_BF16, status=None, max_ctas=0, combine=None,
+            tile_mode=0) -> None:
     """Block-scaled FP8 grouped GEMM; see ``hmc_mx_gemm_args`` for the operand layouts. ``combine`` as in
-    ``grouped_gemm``: the rows leave the epilogue for their source ranks and ``c`` may be None."""
+    ``grouped_gemm``: the rows leave the epilogue for their source ranks and ``c`` may be None. ``tile_mode``:
+    0 = 256 x 256 CTA-pair tiles where the shape allows, 1 = 128 x 128 tiles, 2 = pairs or an error."""
     device = _require_cuda(a, a_scale, b, b_scale, c, group_ends, status)
     args = _lib.MxGemmArgs()
     args.mode, args.b_major, args.epilogue = mode, b_major, epilogue
-    args.groups, args.max_ctas = group_ends.numel(), max_ctas
+    args.groups, args.max_ctas, args.tile_mode = group_ends.numel(), max_ctas, tile_mode
     args.rows, args.pad_blocks, args.m, args.n, args.k = rows, pad_blocks, m, n, k
     args.a, args.a_scale = a.data_ptr(), a_scale.data_ptr()
     args.b, args.b_scale = b.data_ptr(), b_scale.data_ptr()

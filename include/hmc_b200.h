@@ -183,7 +183,8 @@ typedef struct hmc_mx_gemm_args {
   int32_t epilogue; /* HMC_EPI_STORE_BF16, or HMC_EPI_STORE_F32 (RAGGED_K only) */
   int32_t groups;
   int32_t max_ctas;
-  int32_t reserved;
+  int32_t tile_mode;  /* HMC_TILE_AUTO, _SINGLE (128 x 128 tiles) or _PAIR (256 x 256 CTA-pair tiles; needs n % 256 == 0,
+                         and m % 256 == 0 for RAGGED_K). AUTO takes pairs wherever the shape allows them. */
   int64_t rows;       /* un-padded rows (sum of the groups) */
   int64_t pad_blocks; /* 128-row blocks the padded activation buffers hold */
   int64_t m;          /* RAGGED_K only */

@@ -159,6 +159,53 @@ def test_mxfp8_experts_forward_backward(cuda_device, tokens, hidden, inter, expe
     assert (w1.grad[1] == 0).all() and (w2.grad[1] == 0).all(), "cold expert gradients must be exact zeros"
 
 
+@pytest.mark.parametrize("counts", [[300, 0, 129, 640, 1, 256], [128], [1000, 385]])
+def test_cta_pair_tiles_equal_one_cta_tiles_bit_for_bit(cuda_device, counts):
+    """The 256 x 256 CTA-pair kernel and the 128 x 128 kernel accumulate the same products in the same order,
+    so all three layouts (NN forward, NT for dA / dX, TN for the weight gradients) must agree exactly; the
+    one-CTA kernel is the one checked against the oracle above. Groups with an odd number of 128-row blocks
+    leave half a pair tile empty; a group without rows gets exact-zero weight gradients."""
+    from hyper_multicore_b200 import kernels as K
+
+    dev = cuda_device
+    g = torch.Generator().manual_seed(len(counts))
+    experts, rows, k, n = len(counts), sum(counts), 512, 768
+    ends = torch.tensor(counts, dtype=torch.int64).cumsum(0).to(dev)
+    x = torch.randn(rows, k, generator=g).bfloat16().to(dev)
+    dy = torch.randn(rows, n, generator=g).bfloat16().to(dev)
+    w = (torch.randn(experts, k, n, generator=g) * 0.05).bfloat16().to(dev)
+    fields = K.mx_quant_weight(w)
+    xq = K.mx_quant(x, ends, k, want_row=True, want_col=True)
+    dyq = K.mx_quant(dy, ends, n, want_row=True, want_col=True)
+    status = torch.zeros(4, dtype=torch.int32, device=dev)
+
+    def both(run, shape, dtype=torch.bfloat16):
+        outs = []
+        for tile_mode in (1, 2):
+            c = torch.full(shape, 7.0, dtype=dtype, device=dev)
+            run(c, tile_mode)
+            outs.append(c)
+        assert int(status[0]) == 0, status.tolist()
+        assert torch.isfinite(outs[0].float()).all() and outs[0].float().abs().sum() > 0
+        assert torch.equal(outs[0], outs[1])
+
+    # NN: y = x @ w, scales of w along its rows (the contraction)
+    col_atoms = K.mx_pack_weight_scale(fields["col_scale"], 0, experts, k, n)
+    both(lambda c, tm: K.mx_gemm(xq.row_data, xq.row_scale, fields["col_data"], col_atoms, c, ends, mode=K.HMC_GEMM_RAGGED_M,
+                                 rows=rows, pad_blocks=xq.pad_blocks, n=n, k=k, b_major=K.HMC_MAJOR_MN, status=status,
+                                 tile_mode=tm), (rows, n))
+    # NT: dx = dy @ w^T, scales of w along its columns
+    row_atoms = K.mx_pack_weight_scale(fields["row_scale"], 1, experts, k, n)
+    both(lambda c, tm: K.mx_gemm(dyq.row_data, dyq.row_scale, fields["row_data"], row_atoms, c, ends, mode=K.HMC_GEMM_RAGGED_M,
+                                 rows=rows, pad_blocks=dyq.pad_blocks, n=k, k=n, b_major=K.HMC_MAJOR_K, status=status,
+                                 tile_mode=tm), (rows, k))
+    # TN: dw = x^T @ dy per group, both operands quantised down the rows
+    for epilogue, dtype in ((K.HMC_EPI_STORE_BF16, torch.bfloat16), (K.HMC_EPI_STORE_F32, torch.float32)):
+        both(lambda c, tm: K.mx_gemm(xq.col_data, xq.col_scale, dyq.col_data, dyq.col_scale, c, ends, mode=K.HMC_GEMM_RAGGED_K,
+                                     rows=rows, pad_blocks=xq.pad_blocks, m=k, n=n, epilogue=epilogue, status=status,
+                                     tile_mode=tm), (experts, k, n), dtype)
+
+
 def test_requantised_weights_replace_cached_scale_factors(cuda_device):
     """One module, weights updated in place and re-quantised between calls (an optimiser step): the new
     field tensors tend to land in the memory the old ones just freed, and fresh weights may even get a
