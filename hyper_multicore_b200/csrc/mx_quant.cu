@@ -20,8 +20,6 @@ constexpr int TILE = 128;
 constexpr int LDB = TILE + 8;  // shared-memory row stride in BF16 elements (16-byte rows, conflict-free both ways)
 constexpr int THREADS = 256;
 
-__device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)); }
-
 // biased UE8M0 exponent of a block whose largest magnitude is `amax`
 __device__ __forceinline__ uint32_t block_exponent(float amax) {
   if (!(amax > 0.f)) return 127u;
@@ -53,158 +51,202 @@ struct QuantParams {
   __nv_bfloat16* dense;
 };
 
-// One CTA per (128-row padded block, 128-column block).
-__global__ void __launch_bounds__(THREADS, 3) mx_quant_kernel(const QuantParams p) {
-  extern __shared__ __align__(16) __nv_bfloat16 tile[];  // [TILE][LDB], BF16-exact values
+// Where a tile goes: rows [row0, row0 + valid) of the un-padded source are rows [pad_row0, ...) of the padded
+// outputs; the tile covers output columns [out_c0, out_c0 + 128).
+struct TilePlace {
+  long long row0;
+  long long pad_row0;
+  int valid;
+  int pb;
+  int out_c0;
+};
+
+// Eight finished (BF16-exact) values of row r, columns out_c0 + c .. + 7: dense copy, shared-memory copy for the
+// column pass, and the row-quantised bytes with their scale. The four threads of a 32-column block are
+// neighbouring lanes, so the block maximum is two shuffles away.
+__device__ __forceinline__ void emit_row_piece(const QuantParams& p, const TilePlace& t, const float (&v)[8], int r, int c,
+                                               __nv_bfloat16* tile) {
+  const int width = p.width;
+  const uint4 packed = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]),
+                                  pack_bf16x2(v[6], v[7]));
+  if (p.dense != nullptr && r < t.valid) *reinterpret_cast<uint4*>(p.dense + (t.row0 + r) * width + t.out_c0 + c) = packed;
+  if (p.col_data != nullptr) *reinterpret_cast<uint4*>(tile + r * LDB + c) = packed;
+  if (p.row_data != nullptr) {
+    float amax = 0.f;
+#pragma unroll
+    for (int q = 0; q < 8; ++q) amax = fmaxf(amax, fabsf(v[q]));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    const uint32_t e = block_exponent(amax);
+    const float inv = inverse_scale(e);
+    uint2 q;
+    q.x = e4m3x2(v[0] * inv, v[1] * inv) | (e4m3x2(v[2] * inv, v[3] * inv) << 16);
+    q.y = e4m3x2(v[4] * inv, v[5] * inv) | (e4m3x2(v[6] * inv, v[7] * inv) << 16);
+    *reinterpret_cast<uint2*>(p.row_data + (t.pad_row0 + r) * width + t.out_c0 + c) = q;
+    if ((threadIdx.x & 3) == 0) {
+      uint8_t* row_atom = p.row_scale + (static_cast<long long>(t.out_c0 / TILE) * p.pad_blocks + t.pb) * 512;
+      row_atom[(r & 31) * 16 + (r >> 5) * 4 + (c >> 5)] = static_cast<uint8_t>(e);
+    }
+  }
+}
+
+// 32-element blocks down each column of one shared-memory tile: one thread per (column pair, 32-row block).
+__device__ __forceinline__ void column_pass(const QuantParams& p, const TilePlace& t, const __nv_bfloat16* tile) {
+  const int width = p.width;
+  uint8_t* atom = p.col_scale + (static_cast<long long>(t.pb) * (width / TILE) + t.out_c0 / TILE) * 512;
+  const int cp = threadIdx.x & 63;
+  const int jb = threadIdx.x >> 6;
+  const uint32_t* src = reinterpret_cast<const uint32_t*>(tile + (32 * jb) * LDB + 2 * cp);
+  uint32_t w[32];
+  float amax0 = 0.f, amax1 = 0.f;
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    w[i] = src[i * (LDB / 2)];
+    const float2 f = unpack_bf16x2(w[i]);
+    amax0 = fmaxf(amax0, fabsf(f.x));
+    amax1 = fmaxf(amax1, fabsf(f.y));
+  }
+  const uint32_t e0 = block_exponent(amax0), e1 = block_exponent(amax1);
+  const float inv0 = inverse_scale(e0), inv1 = inverse_scale(e1);
+  uint8_t* dst = p.col_data + (t.pad_row0 + 32 * jb) * width + t.out_c0 + 2 * cp;
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    const float2 f = unpack_bf16x2(w[i]);
+    *reinterpret_cast<uint16_t*>(dst + static_cast<long long>(i) * width) =
+        static_cast<uint16_t>(e4m3x2(f.x * inv0, f.y * inv1));
+  }
+  const int c_even = 2 * cp;
+  atom[(c_even & 31) * 16 + (c_even >> 5) * 4 + jb] = static_cast<uint8_t>(e0);
+  atom[((c_even + 1) & 31) * 16 + ((c_even + 1) >> 5) * 4 + jb] = static_cast<uint8_t>(e1);
+}
+
+__device__ __forceinline__ float sigmoid_f(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
+
+// One CTA per (128-row padded block, 128-column block of the source). KIND is a compile-time constant so
+// that each variant is straight-line code whose global loads are all issued before the first of them is
+// used. The SwiGLU-grad variant reads dAct, gate and up once and produces both halves of [dgate | dup].
+template <int KIND>
+__global__ void __launch_bounds__(THREADS, 2) mx_quant_kernel(const QuantParams p) {
+  extern __shared__ __align__(16) __nv_bfloat16 tile[];  // [TILE][LDB] (two of them for SwiGLU-grad), BF16-exact values
   __shared__ long long s_row0;
   __shared__ int s_valid;
   const int pb = blockIdx.x;
   const int cb = blockIdx.y;
-  // locate the padded block: groups own ceil(rows / 128) consecutive blocks each. The group ends are
-  // fetched by all threads at once (one memory latency), then one thread walks the block counts.
+  // Locate the padded block: groups own ceil(rows / 128) consecutive blocks each. All threads fetch the
+  // group ends at once (one memory latency); the first warp then scans the block counts 32 groups at a time.
   __shared__ int s_blocks[HMC_CTRL_MAX_LOCAL_EXPERTS];
   for (int g = threadIdx.x; g < p.groups; g += THREADS) {
     const long long end = p.group_ends[g];
     const long long prev = g > 0 ? p.group_ends[g - 1] : 0;
     s_blocks[g] = static_cast<int>((end - prev + 127) / 128);
   }
+  if (threadIdx.x == 0) s_valid = -1;
   __syncthreads();
-  if (threadIdx.x == 0) {
-    int block = 0;
-    s_valid = -1;
-    for (int g = 0; g < p.groups; ++g) {
-      const int blocks = s_blocks[g];
-      if (pb < block + blocks) {
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    int base = 0;
+    for (int g0 = 0; g0 < p.groups; g0 += 32) {
+      const int g = g0 + lane;
+      const int blocks = g < p.groups ? s_blocks[g] : 0;
+      int incl = blocks;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int other = __shfl_up_sync(0xffffffffu, incl, d);
+        if (lane >= d) incl += other;
+      }
+      const int start = base + incl - blocks;
+      const bool hit = pb >= start && pb < start + blocks;
+      if (hit) {
         const long long prev = g > 0 ? p.group_ends[g - 1] : 0;
         const long long end = p.group_ends[g];
-        s_row0 = prev + static_cast<long long>(pb - block) * 128;
+        s_row0 = prev + static_cast<long long>(pb - start) * 128;
         s_valid = static_cast<int>(min(static_cast<long long>(128), end - s_row0));
-        break;
       }
-      block += blocks;
+      if (__ballot_sync(0xffffffffu, hit) != 0u) break;
+      base += __shfl_sync(0xffffffffu, incl, 31);
     }
   }
   __syncthreads();
-  const int valid = s_valid;
-  if (valid < 0) return;  // a spare block past the last group: never read by the GEMM
-  const long long row0 = s_row0;
+  if (s_valid < 0) return;  // a spare block past the last group: never read by the GEMM
   const int width = p.width;
-  const int c0 = cb * TILE;
+  const int inter = width / 2;  // SwiGLU-grad: src = dAct[rows, inter], aux = U[rows, width] = [gate | up]
+  TilePlace t;
+  t.row0 = s_row0;
+  t.pad_row0 = static_cast<long long>(pb) * TILE;
+  t.valid = s_valid;
+  t.pb = pb;
+  t.out_c0 = cb * TILE;
+  TilePlace t_up = t;  // SwiGLU-grad: the dup half of the same columns
+  t_up.out_c0 = inter + cb * TILE;
+  __nv_bfloat16* tile_up = tile + TILE * LDB;
 
-  // ---- load (and transform) the tile, 8 BF16 per access. Sixteen threads cover one row, so the four
-  // threads of a 32-column block are neighbours: the row-wise block maximum is two shuffles away and
-  // the row-quantised bytes leave straight from registers; only the column pass needs shared memory.
-  const long long pad_row0 = static_cast<long long>(pb) * TILE;
-  uint8_t* row_atom = p.row_data != nullptr ? p.row_scale + (static_cast<long long>(cb) * p.pad_blocks + pb) * 512 : nullptr;
-#pragma unroll 2
-  for (int i = threadIdx.x; i < TILE * (TILE / 8); i += THREADS) {
-    const int r = i >> 4;
-    const int c = (i & 15) * 8;
-    float v[8];
-    if (r < valid) {
-      const long long row = row0 + r;
-      if (p.kind == HMC_MXQ_PLAIN) {
-        const uint4 q = ld_nc_16(p.src + row * width + c0 + c);
-        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+  // ---- load (and transform) the tile, 8 BF16 per access: a thread owns columns c .. c+7 of rows rbase,
+  // rbase + 16, ...; the loads of PASS rows are in flight together.
+  const int rbase = threadIdx.x >> 4;
+  const int c = (threadIdx.x & 15) * 8;
+  const int c0 = cb * TILE;
+  constexpr int PASS = KIND == HMC_MXQ_SWIGLU_GRAD ? 4 : 8;
+#pragma unroll 1
+  for (int j0 = 0; j0 < TILE / 16; j0 += PASS) {
+    uint4 ra[PASS], rb[PASS], rc[PASS];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float2 f = unpack_bf16x2(w[j]);
-          v[2 * j] = f.x;
-          v[2 * j + 1] = f.y;
-        }
-      } else if (p.kind == HMC_MXQ_SWIGLU) {
-        // src = U[rows, 2 * width] = [gate | up]
-        const uint4 gq = ld_nc_16(p.src + row * 2 * width + c0 + c);
-        const uint4 uq = ld_nc_16(p.src + row * 2 * width + width + c0 + c);
-        const uint32_t gw[4] = {gq.x, gq.y, gq.z, gq.w};
-        const uint32_t uw[4] = {uq.x, uq.y, uq.z, uq.w};
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float2 g = unpack_bf16x2(gw[j]);
-          const float2 u = unpack_bf16x2(uw[j]);
-          v[2 * j] = bf16_round(silu_f(g.x) * u.x);
-          v[2 * j + 1] = bf16_round(silu_f(g.y) * u.y);
-        }
-      } else {
-        // src = dAct[rows, width / 2], aux = U[rows, width]; result = [dgate | dup]
-        const int inter = width / 2;
-        const int col = c0 + c;
-        const bool gate_half = col < inter;
-        const int ic = gate_half ? col : col - inter;
-        const uint4 dq = ld_nc_16(p.src + row * inter + ic);
-        const uint4 gq = ld_nc_16(p.aux + row * width + ic);
-        const uint4 uq = ld_nc_16(p.aux + row * width + inter + ic);
-        const uint32_t dw[4] = {dq.x, dq.y, dq.z, dq.w};
-        const uint32_t gw[4] = {gq.x, gq.y, gq.z, gq.w};
-        const uint32_t uw[4] = {uq.x, uq.y, uq.z, uq.w};
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float2 d = unpack_bf16x2(dw[j]);
-          const float2 g = unpack_bf16x2(gw[j]);
-          const float2 u = unpack_bf16x2(uw[j]);
-          const float s0 = 1.0f / (1.0f + __expf(-g.x));
-          const float s1 = 1.0f / (1.0f + __expf(-g.y));
-          if (gate_half) {
-            v[2 * j] = bf16_round(d.x * u.x * s0 * (1.0f + g.x * (1.0f - s0)));
-            v[2 * j + 1] = bf16_round(d.y * u.y * s1 * (1.0f + g.y * (1.0f - s1)));
-          } else {
-            v[2 * j] = bf16_round(d.x * (g.x * s0));
-            v[2 * j + 1] = bf16_round(d.y * (g.y * s1));
-          }
+    for (int j = 0; j < PASS; ++j) {
+      const int r = rbase + 16 * (j0 + j);
+      ra[j] = rb[j] = rc[j] = make_uint4(0, 0, 0, 0);  // padding rows quantise to zeros in every variant
+      if (r < t.valid) {
+        const long long row = t.row0 + r;
+        if (KIND == HMC_MXQ_PLAIN) {
+          ra[j] = ld_nc_16(p.src + row * width + c0 + c);
+        } else if (KIND == HMC_MXQ_SWIGLU) {
+          // src = U[rows, 2 * width] = [gate | up]
+          ra[j] = ld_nc_16(p.src + row * 2 * width + c0 + c);
+          rb[j] = ld_nc_16(p.src + row * 2 * width + width + c0 + c);
+        } else {
+          ra[j] = ld_nc_16(p.aux + row * width + c0 + c);
+          rb[j] = ld_nc_16(p.aux + row * width + inter + c0 + c);
+          rc[j] = ld_nc_16(p.src + row * inter + c0 + c);
         }
       }
-    } else {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) v[j] = 0.f;
     }
-    // every value is BF16-exact here
-    const uint4 packed = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]),
-                                    pack_bf16x2(v[6], v[7]));
-    if (p.dense != nullptr && r < valid) *reinterpret_cast<uint4*>(p.dense + (row0 + r) * width + c0 + c) = packed;
-    if (p.col_data != nullptr) *reinterpret_cast<uint4*>(tile + r * LDB + c) = packed;
-    if (p.row_data != nullptr) {
-      float amax = 0.f;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
-      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-      const uint32_t e = block_exponent(amax);
-      const float inv = inverse_scale(e);
-      uint2 q;
-      q.x = e4m3x2(v[0] * inv, v[1] * inv) | (e4m3x2(v[2] * inv, v[3] * inv) << 16);
-      q.y = e4m3x2(v[4] * inv, v[5] * inv) | (e4m3x2(v[6] * inv, v[7] * inv) << 16);
-      *reinterpret_cast<uint2*>(p.row_data + (pad_row0 + r) * width + c0 + c) = q;
-      if ((threadIdx.x & 3) == 0) row_atom[(r & 31) * 16 + (r >> 5) * 4 + (c >> 5)] = static_cast<uint8_t>(e);
+    for (int j = 0; j < PASS; ++j) {
+      const int r = rbase + 16 * (j0 + j);
+      const uint32_t aw[4] = {ra[j].x, ra[j].y, ra[j].z, ra[j].w};
+      const uint32_t bw[4] = {rb[j].x, rb[j].y, rb[j].z, rb[j].w};
+      const uint32_t cw[4] = {rc[j].x, rc[j].y, rc[j].z, rc[j].w};
+      float v[8];
+      float v_up[8];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        if (KIND == HMC_MXQ_PLAIN) {
+          const float2 f = unpack_bf16x2(aw[q]);
+          v[2 * q] = f.x;
+          v[2 * q + 1] = f.y;
+        } else if (KIND == HMC_MXQ_SWIGLU) {
+          const float2 g = unpack_bf16x2(aw[q]);
+          const float2 u = unpack_bf16x2(bw[q]);
+          v[2 * q] = bf16_round(g.x * sigmoid_f(g.x) * u.x);
+          v[2 * q + 1] = bf16_round(g.y * sigmoid_f(g.y) * u.y);
+        } else {
+          const float2 g = unpack_bf16x2(aw[q]);
+          const float2 u = unpack_bf16x2(bw[q]);
+          const float2 d = unpack_bf16x2(cw[q]);
+          const float s0 = sigmoid_f(g.x);
+          const float s1 = sigmoid_f(g.y);
+          v[2 * q] = bf16_round(d.x * u.x * s0 * (1.0f + g.x * (1.0f - s0)));
+          v[2 * q + 1] = bf16_round(d.y * u.y * s1 * (1.0f + g.y * (1.0f - s1)));
+          v_up[2 * q] = bf16_round(d.x * (g.x * s0));
+          v_up[2 * q + 1] = bf16_round(d.y * (g.y * s1));
+        }
+      }
+      emit_row_piece(p, t, v, r, c, tile);
+      if (KIND == HMC_MXQ_SWIGLU_GRAD) emit_row_piece(p, t_up, v_up, r, c, tile_up);
     }
   }
-  // ---- 32-element blocks down each column: one thread per (column pair, 32-row block)
   if (p.col_data != nullptr) {
     __syncthreads();
-    uint8_t* atom = p.col_scale + (static_cast<long long>(pb) * (width / TILE) + cb) * 512;
-    const int cp = threadIdx.x & 63;
-    const int jb = threadIdx.x >> 6;
-    const uint32_t* src = reinterpret_cast<const uint32_t*>(tile + (32 * jb) * LDB + 2 * cp);
-    uint32_t w[32];
-    float amax0 = 0.f, amax1 = 0.f;
-#pragma unroll
-    for (int i = 0; i < 32; ++i) {
-      w[i] = src[i * (LDB / 2)];
-      const float2 f = unpack_bf16x2(w[i]);
-      amax0 = fmaxf(amax0, fabsf(f.x));
-      amax1 = fmaxf(amax1, fabsf(f.y));
-    }
-    const uint32_t e0 = block_exponent(amax0), e1 = block_exponent(amax1);
-    const float inv0 = inverse_scale(e0), inv1 = inverse_scale(e1);
-    uint8_t* dst = p.col_data + (pad_row0 + 32 * jb) * width + c0 + 2 * cp;
-#pragma unroll
-    for (int i = 0; i < 32; ++i) {
-      const float2 f = unpack_bf16x2(w[i]);
-      *reinterpret_cast<uint16_t*>(dst + static_cast<long long>(i) * width) =
-          static_cast<uint16_t>(e4m3x2(f.x * inv0, f.y * inv1));
-    }
-    const int c_even = 2 * cp;
-    atom[(c_even & 31) * 16 + (c_even >> 5) * 4 + jb] = static_cast<uint8_t>(e0);
-    atom[((c_even + 1) & 31) * 16 + ((c_even + 1) >> 5) * 4 + jb] = static_cast<uint8_t>(e1);
+    column_pass(p, t, tile);
+    if (KIND == HMC_MXQ_SWIGLU_GRAD) column_pass(p, t_up, tile_up);
   }
 }
 
@@ -335,14 +377,26 @@ extern "C" int hmc_mx_quant(const hmc_mx_quant_args* args, void* stream_ptr) {
   p.col_data = static_cast<uint8_t*>(a.col_data);
   p.col_scale = static_cast<uint8_t*>(a.col_scale);
   p.dense = static_cast<__nv_bfloat16*>(a.dense);
-  static PerDeviceFlag configured{};
-  const int smem = TILE * LDB * sizeof(__nv_bfloat16);
-  if (int rc = allow_dynamic_smem(mx_quant_kernel, smem, configured)) return rc;
+  const bool grad = a.kind == HMC_MXQ_SWIGLU_GRAD;  // one CTA produces the dgate and the dup tile of its columns
+  const int smem = (grad ? 2 : 1) * TILE * LDB * sizeof(__nv_bfloat16);
   // only blocks that can hold rows are launched: ceil(rows / 128) + groups bounds them
   long long blocks = (a.rows + 127) / 128 + a.groups;
   if (blocks > a.pad_blocks) blocks = a.pad_blocks;
-  dim3 grid(static_cast<unsigned>(blocks), static_cast<unsigned>(a.width / 128));
-  mx_quant_kernel<<<grid, THREADS, smem, static_cast<cudaStream_t>(stream_ptr)>>>(p);
+  dim3 grid(static_cast<unsigned>(blocks), static_cast<unsigned>(a.width / (grad ? 256 : 128)));
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  if (a.kind == HMC_MXQ_PLAIN) {
+    static PerDeviceFlag configured{};
+    if (int rc = allow_dynamic_smem(mx_quant_kernel<HMC_MXQ_PLAIN>, smem, configured)) return rc;
+    mx_quant_kernel<HMC_MXQ_PLAIN><<<grid, THREADS, smem, stream>>>(p);
+  } else if (a.kind == HMC_MXQ_SWIGLU) {
+    static PerDeviceFlag configured{};
+    if (int rc = allow_dynamic_smem(mx_quant_kernel<HMC_MXQ_SWIGLU>, smem, configured)) return rc;
+    mx_quant_kernel<HMC_MXQ_SWIGLU><<<grid, THREADS, smem, stream>>>(p);
+  } else {
+    static PerDeviceFlag configured{};
+    if (int rc = allow_dynamic_smem(mx_quant_kernel<HMC_MXQ_SWIGLU_GRAD>, smem, configured)) return rc;
+    mx_quant_kernel<HMC_MXQ_SWIGLU_GRAD><<<grid, THREADS, smem, stream>>>(p);
+  }
   HMC_LAUNCH_OK();
   return 0;
 }
