@@ -361,20 +361,17 @@ class MoeLayerRun:
         ctx, shape = self.ctx, self.shape
         total_ms, launches = ctx.timed(self.step, steps, warmup)
         self.module.check_status()
-        profile_steps = min(steps, 5)
-        with _lib.profile() as prof:
-            for _ in range(profile_steps):
-                self.step()
-            ctx.barrier()
+        per_step = profiled_steps(ctx, self.step, min(steps, 5))
         kind = "mx_gemm" if self.precision == "mxfp8" else "grouped_gemm"
-        gemm_ms = ctx.max_over_ranks(prof.ms[kind] / profile_steps)
-        quant_ms = ctx.max_over_ranks(prof.ms["mx_quant"] / profile_steps)
+        gemm_ms = ctx.max_over_ranks(statistics.median(s["ms"].get(kind, 0.0) for s in per_step))
+        quant_ms = ctx.max_over_ranks(statistics.median(s["ms"].get("mx_quant", 0.0) for s in per_step))
+        gemm_calls = per_step[-1]["calls"].get(kind, 0)
         ms_per_step = total_ms / steps
         rows_max = max(self.received_rows)
         flops = shape.flops_per_token // shape.top_k * rows_max  # 18*H*I per routed row, on the most loaded rank
         return {
             "ms_per_step": ms_per_step, "tokens_per_s": ctx.world * shape.tokens / (ms_per_step * 1e-3),
-            "launches": launches, "gemm_ms_per_step": gemm_ms, "gemm_launches_per_step": prof.calls[kind] // profile_steps,
+            "launches": launches, "gemm_ms_per_step": gemm_ms, "gemm_launches_per_step": gemm_calls,
             "quant_ms_per_step": quant_ms, "non_gemm_ms_per_step": ms_per_step - gemm_ms,
             "gemm_tflops": flops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else None,
             "layer_tflops": flops / (ms_per_step * 1e-3) / 1e12, "flops_per_step": flops,
@@ -663,43 +660,64 @@ def nccl_layer_measure(ctx: Context, run: MoeLayerRun, steps: int, warmup: int) 
                     "grouped GEMMs; the baseline of the reference's examples (AllToAllTokenDispatcher)"}
 
 
-def write_timeline(ctx: Context, run: MoeLayerRun, path: str) -> None:
-    """Call-by-call device timeline of one forward + backward step (CUDA events around every entry point of
-    the native library, on its stream): kind, start, duration and the gap to the previous call. Rank 0 writes it."""
+def profiled_steps(ctx: Context, step, steps: int, before=None, after=None) -> list:
+    """Device time per kind of native entry point for each of `steps` steps (CUDA events around every entry point,
+    recorded by the library on its stream). Two profiled steps run first and are discarded: they fill the
+    library's event pool, so that no event is created between a start event and its kernel in the steps that
+    count; `before` / `after` are called right around those. Returns one {"ms": {kind: ms}, "calls": {kind: n}, "records": [(kind, start_ms, ms), ...]} per step."""
     import ctypes
 
     from hyper_multicore_b200 import _lib
 
     lib = _lib.load()
-    steps = 3
-    for _ in range(3):
-        run.step()
-    ctx.barrier()
+    with _lib.profile():
+        for _ in range(2):
+            step()
+        ctx.barrier()
     lib.hmc_profile_enable(1)
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    start.record()
+    # Keep the device busy for a few milliseconds first, so that the host stays ahead of it for the whole pass:
+    # a start event that runs while the device idles would add the host's launch latency to the call's time.
+    torch.cuda._sleep(10_000_000)
+    if before is not None:
+        before()
     for _ in range(steps):
-        run.step()
-    stop.record()
+        step()
+    if after is not None:
+        after()
     ctx.barrier()
     lib.hmc_profile_enable(0)
-    capacity = 4096
+    capacity = 1 << 14
     kinds, begins, lengths = (ctypes.c_int32 * capacity)(), (ctypes.c_double * capacity)(), (ctypes.c_double * capacity)()
     count = lib.hmc_profile_dump(kinds, begins, lengths, capacity)
+    per_step = count // steps
+    out = []
+    for s in range(steps):
+        records = [(_lib.HMC_PROFILE_KINDS[kinds[i]], begins[i], lengths[i]) for i in range(s * per_step, (s + 1) * per_step)]
+        ms, calls = {}, {}
+        for name, _, length in records:
+            ms[name] = ms.get(name, 0.0) + length
+            calls[name] = calls.get(name, 0) + 1
+        out.append({"ms": ms, "calls": calls, "records": records})
+    return out
+
+
+def write_timeline(ctx: Context, run: MoeLayerRun, path: str) -> None:
+    """Call-by-call device timeline of one forward + backward step (CUDA events around every entry point of
+    the native library, on its stream): kind, start, duration and the gap to the previous call. Rank 0 writes it."""
+    steps = 3
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    per_step = profiled_steps(ctx, run.step, steps, before=start.record, after=stop.record)
     if ctx.rank != 0:
         return
-    per_step = count // steps
-    first = (steps - 1) * per_step
+    records = per_step[-1]["records"]
     lines = [f"# one step of {steps} (the last), rank 0 of {ctx.world}; {config(run.shape, ctx.world, run.precision)['workload']}",
              f"# step time over the {steps} profiled steps: {start.elapsed_time(stop) / steps * 1e3:.1f} us",
              "#   start us    gap us  call kind        duration us"]
-    previous_end, totals = begins[first], {}
-    for i in range(first, count):
-        name = _lib.HMC_PROFILE_KINDS[kinds[i]]
-        lines.append(f"{1e3 * (begins[i] - begins[first]):12.1f} {1e3 * (begins[i] - previous_end):9.1f}  {name:14s} {1e3 * lengths[i]:12.1f}")
-        previous_end = begins[i] + lengths[i]
-        totals[name] = totals.get(name, 0.0) + lengths[i]
-    lines.append("# per kind (us): " + ", ".join(f"{k} {1e3 * v:.1f}" for k, v in totals.items()))
+    origin = previous_end = records[0][1]
+    for name, begin, length in records:
+        lines.append(f"{1e3 * (begin - origin):12.1f} {1e3 * (begin - previous_end):9.1f}  {name:14s} {1e3 * length:12.1f}")
+        previous_end = begin + length
+    lines.append("# per kind (us): " + ", ".join(f"{k} {1e3 * v:.1f}" for k, v in per_step[-1]["ms"].items()))
     Path(path).write_text("\n".join(lines) + "\n")
 
 
@@ -843,7 +861,7 @@ def run_gpu(args) -> None:
         "clocks": clocks, "e2e": e2e, "gpu_launches": main["launches"], "parity": parity,
         "roofline": {
             "bound": "tensor",
-            "kernel": ("mx_gemm_kernel (tcgen05 block-scaled FP8" if mx else "grouped_gemm_kernel (tcgen05") +
+            "kernel": ("mx_gemm_pair_kernel (tcgen05 block-scaled FP8 on CTA pairs" if mx else "grouped_gemm_kernel (tcgen05") +
                       f", {main['gemm_launches_per_step']} launches per step)",
             "achieved": gemm_tflops, "peak": burst, "unit": "TFLOP/s", "frac": gemm_tflops / burst,
             "peak_source": (("2 x " if mx else "") + f"cuBLAS bf16 burst rate {peaks['source']}: the timed region is tens of "
