@@ -359,12 +359,18 @@ class MoeLayerRun:
         from hyper_multicore_b200 import _lib
 
         ctx, shape = self.ctx, self.shape
-        total_ms, launches = ctx.timed(self.step, steps, warmup)
-        self.module.check_status()
-        per_step = profiled_steps(ctx, self.step, min(steps, 5))
+        # The dominant kernels carry their own CUDA events inside the timed region (recorded by the library on its
+        # stream around the GEMM - and for MXFP8 the quantiser - launches only: a few microseconds per step).
+        lib = _lib.load()
         kind = "mx_gemm" if self.precision == "mxfp8" else "grouped_gemm"
-        gemm_ms = ctx.max_over_ranks(statistics.median(s["ms"].get(kind, 0.0) for s in per_step))
-        quant_ms = ctx.max_over_ranks(statistics.median(s["ms"].get("mx_quant", 0.0) for s in per_step))
+        watched = [kind, "mx_quant"] if self.precision == "mxfp8" else [kind]
+        lib.hmc_profile_enable_kinds(sum(1 << _lib.HMC_PROFILE_KINDS.index(k) for k in watched))
+        total_ms, launches = ctx.timed(self.step, steps, warmup)
+        lib.hmc_profile_enable(0)
+        self.module.check_status()
+        per_step = dumped_steps(lib, warmup + steps)[warmup:]
+        gemm_ms = ctx.max_over_ranks(statistics.fmean(s["ms"].get(kind, 0.0) for s in per_step))
+        quant_ms = ctx.max_over_ranks(statistics.fmean(s["ms"].get("mx_quant", 0.0) for s in per_step))
         gemm_calls = per_step[-1]["calls"].get(kind, 0)
         ms_per_step = total_ms / steps
         rows_max = max(self.received_rows)
@@ -662,22 +668,19 @@ def nccl_layer_measure(ctx: Context, run: MoeLayerRun, steps: int, warmup: int) 
 
 def profiled_steps(ctx: Context, step, steps: int, before=None, after=None) -> list:
     """Device time per kind of native entry point for each of `steps` steps (CUDA events around every entry point,
-    recorded by the library on its stream). Two profiled steps run first and are discarded: they fill the
-    library's event pool, so that no event is created between a start event and its kernel in the steps that
-    count; `before` / `after` are called right around those. Returns one {"ms": {kind: ms}, "calls": {kind: n}, "records": [(kind, start_ms, ms), ...]} per step."""
-    import ctypes
-
+    recorded by the library on its stream). Two more steps are queued first and dropped from the result, with no
+    idle gap after them: the host is then ahead of the device for the steps that count (a start event that runs
+    on an idle device would add the host's launch latency to the call). `before` / `after` are called right around
+    the counted steps. Returns one {"ms": {kind: ms}, "calls": {kind: n}, "records": [(kind, start_ms, ms), ...]}
+    per step."""
     from hyper_multicore_b200 import _lib
 
+    lead = 2
     lib = _lib.load()
-    with _lib.profile():
-        for _ in range(2):
-            step()
-        ctx.barrier()
+    ctx.barrier()
     lib.hmc_profile_enable(1)
-    # Keep the device busy for a few milliseconds first, so that the host stays ahead of it for the whole pass:
-    # a start event that runs while the device idles would add the host's launch latency to the call's time.
-    torch.cuda._sleep(10_000_000)
+    for _ in range(lead):
+        step()
     if before is not None:
         before()
     for _ in range(steps):
@@ -686,6 +689,15 @@ def profiled_steps(ctx: Context, step, steps: int, before=None, after=None) -> l
         after()
     ctx.barrier()
     lib.hmc_profile_enable(0)
+    return dumped_steps(lib, lead + steps)[lead:]
+
+
+def dumped_steps(lib, steps: int) -> list:
+    """The library's recorded calls, split evenly into `steps` consecutive steps."""
+    import ctypes
+
+    from hyper_multicore_b200 import _lib
+
     capacity = 1 << 14
     kinds, begins, lengths = (ctypes.c_int32 * capacity)(), (ctypes.c_double * capacity)(), (ctypes.c_double * capacity)()
     count = lib.hmc_profile_dump(kinds, begins, lengths, capacity)

@@ -346,6 +346,7 @@ SIGNATURES: dict[str, tuple] = {
     "hmc_worker_queue_layout_version": (_I, []),
     "hmc_launch_count": (_L, []),
     "hmc_profile_enable": (_I, [_I]),
+    "hmc_profile_enable_kinds": (_I, [ctypes.c_uint32]),
     "hmc_profile_collect": (_I, [ctypes.POINTER(c_double), ctypes.POINTER(c_int64), _I]),
     "hmc_profile_dump": (_I, [ctypes.POINTER(c_int32), ctypes.POINTER(c_double), ctypes.POINTER(c_double), _I]),
     "hmc_grouped_gemm": (_I, [ctypes.POINTER(GroupedGemmArgs), _P]),

@@ -7,6 +7,8 @@
 // (utilities.asc:162-209), weighted un-permutation and its gradients (route.py:1029-1051,
 // torch/csrc/mega_moe_unpermute.cpp:56-65, moe_token_permute_grad.cpp:29-38) and
 // ZeroEmptyExpertGrad (utilities.asc:17-54).
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 
 namespace hmc {
@@ -117,6 +119,147 @@ chunk_rank_kernel(const void* __restrict__ indices, int is_i64, long long entrie
   if (i < entries) {
     e = load_index(indices, is_i64, i);
     if (e < 0 || e >= experts) e = -1;
+  }
+  for (int w = 0; w < SORT_THREADS / 32; ++w) {
+    if (w == warp) {
+      const unsigned peers = __match_any_sync(0xffffffffu, e);
+      if (e >= 0) {
+        const int rank_in_warp = __popc(peers & ((1u << lane) - 1u));
+        const int leader = __ffs(peers) - 1;
+        int base = 0;
+        if (lane == leader) {
+          base = cursor[e];
+          cursor[e] = base + __popc(peers);
+        }
+        base = __shfl_sync(peers, base, leader);
+        const int dest = base + rank_in_warp;
+        mapping[i] = dest;
+        if (source_of_row != nullptr) source_of_row[dest] = static_cast<int>(i);
+        if (expert_of_row != nullptr) expert_of_row[dest] = static_cast<int>(e);
+      } else if (i < entries) {
+        mapping[i] = -1;
+      }
+    }
+    __syncthreads();
+  }
+}
+
+// ---- the three passes in one cooperative launch ----------------------------------------------
+// For route counts whose chunks are all resident at once (one CTA per chunk): histogram, one grid-wide
+// barrier, then every CTA derives its own destination bases from the table of all chunks (a column sum over
+// the chunks before it plus an exclusive scan over the experts) and ranks its entries. Same stable order as
+// the three-kernel path: chunks in flat order, warps in flat order inside a chunk, lanes inside a warp.
+constexpr int RANK_PARALLEL_EXPERTS = 256;  // per-warp counters of the parallel ranking fit shared memory up to here
+
+__device__ __forceinline__ int warp_inclusive_scan(int v, int lane) {
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    const int other = __shfl_up_sync(0xffffffffu, v, d);
+    if (lane >= d) v += other;
+  }
+  return v;
+}
+
+__global__ void __launch_bounds__(SORT_THREADS)
+sort_routes_fused_kernel(const void* __restrict__ indices, int is_i64, long long entries, int experts,
+                         int* __restrict__ chunk_counts, int* __restrict__ mapping, int* __restrict__ source_of_row,
+                         int* __restrict__ expert_of_row, int* __restrict__ counts_out, long long* __restrict__ ends_out,
+                         int* __restrict__ status) {
+  extern __shared__ int smem[];   // cursor [experts], then per-warp counters [32][experts] when experts <= 256
+  int* cursor = smem;
+  int* warp_counts = smem + experts;
+  __shared__ int warp_sums[32];
+  __shared__ int pass_total;
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int chunk = blockIdx.x;
+  const int chunks = gridDim.x;
+  const bool parallel_rank = experts <= RANK_PARALLEL_EXPERTS;
+
+  // ---- histogram of this chunk
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) cursor[e] = 0;
+  __syncthreads();
+  const long long i = static_cast<long long>(chunk) * SORT_CHUNK + threadIdx.x;
+  long long e = -1;
+  if (i < entries) {
+    e = load_index(indices, is_i64, i);
+    if (e >= 0 && e < experts) {
+      atomicAdd(&cursor[e], 1);
+    } else {
+      report_status(status, HMC_STATUS_BAD_INDEX, static_cast<int>(i), static_cast<int>(e), experts);
+      e = -1;
+    }
+  }
+  __syncthreads();
+  for (int x = threadIdx.x; x < experts; x += blockDim.x) chunk_counts[static_cast<long long>(chunk) * experts + x] = cursor[x];
+  cooperative_groups::this_grid().sync();
+
+  // ---- destination bases of this chunk: rows of earlier experts + rows of this expert in earlier chunks
+  int carry = 0;
+  for (int first = 0; first < experts; first += SORT_THREADS) {
+    const int x = first + threadIdx.x;
+    int below = 0, total = 0;
+    if (x < experts) {
+      for (int c = 0; c < chunks; ++c) {
+        const int v = chunk_counts[static_cast<long long>(c) * experts + x];
+        total += v;
+        if (c < chunk) below += v;
+      }
+    }
+    const int incl = warp_inclusive_scan(total, lane);
+    if (lane == 31) warp_sums[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+      const int sum = warp_sums[lane];
+      const int scanned = warp_inclusive_scan(sum, lane);
+      warp_sums[lane] = scanned - sum;
+      if (lane == 31) pass_total = scanned;
+    }
+    __syncthreads();
+    if (x < experts) {
+      const int expert_base = carry + warp_sums[warp] + incl - total;
+      cursor[x] = expert_base + below;
+      if (chunk == 0) {
+        if (counts_out != nullptr) counts_out[x] = total;
+        if (ends_out != nullptr) ends_out[x] = expert_base + total;
+      }
+    }
+    carry += pass_total;
+    __syncthreads();
+  }
+  // Rejected expert ids leave the last rows without an owner: mark them so that no consumer reads a stale
+  // expert or source there (`carry` is the number of rows that were placed).
+  for (long long r = carry + i; r < entries; r += static_cast<long long>(chunks) * SORT_CHUNK) {
+    if (expert_of_row != nullptr) expert_of_row[r] = -1;
+    if (source_of_row != nullptr) source_of_row[r] = -1;
+  }
+
+  // ---- stable rank inside the chunk
+  if (parallel_rank) {
+    for (int x = threadIdx.x; x < 32 * experts; x += blockDim.x) warp_counts[x] = 0;
+    __syncthreads();
+    const unsigned peers = __match_any_sync(0xffffffffu, e);
+    const int leader = __ffs(peers) - 1;
+    if (e >= 0 && lane == leader) warp_counts[warp * experts + e] = __popc(peers);
+    __syncthreads();
+    for (int x = threadIdx.x; x < experts; x += blockDim.x) {
+      int run = cursor[x];
+      for (int w = 0; w < SORT_THREADS / 32; ++w) {
+        const int v = warp_counts[w * experts + x];
+        warp_counts[w * experts + x] = run;
+        run += v;
+      }
+    }
+    __syncthreads();
+    if (e >= 0) {
+      const int dest = warp_counts[warp * experts + e] + __popc(peers & ((1u << lane) - 1u));
+      mapping[i] = dest;
+      if (source_of_row != nullptr) source_of_row[dest] = static_cast<int>(i);
+      if (expert_of_row != nullptr) expert_of_row[dest] = static_cast<int>(e);
+    } else if (i < entries) {
+      mapping[i] = -1;
+    }
+    return;
   }
   for (int w = 0; w < SORT_THREADS / 32; ++w) {
     if (w == warp) {
@@ -367,9 +510,20 @@ zero_empty_kernel(uint4* __restrict__ first, long long first_vec_per_expert, uin
       second[e * second_vec_per_expert + v] = zero;
 }
 
-// Offset descriptors for push dispatch from the gathered count table counts[ep][experts].
-// One CTA; thread s < ep scans source s, thread d < ep scans destination d. Row units.
-__global__ void __launch_bounds__(256)
+// Offset descriptors for push dispatch from the gathered count table counts[ep][experts]. Row units.
+// One CTA; every running sum below is a warp scan over 32 table entries at a time: warp 0 lays out this
+// rank's send order, warps 1 .. ep the sources' expert-major buffers, warps ep+1 .. 2*ep the destinations'
+// receive buffers (the warps take these jobs round-robin when the CTA has fewer).
+__device__ __forceinline__ long long warp_inclusive_scan_ll(long long v, int lane) {
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    const long long other = __shfl_up_sync(0xffffffffu, v, d);
+    if (lane >= d) v += other;
+  }
+  return v;
+}
+
+__global__ void __launch_bounds__(1024)
 route_offsets_kernel(const int* __restrict__ counts, int ep, int experts, int rank,
                      long long* __restrict__ dispatch_src_off, long long* __restrict__ dispatch_target_off,
                      int* __restrict__ dispatch_size, long long* __restrict__ combine_src_off,
@@ -377,8 +531,7 @@ route_offsets_kernel(const int* __restrict__ counts, int ep, int experts, int ra
                      long long* __restrict__ group_list, long long* __restrict__ totals,
                      long long* __restrict__ recv_segment_start, long long* __restrict__ send_order_start,
                      int stage_table) {
-  // The scans below are serial chains of dependent loads: from shared memory they cost a few cycles each,
-  // from global memory a round trip each (19 us for 32 experts). Tables of up to 48 KiB are staged.
+  // Tables of up to 48 KiB are staged in shared memory: one global round trip for the whole table.
   extern __shared__ int staged[];
   const int* table = counts;
   if (stage_table) {
@@ -387,54 +540,75 @@ route_offsets_kernel(const int* __restrict__ counts, int ep, int experts, int ra
     table = staged;
   }
   const int local = experts / ep;
-  if (threadIdx.x == 0 && send_order_start != nullptr) {
-    // Order in which this rank sends its rows when the dispatch rides inside the consuming GEMM: local
-    // expert 0 of every destination first (destinations rank + 1, rank + 2, ..., this rank last), then
-    // local expert 1, ... so that on every owner expert 0 completes after 1 / local of the transfer and
-    // its tiles run while the later experts' rows still travel. Entry q = le * ep + dd holds the first
-    // position of segment (destination (rank + 1 + dd) % ep, local expert le) in that order.
+  const int lane = threadIdx.x & 31;
+  const int warps = blockDim.x >> 5;
+  for (int job = threadIdx.x >> 5; job < 1 + 2 * ep; job += warps) {
     long long run = 0;
-    for (int le = 0; le < local; ++le) {
-      for (int dd = 0; dd < ep; ++dd) {
-        const int d = (rank + 1 + dd) % ep;
-        send_order_start[le * ep + dd] = run;
-        run += table[rank * experts + d * local + le];
-      }
-    }
-    send_order_start[experts] = run;
-  }
-  for (int s = threadIdx.x; s < ep; s += blockDim.x) {
-    // source_prefix[s][e]: first row of expert e in source s's expert-major routed buffer
-    long long run = 0;
-    for (int e = 0; e < experts; ++e) {
-      const int c = table[s * experts + e];
-      if (s == rank) {
-        dispatch_src_off[e] = run;
-        dispatch_size[e] = c;
-      }
-      if (e >= rank * local && e < (rank + 1) * local) {
-        combine_target_off[s * local + (e - rank * local)] = run;
-        combine_size[s * local + (e - rank * local)] = c;
-      }
-      run += c;
-    }
-    if (s == rank && totals != nullptr) totals[0] = run;  // rows this rank routes (tokens * top_k)
-  }
-  for (int d = threadIdx.x; d < ep; d += blockDim.x) {
-    // destination d lays its receive buffer out local-expert-major, then by source rank
-    long long run = 0;
-    for (int le = 0; le < local; ++le) {
-      for (int s = 0; s < ep; ++s) {
-        if (s == rank) dispatch_target_off[d * local + le] = run;
-        if (d == rank) {
-          combine_src_off[s * local + le] = run;
-          if (recv_segment_start != nullptr) recv_segment_start[le * ep + s] = run;
+    if (job == 0) {
+      if (send_order_start == nullptr) continue;
+      // Order in which this rank sends its rows when the dispatch rides inside the consuming GEMM: local
+      // expert 0 of every destination first (destinations rank + 1, rank + 2, ..., this rank last), then
+      // local expert 1, ... so that on every owner expert 0 completes after 1 / local of the transfer and
+      // its tiles run while the later experts' rows still travel. Entry q = le * ep + dd holds the first
+      // position of segment (destination (rank + 1 + dd) % ep, local expert le) in that order.
+      for (int q0 = 0; q0 < experts; q0 += 32) {
+        const int q = q0 + lane;
+        int c = 0;
+        if (q < experts) {
+          const int le = q / ep, dd = q % ep;
+          c = table[rank * experts + ((rank + 1 + dd) % ep) * local + le];
         }
-        run += table[s * experts + d * local + le];
+        const long long incl = warp_inclusive_scan_ll(c, lane);
+        if (q < experts) send_order_start[q] = run + incl - c;
+        run += __shfl_sync(0xffffffffu, incl, 31);
       }
-      if (d == rank) group_list[le] = run;
+      if (lane == 0) send_order_start[experts] = run;
+    } else if (job <= ep) {
+      // source s: first row of expert e in its expert-major routed buffer
+      const int s = job - 1;
+      for (int e0 = 0; e0 < experts; e0 += 32) {
+        const int e = e0 + lane;
+        const int c = e < experts ? table[s * experts + e] : 0;
+        const long long incl = warp_inclusive_scan_ll(c, lane);
+        const long long first = run + incl - c;
+        if (e < experts) {
+          if (s == rank) {
+            dispatch_src_off[e] = first;
+            dispatch_size[e] = c;
+          }
+          if (e >= rank * local && e < (rank + 1) * local) {
+            combine_target_off[s * local + (e - rank * local)] = first;
+            combine_size[s * local + (e - rank * local)] = c;
+          }
+        }
+        run += __shfl_sync(0xffffffffu, incl, 31);
+      }
+      if (s == rank && totals != nullptr && lane == 0) totals[0] = run;  // rows this rank routes (tokens * top_k)
+    } else {
+      // destination d lays its receive buffer out local-expert-major, then by source rank: entry q = le * ep + s
+      const int d = job - 1 - ep;
+      for (int q0 = 0; q0 < experts; q0 += 32) {
+        const int q = q0 + lane;
+        int c = 0, le = 0, src = 0;
+        if (q < experts) {
+          le = q / ep;
+          src = q % ep;
+          c = table[src * experts + d * local + le];
+        }
+        const long long incl = warp_inclusive_scan_ll(c, lane);
+        const long long first = run + incl - c;
+        if (q < experts) {
+          if (src == rank) dispatch_target_off[d * local + le] = first;
+          if (d == rank) {
+            combine_src_off[src * local + le] = first;
+            if (recv_segment_start != nullptr) recv_segment_start[le * ep + src] = first;
+            if (src == ep - 1) group_list[le] = first + c;  // rows of local experts 0 .. le
+          }
+        }
+        run += __shfl_sync(0xffffffffu, incl, 31);
+      }
+      if (d == rank && totals != nullptr && lane == 0) totals[1] = run;  // rows this rank receives
     }
-    if (d == rank && totals != nullptr) totals[1] = run;  // rows this rank receives
   }
 }
 
@@ -458,6 +632,32 @@ __global__ void histogram_kernel(const void* __restrict__ indices, int is_i64, l
 }  // namespace hmc
 
 using namespace hmc;
+
+static size_t fused_sort_smem(int experts) {
+  return static_cast<size_t>(experts) * sizeof(int) * (experts <= RANK_PARALLEL_EXPERTS ? 33 : 1);
+}
+
+// Chunks (= CTAs) of the one-launch sort that are resident together on the current device, 0 where cooperative
+// launches are not supported. Asked once per device and expert-count class.
+static int fused_sort_capacity(int experts) {
+  static int cached[64][2];
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return 0;
+  const int cls = experts <= RANK_PARALLEL_EXPERTS ? 0 : 1;
+  if (cached[device][cls] == 0) {
+    int cooperative = 0, per_sm = 0;
+    cudaDeviceGetAttribute(&cooperative, cudaDevAttrCooperativeLaunch, device);
+    // the largest shared-memory request of the class bounds the occupancy of every member
+    const size_t smem = cls == 0 ? fused_sort_smem(RANK_PARALLEL_EXPERTS) : fused_sort_smem(4096);
+    if (cooperative != 0 && smem <= 48 * 1024 &&
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, sort_routes_fused_kernel, SORT_THREADS, smem) == cudaSuccess &&
+        per_sm > 0)
+      cached[device][cls] = per_sm * sm_count();
+    else
+      cached[device][cls] = -1;
+  }
+  return cached[device][cls] > 0 ? cached[device][cls] : 0;
+}
 
 extern "C" int64_t hmc_moe_sort_workspace_bytes(int64_t entries, int64_t experts) {
   const int64_t chunks = (entries + SORT_CHUNK - 1) / SORT_CHUNK;
@@ -504,6 +704,18 @@ extern "C" int hmc_moe_sort_routes(const void* indices, int indices_are_i64, int
   const int e = static_cast<int>(experts);
   const size_t smem = experts * sizeof(int);
   int* chunk_counts = static_cast<int*>(workspace);
+  if (chunks <= fused_sort_capacity(e)) {
+    // every chunk's CTA is resident at once: one cooperative launch instead of three kernels
+    long long entries_arg = entries;
+    int experts_arg = e;
+    long long* ends = reinterpret_cast<long long*>(cumulative);
+    void* params[] = {&indices, &indices_are_i64, &entries_arg, &experts_arg, &chunk_counts, &mapping, &source_of_row,
+                      &expert_of_row, &counts, &ends, &status};
+    HMC_CUDA_OK(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(sort_routes_fused_kernel), dim3(chunks),
+                                            dim3(SORT_THREADS), params, fused_sort_smem(e), stream));
+    count_launch();
+    return 0;
+  }
   chunk_histogram_kernel<<<chunks, SORT_THREADS, smem, stream>>>(indices, indices_are_i64, entries, e,
                                                                chunk_counts, status);
   HMC_LAUNCH_OK();
@@ -666,7 +878,8 @@ extern "C" int hmc_route_offsets(const int32_t* counts, int64_t ep, int64_t expe
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
   const size_t table_bytes = static_cast<size_t>(ep) * experts * sizeof(int);
   const int stage_table = table_bytes <= 48 * 1024;
-  route_offsets_kernel<<<1, 256, stage_table ? table_bytes : 0, stream>>>(
+  const int offsets_threads = 32 * static_cast<int>(1 + 2 * ep < 32 ? 1 + 2 * ep : 32);  // one warp per running sum
+  route_offsets_kernel<<<1, offsets_threads, stage_table ? table_bytes : 0, stream>>>(
       counts, static_cast<int>(ep), static_cast<int>(experts), static_cast<int>(rank),
       reinterpret_cast<long long*>(dispatch_src_off), reinterpret_cast<long long*>(dispatch_target_off),
       dispatch_size, reinterpret_cast<long long*>(combine_src_off), reinterpret_cast<long long*>(combine_target_off),

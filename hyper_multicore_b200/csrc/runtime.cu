@@ -39,7 +39,7 @@ static cudaEvent_t take_event() {
 }
 
 ProfileScope::ProfileScope(int kind, cudaStream_t stream) : kind_(kind), stream_(stream), start_(nullptr), active_(false) {
-  if (g_profile_on.load(std::memory_order_relaxed) == 0) return;
+  if (((g_profile_on.load(std::memory_order_relaxed) >> kind) & 1) == 0) return;
   start_ = take_event();
   if (start_ == nullptr) return;
   if (cudaEventRecord(start_, stream_) != cudaSuccess) {
@@ -90,9 +90,9 @@ extern "C" int hmc_mega_moe_transport_version(void) { return 2; }
 extern "C" int hmc_worker_queue_layout_version(void) { return 2; }
 extern "C" int64_t hmc_launch_count(void) { return hmc::g_launches.load(std::memory_order_relaxed); }
 
-extern "C" int hmc_profile_enable(int on) {
+extern "C" int hmc_profile_enable_kinds(uint32_t kinds_mask) {
   using namespace hmc;
-  if (on) {
+  if (kinds_mask != 0) {
     std::lock_guard<std::mutex> lock(g_profile_mutex);
     while (g_profile_pool.size() < 1024) {
       cudaEvent_t e = nullptr;
@@ -100,9 +100,11 @@ extern "C" int hmc_profile_enable(int on) {
       g_profile_pool.push_back(e);
     }
   }
-  g_profile_on.store(on ? 1 : 0, std::memory_order_relaxed);
+  g_profile_on.store(static_cast<int>(kinds_mask & ((1u << HMC_PROFILE_KINDS) - 1u)), std::memory_order_relaxed);
   return 0;
 }
+
+extern "C" int hmc_profile_enable(int on) { return hmc_profile_enable_kinds(on ? (1u << HMC_PROFILE_KINDS) - 1u : 0u); }
 
 extern "C" int hmc_profile_dump(int32_t* kinds, double* start_ms, double* duration_ms, int capacity) {
   using namespace hmc;

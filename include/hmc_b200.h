@@ -48,7 +48,9 @@ int hmc_worker_queue_layout_version(void);
 /* Measurement helpers, no counterpart in the reference. hmc_launch_count: kernels this library has launched
  * in this process. While hmc_profile_enable(1) is in force, every call of the entry points listed below is
  * bracketed by two CUDA events on its stream; hmc_profile_collect waits for them, adds the device time and the
- * number of calls per kind into ms_by_kind / calls_by_kind [kinds] and forgets them (it synchronises). */
+ * number of calls per kind into ms_by_kind / calls_by_kind [kinds] and forgets them (it synchronises).
+ * hmc_profile_enable_kinds(mask) brackets only the kinds whose bit (1 << HMC_PROFILE_*) is set, so that a timed
+ * region can carry the events of its dominant kernel alone. */
 #define HMC_PROFILE_GROUPED_GEMM 0 /* hmc_grouped_gemm */
 #define HMC_PROFILE_MX_GEMM 1      /* hmc_mx_gemm */
 #define HMC_PROFILE_MX_QUANT 2     /* hmc_mx_quant */
@@ -57,6 +59,7 @@ int hmc_worker_queue_layout_version(void);
 #define HMC_PROFILE_KINDS 5
 int64_t hmc_launch_count(void);
 int hmc_profile_enable(int on);
+int hmc_profile_enable_kinds(uint32_t kinds_mask);
 int hmc_profile_collect(double* ms_by_kind, int64_t* calls_by_kind, int kinds);
 /* Like hmc_profile_collect, but returns the calls one by one in the order they were made: kind, start (ms after
  * the first call's start) and duration of up to `capacity` calls. Returns the number of calls written. */
