@@ -311,7 +311,7 @@ extern "C" int hmc_gate_project_promoted(const void* x_bf16, const void* w, int 
                                          int64_t hidden, int64_t experts, float* logits, void* workspace,
                                          int64_t workspace_bytes, int32_t* status, void* stream_ptr) {
   using namespace hmc;
-  HMC_REQUIRE(x_bf16 && w && logits && workspace, HMC_ERR_INVALID, "hmc_gate_project_promoted: null tensor pointer");
+  HMC_REQUIRE(x_bf16 && logits && workspace, HMC_ERR_INVALID, "hmc_gate_project_promoted: null tensor pointer");
   HMC_REQUIRE(tokens > 0 && experts > 0 && hidden > 0 && hidden % 8 == 0, HMC_ERR_INVALID,
               "hmc_gate_project_promoted: extents must be positive and hidden a multiple of 8");
   HMC_REQUIRE(tokens < (1ll << 31) && hidden < (1ll << 31) && experts <= 65536, HMC_ERR_LIMIT,
@@ -326,9 +326,11 @@ extern "C" int hmc_gate_project_promoted(const void* x_bf16, const void* w, int 
   const int parts = w_is_bf16 ? 1 : 3;
   __nv_bfloat16* split = static_cast<__nv_bfloat16*>(workspace);
   const long long split_elems = static_cast<long long>(epad) * hidden;
-  gate_split_parts_kernel<<<static_cast<unsigned>((split_elems + 255) / 256), 256, 0, stream>>>(
-      w, w_is_bf16, static_cast<int>(experts), epad, parts, hidden, split);
-  HMC_LAUNCH_OK();
+  if (w != nullptr) {  // w == NULL: the workspace still holds the parts of an earlier call with the same weight
+    gate_split_parts_kernel<<<static_cast<unsigned>((split_elems + 255) / 256), 256, 0, stream>>>(
+        w, w_is_bf16, static_cast<int>(experts), epad, parts, hidden, split);
+    HMC_LAUNCH_OK();
+  }
 
   CUtensorMap tx, tw;
   int rc;

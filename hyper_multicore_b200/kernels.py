@@ -190,9 +190,21 @@ def gate_project(x: torch.Tensor, weight: torch.Tensor, use_tensor_cores: bool |
         return logits
     if eligible and use_tensor_cores:
         need = _lib.load().hmc_gate_project_promoted_workspace_bytes(x.shape[1], weight.shape[0])
-        workspace = torch.empty(need, dtype=torch.uint8, device=device)
-        _call("hmc_gate_project_promoted", device, x.data_ptr(), weight.data_ptr(), int(weight.dtype == torch.bfloat16),
-              x.shape[0], x.shape[1], weight.shape[0], logits.data_ptr(), workspace.data_ptr(), need, None)
+        # The BF16 parts of the weight stay with the weight tensor until it is written to again (its version
+        # counter moves with every in-place update, e.g. an optimiser step).
+        cached = getattr(weight, "_hmc_gate_parts", None)
+        fresh = cached is None or cached[0] != weight._version or cached[1].device != device or cached[1].numel() != need
+        if fresh:
+            cached = (weight._version, torch.empty(need, dtype=torch.uint8, device=device))
+        workspace = cached[1]
+        _call("hmc_gate_project_promoted", device, x.data_ptr(), weight.data_ptr() if fresh else None,
+              int(weight.dtype == torch.bfloat16), x.shape[0], x.shape[1], weight.shape[0], logits.data_ptr(),
+              workspace.data_ptr(), need, None)
+        if fresh:
+            try:
+                weight._hmc_gate_parts = cached
+            except (AttributeError, RuntimeError):  # a tensor that takes no attributes: split again next time
+                pass
         return logits
     _call("hmc_gate_project", device, x.data_ptr(), int(x.dtype == torch.bfloat16), weight.data_ptr(),
           int(weight.dtype == torch.bfloat16), x.shape[0], x.shape[1], weight.shape[0], logits.data_ptr())

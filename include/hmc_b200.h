@@ -311,8 +311,10 @@ int hmc_gate_project_tc(const void* x_bf16, const void* w, int w_is_bf16, int64_
 /* tcgen05 projection with a bounded accumulation chain: the dominant BF16 part of the weight accumulates in
  * the tensor core for 128 elements of K at a time and is promoted into FP32 registers in between, which
  * keeps the result within the reference's logits tolerance (1e-5 / 1e-6). One kernel after the weight
- * split; workspace = three BF16 parts of the weight, padded to 64 experts. status (optional,
- * HMC_STATUS_WORDS) receives pipeline time-outs. */
+ * split; workspace = three BF16 parts of the weight, padded to 64 experts. A caller that keeps the workspace
+ * between calls may pass w = NULL while the weight is unchanged: the split is then skipped and the parts of the
+ * earlier call are used (w_is_bf16 must be the same as in that call). status (optional, HMC_STATUS_WORDS)
+ * receives pipeline time-outs. */
 int64_t hmc_gate_project_promoted_workspace_bytes(int64_t hidden, int64_t experts);
 int hmc_gate_project_promoted(const void* x_bf16, const void* w, int w_is_bf16, int64_t tokens, int64_t hidden,
                               int64_t experts, float* logits, void* workspace, int64_t workspace_bytes,

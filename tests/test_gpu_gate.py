@@ -155,6 +155,27 @@ def test_projection_is_fp32_accurate(cuda_device, x_dtype, w_dtype):
         torch.testing.assert_close(got, case["logits"], rtol=1e-5, atol=1e-6)
 
 
+def test_projection_follows_in_place_weight_updates(cuda_device):
+    """The BF16 parts of the weight are kept with the weight tensor between calls and split again after an
+    in-place update (an optimiser step): the logits must follow the new values, and an unchanged weight must
+    reproduce its logits bit for bit from the kept parts."""
+    from hyper_multicore_b200 import kernels as K
+
+    g = torch.Generator().manual_seed(11)
+    x = torch.randn(256, 512, generator=g).bfloat16().to(cuda_device)
+    w = (torch.randn(64, 512, generator=g) * 0.05).to(cuda_device)
+    first = K.gate_project(x, w)
+    again = K.gate_project(x, w)
+    assert torch.equal(first, again)
+    with torch.no_grad():
+        w.add_(torch.randn(64, 512, generator=g).to(cuda_device) * 0.05)
+    updated = K.gate_project(x, w)
+    exact = x.double() @ w.double().T
+    torch.testing.assert_close(updated.double(), exact, rtol=1e-5, atol=1e-5)
+    assert not torch.equal(first, updated)
+    assert torch.equal(updated, K.gate_project(x, w))
+
+
 def test_projection_at_the_multimodal_gate_shape(cuda_device):
     """8192 tokens x hidden 4096 x 64 experts: the tensor-core path against a float64 reference."""
     from hyper_multicore_b200 import kernels as K

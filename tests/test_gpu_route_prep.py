@@ -12,8 +12,12 @@ pytestmark = pytest.mark.gpu
 
 @pytest.mark.parametrize("tokens,top_k,experts,dtype", [
     (0, 2, 4, torch.int64), (1, 1, 1, torch.int32), (17, 2, 4, torch.int64), (128, 4, 32, torch.int32),
-    (129, 3, 7, torch.int64), (4096, 4, 32, torch.int64), (8192, 8, 256, torch.int32), (5000, 6, 1000, torch.int64)])
+    (129, 3, 7, torch.int64), (4096, 4, 32, torch.int64), (8192, 8, 256, torch.int32), (5000, 6, 1000, torch.int64),
+    (60000, 8, 64, torch.int32)])
 def test_sort_routes_is_bit_exact(cuda_device, tokens, top_k, experts, dtype):
+    """Up to a few hundred thousand routes the sort is one cooperative launch (per-warp counters up to 256 experts,
+    warps taking turns beyond); the 480000-route case needs more chunks than are resident at once and takes the
+    three-kernel path."""
     from hyper_multicore_b200 import _lib, kernels as K
 
     rng = np.random.default_rng(tokens + experts)
