@@ -4,12 +4,15 @@
 // module.py:195-198) for BF16 hidden states. x is exact in BF16; the FP32 weight is split into three
 // BF16 parts hi + mid + lo that reproduce it to 24 bits, so every product is exact in FP32 and the
 // only error left is the accumulation inside the tensor core, which grows with the length of the
-// accumulation chain. The chain of the dominant (hi) part is therefore cut every 128 elements of K:
-// two TMEM accumulators alternate, and while the tensor core fills one, the epilogue warps add the
-// other into FP32 registers (round-to-nearest adds on the CUDA cores). The mid and lo parts are
-// 2^-8 and 2^-16 of the result, so their single long chain adds nothing measurable.
+// accumulation chain. The chain is therefore cut every 128 elements of K: two TMEM accumulators
+// alternate, and while the tensor core fills one, the epilogue warps add the other into FP32 registers
+// (round-to-nearest adds on the CUDA cores). The three parts are stacked along N (64 experts x 3 = 192
+// accumulator columns), so one M128 N192 K16 instruction does what three N64 ones did - the kernel was
+// bound by the number of MMA instructions, not by their flops or by its loads. The mid and lo parts
+// (2^-8 and 2^-16 of the result) are promoted with the hi part and summed in a register set of their own.
 //
-// One CTA per 128 tokens x 64 experts (x K-slice): warp 0 = TMA producer, warp 1 = MMA issuer and TMEM
+// One CTA per 128 tokens x 64 experts (x K-slice; the two K-slices of a tile form a cluster and the first adds
+// the second's partial sums, a + b, so results repeat bit for bit): warp 0 = TMA producer, warp 1 = MMA issuer and TMEM
 // owner, warps 2..5 = promotion + epilogue (one per TMEM lane quarter).
 #include <cuda.h>
 
@@ -25,13 +28,14 @@ constexpr int GM = 128;                      // tokens per CTA
 constexpr int GN = 64;                       // experts per CTA
 constexpr int GK = 64;                       // K elements per pipeline stage (128-byte rows)
 constexpr int G_STAGES = 4;
-constexpr int G_PROMOTE = 2;                 // stages per accumulation chain of the hi part (128 K elements)
+constexpr int G_PROMOTE = 2;                 // stages per accumulation chain (128 K elements)
+constexpr int ACC_COLS = 3 * GN;             // TMEM columns of one accumulator: 64 experts x up to 3 weight parts
 constexpr int A_BYTES = GM * GK * 2;         // 16 KiB
 constexpr int B_BYTES = GN * GK * 2;         // 8 KiB per weight part
 constexpr int G_STAGE_BYTES = A_BYTES + 3 * B_BYTES;
 constexpr int G_THREADS = 6 * 32;
 constexpr int G_SMEM_BYTES = G_STAGES * G_STAGE_BYTES + 1024 + 256;
-constexpr uint32_t G_TMEM_COLS = 256;        // hi[0] @0, hi[1] @64, mid+lo @128
+constexpr uint32_t G_TMEM_COLS = 512;        // two accumulators of 64 x parts columns: @0 and @192
 constexpr uint32_t SWIZZLE_128B = 2;
 constexpr uint64_t G_BUDGET_NS = 4ull * 1000 * 1000 * 1000;
 
@@ -77,8 +81,7 @@ gate_project_promoted_kernel(const __grid_constant__ CUtensorMap tm_x, const __g
   uint64_t* empty_bar = bars + G_STAGES;           // [G_STAGES]
   uint64_t* hi_full_bar = bars + 2 * G_STAGES;     // [2]
   uint64_t* hi_empty_bar = bars + 2 * G_STAGES + 2;  // [2]
-  uint64_t* ml_full_bar = bars + 2 * G_STAGES + 4;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * G_STAGES + 5);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * G_STAGES + 4);
   volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -98,7 +101,6 @@ gate_project_promoted_kernel(const __grid_constant__ CUtensorMap tm_x, const __g
       mbar_init(&hi_full_bar[b], 1);
       mbar_init(&hi_empty_bar[b], 4);  // one arrival per promotion warp
     }
-    mbar_init(ml_full_bar, 1);
     *abort_word = 0;
     mbar_fence_init();
     prefetch_tensormap(&tm_x);
@@ -112,6 +114,11 @@ gate_project_promoted_kernel(const __grid_constant__ CUtensorMap tm_x, const __g
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  const int quarter = warp & 3;
+  float sum[GN];  // hi part (then the whole result); lives past the role branches for the cluster exchange
+#pragma unroll
+  for (int c = 0; c < GN; ++c) sum[c] = 0.f;
+  bool ok = true;
 
   if (warp == 0) {
     // ======================================================================== TMA producer
@@ -140,8 +147,8 @@ gate_project_promoted_kernel(const __grid_constant__ CUtensorMap tm_x, const __g
     int stage = 0;
     uint32_t phase = 0;
     uint32_t empty_phase[2] = {0, 0};
-    constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((GN >> 3) << 17) | ((GM >> 4) << 24);
-    bool ok = true;
+    // BF16 x BF16 -> FP32, K-major operands, M = 128, N = 64 experts x parts
+    const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (((GN * p.parts) >> 3) << 17) | ((GM >> 4) << 24);
     for (int i = 0; ok && i < nkb; ++i) {
       const int buf = (i / G_PROMOTE) & 1;
       const bool chain_start = i % G_PROMOTE == 0;
@@ -163,24 +170,14 @@ gate_project_promoted_kernel(const __grid_constant__ CUtensorMap tm_x, const __g
       if (lane == 0) {
         const uint32_t a_addr = smem_u32(smem + stage * G_STAGE_BYTES);
         const uint64_t da = make_smem_desc(a_addr, 16, 1024, SWIZZLE_128B);
-        const uint64_t db_hi = make_smem_desc(a_addr + A_BYTES, 16, 1024, SWIZZLE_128B);
-        const uint32_t tm_hi = tmem_base + static_cast<uint32_t>(buf * GN);
-        const uint32_t tm_ml = tmem_base + 2 * GN;
+        // the parts' 64-row tiles lie back to back: one B operand of 64 x parts rows
+        const uint64_t db = make_smem_desc(a_addr + A_BYTES, 16, 1024, SWIZZLE_128B);
+        const uint32_t tm_acc = tmem_base + static_cast<uint32_t>(buf * ACC_COLS);
 #pragma unroll
         for (int ks = 0; ks < GK / 16; ++ks)
-          umma_bf16(tm_hi, da + 2 * ks, db_hi + 2 * ks, idesc, (!chain_start || ks > 0) ? 1u : 0u);
-        if (p.parts == 3) {
-          const uint64_t db_mid = make_smem_desc(a_addr + A_BYTES + B_BYTES, 16, 1024, SWIZZLE_128B);
-          const uint64_t db_lo = make_smem_desc(a_addr + A_BYTES + 2 * B_BYTES, 16, 1024, SWIZZLE_128B);
-#pragma unroll
-          for (int ks = 0; ks < GK / 16; ++ks)
-            umma_bf16(tm_ml, da + 2 * ks, db_mid + 2 * ks, idesc, (i > 0 || ks > 0) ? 1u : 0u);
-#pragma unroll
-          for (int ks = 0; ks < GK / 16; ++ks) umma_bf16(tm_ml, da + 2 * ks, db_lo + 2 * ks, idesc, 1u);
-        }
+          umma_bf16(tm_acc, da + 2 * ks, db + 2 * ks, idesc, (!chain_start || ks > 0) ? 1u : 0u);
         umma_commit(&empty_bar[stage]);
         if (chain_end) umma_commit(&hi_full_bar[buf]);
-        if (i == nkb - 1) umma_commit(ml_full_bar);
       }
       __syncwarp();
       if (chain_end) empty_phase[buf] ^= 1u;
@@ -191,14 +188,12 @@ gate_project_promoted_kernel(const __grid_constant__ CUtensorMap tm_x, const __g
     }
   } else {
     // ======================================================================== promotion + epilogue
-    const int quarter = warp & 3;
     const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
-    float sum[GN];
+    float minor[GN];  // mid + lo parts
 #pragma unroll
-    for (int c = 0; c < GN; ++c) sum[c] = 0.f;
+    for (int c = 0; c < GN; ++c) minor[c] = 0.f;
     uint32_t full_phase[2] = {0, 0};
     const int chains = (nkb + G_PROMOTE - 1) / G_PROMOTE;
-    bool ok = true;
     for (int it = 0; ok && it < chains; ++it) {
       const int buf = it & 1;
       if (!mbar_wait(&hi_full_bar[buf], full_phase[buf], abort_word, G_BUDGET_NS)) {
@@ -207,56 +202,73 @@ gate_project_promoted_kernel(const __grid_constant__ CUtensorMap tm_x, const __g
         break;
       }
       tc_fence_after_sync();
+      const uint32_t acc = tmem_base + lane_base + static_cast<uint32_t>(buf * ACC_COLS);
       uint32_t v[32], w[32];
-      tmem_ld_32x32(tmem_base + lane_base + static_cast<uint32_t>(buf * GN), v);
-      tmem_ld_32x32(tmem_base + lane_base + static_cast<uint32_t>(buf * GN + 32), w);
+      tmem_ld_32x32(acc, v);
+      tmem_ld_32x32(acc + 32, w);
       tmem_ld_wait();
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&hi_empty_bar[buf]);  // the tensor core may start the next chain here
 #pragma unroll
       for (int c = 0; c < 32; ++c) {
         sum[c] += __uint_as_float(v[c]);
         sum[32 + c] += __uint_as_float(w[c]);
       }
+      if (p.parts == 3) {
+#pragma unroll 1
+        for (int part = 1; part < 3; ++part) {
+          tmem_ld_32x32(acc + static_cast<uint32_t>(part * GN), v);
+          tmem_ld_32x32(acc + static_cast<uint32_t>(part * GN + 32), w);
+          tmem_ld_wait();
+#pragma unroll
+          for (int c = 0; c < 32; ++c) {
+            minor[c] += __uint_as_float(v[c]);
+            minor[32 + c] += __uint_as_float(w[c]);
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&hi_empty_bar[buf]);  // the tensor core may start the next chain here
       full_phase[buf] ^= 1u;
     }
-    if (ok && p.parts == 3 && nkb > 0) {
-      if (!mbar_wait(ml_full_bar, 0u, abort_word, G_BUDGET_NS)) {
-        if (lane == 0) report_status(p.status, HMC_STATUS_TIMEOUT_PIPELINE, 4, 0, 0);
-        ok = false;
-      } else {
-        tc_fence_after_sync();
-        uint32_t v[32], w[32];
-        tmem_ld_32x32(tmem_base + lane_base + 2 * GN, v);
-        tmem_ld_32x32(tmem_base + lane_base + 2 * GN + 32, w);
-        tmem_ld_wait();
+    if (p.parts == 3) {
 #pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          sum[c] += __uint_as_float(v[c]);
-          sum[32 + c] += __uint_as_float(w[c]);
-        }
-      }
+      for (int c = 0; c < GN; ++c) sum[c] += minor[c];
     }
-    const long long row = static_cast<long long>(m0) + quarter * 32 + lane;
-    if (ok && row < p.tokens && nkb > 0) {
-      float* dst = p.logits + row * p.experts + e0;
-      if (gridDim.z == 1) {
-        if (p.experts % 4 == 0) {
+  }
+
+  // Two K-slices are the two CTAs of a cluster: the second hands its partial sums to the first through
+  // distributed shared memory (the pipeline ring is idle by then), which adds them and stores the logits once.
+  const bool sliced = gridDim.z > 1;
+  const uint32_t slice = sliced ? cluster_ctarank() : 0u;
+  const long long row = static_cast<long long>(m0) + quarter * 32 + lane;
+  if (sliced) {
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_sync_all();  // both CTAs' rings are drained
+    if (warp >= 2 && slice == 1) {
+      const uint32_t peer = map_to_cta(smem_u32(smem), 0);
+      const int r = quarter * 32 + lane;
 #pragma unroll
-          for (int c = 0; c < GN; c += 4)
-            if (e0 + c < p.experts) *reinterpret_cast<float4*>(dst + c) = make_float4(sum[c], sum[c + 1], sum[c + 2], sum[c + 3]);
-        } else {
+      for (int c = 0; c < GN; ++c) st_shared_cluster_f32(peer + static_cast<uint32_t>((c * GM + r) * 4), sum[c]);
+    }
+    cluster_sync_all();
+    if (warp >= 2 && slice == 0) {
+      const float* exchange = reinterpret_cast<const float*>(smem);
+      const int r = quarter * 32 + lane;
 #pragma unroll
-          for (int c = 0; c < GN; ++c)
-            if (e0 + c < p.experts) dst[c] = sum[c];
-        }
-      } else {
-        // two K-slices: 0 + a + b is the same number in either order, so the result stays deterministic
+      for (int c = 0; c < GN; ++c) sum[c] += exchange[c * GM + r];
+    }
+  }
+  if (warp >= 2 && slice == 0 && ok && row < p.tokens && nkb > 0) {
+    float* dst = p.logits + row * p.experts + e0;
+    if (p.experts % 4 == 0) {
 #pragma unroll
-        for (int c = 0; c < GN; ++c)
-          if (e0 + c < p.experts) atomicAdd(dst + c, sum[c]);
-      }
+      for (int c = 0; c < GN; c += 4)
+        if (e0 + c < p.experts) *reinterpret_cast<float4*>(dst + c) = make_float4(sum[c], sum[c + 1], sum[c + 2], sum[c + 3]);
+    } else {
+#pragma unroll
+      for (int c = 0; c < GN; ++c)
+        if (e0 + c < p.experts) dst[c] = sum[c];
     }
   }
 
@@ -351,11 +363,22 @@ extern "C" int hmc_gate_project_promoted(const void* x_bf16, const void* w, int 
   // a second K-slice when one slice per tile would leave most SMs idle
   const int slices = (static_cast<long long>(m_tiles) * n_tiles * 2 <= 2ll * sm_count() && p.k_blocks >= 4 * G_PROMOTE) ? 2 : 1;
   p.k_per_slice = ((p.k_blocks + slices - 1) / slices + G_PROMOTE - 1) / G_PROMOTE * G_PROMOTE;
-  if (slices > 1) HMC_CUDA_OK(cudaMemsetAsync(logits, 0, sizeof(float) * tokens * experts, stream));
   static PerDeviceFlag configured{};
   if (int rc = allow_dynamic_smem(gate_project_promoted_kernel, G_SMEM_BYTES, configured)) return rc;
   dim3 grid(m_tiles, n_tiles, static_cast<unsigned>(slices));
-  gate_project_promoted_kernel<<<grid, G_THREADS, G_SMEM_BYTES, stream>>>(tx, tw, p);
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = dim3(G_THREADS);
+  config.dynamicSmemBytes = G_SMEM_BYTES;
+  config.stream = stream;
+  cudaLaunchAttribute cluster;
+  cluster.id = cudaLaunchAttributeClusterDimension;
+  cluster.val.clusterDim.x = 1;
+  cluster.val.clusterDim.y = 1;
+  cluster.val.clusterDim.z = static_cast<unsigned>(slices);  // the K-slices of a tile exchange through shared memory
+  config.attrs = &cluster;
+  config.numAttrs = 1;
+  HMC_CUDA_OK(cudaLaunchKernelEx(&config, gate_project_promoted_kernel, tx, tw, p));
   HMC_LAUNCH_OK();
   return 0;
 }
