@@ -12,6 +12,8 @@
 //             -> dW2, dW1 -> bounded wait -> Top-K sum of dX
 #include <string.h>
 
+#include <stdlib.h>
+
 #include "common.cuh"
 
 namespace hmc {
@@ -720,13 +722,27 @@ extern "C" int hmc_mega_moe_mxfp8(const hmc_mega_moe_mxfp8_args* args, void* str
     hmc_mx_quant_args q = mx_quant_args(HMC_MXQ_PLAIN, s, a.pad_blocks, s.hidden, x_recv, nullptr, a.group_list, a.x_row,
                                         a.x_scale, a.x_col, a.x_col_scale);
     HMC_TRY(hmc_mx_quant(&q, stream));
-    hmc_mx_gemm_args g1 = mx_gemm_args(HMC_GEMM_RAGGED_M, HMC_MAJOR_MN, HMC_EPI_STORE_BF16, s, a.pad_blocks, 0, 2 * s.inter,
-                                       s.hidden, a.x_row, a.x_scale, a.w1_col_data, a.w1_col_scale, a.up, a.group_list,
-                                       status);
+    // GMM1 quantises bf16(silu(gate) * up) in its own epilogue (U is written once and not read again in this call);
+    // HMC_MX_FUSED_SWIGLU=0 keeps the plain GEMM followed by the stand-alone SwiGLU quantiser.
+    static const bool fused_swiglu = [] {
+      const char* v = getenv("HMC_MX_FUSED_SWIGLU");
+      return v == nullptr || v[0] != '0';
+    }();
+    hmc_mx_gemm_args g1 = mx_gemm_args(HMC_GEMM_RAGGED_M, HMC_MAJOR_MN, fused_swiglu ? HMC_EPI_SWIGLU_MXQ : HMC_EPI_STORE_BF16, s,
+                                       a.pad_blocks, 0, 2 * s.inter, s.hidden, a.x_row, a.x_scale, a.w1_col_data,
+                                       a.w1_col_scale, a.up, a.group_list, status);
+    if (fused_swiglu) {
+      g1.act_row_data = a.a_row;
+      g1.act_row_scale = a.a_scale;
+      g1.act_col_data = a.a_col;
+      g1.act_col_scale = a.a_col_scale;
+    }
     HMC_TRY(hmc_mx_gemm(&g1, stream));
-    hmc_mx_quant_args qa = mx_quant_args(HMC_MXQ_SWIGLU, s, a.pad_blocks, s.inter, a.up, nullptr, a.group_list, a.a_row,
-                                         a.a_scale, a.a_col, a.a_col_scale);
-    HMC_TRY(hmc_mx_quant(&qa, stream));
+    if (!fused_swiglu) {
+      hmc_mx_quant_args qa = mx_quant_args(HMC_MXQ_SWIGLU, s, a.pad_blocks, s.inter, a.up, nullptr, a.group_list, a.a_row,
+                                           a.a_scale, a.a_col, a.a_col_scale);
+      HMC_TRY(hmc_mx_quant(&qa, stream));
+    }
     hmc_mx_gemm_args g2 = mx_gemm_args(HMC_GEMM_RAGGED_M, HMC_MAJOR_MN, HMC_EPI_STORE_BF16, s, a.pad_blocks, 0, s.hidden,
                                        s.inter, a.a_row, a.a_scale, a.w2_col_data, a.w2_col_scale, ep1 ? a.down : nullptr,
                                        a.group_list, status);

@@ -423,7 +423,21 @@ extern "C" int hmc_mx_gemm(const hmc_mx_gemm_args* args, void* stream_ptr) {
   CUtensorMap ta, tb, tc;
   int rc;
   if (a.mode == HMC_GEMM_RAGGED_M) {
-    HMC_REQUIRE(a.epilogue == HMC_EPI_STORE_BF16, HMC_ERR_INVALID, "hmc_mx_gemm: RAGGED_M writes BF16 rows");
+    HMC_REQUIRE(a.epilogue == HMC_EPI_STORE_BF16 || a.epilogue == HMC_EPI_SWIGLU_MXQ, HMC_ERR_INVALID,
+                "hmc_mx_gemm: RAGGED_M writes BF16 rows (optionally with the quantised SwiGLU beside them)");
+    if (a.epilogue == HMC_EPI_SWIGLU_MXQ) {
+      HMC_REQUIRE(use_pairs && a.b_major == HMC_MAJOR_MN && a.combine == nullptr && a.c != nullptr, HMC_ERR_INVALID,
+                  "hmc_mx_gemm: the SwiGLU + quantise epilogue needs CTA-pair tiles (n %% 256 == 0), an MN-major weight, c "
+                  "and no fused combine");
+      HMC_REQUIRE(a.act_row_data && a.act_row_scale && (a.act_col_data == nullptr) == (a.act_col_scale == nullptr) &&
+                      aligned16(a.act_row_data) && aligned16(a.act_col_data),
+                  HMC_ERR_INVALID,
+                  "hmc_mx_gemm: the SwiGLU + quantise epilogue needs its 16-byte aligned row outputs (the column pair is optional)");
+      p.act_row_data = static_cast<uint8_t*>(a.act_row_data);
+      p.act_row_scale = static_cast<uint8_t*>(a.act_row_scale);
+      p.act_col_data = static_cast<uint8_t*>(a.act_col_data);
+      p.act_col_scale = static_cast<uint8_t*>(a.act_col_scale);
+    }
     HMC_REQUIRE(a.k > 0 && a.k % 128 == 0 && a.k < (1ll << 31), HMC_ERR_LIMIT,
                 "hmc_mx_gemm: k (%lld) must be a positive multiple of 128", (long long)a.k);
     p.k = static_cast<int>(a.k);
@@ -477,7 +491,7 @@ extern "C" int hmc_mx_gemm(const hmc_mx_gemm_args* args, void* stream_ptr) {
     const long long b_atoms = a.mode == HMC_GEMM_RAGGED_M ? static_cast<long long>(p.groups) * p.k_blocks * p.n_atoms
                                                           : static_cast<long long>(p.pad_blocks) * p.n_atoms;
     if ((rc = make_atom_map(&tsa, a.a_scale, a_atoms, 1)) != 0) return rc;
-    if ((rc = make_atom_map(&tsb, a.b_scale, b_atoms, 2)) != 0) return rc;
+    if ((rc = make_atom_map(&tsb, a.b_scale, b_atoms, a.epilogue == HMC_EPI_SWIGLU_MXQ ? 1 : 2)) != 0) return rc;
     p.n_tiles = p.n_atoms / 2;
     p.m_tiles = p.m_atoms / 2;
     const int a_major = a.mode == HMC_GEMM_RAGGED_K ? HMC_MAJOR_MN : HMC_MAJOR_K;

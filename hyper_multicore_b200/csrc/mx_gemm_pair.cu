@@ -20,6 +20,7 @@
 
 #include "common.cuh"
 #include "mx_gemm_shared.cuh"
+#include "mx_quant_shared.cuh"
 #include "sm100.cuh"
 
 namespace hmc {
@@ -41,7 +42,7 @@ constexpr uint32_t SF_SLOT_COLS = 16;
 constexpr int SF_SLOTS = 4;
 using PairWalker = TileWalkerT<2>;
 
-template <int A_MAJOR, int B_MAJOR>
+template <int A_MAJOR, int B_MAJOR, bool SWIGLU>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                     const __grid_constant__ CUtensorMap tm_c, const __grid_constant__ CUtensorMap tm_sa,
@@ -104,7 +105,10 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         // repeats the group's last block; its rows lie past the group's end and are never stored.
         int block = 2 * t.m_idx + static_cast<int>(rank);
         if (block >= t.blocks) block = t.blocks - 1;
-        const int n0 = t.n_idx * PAIR_N + static_cast<int>(rank) * 128;  // this CTA's columns of B
+        // this CTA's columns of B; with the fused SwiGLU the leader takes 128 gate columns and the second CTA the
+        // 128 up columns of the same activation columns, so that a thread's accumulator row holds both
+        constexpr bool swiglu = SWIGLU;
+        const int n0 = swiglu ? static_cast<int>(rank) * (p.n / 2) + t.n_idx * 128 : t.n_idx * PAIR_N + static_cast<int>(rank) * 128;
         for (int kb = 0; kb < kiters; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_word, PIPE_BUDGET_NS)) {
             report_status(p.status, HMC_STATUS_TIMEOUT_PIPELINE, 0, stage, kb);
@@ -123,7 +127,13 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             if (B_MAJOR == HMC_MAJOR_MN) tma_load_3d_pair(b_dst, &tm_b, &full_bar[stage], n0, kb * BK, t.group);
             else tma_load_3d_pair(b_dst, &tm_b, &full_bar[stage], kb * BK, n0, t.group);
             tma_load_2d_pair(sfa_dst, &tm_sa, &full_bar[stage], 0, kb * p.pad_blocks + pad_block);
-            tma_load_2d_pair(sfb_dst, &tm_sb, &full_bar[stage], 0, (t.group * p.k_blocks + kb) * p.n_atoms + 2 * t.n_idx);
+            const int sfb_first = (t.group * p.k_blocks + kb) * p.n_atoms;
+            if (swiglu) {  // one-atom boxes: the gate and the up columns' scales lie half a row of atoms apart
+              tma_load_2d_pair(sfb_dst, &tm_sb, &full_bar[stage], 0, sfb_first + t.n_idx);
+              tma_load_2d_pair(sfb_dst + ATOM_BYTES, &tm_sb, &full_bar[stage], 0, sfb_first + p.n_atoms / 2 + t.n_idx);
+            } else {
+              tma_load_2d_pair(sfb_dst, &tm_sb, &full_bar[stage], 0, sfb_first + 2 * t.n_idx);
+            }
           } else {
             const int pad_block = t.pad_block0 + kb;
             const int m0 = t.m_idx * 256 + static_cast<int>(rank) * 128;
@@ -238,19 +248,118 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       acc_phase ^= 1u;
       tc_fence_after_sync();
       // The warp's 32 rows x 128 columns leave tensor memory in one go; the accumulator is then free again.
-      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(half * 128);
+      // (with the fused SwiGLU: 64 gate columns and the 64 up columns of the same activation columns)
+      constexpr bool swiglu = SWIGLU;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+      const uint32_t first = static_cast<uint32_t>(swiglu ? half * 64 : half * 128);
+      const uint32_t second = static_cast<uint32_t>(swiglu ? 128 + half * 64 : half * 128 + 64);
       uint32_t v[4][32];
-      tmem_ld_32x32(taddr, v[0]);
-      tmem_ld_32x32(taddr + 32, v[1]);
-      tmem_ld_32x32(taddr + 64, v[2]);
-      tmem_ld_32x32(taddr + 96, v[3]);
+      tmem_ld_32x32(taddr + first, v[0]);
+      tmem_ld_32x32(taddr + first + 32, v[1]);
+      tmem_ld_32x32(taddr + second, v[2]);
+      tmem_ld_32x32(taddr + second + 32, v[3]);
       tmem_ld_wait();
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(leader_acc_empty);  // the MMA issuer lives in the leader
 
       uint8_t* row_base = my_stage + lane * 128;
-      if (p.mode == HMC_GEMM_RAGGED_K) {
+      if constexpr (swiglu) {
+        // U leaves as BF16 rows; bf16(silu(gate) * up) of the BF16-rounded gate and up leaves quantised along the
+        // row (32 columns per scale: thread-local) and down the rows (32 rows per scale: this warp's 32 lanes).
+        const int block = 2 * t.m_idx + static_cast<int>(rank);
+        if (block < t.blocks) {  // the repeated block of a half-empty tile stores nothing
+          const int width = p.n / 2;
+          const int pb = t.pad_block0 + block;
+          const long long out_row = t.row0 + static_cast<long long>(block) * 128 + row_in_cta;
+          const long long pad_row = static_cast<long long>(pb) * 128 + row_in_cta;
+          const int acol0 = t.n_idx * 128 + half * 64;  // this warp's activation columns
+          const unsigned long long dst_bits =
+              out_row < t.row1 ? reinterpret_cast<unsigned long long>(static_cast<__nv_bfloat16*>(p.c) + out_row * p.n + acol0) : 0ull;
+          const int sub = lane >> 3;
+          const int piece = lane & 7;
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {  // gate columns, then up columns
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              uint32_t* src = v[2 * j + (q >> 2)] + 8 * (q & 3);
+              uint4 o;
+              o.x = pack_bf16x2(__uint_as_float(src[0]), __uint_as_float(src[1]));
+              o.y = pack_bf16x2(__uint_as_float(src[2]), __uint_as_float(src[3]));
+              o.z = pack_bf16x2(__uint_as_float(src[4]), __uint_as_float(src[5]));
+              o.w = pack_bf16x2(__uint_as_float(src[6]), __uint_as_float(src[7]));
+              *reinterpret_cast<uint4*>(row_base + ((q ^ (lane & 7)) << 4)) = o;
+              // keep the BF16-rounded values: they are what a later reader of U would see
+              const uint32_t words[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+              for (int w = 0; w < 4; ++w) {
+                const float2 f = unpack_bf16x2(words[w]);
+                src[2 * w] = __float_as_uint(f.x);
+                src[2 * w + 1] = __float_as_uint(f.y);
+              }
+            }
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) {
+              const int r = i + sub;
+              const unsigned long long base = __shfl_sync(0xffffffffu, dst_bits, r);
+              if (base != 0) {
+                const uint4 val = *reinterpret_cast<const uint4*>(my_stage + r * 128 + ((piece ^ (r & 7)) << 4));
+                st_16(reinterpret_cast<uint8_t*>(base) + static_cast<long long>(j) * width * 2 + piece * 16, val);
+              }
+            }
+            __syncwarp();
+          }
+#pragma unroll
+          for (int b = 0; b < 2; ++b)
+#pragma unroll
+            for (int c = 0; c < 32; ++c)
+              v[b][c] = __float_as_uint(mxq::swiglu_bf16(__uint_as_float(v[b][c]), __uint_as_float(v[2 + b][c])));
+          uint8_t* row_atom = p.act_row_scale + (static_cast<long long>(t.n_idx) * p.pad_blocks + pb) * ATOM_BYTES;
+          uint8_t* col_atom = p.act_col_scale + (static_cast<long long>(pb) * (width / 128) + t.n_idx) * ATOM_BYTES;
+          const bool want_col = p.act_col_data != nullptr;  // the column-quantised copy only feeds the weight gradients
+#pragma unroll
+          for (int b = 0; b < 2; ++b) {
+            // along the row: one scale for this thread's 32 columns
+            float amax = 0.f;
+#pragma unroll
+            for (int c = 0; c < 32; ++c) amax = fmaxf(amax, fabsf(__uint_as_float(v[b][c])));
+            const uint32_t e_row = mxq::block_exponent(amax);
+            const float inv_row = mxq::inverse_scale(e_row);
+            uint32_t q_row[8], q_col[8];
+            uint32_t my_col_scale = 127u;
+#pragma unroll
+            for (int c = 0; c < 32; c += 4) {
+              uint32_t col_word = 0, row_word = 0;
+#pragma unroll
+              for (int h2 = 0; h2 < 4; h2 += 2) {
+                const float a0 = __uint_as_float(v[b][c + h2]);
+                const float a1 = __uint_as_float(v[b][c + h2 + 1]);
+                if (want_col) {  // down the rows: one scale per column for the 32 rows this warp holds
+                  const uint32_t e0 = mxq::block_exponent(__uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(fabsf(a0)))));
+                  const uint32_t e1 = mxq::block_exponent(__uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(fabsf(a1)))));
+                  if (lane == c + h2) my_col_scale = e0;
+                  if (lane == c + h2 + 1) my_col_scale = e1;
+                  col_word |= mxq::e4m3x2(a0 * mxq::inverse_scale(e0), a1 * mxq::inverse_scale(e1)) << (8 * h2);
+                }
+                row_word |= mxq::e4m3x2(a0 * inv_row, a1 * inv_row) << (8 * h2);
+              }
+              q_col[c >> 2] = col_word;
+              q_row[c >> 2] = row_word;
+            }
+            uint8_t* row_dst = p.act_row_data + pad_row * width + acol0 + 32 * b;
+            st_16(row_dst, make_uint4(q_row[0], q_row[1], q_row[2], q_row[3]));
+            st_16(row_dst + 16, make_uint4(q_row[4], q_row[5], q_row[6], q_row[7]));
+            row_atom[mxq::atom_offset(row_in_cta, half * 2 + b)] = static_cast<uint8_t>(e_row);
+            if (want_col) {
+              uint8_t* col_dst = p.act_col_data + pad_row * width + acol0 + 32 * b;
+              st_16(col_dst, make_uint4(q_col[0], q_col[1], q_col[2], q_col[3]));
+              st_16(col_dst + 16, make_uint4(q_col[4], q_col[5], q_col[6], q_col[7]));
+              col_atom[mxq::atom_offset(half * 64 + 32 * b + lane, quarter)] = static_cast<uint8_t>(my_col_scale);
+            }
+          }
+        }
+      } else if (p.mode == HMC_GEMM_RAGGED_K) {
         const bool f32 = p.epilogue == HMC_EPI_STORE_F32;
         const int m0 = t.m_idx * 256 + static_cast<int>(rank) * 128 + quarter * 32;
         if (f32) {
@@ -360,11 +469,11 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   }
 }
 
-template <int A_MAJOR, int B_MAJOR>
+template <int A_MAJOR, int B_MAJOR, bool SWIGLU>
 int launch_impl(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& tsa,
                 const CUtensorMap& tsb, const Params& p, int grid, cudaStream_t stream) {
   static PerDeviceFlag configured{};
-  auto kernel = mx_gemm_pair_kernel<A_MAJOR, B_MAJOR>;
+  auto kernel = mx_gemm_pair_kernel<A_MAJOR, B_MAJOR, SWIGLU>;
   if (int rc = allow_dynamic_smem(kernel, PAIR_SMEM_BYTES, configured)) return rc;
   kernel<<<grid, NUM_THREADS, PAIR_SMEM_BYTES, stream>>>(ta, tb, tc, tsa, tsb, p);
   HMC_LAUNCH_OK();
@@ -382,11 +491,12 @@ int launch_mx_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUte
   if (p.mode == HMC_GEMM_RAGGED_K) {
     const long long tiles = static_cast<long long>(p.groups) * p.m_tiles * p.n_tiles;
     if (2 * tiles < grid) grid = static_cast<int>(2 * tiles);
-    return launch_impl<HMC_MAJOR_MN, HMC_MAJOR_MN>(ta, tb, tc, tsa, tsb, p, grid, stream);
+    return launch_impl<HMC_MAJOR_MN, HMC_MAJOR_MN, false>(ta, tb, tc, tsa, tsb, p, grid, stream);
   }
   (void)a_major;
-  if (b_major == HMC_MAJOR_MN) return launch_impl<HMC_MAJOR_K, HMC_MAJOR_MN>(ta, tb, tc, tsa, tsb, p, grid, stream);
-  return launch_impl<HMC_MAJOR_K, HMC_MAJOR_K>(ta, tb, tc, tsa, tsb, p, grid, stream);
+  if (p.epilogue == HMC_EPI_SWIGLU_MXQ) return launch_impl<HMC_MAJOR_K, HMC_MAJOR_MN, true>(ta, tb, tc, tsa, tsb, p, grid, stream);
+  if (b_major == HMC_MAJOR_MN) return launch_impl<HMC_MAJOR_K, HMC_MAJOR_MN, false>(ta, tb, tc, tsa, tsb, p, grid, stream);
+  return launch_impl<HMC_MAJOR_K, HMC_MAJOR_K, false>(ta, tb, tc, tsa, tsb, p, grid, stream);
 }
 
 }  // namespace mx

@@ -45,6 +45,11 @@ struct Params {
   int* status;
   int combine_enabled;  // RAGGED_M: rows go to `combine` destinations instead of c
   CombineFuse combine;
+  // HMC_EPI_SWIGLU_MXQ: quantised bf16(silu(gate) * up), width n / 2, in the layouts of the stand-alone quantiser
+  uint8_t* act_row_data;
+  uint8_t* act_row_scale;
+  uint8_t* act_col_data;
+  uint8_t* act_col_scale;
 };
 
 struct Tile {

@@ -9,31 +9,17 @@
 //   shared exponent = floor(log2(max |x| of the block)) - 8   (8 = largest E4M3 exponent)
 //   element         = round-to-nearest-even(x / 2^exponent), saturating at +-448
 // with an all-zero block taking scale 1.
-#include <cuda_fp8.h>
-
 #include "common.cuh"
+#include "mx_quant_shared.cuh"
 
 namespace hmc {
 namespace {
 
+using namespace mxq;
+
 constexpr int TILE = 128;
 constexpr int LDB = TILE + 8;  // shared-memory row stride in BF16 elements (16-byte rows, conflict-free both ways)
 constexpr int THREADS = 256;
-
-// biased UE8M0 exponent of a block whose largest magnitude is `amax`
-__device__ __forceinline__ uint32_t block_exponent(float amax) {
-  if (!(amax > 0.f)) return 127u;
-  const int e = static_cast<int>((__float_as_uint(amax) >> 23) & 0xffu) - 8;
-  return static_cast<uint32_t>(min(max(e, 0), 254));
-}
-__device__ __forceinline__ float inverse_scale(uint32_t biased) { return __uint_as_float((254u - biased) << 23); }
-// two values -> two E4M3 bytes (first value in the low byte), round to nearest even, saturating
-__device__ __forceinline__ uint32_t e4m3x2(float lo, float hi) {
-  return static_cast<uint32_t>(__nv_cvt_float2_to_fp8x2(make_float2(lo, hi), __NV_SATFINITE, __NV_E4M3));
-}
-__device__ __forceinline__ uint8_t to_e4m3(float v) {
-  return static_cast<uint8_t>(__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3));
-}
 
 struct QuantParams {
   int kind;
@@ -119,8 +105,6 @@ __device__ __forceinline__ void column_pass(const QuantParams& p, const TilePlac
   atom[(c_even & 31) * 16 + (c_even >> 5) * 4 + jb] = static_cast<uint8_t>(e0);
   atom[((c_even + 1) & 31) * 16 + ((c_even + 1) >> 5) * 4 + jb] = static_cast<uint8_t>(e1);
 }
-
-__device__ __forceinline__ float sigmoid_f(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
 
 // One CTA per (128-row padded block, 128-column block of the source). KIND is a compile-time constant so
 // that each variant is straight-line code whose global loads are all issued before the first of them is
@@ -225,8 +209,8 @@ __global__ void __launch_bounds__(THREADS, 2) mx_quant_kernel(const QuantParams 
         } else if (KIND == HMC_MXQ_SWIGLU) {
           const float2 g = unpack_bf16x2(aw[q]);
           const float2 u = unpack_bf16x2(bw[q]);
-          v[2 * q] = bf16_round(g.x * sigmoid_f(g.x) * u.x);
-          v[2 * q + 1] = bf16_round(g.y * sigmoid_f(g.y) * u.y);
+          v[2 * q] = swiglu_bf16(g.x, u.x);
+          v[2 * q + 1] = swiglu_bf16(g.y, u.y);
         } else {
           const float2 g = unpack_bf16x2(aw[q]);
           const float2 u = unpack_bf16x2(bw[q]);

@@ -84,6 +84,8 @@ int hmc_profile_dump(int32_t* kinds, double* start_ms, double* duration_ms, int 
 #define HMC_EPI_STORE_F32 1   /* FP32 output (partial weight gradients, mHC projection) */
 #define HMC_EPI_SWIGLU 2      /* B has 2n columns [gate | up]; c = U[rows, 2n], aux = Act[rows, n] */
 #define HMC_EPI_SWIGLU_GRAD 3 /* acc = dAct[rows, n]; aux = U[rows, 2n] (input); c = dU[rows, 2n] */
+#define HMC_EPI_SWIGLU_MXQ 4  /* hmc_mx_gemm only: c = U[rows, n] with n = 2 * width, and bf16(silu(gate) * up) leaves the
+                                 epilogue quantised along both axes (what hmc_mx_quant's HMC_MXQ_SWIGLU would make of U) */
 #define HMC_CLAMP_NONE 0
 #define HMC_CLAMP_BEFORE_SILU 1 /* silu(min(g, L)) * clamp(u, -L, L) */
 #define HMC_CLAMP_AFTER_SILU 2  /* min(silu(g), L) * clamp(u, -L, L) */
@@ -183,7 +185,7 @@ int64_t hmc_grouped_gemm_combine_units(int64_t n);
 typedef struct hmc_mx_gemm_args {
   int32_t mode;     /* HMC_GEMM_RAGGED_M or HMC_GEMM_RAGGED_K */
   int32_t b_major;  /* RAGGED_M: MN = b[groups, k, n], K = b[groups, n, k]. RAGGED_K: ignored */
-  int32_t epilogue; /* HMC_EPI_STORE_BF16, or HMC_EPI_STORE_F32 (RAGGED_K only) */
+  int32_t epilogue; /* HMC_EPI_STORE_BF16, HMC_EPI_STORE_F32 (RAGGED_K only) or HMC_EPI_SWIGLU_MXQ (RAGGED_M only) */
   int32_t groups;
   int32_t max_ctas;
   int32_t tile_mode;  /* HMC_TILE_AUTO, _SINGLE (128 x 128 tiles) or _PAIR (256 x 256 CTA-pair tiles; needs n % 256 == 0,
@@ -202,6 +204,13 @@ typedef struct hmc_mx_gemm_args {
   int32_t* status;
   const hmc_gemm_combine* combine; /* optional, RAGGED_M: rows go to their source ranks (see hmc_gemm_combine);
                                       c may then be NULL; counter units per row: hmc_mx_gemm_combine_units(n) */
+  /* HMC_EPI_SWIGLU_MXQ (RAGGED_M, b_major MN, CTA-pair tiles): the quantised activation in the layouts of
+   * hmc_mx_quant_args, width = n / 2: e4m3 [pad_blocks*128, width] twice and their scale atoms (the column pair may
+   * be NULL). */
+  void* act_row_data;
+  void* act_row_scale;
+  void* act_col_data;
+  void* act_col_scale;
 } hmc_mx_gemm_args;
 
 int hmc_mx_gemm(const hmc_mx_gemm_args* args, void* stream);

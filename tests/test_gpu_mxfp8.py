@@ -206,6 +206,45 @@ def test_cta_pair_tiles_equal_one_cta_tiles_bit_for_bit(cuda_device, counts):
                                      tile_mode=tm), (experts, k, n), dtype)
 
 
+@pytest.mark.parametrize("counts", [[300, 0, 129, 640, 1, 256], [128], [1000, 385]])
+def test_swiglu_quantising_epilogue_equals_gemm_then_quantiser(cuda_device, counts):
+    """GEMM1 with the SwiGLU + dual-axis quantisation in its epilogue writes the same U and, bit for bit, the
+    same quantised activation (both axes, data and scales, padding rows of every used block included) as the
+    plain GEMM followed by the stand-alone SwiGLU quantiser."""
+    from hyper_multicore_b200 import kernels as K
+
+    dev = cuda_device
+    g = torch.Generator().manual_seed(17 + len(counts))
+    experts, rows, k, inter = len(counts), sum(counts), 512, 384
+    ends = torch.tensor(counts, dtype=torch.int64).cumsum(0).to(dev)
+    x = torch.randn(rows, k, generator=g).bfloat16().to(dev)
+    w = (torch.randn(experts, k, 2 * inter, generator=g) * 0.08).bfloat16().to(dev)
+    fields = K.mx_quant_weight(w)
+    atoms = K.mx_pack_weight_scale(fields["col_scale"], 0, experts, k, 2 * inter)
+    xq = K.mx_quant(x, ends, k, want_row=True)
+    status = torch.zeros(4, dtype=torch.int32, device=dev)
+    common = dict(mode=K.HMC_GEMM_RAGGED_M, rows=rows, pad_blocks=xq.pad_blocks, n=2 * inter, k=k, b_major=K.HMC_MAJOR_MN,
+                  status=status)
+    u_plain = torch.zeros(rows, 2 * inter, dtype=torch.bfloat16, device=dev)
+    K.mx_gemm(xq.row_data, xq.row_scale, fields["col_data"], atoms, u_plain, ends, **common)
+    ref = K.mx_quant(u_plain, ends, inter, kind=K.HMC_MXQ_SWIGLU, want_row=True, want_col=True)
+    u_fused = torch.zeros_like(u_plain)
+    got = K.MxActivations(rows, experts, inter, dev, want_row=True, want_col=True)
+    K.mx_gemm(xq.row_data, xq.row_scale, fields["col_data"], atoms, u_fused, ends, epilogue=K.HMC_EPI_SWIGLU_MXQ, act=got,
+              **common)
+    torch.cuda.synchronize()
+    assert int(status[0]) == 0, status.tolist()
+    assert torch.equal(u_plain, u_fused) and u_plain.float().abs().sum() > 0
+    used = sum((c + 127) // 128 for c in counts)  # blocks that hold rows; the spare ones behind them are never written
+    assert got.pad_blocks == ref.pad_blocks
+    assert torch.equal(got.row_data[:used * 128], ref.row_data[:used * 128])
+    assert torch.equal(got.col_data[:used * 128], ref.col_data[:used * 128])
+    row_atoms = lambda q: q.row_scale.view(inter // 128, q.pad_blocks, 512)[:, :used]
+    col_atoms = lambda q: q.col_scale.view(q.pad_blocks, inter // 128, 512)[:used]
+    assert torch.equal(row_atoms(got), row_atoms(ref))
+    assert torch.equal(col_atoms(got), col_atoms(ref))
+
+
 def test_requantised_weights_replace_cached_scale_factors(cuda_device):
     """One module, weights updated in place and re-quantised between calls (an optimiser step): the new
     field tensors tend to land in the memory the old ones just freed, and fresh weights may even get a
