@@ -24,6 +24,7 @@ HMC_EPI_STORE_F32 = 1
 HMC_EPI_SWIGLU = 2
 HMC_EPI_SWIGLU_GRAD = 3
 HMC_EPI_SWIGLU_MXQ = 4
+HMC_EPI_SWIGLU_GRAD_MXQ = 5
 HMC_STATUS_WORDS = 8
 HMC_CTRL_SOURCE = 1296
 HMC_CTRL_COUNTS = 1552
@@ -215,6 +216,7 @@ class MxGemmArgs(ctypes.Structure):
         ("a", c_void_p), ("a_scale", c_void_p), ("b", c_void_p), ("b_scale", c_void_p), ("c", c_void_p),
         ("group_ends", c_void_p), ("status", c_void_p), ("combine", c_void_p),
         ("act_row_data", c_void_p), ("act_row_scale", c_void_p), ("act_col_data", c_void_p), ("act_col_scale", c_void_p),
+        ("aux", c_void_p),
     ]
 
 

@@ -813,15 +813,32 @@ extern "C" int hmc_mega_moe_mxfp8_grad(const hmc_mega_moe_mxfp8_grad_args* args,
     hmc_mx_quant_args q = mx_quant_args(HMC_MXQ_PLAIN, s, a.pad_blocks, s.hidden, dy_recv, nullptr, a.group_list, a.dy_row,
                                         a.dy_scale, want_dw ? a.dy_col : nullptr, want_dw ? a.dy_col_scale : nullptr);
     HMC_TRY(hmc_mx_quant(&q, stream));
-    // W2 [e, I, H] row-quantised (blocks along H) is the K-major B of dA = dY . W2^T
-    hmc_mx_gemm_args g1 = mx_gemm_args(HMC_GEMM_RAGGED_M, HMC_MAJOR_K, HMC_EPI_STORE_BF16, s, a.pad_blocks, 0, s.inter,
-                                       s.hidden, a.dy_row, a.dy_scale, a.w2_row_data, a.w2_row_scale, a.da, a.group_list,
-                                       status);
+    // W2 [e, I, H] row-quantised (blocks along H) is the K-major B of dA = dY . W2^T. The GEMM can also produce
+    // the quantised dU = SwiGLU-grad(dA, U) in its epilogue (HMC_MX_FUSED_SWIGLU_GRAD=1, I a multiple of 256), but
+    // eight epilogue warps per SM evaluate the sigmoids and the two quantisations more slowly than the stand-alone
+    // quantiser's full grid does (dA 390 us against 134 + 87 us on the 4096-token bench shape): off by default.
+    static const bool fused_allowed = [] {
+      const char* v = getenv("HMC_MX_FUSED_SWIGLU_GRAD");
+      return v != nullptr && v[0] == '1';
+    }();
+    const bool fused_grad = fused_allowed && s.inter % 256 == 0;
+    hmc_mx_gemm_args g1 = mx_gemm_args(HMC_GEMM_RAGGED_M, HMC_MAJOR_K, fused_grad ? HMC_EPI_SWIGLU_GRAD_MXQ : HMC_EPI_STORE_BF16,
+                                       s, a.pad_blocks, 0, s.inter, s.hidden, a.dy_row, a.dy_scale, a.w2_row_data,
+                                       a.w2_row_scale, fused_grad ? nullptr : a.da, a.group_list, status);
+    if (fused_grad) {
+      g1.aux = a.up;
+      g1.act_row_data = a.du_row;
+      g1.act_row_scale = a.du_scale;
+      g1.act_col_data = want_dw ? a.du_col : nullptr;
+      g1.act_col_scale = want_dw ? a.du_col_scale : nullptr;
+    }
     HMC_TRY(hmc_mx_gemm(&g1, stream));
-    hmc_mx_quant_args qu = mx_quant_args(HMC_MXQ_SWIGLU_GRAD, s, a.pad_blocks, 2 * s.inter, a.da, a.up, a.group_list,
-                                         a.du_row, a.du_scale, want_dw ? a.du_col : nullptr,
-                                         want_dw ? a.du_col_scale : nullptr);
-    HMC_TRY(hmc_mx_quant(&qu, stream));
+    if (!fused_grad) {
+      hmc_mx_quant_args qu = mx_quant_args(HMC_MXQ_SWIGLU_GRAD, s, a.pad_blocks, 2 * s.inter, a.da, a.up, a.group_list,
+                                           a.du_row, a.du_scale, want_dw ? a.du_col : nullptr,
+                                           want_dw ? a.du_col_scale : nullptr);
+      HMC_TRY(hmc_mx_quant(&qu, stream));
+    }
     hmc_mx_gemm_args g2 = mx_gemm_args(HMC_GEMM_RAGGED_M, HMC_MAJOR_K, HMC_EPI_STORE_BF16, s, a.pad_blocks, 0, s.hidden,
                                        2 * s.inter, a.du_row, a.du_scale, a.w1_row_data, a.w1_row_scale,
                                        ep1 ? a.dx : nullptr, a.group_list, status);

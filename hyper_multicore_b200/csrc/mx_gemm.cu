@@ -369,7 +369,9 @@ extern "C" int hmc_mx_gemm(const hmc_mx_gemm_args* args, void* stream_ptr) {
               "hmc_mx_gemm: groups and pad_blocks must be positive, rows non-negative");
   HMC_REQUIRE(a.pad_blocks >= (a.rows + 127) / 128 && a.pad_blocks * 128 < (1ll << 31), HMC_ERR_INVALID,
               "hmc_mx_gemm: pad_blocks (%lld) cannot hold %lld rows", (long long)a.pad_blocks, (long long)a.rows);
-  HMC_REQUIRE(a.a && a.b && (a.c || a.combine) && a.a_scale && a.b_scale && a.group_ends, HMC_ERR_INVALID,
+  HMC_REQUIRE(a.a && a.b && (a.c || a.combine || a.epilogue == HMC_EPI_SWIGLU_GRAD_MXQ) && a.a_scale && a.b_scale &&
+                  a.group_ends,
+              HMC_ERR_INVALID,
               "hmc_mx_gemm: null tensor pointer");
   HMC_REQUIRE(aligned16(a.a) && aligned16(a.b) && aligned16(a.c) && aligned16(a.a_scale) && aligned16(a.b_scale),
               HMC_ERR_INVALID, "hmc_mx_gemm: tensors must be 16-byte aligned");
@@ -423,20 +425,25 @@ extern "C" int hmc_mx_gemm(const hmc_mx_gemm_args* args, void* stream_ptr) {
   CUtensorMap ta, tb, tc;
   int rc;
   if (a.mode == HMC_GEMM_RAGGED_M) {
-    HMC_REQUIRE(a.epilogue == HMC_EPI_STORE_BF16 || a.epilogue == HMC_EPI_SWIGLU_MXQ, HMC_ERR_INVALID,
-                "hmc_mx_gemm: RAGGED_M writes BF16 rows (optionally with the quantised SwiGLU beside them)");
-    if (a.epilogue == HMC_EPI_SWIGLU_MXQ) {
-      HMC_REQUIRE(use_pairs && a.b_major == HMC_MAJOR_MN && a.combine == nullptr && a.c != nullptr, HMC_ERR_INVALID,
-                  "hmc_mx_gemm: the SwiGLU + quantise epilogue needs CTA-pair tiles (n %% 256 == 0), an MN-major weight, c "
-                  "and no fused combine");
+    const bool fused = a.epilogue == HMC_EPI_SWIGLU_MXQ || a.epilogue == HMC_EPI_SWIGLU_GRAD_MXQ;
+    HMC_REQUIRE(a.epilogue == HMC_EPI_STORE_BF16 || fused, HMC_ERR_INVALID,
+                "hmc_mx_gemm: RAGGED_M writes BF16 rows (optionally with a quantised SwiGLU / SwiGLU-grad beside them)");
+    if (fused) {
+      const bool grad = a.epilogue == HMC_EPI_SWIGLU_GRAD_MXQ;
+      HMC_REQUIRE(use_pairs && a.b_major == (grad ? HMC_MAJOR_K : HMC_MAJOR_MN) && a.combine == nullptr, HMC_ERR_INVALID,
+                  "hmc_mx_gemm: a quantising epilogue needs CTA-pair tiles (n %% 256 == 0), an %s weight and no fused combine",
+                  grad ? "K-major" : "MN-major");
+      HMC_REQUIRE(grad ? (a.aux != nullptr && aligned16(a.aux)) : a.c != nullptr, HMC_ERR_INVALID,
+                  "hmc_mx_gemm: the SwiGLU epilogue writes U into c; the SwiGLU-grad epilogue reads U from aux");
       HMC_REQUIRE(a.act_row_data && a.act_row_scale && (a.act_col_data == nullptr) == (a.act_col_scale == nullptr) &&
                       aligned16(a.act_row_data) && aligned16(a.act_col_data),
                   HMC_ERR_INVALID,
-                  "hmc_mx_gemm: the SwiGLU + quantise epilogue needs its 16-byte aligned row outputs (the column pair is optional)");
+                  "hmc_mx_gemm: a quantising epilogue needs its 16-byte aligned row outputs (the column pair is optional)");
       p.act_row_data = static_cast<uint8_t*>(a.act_row_data);
       p.act_row_scale = static_cast<uint8_t*>(a.act_row_scale);
       p.act_col_data = static_cast<uint8_t*>(a.act_col_data);
       p.act_col_scale = static_cast<uint8_t*>(a.act_col_scale);
+      p.aux = a.aux;
     }
     HMC_REQUIRE(a.k > 0 && a.k % 128 == 0 && a.k < (1ll << 31), HMC_ERR_LIMIT,
                 "hmc_mx_gemm: k (%lld) must be a positive multiple of 128", (long long)a.k);

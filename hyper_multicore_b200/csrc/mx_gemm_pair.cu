@@ -42,7 +42,81 @@ constexpr uint32_t SF_SLOT_COLS = 16;
 constexpr int SF_SLOTS = 4;
 using PairWalker = TileWalkerT<2>;
 
-template <int A_MAJOR, int B_MAJOR, bool SWIGLU>
+// Where one warp's quantised values go: row r_in_block of padded block pb, in a [pad_rows, width] tensor pair
+// (row-quantised, and optionally column-quantised) with their scale atoms.
+struct QuantOut {
+  uint8_t* row_data;
+  uint8_t* row_scale;
+  uint8_t* col_data;   // nullptr: no column-quantised copy
+  uint8_t* col_scale;
+  int width;
+  int pad_blocks;
+  int pb;
+  int r_in_block;      // this thread's row of the 128-row block: 32 * quarter + lane
+};
+
+// Quantises 32 BF16-exact values of this thread's row, columns [col, col + 32) (col a multiple of 32), along the
+// row (one scale for the 32 values: thread-local) and down the rows (one scale per column for the 32 rows the
+// warp's lanes hold), exactly as mx_quant_kernel does from a tile in memory. The 32 column maxima come from a
+// transpose-reduce over the warp (31 shuffles: at every step a lane hands the half of its columns it does not
+// keep to the lane `half` away, so lane L ends with the maximum of column L); the 32 exponents then go round
+// through 32 bytes of the warp's shared-memory stage.
+__device__ __forceinline__ void quantise_chunk(const float (&a)[32], const QuantOut& o, int col, int lane, uint8_t* scratch) {
+  const long long pad_row = static_cast<long long>(o.pb) * 128 + o.r_in_block;
+  const int cb = col >> 7;           // 128-column block
+  const int kk = (col & 127) >> 5;   // 32-column block inside it
+  float amax = 0.f;
+#pragma unroll
+  for (int c = 0; c < 32; ++c) amax = fmaxf(amax, fabsf(a[c]));
+  const uint32_t e_row = mxq::block_exponent(amax);
+  const float inv_row = mxq::inverse_scale(e_row);
+  uint32_t q_row[8];
+#pragma unroll
+  for (int c = 0; c < 32; c += 4)
+    q_row[c >> 2] = mxq::e4m3x2(a[c] * inv_row, a[c + 1] * inv_row) | (mxq::e4m3x2(a[c + 2] * inv_row, a[c + 3] * inv_row) << 16);
+  uint8_t* row_dst = o.row_data + pad_row * o.width + col;
+  st_16(row_dst, make_uint4(q_row[0], q_row[1], q_row[2], q_row[3]));
+  st_16(row_dst + 16, make_uint4(q_row[4], q_row[5], q_row[6], q_row[7]));
+  o.row_scale[(static_cast<long long>(cb) * o.pad_blocks + o.pb) * ATOM_BYTES + mxq::atom_offset(o.r_in_block, kk)] =
+      static_cast<uint8_t>(e_row);
+  if (o.col_data == nullptr) return;
+
+  uint32_t m[32];  // |a| as integers: the order of non-negative floats
+#pragma unroll
+  for (int c = 0; c < 32; ++c) m[c] = __float_as_uint(fabsf(a[c]));
+#pragma unroll
+  for (int half = 16; half >= 1; half >>= 1) {
+    const bool upper = (lane & half) != 0;
+#pragma unroll
+    for (int i = 0; i < half; ++i) {
+      const uint32_t send = upper ? m[i] : m[i + half];
+      const uint32_t keep = upper ? m[i + half] : m[i];
+      m[i] = max(keep, __shfl_xor_sync(0xffffffffu, send, half));
+    }
+  }
+  const uint32_t e_mine = mxq::block_exponent(__uint_as_float(m[0]));  // scale of column `lane`
+  __syncwarp();
+  scratch[lane] = static_cast<uint8_t>(e_mine);
+  __syncwarp();
+  const uint4 e_lo = *reinterpret_cast<const uint4*>(scratch);
+  const uint4 e_hi = *reinterpret_cast<const uint4*>(scratch + 16);
+  const uint32_t e_words[8] = {e_lo.x, e_lo.y, e_lo.z, e_lo.w, e_hi.x, e_hi.y, e_hi.z, e_hi.w};
+  uint32_t q_col[8];
+#pragma unroll
+  for (int c = 0; c < 32; c += 4) {
+    const uint32_t e4 = e_words[c >> 2];
+    const float i0 = mxq::inverse_scale(e4 & 0xffu), i1 = mxq::inverse_scale((e4 >> 8) & 0xffu);
+    const float i2 = mxq::inverse_scale((e4 >> 16) & 0xffu), i3 = mxq::inverse_scale(e4 >> 24);
+    q_col[c >> 2] = mxq::e4m3x2(a[c] * i0, a[c + 1] * i1) | (mxq::e4m3x2(a[c + 2] * i2, a[c + 3] * i3) << 16);
+  }
+  uint8_t* col_dst = o.col_data + pad_row * o.width + col;
+  st_16(col_dst, make_uint4(q_col[0], q_col[1], q_col[2], q_col[3]));
+  st_16(col_dst + 16, make_uint4(q_col[4], q_col[5], q_col[6], q_col[7]));
+  o.col_scale[(static_cast<long long>(o.pb) * (o.width / 128) + cb) * ATOM_BYTES +
+              mxq::atom_offset((col & 127) + lane, o.r_in_block >> 5)] = static_cast<uint8_t>(e_mine);
+}
+
+template <int A_MAJOR, int B_MAJOR, int FUSED>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                     const __grid_constant__ CUtensorMap tm_c, const __grid_constant__ CUtensorMap tm_sa,
@@ -107,7 +181,7 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         if (block >= t.blocks) block = t.blocks - 1;
         // this CTA's columns of B; with the fused SwiGLU the leader takes 128 gate columns and the second CTA the
         // 128 up columns of the same activation columns, so that a thread's accumulator row holds both
-        constexpr bool swiglu = SWIGLU;
+        constexpr bool swiglu = FUSED == 1;
         const int n0 = swiglu ? static_cast<int>(rank) * (p.n / 2) + t.n_idx * 128 : t.n_idx * PAIR_N + static_cast<int>(rank) * 128;
         for (int kb = 0; kb < kiters; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_word, PIPE_BUDGET_NS)) {
@@ -249,7 +323,7 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       tc_fence_after_sync();
       // The warp's 32 rows x 128 columns leave tensor memory in one go; the accumulator is then free again.
       // (with the fused SwiGLU: 64 gate columns and the 64 up columns of the same activation columns)
-      constexpr bool swiglu = SWIGLU;
+      constexpr bool swiglu = FUSED == 1;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
       const uint32_t first = static_cast<uint32_t>(swiglu ? half * 64 : half * 128);
       const uint32_t second = static_cast<uint32_t>(swiglu ? 128 + half * 64 : half * 128 + 64);
@@ -264,7 +338,7 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       if (lane == 0) mbar_arrive_cluster(leader_acc_empty);  // the MMA issuer lives in the leader
 
       uint8_t* row_base = my_stage + lane * 128;
-      if constexpr (swiglu) {
+      if constexpr (FUSED == 1) {
         // U leaves as BF16 rows; bf16(silu(gate) * up) of the BF16-rounded gate and up leaves quantised along the
         // row (32 columns per scale: thread-local) and down the rows (32 rows per scale: this warp's 32 lanes).
         const int block = 2 * t.m_idx + static_cast<int>(rank);
@@ -315,48 +389,63 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
 #pragma unroll
             for (int c = 0; c < 32; ++c)
               v[b][c] = __float_as_uint(mxq::swiglu_bf16(__uint_as_float(v[b][c]), __uint_as_float(v[2 + b][c])));
-          uint8_t* row_atom = p.act_row_scale + (static_cast<long long>(t.n_idx) * p.pad_blocks + pb) * ATOM_BYTES;
-          uint8_t* col_atom = p.act_col_scale + (static_cast<long long>(pb) * (width / 128) + t.n_idx) * ATOM_BYTES;
-          const bool want_col = p.act_col_data != nullptr;  // the column-quantised copy only feeds the weight gradients
+          QuantOut out{p.act_row_data, p.act_row_scale, p.act_col_data, p.act_col_scale, width, p.pad_blocks, pb, row_in_cta};
 #pragma unroll
           for (int b = 0; b < 2; ++b) {
-            // along the row: one scale for this thread's 32 columns
-            float amax = 0.f;
+            float act[32];
 #pragma unroll
-            for (int c = 0; c < 32; ++c) amax = fmaxf(amax, fabsf(__uint_as_float(v[b][c])));
-            const uint32_t e_row = mxq::block_exponent(amax);
-            const float inv_row = mxq::inverse_scale(e_row);
-            uint32_t q_row[8], q_col[8];
-            uint32_t my_col_scale = 127u;
+            for (int c = 0; c < 32; ++c) act[c] = __uint_as_float(v[b][c]);
+            quantise_chunk(act, out, acol0 + 32 * b, lane, my_stage);
+          }
+        }
+      } else if constexpr (FUSED == 2) {
+        // acc = dAct. With the saved U = [gate | up] of the same rows: dU = [dgate | dup], rounded to BF16 and
+        // quantised along both axes, 32 columns at a time; dAct itself is stored only when the caller wants it.
+        const int block = 2 * t.m_idx + static_cast<int>(rank);
+        if (block < t.blocks) {
+          const int inter = p.n;
+          const int pb = t.pad_block0 + block;
+          const long long out_row = t.row0 + static_cast<long long>(block) * 128 + row_in_cta;
+          const bool row_valid = out_row < t.row1;
+          QuantOut out{p.act_row_data, p.act_row_scale, p.act_col_data, p.act_col_scale, 2 * inter, p.pad_blocks, pb, row_in_cta};
+          const __nv_bfloat16* u_row = static_cast<const __nv_bfloat16*>(p.aux) + out_row * 2 * inter;
+          __nv_bfloat16* da_row = p.c != nullptr ? static_cast<__nv_bfloat16*>(p.c) + out_row * inter : nullptr;
 #pragma unroll
-            for (int c = 0; c < 32; c += 4) {
-              uint32_t col_word = 0, row_word = 0;
+          for (int c4 = 0; c4 < 4; ++c4) {
+            const int acol = t.n_idx * PAIR_N + half * 128 + 32 * c4;
+            uint4 graw[4], uraw[4];
 #pragma unroll
-              for (int h2 = 0; h2 < 4; h2 += 2) {
-                const float a0 = __uint_as_float(v[b][c + h2]);
-                const float a1 = __uint_as_float(v[b][c + h2 + 1]);
-                if (want_col) {  // down the rows: one scale per column for the 32 rows this warp holds
-                  const uint32_t e0 = mxq::block_exponent(__uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(fabsf(a0)))));
-                  const uint32_t e1 = mxq::block_exponent(__uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(fabsf(a1)))));
-                  if (lane == c + h2) my_col_scale = e0;
-                  if (lane == c + h2 + 1) my_col_scale = e1;
-                  col_word |= mxq::e4m3x2(a0 * mxq::inverse_scale(e0), a1 * mxq::inverse_scale(e1)) << (8 * h2);
-                }
-                row_word |= mxq::e4m3x2(a0 * inv_row, a1 * inv_row) << (8 * h2);
+            for (int q = 0; q < 4; ++q) {
+              graw[q] = uraw[q] = make_uint4(0, 0, 0, 0);
+              if (row_valid) {
+                graw[q] = ld_nc_16(u_row + acol + 8 * q);
+                uraw[q] = ld_nc_16(u_row + inter + acol + 8 * q);
               }
-              q_col[c >> 2] = col_word;
-              q_row[c >> 2] = row_word;
             }
-            uint8_t* row_dst = p.act_row_data + pad_row * width + acol0 + 32 * b;
-            st_16(row_dst, make_uint4(q_row[0], q_row[1], q_row[2], q_row[3]));
-            st_16(row_dst + 16, make_uint4(q_row[4], q_row[5], q_row[6], q_row[7]));
-            row_atom[mxq::atom_offset(row_in_cta, half * 2 + b)] = static_cast<uint8_t>(e_row);
-            if (want_col) {
-              uint8_t* col_dst = p.act_col_data + pad_row * width + acol0 + 32 * b;
-              st_16(col_dst, make_uint4(q_col[0], q_col[1], q_col[2], q_col[3]));
-              st_16(col_dst + 16, make_uint4(q_col[4], q_col[5], q_col[6], q_col[7]));
-              col_atom[mxq::atom_offset(half * 64 + 32 * b + lane, quarter)] = static_cast<uint8_t>(my_col_scale);
+            float dgate[32], dup[32];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const uint32_t gw[4] = {graw[q].x, graw[q].y, graw[q].z, graw[q].w};
+              const uint32_t uw[4] = {uraw[q].x, uraw[q].y, uraw[q].z, uraw[q].w};
+              uint32_t dw[4];
+#pragma unroll
+              for (int w = 0; w < 4; ++w) {
+                const int c = 8 * q + 2 * w;
+                dw[w] = pack_bf16x2(__uint_as_float(v[c4][c]), __uint_as_float(v[c4][c + 1]));
+                const float2 d = unpack_bf16x2(dw[w]);  // dAct as a reader of the BF16 tensor would see it
+                const float2 g = unpack_bf16x2(gw[w]);
+                const float2 u = unpack_bf16x2(uw[w]);
+                const float s0 = mxq::sigmoid_f(g.x);
+                const float s1 = mxq::sigmoid_f(g.y);
+                dgate[c] = bf16_round(d.x * u.x * s0 * (1.0f + g.x * (1.0f - s0)));
+                dgate[c + 1] = bf16_round(d.y * u.y * s1 * (1.0f + g.y * (1.0f - s1)));
+                dup[c] = bf16_round(d.x * (g.x * s0));
+                dup[c + 1] = bf16_round(d.y * (g.y * s1));
+              }
+              if (da_row != nullptr && row_valid) st_16(da_row + acol + 8 * q, make_uint4(dw[0], dw[1], dw[2], dw[3]));
             }
+            quantise_chunk(dgate, out, acol, lane, my_stage);
+            quantise_chunk(dup, out, inter + acol, lane, my_stage);
           }
         }
       } else if (p.mode == HMC_GEMM_RAGGED_K) {
@@ -469,11 +558,11 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   }
 }
 
-template <int A_MAJOR, int B_MAJOR, bool SWIGLU>
+template <int A_MAJOR, int B_MAJOR, int FUSED>
 int launch_impl(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& tsa,
                 const CUtensorMap& tsb, const Params& p, int grid, cudaStream_t stream) {
   static PerDeviceFlag configured{};
-  auto kernel = mx_gemm_pair_kernel<A_MAJOR, B_MAJOR, SWIGLU>;
+  auto kernel = mx_gemm_pair_kernel<A_MAJOR, B_MAJOR, FUSED>;
   if (int rc = allow_dynamic_smem(kernel, PAIR_SMEM_BYTES, configured)) return rc;
   kernel<<<grid, NUM_THREADS, PAIR_SMEM_BYTES, stream>>>(ta, tb, tc, tsa, tsb, p);
   HMC_LAUNCH_OK();
@@ -491,12 +580,13 @@ int launch_mx_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUte
   if (p.mode == HMC_GEMM_RAGGED_K) {
     const long long tiles = static_cast<long long>(p.groups) * p.m_tiles * p.n_tiles;
     if (2 * tiles < grid) grid = static_cast<int>(2 * tiles);
-    return launch_impl<HMC_MAJOR_MN, HMC_MAJOR_MN, false>(ta, tb, tc, tsa, tsb, p, grid, stream);
+    return launch_impl<HMC_MAJOR_MN, HMC_MAJOR_MN, 0>(ta, tb, tc, tsa, tsb, p, grid, stream);
   }
   (void)a_major;
-  if (p.epilogue == HMC_EPI_SWIGLU_MXQ) return launch_impl<HMC_MAJOR_K, HMC_MAJOR_MN, true>(ta, tb, tc, tsa, tsb, p, grid, stream);
-  if (b_major == HMC_MAJOR_MN) return launch_impl<HMC_MAJOR_K, HMC_MAJOR_MN, false>(ta, tb, tc, tsa, tsb, p, grid, stream);
-  return launch_impl<HMC_MAJOR_K, HMC_MAJOR_K, false>(ta, tb, tc, tsa, tsb, p, grid, stream);
+  if (p.epilogue == HMC_EPI_SWIGLU_MXQ) return launch_impl<HMC_MAJOR_K, HMC_MAJOR_MN, 1>(ta, tb, tc, tsa, tsb, p, grid, stream);
+  if (p.epilogue == HMC_EPI_SWIGLU_GRAD_MXQ) return launch_impl<HMC_MAJOR_K, HMC_MAJOR_K, 2>(ta, tb, tc, tsa, tsb, p, grid, stream);
+  if (b_major == HMC_MAJOR_MN) return launch_impl<HMC_MAJOR_K, HMC_MAJOR_MN, 0>(ta, tb, tc, tsa, tsb, p, grid, stream);
+  return launch_impl<HMC_MAJOR_K, HMC_MAJOR_K, 0>(ta, tb, tc, tsa, tsb, p, grid, stream);
 }
 
 }  // namespace mx

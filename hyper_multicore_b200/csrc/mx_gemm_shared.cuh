@@ -50,6 +50,7 @@ struct Params {
   uint8_t* act_row_scale;
   uint8_t* act_col_data;
   uint8_t* act_col_scale;
+  const void* aux;  // HMC_EPI_SWIGLU_GRAD_MXQ: the saved U [rows, 2n] of the same rows (the outputs above are dU, width 2n)
 };
 
 struct Tile {

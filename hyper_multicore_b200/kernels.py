@@ -12,7 +12,7 @@ import os
 import torch
 
 from . import _lib
-from ._lib import (HMC_EPI_STORE_BF16, HMC_EPI_STORE_F32, HMC_EPI_SWIGLU, HMC_EPI_SWIGLU_GRAD, HMC_EPI_SWIGLU_MXQ,
+from ._lib import (HMC_EPI_STORE_BF16, HMC_EPI_STORE_F32, HMC_EPI_SWIGLU, HMC_EPI_SWIGLU_GRAD, HMC_EPI_SWIGLU_GRAD_MXQ, HMC_EPI_SWIGLU_MXQ,
                    HMC_GEMM_RAGGED_K, HMC_GEMM_RAGGED_M, HMC_MAJOR_K, HMC_MAJOR_MN, GroupedGemmArgs)
 
 
@@ -548,12 +548,14 @@ def mx_gemm_combine_units(n: int) -> int:
 
 def mx_gemm(a, a_scale, b, b_scale, c, group_ends, *, mode, rows, pad_blocks, n, k=0, m=0,
             b_major=HMC_MAJOR_MN, epilogue=HMC_EPI_STORE_BF16, status=None, max_ctas=0, combine=None,
-            tile_mode=0, act: "MxActivations | None" = None) -> None:
+            tile_mode=0, act: "MxActivations | None" = None, aux=None) -> None:
     """Block-scaled FP8 grouped GEMM; see ``hmc_mx_gemm_args`` for the operand layouts. ``combine`` as in
     ``grouped_gemm``: the rows leave the epilogue for their source ranks and ``c`` may be None. ``tile_mode``:
     0 = 256 x 256 CTA-pair tiles where the shape allows, 1 = 128 x 128 tiles, 2 = pairs or an error.
     ``epilogue=HMC_EPI_SWIGLU_MXQ``: ``c`` = U [rows, n] and ``act`` (an ``MxActivations`` of width n / 2 with both
-    axes) receives the quantised bf16(silu(gate) * up)."""
+    axes) receives the quantised bf16(silu(gate) * up). ``epilogue=HMC_EPI_SWIGLU_GRAD_MXQ``: the accumulator is
+    dAct [rows, n], ``aux`` = the saved U [rows, 2n], ``act`` (width 2n) receives the quantised dU and ``c`` (dAct)
+    may be None."""
     device = _require_cuda(a, a_scale, b, b_scale, c, group_ends, status)
     args = _lib.MxGemmArgs()
     args.mode, args.b_major, args.epilogue = mode, b_major, epilogue
@@ -566,7 +568,8 @@ def mx_gemm(a, a_scale, b, b_scale, c, group_ends, *, mode, rows, pad_blocks, n,
     args.status = _lib.ptr(status)
     if act is not None:
         args.act_row_data, args.act_row_scale = act.row_data.data_ptr(), act.row_scale.data_ptr()
-        args.act_col_data, args.act_col_scale = act.col_data.data_ptr(), act.col_scale.data_ptr()
+        args.act_col_data, args.act_col_scale = _lib.ptr(act.col_data), _lib.ptr(act.col_scale)
+    args.aux = _lib.ptr(aux)
     fused = None
     if combine is not None:
         fused = _combine_struct(combine)

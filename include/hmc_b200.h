@@ -84,6 +84,9 @@ int hmc_profile_dump(int32_t* kinds, double* start_ms, double* duration_ms, int 
 #define HMC_EPI_STORE_F32 1   /* FP32 output (partial weight gradients, mHC projection) */
 #define HMC_EPI_SWIGLU 2      /* B has 2n columns [gate | up]; c = U[rows, 2n], aux = Act[rows, n] */
 #define HMC_EPI_SWIGLU_GRAD 3 /* acc = dAct[rows, n]; aux = U[rows, 2n] (input); c = dU[rows, 2n] */
+#define HMC_EPI_SWIGLU_GRAD_MXQ 5 /* hmc_mx_gemm only: acc = dAct[rows, n]; aux = U[rows, 2n]; dU = [dgate | dup] leaves the
+                                    epilogue quantised along both axes (hmc_mx_quant's HMC_MXQ_SWIGLU_GRAD); c = dAct is
+                                    optional */
 #define HMC_EPI_SWIGLU_MXQ 4  /* hmc_mx_gemm only: c = U[rows, n] with n = 2 * width, and bf16(silu(gate) * up) leaves the
                                  epilogue quantised along both axes (what hmc_mx_quant's HMC_MXQ_SWIGLU would make of U) */
 #define HMC_CLAMP_NONE 0
@@ -185,7 +188,8 @@ int64_t hmc_grouped_gemm_combine_units(int64_t n);
 typedef struct hmc_mx_gemm_args {
   int32_t mode;     /* HMC_GEMM_RAGGED_M or HMC_GEMM_RAGGED_K */
   int32_t b_major;  /* RAGGED_M: MN = b[groups, k, n], K = b[groups, n, k]. RAGGED_K: ignored */
-  int32_t epilogue; /* HMC_EPI_STORE_BF16, HMC_EPI_STORE_F32 (RAGGED_K only) or HMC_EPI_SWIGLU_MXQ (RAGGED_M only) */
+  int32_t epilogue; /* HMC_EPI_STORE_BF16, HMC_EPI_STORE_F32 (RAGGED_K only), HMC_EPI_SWIGLU_MXQ or
+                       HMC_EPI_SWIGLU_GRAD_MXQ (RAGGED_M only) */
   int32_t groups;
   int32_t max_ctas;
   int32_t tile_mode;  /* HMC_TILE_AUTO, _SINGLE (128 x 128 tiles) or _PAIR (256 x 256 CTA-pair tiles; needs n % 256 == 0,
@@ -211,6 +215,9 @@ typedef struct hmc_mx_gemm_args {
   void* act_row_scale;
   void* act_col_data;
   void* act_col_scale;
+  /* HMC_EPI_SWIGLU_GRAD_MXQ (RAGGED_M, b_major K, CTA-pair tiles): aux = the saved U [rows, 2n] bf16; the four
+   * outputs above receive dU, width = 2n; c (dAct, bf16 [rows, n]) may be NULL. */
+  const void* aux;
 } hmc_mx_gemm_args;
 
 int hmc_mx_gemm(const hmc_mx_gemm_args* args, void* stream);

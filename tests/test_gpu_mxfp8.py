@@ -245,6 +245,49 @@ def test_swiglu_quantising_epilogue_equals_gemm_then_quantiser(cuda_device, coun
     assert torch.equal(col_atoms(got), col_atoms(ref))
 
 
+@pytest.mark.parametrize("counts", [[300, 0, 129, 640, 1, 256], [128], [1000, 385]])
+@pytest.mark.parametrize("want_da", [True, False])
+def test_swiglu_grad_quantising_epilogue_equals_gemm_then_quantiser(cuda_device, counts, want_da):
+    """dA = dY . W2^T with the SwiGLU-grad + dual-axis quantisation in its epilogue gives, bit for bit, the
+    quantised dU = [dgate | dup] of the plain GEMM followed by the stand-alone SwiGLU-grad quantiser, and the
+    same dAct when that is asked for."""
+    from hyper_multicore_b200 import kernels as K
+
+    dev = cuda_device
+    g = torch.Generator().manual_seed(29 + len(counts))
+    experts, rows, hidden, inter = len(counts), sum(counts), 384, 256
+    ends = torch.tensor(counts, dtype=torch.int64).cumsum(0).to(dev)
+    dy = torch.randn(rows, hidden, generator=g).bfloat16().to(dev)
+    u = torch.randn(rows, 2 * inter, generator=g).bfloat16().to(dev)
+    w2 = (torch.randn(experts, inter, hidden, generator=g) * 0.08).bfloat16().to(dev)
+    fields = K.mx_quant_weight(w2)
+    atoms = K.mx_pack_weight_scale(fields["row_scale"], 1, experts, inter, hidden)
+    dyq = K.mx_quant(dy, ends, hidden, want_row=True)
+    status = torch.zeros(4, dtype=torch.int32, device=dev)
+    common = dict(mode=K.HMC_GEMM_RAGGED_M, rows=rows, pad_blocks=dyq.pad_blocks, n=inter, k=hidden, b_major=K.HMC_MAJOR_K,
+                  status=status)
+    da_plain = torch.zeros(rows, inter, dtype=torch.bfloat16, device=dev)
+    K.mx_gemm(dyq.row_data, dyq.row_scale, fields["row_data"], atoms, da_plain, ends, **common)
+    ref = K.mx_quant(da_plain, ends, 2 * inter, kind=K.HMC_MXQ_SWIGLU_GRAD, aux=u, want_row=True, want_col=True)
+    da_fused = torch.zeros_like(da_plain) if want_da else None
+    got = K.MxActivations(rows, experts, 2 * inter, dev, want_row=True, want_col=True)
+    K.mx_gemm(dyq.row_data, dyq.row_scale, fields["row_data"], atoms, da_fused, ends, epilogue=K.HMC_EPI_SWIGLU_GRAD_MXQ,
+              act=got, aux=u, **common)
+    torch.cuda.synchronize()
+    assert int(status[0]) == 0, status.tolist()
+    if want_da:
+        assert torch.equal(da_plain, da_fused)
+    assert da_plain.float().abs().sum() > 0
+    used = sum((c + 127) // 128 for c in counts)
+    assert torch.equal(got.row_data[:used * 128], ref.row_data[:used * 128])
+    assert torch.equal(got.col_data[:used * 128], ref.col_data[:used * 128])
+    width = 2 * inter
+    assert torch.equal(got.row_scale.view(width // 128, got.pad_blocks, 512)[:, :used],
+                       ref.row_scale.view(width // 128, ref.pad_blocks, 512)[:, :used])
+    assert torch.equal(got.col_scale.view(got.pad_blocks, width // 128, 512)[:used],
+                       ref.col_scale.view(ref.pad_blocks, width // 128, 512)[:used])
+
+
 def test_requantised_weights_replace_cached_scale_factors(cuda_device):
     """One module, weights updated in place and re-quantised between calls (an optimiser step): the new
     field tensors tend to land in the memory the old ones just freed, and fresh weights may even get a
