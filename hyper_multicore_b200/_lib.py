@@ -216,7 +216,7 @@ class MxGemmArgs(ctypes.Structure):
         ("a", c_void_p), ("a_scale", c_void_p), ("b", c_void_p), ("b_scale", c_void_p), ("c", c_void_p),
         ("group_ends", c_void_p), ("status", c_void_p), ("combine", c_void_p),
         ("act_row_data", c_void_p), ("act_row_scale", c_void_p), ("act_col_data", c_void_p), ("act_col_scale", c_void_p),
-        ("aux", c_void_p),
+        ("aux", c_void_p), ("skip_flag", c_void_p),
     ]
 
 
@@ -228,7 +228,7 @@ class MxQuantArgs(ctypes.Structure):
         ("rows", c_int64), ("pad_blocks", c_int64), ("width", c_int64),
         ("src", c_void_p), ("aux", c_void_p), ("group_ends", c_void_p),
         ("row_data", c_void_p), ("row_scale", c_void_p), ("col_data", c_void_p), ("col_scale", c_void_p),
-        ("dense", c_void_p),
+        ("dense", c_void_p), ("skip_flag", c_void_p),
     ]
 
 
@@ -303,6 +303,7 @@ class MegaMoeMxfp8Args(ctypes.Structure):
         ("received_rows", c_int64), ("pad_blocks", c_int64), ("dispatch_src_index", c_void_p),
         ("expert_of_row", c_void_p), ("recv_segment_start", c_void_p), ("transport", c_void_p),
         ("saved_combine", c_void_p), ("mapping", c_void_p), ("topk_probs", c_void_p), ("output", c_void_p),
+        ("skip_flag", c_void_p),
     ]
 
 
@@ -324,7 +325,7 @@ class MegaMoeMxfp8GradArgs(ctypes.Structure):
         ("weight_grad_f32", c_int32), ("reserved", c_int32), ("recv_segment_start", c_void_p),
         ("expert_of_row", c_void_p), ("transport", c_void_p), ("grad_output", c_void_p),
         ("saved_combine", c_void_p), ("mapping", c_void_p), ("topk_probs", c_void_p), ("grad_probs", c_void_p),
-        ("grad_hidden", c_void_p),
+        ("grad_hidden", c_void_p), ("skip_flag", c_void_p),
     ]
 
 HMC_MAX_EP = 16
@@ -395,6 +396,7 @@ SIGNATURES: dict[str, tuple] = {
     "hmc_ep_wait": (_I, [_P, _I, c_uint64, _P, _P]),
     "hmc_ep_wait_unless": (_I, [_P, _I, c_uint64, _P, _P, _P]),
     "hmc_route_guard": (_I, [_P, _L, _L, _L, _L, _P, _P, _P, _P]),
+    "hmc_ep_wait_groups_unless": (_I, [_P, _P, _L, ctypes.c_uint64, _P, _P, _P]),
     "hmc_ep_wait_groups": (_I, [_P, _P, _L, c_uint64, _P, _P]),
     "hmc_mega_mhc_workspace_bytes": (_L, [_L, _L]),
     "hmc_mega_mhc_grad_workspace_bytes": (_L, [_L, _L]),

@@ -320,9 +320,10 @@ __global__ void ep_wait_kernel(const int* counter, int expected, unsigned long l
 
 // One thread per group: bounded wait until the group's arrival counter covers its rows.
 __global__ void ep_wait_groups_kernel(const int* counters, const long long* group_ends, int groups,
-                                      unsigned long long budget_ns, int* status) {
+                                      unsigned long long budget_ns, int* status, const int* skip_flag) {
   const int g = blockIdx.x * blockDim.x + threadIdx.x;
   if (g >= groups) return;
+  if (skip_flag != nullptr && *skip_flag != 0) return;  // the call was not admitted: nothing is on its way
   const long long prev = g == 0 ? 0 : group_ends[g - 1];
   const int need = static_cast<int>(group_ends[g] - prev);
   int seen = 0;
@@ -636,14 +637,19 @@ extern "C" int hmc_route_guard(const int32_t* table, int64_t ep, int64_t experts
   return 0;
 }
 
-extern "C" int hmc_ep_wait_groups(const int32_t* counters, const int64_t* group_ends, int64_t groups,
-                                  uint64_t budget_ns, int32_t* status, void* stream_ptr) {
+extern "C" int hmc_ep_wait_groups_unless(const int32_t* counters, const int64_t* group_ends, int64_t groups,
+                                         uint64_t budget_ns, int32_t* status, const int32_t* skip_flag, void* stream_ptr) {
   HMC_REQUIRE(counters != nullptr && group_ends != nullptr && groups > 0 && groups <= HMC_CTRL_MAX_LOCAL_EXPERTS,
               HMC_ERR_INVALID, "hmc_ep_wait_groups: bad arguments");
   ProfileScope profile(HMC_PROFILE_EP, static_cast<cudaStream_t>(stream_ptr));
   ep_wait_groups_kernel<<<static_cast<unsigned>((groups + 127) / 128), 128, 0, static_cast<cudaStream_t>(stream_ptr)>>>(
       counters, reinterpret_cast<const long long*>(group_ends), static_cast<int>(groups),
-      budget_ns ? budget_ns : 10ull * 1000 * 1000 * 1000, status);
+      budget_ns ? budget_ns : 10ull * 1000 * 1000 * 1000, status, skip_flag);
   HMC_LAUNCH_OK();
   return 0;
+}
+
+extern "C" int hmc_ep_wait_groups(const int32_t* counters, const int64_t* group_ends, int64_t groups,
+                                  uint64_t budget_ns, int32_t* status, void* stream_ptr) {
+  return hmc_ep_wait_groups_unless(counters, group_ends, groups, budget_ns, status, nullptr, stream_ptr);
 }

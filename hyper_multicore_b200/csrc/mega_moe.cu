@@ -606,7 +606,8 @@ struct MxExchange {
 int mx_exchange(const hmc_moe_transport& t, const Shape& s, const void* src, const int32_t* src_index,
                 const int32_t* expert_of_row, const int64_t* src_off, const int64_t* target_off,
                 const int64_t* group_list, const int64_t* recv_segment_start, const int64_t* combine_target_off,
-                void* dispatch_buffer, int32_t* ctrl, int32_t* status, cudaStream_t stream, const void** received) {
+                void* dispatch_buffer, int32_t* ctrl, int32_t* status, cudaStream_t stream, const void** received,
+                const int32_t* skip_flag = nullptr) {
   const bool ep1 = t.ep == 1;
   if (ep1) {
     if (src_index == nullptr) {
@@ -632,14 +633,15 @@ int mx_exchange(const hmc_moe_transport& t, const Shape& s, const void* src, con
   }
   HMC_REQUIRE(t.peer_dispatch[t.rank] == dispatch_buffer, HMC_ERR_INVALID,
               "the dispatch buffer must be this rank's entry of transport.peer_dispatch");
-  hmc_ep_dispatch_args d = make_dispatch(t, src, src_index, expert_of_row, src_off, target_off, s, ctrl, status);
+  hmc_ep_dispatch_args d = make_dispatch(t, src, src_index, expert_of_row, src_off, target_off, s, ctrl, status, nullptr,
+                                         skip_flag);
   HMC_TRY(hmc_ep_dispatch(&d, stream));
-  return hmc_ep_wait_groups(ctrl + HMC_CTRL_ARRIVAL, group_list, s.local, t.wait_budget_ns, status, stream);
+  return hmc_ep_wait_groups_unless(ctrl + HMC_CTRL_ARRIVAL, group_list, s.local, t.wait_budget_ns, status, skip_flag, stream);
 }
 
 hmc_mx_quant_args mx_quant_args(int kind, const Shape& s, int64_t pad_blocks, int64_t width, const void* src,
                                 const void* aux, const int64_t* group_list, void* row_data, void* row_scale,
-                                void* col_data, void* col_scale) {
+                                void* col_data, void* col_scale, const int32_t* skip_flag = nullptr) {
   hmc_mx_quant_args q;
   memset(&q, 0, sizeof(q));
   q.kind = kind;
@@ -650,6 +652,7 @@ hmc_mx_quant_args mx_quant_args(int kind, const Shape& s, int64_t pad_blocks, in
   q.src = src;
   q.aux = aux;
   q.group_ends = group_list;
+  q.skip_flag = skip_flag;
   q.row_data = row_data;
   q.row_scale = row_scale;
   q.col_data = col_data;
@@ -659,7 +662,8 @@ hmc_mx_quant_args mx_quant_args(int kind, const Shape& s, int64_t pad_blocks, in
 
 hmc_mx_gemm_args mx_gemm_args(int mode, int b_major, int epilogue, const Shape& s, int64_t pad_blocks, int64_t m,
                               int64_t n, int64_t k, const void* a, const void* a_scale, const void* b,
-                              const void* b_scale, void* c, const int64_t* group_list, int32_t* status) {
+                              const void* b_scale, void* c, const int64_t* group_list, int32_t* status,
+                              const int32_t* skip_flag = nullptr) {
   hmc_mx_gemm_args g;
   memset(&g, 0, sizeof(g));
   g.mode = mode;
@@ -678,6 +682,7 @@ hmc_mx_gemm_args mx_gemm_args(int mode, int b_major, int epilogue, const Shape& 
   g.c = c;
   g.group_ends = group_list;
   g.status = status;
+  g.skip_flag = skip_flag;
   return g;
 }
 
@@ -716,11 +721,11 @@ extern "C" int hmc_mega_moe_mxfp8(const hmc_mega_moe_mxfp8_args* args, void* str
   const void* x_recv = nullptr;
   HMC_TRY(mx_exchange(t, s, a.source_buffer, a.dispatch_src_index, a.expert_of_row, a.dispatch_src_off, a.dispatch_target_off,
                       a.group_list, a.recv_segment_start, a.combine_target_off, a.dispatch_buffer, ctrl, status, stream,
-                      &x_recv));
+                      &x_recv, a.skip_flag));
   hmc_gemm_combine combine;
   if (s.received > 0) {
     hmc_mx_quant_args q = mx_quant_args(HMC_MXQ_PLAIN, s, a.pad_blocks, s.hidden, x_recv, nullptr, a.group_list, a.x_row,
-                                        a.x_scale, a.x_col, a.x_col_scale);
+                                        a.x_scale, a.x_col, a.x_col_scale, a.skip_flag);
     HMC_TRY(hmc_mx_quant(&q, stream));
     // GMM1 quantises bf16(silu(gate) * up) in its own epilogue (U is written once and not read again in this call);
     // HMC_MX_FUSED_SWIGLU=0 keeps the plain GEMM followed by the stand-alone SwiGLU quantiser.
@@ -730,7 +735,7 @@ extern "C" int hmc_mega_moe_mxfp8(const hmc_mega_moe_mxfp8_args* args, void* str
     }();
     hmc_mx_gemm_args g1 = mx_gemm_args(HMC_GEMM_RAGGED_M, HMC_MAJOR_MN, fused_swiglu ? HMC_EPI_SWIGLU_MXQ : HMC_EPI_STORE_BF16, s,
                                        a.pad_blocks, 0, 2 * s.inter, s.hidden, a.x_row, a.x_scale, a.w1_col_data,
-                                       a.w1_col_scale, a.up, a.group_list, status);
+                                       a.w1_col_scale, a.up, a.group_list, status, a.skip_flag);
     if (fused_swiglu) {
       g1.act_row_data = a.a_row;
       g1.act_row_scale = a.a_scale;
@@ -740,12 +745,12 @@ extern "C" int hmc_mega_moe_mxfp8(const hmc_mega_moe_mxfp8_args* args, void* str
     HMC_TRY(hmc_mx_gemm(&g1, stream));
     if (!fused_swiglu) {
       hmc_mx_quant_args qa = mx_quant_args(HMC_MXQ_SWIGLU, s, a.pad_blocks, s.inter, a.up, nullptr, a.group_list, a.a_row,
-                                           a.a_scale, a.a_col, a.a_col_scale);
+                                           a.a_scale, a.a_col, a.a_col_scale, a.skip_flag);
       HMC_TRY(hmc_mx_quant(&qa, stream));
     }
     hmc_mx_gemm_args g2 = mx_gemm_args(HMC_GEMM_RAGGED_M, HMC_MAJOR_MN, HMC_EPI_STORE_BF16, s, a.pad_blocks, 0, s.hidden,
                                        s.inter, a.a_row, a.a_scale, a.w2_col_data, a.w2_col_scale, ep1 ? a.down : nullptr,
-                                       a.group_list, status);
+                                       a.group_list, status, a.skip_flag);
     if (!ep1) {
       combine = make_combine(t, a.recv_segment_start, a.combine_target_off, s.local);
       g2.combine = &combine;
@@ -754,17 +759,19 @@ extern "C" int hmc_mega_moe_mxfp8(const hmc_mega_moe_mxfp8_args* args, void* str
   }
   const void* routed = a.down;
   if (!ep1) {
-    HMC_TRY(hmc_ep_wait(ctrl + HMC_CTRL_COMBINE, static_cast<int32_t>(s.routed * hmc_mx_gemm_combine_units(s.hidden)),
-                        t.wait_budget_ns, status, stream));
+    HMC_TRY(hmc_ep_wait_unless(ctrl + HMC_CTRL_COMBINE, static_cast<int32_t>(s.routed * hmc_mx_gemm_combine_units(s.hidden)),
+                               t.wait_budget_ns, status, a.skip_flag, stream));
     routed = a.routed_buffer;
     if (a.saved_combine != nullptr) {
       HMC_TRY(copies.begin());
-      HMC_TRY(copies.copy(a.saved_combine, a.routed_buffer, static_cast<size_t>(s.routed) * s.hidden * 2));
+      // (a call that does not fit the workspace is a no-op on the device: copy no more than the buffer holds)
+      const int64_t held = s.routed < t.combine_rows_limit ? s.routed : t.combine_rows_limit;
+      HMC_TRY(copies.copy(a.saved_combine, a.routed_buffer, static_cast<size_t>(held) * s.hidden * 2));
     }
   }
   if (a.output != nullptr && s.tokens > 0)
-    HMC_TRY(hmc_moe_unpermute(routed, a.mapping, a.topk_probs, s.tokens, s.top_k, s.hidden,
-                              ep1 ? s.rows : t.combine_rows_limit, a.output, status, stream));
+    HMC_TRY(moe_unpermute_unless(routed, a.mapping, a.topk_probs, s.tokens, s.top_k, s.hidden,
+                                 ep1 ? s.rows : t.combine_rows_limit, a.output, status, a.skip_flag, stream));
   return copies.end();
 }
 

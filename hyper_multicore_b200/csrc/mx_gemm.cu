@@ -390,6 +390,7 @@ extern "C" int hmc_mx_gemm(const hmc_mx_gemm_args* args, void* stream_ptr) {
   p.b_scale = static_cast<const uint8_t*>(a.b_scale);
   p.c = a.c;
   p.status = a.status;
+  p.skip_flag = a.skip_flag;
   p.n = static_cast<int>(a.n);
   p.n_tiles = static_cast<int>(a.n / BN);
   p.n_atoms = p.n_tiles;

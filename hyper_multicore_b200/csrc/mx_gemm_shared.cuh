@@ -50,6 +50,7 @@ struct Params {
   uint8_t* act_row_scale;
   uint8_t* act_col_data;
   uint8_t* act_col_scale;
+  const int* skip_flag;  // non-zero when the launch runs: no tile is processed (the call was not admitted)
   const void* aux;  // HMC_EPI_SWIGLU_GRAD_MXQ: the saved U [rows, 2n] of the same rows (the outputs above are dU, width 2n)
 };
 
@@ -78,7 +79,10 @@ struct TileWalkerT {
   int blocks = 0;
   int tiles_in_group = 0;
 
-  __device__ explicit TileWalkerT(const Params& params) : p(params) { load_group(); }
+  __device__ explicit TileWalkerT(const Params& params) : p(params) {
+    if (p.skip_flag != nullptr && *p.skip_flag != 0) group = p.groups;  // every role sees an empty problem
+    load_group();
+  }
 
   __device__ int row_tiles() const {
     return p.mode == HMC_GEMM_RAGGED_M ? (blocks + BLOCKS_PER_TILE - 1) / BLOCKS_PER_TILE : p.m_tiles;

@@ -35,6 +35,7 @@ struct QuantParams {
   uint8_t* col_data;
   uint8_t* col_scale;
   __nv_bfloat16* dense;
+  const int* skip_flag;
 };
 
 // Where a tile goes: rows [row0, row0 + valid) of the un-padded source are rows [pad_row0, ...) of the padded
@@ -114,6 +115,7 @@ __global__ void __launch_bounds__(THREADS, 2) mx_quant_kernel(const QuantParams 
   extern __shared__ __align__(16) __nv_bfloat16 tile[];  // [TILE][LDB] (two of them for SwiGLU-grad), BF16-exact values
   __shared__ long long s_row0;
   __shared__ int s_valid;
+  if (p.skip_flag != nullptr && *p.skip_flag != 0) return;  // the call was not admitted (hmc_route_guard)
   const int pb = blockIdx.x;
   const int cb = blockIdx.y;
   // Locate the padded block: groups own ceil(rows / 128) consecutive blocks each. All threads fetch the
@@ -361,6 +363,7 @@ extern "C" int hmc_mx_quant(const hmc_mx_quant_args* args, void* stream_ptr) {
   p.col_data = static_cast<uint8_t*>(a.col_data);
   p.col_scale = static_cast<uint8_t*>(a.col_scale);
   p.dense = static_cast<__nv_bfloat16*>(a.dense);
+  p.skip_flag = a.skip_flag;
   const bool grad = a.kind == HMC_MXQ_SWIGLU_GRAD;  // one CTA produces the dgate and the dup tile of its columns
   const int smem = (grad ? 2 : 1) * TILE * LDB * sizeof(__nv_bfloat16);
   // only blocks that can hold rows are launched: ceil(rows / 128) + groups bounds them

@@ -538,12 +538,13 @@ class MegaMoeExperts(torch.nn.Module):
             from ...symm import PeerControl  # pylint: disable=import-outside-toplevel
 
             self._group.control = PeerControl(self._ep_group, self.num_experts, device)  # collective, once
-        # Steady state of a BF16 push group: the operator is queued WITHOUT waiting for the count table. The
-        # route guard decides on the device whether the call fits the live workspace; the table is validated
-        # below, once everything is queued (the first call, pull dispatch and MXFP8 size buffers from the table).
+        # Steady state of a push group: the operator is queued WITHOUT waiting for the count table. The route
+        # guard decides on the device whether the call fits the live workspace; the table is validated below,
+        # once everything is queued (the first call and pull dispatch size buffers from the table; the MXFP8
+        # backend sizes its per-call buffers for the workspace's capacity instead of the rows received).
         workspace = self._workspace
         defer = None
-        if (self._defer_route and self.ep_size > 1 and not self._pull and self._precision == "bf16"
+        if (self._defer_route and self.ep_size > 1 and not self._pull
                 and isinstance(workspace, PeerWorkspace) and self._group.control is not None):
             defer = (workspace.capacity_rows, workspace.routed_rows)
         route = prepare_route(hidden_flat, topk_ids.contiguous(), num_experts=self.num_experts, top_k=self.top_k,
@@ -816,7 +817,8 @@ class MegaMoeExperts(torch.nn.Module):
         routed_out = down_proj if ep1 else torch.empty(max(routed_rows, 1), hid, **bf16)
         out = torch.empty(hidden.shape[0], hid, **bf16)
         launch = self._launch(route, transport, dispatch_src_index=route.source_of_row, pad_blocks=x_q.pad_blocks,
-                              saved_combine=None if ep1 else routed_out, topk_probs=probs, output=out)
+                              saved_combine=None if ep1 else routed_out, topk_probs=probs, output=out,
+                              skip_flag=route.skip_flag)
         buffers = [
             dispatch_buffer, off["dispatch_target_off"], hidden, off["dispatch_src_off"], off["dispatch_size"],
             root1.col_data, off["group_list"], up_proj, act_q.row_data, root2.col_data, off["group_list"], down_proj,

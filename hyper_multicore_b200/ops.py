@@ -421,6 +421,7 @@ def _mx_common(args, launch: MegaMoeLaunch, events, rank_id, ep, expert_num, hid
     args.transport = ctypes.cast(ctypes.pointer(transport), ctypes.c_void_p)
     args.saved_combine = _ptr(launch.saved_combine)
     args.mapping, args.topk_probs = _ptr(launch.mapping), _ptr(launch.topk_probs)
+    args.skip_flag = _ptr(launch.skip_flag)
     return transport  # kept alive by the caller until the native call returns
 
 

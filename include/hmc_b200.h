@@ -218,6 +218,8 @@ typedef struct hmc_mx_gemm_args {
   /* HMC_EPI_SWIGLU_GRAD_MXQ (RAGGED_M, b_major K, CTA-pair tiles): aux = the saved U [rows, 2n] bf16; the four
    * outputs above receive dU, width = 2n; c (dAct, bf16 [rows, n]) may be NULL. */
   const void* aux;
+  const int32_t* skip_flag; /* optional device word: non-zero when the launch runs = the launch does nothing (see
+                               hmc_route_guard) */
 } hmc_mx_gemm_args;
 
 int hmc_mx_gemm(const hmc_mx_gemm_args* args, void* stream);
@@ -241,6 +243,7 @@ typedef struct hmc_mx_quant_args {
   void* col_data;             /* optional out: e4m3 [pad_blocks*128, width], 32-blocks down the rows */
   void* col_scale;            /* atoms [pad_blocks][width/128] */
   void* dense;                /* optional out: bf16 [rows, width] un-padded (the un-quantised result) */
+  const int32_t* skip_flag;   /* optional device word: non-zero when the launch runs = the launch does nothing */
 } hmc_mx_quant_args;
 
 int hmc_mx_quant(const hmc_mx_quant_args* args, void* stream);
@@ -644,6 +647,8 @@ int hmc_ep_combine(const hmc_ep_combine_args* args, void* stream);
 /* Bounded device-side wait until *counter >= expected; on time-out writes HMC_STATUS_TIMEOUT_ARRIVAL. */
 int hmc_ep_wait(const int32_t* counter, int32_t expected, uint64_t budget_ns, int32_t* status, void* stream);
 /* The same wait, skipped when *skip_flag is non-zero (skip_flag may be NULL). */
+int hmc_ep_wait_groups_unless(const int32_t* counters, const int64_t* group_ends, int64_t groups, uint64_t budget_ns,
+                               int32_t* status, const int32_t* skip_flag, void* stream);
 int hmc_ep_wait_unless(const int32_t* counter, int32_t expected, uint64_t budget_ns, int32_t* status,
                        const int32_t* skip_flag, void* stream);
 /* Admission check of one expert-parallel call ON THE DEVICE, so that the host need not wait for the count table
@@ -874,6 +879,7 @@ typedef struct hmc_mega_moe_mxfp8_args {
   const int32_t* mapping;             /* optional epilogue as in hmc_mega_moe_args */
   const float* topk_probs;
   void* output;
+  const int32_t* skip_flag;           /* as in hmc_mega_moe_args: the device-side admission decision of hmc_route_guard */
 } hmc_mega_moe_mxfp8_args;
 
 typedef struct hmc_mega_moe_mxfp8_grad_args {
@@ -926,6 +932,7 @@ typedef struct hmc_mega_moe_mxfp8_grad_args {
   const float* topk_probs;
   float* grad_probs;
   void* grad_hidden;
+  const int32_t* skip_flag;
 } hmc_mega_moe_mxfp8_grad_args;
 
 int hmc_mega_moe(const hmc_mega_moe_args* args, void* stream);
