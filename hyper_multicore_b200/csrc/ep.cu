@@ -60,18 +60,27 @@ ep_dispatch_kernel(const uint4* __restrict__ tokens, const int* __restrict__ sou
                    int ep, int local_experts, long long capacity_rows, PeerTable peers,
                    const int* __restrict__ local_ctrl, int generation, unsigned long long budget_ns,
                    int* __restrict__ status, const float* __restrict__ row_values,
-                   const int* __restrict__ value_index, long long value_plane_offset, const int* __restrict__ skip_flag) {
+                   const int* __restrict__ value_index, long long value_plane_offset, const int* __restrict__ skip_flag,
+                   int rank) {
   __shared__ int seen[HMC_MAX_EP];
   __shared__ int chunk_expert[ROWS_PER_CHUNK];
   __shared__ int failed;
+  __shared__ long long first_chunk;
   if (skip_flag != nullptr && *reinterpret_cast<const volatile int*>(skip_flag) != 0) return;
   if (threadIdx.x < HMC_MAX_EP) seen[threadIdx.x] = -1;
-  if (threadIdx.x == 0) failed = 0;
+  if (threadIdx.x == 0) {
+    failed = 0;
+    // The rows are expert-major, i.e. destination-major, and the grid walks them as one moving window: if every
+    // rank started at row 0, all of them would send to rank 0's experts first, then to rank 1's, ... and one
+    // receiver's link at a time would carry the whole group's traffic. Rank r starts with the rows of rank r + 1.
+    first_chunk = ep > 1 ? dispatch_src_off[((rank + 1) % ep) * local_experts] / ROWS_PER_CHUNK : 0;
+  }
   __syncthreads();
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const long long chunks = (rows + ROWS_PER_CHUNK - 1) / ROWS_PER_CHUNK;
-  for (long long chunk = blockIdx.x; chunk < chunks; chunk += gridDim.x) {
+  for (long long turn = blockIdx.x; turn < chunks; turn += gridDim.x) {
+    const long long chunk = (turn + first_chunk) % chunks;
     const long long j0 = chunk * ROWS_PER_CHUNK;
     const int count = static_cast<int>(min(static_cast<long long>(ROWS_PER_CHUNK), rows - j0));
     if (threadIdx.x < count) {
@@ -524,6 +533,8 @@ extern "C" int hmc_ep_dispatch(const hmc_ep_dispatch_args* args, void* stream_pt
   HMC_REQUIRE(a.local_experts > 0 && a.local_experts <= HMC_CTRL_MAX_LOCAL_EXPERTS, HMC_ERR_LIMIT,
               "hmc_ep_dispatch: local experts must be in [1, %d]", HMC_CTRL_MAX_LOCAL_EXPERTS);
   HMC_REQUIRE(a.rows > 0 && a.rows < (1ll << 31) && a.top_k > 0, HMC_ERR_INVALID, "hmc_ep_dispatch: bad extents");
+  HMC_REQUIRE(a.rank >= 0 && a.rank < a.ep, HMC_ERR_INVALID, "hmc_ep_dispatch: rank %lld outside [0, %lld)", (long long)a.rank,
+              (long long)a.ep);
   HMC_REQUIRE(a.row_values == nullptr || (a.value_plane_offset >= a.capacity_rows * a.hidden * 2 &&
                                           a.value_plane_offset % 4 == 0),
               HMC_ERR_INVALID, "hmc_ep_dispatch: the value plane must lie behind the rows of the receive buffer");
@@ -537,7 +548,7 @@ extern "C" int hmc_ep_dispatch(const hmc_ep_dispatch_args* args, void* stream_pt
       a.rows, static_cast<int>(a.top_k), static_cast<int>(a.hidden / 8), static_cast<int>(a.ep),
       static_cast<int>(a.local_experts), a.capacity_rows, table, a.local_ctrl, a.generation,
       a.budget_ns ? a.budget_ns : 10ull * 1000 * 1000 * 1000, a.status, a.row_values, a.value_index,
-      a.value_plane_offset, a.skip_flag);
+      a.value_plane_offset, a.skip_flag, static_cast<int>(a.rank));
   HMC_LAUNCH_OK();
   return 0;
 }
