@@ -8,6 +8,7 @@
 // torch/csrc/mega_moe_unpermute.cpp:56-65, moe_token_permute_grad.cpp:29-38) and
 // ZeroEmptyExpertGrad (utilities.asc:17-54).
 #include <cooperative_groups.h>
+#include <cuda_bf16.h>
 
 #include "common.cuh"
 
@@ -355,7 +356,11 @@ unpermute_kernel(const uint4* __restrict__ y, const int* __restrict__ mapping, c
   }
   __syncthreads();
   for (int v = threadIdx.x; v < vec_per_row; v += blockDim.x) {
-    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    // Running sums as packed BF16 pairs: a BF16 add rounds the exact sum once, which is what
+    // bf16(float(a) + float(b)) does, and the weighted term is the FP32 product rounded once.
+    __nv_bfloat162 acc[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[j] = __floats2bfloat162_rn(0.f, 0.f);
     for (int k0 = 0; k0 < top_k; k0 += 4) {
       // four rows in flight: the loads do not depend on the running sum
       uint4 q[4];
@@ -372,16 +377,15 @@ unpermute_kernel(const uint4* __restrict__ y, const int* __restrict__ mapping, c
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           const float2 f = unpack_bf16x2(words[j]);
-          acc[2 * j] = bf16_round(acc[2 * j] + bf16_round(f.x * w));
-          acc[2 * j + 1] = bf16_round(acc[2 * j + 1] + bf16_round(f.y * w));
+          acc[j] = __hadd2(acc[j], __floats2bfloat162_rn(f.x * w, f.y * w));
         }
       }
     }
     uint4 o;
-    o.x = pack_bf16x2(acc[0], acc[1]);
-    o.y = pack_bf16x2(acc[2], acc[3]);
-    o.z = pack_bf16x2(acc[4], acc[5]);
-    o.w = pack_bf16x2(acc[6], acc[7]);
+    o.x = *reinterpret_cast<const uint32_t*>(&acc[0]);
+    o.y = *reinterpret_cast<const uint32_t*>(&acc[1]);
+    o.z = *reinterpret_cast<const uint32_t*>(&acc[2]);
+    o.w = *reinterpret_cast<const uint32_t*>(&acc[3]);
     st_cs_16(out + t * vec_per_row + v, o);
   }
 }
@@ -465,7 +469,9 @@ permute_grad_kernel(const uint4* __restrict__ grad_permuted, const int* __restri
   }
   __syncthreads();
   for (int v = threadIdx.x; v < vec_per_row; v += blockDim.x) {
-    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    __nv_bfloat162 acc[4];  // packed BF16 running sums: one rounding of the exact sum per addition
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[j] = __floats2bfloat162_rn(0.f, 0.f);
     for (int k0 = 0; k0 < top_k; k0 += 4) {
       uint4 q[4];  // four rows in flight: the loads do not depend on the running sum
 #pragma unroll
@@ -478,18 +484,15 @@ permute_grad_kernel(const uint4* __restrict__ grad_permuted, const int* __restri
         if (k0 + i >= top_k || order[k0 + i] < 0) continue;
         const uint32_t words[4] = {q[i].x, q[i].y, q[i].z, q[i].w};
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float2 f = unpack_bf16x2(words[j]);
-          acc[2 * j] = bf16_round(acc[2 * j] + f.x);  // the first row passes unchanged: 0 + x is exact
-          acc[2 * j + 1] = bf16_round(acc[2 * j + 1] + f.y);
-        }
+        for (int j = 0; j < 4; ++j)  // the first row passes unchanged: 0 + x is exact
+          acc[j] = __hadd2(acc[j], *reinterpret_cast<const __nv_bfloat162*>(&words[j]));
       }
     }
     uint4 o;
-    o.x = pack_bf16x2(acc[0], acc[1]);
-    o.y = pack_bf16x2(acc[2], acc[3]);
-    o.z = pack_bf16x2(acc[4], acc[5]);
-    o.w = pack_bf16x2(acc[6], acc[7]);
+    o.x = *reinterpret_cast<const uint32_t*>(&acc[0]);
+    o.y = *reinterpret_cast<const uint32_t*>(&acc[1]);
+    o.z = *reinterpret_cast<const uint32_t*>(&acc[2]);
+    o.w = *reinterpret_cast<const uint32_t*>(&acc[3]);
     st_cs_16(grad_tokens + t * vec_per_row + v, o);
   }
 }
