@@ -17,6 +17,8 @@ namespace {
 
 using namespace mxq;
 
+__device__ __forceinline__ __nv_bfloat162 as_bf162(uint32_t v) { return *reinterpret_cast<const __nv_bfloat162*>(&v); }
+
 constexpr int TILE = 128;
 constexpr int LDB = TILE + 8;  // shared-memory row stride in BF16 elements (16-byte rows, conflict-free both ways)
 constexpr int THREADS = 256;
@@ -51,17 +53,17 @@ struct TilePlace {
 // Eight finished (BF16-exact) values of row r, columns out_c0 + c .. + 7: dense copy, shared-memory copy for the
 // column pass, and the row-quantised bytes with their scale. The four threads of a 32-column block are
 // neighbouring lanes, so the block maximum is two shuffles away.
-__device__ __forceinline__ void emit_row_piece(const QuantParams& p, const TilePlace& t, const float (&v)[8], int r, int c,
-                                               __nv_bfloat16* tile) {
+__device__ __forceinline__ void emit_row_piece(const QuantParams& p, const TilePlace& t, const uint4& packed,
+                                               const float (&v)[8], int r, int c, __nv_bfloat16* tile) {
   const int width = p.width;
-  const uint4 packed = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]),
-                                  pack_bf16x2(v[6], v[7]));
   if (p.dense != nullptr && r < t.valid) *reinterpret_cast<uint4*>(p.dense + (t.row0 + r) * width + t.out_c0 + c) = packed;
   if (p.col_data != nullptr) *reinterpret_cast<uint4*>(tile + r * LDB + c) = packed;
   if (p.row_data != nullptr) {
-    float amax = 0.f;
-#pragma unroll
-    for (int q = 0; q < 8; ++q) amax = fmaxf(amax, fabsf(v[q]));
+    // largest magnitude of the eight values, on the packed BF16 pairs (a maximum is exact in any format)
+    const __nv_bfloat162 m01 = __hmax2(__habs2(as_bf162(packed.x)), __habs2(as_bf162(packed.y)));
+    const __nv_bfloat162 m23 = __hmax2(__habs2(as_bf162(packed.z)), __habs2(as_bf162(packed.w)));
+    const float2 pair = __bfloat1622float2(__hmax2(m01, m23));
+    float amax = fmaxf(pair.x, pair.y);
     amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
     amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
     const uint32_t e = block_exponent(amax);
@@ -85,15 +87,14 @@ __device__ __forceinline__ void column_pass(const QuantParams& p, const TilePlac
   const int jb = threadIdx.x >> 6;
   const uint32_t* src = reinterpret_cast<const uint32_t*>(tile + (32 * jb) * LDB + 2 * cp);
   uint32_t w[32];
-  float amax0 = 0.f, amax1 = 0.f;
+  __nv_bfloat162 amax = __floats2bfloat162_rn(0.f, 0.f);  // both columns at once, on the packed pairs
 #pragma unroll
   for (int i = 0; i < 32; ++i) {
     w[i] = src[i * (LDB / 2)];
-    const float2 f = unpack_bf16x2(w[i]);
-    amax0 = fmaxf(amax0, fabsf(f.x));
-    amax1 = fmaxf(amax1, fabsf(f.y));
+    amax = __hmax2(amax, __habs2(as_bf162(w[i])));
   }
-  const uint32_t e0 = block_exponent(amax0), e1 = block_exponent(amax1);
+  const float2 amax_f = __bfloat1622float2(amax);
+  const uint32_t e0 = block_exponent(amax_f.x), e1 = block_exponent(amax_f.y);
   const float inv0 = inverse_scale(e0), inv1 = inverse_scale(e1);
   uint8_t* dst = p.col_data + (t.pad_row0 + 32 * jb) * width + t.out_c0 + 2 * cp;
 #pragma unroll
@@ -225,8 +226,15 @@ __global__ void __launch_bounds__(THREADS, 2) mx_quant_kernel(const QuantParams 
           v_up[2 * q + 1] = bf16_round(d.y * (g.y * s1));
         }
       }
-      emit_row_piece(p, t, v, r, c, tile);
-      if (KIND == HMC_MXQ_SWIGLU_GRAD) emit_row_piece(p, t_up, v_up, r, c, tile_up);
+      // the same eight values as BF16 pairs (the plain variant's input words are exactly that)
+      const uint4 packed = KIND == HMC_MXQ_PLAIN ? ra[j]
+                                                 : make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]),
+                                                              pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]));
+      emit_row_piece(p, t, packed, v, r, c, tile);
+      if (KIND == HMC_MXQ_SWIGLU_GRAD)
+        emit_row_piece(p, t_up, make_uint4(pack_bf16x2(v_up[0], v_up[1]), pack_bf16x2(v_up[2], v_up[3]),
+                                           pack_bf16x2(v_up[4], v_up[5]), pack_bf16x2(v_up[6], v_up[7])),
+                       v_up, r, c, tile_up);
     }
   }
   if (p.col_data != nullptr) {
