@@ -124,30 +124,34 @@ __device__ __forceinline__ void sinkhorn_forward(const float (&logit)[16], float
       den += e[c];
     }
     s[r] = den;
+    const float inv = 1.0f / den;  // one division per normaliser; the four entries take a multiplication each
 #pragma unroll
-    for (int c = 0; c < 4; ++c) m[r * 4 + c] = e[c] / den + eps;
+    for (int c = 0; c < 4; ++c) m[r * 4 + c] = e[c] * inv + eps;
   }
   emit(0, s);
 #pragma unroll
   for (int c = 0; c < 4; ++c) {
     s[c] = m[c] + m[4 + c] + m[8 + c] + m[12 + c] + eps;
+    const float inv = 1.0f / s[c];
 #pragma unroll
-    for (int r = 0; r < 4; ++r) m[r * 4 + c] /= s[c];
+    for (int r = 0; r < 4; ++r) m[r * 4 + c] *= inv;
   }
   emit(1, s);
   for (int it = 1; it < iters; ++it) {
 #pragma unroll
     for (int r = 0; r < 4; ++r) {
       s[r] = m[r * 4] + m[r * 4 + 1] + m[r * 4 + 2] + m[r * 4 + 3] + eps;
+      const float inv = 1.0f / s[r];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) m[r * 4 + c] /= s[r];
+      for (int c = 0; c < 4; ++c) m[r * 4 + c] *= inv;
     }
     emit(2 * it, s);
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
       s[c] = m[c] + m[4 + c] + m[8 + c] + m[12 + c] + eps;
+      const float inv = 1.0f / s[c];
 #pragma unroll
-      for (int r = 0; r < 4; ++r) m[r * 4 + c] /= s[c];
+      for (int r = 0; r < 4; ++r) m[r * 4 + c] *= inv;
     }
     emit(2 * it + 1, s);
   }
@@ -257,9 +261,10 @@ mhc_mapping_grad_kernel(const float* __restrict__ hc_before_norm, const float* _
           float dot = 0.f;
 #pragma unroll
           for (int rr = 0; rr < 4; ++rr) dot += g[rr * 4 + c] * m[rr * 4 + c];
+          const float inv = 1.0f / s[c];
 #pragma unroll
           for (int rr = 0; rr < 4; ++rr) {
-            g[rr * 4 + c] = (g[rr * 4 + c] - dot) / s[c];
+            g[rr * 4 + c] = (g[rr * 4 + c] - dot) * inv;
             m[rr * 4 + c] *= s[c];
           }
         }
@@ -269,9 +274,10 @@ mhc_mapping_grad_kernel(const float* __restrict__ hc_before_norm, const float* _
           float dot = 0.f;
 #pragma unroll
           for (int c = 0; c < 4; ++c) dot += g[rr * 4 + c] * m[rr * 4 + c];
+          const float inv = 1.0f / s[rr];
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
-            g[rr * 4 + c] = (g[rr * 4 + c] - dot) / s[rr];
+            g[rr * 4 + c] = (g[rr * 4 + c] - dot) * inv;
             m[rr * 4 + c] *= s[rr];
           }
         }
