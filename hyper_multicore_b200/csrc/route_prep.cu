@@ -398,43 +398,63 @@ unpermute_grad_kernel(const uint4* __restrict__ y, const uint4* __restrict__ gra
                       const int* __restrict__ mapping, const float* __restrict__ probs, long long tokens,
                       int top_k, int vec_per_row, long long permuted_rows, uint4* __restrict__ grad_permuted,
                       float* __restrict__ grad_probs, int* __restrict__ status) {
-  __shared__ float partial[4];
+  __shared__ float partial[4][4];
   const long long t = blockIdx.x;
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
-  for (int k = 0; k < top_k; ++k) {
-    const int r = mapping[t * top_k + k];
-    const float w = probs[t * top_k + k];
-    float dot = 0.f;
-    if (r >= 0 && r < permuted_rows) {
-      for (int v = threadIdx.x; v < vec_per_row; v += blockDim.x) {
-        const uint4 g = ld_16(grad_out + t * vec_per_row + v);
-        const uint32_t gw[4] = {g.x, g.y, g.z, g.w};
-        uint32_t ow[4];
-        float2 yf[4];
-        if (y != nullptr) {
-          const uint4 q = ld_nc_16(y + static_cast<long long>(r) * vec_per_row + v);
-          yf[0] = unpack_bf16x2(q.x);
-          yf[1] = unpack_bf16x2(q.y);
-          yf[2] = unpack_bf16x2(q.z);
-          yf[3] = unpack_bf16x2(q.w);
+  // Four routes of the token at a time: dOut[t] is read once for the four, their forward rows are in flight
+  // together, and one block reduction serves four dot products.
+  for (int k0 = 0; k0 < top_k; k0 += 4) {
+    int r[4];
+    float w[4];
+    float dot[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      r[i] = -1;
+      w[i] = 0.f;
+      if (k0 + i < top_k) {
+        r[i] = mapping[t * top_k + k0 + i];
+        w[i] = probs[t * top_k + k0 + i];
+        if (r[i] < 0 || r[i] >= permuted_rows) {
+          if (threadIdx.x == 0) report_status(status, HMC_STATUS_BAD_INDEX, static_cast<int>(t), k0 + i, r[i]);
+          r[i] = -1;
         }
+      }
+    }
+    for (int v = threadIdx.x; v < vec_per_row; v += blockDim.x) {
+      const uint4 g = ld_16(grad_out + t * vec_per_row + v);
+      const uint32_t gw[4] = {g.x, g.y, g.z, g.w};
+      uint4 q[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        q[i] = (y != nullptr && r[i] >= 0) ? ld_nc_16(y + static_cast<long long>(r[i]) * vec_per_row + v) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        if (r[i] < 0) continue;
+        const uint32_t yw[4] = {q[i].x, q[i].y, q[i].z, q[i].w};
+        uint32_t ow[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           const float2 gf = unpack_bf16x2(gw[j]);
-          ow[j] = pack_bf16x2(gf.x * w, gf.y * w);
-          if (y != nullptr) dot += gf.x * yf[j].x + gf.y * yf[j].y;
+          ow[j] = pack_bf16x2(gf.x * w[i], gf.y * w[i]);
+          if (y != nullptr) {
+            const float2 yf = unpack_bf16x2(yw[j]);
+            dot[i] += gf.x * yf.x + gf.y * yf.y;
+          }
         }
-        st_cs_16(grad_permuted + static_cast<long long>(r) * vec_per_row + v, make_uint4(ow[0], ow[1], ow[2], ow[3]));
+        st_cs_16(grad_permuted + static_cast<long long>(r[i]) * vec_per_row + v, make_uint4(ow[0], ow[1], ow[2], ow[3]));
       }
-    } else if (threadIdx.x == 0) {
-      report_status(status, HMC_STATUS_BAD_INDEX, static_cast<int>(t), k, r);
     }
     if (grad_probs != nullptr) {
-      dot = warp_sum(dot);
-      if (lane == 0) partial[warp] = dot;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float sum = warp_sum(dot[i]);
+        if (lane == 0) partial[warp][i] = sum;
+      }
       __syncthreads();
-      if (threadIdx.x == 0) grad_probs[t * top_k + k] = partial[0] + partial[1] + partial[2] + partial[3];
+      if (threadIdx.x < 4 && k0 + threadIdx.x < top_k)
+        grad_probs[t * top_k + k0 + threadIdx.x] =
+            partial[0][threadIdx.x] + partial[1][threadIdx.x] + partial[2][threadIdx.x] + partial[3][threadIdx.x];
       __syncthreads();
     }
   }
