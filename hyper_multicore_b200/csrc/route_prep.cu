@@ -335,11 +335,18 @@ unpermute_kernel(const uint4* __restrict__ y, const int* __restrict__ mapping, c
   __shared__ float weight[MAX_TOP_K];
   if (skip_flag != nullptr && *reinterpret_cast<const volatile int*>(skip_flag) != 0) return;  // uniform per launch
   const long long t = blockIdx.x;
+  __shared__ int raw_rows[MAX_TOP_K];
+  __shared__ float raw_weight[MAX_TOP_K];
+  if (threadIdx.x < top_k) {  // one memory latency for all routes of the token
+    raw_rows[threadIdx.x] = mapping[t * top_k + threadIdx.x];
+    raw_weight[threadIdx.x] = probs != nullptr ? probs[t * top_k + threadIdx.x] : 1.0f;
+  }
+  __syncthreads();
   if (threadIdx.x == 0) {
     // insertion sort of the (row, weight) pairs by row; top_k is small
     for (int k = 0; k < top_k; ++k) {
-      int r = mapping[t * top_k + k];
-      float w = probs != nullptr ? probs[t * top_k + k] : 1.0f;
+      int r = raw_rows[k];
+      float w = raw_weight[k];
       if (r < 0 || r >= y_rows) {
         report_status(status, HMC_STATUS_BAD_INDEX, static_cast<int>(t), k, r);
         r = -1;
@@ -471,10 +478,13 @@ permute_grad_kernel(const uint4* __restrict__ grad_permuted, const int* __restri
                     int* __restrict__ status) {
   __shared__ int order[MAX_TOP_K];
   const long long t = blockIdx.x;
+  __shared__ int raw_rows[MAX_TOP_K];
+  if (threadIdx.x < top_k) raw_rows[threadIdx.x] = mapping[t * top_k + threadIdx.x];  // one memory latency for all routes
+  __syncthreads();
   if (threadIdx.x == 0) {
     // insertion sort by descending row; rejected entries (-1) sink to the end
     for (int k = 0; k < top_k; ++k) {
-      int r = mapping[t * top_k + k];
+      int r = raw_rows[k];
       if (r < 0 || r >= rows) {
         report_status(status, HMC_STATUS_BAD_INDEX, static_cast<int>(t), k, r);
         r = -1;
