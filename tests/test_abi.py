@@ -27,6 +27,17 @@ def test_python_binding_covers_the_header():
     assert _declared_symbols() == set(_lib.SIGNATURES)
 
 
+def test_python_constants_equal_the_header_defines():
+    """Every integer ``#define HMC_*`` of the header that the binding names too has the same value there."""
+    header = (ROOT / "include" / "hmc_b200.h").read_text()
+    defines = {name: int(value, 0) for name, value in re.findall(r"^#define\s+(HMC_[A-Z0-9_]+)\s+(-?(?:0x[0-9a-fA-F]+|\d+))\b",
+                                                                header, flags=re.M)}
+    shared = [name for name in defines if isinstance(getattr(_lib, name, None), int)]
+    assert len(shared) >= 15, shared
+    for name in shared:
+        assert getattr(_lib, name) == defines[name], (name, getattr(_lib, name), defines[name])
+
+
 def test_versions_and_error_text():
     lib = _lib.load()
     assert lib.hmc_abi_version() == 1
