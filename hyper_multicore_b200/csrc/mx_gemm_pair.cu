@@ -14,6 +14,12 @@
 // Roles as in the other pair kernels: warp 0 = TMA producer (both CTAs), warp 1 = MMA issuer (leader) and
 // TMEM owner, warps 2..9 = epilogue (both CTAs, each on its own 128 accumulator rows).
 //
+// Two epilogues quantise their own result (template argument FUSED), bit-identical to the stand-alone quantiser
+// run on the stored result: 1 = GMM1, where the leader loads gate columns and the second CTA the up columns of
+// the same activation columns, U leaves as BF16 and bf16(silu(gate) * up) leaves as E4M3 along both axes; 2 = the
+// dA GEMM, which reads the saved U and emits the quantised dU = [dgate | dup] (correct, but slower than the
+// separate quantiser launch: the operator keeps it off).
+//
 // Replaces the reference's MX GMM worker (hyper_multicore/ops/common/mega_moe/adapters/arch35/gmm/
 // mxfp8_worker.h:15-159; layouts NN forward, NT for dA / dX, TN for dW: tasks/gmm_mxfp8.py).
 #include <cuda.h>
