@@ -112,7 +112,7 @@ __device__ __forceinline__ void column_pass(const QuantParams& p, const TilePlac
 // that each variant is straight-line code whose global loads are all issued before the first of them is
 // used. The SwiGLU-grad variant reads dAct, gate and up once and produces both halves of [dgate | dup].
 template <int KIND>
-__global__ void __launch_bounds__(THREADS, 2) mx_quant_kernel(const QuantParams p) {
+__global__ void __launch_bounds__(THREADS, 3) mx_quant_kernel(const QuantParams p) {
   extern __shared__ __align__(16) __nv_bfloat16 tile[];  // [TILE][LDB] (two of them for SwiGLU-grad), BF16-exact values
   __shared__ long long s_row0;
   __shared__ int s_valid;
