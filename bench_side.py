@@ -211,7 +211,7 @@ def measure(workload: str, rank: int, world: int, device, steps: int, warmup: in
         d2h = sum(t.numel() * t.element_size() for t in outs_h)
         t, h, e, k = tokens, GATE["hidden"], GATE["experts"], GATE["top_k"]
         algorithmic_bytes = t * h * 2 + e * h * 4 + t * e * 4 + t * k * 4 + t * k * 8 + e * 4 + t * k * 4
-        kernel_note = "gate_project_promoted_kernel (tcgen05) + gate_route_kernel + sort kernels"
+        kernel_note = "gate_project_promoted_kernel<route> (tcgen05 projection, Route in its epilogue) + sort_routes_fused_kernel"
         dtype = "f32 (bf16 activations, int32/int64 indices)"
     else:
         tokens, hidden = MHC["tokens"], MHC["hidden"]

@@ -364,6 +364,8 @@ SIGNATURES: dict[str, tuple] = {
     "hmc_gate_project_promoted_workspace_bytes": (_L, [_L, _L]),
     "hmc_gate_project_promoted": (_I, [_P, _P, _I, _L, _L, _L, _P, _P, _L, _P, _P]),
     "hmc_gate_route": (_I, [ctypes.POINTER(GateRouteArgs), _P]),
+    "hmc_gate_project_route_supported": (_I, [_L, _I]),
+    "hmc_gate_project_route": (_I, [_P, _P, _I, _L, _P, _P, _L, ctypes.POINTER(GateRouteArgs), _P, _P]),
     "hmc_gate_route_grad": (_I, [ctypes.POINTER(GateRouteGradArgs), _P]),
     "hmc_gate_project": (_I, [_P, _I, _P, _I, _L, _L, _L, _P, _P]),
     "hmc_gate_project_workspace_bytes": (_L, [_L, _L, _L]),

@@ -86,7 +86,7 @@ gate_route_kernel(const float* __restrict__ logits, const float* __restrict__ te
     const int e = lane + 32 * i;
     if (e < experts) {
       score_out[e] = score[i];
-      biased[i] = score[i] + bias[e];
+      biased[i] = __fadd_rn(score[i], bias[e]);  // never contracted with the softmax scaling: the sum torch rounds
     } else {
       biased[i] = NEG_INF;
     }

@@ -14,7 +14,12 @@
 // One CTA per 128 tokens x 64 experts (x K-slice; the two K-slices of a tile form a cluster and the first adds
 // the second's partial sums, a + b, so results repeat bit for bit): warp 0 = TMA producer, warp 1 = MMA issuer and TMEM
 // owner, warps 2..5 = promotion + epilogue (one per TMEM lane quarter).
+//
+// With at most 64 experts an epilogue thread ends up holding the whole logits row of one token, so the ROUTE
+// instance of the kernel goes on to score, bias, select and weigh that token (the work of gate_route_kernel) and
+// the logits are written once and never read back.
 #include <cuda.h>
+#include <math.h>
 
 #include "common.cuh"
 #include "sm100.cuh"
@@ -49,7 +54,107 @@ struct GateParams {
   int k_per_slice; // k-blocks per K-slice (gridDim.z slices)
   float* logits;
   int* status;
+  // ROUTE instance only
+  const float* text_bias;
+  const float* vision_bias;
+  const uint8_t* image_mask;
+  int use_vision_bias;
+  int top_k;
+  int scoring;
+  float scale;
+  float* weights;
+  long long* indices;
+  float* route_scores;
+  float* selected;
+  float* denominator;
 };
+
+// Route of one token whose logits row v[0, experts) sits in the registers of one thread. Every output equals
+// gate_route_kernel's bit for bit: the same elementwise functions, the softmax sum added in that kernel's order
+// (lane l of its warp holds experts l and l + 32, then a butterfly over the lanes), selection by the largest
+// biased score with NaN as +inf and ties to the lower expert.
+__device__ __forceinline__ void route_token(float (&v)[GN], long long token, const GateParams& p) {
+  const int experts = p.experts;
+  if (p.scoring == HMC_SCORE_SOFTMAX) {
+    float m = -INFINITY;
+#pragma unroll
+    for (int c = 0; c < GN; ++c)
+      if (c < experts) m = fmaxf(m, v[c]);
+    float part[32];
+#pragma unroll
+    for (int l = 0; l < 32; ++l) {
+      v[l] = l < experts ? expf(v[l] - m) : 0.f;
+      v[l + 32] = l + 32 < experts ? expf(v[l + 32] - m) : 0.f;
+      part[l] = v[l] + v[l + 32];
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+      for (int l = 0; l < o; ++l) part[l] = part[l] + part[l + o];
+    }
+    const float inv = 1.0f / part[0];
+#pragma unroll
+    for (int c = 0; c < GN; ++c) v[c] *= inv;
+  } else if (p.scoring == HMC_SCORE_SIGMOID) {
+#pragma unroll
+    for (int c = 0; c < GN; ++c) v[c] = 1.0f / (1.0f + expf(-v[c]));
+  } else {
+#pragma unroll
+    for (int c = 0; c < GN; ++c) {
+      const float x = v[c];
+      v[c] = sqrtf(x > 20.0f ? x : log1pf(expf(x)));  // torch softplus(beta = 1, threshold = 20)
+    }
+  }
+
+  float* score_out = p.route_scores + token * experts;
+  if (experts % 4 == 0) {
+#pragma unroll
+    for (int c = 0; c < GN; c += 4)
+      if (c < experts) *reinterpret_cast<float4*>(score_out + c) = make_float4(v[c], v[c + 1], v[c + 2], v[c + 3]);
+  } else {
+#pragma unroll
+    for (int c = 0; c < GN; ++c)
+      if (c < experts) score_out[c] = v[c];
+  }
+
+  const float* bias = (p.use_vision_bias && p.image_mask[token]) ? p.vision_bias : p.text_bias;
+  float biased[GN];
+#pragma unroll
+  for (int c = 0; c < GN; ++c) biased[c] = c < experts ? __fadd_rn(v[c], __ldg(bias + c)) : -INFINITY;
+
+  float* sel_out = p.selected + token * p.top_k;
+  long long* idx_out = p.indices + token * p.top_k;
+  unsigned long long taken = 0;
+  float total = 0.f;
+  for (int k = 0; k < p.top_k; ++k) {
+    float best = -INFINITY;
+    float win = 0.f;
+    int best_idx = 0x7fffffff;
+#pragma unroll
+    for (int c = 0; c < GN; ++c) {
+      if (c < experts && !((taken >> c) & 1ull)) {
+        const float key = isnan(biased[c]) ? INFINITY : biased[c];
+        if (best_idx == 0x7fffffff || key > best) {
+          best = key;
+          best_idx = c;
+          win = v[c];
+        }
+      }
+    }
+    if (best_idx == 0x7fffffff) break;  // top_k <= experts: not reached
+    taken |= 1ull << best_idx;
+    total += win;
+    sel_out[k] = win;
+    idx_out[k] = best_idx;
+  }
+  const float denom = total + 1.0e-20f;
+  p.denominator[token] = denom;
+  for (int k = 0; k < p.top_k; ++k) {
+    float w = sel_out[k];
+    if (p.top_k > 1) w = w / denom;
+    p.weights[token * p.top_k + k] = w * p.scale;
+  }
+}
 
 // FP32 (or BF16) weight [E, H] -> BF16 parts stacked as rows [part * epad + e] of a [parts * epad, H] matrix
 __global__ void gate_split_parts_kernel(const void* __restrict__ w, int w_is_bf16, int experts, int epad, int parts,
@@ -70,6 +175,7 @@ __global__ void gate_split_parts_kernel(const void* __restrict__ w, int w_is_bf1
   }
 }
 
+template <bool ROUTE>
 __global__ void __launch_bounds__(G_THREADS, 1)
 gate_project_promoted_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
                              const GateParams p) {
@@ -270,6 +376,7 @@ gate_project_promoted_kernel(const __grid_constant__ CUtensorMap tm_x, const __g
       for (int c = 0; c < GN; ++c)
         if (e0 + c < p.experts) dst[c] = sum[c];
     }
+    if constexpr (ROUTE) route_token(sum, row, p);  // one column tile: sum[] is the token's whole row
   }
 
   tc_fence_before_sync();
@@ -319,21 +426,23 @@ extern "C" int64_t hmc_gate_project_promoted_workspace_bytes(int64_t hidden, int
   return 3 * epad * hidden * 2;
 }
 
-extern "C" int hmc_gate_project_promoted(const void* x_bf16, const void* w, int w_is_bf16, int64_t tokens,
-                                         int64_t hidden, int64_t experts, float* logits, void* workspace,
-                                         int64_t workspace_bytes, int32_t* status, void* stream_ptr) {
-  using namespace hmc;
-  HMC_REQUIRE(x_bf16 && logits && workspace, HMC_ERR_INVALID, "hmc_gate_project_promoted: null tensor pointer");
+namespace hmc {
+namespace {
+
+// Split the weight (unless w == NULL), then one launch of the projection; `route` adds the Route of every token.
+int gate_promoted_launch(const char* who, const void* x_bf16, const void* w, int w_is_bf16, int64_t tokens,
+                         int64_t hidden, int64_t experts, float* logits, void* workspace, int64_t workspace_bytes,
+                         const hmc_gate_route_args* route, int32_t* status, cudaStream_t stream) {
+  HMC_REQUIRE(x_bf16 && logits && workspace, HMC_ERR_INVALID, "%s: null tensor pointer", who);
   HMC_REQUIRE(tokens > 0 && experts > 0 && hidden > 0 && hidden % 8 == 0, HMC_ERR_INVALID,
-              "hmc_gate_project_promoted: extents must be positive and hidden a multiple of 8");
+              "%s: extents must be positive and hidden a multiple of 8", who);
   HMC_REQUIRE(tokens < (1ll << 31) && hidden < (1ll << 31) && experts <= 65536, HMC_ERR_LIMIT,
-              "hmc_gate_project_promoted: extent too large");
+              "%s: extent too large", who);
   HMC_REQUIRE(workspace_bytes >= hmc_gate_project_promoted_workspace_bytes(hidden, experts), HMC_ERR_INVALID,
-              "hmc_gate_project_promoted: workspace holds %lld bytes, %lld needed", (long long)workspace_bytes,
+              "%s: workspace holds %lld bytes, %lld needed", who, (long long)workspace_bytes,
               (long long)hmc_gate_project_promoted_workspace_bytes(hidden, experts));
   HMC_REQUIRE(aligned16(x_bf16) && aligned16(workspace) && aligned16(logits), HMC_ERR_INVALID,
-              "hmc_gate_project_promoted: 16-byte alignment");
-  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+              "%s: 16-byte alignment", who);
   const int epad = static_cast<int>((experts + GN - 1) / GN * GN);
   const int parts = w_is_bf16 ? 1 : 3;
   __nv_bfloat16* split = static_cast<__nv_bfloat16*>(workspace);
@@ -358,13 +467,32 @@ extern "C" int hmc_gate_project_promoted(const void* x_bf16, const void* w, int 
   p.k_blocks = static_cast<int>((hidden + GK - 1) / GK);
   p.logits = logits;
   p.status = status;
+  if (route != nullptr) {
+    p.text_bias = route->text_bias;
+    p.vision_bias = route->vision_bias;
+    p.image_mask = route->image_mask;
+    p.use_vision_bias = route->use_vision_bias;
+    p.top_k = route->top_k;
+    p.scoring = route->scoring;
+    p.scale = route->scale;
+    p.weights = route->weights;
+    p.indices = reinterpret_cast<long long*>(route->indices);
+    p.route_scores = route->route_scores;
+    p.selected = route->selected;
+    p.denominator = route->denominator;
+  }
   const unsigned m_tiles = static_cast<unsigned>((tokens + GM - 1) / GM);
   const unsigned n_tiles = static_cast<unsigned>(epad / GN);
   // a second K-slice when one slice per tile would leave most SMs idle
   const int slices = (static_cast<long long>(m_tiles) * n_tiles * 2 <= 2ll * sm_count() && p.k_blocks >= 4 * G_PROMOTE) ? 2 : 1;
   p.k_per_slice = ((p.k_blocks + slices - 1) / slices + G_PROMOTE - 1) / G_PROMOTE * G_PROMOTE;
   static PerDeviceFlag configured{};
-  if (int rc = allow_dynamic_smem(gate_project_promoted_kernel, G_SMEM_BYTES, configured)) return rc;
+  static PerDeviceFlag configured_route{};
+  if (route != nullptr) {
+    if (int rc2 = allow_dynamic_smem(gate_project_promoted_kernel<true>, G_SMEM_BYTES, configured_route)) return rc2;
+  } else {
+    if (int rc2 = allow_dynamic_smem(gate_project_promoted_kernel<false>, G_SMEM_BYTES, configured)) return rc2;
+  }
   dim3 grid(m_tiles, n_tiles, static_cast<unsigned>(slices));
   cudaLaunchConfig_t config = {};
   config.gridDim = grid;
@@ -378,7 +506,50 @@ extern "C" int hmc_gate_project_promoted(const void* x_bf16, const void* w, int 
   cluster.val.clusterDim.z = static_cast<unsigned>(slices);  // the K-slices of a tile exchange through shared memory
   config.attrs = &cluster;
   config.numAttrs = 1;
-  HMC_CUDA_OK(cudaLaunchKernelEx(&config, gate_project_promoted_kernel, tx, tw, p));
+  if (route != nullptr)
+    HMC_CUDA_OK(cudaLaunchKernelEx(&config, gate_project_promoted_kernel<true>, tx, tw, p));
+  else
+    HMC_CUDA_OK(cudaLaunchKernelEx(&config, gate_project_promoted_kernel<false>, tx, tw, p));
   HMC_LAUNCH_OK();
   return 0;
+}
+
+}  // namespace
+}  // namespace hmc
+
+extern "C" int hmc_gate_project_promoted(const void* x_bf16, const void* w, int w_is_bf16, int64_t tokens,
+                                         int64_t hidden, int64_t experts, float* logits, void* workspace,
+                                         int64_t workspace_bytes, int32_t* status, void* stream_ptr) {
+  return hmc::gate_promoted_launch("hmc_gate_project_promoted", x_bf16, w, w_is_bf16, tokens, hidden, experts, logits,
+                                   workspace, workspace_bytes, nullptr, status, static_cast<cudaStream_t>(stream_ptr));
+}
+
+extern "C" int hmc_gate_project_route_supported(int64_t experts, int32_t n_group) {
+  return experts >= 1 && experts <= hmc::GN && n_group == 0;
+}
+
+extern "C" int hmc_gate_project_route(const void* x_bf16, const void* w, int w_is_bf16, int64_t hidden, float* logits,
+                                      void* workspace, int64_t workspace_bytes, const hmc_gate_route_args* route,
+                                      int32_t* status, void* stream_ptr) {
+  using namespace hmc;
+  HMC_REQUIRE(route != nullptr, HMC_ERR_INVALID, "hmc_gate_project_route: null route arguments");
+  const hmc_gate_route_args& a = *route;
+  HMC_REQUIRE(hmc_gate_project_route_supported(a.experts, a.n_group), HMC_ERR_LIMIT,
+              "hmc_gate_project_route: needs at most %d experts and no group limit (experts %d, n_group %d)", GN,
+              a.experts, a.n_group);
+  // The argument contract of hmc_gate_route; its logits are the ones this call computes.
+  HMC_REQUIRE(a.tokens > 0, HMC_ERR_INVALID, "hmc_gate_project_route: tokens must be positive, got %lld",
+              (long long)a.tokens);
+  HMC_REQUIRE(a.top_k >= 1 && a.top_k <= a.experts, HMC_ERR_INVALID,
+              "hmc_gate_project_route: top_k must be in [1, experts], got %d", a.top_k);
+  HMC_REQUIRE(isfinite(a.scale), HMC_ERR_INVALID, "hmc_gate_project_route: routed scaling factor must be finite");
+  HMC_REQUIRE(a.scoring >= HMC_SCORE_SQRTSOFTPLUS && a.scoring <= HMC_SCORE_SIGMOID, HMC_ERR_INVALID,
+              "hmc_gate_project_route: unknown scoring function %d", a.scoring);
+  HMC_REQUIRE(a.text_bias && a.weights && a.indices && a.route_scores && a.selected && a.denominator, HMC_ERR_INVALID,
+              "hmc_gate_project_route: null tensor pointer");
+  HMC_REQUIRE(!a.use_vision_bias || (a.vision_bias && a.image_mask), HMC_ERR_INVALID,
+              "hmc_gate_project_route: vision routing needs vision_bias and image_mask");
+  HMC_REQUIRE(aligned16(a.route_scores), HMC_ERR_INVALID, "hmc_gate_project_route: route_scores needs 16-byte alignment");
+  return gate_promoted_launch("hmc_gate_project_route", x_bf16, w, w_is_bf16, a.tokens, hidden, a.experts, logits,
+                              workspace, workspace_bytes, route, status, static_cast<cudaStream_t>(stream_ptr));
 }

@@ -189,26 +189,91 @@ def gate_project(x: torch.Tensor, weight: torch.Tensor, use_tensor_cores: bool |
               x.shape[0], x.shape[1], weight.shape[0], logits.data_ptr(), workspace.data_ptr(), need)
         return logits
     if eligible and use_tensor_cores:
-        need = _lib.load().hmc_gate_project_promoted_workspace_bytes(x.shape[1], weight.shape[0])
-        # The BF16 parts of the weight stay with the weight tensor until it is written to again (its version
-        # counter moves with every in-place update, e.g. an optimiser step).
-        cached = getattr(weight, "_hmc_gate_parts", None)
-        fresh = cached is None or cached[0] != weight._version or cached[1].device != device or cached[1].numel() != need
-        if fresh:
-            cached = (weight._version, torch.empty(need, dtype=torch.uint8, device=device))
-        workspace = cached[1]
+        workspace, fresh, keep = _gate_weight_parts(weight, x.shape[1], device)
         _call("hmc_gate_project_promoted", device, x.data_ptr(), weight.data_ptr() if fresh else None,
               int(weight.dtype == torch.bfloat16), x.shape[0], x.shape[1], weight.shape[0], logits.data_ptr(),
-              workspace.data_ptr(), need, None)
+              workspace.data_ptr(), workspace.numel(), None)
+        keep()
+        return logits
+    _call("hmc_gate_project", device, x.data_ptr(), int(x.dtype == torch.bfloat16), weight.data_ptr(),
+          int(weight.dtype == torch.bfloat16), x.shape[0], x.shape[1], weight.shape[0], logits.data_ptr())
+    return logits
+
+
+def _gate_weight_parts(weight: torch.Tensor, hidden: int, device: torch.device):
+    """Workspace holding the BF16 parts of ``weight``, whether the kernel has to fill it, and a call that keeps it.
+
+    The parts stay with the weight tensor until it is written to again (its version counter moves with every
+    in-place update, e.g. an optimiser step).
+    """
+    need = _lib.load().hmc_gate_project_promoted_workspace_bytes(hidden, weight.shape[0])
+    cached = getattr(weight, "_hmc_gate_parts", None)
+    fresh = cached is None or cached[0] != weight._version or cached[1].device != device or cached[1].numel() != need
+    if fresh:
+        cached = (weight._version, torch.empty(need, dtype=torch.uint8, device=device))
+
+    def keep() -> None:
         if fresh:
             try:
                 weight._hmc_gate_parts = cached
             except (AttributeError, RuntimeError):  # a tensor that takes no attributes: split again next time
                 pass
-        return logits
-    _call("hmc_gate_project", device, x.data_ptr(), int(x.dtype == torch.bfloat16), weight.data_ptr(),
-          int(weight.dtype == torch.bfloat16), x.shape[0], x.shape[1], weight.shape[0], logits.data_ptr())
-    return logits
+
+    return cached[1], fresh, keep
+
+
+def gate_route_fusable(x: torch.Tensor, weight: torch.Tensor, n_group: int = 0) -> bool:
+    """True when projection and Route run as one launch (``gate_project_route``): BF16 hidden states that take
+    the promoted tcgen05 projection, at most 64 experts, no group limit."""
+    if os.environ.get("HMC_GATE_TENSOR_CORES", _GATE_DEFAULT) != "1" or os.environ.get("HMC_GATE_FUSED_ROUTE", "1") != "1":
+        return False
+    if not (x.is_cuda and x.dtype == torch.bfloat16 and x.ndim == 2 and x.shape[1] % 8 == 0 and x.shape[0] >= 128):
+        return False
+    if weight.dtype not in (torch.bfloat16, torch.float32):
+        return False
+    return bool(_lib.load().hmc_gate_project_route_supported(weight.shape[0], n_group))
+
+
+def gate_project_route(x, weight, text_bias, vision_bias, image_mask, use_vision_bias, top_k, scale, scoring):
+    """Projection and Route in one launch; the caller checks ``gate_route_fusable`` first.
+
+    Returns (logits [T, E], weights [T, K], indices [T, K] int64, route_scores [T, E], selected [T, K],
+    denominator [T, 1]), bit for bit what ``gate_project`` followed by ``gate_route_out`` produce.
+    """
+    device = _require_cuda(x, weight, text_bias, vision_bias)
+    x = x.contiguous()
+    weight = weight.contiguous()
+    tokens, experts = x.shape[0], weight.shape[0]
+    f32 = {"dtype": torch.float32, "device": device}
+    logits = torch.empty((tokens, experts), **f32)
+    weights = torch.empty((tokens, top_k), **f32)
+    indices = torch.empty((tokens, top_k), dtype=torch.int64, device=device)
+    scores = torch.empty((tokens, experts), **f32)
+    selected = torch.empty((tokens, top_k), **f32)
+    denominator = torch.empty((tokens, 1), **f32)
+    args = _lib.GateRouteArgs()
+    args.logits = None
+    args.text_bias = text_bias.data_ptr()
+    args.vision_bias = vision_bias.data_ptr()
+    args.image_mask = _lib.ptr(image_mask) if use_vision_bias else None
+    args.use_vision_bias = int(bool(use_vision_bias))
+    args.experts = experts
+    args.top_k = top_k
+    args.scoring = _lib.HMC_SCORE[scoring]
+    args.tokens = tokens
+    args.scale = scale
+    args.weights = weights.data_ptr()
+    args.indices = indices.data_ptr()
+    args.route_scores = scores.data_ptr()
+    args.selected = selected.data_ptr()
+    args.denominator = denominator.data_ptr()
+    args.n_group, args.topk_group = 0, 0
+    workspace, fresh, keep = _gate_weight_parts(weight, x.shape[1], device)
+    _call("hmc_gate_project_route", device, x.data_ptr(), weight.data_ptr() if fresh else None,
+          int(weight.dtype == torch.bfloat16), x.shape[1], logits.data_ptr(), workspace.data_ptr(), workspace.numel(),
+          ctypes.byref(args), None)
+    keep()
+    return logits, weights, indices, scores, selected, denominator
 
 
 def gate_route_out(logits, text_bias, vision_bias, image_mask, use_vision_bias, top_k, scale, scoring,

@@ -84,6 +84,41 @@ class _RouteFunction(torch.autograd.Function):
         return (grad_logits,) + (None,) * 9
 
 
+class _GateFunction(torch.autograd.Function):
+    """Projection and Route as one launch; the backward of ``_RouteFunction`` followed by ``_ProjectFunction``'s."""
+
+    @staticmethod
+    def forward(ctx, hidden, weight, text_bias, vision_bias, image_mask, use_vision_bias, top_k, scale, scoring):  # pylint: disable=arguments-differ
+        ctx.set_materialize_grads(False)
+        logits, weights, indices, scores, selected, denominator = kernels.gate_project_route(
+            hidden, weight, text_bias.detach(), vision_bias.detach(), image_mask, use_vision_bias, top_k, scale, scoring)
+        ctx.save_for_backward(hidden, weight, logits, indices, scores, selected, denominator)
+        ctx.config = (top_k, scale, scoring)
+        ctx.mark_non_differentiable(indices)
+        return logits, weights, indices
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, grad_logits, grad_weights, grad_indices):  # pylint: disable=arguments-differ
+        del grad_indices
+        hidden, weight, logits, indices, scores, selected, denominator = ctx.saved_tensors
+        top_k, scale, scoring = ctx.config
+        total = None
+        if grad_weights is not None:
+            total = torch.empty_like(logits)
+            kernels.gate_route_grad_out(logits, scores, selected, denominator, indices,
+                                        grad_weights.contiguous().float(), top_k, scale, scoring, total)
+        if grad_logits is not None:
+            total = grad_logits if total is None else total + grad_logits
+        grad_hidden = grad_weight = None
+        if total is not None:
+            if ctx.needs_input_grad[0]:
+                grad_hidden = (total @ weight.float()).to(hidden.dtype)
+            if ctx.needs_input_grad[1]:
+                grad_weight = (total.t() @ hidden.float()).to(weight.dtype)
+        return (grad_hidden, grad_weight) + (None,) * 7
+
+
 class MegaGate(torch.nn.Module):
     """Project hidden states and select experts."""
 
@@ -190,17 +225,22 @@ class MegaGate(torch.nn.Module):
         else:
             mask = None
         needs_grad = torch.is_grad_enabled() and (flattened.requires_grad or self.weight.requires_grad)
-        if needs_grad:
-            logits = _ProjectFunction.apply(flattened, self.weight)
-        else:
-            logits = kernels.gate_project(flattened, self.weight)
         text_bias = self.bias.detach().float()
         vision_bias = self.bias_vl.detach().float() if use_vision else text_bias
+        if kernels.gate_route_fusable(flattened, self.weight, self.n_group):
+            # one launch: the projection's epilogue routes the token whose logits it holds
+            if needs_grad:
+                return _GateFunction.apply(flattened, self.weight, text_bias, vision_bias, mask, use_vision, self.top_k,
+                                           self.routed_scaling_factor, self.scoring_func)
+            return kernels.gate_project_route(flattened, self.weight, text_bias, vision_bias, mask, use_vision,
+                                              self.top_k, self.routed_scaling_factor, self.scoring_func)[:3]
         if needs_grad:
+            logits = _ProjectFunction.apply(flattened, self.weight)
             weights, indices = _RouteFunction.apply(logits, text_bias, vision_bias, mask, use_vision, self.top_k,
                                                     self.routed_scaling_factor, self.scoring_func, self.n_group,
                                                     self.topk_group)
         else:
+            logits = kernels.gate_project(flattened, self.weight)
             weights, indices = route(logits, text_bias, vision_bias, mask, use_vision, self.top_k,
                                      self.routed_scaling_factor, self.scoring_func, self.n_group,
                                      self.topk_group)[:2]

@@ -339,6 +339,18 @@ int hmc_gate_project_promoted(const void* x_bf16, const void* w, int w_is_bf16, 
                               int64_t experts, float* logits, void* workspace, int64_t workspace_bytes,
                               int32_t* status, void* stream);
 
+/* The same projection followed, in the same launch, by the Route of every token (MegaGate.forward,
+ * hyper_multicore/modules/mega_gate/module.py:189-227, as one device pass): with at most 64 experts and no group
+ * limit (hmc_gate_project_route_supported) a thread of the projection's epilogue holds a token's whole logits row and
+ * scores, biases, selects and weighs it there. route->logits is ignored - the logits computed here are routed and
+ * also written to `logits`; route->tokens and route->experts give the extents; every output of hmc_gate_route is
+ * produced, bit for bit what hmc_gate_project_promoted followed by hmc_gate_route writes. workspace, w == NULL and
+ * status as for hmc_gate_project_promoted. */
+int hmc_gate_project_route_supported(int64_t experts, int32_t n_group);
+int hmc_gate_project_route(const void* x_bf16, const void* w, int w_is_bf16, int64_t hidden, float* logits,
+                           void* workspace, int64_t workspace_bytes, const hmc_gate_route_args* route, int32_t* status,
+                           void* stream);
+
 /* ------------------------------------------------------------------------------------------
  * MoE route preparation and token (un)permutation.
  * hmc_moe_histogram         : _resolve_counts (hyper_multicore/modules/mega_moe/route.py:186-211)

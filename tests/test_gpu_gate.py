@@ -239,3 +239,90 @@ def test_group_limited_routing(cuda_device, experts, n_group, topk_group, top_k,
     with pytest.raises(ValueError):
         MegaGate(hidden_size=64, num_experts=experts, top_k=top_k, scoring_func=scoring, routed_scaling_factor=1.0,
                  n_group=7, topk_group=1)
+
+
+@pytest.mark.parametrize("scoring", ["sqrtsoftplus", "softmax", "sigmoid"])
+@pytest.mark.parametrize("tokens,experts,top_k,vision,w_dtype", [
+    (1000, 64, 6, True, torch.float32),     # two K-slices per token tile, ragged last tile
+    (20000, 64, 8, False, torch.float32),   # one K-slice
+    (300, 48, 48, True, torch.float32),     # every expert selected, experts not a multiple of 32
+    (129, 20, 1, False, torch.float32),     # top-1: weights are not normalised
+    (4096, 32, 4, True, torch.bfloat16),    # BF16 router weight (one part)
+    (777, 33, 5, True, torch.float32),      # odd expert count: scalar stores
+])
+def test_fused_projection_and_route_equal_the_two_launches_bit_for_bit(cuda_device, scoring, tokens, experts, top_k,
+                                                                       vision, w_dtype):
+    """The projection's epilogue routes the token it holds: all six outputs equal projection-then-Route exactly."""
+    from hyper_multicore_b200 import kernels as K
+
+    torch.manual_seed(tokens + experts)
+    dev = cuda_device
+    x = torch.randn(tokens, 512, device=dev).bfloat16()
+    w = (torch.randn(experts, 512, device=dev) * 0.2).to(w_dtype)
+    bias = torch.empty(experts, device=dev).uniform_(-0.1, 0.1)
+    bias_vl = torch.empty(experts, device=dev).uniform_(-0.1, 0.1)
+    mask = (torch.rand(tokens, device=dev) < 0.3) if vision else None
+    assert K.gate_route_fusable(x, w)
+    fused = K.gate_project_route(x, w, bias, bias_vl if vision else bias, mask, vision, top_k, 2.5, scoring)
+    logits = K.gate_project(x, w)
+    two = _route(K, logits, bias, bias_vl, mask, top_k, 2.5, scoring)
+    torch.cuda.synchronize()
+    assert torch.equal(fused[0], logits)
+    for got, name in zip(fused[1:], ("weights", "indices", "route_scores", "selected", "denominator")):
+        assert torch.equal(got, two[name]), name
+    # and the Route itself against the oracle on the same logits
+    ref = ogate.route_from_logits(logits.cpu(), bias.cpu(), bias_vl.cpu() if vision else None,
+                                  None if mask is None else mask.cpu(), top_k, scoring, 2.5)
+    safe = ogate.topk_margin(ref["biased"], top_k) > 1e-6
+    got_idx, got_w = sorted_sets(fused[2].cpu(), fused[1].cpu())
+    ref_idx, ref_w = sorted_sets(ref["indices"], ref["weights"])
+    assert torch.equal(got_idx[safe], ref_idx[safe])
+    torch.testing.assert_close(got_w[safe], ref_w[safe], rtol=1e-5, atol=1e-6)
+
+
+def test_fused_route_is_limited_to_one_expert_tile_without_groups(cuda_device):
+    from hyper_multicore_b200 import kernels as K
+
+    x = torch.randn(256, 64, device=cuda_device).bfloat16()
+    assert K.gate_route_fusable(x, torch.randn(64, 64, device=cuda_device))
+    assert not K.gate_route_fusable(x, torch.randn(65, 64, device=cuda_device))
+    assert not K.gate_route_fusable(x, torch.randn(64, 64, device=cuda_device), n_group=4)
+    assert not K.gate_route_fusable(x.float(), torch.randn(64, 64, device=cuda_device))
+    assert not K.gate_route_fusable(x[:100], torch.randn(64, 64, device=cuda_device))
+
+
+@pytest.mark.parametrize("scoring", ["sqrtsoftplus", "softmax", "sigmoid"])
+def test_module_gradients_do_not_depend_on_the_fusion(cuda_device, scoring, monkeypatch):
+    """MegaGate with the one-launch forward and with projection and Route apart: same outputs, same gradients."""
+    from hyper_multicore_b200 import MegaGate
+
+    torch.manual_seed(23)
+    gate = MegaGate(hidden_size=256, num_experts=64, top_k=6, scoring_func=scoring, routed_scaling_factor=2.5,
+                    vision_enabled=True, initializer_range=0.2).to(cuda_device)
+    with torch.no_grad():
+        gate.bias.uniform_(-0.1, 0.1)
+        gate.bias_vl.uniform_(-0.1, 0.1)
+    x = torch.randn(2, 192, 256, device=cuda_device).bfloat16()
+    mask = torch.rand(2, 192, device=cuda_device) < 0.3
+    g_w = torch.randn(384, 6, device=cuda_device)
+    g_l = torch.randn(384, 64, device=cuda_device) * 0.1
+    results = []
+    for fused in ("1", "0"):
+        monkeypatch.setenv("HMC_GATE_FUSED_ROUTE", fused)
+        gate.weight.grad = None
+        xd = x.clone().requires_grad_(True)
+        logits, weights, indices = gate(xd, mask)
+        torch.autograd.backward((weights, logits), (g_w, g_l))
+        results.append((logits.detach(), weights.detach(), indices, xd.grad, gate.weight.grad.clone()))
+    one, two = results
+    for a, b in zip(one[:3], two[:3]):
+        assert torch.equal(a, b)
+    torch.testing.assert_close(one[3].float(), two[3].float(), rtol=1e-6, atol=1e-7)
+    torch.testing.assert_close(one[4], two[4], rtol=1e-6, atol=1e-7)
+    # only the weights' gradient, and only the logits'
+    for pick in (0, 1):
+        monkeypatch.setenv("HMC_GATE_FUSED_ROUTE", "1")
+        xd = x.clone().requires_grad_(True)
+        logits, weights, _ = gate(xd, mask)
+        (weights if pick == 0 else logits).backward(g_w if pick == 0 else g_l)
+        assert torch.isfinite(xd.grad.float()).all()
