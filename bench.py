@@ -743,7 +743,8 @@ def side_workload(ctx: Context, workload: str, steps: int, warmup: int, peaks: d
             "tokens_per_s": result["tokens"] / (result["ms_per_step"] * 1e-3),
             "algorithmic_bytes_per_step": result["algorithmic_bytes"], "gbs": gbs, "frac_of_hbm": gbs / peaks["hbm_gbs"],
             "hbm_peak_gbs": peaks["hbm_gbs"], "peak_source": peaks["source"] + " (copy bandwidth)",
-            "stage_ms": result["stage_ms"]}
+            "stage_ms": result["stage_ms"], "launch_mode": result["launch_mode"],
+            "eager_ms_per_step": result["eager_ms_per_step"]}
 
 
 def run_gpu(args) -> None:

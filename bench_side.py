@@ -14,6 +14,7 @@ from __future__ import annotations
 import json
 import os
 import statistics
+import sys
 import time
 from pathlib import Path
 
@@ -199,8 +200,43 @@ def measure(workload: str, rank: int, world: int, device, steps: int, warmup: in
                                                  lambda: kernels.moe_sort_routes(ids, GATE["experts"]))
             return weights, ids, counts, mapping
 
-        def step_resident():
+        def step_eager():
             run(x_d, mask_d)
+
+        def capture_step():
+            """The step's launches as one CUDA graph, replayed per step: the eager step is bound by the host's launch
+            path (two launches of about 25 and 10 us). None when capture is refused or replays differ from eager."""
+            try:
+                eager = run(x_d, mask_d)  # also caches the weight parts and the kernels' launch attributes
+                torch.cuda.synchronize(device)
+                graph = torch.cuda.CUDAGraph()
+                before = _lib.launch_count()
+                with torch.cuda.graph(graph):
+                    captured = run(x_d, mask_d)
+                per_replay = _lib.launch_count() - before
+                for t in captured:
+                    t.zero_()
+                graph.replay()
+                torch.cuda.synchronize(device)
+                if per_replay <= 0 or not all(torch.equal(a, b) for a, b in zip(eager, captured)):
+                    return None
+                return graph, captured, per_replay
+            except Exception as exc:  # pylint: disable=broad-except
+                print(f"[bench] gate: CUDA graph capture refused ({exc}); timing the eager step", file=sys.stderr, flush=True)
+                try:
+                    torch.cuda.synchronize(device)
+                except Exception:  # pylint: disable=broad-except
+                    pass
+                return None
+
+        captured_step = capture_step() if os.environ.get("HMC_BENCH_GATE_GRAPH", "1") == "1" else None
+        if captured_step is not None:
+            graph_launches = captured_step[2]
+
+            def step_resident():
+                captured_step[0].replay()
+        else:
+            step_resident = step_eager
 
         def step_host():
             results = run(pinned[0].to(device, non_blocking=True), pinned[1].to(device, non_blocking=True))
@@ -242,6 +278,8 @@ def measure(workload: str, rank: int, world: int, device, steps: int, warmup: in
 
         def step_resident():
             run(acts_d, grads)
+
+        step_eager = step_resident
 
         def step_host():
             acts = [t.to(device, non_blocking=True).requires_grad_(True) for t in acts_h]
@@ -291,6 +329,10 @@ def measure(workload: str, rank: int, world: int, device, steps: int, warmup: in
         return reduce_max(total), _lib.launch_count() - launches_before
 
     total_ms, launches = timed(step_resident, steps, warmup)
+    eager_ms = None
+    if step_resident is not step_eager:
+        launches = graph_launches * steps  # a replay launches what the capture recorded
+        eager_ms = timed(step_eager, steps, warmup)[0]
     e2e_ms = timed(step_host, steps, 3)[0] if with_e2e else None
 
     collecting[0] = True
@@ -298,13 +340,15 @@ def measure(workload: str, rank: int, world: int, device, steps: int, warmup: in
     for _ in range(profile_steps):
         if flush is not None:
             flush.zero_()
-        step_resident()
+        step_eager()
     barrier()
     collecting[0] = False
     stage_ms = {name: sum(a.elapsed_time(b) for a, b in pairs) / profile_steps for name, pairs in stages.items()}
     return {"tokens": tokens, "ms_per_step": total_ms / steps, "launches": launches,
             "e2e_ms_per_step": e2e_ms / steps if e2e_ms is not None else None, "h2d": h2d, "d2h": d2h,
-            "algorithmic_bytes": algorithmic_bytes, "kernel_note": kernel_note, "dtype": dtype, "stage_ms": stage_ms}
+            "algorithmic_bytes": algorithmic_bytes, "kernel_note": kernel_note, "dtype": dtype, "stage_ms": stage_ms,
+            "launch_mode": "eager" if eager_ms is None else "CUDA graph of the step's launches, replayed per step",
+            "eager_ms_per_step": None if eager_ms is None else eager_ms / steps}
 
 
 def run_gpu(args, workload: str, clock_sampler_cls) -> None:
@@ -356,7 +400,8 @@ def run_gpu(args, workload: str, clock_sampler_cls) -> None:
         "e2e": {"value": world * tokens / (result["e2e_ms_per_step"] * 1e-3), "unit": "tokens/s",
                 "h2d_bytes_per_step": result["h2d"], "d2h_bytes_per_step": result["d2h"],
                 "ms_per_step": result["e2e_ms_per_step"]},
-        "gpu_launches": result["launches"],
+        "gpu_launches": result["launches"], "launch_mode": result["launch_mode"],
+        "eager_ms_per_step": result["eager_ms_per_step"],
         "roofline": {"bound": "hbm", "kernel": result["kernel_note"], "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak, "peak_source": note,
                      "traffic": result["algorithmic_bytes"],

@@ -117,32 +117,53 @@ __device__ __forceinline__ void route_token(float (&v)[GN], long long token, con
       if (c < experts) score_out[c] = v[c];
   }
 
+  // Selection keys: the biased scores as integers in float order (NaN as +inf, -0 as +0), so that one value below
+  // every float - INT_MIN - can mark an expert that is absent or already taken and a pass costs one compare per expert.
   const float* bias = (p.use_vision_bias && p.image_mask[token]) ? p.vision_bias : p.text_bias;
-  float biased[GN];
+  constexpr int GONE = static_cast<int>(0x80000000u);
+  int key[GN];
 #pragma unroll
-  for (int c = 0; c < GN; ++c) biased[c] = c < experts ? __fadd_rn(v[c], __ldg(bias + c)) : -INFINITY;
+  for (int c = 0; c < GN; ++c) {
+    float b = c < experts ? __fadd_rn(v[c], __ldg(bias + c)) : 0.f;
+    b = isnan(b) ? INFINITY : __fadd_rn(b, 0.f);
+    const int bits = __float_as_int(b);
+    key[c] = c < experts ? (bits ^ ((bits >> 31) & 0x7fffffff)) : GONE;
+  }
 
   float* sel_out = p.selected + token * p.top_k;
   long long* idx_out = p.indices + token * p.top_k;
-  unsigned long long taken = 0;
   float total = 0.f;
   for (int k = 0; k < p.top_k; ++k) {
-    float best = -INFINITY;
-    float win = 0.f;
-    int best_idx = 0x7fffffff;
+    // four independent chains over 16 experts each, joined in expert order: the largest key, ties to the lower expert
+    int best[4], best_at[4];
 #pragma unroll
-    for (int c = 0; c < GN; ++c) {
-      if (c < experts && !((taken >> c) & 1ull)) {
-        const float key = isnan(biased[c]) ? INFINITY : biased[c];
-        if (best_idx == 0x7fffffff || key > best) {
-          best = key;
-          best_idx = c;
-          win = v[c];
+    for (int q = 0; q < 4; ++q) {
+      best[q] = GONE;
+      best_at[q] = 0x7fffffff;
+#pragma unroll
+      for (int c = 16 * q; c < 16 * q + 16; ++c) {
+        if (key[c] > best[q]) {
+          best[q] = key[c];
+          best_at[q] = c;
         }
       }
     }
+    int top = best[0], best_idx = best_at[0];
+#pragma unroll
+    for (int q = 1; q < 4; ++q) {
+      if (best[q] > top) {
+        top = best[q];
+        best_idx = best_at[q];
+      }
+    }
     if (best_idx == 0x7fffffff) break;  // top_k <= experts: not reached
-    taken |= 1ull << best_idx;
+    float win = 0.f;
+#pragma unroll
+    for (int c = 0; c < GN; ++c) {
+      const bool hit = c == best_idx;
+      win = hit ? v[c] : win;
+      key[c] = hit ? GONE : key[c];
+    }
     total += win;
     sel_out[k] = win;
     idx_out[k] = best_idx;
