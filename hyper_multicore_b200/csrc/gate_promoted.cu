@@ -177,6 +177,133 @@ __device__ __forceinline__ void route_token(float (&v)[GN], long long token, con
   }
 }
 
+// The same Route with two threads per token, lanes l and l + 16 of a warp: thread `half` holds experts
+// [32 * half, 32 * half + 32) in v[] and the two exchange what the other needs by shuffles, so every phase is half as
+// long. Used when the two K-slices of a tile each finish 64 of its tokens. The whole warp runs every step (`valid`
+// only guards the stores); results are those of route_token bit for bit.
+constexpr int ROUTE_PITCH = GN + 1;             // words per token row staged in shared memory
+constexpr int ROUTE_SMEM_OFFSET = GN * GM * 4;  // behind the K-slice exchange area
+static_assert(ROUTE_SMEM_OFFSET + (GM / 2) * ROUTE_PITCH * 4 <= G_STAGES * G_STAGE_BYTES, "staged rows fit in the idle ring");
+
+__device__ __forceinline__ void route_pair(float (&v)[32], int half, long long token, bool valid, const GateParams& p) {
+  constexpr unsigned FULL = 0xffffffffu;
+  constexpr int GONE = static_cast<int>(0x80000000u);
+  const int experts = p.experts;
+  const int base = 32 * half;
+  if (valid) {
+    float* dst = p.logits + token * experts + base;
+    if (experts % 4 == 0) {
+#pragma unroll
+      for (int i = 0; i < 32; i += 4)
+        if (base + i < experts) *reinterpret_cast<float4*>(dst + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (base + i < experts) dst[i] = v[i];
+    }
+  }
+  if (p.scoring == HMC_SCORE_SOFTMAX) {
+    float m = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < 32; ++i)
+      if (base + i < experts) m = fmaxf(m, v[i]);
+    m = fmaxf(m, __shfl_xor_sync(FULL, m, 16));
+    float part[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      v[i] = base + i < experts ? expf(v[i] - m) : 0.f;
+      part[i] = v[i] + __shfl_xor_sync(FULL, v[i], 16);  // experts i and i + 32, as a lane of gate_route_kernel adds them
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+      for (int l = 0; l < o; ++l) part[l] = part[l] + part[l + o];
+    }
+    const float inv = 1.0f / part[0];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] *= inv;
+  } else if (p.scoring == HMC_SCORE_SIGMOID) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = 1.0f / (1.0f + expf(-v[i]));
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      const float x = v[i];
+      v[i] = sqrtf(x > 20.0f ? x : log1pf(expf(x)));  // torch softplus(beta = 1, threshold = 20)
+    }
+  }
+  if (valid) {
+    float* dst = p.route_scores + token * experts + base;
+    if (experts % 4 == 0) {
+#pragma unroll
+      for (int i = 0; i < 32; i += 4)
+        if (base + i < experts) *reinterpret_cast<float4*>(dst + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (base + i < experts) dst[i] = v[i];
+    }
+  }
+
+  const float* bias = (valid && p.use_vision_bias && p.image_mask[token]) ? p.vision_bias : p.text_bias;
+  int key[32];
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    float b = base + i < experts ? __fadd_rn(v[i], __ldg(bias + base + i)) : 0.f;
+    b = isnan(b) ? INFINITY : __fadd_rn(b, 0.f);
+    const int bits = __float_as_int(b);
+    key[i] = base + i < experts ? (bits ^ ((bits >> 31) & 0x7fffffff)) : GONE;
+  }
+  float total = 0.f;
+  for (int k = 0; k < p.top_k; ++k) {
+    int best = GONE, at = 0x7fffffff, best_hi = GONE, at_hi = 0x7fffffff;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      if (key[i] > best) {
+        best = key[i];
+        at = base + i;
+      }
+      if (key[16 + i] > best_hi) {
+        best_hi = key[16 + i];
+        at_hi = base + 16 + i;
+      }
+    }
+    if (best_hi > best) {
+      best = best_hi;
+      at = at_hi;
+    }
+    const int other = __shfl_xor_sync(FULL, best, 16);
+    const int other_at = __shfl_xor_sync(FULL, at, 16);
+    if (other > best || (other == best && other_at < at)) {
+      best = other;
+      at = other_at;
+    }
+    float win = 0.f;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      const bool hit = base + i == at;
+      win = hit ? v[i] : win;
+      key[i] = hit ? GONE : key[i];
+    }
+    const float other_win = __shfl_xor_sync(FULL, win, 16);
+    if ((at >> 5) != half) win = other_win;
+    total += win;
+    if (valid && half == 0) {
+      p.selected[token * p.top_k + k] = win;
+      p.indices[token * p.top_k + k] = at;
+    }
+  }
+  if (valid && half == 0) {
+    const float denom = total + 1.0e-20f;
+    p.denominator[token] = denom;
+    for (int k = 0; k < p.top_k; ++k) {
+      float w = p.selected[token * p.top_k + k];
+      if (p.top_k > 1) w = w / denom;
+      p.weights[token * p.top_k + k] = w * p.scale;
+    }
+  }
+}
+
 // FP32 (or BF16) weight [E, H] -> BF16 parts stacked as rows [part * epad + e] of a [parts * epad, H] matrix
 __global__ void gate_split_parts_kernel(const void* __restrict__ w, int w_is_bf16, int experts, int epad, int parts,
                                         long long hidden, __nv_bfloat16* __restrict__ split) {
@@ -363,41 +490,75 @@ gate_project_promoted_kernel(const __grid_constant__ CUtensorMap tm_x, const __g
     }
   }
 
-  // Two K-slices are the two CTAs of a cluster: the second hands its partial sums to the first through
-  // distributed shared memory (the pipeline ring is idle by then), which adds them and stores the logits once.
+  // Two K-slices are the two CTAs of a cluster and exchange partial sums through distributed shared memory (the
+  // pipeline ring is idle by then); a result is always slice 0's sum + slice 1's.
   const bool sliced = gridDim.z > 1;
   const uint32_t slice = sliced ? cluster_ctarank() : 0u;
   const long long row = static_cast<long long>(m0) + quarter * 32 + lane;
-  if (sliced) {
+  if (ROUTE && sliced) {
+    // Each slice finishes 64 of the tile's tokens - slice 0 rows 0..63, slice 1 rows 64..127 - and routes them with
+    // two threads per token.
     tc_fence_before_sync();
     __syncthreads();
     cluster_sync_all();  // both CTAs' rings are drained
-    if (warp >= 2 && slice == 1) {
-      const uint32_t peer = map_to_cta(smem_u32(smem), 0);
-      const int r = quarter * 32 + lane;
-#pragma unroll
-      for (int c = 0; c < GN; ++c) st_shared_cluster_f32(peer + static_cast<uint32_t>((c * GM + r) * 4), sum[c]);
-    }
-    cluster_sync_all();
-    if (warp >= 2 && slice == 0) {
-      const float* exchange = reinterpret_cast<const float*>(smem);
-      const int r = quarter * 32 + lane;
-#pragma unroll
-      for (int c = 0; c < GN; ++c) sum[c] += exchange[c * GM + r];
-    }
-  }
-  if (warp >= 2 && slice == 0 && ok && row < p.tokens && nkb > 0) {
-    float* dst = p.logits + row * p.experts + e0;
-    if (p.experts % 4 == 0) {
-#pragma unroll
-      for (int c = 0; c < GN; c += 4)
-        if (e0 + c < p.experts) *reinterpret_cast<float4*>(dst + c) = make_float4(sum[c], sum[c + 1], sum[c + 2], sum[c + 3]);
-    } else {
+    const int r = quarter * 32 + lane;
+    const bool finish_here = (r < GM / 2) == (slice == 0u);
+    if (warp >= 2 && !finish_here) {
+      const uint32_t peer = map_to_cta(smem_u32(smem), slice ^ 1u);
 #pragma unroll
       for (int c = 0; c < GN; ++c)
-        if (e0 + c < p.experts) dst[c] = sum[c];
+        st_shared_cluster_f32(peer + static_cast<uint32_t>((c * (GM / 2) + (r & 63)) * 4), sum[c]);
     }
-    if constexpr (ROUTE) route_token(sum, row, p);  // one column tile: sum[] is the token's whole row
+    cluster_sync_all();
+    float* rows = reinterpret_cast<float*>(smem + ROUTE_SMEM_OFFSET);
+    if (warp >= 2 && finish_here) {
+      const float* exchange = reinterpret_cast<const float*>(smem);
+      float* mine = rows + (r & 63) * ROUTE_PITCH;
+#pragma unroll
+      for (int c = 0; c < GN; ++c) mine[c] = sum[c] + exchange[c * (GM / 2) + (r & 63)];
+    }
+    __syncthreads();
+    if (warp >= 2 && nkb > 0) {
+      const int half = lane >> 4;
+      const int local = quarter * 16 + (lane & 15);
+      const long long token = static_cast<long long>(m0) + static_cast<long long>(slice) * (GM / 2) + local;
+      float v[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = rows[local * ROUTE_PITCH + half * 32 + i];
+      route_pair(v, half, token, token < p.tokens, p);
+    }
+  } else {
+    if (sliced) {
+      tc_fence_before_sync();
+      __syncthreads();
+      cluster_sync_all();  // both CTAs' rings are drained
+      if (warp >= 2 && slice == 1) {
+        const uint32_t peer = map_to_cta(smem_u32(smem), 0);
+        const int r = quarter * 32 + lane;
+#pragma unroll
+        for (int c = 0; c < GN; ++c) st_shared_cluster_f32(peer + static_cast<uint32_t>((c * GM + r) * 4), sum[c]);
+      }
+      cluster_sync_all();
+      if (warp >= 2 && slice == 0) {
+        const float* exchange = reinterpret_cast<const float*>(smem);
+        const int r = quarter * 32 + lane;
+#pragma unroll
+        for (int c = 0; c < GN; ++c) sum[c] += exchange[c * GM + r];
+      }
+    }
+    if (warp >= 2 && slice == 0 && ok && row < p.tokens && nkb > 0) {
+      float* dst = p.logits + row * p.experts + e0;
+      if (p.experts % 4 == 0) {
+#pragma unroll
+        for (int c = 0; c < GN; c += 4)
+          if (e0 + c < p.experts) *reinterpret_cast<float4*>(dst + c) = make_float4(sum[c], sum[c + 1], sum[c + 2], sum[c + 3]);
+      } else {
+#pragma unroll
+        for (int c = 0; c < GN; ++c)
+          if (e0 + c < p.experts) dst[c] = sum[c];
+      }
+      if constexpr (ROUTE) route_token(sum, row, p);  // one column tile: sum[] is the token's whole row
+    }
   }
 
   tc_fence_before_sync();
