@@ -17,7 +17,8 @@
 //
 // With at most 64 experts an epilogue thread ends up holding the whole logits row of one token, so the ROUTE
 // instance of the kernel goes on to score, bias, select and weigh that token (the work of gate_route_kernel) and
-// the logits are written once and never read back.
+// the logits are written once and never read back. Where a tile has two K-slices, each slice finishes 64 of its
+// tokens and routes them with two threads per token (route_pair); otherwise one thread routes its token (route_token).
 #include <cuda.h>
 #include <math.h>
 
