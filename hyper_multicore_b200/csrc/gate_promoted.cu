@@ -45,6 +45,9 @@ constexpr uint32_t G_TMEM_COLS = 512;        // two accumulators of 64 x parts c
 constexpr uint32_t SWIZZLE_128B = 2;
 constexpr uint64_t G_BUDGET_NS = 4ull * 1000 * 1000 * 1000;
 
+// [host-testable begin] From here to the matching end mark the code is plain C++ apart from a handful of intrinsics;
+// tests/test_gate_route_host.py compiles it for the CPU with stand-ins for those and checks the Route against the
+// reference fixtures without a GPU.
 struct GateParams {
   long long tokens;
   int hidden;
@@ -304,6 +307,8 @@ __device__ __forceinline__ void route_pair(float (&v)[32], int half, long long t
     }
   }
 }
+
+// [host-testable end]
 
 // FP32 (or BF16) weight [E, H] -> BF16 parts stacked as rows [part * epad + e] of a [parts * epad, H] matrix
 __global__ void gate_split_parts_kernel(const void* __restrict__ w, int w_is_bf16, int experts, int epad, int parts,
