@@ -229,7 +229,8 @@ def measure(workload: str, rank: int, world: int, device, steps: int, warmup: in
                     pass
                 return None
 
-        captured_step = capture_step() if os.environ.get("HMC_BENCH_GATE_GRAPH", "1") == "1" else None
+        # one rank only: with a process group alive its watchdog thread may touch the device during a capture
+        captured_step = capture_step() if world == 1 and os.environ.get("HMC_BENCH_GATE_GRAPH", "1") == "1" else None
         if captured_step is not None:
             graph_launches = captured_step[2]
 
